@@ -1,0 +1,94 @@
+// Shared declarations of the kernel library: C ABI, error reporting, dtype codes, reductions.
+//
+// Every entry point is `extern "C"`, takes raw device pointers, sizes and a stream, allocates
+// nothing, and returns 0 or a non-zero code after storing a message that mrun_last_error()
+// returns.  Sizes that a kernel cannot take are refused here, never computed wrongly.
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#define MRUN_API extern "C" __attribute__((visibility("default")))
+
+// dtype codes of the C ABI
+enum : int { MRUN_F32 = 0, MRUN_BF16 = 1 };
+
+// Stores a printf-style message for the calling thread and returns a non-zero code.
+int mrun_set_error(const char* fmt, ...);
+
+#define MRUN_REQUIRE(cond, ...)                       \
+    do {                                              \
+        if (!(cond)) return mrun_set_error(__VA_ARGS__); \
+    } while (0)
+
+#define MRUN_CHECK_LAUNCH(name)                                                         \
+    do {                                                                                \
+        cudaError_t err__ = cudaGetLastError();                                         \
+        if (err__ != cudaSuccess)                                                       \
+            return mrun_set_error("%s: launch failed: %s", name, cudaGetErrorString(err__)); \
+    } while (0)
+
+#define MRUN_CHECK_CUDA(call, name)                                                     \
+    do {                                                                                \
+        cudaError_t err__ = (call);                                                     \
+        if (err__ != cudaSuccess)                                                       \
+            return mrun_set_error("%s: %s", name, cudaGetErrorString(err__));           \
+    } while (0)
+
+namespace mrun {
+
+__device__ __forceinline__ float to_float(float v) { return v; }
+__device__ __forceinline__ float to_float(__nv_bfloat16 v) { return __bfloat162float(v); }
+
+template <typename T> __device__ __forceinline__ T from_float(float v);
+template <> __device__ __forceinline__ float from_float<float>(float v) { return v; }
+template <> __device__ __forceinline__ __nv_bfloat16 from_float<__nv_bfloat16>(float v) {
+    return __float2bfloat16_rn(v);
+}
+
+// Sum over a warp in a fixed butterfly order: every lane gets the same bits.
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+    return v;
+}
+
+// Block-wide sum / max for blockDim.x a multiple of 32 (at most 1024).  `scratch` holds 33
+// floats.  The order of additions depends on blockDim.x only, so a row's result does not depend
+// on what else the launch computes.
+__device__ __forceinline__ float block_sum(float v, float* scratch) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
+    v = warp_sum(v);
+    __syncthreads();
+    if (lane == 0) scratch[warp] = v;
+    __syncthreads();
+    if (warp == 0) {
+        float t = lane < nwarps ? scratch[lane] : 0.f;
+        t = warp_sum(t);
+        if (lane == 0) scratch[32] = t;
+    }
+    __syncthreads();
+    return scratch[32];
+}
+__device__ __forceinline__ float block_max(float v, float* scratch) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
+    v = warp_max(v);
+    __syncthreads();
+    if (lane == 0) scratch[warp] = v;
+    __syncthreads();
+    if (warp == 0) {
+        float t = lane < nwarps ? scratch[lane] : -INFINITY;
+        t = warp_max(t);
+        if (lane == 0) scratch[32] = t;
+    }
+    __syncthreads();
+    return scratch[32];
+}
+
+}  // namespace mrun

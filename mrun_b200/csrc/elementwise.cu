@@ -1,0 +1,274 @@
+// Memory-bound kernels of the step: embedding gather, residual-add + RMSNorm, rotation table,
+// per-head QK RMSNorm + rotary + key/value write into pages, gated activation.
+//
+// All arithmetic is 32-bit and each result is rounded once into the activation dtype.  The
+// residual stream itself is kept in 32-bit in both precisions.
+#include "common.cuh"
+
+using namespace mrun;
+
+// ------------------------------------------------------------------------------------------
+// Embedding: out[t, :] = float(table[ids[t], :]).  An id outside [0, vocab) gives a zero row;
+// the host checks ids before the step, this only keeps the kernel inside the table.
+// Reference call site: crates/mrun-engine/src/load.rs:330-335.
+// ------------------------------------------------------------------------------------------
+template <typename TW>
+__global__ void embed_kernel(const TW* __restrict__ table, const int* __restrict__ ids,
+                             float* __restrict__ out, int hidden, int vocab) {
+    const int t = blockIdx.x;
+    const int id = ids[t];
+    const bool ok = id >= 0 && id < vocab;
+    const TW* row = table + (size_t)(ok ? id : 0) * hidden;
+    float* dst = out + (size_t)t * hidden;
+    for (int h = threadIdx.x; h < hidden; h += blockDim.x) dst[h] = ok ? to_float(row[h]) : 0.f;
+}
+
+MRUN_API int mrun_embed(const void* table, int table_dtype, const int* ids, float* out, int tokens,
+                        int hidden, int vocab, cudaStream_t stream) {
+    MRUN_REQUIRE(tokens >= 0 && hidden > 0 && vocab > 0, "embed: bad sizes tokens=%d hidden=%d vocab=%d",
+                 tokens, hidden, vocab);
+    if (tokens == 0) return 0;
+    if (table_dtype == MRUN_F32)
+        embed_kernel<float><<<tokens, 256, 0, stream>>>((const float*)table, ids, out, hidden, vocab);
+    else if (table_dtype == MRUN_BF16)
+        embed_kernel<__nv_bfloat16><<<tokens, 256, 0, stream>>>((const __nv_bfloat16*)table, ids, out,
+                                                                 hidden, vocab);
+    else
+        return mrun_set_error("embed: unknown dtype code %d", table_dtype);
+    MRUN_CHECK_LAUNCH("embed");
+    return 0;
+}
+
+// ------------------------------------------------------------------------------------------
+// Residual add + RMSNorm.
+//   v = resid[src] + delta[src]   (delta may be null)
+//   if rows == null: resid[src] = v            (the stream advances)
+//   out[r] = v * rsqrt(mean(v^2) + eps) * weight
+// With `rows` the kernel reads row rows[r] and leaves the stream untouched (final norm at the
+// wanted positions only).  eps is added to the mean of squares
+// (crates/mrun-engine/src/models/gated_delta.rs:11-13 states the form).
+// One block of 256 threads per row whatever the batch, so the order of additions is fixed.
+// ------------------------------------------------------------------------------------------
+template <typename TA>
+__global__ void add_rmsnorm_kernel(float* __restrict__ resid, const TA* __restrict__ delta,
+                                   const float* __restrict__ weight, float eps, TA* __restrict__ out,
+                                   const int* __restrict__ rows, int hidden) {
+    extern __shared__ float row_buf[];
+    __shared__ float scratch[33];
+    const int r = blockIdx.x;
+    const size_t src = (size_t)(rows ? rows[r] : r) * hidden;
+    float ss = 0.f;
+    for (int h = threadIdx.x; h < hidden; h += blockDim.x) {
+        float v = resid[src + h];
+        if (delta) v += to_float(delta[src + h]);
+        row_buf[h] = v;
+        ss += v * v;
+    }
+    ss = block_sum(ss, scratch);
+    const float inv = rsqrtf(ss / (float)hidden + eps);
+    TA* dst = out + (size_t)r * hidden;
+    for (int h = threadIdx.x; h < hidden; h += blockDim.x) {
+        const float v = row_buf[h];
+        if (!rows && delta) resid[src + h] = v;
+        dst[h] = from_float<TA>(v * inv * weight[h]);
+    }
+}
+
+MRUN_API int mrun_add_rmsnorm(float* resid, const void* delta, const float* weight, float eps, void* out,
+                              int act_dtype, const int* rows, int n_rows, int hidden,
+                              cudaStream_t stream) {
+    MRUN_REQUIRE(n_rows >= 0 && hidden > 0, "add_rmsnorm: bad sizes rows=%d hidden=%d", n_rows, hidden);
+    const size_t smem = (size_t)hidden * sizeof(float);
+    MRUN_REQUIRE(smem <= 200 * 1024, "add_rmsnorm: hidden=%d exceeds the supported 51200", hidden);
+    if (n_rows == 0) return 0;
+    if (act_dtype == MRUN_F32) {
+        if (smem > 48 * 1024)
+            MRUN_CHECK_CUDA(cudaFuncSetAttribute(add_rmsnorm_kernel<float>,
+                                                 cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem),
+                            "add_rmsnorm");
+        add_rmsnorm_kernel<float><<<n_rows, 256, smem, stream>>>(resid, (const float*)delta, weight, eps,
+                                                                 (float*)out, rows, hidden);
+    } else if (act_dtype == MRUN_BF16) {
+        if (smem > 48 * 1024)
+            MRUN_CHECK_CUDA(cudaFuncSetAttribute(add_rmsnorm_kernel<__nv_bfloat16>,
+                                                 cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem),
+                            "add_rmsnorm");
+        add_rmsnorm_kernel<__nv_bfloat16><<<n_rows, 256, smem, stream>>>(
+            resid, (const __nv_bfloat16*)delta, weight, eps, (__nv_bfloat16*)out, rows, hidden);
+    } else {
+        return mrun_set_error("add_rmsnorm: unknown dtype code %d", act_dtype);
+    }
+    MRUN_CHECK_LAUNCH("add_rmsnorm");
+    return 0;
+}
+
+// ------------------------------------------------------------------------------------------
+// Rotation table: out[t, j] = (cos a, sin a), a = position[t] * inv_freq[j], the product and the
+// functions in 64-bit, rounded once (the reference's explicit form computes the angle in
+// 64-bit too, crates/mrun-engine/src/models/common.rs:264-270).  A negative position (padding)
+// gives (1, 0).
+// ------------------------------------------------------------------------------------------
+__global__ void rotary_table_kernel(const int* __restrict__ positions, const double* __restrict__ inv_freq,
+                                    float2* __restrict__ out, int tokens, int half) {
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= tokens * half) return;
+    const int t = i / half, j = i - t * half;
+    const int p = positions[t];
+    if (p < 0) {
+        out[i] = make_float2(1.f, 0.f);
+        return;
+    }
+    double s, c;
+    sincos((double)p * inv_freq[j], &s, &c);
+    out[i] = make_float2((float)c, (float)s);
+}
+
+MRUN_API int mrun_rotary_table(const int* positions, const double* inv_freq, float* out, int tokens,
+                               int half, cudaStream_t stream) {
+    MRUN_REQUIRE(tokens >= 0 && half > 0, "rotary_table: bad sizes tokens=%d half=%d", tokens, half);
+    if (tokens == 0) return 0;
+    const int n = tokens * half;
+    rotary_table_kernel<<<(n + 255) / 256, 256, 0, stream>>>(positions, inv_freq, (float2*)out, tokens, half);
+    MRUN_CHECK_LAUNCH("rotary_table");
+    return 0;
+}
+
+// ------------------------------------------------------------------------------------------
+// Per-head RMSNorm of q and k, rotation of q and k, write of k and v into pages.
+//   qkv: [tokens, (heads + 2 kv_heads) * head_dim], q heads first, then k heads, then v heads.
+//   q is normed and rotated in place.  k (normed, rotated) and v (as is) go to
+//   cache[page, kv_head, offset, :] with page * page_size + offset = slots[t]; a negative slot
+//   skips the write (padding token, or a layer that only reads a cache).
+// Order of operations: norm before rotation, v untouched
+// (crates/mrun-engine/src/models/common.rs:183,194-198); pairing (j, j + rotary_dim/2)
+// (crates/mrun-engine/src/models/common.rs:221,271-280).
+// One warp per (token, head); the head's vector is staged in shared memory in 32-bit.
+// ------------------------------------------------------------------------------------------
+template <typename TA>
+__global__ void qk_norm_rope_cache_kernel(TA* __restrict__ qkv, const float* __restrict__ q_weight,
+                                          const float* __restrict__ k_weight, float eps,
+                                          const float2* __restrict__ rot, int rotary_dim,
+                                          const int* __restrict__ slots, TA* __restrict__ k_cache,
+                                          TA* __restrict__ v_cache, int tokens, int heads, int kv_heads,
+                                          int head_dim, int page_size) {
+    extern __shared__ float vec_buf[];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int per_token = heads + 2 * kv_heads;
+    const long item = (long)blockIdx.x * (blockDim.x >> 5) + warp;
+    if (item >= (long)tokens * per_token) return;
+    const int t = (int)(item / per_token), slot_head = (int)(item - (long)t * per_token);
+    float* vec = vec_buf + warp * head_dim;
+    TA* src = qkv + ((size_t)t * per_token + slot_head) * head_dim;
+
+    const bool is_q = slot_head < heads;
+    const bool is_k = !is_q && slot_head < heads + kv_heads;
+    const int kv_head = is_q ? 0 : (is_k ? slot_head - heads : slot_head - heads - kv_heads);
+    const int slot = slots ? slots[t] : -1;
+    if (!is_q && slot < 0) return;
+
+    TA* dst;
+    if (is_q) {
+        dst = src;
+    } else {
+        const int page = slot / page_size, off = slot - page * page_size;
+        TA* cache = is_k ? k_cache : v_cache;
+        dst = cache + (((size_t)page * kv_heads + kv_head) * page_size + off) * head_dim;
+    }
+
+    if (!is_q && !is_k) {  // v: plain copy
+        for (int e = lane; e < head_dim; e += 32) dst[e] = src[e];
+        return;
+    }
+
+    float ss = 0.f;
+    for (int e = lane; e < head_dim; e += 32) {
+        const float v = to_float(src[e]);
+        vec[e] = v;
+        ss += v * v;
+    }
+    const float* weight = is_q ? q_weight : k_weight;
+    if (weight) {
+        ss = warp_sum(ss);
+        const float inv = rsqrtf(ss / (float)head_dim + eps);
+        __syncwarp();
+        for (int e = lane; e < head_dim; e += 32) vec[e] = vec[e] * inv * weight[e];
+    }
+    __syncwarp();
+    const int half = rotary_dim >> 1;
+    if (rot) {
+        const float2* cs = rot + (size_t)t * half;
+        for (int j = lane; j < half; j += 32) {
+            const float x1 = vec[j], x2 = vec[j + half];
+            const float2 c = cs[j];
+            dst[j] = from_float<TA>(x1 * c.x - x2 * c.y);
+            dst[j + half] = from_float<TA>(x2 * c.x + x1 * c.y);
+        }
+        for (int e = rotary_dim + lane; e < head_dim; e += 32) dst[e] = from_float<TA>(vec[e]);
+    } else {
+        for (int e = lane; e < head_dim; e += 32) dst[e] = from_float<TA>(vec[e]);
+    }
+}
+
+MRUN_API int mrun_qk_norm_rope_cache(void* qkv, int act_dtype, const float* q_weight, const float* k_weight,
+                                     float eps, const float* rot, int rotary_dim, const int* slots,
+                                     void* k_cache, void* v_cache, int tokens, int heads, int kv_heads,
+                                     int head_dim, int page_size, cudaStream_t stream) {
+    MRUN_REQUIRE(tokens >= 0 && heads > 0 && kv_heads > 0 && head_dim > 0 && page_size > 0,
+                 "qk_norm_rope_cache: bad sizes");
+    MRUN_REQUIRE(head_dim <= 1024, "qk_norm_rope_cache: head_dim=%d exceeds the supported 1024", head_dim);
+    MRUN_REQUIRE(rotary_dim >= 0 && rotary_dim <= head_dim && rotary_dim % 2 == 0,
+                 "qk_norm_rope_cache: rotary_dim=%d must be even and at most head_dim=%d", rotary_dim,
+                 head_dim);
+    MRUN_REQUIRE((q_weight == nullptr) == (k_weight == nullptr),
+                 "qk_norm_rope_cache: q and k norm weights come together");
+    MRUN_REQUIRE(slots == nullptr || (k_cache && v_cache), "qk_norm_rope_cache: slots without a cache");
+    if (tokens == 0) return 0;
+    const int warps = 4;
+    const long items = (long)tokens * (heads + 2 * kv_heads);
+    const unsigned blocks = (unsigned)((items + warps - 1) / warps);
+    const size_t smem = (size_t)warps * head_dim * sizeof(float);
+    if (act_dtype == MRUN_F32)
+        qk_norm_rope_cache_kernel<float><<<blocks, warps * 32, smem, stream>>>(
+            (float*)qkv, q_weight, k_weight, eps, (const float2*)rot, rotary_dim, slots, (float*)k_cache,
+            (float*)v_cache, tokens, heads, kv_heads, head_dim, page_size);
+    else if (act_dtype == MRUN_BF16)
+        qk_norm_rope_cache_kernel<__nv_bfloat16><<<blocks, warps * 32, smem, stream>>>(
+            (__nv_bfloat16*)qkv, q_weight, k_weight, eps, (const float2*)rot, rotary_dim, slots,
+            (__nv_bfloat16*)k_cache, (__nv_bfloat16*)v_cache, tokens, heads, kv_heads, head_dim, page_size);
+    else
+        return mrun_set_error("qk_norm_rope_cache: unknown dtype code %d", act_dtype);
+    MRUN_CHECK_LAUNCH("qk_norm_rope_cache");
+    return 0;
+}
+
+// ------------------------------------------------------------------------------------------
+// Gated activation: out[t, i] = act(gate_up[t, i]) * gate_up[t, inter + i], act = SiLU
+// (z * sigmoid(z), crates/mrun-engine/src/models/activations.rs:46-59), in 32-bit.
+// ------------------------------------------------------------------------------------------
+template <typename TA>
+__global__ void swiglu_kernel(const TA* __restrict__ gate_up, TA* __restrict__ out, long total, int inter) {
+    const long i = (long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= total) return;
+    const long t = i / inter;
+    const int c = (int)(i - t * inter);
+    const float g = to_float(gate_up[t * 2 * inter + c]);
+    const float u = to_float(gate_up[t * 2 * inter + inter + c]);
+    out[i] = from_float<TA>(g / (1.f + expf(-g)) * u);
+}
+
+MRUN_API int mrun_swiglu(const void* gate_up, void* out, int act_dtype, int tokens, int inter,
+                         cudaStream_t stream) {
+    MRUN_REQUIRE(tokens >= 0 && inter > 0, "swiglu: bad sizes tokens=%d inter=%d", tokens, inter);
+    if (tokens == 0) return 0;
+    const long total = (long)tokens * inter;
+    const unsigned blocks = (unsigned)((total + 255) / 256);
+    if (act_dtype == MRUN_F32)
+        swiglu_kernel<float><<<blocks, 256, 0, stream>>>((const float*)gate_up, (float*)out, total, inter);
+    else if (act_dtype == MRUN_BF16)
+        swiglu_kernel<__nv_bfloat16><<<blocks, 256, 0, stream>>>((const __nv_bfloat16*)gate_up,
+                                                                 (__nv_bfloat16*)out, total, inter);
+    else
+        return mrun_set_error("swiglu: unknown dtype code %d", act_dtype);
+    MRUN_CHECK_LAUNCH("swiglu");
+    return 0;
+}

@@ -1,0 +1,220 @@
+"""Typed wrappers over the kernel library: they check dtypes, layouts and devices, and pass raw
+pointers with the current CUDA stream.  Every function needs CUDA tensors; none has a CPU path.
+"""
+from __future__ import annotations
+
+import ctypes
+from typing import Optional
+
+import torch
+
+from . import lib as _lib
+from .lib import KernelError
+
+F32, BF16 = 0, 1
+_c_void_p, _c_int, _c_long, _c_float = ctypes.c_void_p, ctypes.c_int, ctypes.c_long, ctypes.c_float
+
+
+def dtype_code(dtype: torch.dtype) -> int:
+    if dtype == torch.float32:
+        return F32
+    if dtype == torch.bfloat16:
+        return BF16
+    raise KernelError(f"dtype {dtype} has no kernel (float32 and bfloat16 do)")
+
+
+def _stream() -> ctypes.c_void_p:
+    return _c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def _ptr(t: Optional[torch.Tensor]) -> ctypes.c_void_p:
+    return _c_void_p(0 if t is None else t.data_ptr())
+
+
+def _check(t: torch.Tensor, name: str, dtype: Optional[torch.dtype] = None, dense: bool = True) -> None:
+    if not t.is_cuda:
+        raise KernelError(f"{name} is on {t.device}; the kernels run on CUDA only")
+    if dtype is not None and t.dtype != dtype:
+        raise KernelError(f"{name} has dtype {t.dtype}, expected {dtype}")
+    if dense and not t.is_contiguous():
+        raise KernelError(f"{name} is not contiguous")
+
+
+def embed(table: torch.Tensor, ids: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+    """out[t] = float(table[ids[t]]); out is float32 [tokens, hidden]."""
+    _check(table, "table"); _check(ids, "ids", torch.int32); _check(out, "out", torch.float32)
+    vocab, hidden = table.shape
+    tokens = ids.numel()
+    if out.shape != (tokens, hidden):
+        raise KernelError(f"embed: out is {tuple(out.shape)}, expected {(tokens, hidden)}")
+    _lib.core().call("mrun_embed", _ptr(table), dtype_code(table.dtype), _ptr(ids), _ptr(out),
+                     _c_int(tokens), _c_int(hidden), _c_int(vocab), _stream())
+    return out
+
+
+def add_rmsnorm(resid: torch.Tensor, delta: Optional[torch.Tensor], weight: torch.Tensor, eps: float,
+                out: torch.Tensor, rows: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """resid (+= delta) then out = rmsnorm(resid) * weight; with ``rows`` only those rows are
+    normed and resid is left as it is."""
+    _check(resid, "resid", torch.float32); _check(weight, "weight", torch.float32); _check(out, "out")
+    hidden = resid.shape[-1]
+    n_rows = resid.shape[0] if rows is None else rows.numel()
+    if delta is not None:
+        _check(delta, "delta", out.dtype)
+        if delta.shape != resid.shape:
+            raise KernelError(f"add_rmsnorm: delta {tuple(delta.shape)} vs resid {tuple(resid.shape)}")
+    if rows is not None:
+        _check(rows, "rows", torch.int32)
+    if weight.numel() != hidden or out.shape != (n_rows, hidden):
+        raise KernelError(f"add_rmsnorm: weight {tuple(weight.shape)}, out {tuple(out.shape)}, "
+                          f"expected hidden {hidden}, rows {n_rows}")
+    _lib.core().call("mrun_add_rmsnorm", _ptr(resid), _ptr(delta), _ptr(weight), _c_float(eps), _ptr(out),
+                     dtype_code(out.dtype), _ptr(rows), _c_int(n_rows), _c_int(hidden), _stream())
+    return out
+
+
+def rotary_table(positions: torch.Tensor, inv_freq: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+    """out[t, j] = (cos, sin)(positions[t] * inv_freq[j]); inv_freq is float64."""
+    _check(positions, "positions", torch.int32); _check(inv_freq, "inv_freq", torch.float64)
+    _check(out, "out", torch.float32)
+    tokens, half = positions.numel(), inv_freq.numel()
+    if out.shape != (tokens, half, 2):
+        raise KernelError(f"rotary_table: out is {tuple(out.shape)}, expected {(tokens, half, 2)}")
+    _lib.core().call("mrun_rotary_table", _ptr(positions), _ptr(inv_freq), _ptr(out), _c_int(tokens),
+                     _c_int(half), _stream())
+    return out
+
+
+def qk_norm_rope_cache(qkv: torch.Tensor, heads: int, kv_heads: int, head_dim: int,
+                       q_weight: Optional[torch.Tensor], k_weight: Optional[torch.Tensor], eps: float,
+                       rot: Optional[torch.Tensor], rotary_dim: int, slots: Optional[torch.Tensor],
+                       k_cache: Optional[torch.Tensor], v_cache: Optional[torch.Tensor],
+                       page_size: int) -> None:
+    """In place on the q part of ``qkv``; k and v go into the pages that ``slots`` names."""
+    _check(qkv, "qkv")
+    tokens = qkv.shape[0]
+    if qkv.shape[1] != (heads + 2 * kv_heads) * head_dim:
+        raise KernelError(f"qk_norm_rope_cache: qkv is {tuple(qkv.shape)}, expected width "
+                          f"{(heads + 2 * kv_heads) * head_dim}")
+    for name, w in (("q_weight", q_weight), ("k_weight", k_weight)):
+        if w is not None:
+            _check(w, name, torch.float32)
+            if w.numel() != head_dim:
+                raise KernelError(f"qk_norm_rope_cache: {name} has {w.numel()} elements, head_dim is {head_dim}")
+    if rot is not None:
+        _check(rot, "rot", torch.float32)
+        if rot.shape != (tokens, rotary_dim // 2, 2):
+            raise KernelError(f"qk_norm_rope_cache: rot is {tuple(rot.shape)}, expected "
+                              f"{(tokens, rotary_dim // 2, 2)}")
+    if slots is not None:
+        _check(slots, "slots", torch.int32)
+        if slots.numel() != tokens:
+            raise KernelError("qk_norm_rope_cache: one slot per token is needed")
+        for name, c in (("k_cache", k_cache), ("v_cache", v_cache)):
+            _check(c, name, qkv.dtype)
+            if c.dim() != 4 or c.shape[1:] != (kv_heads, page_size, head_dim):
+                raise KernelError(f"qk_norm_rope_cache: {name} is {tuple(c.shape)}, expected "
+                                  f"[pages, {kv_heads}, {page_size}, {head_dim}]")
+    _lib.core().call("mrun_qk_norm_rope_cache", _ptr(qkv), dtype_code(qkv.dtype), _ptr(q_weight),
+                     _ptr(k_weight), _c_float(eps), _ptr(rot), _c_int(rotary_dim if rot is not None else 0),
+                     _ptr(slots), _ptr(k_cache), _ptr(v_cache), _c_int(tokens), _c_int(heads),
+                     _c_int(kv_heads), _c_int(head_dim), _c_int(page_size), _stream())
+
+
+def paged_attention_generic(q: torch.Tensor, q_stride: int, out: torch.Tensor, k_cache: torch.Tensor,
+                            v_cache: torch.Tensor, block_tables: torch.Tensor, token_seg: torch.Tensor,
+                            positions: torch.Tensor, heads: int, scale: float, window: int = 0) -> torch.Tensor:
+    """Attention of every token over its request's pages, 32-bit arithmetic on CUDA cores.
+
+    ``q`` may be a view into a wider buffer: row t starts ``q_stride`` elements after row t-1.
+    """
+    _check(q, "q", dense=False); _check(out, "out", q.dtype)
+    _check(k_cache, "k_cache", q.dtype); _check(v_cache, "v_cache", q.dtype)
+    _check(block_tables, "block_tables", torch.int32); _check(token_seg, "token_seg", torch.int32)
+    _check(positions, "positions", torch.int32)
+    pages, kv_heads, page_size, head_dim = k_cache.shape
+    tokens = positions.numel()
+    if v_cache.shape != k_cache.shape:
+        raise KernelError("paged_attention: k and v caches differ in shape")
+    if out.shape != (tokens, heads * head_dim) or token_seg.numel() != tokens:
+        raise KernelError(f"paged_attention: out {tuple(out.shape)} / token_seg {token_seg.numel()} "
+                          f"do not match {tokens} tokens of {heads}x{head_dim}")
+    if block_tables.dim() != 2:
+        raise KernelError("paged_attention: block_tables must be [segments, max_blocks]")
+    _lib.core().call("mrun_paged_attention_generic", _ptr(q), _c_long(q_stride), _ptr(out), _ptr(k_cache),
+                     _ptr(v_cache), dtype_code(q.dtype), _ptr(block_tables), _c_int(block_tables.shape[1]),
+                     _ptr(token_seg), _ptr(positions), _c_int(tokens), _c_int(heads), _c_int(kv_heads),
+                     _c_int(head_dim), _c_int(page_size), _c_long(pages * kv_heads * page_size),
+                     _c_float(scale), _c_int(window), _stream())
+    return out
+
+
+def swiglu(gate_up: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+    """out = silu(gate_up[:, :I]) * gate_up[:, I:]."""
+    _check(gate_up, "gate_up"); _check(out, "out", gate_up.dtype)
+    tokens, inter = out.shape
+    if gate_up.shape != (tokens, 2 * inter):
+        raise KernelError(f"swiglu: gate_up {tuple(gate_up.shape)} vs out {tuple(out.shape)}")
+    _lib.core().call("mrun_swiglu", _ptr(gate_up), _ptr(out), dtype_code(out.dtype), _c_int(tokens),
+                     _c_int(inter), _stream())
+    return out
+
+
+def gemm_f32_nt(x: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """y = x @ w.T in IEEE 32-bit with a fixed summation order.  x may have a row stride."""
+    _check(x, "x", torch.float32, dense=False); _check(w, "w", torch.float32)
+    if x.dim() != 2 or w.dim() != 2 or x.shape[1] != w.shape[1] or x.stride(1) != 1:
+        raise KernelError(f"gemm_f32_nt: x {tuple(x.shape)} (strides {x.stride()}) vs w {tuple(w.shape)}")
+    m, k = x.shape
+    n = w.shape[0]
+    if out is None:
+        out = torch.empty((m, n), dtype=torch.float32, device=x.device)
+    _check(out, "out", torch.float32)
+    if out.shape != (m, n):
+        raise KernelError(f"gemm_f32_nt: out is {tuple(out.shape)}, expected {(m, n)}")
+    _lib.core().call("mrun_gemm_f32_nt", _ptr(x), _ptr(w), _ptr(out), _c_int(m), _c_int(n), _c_int(k),
+                     _c_long(x.stride(0) if m > 1 else k), _c_long(n), _stream())
+    return out
+
+
+def linear(x: torch.Tensor, w: torch.Tensor, out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
+    """y = x @ w.T.  float32: this library's own IEEE kernel.  bfloat16: the vendor GEMM library
+    with 32-bit accumulation (the reference calls its array library's matmul for the same
+    products, crates/mrun-engine/src/load.rs:294-306)."""
+    if x.dtype == torch.float32:
+        return gemm_f32_nt(x, w)
+    _check(x, "x", torch.bfloat16, dense=False); _check(w, "w", torch.bfloat16)
+    if out_dtype is None or out_dtype == torch.bfloat16:
+        return torch.mm(x, w.t())
+    return torch.mm(x, w.t(), out_dtype=out_dtype)
+
+
+def sample(logits: torch.Tensor, out: torch.Tensor, temperature: Optional[torch.Tensor] = None,
+           top_p: Optional[torch.Tensor] = None, top_k: Optional[torch.Tensor] = None,
+           min_p: Optional[torch.Tensor] = None, keys: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """One token per row of float32 logits; per-row parameter arrays, None = neutral."""
+    _check(logits, "logits", torch.float32); _check(out, "out", torch.int32)
+    rows, vocab = logits.shape
+    for name, t, dt in (("temperature", temperature, torch.float32), ("top_p", top_p, torch.float32),
+                        ("top_k", top_k, torch.int32), ("min_p", min_p, torch.float32),
+                        ("keys", keys, torch.int64)):
+        if t is not None:
+            _check(t, name, dt)
+            if t.numel() < rows:
+                raise KernelError(f"sample: {name} has {t.numel()} entries for {rows} rows")
+    if out.numel() < rows:
+        raise KernelError(f"sample: out has {out.numel()} entries for {rows} rows")
+    _lib.core().call("mrun_sample", _ptr(logits), _c_int(rows), _c_int(vocab), _ptr(temperature), _ptr(top_p),
+                     _ptr(top_k), _ptr(min_p), _ptr(keys), _ptr(out), _stream())
+    return out
+
+
+def repetition_penalty(logits: torch.Tensor, recent: torch.Tensor, penalty: torch.Tensor) -> None:
+    """In place: the logits of the ids in recent[row] (negative = empty) are penalised."""
+    _check(logits, "logits", torch.float32); _check(recent, "recent", torch.int32)
+    _check(penalty, "penalty", torch.float32)
+    rows, vocab = logits.shape
+    if recent.dim() != 2 or recent.shape[0] != rows or penalty.numel() < rows:
+        raise KernelError(f"repetition_penalty: recent {tuple(recent.shape)}, penalty {penalty.numel()}, rows {rows}")
+    _lib.core().call("mrun_repetition_penalty", _ptr(logits), _c_int(rows), _c_int(vocab), _ptr(recent),
+                     _c_int(recent.shape[1]), _ptr(penalty), _stream())
