@@ -1,0 +1,276 @@
+#!/usr/bin/env python3
+"""Decode and prefill throughput of the engine on one B200, at the Qwen3-8B layer sizes with
+random weights and seeded synthetic token ids.
+
+    python bench.py [--gpus 1] [--steps K] [--warmup W] [--layers L] [--impl ours|reference]
+
+A *step* is one decode step of a batch of 8 requests that each hold 1,024 tokens of context.
+``value`` is decoded tokens per second over exactly K steps, timed on the device with CUDA events
+after W warm-up steps, through the same captured step and host loop that generation uses.
+``e2e`` is the same quantity through ``Engine.generate`` with host token lists in and out.
+The line also carries a 2,048-token prefill, the decode step's HBM roofline, and decode at batch
+1 and 64.  Weights (15 GB) are far larger than L2, so every step reads them from HBM.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "source": "fallback"}
+
+QWEN3_8B = dict(num_hidden_layers=36, hidden_size=4096, num_attention_heads=32, num_key_value_heads=8,
+                head_dim=128, intermediate_size=12288, vocab_size=151936, max_position_embeddings=8192,
+                rms_norm_eps=1e-6, rope_theta=1000000.0, tie_word_embeddings=False)
+CONTEXT = 1024
+PREFILL_TOKENS = 2048
+
+
+def load_peaks() -> dict:
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    try:
+        with open(path) as f:
+            data = json.load(f)
+        peaks = {"hbm_gbs": float(data["hbm_gbs"]), "bf16_tflops": float(data["bf16_tflops"]),
+                 "source": "measured"}
+        if "bf16_tflops_sustained" in data:
+            peaks["bf16_tflops_sustained"] = float(data["bf16_tflops_sustained"])
+        return peaks
+    except (OSError, KeyError, ValueError, TypeError):
+        return dict(FALLBACK_PEAKS)
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while a timed region runs."""
+
+    FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+              "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self):
+        self.proc = None
+        self.lines = []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", "-i", "0", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
+                 "-lms", "200"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except OSError:
+            self.proc = None
+
+    def stop(self) -> dict:
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.25)
+        self.proc.terminate()
+        try:
+            out, _ = self.proc.communicate(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+            out, _ = self.proc.communicate()
+        clocks, max_clock, reasons = [], None, set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in out.splitlines():
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) < 6:
+                continue
+            try:
+                clocks.append(float(parts[0]))
+                max_clock = float(parts[1])
+            except ValueError:
+                continue
+            for name, value in zip(names, parts[2:6]):
+                if value.lower() == "active":
+                    reasons.add(name)
+        return {"sm_mhz": statistics.median(clocks) if clocks else None, "sm_max_mhz": max_clock,
+                "samples": len(clocks), "reasons": sorted(reasons)}
+
+
+def seeded_tokens(vocab: int, n: int, seed: int):
+    import numpy as np
+    return np.random.default_rng(seed).integers(0, vocab, size=n).tolist()
+
+
+def fill_requests(executor, batch: int, context: int, vocab: int, tag: str):
+    """Admits ``batch`` requests and brings each to ``context`` tokens; returns them with the
+    last token fed still to come (so the next step is a decode step at that context)."""
+    from mrun_b200.engine import StepEntry
+    requests = [executor.admit((tag, i)) for i in range(batch)]
+    per_step = max(1, PREFILL_TOKENS // context)
+    for start in range(0, batch, per_step):
+        group = requests[start:start + per_step]
+        executor.step([StepEntry(r, seeded_tokens(vocab, context - 1, 1000 + start + i), [])
+                       for i, r in enumerate(group)])
+    return requests
+
+
+def time_decode(executor, requests, vocab: int, steps: int, warmup: int):
+    """Device time of ``steps`` decode steps: captured step + token read-back, as generation does."""
+    import torch
+    from mrun_b200.engine import StepEntry
+    tokens = seeded_tokens(vocab, len(requests), 7)
+    def one():
+        nonlocal tokens
+        out = executor.decode_step([StepEntry(r, [t], [0]) for r, t in zip(requests, tokens)])
+        tokens = out.to("cpu").tolist()
+    for _ in range(warmup):
+        one()
+    torch.cuda.synchronize()
+    begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    launches = executor.launches.total
+    begin.record()
+    for _ in range(steps):
+        one()
+    end.record()
+    torch.cuda.synchronize()
+    return begin.elapsed_time(end), executor.launches.total - launches
+
+
+def main() -> int:
+    parser = argparse.ArgumentParser()
+    parser.add_argument("--gpus", type=int, default=1)
+    parser.add_argument("--steps", type=int, default=64)
+    parser.add_argument("--warmup", type=int, default=8)
+    parser.add_argument("--impl", choices=["ours", "reference"], default="ours")
+    parser.add_argument("--layers", type=int, default=None,
+                        help="run fewer layers than the configuration has (both numbers are reported)")
+    parser.add_argument("--skip-points", action="store_true", help="only the batch-8 decode and the prefill")
+    args = parser.parse_args()
+
+    if args.impl == "reference":
+        print(json.dumps({"impl": "reference", "unavailable":
+                          "hupe1980/mrun is a Rust workspace over an Apple Metal array library (nuvec): "
+                          "no cargo/rustc here, no pip-installable package, no Metal device"}))
+        return 0
+    if args.gpus != 1:
+        print(f"bench.py measures one GPU: this engine has no multi-GPU path, --gpus {args.gpus} is not run")
+        return 2
+    if args.warmup < 3:
+        args.warmup = 3
+
+    import torch
+    from mrun_b200 import Engine
+    from mrun_b200.config import Qwen3Config
+    from mrun_b200.kernels import lib as kernel_lib
+
+    peaks = load_peaks()
+    sizes = dict(QWEN3_8B)
+    full_layers = sizes["num_hidden_layers"]
+    if args.layers is not None:
+        sizes["num_hidden_layers"] = args.layers
+    config = Qwen3Config(**sizes)
+    page_size = 16
+    batches = [8] if args.skip_points else [8, 1, 64]
+    slack = args.steps + args.warmup + 64
+    capacity = max(max(batches) * (CONTEXT + slack), 8 * (CONTEXT + 2 * slack)) + PREFILL_TOKENS + 4 * 64
+    engine = Engine.from_config(config, seed=0, dtype="bfloat16", page_size=page_size,
+                                num_pages=-(-capacity // page_size), max_requests=max(64, max(batches)),
+                                max_batch_tokens=PREFILL_TOKENS)
+    executor = engine.executor
+    vocab = config.vocab_size
+    kv_bytes = config.kv_bytes_per_token(2)
+    weight_bytes = executor.model.weight_bytes() - vocab * config.hidden_size * 2  # embedding rows: B rows only
+
+    # ---------------------------------------------------------------- prefill, 2,048 tokens
+    from mrun_b200.engine import StepEntry
+    prompt = seeded_tokens(vocab, PREFILL_TOKENS, 3)
+    times = []
+    for i in range(2 + 3):
+        request = executor.admit(("prefill", i))
+        torch.cuda.synchronize()
+        begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        begin.record()
+        executor.step([StepEntry(request, prompt, [PREFILL_TOKENS - 1])])
+        end.record()
+        torch.cuda.synchronize()
+        executor.release(request)
+        if i >= 2:
+            times.append(begin.elapsed_time(end))
+    prefill_ms = statistics.median(times)
+    h, d = config.hidden_size, config.head_dim
+    linear_params = config.num_hidden_layers * ((config.num_attention_heads + 2 * config.num_key_value_heads) * d * h
+                                                + config.num_attention_heads * d * h
+                                                + 3 * h * config.intermediate_size)
+    prefill_flops = 2.0 * PREFILL_TOKENS * linear_params + 2.0 * vocab * h \
+        + config.num_hidden_layers * 2.0 * PREFILL_TOKENS ** 2 * config.num_attention_heads * d
+    prefill = {"value": round(PREFILL_TOKENS / prefill_ms * 1e3, 1), "tokens": PREFILL_TOKENS,
+               "ms": round(prefill_ms, 3),
+               "frac": round(prefill_flops / (prefill_ms * 1e-3) / (peaks["bf16_tflops"] * 1e12), 4)}
+
+    # ---------------------------------------------------------------- decode at batch 8 / 1 / 64
+    results = {}
+    clocks = {}
+    launches = 0
+    for batch in batches:
+        requests = fill_requests(executor, batch, CONTEXT, vocab, f"decode{batch}")
+        sampler = ClockSampler()
+        if batch == 8:
+            sampler.start()
+        ms, n_launch = time_decode(executor, requests, vocab, args.steps, args.warmup)
+        if batch == 8:
+            clocks = sampler.stop()
+            launches = n_launch
+        for r in requests:
+            executor.release(r)
+        results[batch] = ms
+    ms_per_step = results[8] / args.steps
+    value = 8 * args.steps / (results[8] * 1e-3)
+    context_mid = CONTEXT + args.warmup + args.steps / 2.0
+    step_bytes = weight_bytes + 8 * context_mid * kv_bytes + 8 * h * 2
+    achieved = step_bytes / (ms_per_step * 1e-3) / 1e9
+    roofline = {"bound": "hbm", "achieved": round(achieved, 1), "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                "frac": round(achieved / peaks["hbm_gbs"], 4), "of": peaks["source"]}
+    points = {f"decode_b{b}": round(b * args.steps / (results[b] * 1e-3), 1) for b in batches if b != 8}
+
+    # ---------------------------------------------------------------- end to end, Engine.generate
+    out_tokens = args.steps + 1
+    prompts = [seeded_tokens(vocab, CONTEXT, 50 + i) for i in range(8)]
+    engine.generate(prompts[:2], max_tokens=4, ignore_eos=True)          # warm the mixed-step shapes
+    uploaded = executor.staging.bytes_uploaded
+    steps_before = engine.stats.steps
+    d2h_before = engine.stats.d2h_bytes
+    torch.cuda.synchronize()
+    generations = engine.generate(prompts, max_tokens=out_tokens, ignore_eos=True)
+    torch.cuda.synchronize()
+    last_first = max(g.first_token_time for g in generations)
+    finished = max(g.finished_time for g in generations)
+    decoded = sum(sum(1 for t in g.token_times if t > last_first) for g in generations)
+    e2e_value = decoded / max(finished - last_first, 1e-9)
+    n_steps = max(1, engine.stats.steps - steps_before)
+    e2e = {"value": round(e2e_value, 1), "unit": "tok/s",
+           "h2d_bytes_per_step": round((executor.staging.bytes_uploaded - uploaded) / n_steps, 1),
+           "d2h_bytes_per_step": round((engine.stats.d2h_bytes - d2h_before) / n_steps, 1)}
+
+    line = {
+        "metric": "decode tok/s at batch 8 (Qwen3-8B bf16, 1,024-token prompts)",
+        "value": round(value, 1), "unit": "tok/s", "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": round(ms_per_step, 4), "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "bf16", "data": "synthetic (seeded uniform token ids, N(0,0.02) weights)",
+        "impl": "ours",
+        "config": {
+            "model": "Qwen3-8B shape", "layers": config.num_hidden_layers, "layers_of_config": full_layers,
+            "hidden": h, "heads": config.num_attention_heads, "kv_heads": config.num_key_value_heads,
+            "head_dim": d, "intermediate": config.intermediate_size, "vocab": vocab,
+            "rope_theta": config.rope_theta, "rms_norm_eps": config.rms_norm_eps,
+            "tied": config.tie_word_embeddings, "global_batch": 8, "seq_len": CONTEXT,
+            "max_context": config.max_position_embeddings, "page_size": page_size,
+            "parallelism": "single GPU", "l2": "inputs larger than L2 (15 GB of weights per step)",
+        },
+        "e2e": e2e, "gpu_launches": launches, "clocks": clocks,
+        "prefill": prefill, "roofline": roofline, "points": points,
+        "peaks": peaks, "kernel_entry_calls": kernel_lib.call_count(),
+    }
+    print(json.dumps(line))
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -21,6 +21,8 @@ from __future__ import annotations
 from dataclasses import dataclass, field
 from typing import Dict, List, Optional, Sequence, Tuple
 
+import numpy as np
+
 from .needs import FixedState, PagedKV
 from .pages import OutOfPages, PagePool
 
@@ -50,11 +52,25 @@ class AppendPlan:
 
 
 class PagedGroup:
-    def __init__(self, key: tuple, window: Optional[int], num_pages: int):
+    """One pool of pages and the block table of every state slot: ``table[slot, block]`` is the
+    page of logical block ``block`` of the request in ``slot`` (FREED where it holds none).  The
+    host copy is authoritative; changes are queued and reach the device copy in one scatter at
+    the start of the next step (:meth:`CacheManager.drain_table_updates`)."""
+
+    def __init__(self, key: tuple, window: Optional[int], num_pages: int, max_requests: int,
+                 max_blocks: int):
         self.key = key
         self.window = window
         self.pool = PagePool(num_pages, what=f"pages of group {key}")
         self.entries: List[int] = []
+        self.max_blocks = max_blocks
+        self.table = np.full((max_requests, max_blocks), FREED, dtype=np.int32)
+        self.table_device = None
+        self.updates: List[Tuple[int, int]] = []        # (flat index, page)
+
+    def set(self, slot: int, block: int, page: int) -> None:
+        self.table[slot, block] = page
+        self.updates.append((slot * self.max_blocks + block, page))
 
 
 class EntryCache:
@@ -69,7 +85,8 @@ class EntryCache:
 
 class CacheManager:
     def __init__(self, needs: Sequence[object], shares: Sequence[Optional[int]], page_size: int,
-                 num_pages: int, max_requests: int, device=None, dtype=None):
+                 num_pages: int, max_requests: int, device=None, dtype=None,
+                 max_blocks_per_request: Optional[int] = None):
         """``needs[i]`` is the need of schedule entry i (None: keeps nothing); ``shares[i]`` is the
         entry whose cache entry i reads instead of owning one.  ``device`` None builds the
         bookkeeping only (no tensors), which is what the host-side tests use."""
@@ -81,6 +98,8 @@ class CacheManager:
         self.num_pages = num_pages
         self.max_requests = max_requests
         self.device, self.dtype = device, dtype
+        # a request never holds more logical blocks than its longest sequence needs
+        self.max_blocks = max(1, min(max_blocks_per_request or num_pages, max(num_pages, 1)))
         self.groups: Dict[tuple, PagedGroup] = {}
         self.entries: List[Optional[EntryCache]] = []
         self._slots = PagePool(max_requests, what="state slots")
@@ -102,7 +121,12 @@ class CacheManager:
                 key = need.group_key()
                 group = self.groups.get(key)
                 if group is None:
-                    group = self.groups[key] = PagedGroup(key, need.window, num_pages)
+                    group = self.groups[key] = PagedGroup(key, need.window, num_pages, max_requests,
+                                                          self.max_blocks)
+                    if device is not None:
+                        import torch
+                        group.table_device = torch.full((max_requests, self.max_blocks), FREED,
+                                                        dtype=torch.int32, device=device)
                 group.entries.append(i)
                 k = v = None
                 if device is not None:
@@ -167,6 +191,9 @@ class CacheManager:
             raise ValueError(f"request {request.request_id!r} has an uncommitted step")
         for key, group in self.groups.items():
             group.pool.free(request.pages_held(key))
+            for block, page in enumerate(request.blocks[key]):
+                if page != FREED:
+                    group.set(request.slot, block, FREED)
             request.blocks[key] = []
         self._slots.free([request.slot])
         request.released = True
@@ -191,6 +218,9 @@ class CacheManager:
                 raise ValueError(f"request {request.request_id!r}: a step brings at least one token")
             if request.pending:
                 raise ValueError(f"request {request.request_id!r} has an uncommitted step")
+            if self.groups and self.blocks_for(request.length + tokens) > self.max_blocks:
+                raise OutOfPages(f"blocks of request {request.request_id!r}",
+                                 self.blocks_for(request.length + tokens), self.max_blocks)
             for key, n in self.pages_needed(request, tokens).items():
                 wanted[key] += n
         for key, n in wanted.items():
@@ -201,9 +231,13 @@ class CacheManager:
         for request, tokens in items:
             for key, n in self.pages_needed(request, tokens).items():
                 if n:
-                    pages = self.groups[key].pool.alloc(n)
-                    taken.append((request, key, len(request.blocks[key]), pages))
+                    group = self.groups[key]
+                    pages = group.pool.alloc(n)
+                    first = len(request.blocks[key])
+                    taken.append((request, key, first, pages))
                     request.blocks[key].extend(pages)
+                    for i, page in enumerate(pages):
+                        group.set(request.slot, first + i, page)
             request.pending = tokens
         return AppendPlan(list(items), taken)
 
@@ -225,6 +259,7 @@ class CacheManager:
                     group.pool.free([blocks[b] for b in passed])
                     for b in passed:
                         blocks[b] = FREED
+                        group.set(request.slot, b, FREED)
 
     def rollback(self, plan: AppendPlan) -> None:
         if plan.done:
@@ -235,8 +270,23 @@ class CacheManager:
             assert blocks[first:first + len(pages)] == pages and len(blocks) == first + len(pages)
             del blocks[first:]
             self.groups[key].pool.free(pages)
+            for i in range(len(pages)):
+                self.groups[key].set(request.slot, first + i, FREED)
         for request, _ in plan.items:
             request.pending = 0
+
+    # ------------------------------------------------------------------ device tables
+    def drain_table_updates(self) -> Dict[tuple, Tuple[np.ndarray, np.ndarray]]:
+        """The queued block-table changes per group as (flat indices, pages), oldest first with
+        only the last change of an index kept; the queues are emptied."""
+        out = {}
+        for key, group in self.groups.items():
+            if group.updates:
+                last = dict(group.updates)          # later entries overwrite earlier ones
+                out[key] = (np.fromiter(last.keys(), dtype=np.int32, count=len(last)),
+                            np.fromiter(last.values(), dtype=np.int32, count=len(last)))
+                group.updates = []
+        return out
 
     # ------------------------------------------------------------------ checks
     def check_invariants(self) -> None:
@@ -257,5 +307,11 @@ class CacheManager:
             for page in held:
                 if not group.pool.is_held(page):
                     raise AssertionError(f"group {key}: page {page} is in a block table and free")
+            for request in self._live.values():
+                row = self.groups[key].table[request.slot]
+                blocks = request.blocks[key]
+                if list(row[:len(blocks)]) != blocks or (row[len(blocks):] != FREED).any():
+                    raise AssertionError(f"group {key}: the block table of slot {request.slot} differs "
+                                         f"from request {request.request_id!r}'s pages")
             if len(held) + group.pool.free_count != group.pool.num_pages:
                 raise AssertionError(f"group {key}: {group.pool.num_pages - len(held) - group.pool.free_count} pages lost")

@@ -23,7 +23,7 @@ __global__ void __launch_bounds__(THREADS)
 paged_attention_generic_kernel(const TA* __restrict__ q, long q_stride, TA* __restrict__ out,
                                const TA* __restrict__ k_cache, const TA* __restrict__ v_cache,
                                const int* __restrict__ block_tables, int max_blocks,
-                               const int* __restrict__ token_seg, const int* __restrict__ positions,
+                               const int* __restrict__ token_slot, const int* __restrict__ positions,
                                int heads, int kv_heads, int head_dim, int page_size, float scale,
                                int window) {
     extern __shared__ float smem[];
@@ -40,7 +40,7 @@ paged_attention_generic_kernel(const TA* __restrict__ q, long q_stride, TA* __re
         return;
     }
     const int kvh = h / (heads / kv_heads);
-    const int* table = block_tables + (size_t)token_seg[t] * max_blocks;
+    const int* table = block_tables + (size_t)token_slot[t] * max_blocks;
     const TA* qrow = q + (size_t)t * q_stride + (size_t)h * head_dim;
     for (int d = tid; d < head_dim; d += THREADS) qs[d] = to_float(qrow[d]);
     __syncthreads();
@@ -97,10 +97,10 @@ paged_attention_generic_kernel(const TA* __restrict__ q, long q_stride, TA* __re
 
 // q: row t starts at q + t * q_stride, heads contiguous [heads, head_dim].
 // out: dense [tokens, heads * head_dim].  caches: [pages, kv_heads, page_size, head_dim].
-// block_tables: [segments, max_blocks]; token_seg[t] picks the row; positions[t] < 0 = padding.
+// block_tables: [slots, max_blocks], one row per state slot; token_slot[t] picks the row; positions[t] < 0 = padding.
 MRUN_API int mrun_paged_attention_generic(const void* q, long q_stride, void* out, const void* k_cache,
                                           const void* v_cache, int act_dtype, const int* block_tables,
-                                          int max_blocks, const int* token_seg, const int* positions,
+                                          int max_blocks, const int* token_slot, const int* positions,
                                           int tokens, int heads, int kv_heads, int head_dim,
                                           int page_size, long cache_rows, float scale, int window,
                                           cudaStream_t stream) {
@@ -120,12 +120,12 @@ MRUN_API int mrun_paged_attention_generic(const void* q, long q_stride, void* ou
     if (act_dtype == MRUN_F32)
         paged_attention_generic_kernel<float><<<grid, THREADS, smem, stream>>>(
             (const float*)q, q_stride, (float*)out, (const float*)k_cache, (const float*)v_cache,
-            block_tables, max_blocks, token_seg, positions, heads, kv_heads, head_dim, page_size, scale,
+            block_tables, max_blocks, token_slot, positions, heads, kv_heads, head_dim, page_size, scale,
             window);
     else if (act_dtype == MRUN_BF16)
         paged_attention_generic_kernel<__nv_bfloat16><<<grid, THREADS, smem, stream>>>(
             (const __nv_bfloat16*)q, q_stride, (__nv_bfloat16*)out, (const __nv_bfloat16*)k_cache,
-            (const __nv_bfloat16*)v_cache, block_tables, max_blocks, token_seg, positions, heads, kv_heads,
+            (const __nv_bfloat16*)v_cache, block_tables, max_blocks, token_slot, positions, heads, kv_heads,
             head_dim, page_size, scale, window);
     else
         return mrun_set_error("paged_attention_generic: unknown dtype code %d", act_dtype);

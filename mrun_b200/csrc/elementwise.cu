@@ -272,3 +272,24 @@ MRUN_API int mrun_swiglu(const void* gate_up, void* out, int act_dtype, int toke
     MRUN_CHECK_LAUNCH("swiglu");
     return 0;
 }
+
+// ------------------------------------------------------------------------------------------
+// Scatter of 32-bit integers: dst[index[i]] = value[i].  Brings the block tables on the device up
+// to date with the pages the host handed out or took back since the last step.
+// ------------------------------------------------------------------------------------------
+__global__ void scatter_i32_kernel(int* __restrict__ dst, const int* __restrict__ index,
+                                   const int* __restrict__ value, int n, long dst_size) {
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    const long at = index[i];
+    if (at >= 0 && at < dst_size) dst[at] = value[i];
+}
+
+MRUN_API int mrun_scatter_i32(int* dst, const int* index, const int* value, int n, long dst_size,
+                              cudaStream_t stream) {
+    MRUN_REQUIRE(n >= 0 && dst_size >= 0, "scatter_i32: bad sizes n=%d dst_size=%ld", n, dst_size);
+    if (n == 0) return 0;
+    scatter_i32_kernel<<<(n + 255) / 256, 256, 0, stream>>>(dst, index, value, n, dst_size);
+    MRUN_CHECK_LAUNCH("scatter_i32");
+    return 0;
+}

@@ -2,7 +2,8 @@
 
 A step is a flat batch of tokens cut into *segments*: one per request, each a run of consecutive
 tokens of that request (a portion of its prompt, or one decoded token).  Everything a kernel needs
-is in int32 device arrays built on the host in one pinned buffer and copied once.
+is in int32 device arrays that the host lays out in one pinned buffer and copies once.  The block
+tables live on the device, one row per state slot, and only their changes travel.
 """
 from __future__ import annotations
 
@@ -13,6 +14,7 @@ import numpy as np
 import torch
 
 from ..cache.manager import FREED, CacheManager, RequestCache
+from ..kernels import ops
 
 
 @dataclass
@@ -36,19 +38,19 @@ class SegmentInfo:
 class GroupView:
     """A cache group's view of the step."""
 
-    block_tables: torch.Tensor   # int32 [segments, max_blocks], FREED where no page is held
-    slot_mapping: torch.Tensor   # int32 [tokens]: page * page_size + offset of each new token
+    block_tables: torch.Tensor   # int32 [state slots, max_blocks], FREED where no page is held
+    slot_mapping: torch.Tensor   # int32 [tokens]: page * page_size + offset of each new token, -1 = none
     max_blocks: int
 
 
 @dataclass
 class StepContext:
-    num_tokens: int
+    num_tokens: int              # rows of the batch, padding rows included
     num_segments: int
     segments: List[SegmentInfo]
     token_ids: torch.Tensor      # int32 [tokens]
     positions: torch.Tensor      # int32 [tokens]; negative = padding row
-    token_seg: torch.Tensor      # int32 [tokens]: segment of each token
+    token_slot: torch.Tensor     # int32 [tokens]: state slot (block-table row) of each token
     seg_q_start: torch.Tensor    # int32 [segments + 1]
     seg_kv_len: torch.Tensor     # int32 [segments]: keys visible to the segment's last token
     seg_slot: torch.Tensor       # int32 [segments]
@@ -67,17 +69,18 @@ class StepContext:
 
 
 class HostStaging:
-    """Two pinned buffers used in turn; a buffer is reused only after its copy has finished."""
+    """Pinned buffers used in turn; a buffer is reused only after its copy has finished."""
 
-    def __init__(self, device: torch.device):
+    def __init__(self, device: torch.device, depth: int = 4):
         self.device = device
-        self._buffers: List[Optional[torch.Tensor]] = [None, None]
-        self._events: List[Optional[torch.cuda.Event]] = [None, None]
+        self._buffers: List[Optional[torch.Tensor]] = [None] * depth
+        self._events: List[Optional[torch.cuda.Event]] = [None] * depth
         self._turn = 0
+        self.bytes_uploaded = 0
 
-    def upload(self, host: np.ndarray) -> torch.Tensor:
+    def upload(self, host: np.ndarray, out: Optional[torch.Tensor] = None) -> torch.Tensor:
         i = self._turn
-        self._turn ^= 1
+        self._turn = (self._turn + 1) % len(self._buffers)
         if self._events[i] is not None:
             self._events[i].synchronize()
         n = host.size
@@ -85,70 +88,100 @@ class HostStaging:
             self._buffers[i] = torch.empty(max(4096, 2 * n), dtype=torch.int32, pin_memory=True)
         pinned = self._buffers[i][:n]
         pinned.numpy()[:] = host
-        out = torch.empty(n, dtype=torch.int32, device=self.device)
-        out.copy_(pinned, non_blocking=True)
+        if out is None:
+            out = torch.empty(n, dtype=torch.int32, device=self.device)
+        out[:n].copy_(pinned, non_blocking=True)
         event = torch.cuda.Event()
         event.record()
         self._events[i] = event
+        self.bytes_uploaded += 4 * n
         return out
 
 
-def build_context(entries: Sequence[StepEntry], manager: CacheManager, staging: HostStaging) -> StepContext:
-    """Lays the step out.  The requests' pages for the new tokens are already planned
-    (``request.pending`` tokens, blocks extended)."""
-    page_size = manager.page_size
-    n_seg = len(entries)
-    lengths = [len(e.tokens) for e in entries]
-    total = sum(lengths)
-    keys = list(manager.groups)
-    max_blocks = max(1, max(len(e.request.blocks[k]) for e in entries for k in keys) if keys else 1)
+RECENT = 20   # token ids per row that the repetition penalty looks at
 
-    per_group = total + n_seg * max_blocks
-    host = np.empty(3 * total + (n_seg + 1) + 2 * n_seg + len(keys) * per_group, dtype=np.int32)
-    token_ids, positions, token_seg = host[:total], host[total:2 * total], host[2 * total:3 * total]
-    at = 3 * total
-    seg_q_start = host[at:at + n_seg + 1]; at += n_seg + 1
-    seg_kv_len = host[at:at + n_seg]; at += n_seg
-    seg_slot = host[at:at + n_seg]; at += n_seg
-    group_off = at
+
+def layout(tokens: int, segments: int, groups: int, sampling_rows: int = 0) -> Dict[str, slice]:
+    """Where each array sits in the step's int32 buffer.  With ``sampling_rows`` the buffer also
+    carries the per-row sampling settings (floats as their bit patterns, 64-bit keys as pairs on
+    an even offset)."""
+    names = [("token_ids", tokens), ("positions", tokens), ("token_slot", tokens),
+             ("seg_q_start", segments + 1), ("seg_kv_len", segments), ("seg_slot", segments)]
+    names += [(f"slot_mapping{g}", tokens) for g in range(groups)]
+    if sampling_rows:
+        r = sampling_rows
+        names += [("temperature", r), ("top_p", r), ("min_p", r), ("penalty", r), ("top_k", r),
+                  ("recent", RECENT * r), ("keys", 2 * r)]
+    out, at = {}, 0
+    for name, n in names:
+        if name == "keys":
+            at += at % 2
+        out[name] = slice(at, at + n)
+        at += n
+    out["_size"] = slice(0, at)
+    return out
+
+
+def push_table_updates(manager: CacheManager, staging: HostStaging) -> None:
+    """Brings the device block tables up to date with what the host handed out or took back."""
+    for key, (index, value) in manager.drain_table_updates().items():
+        both = staging.upload(np.concatenate([index, value]))
+        n = index.size
+        ops.scatter_i32(manager.groups[key].table_device, both[:n], both[n:])
+
+
+def build_context(entries: Sequence[StepEntry], manager: CacheManager, staging: HostStaging,
+                  pad_tokens: Optional[int] = None, out: Optional[torch.Tensor] = None,
+                  sampling=None) -> StepContext:
+    """Lays the step out.  The requests' pages for the new tokens are already planned
+    (``request.pending`` tokens, blocks extended).  ``pad_tokens`` appends padding rows
+    (position -1, no cache slot) up to that many rows and pads the segment arrays to the same
+    count, for steps that replay a captured graph of fixed shape; ``out`` is the graph's own
+    buffer to fill, and ``sampling(host, where)`` fills the sampling settings it also carries."""
+    page_size = manager.page_size
+    lengths = [len(e.tokens) for e in entries]
+    real = sum(lengths)
+    total = max(real, pad_tokens or 0)
+    n_seg = len(entries) if pad_tokens is None else pad_tokens
+    keys = list(manager.groups)
+    where = layout(total, n_seg, len(keys), total if sampling is not None else 0)
+    host = np.zeros(where["_size"].stop, dtype=np.int32)
+    if sampling is not None:
+        sampling(host, where)
+    token_ids, positions, token_slot = host[where["token_ids"]], host[where["positions"]], host[where["token_slot"]]
+    seg_q_start, seg_kv_len, seg_slot = host[where["seg_q_start"]], host[where["seg_kv_len"]], host[where["seg_slot"]]
+    positions[real:] = -1
+    maps = [host[where[f"slot_mapping{g}"]] for g in range(len(keys))]
+    for m in maps:
+        m[real:] = -1
 
     segments: List[SegmentInfo] = []
     row = 0
     for s, entry in enumerate(entries):
         n, start = lengths[s], entry.request.length
         token_ids[row:row + n] = np.asarray(entry.tokens, dtype=np.int64)
-        positions[row:row + n] = np.arange(start, start + n, dtype=np.int32)
-        token_seg[row:row + n] = s
+        pos = np.arange(start, start + n, dtype=np.int32)
+        positions[row:row + n] = pos
+        token_slot[row:row + n] = entry.request.slot
         seg_q_start[s] = row
         seg_kv_len[s] = start + n
         seg_slot[s] = entry.request.slot
+        for g, key in enumerate(keys):
+            blocks = np.asarray(entry.request.blocks[key], dtype=np.int32)
+            pages = blocks[pos // page_size]
+            maps[g][row:row + n] = np.where(pages == FREED, -1, pages * page_size + pos % page_size)
         segments.append(SegmentInfo(entry.request.slot, row, n, start))
         row += n
-    seg_q_start[n_seg] = total
+    seg_q_start[len(entries):] = real
 
-    for g, key in enumerate(keys):
-        base = group_off + g * per_group
-        slot_mapping = host[base:base + total]
-        tables = host[base + total:base + per_group].reshape(n_seg, max_blocks)
-        tables[:] = FREED
-        for s, entry in enumerate(entries):
-            blocks = np.asarray(entry.request.blocks[key], dtype=np.int32)
-            tables[s, :len(blocks)] = blocks
-            pos = positions[seg_q_start[s]:seg_q_start[s + 1]]
-            pages = blocks[pos // page_size]
-            slot_mapping[seg_q_start[s]:seg_q_start[s + 1]] = np.where(
-                pages == FREED, -1, pages * page_size + pos % page_size)
-
-    dev = staging.upload(host)
-    groups = {}
-    for g, key in enumerate(keys):
-        base = group_off + g * per_group
-        groups[key] = GroupView(dev[base + total:base + per_group].view(n_seg, max_blocks),
-                                dev[base:base + total], max_blocks)
-    at = 3 * total
+    push_table_updates(manager, staging)
+    dev = staging.upload(host, out)
+    groups = {key: GroupView(manager.groups[key].table_device, dev[where[f"slot_mapping{g}"]],
+                             manager.groups[key].max_blocks)
+              for g, key in enumerate(keys)}
     return StepContext(
         num_tokens=total, num_segments=n_seg, segments=segments,
-        token_ids=dev[:total], positions=dev[total:2 * total], token_seg=dev[2 * total:3 * total],
-        seg_q_start=dev[at:at + n_seg + 1], seg_kv_len=dev[at + n_seg + 1:at + 2 * n_seg + 1],
-        seg_slot=dev[at + 2 * n_seg + 1:at + 3 * n_seg + 1], groups=groups,
+        token_ids=dev[where["token_ids"]], positions=dev[where["positions"]],
+        token_slot=dev[where["token_slot"]], seg_q_start=dev[where["seg_q_start"]],
+        seg_kv_len=dev[where["seg_kv_len"]], seg_slot=dev[where["seg_slot"]], groups=groups,
         max_q_len=max(lengths), max_kv_len=int(seg_kv_len.max()), page_size=page_size)

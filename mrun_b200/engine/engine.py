@@ -1,0 +1,218 @@
+"""The Python entry point: ``Engine(...).generate(prompts, ...)``, token ids in, token ids out.
+
+The reference has no Python API; its token-ids-in program is
+``generate <model-dir> <ids> [max-tokens]`` (crates/mrun-engine/examples/generate.rs:1-13) and
+its sampling options are those of ``mrun run`` (crates/mrun/src/cli/run.rs:27-79).  This class
+follows both: the same option names and meanings, the same finish reasons.
+"""
+from __future__ import annotations
+
+import time
+from dataclasses import dataclass, field
+from typing import List, Optional, Sequence, Union
+
+import numpy as np
+import torch
+
+from ..cache.pages import OutOfPages
+from ..sampling.params import REPETITION_CONTEXT, SamplingParams, draw_key
+from ..sampling.sampler import Sampler
+from .batch import RECENT, StepEntry
+from .executor import Executor
+from .loading import executor_from_config, executor_from_folder
+from .scheduler import Request, Scheduler, StepPlan
+
+
+@dataclass
+class Generation:
+    tokens: List[int]
+    finish_reason: str
+    message: str = ""
+    prompt_tokens: int = 0
+    time_to_first_token_s: float = 0.0
+    total_s: float = 0.0
+    preemptions: int = 0
+    first_token_time: float = 0.0                 # host clock (perf_counter) readings
+    finished_time: float = 0.0
+    token_times: List[float] = field(default_factory=list)
+
+
+@dataclass
+class EngineStats:
+    steps: int = 0
+    tokens_in: int = 0
+    tokens_out: int = 0
+    h2d_bytes: int = 0
+    d2h_bytes: int = 0
+    preemptions: int = 0
+
+
+class Engine:
+    def __init__(self, executor: Executor, max_batch_tokens: int = 2048, reserve: bool = True,
+                 max_queue: Optional[int] = None):
+        self.executor = executor
+        self.max_batch_tokens = max_batch_tokens
+        self.reserve = reserve
+        self.max_queue = max_queue
+        self.sampler = Sampler(executor.device)
+        self.eos_token_ids = tuple(executor.spec.eos_token_ids)
+        self.stats = EngineStats()
+        self._next_id = 0
+
+    # ------------------------------------------------------------------ construction
+    @classmethod
+    def from_folder(cls, model_dir: str, dtype: str = "bfloat16", page_size: int = 16,
+                    num_pages: Optional[int] = None, context: Optional[int] = None,
+                    max_requests: int = 64, max_batch_tokens: int = 2048, reserve: bool = True,
+                    device: str = "cuda:0", **kw) -> "Engine":
+        pages = _pages_for(num_pages, context, page_size)
+        executor = executor_from_folder(model_dir, dtype=dtype, page_size=page_size, num_pages=pages,
+                                        max_requests=max_requests, device=device)
+        return cls(executor, max_batch_tokens=max_batch_tokens, reserve=reserve, **kw)
+
+    @classmethod
+    def from_config(cls, config, seed: int = 0, dtype: str = "bfloat16", std: float = 0.02,
+                    norm_noise: float = 0.0, page_size: int = 16, num_pages: Optional[int] = None,
+                    context: Optional[int] = None, max_requests: int = 64, max_batch_tokens: int = 2048,
+                    reserve: bool = True, device: str = "cuda:0", **kw) -> "Engine":
+        pages = _pages_for(num_pages, context, page_size)
+        executor = executor_from_config(config, seed, dtype=dtype, std=std, norm_noise=norm_noise,
+                                        page_size=page_size, num_pages=pages, max_requests=max_requests,
+                                        device=device)
+        return cls(executor, max_batch_tokens=max_batch_tokens, reserve=reserve, **kw)
+
+    # ------------------------------------------------------------------ generation
+    def generate(self, prompts: Sequence[Sequence[int]], max_tokens: int = 2048, temperature: float = 0.0,
+                 top_p: float = 1.0, top_k: int = 0, min_p: float = 0.0, seed: Optional[int] = None,
+                 repetition_penalty: float = 1.0, ignore_eos: bool = False,
+                 sampling: Optional[Sequence[SamplingParams]] = None) -> List[Generation]:
+        """Generates for every prompt (lists of token ids) and returns the results in order.
+        ``sampling`` gives each prompt settings of its own; otherwise all share the keyword
+        values, prompt i drawing with ``seed + i`` when a seed is given."""
+        requests = []
+        for i, prompt in enumerate(prompts):
+            if sampling is not None:
+                params = sampling[i]
+            else:
+                params = SamplingParams(temperature=temperature, top_p=top_p, top_k=top_k, min_p=min_p,
+                                        seed=None if seed is None else seed + i,
+                                        repetition_penalty=repetition_penalty)
+            requests.append(Request(request_id=("gen", self._next_id), prompt=list(map(int, prompt)),
+                                    max_tokens=max_tokens, sampling=params, ignore_eos=ignore_eos))
+            self._next_id += 1
+        self.run(requests)
+        return [Generation(tokens=r.output, finish_reason=r.finish_reason, message=r.message,
+                           prompt_tokens=len(r.prompt),
+                           time_to_first_token_s=max(0.0, r.first_token_at - r.submitted_at) if r.output else 0.0,
+                           total_s=r.finished_at - r.submitted_at, preemptions=r.preemptions,
+                           first_token_time=r.first_token_at, finished_time=r.finished_at,
+                           token_times=r.token_times)
+                for r in requests]
+
+    def run(self, requests: Sequence[Request]) -> None:
+        """Runs the requests to their end through the scheduler and the step function."""
+        scheduler = Scheduler(self.executor.cache, eos_token_ids=self.eos_token_ids,
+                              max_batch_tokens=self.max_batch_tokens, reserve=self.reserve,
+                              max_queue=self.max_queue, max_positions=self.executor.spec.max_positions)
+        for request in requests:
+            scheduler.submit(request)
+        try:
+            while scheduler.has_work():
+                plan = scheduler.schedule()
+                if plan is None:
+                    raise RuntimeError("the scheduler has waiting requests and nothing to run")
+                tokens = self._run_plan(scheduler, plan)
+                if tokens is not None:
+                    scheduler.complete(plan, tokens)
+        finally:
+            for request in list(scheduler.running):
+                scheduler.abort(request, "generation was interrupted")
+        self.stats.preemptions += scheduler.preemptions
+
+    def _run_plan(self, scheduler: Scheduler, plan: StepPlan) -> Optional[List[int]]:
+        entries = [StepEntry(e.request.cache, e.tokens, [len(e.tokens) - 1] if e.wants_logits else [])
+                   for e in plan.entries]
+        sampled = plan.sampled
+        captured = (all(len(e.tokens) == 1 and e.wants_logits for e in plan.entries)
+                    and self.executor.decode_bucket(len(entries)) is not None)
+        try:
+            if captured:
+                tokens = self.executor.decode_step(entries, lambda host, where: _fill_sampling(host, where, sampled))
+            else:
+                logits = self.executor.step(entries)
+        except OutOfPages:
+            if scheduler.preempt_newest() is None:
+                raise
+            return None          # plan again without the preempted request
+        if captured:
+            self.stats.steps += 1
+            self.stats.tokens_in += plan.num_tokens
+            host = tokens.to("cpu").tolist()
+            self.stats.tokens_out += len(host)
+            self.stats.d2h_bytes += 4 * len(host)
+            return host
+        self.stats.steps += 1
+        self.stats.tokens_in += plan.num_tokens
+        if not sampled:
+            return []
+        tokens = self.sampler.sample(
+            logits, [r.sampling for r in sampled], [r.seed for r in sampled],
+            [len(r.output) + 1 for r in sampled],
+            [r.recent(REPETITION_CONTEXT) for r in sampled])
+        host = tokens.to("cpu").tolist()
+        self.stats.tokens_out += len(host)
+        self.stats.d2h_bytes += 4 * len(host)
+        return host
+
+    # ------------------------------------------------------------------ direct stepping
+    def step(self, entries: Sequence[StepEntry]):
+        """The step function itself, for callers that schedule on their own."""
+        return self.executor.step(entries)
+
+    def info(self) -> dict:
+        ex = self.executor
+        return {
+            "architecture": ex.spec.architecture,
+            "dtype": ex.precision.name,
+            "weights_bytes": ex.model.weight_bytes(),
+            "page_size": ex.cache.page_size,
+            "num_pages": ex.cache.num_pages,
+            "cache_bytes": ex.cache.bytes_per_page() * ex.cache.num_pages,
+            "capacity_tokens": ex.cache.num_pages * ex.cache.page_size,
+            "max_requests": ex.cache.max_requests,
+            "max_batch_tokens": self.max_batch_tokens,
+            "eos_token_ids": list(self.eos_token_ids),
+        }
+
+
+def _fill_sampling(host, where, requests: Sequence[Request]) -> None:
+    """Writes the rows' sampling settings into a captured step's input buffer."""
+    n = len(requests)
+    as_bits = lambda values: np.asarray(values, dtype=np.float32).view(np.int32)
+    temperature = host[where["temperature"]]; top_p = host[where["top_p"]]
+    min_p = host[where["min_p"]]; penalty = host[where["penalty"]]
+    top_p[:] = as_bits([1.0])[0]
+    penalty[:] = as_bits([1.0])[0]
+    temperature[:n] = as_bits([r.sampling.temperature for r in requests])
+    top_p[:n] = as_bits([r.sampling.top_p for r in requests])
+    min_p[:n] = as_bits([r.sampling.min_p for r in requests])
+    penalty[:n] = as_bits([r.sampling.repetition_penalty for r in requests])
+    host[where["top_k"]][:n] = [r.sampling.top_k for r in requests]
+    recent = host[where["recent"]].reshape(-1, RECENT)
+    recent[:] = -1
+    keys = np.zeros(len(temperature), dtype=np.uint64)
+    for i, r in enumerate(requests):
+        if not r.sampling.greedy:
+            keys[i] = draw_key(r.seed, len(r.output) + 1)
+        if r.sampling.repetition_penalty != 1.0:
+            ids = r.recent(RECENT)
+            recent[i, :len(ids)] = ids
+    host[where["keys"]] = keys.view(np.int32)
+
+
+def _pages_for(num_pages: Optional[int], context: Optional[int], page_size: int) -> int:
+    if num_pages is not None:
+        return num_pages
+    if context is not None:
+        return -(-context // page_size)
+    return -(-32768 // page_size)

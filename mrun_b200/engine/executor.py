@@ -23,6 +23,24 @@ class StepError(ValueError):
     """A step that cannot run as given (bad token id, bad place, too long)."""
 
 
+class LaunchCounter:
+    """Counts this library's kernel launches (calls through the C ABI) between begin and end."""
+
+    def __init__(self):
+        self.total = 0
+        self._mark = 0
+
+    def begin(self) -> None:
+        from ..kernels import lib
+        self._mark = lib.call_count()
+
+    def end(self) -> int:
+        from ..kernels import lib
+        n = lib.call_count() - self._mark
+        self.total += n
+        return n
+
+
 class Executor:
     def __init__(self, spec: ModelSpec, tensors: Dict[str, torch.Tensor], dtype: str = "bfloat16",
                  page_size: int = 16, num_pages: int = 256, max_requests: int = 8,
@@ -37,9 +55,13 @@ class Executor:
         self.spec = spec
         self.model = Model(spec, tensors, self.runtime)
         self.cache = CacheManager(self.model.cache_needs(), self.model.cache_shares(), page_size,
-                                  num_pages, max_requests, device=self.device, dtype=self.precision.act)
+                                  num_pages, max_requests, device=self.device, dtype=self.precision.act,
+                                  max_blocks_per_request=-(-spec.max_positions // page_size))
         self.staging = HostStaging(self.device)
         self.steps_run = 0
+        self.launches = LaunchCounter()
+        self.use_graphs = self.model.graph_safe
+        self._graphs: Dict[int, "DecodeGraph"] = {}
 
     # ------------------------------------------------------------------ requests
     def admit(self, request_id: object) -> RequestCache:
@@ -91,3 +113,105 @@ class Executor:
         self.cache.commit(plan)
         self.steps_run += 1
         return logits
+
+    # ------------------------------------------------------------------ captured decode step
+    def decode_bucket(self, rows: int) -> Optional[int]:
+        """The captured step size that takes ``rows`` decoding requests, or None."""
+        if not self.use_graphs or rows < 1:
+            return None
+        bucket = 1
+        while bucket < rows:
+            bucket *= 2
+        return bucket if bucket <= max(1, self.cache.max_requests) * 2 else None
+
+    def decode_step(self, entries: Sequence[StepEntry], sampling=None) -> torch.Tensor:
+        """One token for each entry (each brings exactly one token) through a captured graph,
+        sampling included.  ``sampling(host, where)`` writes the rows' sampling settings into the
+        step's buffer (left at greedy when None).  Returns int32 device tokens, one per entry."""
+        self._validate(entries)
+        if any(len(e.tokens) != 1 for e in entries):
+            raise StepError("decode_step takes one token per request")
+        bucket = self.decode_bucket(len(entries))
+        if bucket is None:
+            raise StepError(f"no captured decode step takes {len(entries)} requests")
+        graph = self._graphs.get(bucket)
+        if graph is None:
+            graph = self._graphs[bucket] = DecodeGraph(self, bucket)
+        plan = self.cache.plan_append([(e.request, 1) for e in entries])
+        try:
+            fill = sampling if sampling is not None else _greedy_rows
+            build_context(entries, self.cache, self.staging, pad_tokens=bucket, out=graph.buffer,
+                          sampling=fill)
+            graph.replay()
+            self.launches.total += graph.kernels_per_replay
+        except BaseException:
+            self.cache.rollback(plan)
+            raise
+        self.cache.commit(plan)
+        self.steps_run += 1
+        return graph.tokens[:len(entries)]
+
+    def decode_logits(self, entries: Sequence[StepEntry]) -> torch.Tensor:
+        """The logits of the last :meth:`decode_step` for its entries."""
+        bucket = self.decode_bucket(len(entries))
+        return self._graphs[bucket].logits[:len(entries)]
+
+
+def _greedy_rows(host, where) -> None:
+    host[where["top_p"]] = np.float32(1.0).view(np.int32)
+    host[where["penalty"]] = np.float32(1.0).view(np.int32)
+    host[where["recent"]] = -1
+
+
+class DecodeGraph:
+    """A captured decode step of a fixed number of rows: every request brings one token, the
+    model runs, one token per row is chosen.  Its inputs live in one static int32 buffer that each
+    replay refills; rows beyond the live requests are padding (position -1, no cache slot)."""
+
+    def __init__(self, executor: "Executor", rows: int):
+        from ..kernels import ops
+        from .batch import RECENT, GroupView, StepContext, layout
+        self.rows = rows
+        cache, model, device = executor.cache, executor.model, executor.device
+        keys = list(cache.groups)
+        self.where = where = layout(rows, rows, len(keys), rows)
+        self.buffer = torch.zeros(where["_size"].stop, dtype=torch.int32, device=device)
+        buf = self.buffer
+        buf[where["positions"]] = -1
+        for g in range(len(keys)):
+            buf[where[f"slot_mapping{g}"]] = -1
+        buf[where["recent"]] = -1
+        f32 = lambda name: buf[where[name]].view(torch.float32)
+        buf[where["top_p"]] = torch.ones(rows, dtype=torch.float32, device=device).view(torch.int32)
+        buf[where["penalty"]] = torch.ones(rows, dtype=torch.float32, device=device).view(torch.int32)
+        self.row_index = torch.arange(rows, dtype=torch.int32, device=device)
+        groups = {key: GroupView(cache.groups[key].table_device, buf[where[f"slot_mapping{g}"]],
+                                 cache.groups[key].max_blocks) for g, key in enumerate(keys)}
+        self.ctx = StepContext(
+            num_tokens=rows, num_segments=rows, segments=[], token_ids=buf[where["token_ids"]],
+            positions=buf[where["positions"]], token_slot=buf[where["token_slot"]],
+            seg_q_start=buf[where["seg_q_start"]], seg_kv_len=buf[where["seg_kv_len"]],
+            seg_slot=buf[where["seg_slot"]], groups=groups, max_q_len=1,
+            max_kv_len=executor.spec.max_positions, page_size=cache.page_size)
+        self.tokens = torch.zeros(rows, dtype=torch.int32, device=device)
+
+        def run():
+            self.ctx.shared.clear()
+            logits = model.forward(self.ctx, cache.entries, self.row_index)
+            ops.repetition_penalty(logits, buf[where["recent"]].view(rows, RECENT), f32("penalty"))
+            ops.sample(logits, self.tokens, temperature=f32("temperature"), top_p=f32("top_p"),
+                       top_k=buf[where["top_k"]], min_p=f32("min_p"),
+                       keys=buf[where["keys"]].view(torch.int64))
+            return logits
+
+        executor.launches.begin()
+        run()                               # all rows are padding: nothing is written to the cache
+        self.kernels_per_replay = executor.launches.end()
+        torch.cuda.synchronize(device)
+        self.graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(self.graph):
+            self.logits = run()
+        torch.cuda.synchronize(device)
+
+    def replay(self) -> None:
+        self.graph.replay()

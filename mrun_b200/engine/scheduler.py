@@ -1,0 +1,299 @@
+"""The scheduler: admits requests, cuts prompts into portions under a token budget, lets every
+running request decode, finishes requests and frees what they hold.  Host-side only; it decides,
+the executor computes.
+
+Decisions, with the reference's where it has one
+------------------------------------------------
+* **Refusals** at submission: empty prompt, ``max_tokens`` 0, invalid sampling → ``invalid``; a
+  prompt that leaves no room for one output token in the cache → ``too_long``; the output limit is
+  clamped to what remains (crates/mrun/src/runtime/generate.rs:522-532, 600-636).  A full waiting
+  queue refuses with ``queue_full`` (crates/mrun/src/runtime/queue.rs:80-91).
+* **Admission** is first come, first served: a request starts when a state slot is free and, with
+  ``reserve`` on, when the pages for its prompt plus its clamped output limit fit beside what the
+  running requests have reserved (crates/mrun/src/runtime/handle.rs:497-559).  With reservations
+  a running request never runs out of pages.
+* **A step** holds one token of every running request that has finished its prompt, plus prompt
+  portions while the token budget lasts, the request with the fewest prompt tokens left first,
+  ties by admission order (crates/mrun/src/runtime/lanes.rs:187-196).  A portion is at most
+  ``chunk_len(depth)`` = clamp(budget · 16384 / depth, 128, budget) tokens
+  (crates/mrun-engine/src/engine.rs:481-486).  The portion that ends a prompt asks for the logits
+  of its last token.  Unlike the reference, portions and decoded tokens share one batch.
+* **When pages run out** (only with ``reserve`` off): the running request admitted last gives
+  everything back and returns to the head of the queue; when it is admitted again it feeds its
+  prompt and what it had generated as one prompt.  Requests admitted earlier are never touched,
+  and a request that runs alone always fits because of the refusal above.
+* **Finishing**: an end token (unless ``ignore_eos``) → ``stop``; the output limit → ``length``;
+  the last 512 output tokens repeating with a period of at most 256, checked every 16 tokens →
+  ``repetition`` (crates/mrun/src/runtime/generate.rs:27-33, 420-426, 866-919).
+"""
+from __future__ import annotations
+
+import time
+from collections import deque
+from dataclasses import dataclass, field
+from typing import Deque, Dict, List, Optional, Sequence, Tuple
+
+from ..cache.manager import CacheManager, RequestCache
+from ..sampling.params import GREEDY, SamplingParams, fresh_seed
+
+LOOP_WINDOW, LOOP_MAX_PERIOD, LOOP_CHECK_EVERY = 512, 256, 16
+
+
+def chunk_len(depth: int, budget: int = 2048) -> int:
+    """Longest prompt portion at ``depth`` tokens already in the cache."""
+    return max(min(128, budget), min(budget, budget * 16384 // max(depth, 1)))
+
+
+def looping(output: Sequence[int]) -> bool:
+    if len(output) < LOOP_WINDOW:
+        return False
+    window = output[-LOOP_WINDOW:]
+    return any(all(window[i] == window[i - p] for i in range(p, LOOP_WINDOW))
+               for p in range(1, LOOP_MAX_PERIOD + 1))
+
+
+@dataclass
+class Request:
+    request_id: object
+    prompt: List[int]
+    max_tokens: int = 2048
+    sampling: SamplingParams = GREEDY
+    ignore_eos: bool = False
+    # ---- run state
+    state: str = "new"                 # new | waiting | running | finished
+    output: List[int] = field(default_factory=list)
+    fed: int = 0                       # tokens of prompt + output that are in the cache
+    limit: int = 0                     # clamped output limit
+    seed: int = 0
+    cache: Optional[RequestCache] = None
+    finish_reason: Optional[str] = None
+    message: str = ""
+    order: int = -1                    # admission order
+    reserved_pages: int = 0
+    preemptions: int = 0
+    submitted_at: float = 0.0
+    first_token_at: float = 0.0
+    finished_at: float = 0.0
+    token_times: List[float] = field(default_factory=list)   # when each output token was read back
+
+    @property
+    def sequence_len(self) -> int:
+        return len(self.prompt) + len(self.output)
+
+    @property
+    def remaining(self) -> int:
+        return self.sequence_len - self.fed
+
+    def next_tokens(self, n: int) -> List[int]:
+        start = self.fed
+        p = len(self.prompt)
+        if start + n <= p:
+            return self.prompt[start:start + n]
+        if start >= p:
+            return self.output[start - p:start - p + n]
+        return self.prompt[start:] + self.output[:start + n - p]
+
+    def recent(self, n: int) -> List[int]:
+        if len(self.output) >= n:
+            return self.output[-n:]
+        return (self.prompt + self.output)[-n:]
+
+
+@dataclass
+class PlannedEntry:
+    request: Request
+    tokens: List[int]
+    wants_logits: bool
+
+
+@dataclass
+class StepPlan:
+    entries: List[PlannedEntry]
+
+    @property
+    def num_tokens(self) -> int:
+        return sum(len(e.tokens) for e in self.entries)
+
+    @property
+    def sampled(self) -> List[Request]:
+        return [e.request for e in self.entries if e.wants_logits]
+
+
+class Scheduler:
+    def __init__(self, cache: CacheManager, eos_token_ids: Sequence[int] = (), max_batch_tokens: int = 2048,
+                 max_running: Optional[int] = None, max_queue: Optional[int] = None, reserve: bool = True,
+                 max_positions: Optional[int] = None):
+        if max_batch_tokens < 1:
+            raise ValueError(f"max_batch_tokens must be at least 1, got {max_batch_tokens}")
+        self.cache = cache
+        self.eos = frozenset(eos_token_ids)
+        self.max_batch_tokens = max_batch_tokens
+        self.max_running = min(max_running or cache.max_requests, cache.max_requests)
+        self.max_queue = max_queue
+        self.reserve = reserve
+        self.capacity_tokens = cache.num_pages * cache.page_size
+        if max_positions is not None:
+            self.capacity_tokens = min(self.capacity_tokens, max_positions)
+        self.waiting: Deque[Request] = deque()
+        self.running: List[Request] = []
+        self.finished: List[Request] = []
+        self._admitted = 0
+        self._reserved = 0
+        self.preemptions = 0
+
+    # ------------------------------------------------------------------ submission
+    def submit(self, request: Request) -> Optional[str]:
+        """Queues the request, or finishes it at once with a refusal (returned)."""
+        request.submitted_at = time.perf_counter()
+        reason = None
+        if len(request.prompt) == 0:
+            reason, request.message = "invalid", "the prompt is empty"
+        elif request.max_tokens < 1:
+            reason, request.message = "invalid", "max tokens must be at least 1"
+        else:
+            try:
+                request.sampling.validate()
+            except ValueError as error:
+                reason, request.message = "invalid", str(error)
+        if reason is None:
+            room = self.capacity_tokens - len(request.prompt)
+            if room < 1:
+                reason = "too_long"
+                request.message = (f"prompt is too long: {len(request.prompt)} tokens, the cache holds "
+                                   f"{self.capacity_tokens}")
+            else:
+                request.limit = min(request.max_tokens, room)
+        if reason is None and self.max_queue is not None and len(self.waiting) >= self.max_queue:
+            reason, request.message = "queue_full", f"{len(self.waiting)} requests are waiting already"
+        if reason is not None:
+            self._finish(request, reason)
+            return reason
+        request.seed = request.sampling.seed if request.sampling.seed is not None else fresh_seed()
+        request.state = "waiting"
+        self.waiting.append(request)
+        return None
+
+    def has_work(self) -> bool:
+        return bool(self.waiting or self.running)
+
+    # ------------------------------------------------------------------ admission
+    def _need_pages(self, request: Request) -> int:
+        return self.cache.blocks_for(len(request.prompt) + request.limit)
+
+    def _can_admit(self, request: Request) -> bool:
+        if len(self.running) >= self.max_running or self.cache.free_slots < 1:
+            return False
+        if self.reserve:
+            return self._reserved + self._need_pages(request) <= self.cache.num_pages
+        # on demand: room for its whole sequence and one more page, beside what the running
+        # requests still have to bring in
+        outstanding = sum(self.cache.blocks_for(r.sequence_len) - self.cache.blocks_for(r.fed)
+                          for r in self.running)
+        return self.cache.free_pages() - outstanding >= self.cache.blocks_for(request.sequence_len) + 1 \
+            or not self.running
+
+    def _admit(self) -> None:
+        while self.waiting and self._can_admit(self.waiting[0]):
+            request = self.waiting.popleft()
+            request.cache = self.cache.admit(request.request_id)
+            request.state = "running"
+            request.fed = 0
+            if request.order < 0:
+                request.order = self._admitted
+                self._admitted += 1
+            if self.reserve:
+                request.reserved_pages = self._need_pages(request)
+                self._reserved += request.reserved_pages
+            self.running.append(request)
+
+    # ------------------------------------------------------------------ one step
+    def schedule(self) -> Optional[StepPlan]:
+        self._admit()
+        if not self.running:
+            return None
+        budget = self.max_batch_tokens
+        entries: List[PlannedEntry] = []
+        decoders = [r for r in self.running if r.remaining == 1 and r.fed > 0]
+        for request in decoders[:budget]:
+            entries.append(PlannedEntry(request, request.next_tokens(1), True))
+        budget -= len(entries)
+        readers = sorted((r for r in self.running if not (r.remaining == 1 and r.fed > 0)),
+                         key=lambda r: (r.remaining, r.order))
+        for request in readers:
+            if budget < 1:
+                break
+            n = min(request.remaining, budget, chunk_len(request.fed, self.max_batch_tokens))
+            entries.append(PlannedEntry(request, request.next_tokens(n), n == request.remaining))
+            budget -= n
+        return StepPlan(entries) if entries else None
+
+    def complete(self, plan: StepPlan, sampled: Sequence[int]) -> List[Request]:
+        """Records a finished step: ``sampled`` holds one token per entry that wanted logits, in
+        order.  Returns the requests that finished."""
+        now = time.perf_counter()
+        done: List[Request] = []
+        sampled = list(sampled)
+        if len(sampled) != len(plan.sampled):
+            raise ValueError(f"{len(plan.sampled)} tokens were wanted, {len(sampled)} came")
+        at = 0
+        for entry in plan.entries:
+            request = entry.request
+            request.fed += len(entry.tokens)
+            if not entry.wants_logits:
+                continue
+            token = int(sampled[at])
+            at += 1
+            if not request.output:
+                request.first_token_at = now
+            request.output.append(token)
+            request.token_times.append(now)
+            reason = None
+            if token in self.eos and not request.ignore_eos:
+                reason = "stop"
+            elif len(request.output) >= request.limit:
+                reason = "length"
+            elif len(request.output) % LOOP_CHECK_EVERY == 0 and looping(request.output):
+                reason = "repetition"
+            if reason is not None:
+                self._retire(request)
+                self._finish(request, reason)
+                done.append(request)
+        return done
+
+    # ------------------------------------------------------------------ out of pages
+    def preempt_newest(self) -> Optional[Request]:
+        """Gives back everything the running request admitted last holds and puts it at the head
+        of the queue.  None when at most one request runs (it is never preempted)."""
+        if len(self.running) <= 1:
+            return None
+        victim = max(self.running, key=lambda r: r.order)
+        self._retire(victim)
+        victim.state = "waiting"
+        victim.fed = 0
+        victim.preemptions += 1
+        self.preemptions += 1
+        self.waiting.appendleft(victim)
+        return victim
+
+    def abort(self, request: Request, message: str = "") -> None:
+        if request.state == "running":
+            self._retire(request)
+        elif request.state == "waiting":
+            self.waiting.remove(request)
+        request.message = message
+        self._finish(request, "aborted")
+
+    # ------------------------------------------------------------------ internals
+    def _retire(self, request: Request) -> None:
+        self.running.remove(request)
+        if request.cache is not None:
+            self.cache.release(request.cache)
+            request.cache = None
+        self._reserved -= request.reserved_pages
+        request.reserved_pages = 0
+
+    def _finish(self, request: Request, reason: str) -> None:
+        request.state = "finished"
+        request.finish_reason = reason
+        request.finished_at = time.perf_counter()
+        self.finished.append(request)

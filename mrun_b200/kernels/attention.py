@@ -16,4 +16,4 @@ def paged_attention(q: torch.Tensor, q_stride: int, out: torch.Tensor, cache, gr
     """``q``: the step's queries (row t at ``q_stride * t``, heads contiguous); ``cache``: the
     schedule entry's pages; ``group``: the step's block tables for the cache's group."""
     return ops.paged_attention_generic(q, q_stride, out, cache.k, cache.v, group.block_tables,
-                                       ctx.token_seg, ctx.positions, heads, scale, window)
+                                       ctx.token_slot, ctx.positions, heads, scale, window)

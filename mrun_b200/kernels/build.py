@@ -128,6 +128,13 @@ def build_library(name: str, source_names: Iterable[str],
                 raise BuildError(f"linking {os.path.basename(target)} failed:\n{proc.stdout}")
             os.replace(tmp, target)
             _say(f"built {os.path.basename(target)}")
+            prefix = f"lib{name}_"
+            for other in os.listdir(os.path.dirname(target)):      # builds of older sources
+                if other.startswith(prefix) and other.endswith(".so") and other != os.path.basename(target):
+                    try:
+                        os.remove(os.path.join(os.path.dirname(target), other))
+                    except OSError:
+                        pass
         finally:
             shutil.rmtree(work, ignore_errors=True)
         return target
@@ -138,3 +145,8 @@ CORE_SOURCES = ("common.cu", "elementwise.cu", "gemm_f32.cu", "attention_generic
 
 def build_core() -> str:
     return build_library("mrun_core", CORE_SOURCES)
+
+
+def build_all() -> list[str]:
+    """Every library the package can load (the build check compiles them all)."""
+    return [build_core()]

@@ -41,8 +41,18 @@ class Library:
         return fn
 
     def call(self, name: str, *args) -> None:
+        global _calls
+        _calls += 1
         if self.function(name)(*args) != 0:
             raise KernelError(self._last_error().decode("utf-8", "replace"))
+
+
+_calls = 0
+
+
+def call_count() -> int:
+    """How many kernel entry points were called so far (each launches this library's kernels)."""
+    return _calls
 
 
 _core: Library | None = None

@@ -122,28 +122,29 @@ def qk_norm_rope_cache(qkv: torch.Tensor, heads: int, kv_heads: int, head_dim: i
 
 
 def paged_attention_generic(q: torch.Tensor, q_stride: int, out: torch.Tensor, k_cache: torch.Tensor,
-                            v_cache: torch.Tensor, block_tables: torch.Tensor, token_seg: torch.Tensor,
+                            v_cache: torch.Tensor, block_tables: torch.Tensor, token_slot: torch.Tensor,
                             positions: torch.Tensor, heads: int, scale: float, window: int = 0) -> torch.Tensor:
     """Attention of every token over its request's pages, 32-bit arithmetic on CUDA cores.
 
     ``q`` may be a view into a wider buffer: row t starts ``q_stride`` elements after row t-1.
+    ``block_tables`` has one row per state slot; ``token_slot[t]`` names the row of token t.
     """
     _check(q, "q", dense=False); _check(out, "out", q.dtype)
     _check(k_cache, "k_cache", q.dtype); _check(v_cache, "v_cache", q.dtype)
-    _check(block_tables, "block_tables", torch.int32); _check(token_seg, "token_seg", torch.int32)
+    _check(block_tables, "block_tables", torch.int32); _check(token_slot, "token_slot", torch.int32)
     _check(positions, "positions", torch.int32)
     pages, kv_heads, page_size, head_dim = k_cache.shape
     tokens = positions.numel()
     if v_cache.shape != k_cache.shape:
         raise KernelError("paged_attention: k and v caches differ in shape")
-    if out.shape != (tokens, heads * head_dim) or token_seg.numel() != tokens:
-        raise KernelError(f"paged_attention: out {tuple(out.shape)} / token_seg {token_seg.numel()} "
+    if out.shape != (tokens, heads * head_dim) or token_slot.numel() != tokens:
+        raise KernelError(f"paged_attention: out {tuple(out.shape)} / token_slot {token_slot.numel()} "
                           f"do not match {tokens} tokens of {heads}x{head_dim}")
     if block_tables.dim() != 2:
-        raise KernelError("paged_attention: block_tables must be [segments, max_blocks]")
+        raise KernelError("paged_attention: block_tables must be [slots, max_blocks]")
     _lib.core().call("mrun_paged_attention_generic", _ptr(q), _c_long(q_stride), _ptr(out), _ptr(k_cache),
                      _ptr(v_cache), dtype_code(q.dtype), _ptr(block_tables), _c_int(block_tables.shape[1]),
-                     _ptr(token_seg), _ptr(positions), _c_int(tokens), _c_int(heads), _c_int(kv_heads),
+                     _ptr(token_slot), _ptr(positions), _c_int(tokens), _c_int(heads), _c_int(kv_heads),
                      _c_int(head_dim), _c_int(page_size), _c_long(pages * kv_heads * page_size),
                      _c_float(scale), _c_int(window), _stream())
     return out
@@ -218,3 +219,12 @@ def repetition_penalty(logits: torch.Tensor, recent: torch.Tensor, penalty: torc
         raise KernelError(f"repetition_penalty: recent {tuple(recent.shape)}, penalty {penalty.numel()}, rows {rows}")
     _lib.core().call("mrun_repetition_penalty", _ptr(logits), _c_int(rows), _c_int(vocab), _ptr(recent),
                      _c_int(recent.shape[1]), _ptr(penalty), _stream())
+
+
+def scatter_i32(dst: torch.Tensor, index: torch.Tensor, value: torch.Tensor) -> None:
+    """dst.view(-1)[index[i]] = value[i] for int32 tensors."""
+    _check(dst, "dst", torch.int32); _check(index, "index", torch.int32); _check(value, "value", torch.int32)
+    if index.numel() != value.numel():
+        raise KernelError("scatter_i32: index and value differ in length")
+    _lib.core().call("mrun_scatter_i32", _ptr(dst), _ptr(index), _ptr(value), _c_int(index.numel()),
+                     _c_long(dst.numel()), _stream())
