@@ -1,0 +1,504 @@
+// Paged grouped-query attention on the tensor cores (bf16 operands, 32-bit accumulation and
+// softmax), compiled for one head size: -DMRUN_HEAD_DIM=<multiple of 16, at most 256>.
+//
+// Two kernels share the tile loader and the fragment code:
+//
+//  * prefill: one block per (tile of query tokens, kv head).  The tile's rows are (token, query
+//    head of the kv head's group) pairs, 64 rows, so a key/value tile read once serves the whole
+//    group.  Keys are consumed 64 at a time in position order with an online softmax.
+//  * decode: one block per (token, kv head, split of the keys).  The rows are the group's query
+//    heads of one token (at most 16); the four warps take different 16-key slices of each
+//    64-key tile and are merged at the end; splits are merged by a second kernel through
+//    scratch memory (32-bit partial outputs with their running max and sum).
+//
+// Both read keys and values from the pages (cache[page, kv_head, offset, :]) through the block
+// table of the token's state slot.  A token at position p sees keys lo..p, lo = 0 or
+// p - window + 1.  Keys outside that range, and pages that were given back, are never
+// dereferenced: their tile rows are zero-filled.
+//
+// Math as in the CUDA-core kernel: s = scale * q·k, softmax in 32-bit, o = p·v
+// (crates/mrun-engine/src/models/common.rs:129,199-205).  P is rounded to bf16 for the second
+// product, as the tensor cores take bf16 operands.
+#include <mma.h>
+
+#include "common.cuh"
+
+#ifndef MRUN_HEAD_DIM
+#error "compile with -DMRUN_HEAD_DIM=<head size>"
+#endif
+
+namespace {
+
+constexpr int D = MRUN_HEAD_DIM;
+static_assert(D % 16 == 0 && D >= 16 && D <= 256, "head size must be a multiple of 16, at most 256");
+constexpr int LD = D + 8;            // smem row stride in elements: odd number of 16-byte chunks
+constexpr int BLOCK_N = 64;          // keys per tile
+constexpr int THREADS = 128;
+constexpr int CHUNKS = D / 8;        // 16-byte chunks per row
+constexpr float LOG2E = 1.4426950408889634f;
+
+using bf16 = __nv_bfloat16;
+
+__device__ __forceinline__ unsigned smem_addr(const void* p) {
+    return (unsigned)__cvta_generic_to_shared(p);
+}
+__device__ __forceinline__ void cp_async_16(void* dst, const void* src, bool valid) {
+    const int bytes = valid ? 16 : 0;   // 0 source bytes: the 16 destination bytes become zero
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(smem_addr(dst)), "l"(src), "r"(bytes));
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::); }
+template <int N> __device__ __forceinline__ void cp_async_wait() {
+    asm volatile("cp.async.wait_group %0;\n" ::"n"(N));
+}
+__device__ __forceinline__ void ldmatrix_x4(unsigned (&r)[4], const void* p) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(smem_addr(p)));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(unsigned (&r)[4], const void* p) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(smem_addr(p)));
+}
+__device__ __forceinline__ void mma_bf16(float (&c)[4], const unsigned (&a)[4], unsigned b0, unsigned b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ unsigned pack_bf16(float lo, float hi) {
+    __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<unsigned*>(&v);
+}
+
+// Loads keys key0 .. key0+63 of one kv head into a [64][LD] tile.  Rows whose key lies outside
+// [lo, hi] or whose page is not held are zero-filled.
+__device__ __forceinline__ void load_kv_tile(bf16* tile, const bf16* __restrict__ cache,
+                                             const int* __restrict__ table, int key0, int lo, int hi,
+                                             int kv_heads, int kvh, int page_size) {
+    for (int c = threadIdx.x; c < BLOCK_N * CHUNKS; c += THREADS) {
+        const int row = c / CHUNKS, chunk = c - row * CHUNKS;
+        const int key = key0 + row;
+        bool valid = key >= lo && key <= hi;
+        const bf16* src = cache;
+        if (valid) {
+            const int page = table[key / page_size];
+            valid = page >= 0;
+            if (valid)
+                src = cache + (((size_t)page * kv_heads + kvh) * page_size + key % page_size) * D + chunk * 8;
+        }
+        cp_async_16(tile + row * LD + chunk * 8, src, valid);
+    }
+}
+
+// One 16-row warp tile against `n_keys` (a multiple of 16) keys of a K tile and V tile starting
+// at tile row `krow0`: scores, mask, online softmax update, and o += p·v.
+//   q_tile: the warp's 16 rows [16][LD] in smem.   row_pos/row_lo: visible key range of the
+//   thread's two rows (row g and g + 8); row_pos < 0 marks a padding row.
+template <int N_KEYS>
+__device__ __forceinline__ void attend_tile(const bf16* q_tile, const bf16* k_tile, const bf16* v_tile,
+                                            int krow0, int key_base, float scale_log2, bool need_mask,
+                                            const int (&row_pos)[2], const int (&row_lo)[2],
+                                            float (&m)[2], float (&l)[2], float (&o)[D / 8][4]) {
+    constexpr int NT = N_KEYS / 8;     // score n-tiles
+    const int lane = threadIdx.x & 31;
+    float s[NT][4];
+#pragma unroll
+    for (int i = 0; i < NT; ++i) s[i][0] = s[i][1] = s[i][2] = s[i][3] = 0.f;
+
+#pragma unroll
+    for (int kk = 0; kk < D / 16; ++kk) {
+        unsigned a[4];
+        ldmatrix_x4(a, q_tile + ((lane & 7) + ((lane >> 3) & 1) * 8) * LD + kk * 16 + (lane >> 4) * 8);
+#pragma unroll
+        for (int nt = 0; nt < NT; nt += 2) {
+            unsigned b[4];
+            ldmatrix_x4(b, k_tile + (krow0 + nt * 8 + (lane & 7) + (lane >> 4) * 8) * LD + kk * 16 + ((lane >> 3) & 1) * 8);
+            mma_bf16(s[nt], a, b[0], b[1]);
+            mma_bf16(s[nt + 1], a, b[2], b[3]);
+        }
+    }
+
+    // scale, mask, row maxima
+    float mx[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt) {
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            const int r = e >> 1;
+            float v = s[nt][e] * scale_log2;
+            if (need_mask) {
+                const int key = key_base + krow0 + nt * 8 + (lane & 3) * 2 + (e & 1);
+                if (key > row_pos[r] || key < row_lo[r]) v = -INFINITY;
+            }
+            s[nt][e] = v;
+            mx[r] = fmaxf(mx[r], v);
+        }
+    }
+    float corr[2];
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+        mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 1));
+        mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 2));
+        const float m_new = fmaxf(m[r], mx[r]);
+        corr[r] = (m[r] == -INFINITY) ? 0.f : exp2f(m[r] - m_new);
+        m[r] = m_new;
+    }
+    float sum[2] = {0.f, 0.f};
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt) {
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            const int r = e >> 1;
+            const float p = (m[r] == -INFINITY) ? 0.f : exp2f(s[nt][e] - m[r]);
+            s[nt][e] = p;
+            sum[r] += p;
+        }
+    }
+#pragma unroll
+    for (int r = 0; r < 2; ++r) l[r] = l[r] * corr[r] + sum[r];   // per-thread partial; reduced at the end
+#pragma unroll
+    for (int dt = 0; dt < D / 8; ++dt) {
+        o[dt][0] *= corr[0]; o[dt][1] *= corr[0];
+        o[dt][2] *= corr[1]; o[dt][3] *= corr[1];
+    }
+
+    // o += p · v
+#pragma unroll
+    for (int kk = 0; kk < N_KEYS / 16; ++kk) {
+        unsigned a[4];
+        a[0] = pack_bf16(s[2 * kk][0], s[2 * kk][1]);
+        a[1] = pack_bf16(s[2 * kk][2], s[2 * kk][3]);
+        a[2] = pack_bf16(s[2 * kk + 1][0], s[2 * kk + 1][1]);
+        a[3] = pack_bf16(s[2 * kk + 1][2], s[2 * kk + 1][3]);
+#pragma unroll
+        for (int dt = 0; dt < D / 8; dt += 2) {
+            unsigned b[4];
+            ldmatrix_x4_trans(b, v_tile + (krow0 + kk * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * LD + dt * 8 + (lane >> 4) * 8);
+            mma_bf16(o[dt], a, b[0], b[1]);
+            mma_bf16(o[dt + 1], a, b[2], b[3]);
+        }
+    }
+}
+
+// ------------------------------------------------------------------------------------------
+// Prefill: 64 rows = tokens_per_tile tokens x group heads.
+// ------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(THREADS)
+prefill_kernel(const bf16* __restrict__ q, long q_stride, bf16* __restrict__ out,
+               const bf16* __restrict__ k_cache, const bf16* __restrict__ v_cache,
+               const int* __restrict__ block_tables, int max_blocks, const int* __restrict__ token_slot,
+               const int* __restrict__ positions, const int* __restrict__ tile_tok0,
+               const int* __restrict__ tile_ntok, int heads, int kv_heads, int page_size,
+               float scale_log2, int window) {
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    bf16* q_tile = reinterpret_cast<bf16*>(smem_raw);           // [64][LD]
+    bf16* k_tiles = q_tile + 64 * LD;                           // [2][64][LD]
+    bf16* v_tiles = k_tiles + 2 * BLOCK_N * LD;                 // [2][64][LD]
+
+    const int tile = blockIdx.x, kvh = blockIdx.y;
+    const int group = heads / kv_heads;
+    const int tok0 = tile_tok0[tile], ntok = tile_ntok[tile];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int* table = block_tables + (size_t)token_slot[tok0] * max_blocks;
+    const int n_rows = ntok * group;
+
+    // tokens of a tile are consecutive positions of one request
+    const int pos_first = positions[tok0], pos_last = pos_first + ntok - 1;
+    const int lo_tile = (window > 0 && pos_first - window + 1 > 0) ? pos_first - window + 1 : 0;
+    const int first_block = lo_tile / BLOCK_N, last_block = pos_last / BLOCK_N;
+
+    // q rows: row r = (token r / group, head kvh * group + r % group)
+    for (int c = threadIdx.x; c < 64 * CHUNKS; c += THREADS) {
+        const int row = c / CHUNKS, chunk = c - row * CHUNKS;
+        const bool valid = row < n_rows;
+        const bf16* src = q;
+        if (valid)
+            src = q + (size_t)(tok0 + row / group) * q_stride + (size_t)(kvh * group + row % group) * D + chunk * 8;
+        cp_async_16(q_tile + row * LD + chunk * 8, src, valid);
+    }
+    load_kv_tile(k_tiles, k_cache, table, first_block * BLOCK_N, lo_tile, pos_last, kv_heads, kvh, page_size);
+    load_kv_tile(v_tiles, v_cache, table, first_block * BLOCK_N, lo_tile, pos_last, kv_heads, kvh, page_size);
+    cp_async_commit();
+
+    int row_pos[2], row_lo[2];
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+        const int row = warp * 16 + (lane >> 2) + r * 8;
+        row_pos[r] = row < n_rows ? pos_first + row / group : -1;
+        row_lo[r] = (window > 0 && row_pos[r] - window + 1 > 0) ? row_pos[r] - window + 1 : 0;
+    }
+    // the warp's rows span tokens [w_first, w_last]: blocks above w_last's position are skipped
+    const int w_row0 = warp * 16;
+    const bool warp_active = w_row0 < n_rows;
+    const int w_pos_last = pos_first + (min(w_row0 + 15, n_rows - 1)) / group;
+    const int w_pos_first = pos_first + w_row0 / group;
+
+    float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
+    float o[D / 8][4];
+#pragma unroll
+    for (int dt = 0; dt < D / 8; ++dt) o[dt][0] = o[dt][1] = o[dt][2] = o[dt][3] = 0.f;
+
+    for (int block = first_block; block <= last_block; ++block) {
+        const int stage = (block - first_block) & 1;
+        if (block < last_block) {
+            load_kv_tile(k_tiles + (stage ^ 1) * BLOCK_N * LD, k_cache, table, (block + 1) * BLOCK_N, lo_tile,
+                         pos_last, kv_heads, kvh, page_size);
+            load_kv_tile(v_tiles + (stage ^ 1) * BLOCK_N * LD, v_cache, table, (block + 1) * BLOCK_N, lo_tile,
+                         pos_last, kv_heads, kvh, page_size);
+            cp_async_commit();
+            cp_async_wait<1>();
+        } else {
+            cp_async_wait<0>();
+        }
+        __syncthreads();
+        const int key_base = block * BLOCK_N;
+        if (warp_active && key_base <= w_pos_last) {
+            const int w_lo = (window > 0 && w_pos_first - window + 1 > 0) ? w_pos_first - window + 1 : 0;
+            if (key_base + BLOCK_N - 1 >= w_lo) {
+                // full visibility for every row of the warp needs no mask
+                const int w_lo_last = (window > 0 && w_pos_last - window + 1 > 0) ? w_pos_last - window + 1 : 0;
+                const bool need_mask = key_base + BLOCK_N - 1 > w_pos_first || key_base < w_lo_last;
+                attend_tile<BLOCK_N>(q_tile + w_row0 * LD, k_tiles + stage * BLOCK_N * LD,
+                                     v_tiles + stage * BLOCK_N * LD, 0, key_base, scale_log2, need_mask, row_pos,
+                                     row_lo, m, l, o);
+            }
+        }
+        __syncthreads();
+    }
+
+    // finish the row sums over the quad, normalise, stage through q_tile, write coalesced
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+        l[r] += __shfl_xor_sync(0xffffffffu, l[r], 1);
+        l[r] += __shfl_xor_sync(0xffffffffu, l[r], 2);
+    }
+    const float inv0 = l[0] > 0.f ? 1.f / l[0] : 0.f, inv1 = l[1] > 0.f ? 1.f / l[1] : 0.f;
+    bf16* stage_rows = q_tile + w_row0 * LD;
+#pragma unroll
+    for (int dt = 0; dt < D / 8; ++dt) {
+        const int col = dt * 8 + (lane & 3) * 2;
+        *reinterpret_cast<unsigned*>(stage_rows + (lane >> 2) * LD + col) = pack_bf16(o[dt][0] * inv0, o[dt][1] * inv0);
+        *reinterpret_cast<unsigned*>(stage_rows + ((lane >> 2) + 8) * LD + col) = pack_bf16(o[dt][2] * inv1, o[dt][3] * inv1);
+    }
+    __syncthreads();
+    for (int c = threadIdx.x; c < n_rows * CHUNKS; c += THREADS) {
+        const int row = c / CHUNKS, chunk = c - row * CHUNKS;
+        bf16* dst = out + ((size_t)(tok0 + row / group) * heads + kvh * group + row % group) * D + chunk * 8;
+        *reinterpret_cast<uint4*>(dst) = *reinterpret_cast<const uint4*>(q_tile + row * LD + chunk * 8);
+    }
+}
+
+// ------------------------------------------------------------------------------------------
+// Decode: 16 rows = the group's heads of one token; grid (tokens, kv_heads, splits).
+// part_o: [tokens, heads, splits, D] f32 (unnormalised), part_ml: [tokens, heads, splits, 2].
+// With splits == 1 the output is written directly.
+// ------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(THREADS)
+decode_kernel(const bf16* __restrict__ q, long q_stride, bf16* __restrict__ out,
+              const bf16* __restrict__ k_cache, const bf16* __restrict__ v_cache,
+              const int* __restrict__ block_tables, int max_blocks, const int* __restrict__ token_slot,
+              const int* __restrict__ positions, float* __restrict__ part_o, float* __restrict__ part_ml,
+              int heads, int kv_heads, int page_size, float scale_log2, int window) {
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    bf16* q_tile = reinterpret_cast<bf16*>(smem_raw);           // [16][LD]
+    bf16* k_tiles = q_tile + 16 * LD;                           // [2][64][LD]
+    bf16* v_tiles = k_tiles + 2 * BLOCK_N * LD;                 // [2][64][LD]
+    float* merge = reinterpret_cast<float*>(k_tiles);           // reused after the loop
+
+    const int tok = blockIdx.x, kvh = blockIdx.y, split = blockIdx.z, splits = gridDim.z;
+    const int group = heads / kv_heads;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int pos = positions[tok];
+
+    int first_block = 0, last_block = -1, lo = 0;
+    const int* table = block_tables;
+    if (pos >= 0) {
+        table = block_tables + (size_t)token_slot[tok] * max_blocks;
+        lo = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
+        const int b0 = lo / BLOCK_N, b1 = pos / BLOCK_N;
+        const int per = (b1 - b0 + splits) / splits;            // ceil((b1 - b0 + 1) / splits)
+        first_block = b0 + split * per;
+        last_block = min(b1, first_block + per - 1);
+    }
+
+    float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
+    float o[D / 8][4];
+#pragma unroll
+    for (int dt = 0; dt < D / 8; ++dt) o[dt][0] = o[dt][1] = o[dt][2] = o[dt][3] = 0.f;
+
+    if (first_block <= last_block) {
+        for (int c = threadIdx.x; c < 16 * CHUNKS; c += THREADS) {
+            const int row = c / CHUNKS, chunk = c - row * CHUNKS;
+            const bool valid = row < group;
+            const bf16* src = valid ? q + (size_t)tok * q_stride + (size_t)(kvh * group + row) * D + chunk * 8 : q;
+            cp_async_16(q_tile + row * LD + chunk * 8, src, valid);
+        }
+        load_kv_tile(k_tiles, k_cache, table, first_block * BLOCK_N, lo, pos, kv_heads, kvh, page_size);
+        load_kv_tile(v_tiles, v_cache, table, first_block * BLOCK_N, lo, pos, kv_heads, kvh, page_size);
+        cp_async_commit();
+
+        int row_pos[2], row_lo[2];
+#pragma unroll
+        for (int r = 0; r < 2; ++r) {
+            const int row = (lane >> 2) + r * 8;
+            row_pos[r] = row < group ? pos : -1;
+            row_lo[r] = lo;
+        }
+        for (int block = first_block; block <= last_block; ++block) {
+            const int stage = (block - first_block) & 1;
+            if (block < last_block) {
+                load_kv_tile(k_tiles + (stage ^ 1) * BLOCK_N * LD, k_cache, table, (block + 1) * BLOCK_N, lo, pos,
+                             kv_heads, kvh, page_size);
+                load_kv_tile(v_tiles + (stage ^ 1) * BLOCK_N * LD, v_cache, table, (block + 1) * BLOCK_N, lo, pos,
+                             kv_heads, kvh, page_size);
+                cp_async_commit();
+                cp_async_wait<1>();
+            } else {
+                cp_async_wait<0>();
+            }
+            __syncthreads();
+            const int key_base = block * BLOCK_N;
+            // warp w takes keys 16w .. 16w+15 of the tile
+            if (key_base + warp * 16 <= pos && key_base + warp * 16 + 15 >= lo)
+                attend_tile<16>(q_tile, k_tiles + stage * BLOCK_N * LD, v_tiles + stage * BLOCK_N * LD, warp * 16,
+                                key_base, scale_log2, true, row_pos, row_lo, m, l, o);
+            __syncthreads();
+        }
+    }
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+        l[r] += __shfl_xor_sync(0xffffffffu, l[r], 1);
+        l[r] += __shfl_xor_sync(0xffffffffu, l[r], 2);
+    }
+
+    // merge the four warps: merge[warp][16 rows][D + 2]
+    constexpr int MS = D + 2;
+    __syncthreads();
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+        const int row = (lane >> 2) + r * 8;
+        float* dst = merge + (warp * 16 + row) * MS;
+#pragma unroll
+        for (int dt = 0; dt < D / 8; ++dt) {
+            dst[dt * 8 + (lane & 3) * 2] = o[dt][2 * r];
+            dst[dt * 8 + (lane & 3) * 2 + 1] = o[dt][2 * r + 1];
+        }
+        if ((lane & 3) == 0) {
+            dst[D] = m[r];
+            dst[D + 1] = l[r];
+        }
+    }
+    __syncthreads();
+    for (int i = threadIdx.x; i < group * D; i += THREADS) {
+        const int row = i / D, d = i - row * D;
+        float mm = -INFINITY;
+#pragma unroll
+        for (int w = 0; w < 4; ++w) mm = fmaxf(mm, merge[(w * 16 + row) * MS + D]);
+        float acc = 0.f, ll = 0.f;
+#pragma unroll
+        for (int w = 0; w < 4; ++w) {
+            const float* src = merge + (w * 16 + row) * MS;
+            const float c = (src[D] == -INFINITY) ? 0.f : exp2f(src[D] - mm);
+            acc += src[d] * c;
+            ll += src[D + 1] * c;
+        }
+        const int head = kvh * group + row;
+        if (splits == 1) {
+            out[((size_t)tok * heads + head) * D + d] = __float2bfloat16_rn(ll > 0.f ? acc / ll : 0.f);
+        } else {
+            const size_t at = ((size_t)tok * heads + head) * splits + split;
+            part_o[at * D + d] = acc;
+            if (d == 0) {
+                part_ml[at * 2] = mm;
+                part_ml[at * 2 + 1] = ll;
+            }
+        }
+    }
+}
+
+// Merges the splits of one (token, head): one block of D threads.
+__global__ void combine_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
+                               bf16* __restrict__ out, int splits) {
+    const size_t th = blockIdx.x;
+    const int d = threadIdx.x;
+    float mm = -INFINITY;
+    for (int s = 0; s < splits; ++s) mm = fmaxf(mm, part_ml[(th * splits + s) * 2]);
+    float acc = 0.f, ll = 0.f;
+    for (int s = 0; s < splits; ++s) {
+        const float ms = part_ml[(th * splits + s) * 2];
+        const float c = (ms == -INFINITY) ? 0.f : exp2f(ms - mm);
+        acc += part_o[(th * splits + s) * D + d] * c;
+        ll += part_ml[(th * splits + s) * 2 + 1] * c;
+    }
+    out[th * D + d] = __float2bfloat16_rn(ll > 0.f ? acc / ll : 0.f);
+}
+
+constexpr size_t PREFILL_SMEM = (size_t)(64 + 4 * BLOCK_N) * LD * sizeof(bf16);
+constexpr size_t DECODE_SMEM = (size_t)(16 + 4 * BLOCK_N) * LD * sizeof(bf16);
+static_assert((size_t)4 * 16 * (D + 2) * sizeof(float) <= (size_t)4 * BLOCK_N * LD * sizeof(bf16),
+              "the warp merge area must fit in the key/value tiles");
+
+int check_common(const char* name, int heads, int kv_heads, int head_dim, int page_size, int max_blocks,
+                 int window, int max_group) {
+    MRUN_REQUIRE(head_dim == D, "%s: this library was built for head_dim=%d, got %d", name, D, head_dim);
+    MRUN_REQUIRE(heads > 0 && kv_heads > 0 && heads % kv_heads == 0,
+                 "%s: heads=%d must be a positive multiple of kv_heads=%d", name, heads, kv_heads);
+    MRUN_REQUIRE(heads / kv_heads <= max_group, "%s: %d query heads per kv head exceed the supported %d", name,
+                 heads / kv_heads, max_group);
+    MRUN_REQUIRE(page_size > 0 && max_blocks > 0 && window >= 0, "%s: bad page_size/max_blocks/window", name);
+    MRUN_REQUIRE(kv_heads <= 65535, "%s: kv_heads=%d exceeds 65535", name, kv_heads);
+    return 0;
+}
+
+}  // namespace
+
+MRUN_API int mrun_attn_head_dim() { return D; }
+
+// Tiles: tile i covers tokens tile_tok0[i] .. +tile_ntok[i]-1 (consecutive positions of one request,
+// at most 64 / (heads / kv_heads) of them).
+MRUN_API int mrun_attn_prefill(const void* q, long q_stride, void* out, const void* k_cache, const void* v_cache,
+                               const int* block_tables, int max_blocks, const int* token_slot,
+                               const int* positions, const int* tile_tok0, const int* tile_ntok, int n_tiles,
+                               int heads, int kv_heads, int head_dim, int page_size, float scale, int window,
+                               cudaStream_t stream) {
+    if (int rc = check_common("attn_prefill", heads, kv_heads, head_dim, page_size, max_blocks, window, 64)) return rc;
+    MRUN_REQUIRE(n_tiles >= 0, "attn_prefill: n_tiles=%d", n_tiles);
+    if (n_tiles == 0) return 0;
+    static bool configured = false;
+    if (!configured) {
+        MRUN_CHECK_CUDA(cudaFuncSetAttribute(prefill_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                             (int)PREFILL_SMEM), "attn_prefill");
+        configured = true;
+    }
+    prefill_kernel<<<dim3(n_tiles, kv_heads), THREADS, PREFILL_SMEM, stream>>>(
+        (const bf16*)q, q_stride, (bf16*)out, (const bf16*)k_cache, (const bf16*)v_cache, block_tables, max_blocks,
+        token_slot, positions, tile_tok0, tile_ntok, heads, kv_heads, page_size, scale * LOG2E, window);
+    MRUN_CHECK_LAUNCH("attn_prefill");
+    return 0;
+}
+
+// Every token is a row of its own (positions[t] < 0 = padding, output zero).  part_o and part_ml
+// are scratch of tokens * heads * splits * (D and 2) floats; they may be null when splits == 1.
+MRUN_API int mrun_attn_decode(const void* q, long q_stride, void* out, const void* k_cache, const void* v_cache,
+                              const int* block_tables, int max_blocks, const int* token_slot,
+                              const int* positions, int tokens, float* part_o, float* part_ml, int splits,
+                              int heads, int kv_heads, int head_dim, int page_size, float scale, int window,
+                              cudaStream_t stream) {
+    if (int rc = check_common("attn_decode", heads, kv_heads, head_dim, page_size, max_blocks, window, 16)) return rc;
+    MRUN_REQUIRE(tokens >= 0 && splits >= 1 && splits <= 65535, "attn_decode: tokens=%d splits=%d", tokens, splits);
+    MRUN_REQUIRE(splits == 1 || (part_o && part_ml), "attn_decode: %d splits need scratch memory", splits);
+    if (tokens == 0) return 0;
+    static bool configured = false;
+    if (!configured) {
+        MRUN_CHECK_CUDA(cudaFuncSetAttribute(decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                             (int)DECODE_SMEM), "attn_decode");
+        configured = true;
+    }
+    decode_kernel<<<dim3(tokens, kv_heads, splits), THREADS, DECODE_SMEM, stream>>>(
+        (const bf16*)q, q_stride, (bf16*)out, (const bf16*)k_cache, (const bf16*)v_cache, block_tables, max_blocks,
+        token_slot, positions, part_o, part_ml, heads, kv_heads, page_size, scale * LOG2E, window);
+    MRUN_CHECK_LAUNCH("attn_decode");
+    if (splits > 1) {
+        combine_kernel<<<tokens * heads, D, 0, stream>>>(part_o, part_ml, (bf16*)out, splits);
+        MRUN_CHECK_LAUNCH("attn_combine");
+    }
+    return 0;
+}

@@ -58,6 +58,8 @@ class StepContext:
     max_q_len: int
     max_kv_len: int
     page_size: int
+    real_tokens: int = 0         # rows that are not padding
+    upload: Optional[object] = None              # host int32 array -> device tensor (pinned staging)
     shared: dict = field(default_factory=dict)   # per-step results shared between layers
 
     def group(self, key: tuple) -> GroupView:
@@ -184,4 +186,5 @@ def build_context(entries: Sequence[StepEntry], manager: CacheManager, staging: 
         token_ids=dev[where["token_ids"]], positions=dev[where["positions"]],
         token_slot=dev[where["token_slot"]], seg_q_start=dev[where["seg_q_start"]],
         seg_kv_len=dev[where["seg_kv_len"]], seg_slot=dev[where["seg_slot"]], groups=groups,
-        max_q_len=max(lengths), max_kv_len=int(seg_kv_len.max()), page_size=page_size)
+        max_q_len=max(lengths), max_kv_len=int(seg_kv_len.max()), page_size=page_size,
+        real_tokens=real, upload=staging.upload)

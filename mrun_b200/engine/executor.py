@@ -192,7 +192,7 @@ class DecodeGraph:
             positions=buf[where["positions"]], token_slot=buf[where["token_slot"]],
             seg_q_start=buf[where["seg_q_start"]], seg_kv_len=buf[where["seg_kv_len"]],
             seg_slot=buf[where["seg_slot"]], groups=groups, max_q_len=1,
-            max_kv_len=executor.spec.max_positions, page_size=cache.page_size)
+            max_kv_len=executor.spec.max_positions, page_size=cache.page_size, real_tokens=rows)
         self.tokens = torch.zeros(rows, dtype=torch.int32, device=device)
 
         def run():

@@ -1,19 +1,81 @@
 """Chooses the attention kernel for a step and launches it.
 
 Every kernel reads keys and values from the pages; the tokens of the step were written there by
-the fused norm/rotary/cache kernel just before.  float32 always runs the CUDA-core kernel in
-32-bit arithmetic.
+the fused norm/rotary/cache kernel just before.
+
+* float32, or a shape the tensor-core kernels refuse: the CUDA-core kernel in 32-bit arithmetic.
+* bfloat16, every segment a single token: the split-key decode kernel (scratch for the partial
+  results of the splits, merged by a second kernel).
+* bfloat16 otherwise: the tiled prefill kernel over (tokens x group heads) row tiles.
 """
 from __future__ import annotations
 
+import ctypes
+
+import numpy as np
 import torch
 
+from . import lib as _lib
 from . import ops
+from .ops import _c_float, _c_int, _c_long, _ptr, _stream
+
+SM_COUNT_TARGET = 148 * 4      # blocks wanted in flight for the decode kernel
+MAX_SPLITS = 64
+
+
+def supports_tensor_cores(dtype: torch.dtype, head_dim: int, group: int) -> bool:
+    return dtype == torch.bfloat16 and head_dim % 16 == 0 and 16 <= head_dim <= 256 and group <= 64
+
+
+def decode_splits(tokens: int, kv_heads: int, max_kv_len: int) -> int:
+    blocks = max(1, -(-max_kv_len // 64))
+    return max(1, min(-(-SM_COUNT_TARGET // max(1, tokens * kv_heads)), blocks, MAX_SPLITS))
+
+
+def prefill_tiles(ctx, tokens_per_tile: int):
+    """(first token row, token count) of every row tile, as device int32 arrays; made once per
+    step and group size."""
+    key = ("attention_tiles", tokens_per_tile)
+    tiles = ctx.shared.get(key)
+    if tiles is None:
+        first, count = [], []
+        for seg in ctx.segments:
+            for t0 in range(0, seg.q_len, tokens_per_tile):
+                first.append(seg.q_start + t0)
+                count.append(min(tokens_per_tile, seg.q_len - t0))
+        n = len(first)
+        both = ctx.upload(np.asarray(first + count, dtype=np.int32))
+        tiles = ctx.shared[key] = (both[:n], both[n:], n)
+    return tiles
 
 
 def paged_attention(q: torch.Tensor, q_stride: int, out: torch.Tensor, cache, group, ctx,
                     heads: int, scale: float, window: int) -> torch.Tensor:
     """``q``: the step's queries (row t at ``q_stride * t``, heads contiguous); ``cache``: the
-    schedule entry's pages; ``group``: the step's block tables for the cache's group."""
-    return ops.paged_attention_generic(q, q_stride, out, cache.k, cache.v, group.block_tables,
-                                       ctx.token_slot, ctx.positions, heads, scale, window)
+    schedule entry's pages; ``group``: the step's view of the cache's group."""
+    pages, kv_heads, page_size, head_dim = cache.k.shape
+    ratio = heads // kv_heads
+    if not supports_tensor_cores(q.dtype, head_dim, ratio):
+        return ops.paged_attention_generic(q, q_stride, out, cache.k, cache.v, group.block_tables,
+                                           ctx.token_slot, ctx.positions, heads, scale, window)
+    library = _lib.attention(head_dim)
+    tokens = ctx.num_tokens
+    common = (_ptr(cache.k), _ptr(cache.v), _ptr(group.block_tables), _c_int(group.max_blocks),
+              _ptr(ctx.token_slot), _ptr(ctx.positions))
+    tail = (_c_int(heads), _c_int(kv_heads), _c_int(head_dim), _c_int(page_size), _c_float(scale),
+            _c_int(window), _stream())
+    if ctx.all_decode and ratio <= 16:
+        splits = decode_splits(tokens, kv_heads, ctx.max_kv_len)
+        part_o = part_ml = None
+        if splits > 1:
+            part_o = torch.empty((tokens, heads, splits, head_dim), dtype=torch.float32, device=q.device)
+            part_ml = torch.empty((tokens, heads, splits, 2), dtype=torch.float32, device=q.device)
+        library.call("mrun_attn_decode", _ptr(q), _c_long(q_stride), _ptr(out), *common, _c_int(tokens),
+                     _ptr(part_o), _ptr(part_ml), _c_int(splits), *tail)
+        return out
+    first, count, n_tiles = prefill_tiles(ctx, 64 // ratio)
+    if tokens > ctx.real_tokens:
+        out[ctx.real_tokens:].zero_()
+    library.call("mrun_attn_prefill", _ptr(q), _c_long(q_stride), _ptr(out), *common, _ptr(first),
+                 _ptr(count), _c_int(n_tiles), *tail)
+    return out

@@ -147,6 +147,19 @@ def build_core() -> str:
     return build_library("mrun_core", CORE_SOURCES)
 
 
+def build_attention(head_dim: int) -> str:
+    """The tensor-core attention kernels specialised for one head size."""
+    if head_dim % 16 or not 16 <= head_dim <= 256:
+        raise BuildError(f"the tensor-core attention takes head sizes 16, 32, ... 256, not {head_dim}")
+    return build_library(f"mrun_attn_d{head_dim}", ("common.cu", "attention_mma.cu"),
+                         {"MRUN_HEAD_DIM": head_dim})
+
+
+# head sizes of the configurations this repository measures and tests
+COMMON_HEAD_DIMS = (16, 32, 64, 128)
+
+
 def build_all() -> list[str]:
-    """Every library the package can load (the build check compiles them all)."""
-    return [build_core()]
+    """Every library the package loads for the configurations it measures and tests; other head
+    sizes are built when a model with them is first run."""
+    return [build_core()] + [build_attention(d) for d in COMMON_HEAD_DIMS]

@@ -22,7 +22,7 @@ class Library:
     def __init__(self, path: str, error_symbol: str = "mrun_last_error"):
         self.path = path
         try:
-            self._dll = ctypes.CDLL(path, mode=ctypes.RTLD_GLOBAL)
+            self._dll = ctypes.CDLL(path, mode=ctypes.RTLD_LOCAL)
         except OSError as error:
             raise KernelError(f"cannot open the kernel library {path}: {error}") from None
         self._last_error = getattr(self._dll, error_symbol)
@@ -69,3 +69,16 @@ def core() -> Library:
             raise KernelError(f"{lib.path} was not built for sm_100a")
         _core = lib
     return _core
+
+
+def attention(head_dim: int) -> Library:
+    """The tensor-core attention library for ``head_dim`` (built at first use)."""
+    lib = _attention.get(head_dim)
+    if lib is None:
+        lib = Library(build.build_attention(head_dim))
+        query = lib._dll.mrun_attn_head_dim
+        query.restype = ctypes.c_int
+        if query() != head_dim:
+            raise KernelError(f"{lib.path} was built for head_dim={query()}, not {head_dim}")
+        _attention[head_dim] = lib
+    return lib

@@ -13,13 +13,12 @@ import torch
 from ..cache.needs import PagedKV
 from ..config.spec import AttentionSpec, TensorSpec
 from ..kernels import ops
-from ..kernels.attention import paged_attention
+from ..kernels.attention import paged_attention, supports_tensor_cores
 from .base import NORMS, POSITIONS, Runtime, register_mixer
 
 
 @register_mixer("attention")
 class Attention:
-    graph_safe = True
 
     @staticmethod
     def tensor_specs(spec: AttentionSpec, prefix: str):
@@ -56,6 +55,9 @@ class Attention:
         self.position = None
         if spec.position is not None:
             self.position = POSITIONS.build(spec.position, {}, runtime)
+        # the tiled kernel that very wide groups fall to needs a tile list made on the host
+        ratio = spec.heads // spec.kv_heads
+        self.graph_safe = not (supports_tensor_cores(runtime.precision.act, spec.head_dim, ratio) and ratio > 16)
 
     def cache_need(self):
         return PagedKV(self.spec.kv_heads, self.spec.head_dim, self.spec.window)

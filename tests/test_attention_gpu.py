@@ -1,0 +1,193 @@
+"""The attention kernels alone: the CUDA-core kernel (32-bit and bfloat16), the tensor-core prefill
+kernel and the split-key decode kernel, against plain softmax attention over gathered keys, with
+shuffled pages, odd group sizes, head sizes in steps of 16, windows, and inputs made so that one
+far key carries the whole result."""
+from __future__ import annotations
+
+import numpy as np
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+
+
+class Case:
+    """Segments of (context before the step, new tokens) over a shuffled page pool."""
+
+    def __init__(self, segments, heads, kv_heads, head_dim, page_size, dtype, seed=0, window=0, pad=0):
+        from mrun_b200.engine.batch import GroupView, HostStaging, SegmentInfo, StepContext
+        g = torch.Generator().manual_seed(seed)
+        self.heads, self.kv_heads, self.head_dim, self.page_size, self.window = heads, kv_heads, head_dim, page_size, window
+        self.dtype = dtype
+        total_blocks = sum(-(-(c + n) // page_size) for c, n in segments)
+        pages = total_blocks + 5
+        order = torch.randperm(pages, generator=g).tolist()
+        max_blocks = max(-(-(c + n) // page_size) for c, n in segments) + 2
+        slots = len(segments) + 2
+        table = torch.full((slots, max_blocks), -1, dtype=torch.int32)
+        self.k = (torch.randn(pages, kv_heads, page_size, head_dim, generator=g)).to(dtype)
+        self.v = (torch.randn(pages, kv_heads, page_size, head_dim, generator=g)).to(dtype)
+        tokens = sum(n for _, n in segments)
+        self.q = torch.randn(tokens + pad, heads * head_dim + 24, generator=g).to(dtype)   # a view into a wider buffer
+        positions, token_slot, infos = [], [], []
+        row = 0
+        slot_order = torch.randperm(slots, generator=g).tolist()
+        self.seg_pages = []
+        for s, (context, new) in enumerate(segments):
+            slot = slot_order[s]
+            n_blocks = -(-(context + new) // page_size)
+            mine = [order.pop() for _ in range(n_blocks)]
+            table[slot, :n_blocks] = torch.tensor(mine, dtype=torch.int32)
+            self.seg_pages.append(mine)
+            positions += list(range(context, context + new))
+            token_slot += [slot] * new
+            infos.append(SegmentInfo(slot, row, new, context))
+            row += new
+        positions += [-1] * pad
+        token_slot += [0] * pad
+        self.segments, self.infos, self.tokens, self.pad = segments, infos, tokens, pad
+        self.staging = HostStaging(torch.device(DEV))
+        dev = lambda x: torch.tensor(x, dtype=torch.int32, device=DEV)
+        self.table = table.to(DEV)
+        self.ctx = StepContext(
+            num_tokens=tokens + pad, num_segments=len(segments), segments=infos, token_ids=dev([0] * (tokens + pad)),
+            positions=dev(positions), token_slot=dev(token_slot), seg_q_start=dev([0]), seg_kv_len=dev([0]),
+            seg_slot=dev([0]), groups={}, max_q_len=max(n for _, n in segments),
+            max_kv_len=max(c + n for c, n in segments), page_size=page_size, real_tokens=tokens,
+            upload=self.staging.upload)
+        self.group = GroupView(self.table, dev([0]), max_blocks)
+        self.kd, self.vd, self.qd = self.k.to(DEV), self.v.to(DEV), self.q.to(DEV)
+
+    def keys_of(self, s, cache):
+        context, new = self.segments[s]
+        rows = [cache[self.seg_pages[s][p // self.page_size], :, p % self.page_size] for p in range(context + new)]
+        return torch.stack(rows).float()                       # [S, kv_heads, D]
+
+    def reference(self, scale):
+        out = torch.zeros(self.tokens + self.pad, self.heads, self.head_dim)
+        group = self.heads // self.kv_heads
+        for s, info in enumerate(self.infos):
+            k, v = self.keys_of(s, self.k), self.keys_of(s, self.v)
+            q = self.q[info.q_start:info.q_start + info.q_len, :self.heads * self.head_dim].float().view(info.q_len, self.heads, self.head_dim)
+            for i in range(info.q_len):
+                p = info.pos_start + i
+                lo = max(0, p - self.window + 1) if self.window else 0
+                for h in range(self.heads):
+                    scores = (k[lo:p + 1, h // group] @ q[i, h]) * scale
+                    out[info.q_start + i, h] = torch.softmax(scores, 0) @ v[lo:p + 1, h // group]
+        return out.view(self.tokens + self.pad, -1)
+
+    class Cache:
+        pass
+
+    def run(self, scale, force_generic=False):
+        from mrun_b200.kernels import ops
+        from mrun_b200.kernels.attention import paged_attention
+        out = torch.full((self.tokens + self.pad, self.heads * self.head_dim), 3.0, dtype=self.dtype, device=DEV)
+        cache = Case.Cache()
+        cache.k, cache.v = self.kd, self.vd
+        if force_generic:
+            ops.paged_attention_generic(self.qd, self.qd.stride(0), out, self.kd, self.vd, self.table,
+                                        self.ctx.token_slot, self.ctx.positions, self.heads, scale, self.window)
+        else:
+            paged_attention(self.qd, self.qd.stride(0), out, cache, self.group, self.ctx, self.heads, scale, self.window)
+        return out.float().cpu()
+
+
+SHAPES = [  # heads, kv_heads, head_dim, page_size
+    (4, 2, 16, 16), (6, 3, 32, 8), (7, 1, 48, 4), (8, 8, 64, 32), (10, 2, 80, 16), (32, 8, 128, 16), (2, 1, 256, 16),
+    (3, 1, 96, 1), (40, 2, 64, 16)]
+
+
+@pytest.mark.parametrize("heads,kv_heads,head_dim,page_size", SHAPES)
+@pytest.mark.parametrize("window", [0, 37])
+def test_mixed_batch_against_plain(heads, kv_heads, head_dim, page_size, window):
+    """Prompt portions beside single tokens, contexts up to a few hundred keys."""
+    segments = [(0, 70), (129, 1), (63, 2), (300, 1), (15, 33), (0, 1)]
+    scale = head_dim ** -0.5
+    for dtype, tol in ((torch.float32, 2e-5), (torch.bfloat16, 2e-2)):
+        case = Case(segments, heads, kv_heads, head_dim, page_size, dtype, seed=head_dim + window, window=window)
+        want = case.reference(scale)
+        assert (case.run(scale, force_generic=True) - want).abs().max() <= tol * want.abs().max()
+        if dtype == torch.bfloat16:
+            assert (case.run(scale) - want).abs().max() <= tol * want.abs().max()
+
+
+@pytest.mark.parametrize("heads,kv_heads,head_dim,page_size", SHAPES)
+@pytest.mark.parametrize("window", [0, 100])
+def test_decode_batch_against_plain(heads, kv_heads, head_dim, page_size, window):
+    """Every segment one token (the split-key kernel where the group fits), with padding rows."""
+    segments = [(0, 1), (63, 1), (64, 1), (700, 1), (15, 1), (1023, 1), (200, 1)]
+    scale = head_dim ** -0.5
+    case = Case(segments, heads, kv_heads, head_dim, page_size, torch.bfloat16, seed=7 + head_dim, window=window, pad=3)
+    want = case.reference(scale)
+    got = case.run(scale)
+    assert (got[:case.tokens] - want[:case.tokens]).abs().max() <= 2e-2 * want.abs().max()
+    assert got[case.tokens:].abs().max() == 0, "padding rows must come out as zeros"
+    # more splits than the heuristic picks: the context is cut at every 64 keys
+    case.ctx.max_kv_len = 64 * 64
+    case.ctx.shared.clear()
+    assert (case.run(scale)[:case.tokens] - want[:case.tokens]).abs().max() <= 2e-2 * want.abs().max()
+
+
+@pytest.mark.parametrize("far", [0, 15, 16, 63, 64, 65, 127, 255, 256, 400, 511])
+def test_one_far_key_among_hundreds_carries_the_result(far):
+    """The query is aligned with one key (score far above the rest) whose value is a marker: the
+    output must be that marker, for keys at page and tile edges, in every kernel."""
+    heads, kv_heads, head_dim, page_size, context = 8, 2, 64, 16, 511
+    scale = head_dim ** -0.5
+    for segments, label in (([(context, 1)], "decode"), ([(context - 40, 41)], "prefill")):
+        for dtype in (torch.float32, torch.bfloat16):
+            case = Case(segments, heads, kv_heads, head_dim, page_size, dtype, seed=far)
+            page, off = case.seg_pages[0][far // page_size], far % page_size
+            direction = torch.randn(head_dim, generator=torch.Generator().manual_seed(1))
+            direction /= direction.norm()
+            case.k[page, :, off] = (direction * 40.0).to(dtype)
+            case.v[page, :, off] = 9.0
+            case.q[:, :heads * head_dim] = (direction * 8.0).repeat(heads).to(dtype)
+            case.kd, case.vd, case.qd = case.k.to(DEV), case.v.to(DEV), case.q.to(DEV)
+            for generic in ((True,) if dtype == torch.float32 else (True, False)):
+                got = case.run(scale, force_generic=generic)
+                last = got[case.tokens - 1]
+                assert (last - 9.0).abs().max() < 0.1, (label, dtype, generic, float(last.min()), float(last.max()))
+
+
+def test_window_edge():
+    """With a window of W the key at p - W + 1 counts and the key at p - W does not."""
+    heads, kv_heads, head_dim, page_size, window = 4, 2, 32, 8, 48
+    scale = head_dim ** -0.5
+    for new in (1, 9):
+        for dtype in (torch.float32, torch.bfloat16):
+            for inside in (True, False):
+                context = 130
+                case = Case([(context, new)], heads, kv_heads, head_dim, page_size, dtype, seed=3, window=window)
+                p = context + new - 1
+                marked = p - window + 1 if inside else p - window
+                page, off = case.seg_pages[0][marked // page_size], marked % page_size
+                direction = torch.ones(head_dim) / head_dim ** 0.5
+                case.k[page, :, off] = (direction * 40.0).to(dtype)
+                case.v[page, :, off] = 9.0
+                case.q[-1, :heads * head_dim] = (direction * 8.0).repeat(heads).to(dtype)
+                case.kd, case.vd, case.qd = case.k.to(DEV), case.v.to(DEV), case.q.to(DEV)
+                for generic in ((True,) if dtype == torch.float32 else (True, False)):
+                    last = case.run(scale, force_generic=generic)[case.tokens - 1]
+                    if inside:
+                        assert (last - 9.0).abs().max() < 0.1
+                    else:
+                        assert last.abs().max() < 5.0, "a key outside the window leaked in"
+
+
+def test_given_back_pages_are_not_read():
+    """Block-table entries of -1 below the window (pages given back) are never dereferenced."""
+    heads, kv_heads, head_dim, page_size, window = 4, 1, 64, 16, 40
+    scale = head_dim ** -0.5
+    for segments in ([(500, 1)], [(480, 21)]):
+        case = Case(segments, heads, kv_heads, head_dim, page_size, torch.bfloat16, seed=11, window=window)
+        want = case.reference(scale)
+        first_needed = (segments[0][0] - window + 1) // page_size
+        slot = case.infos[0].slot
+        case.table[slot, :first_needed] = -1
+        for generic in (True, False):
+            got = case.run(scale, force_generic=generic)
+            assert (got - want).abs().max() <= 2e-2 * want.abs().max()

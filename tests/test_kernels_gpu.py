@@ -1,0 +1,224 @@
+"""Each CUDA kernel alone against a plain 32-bit torch formula of the same operation, at sizes
+other than the engine's: widths and vocabularies that are no power of two, head sizes in steps of
+16, odd group sizes, several page sizes, windows."""
+from __future__ import annotations
+
+import math
+
+import numpy as np
+import pytest
+import torch
+
+import plain_qwen3 as plain
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+
+
+def ops():
+    from mrun_b200.kernels import ops as o
+    return o
+
+
+def rnd(*shape, dtype=torch.float32, seed=0, scale=1.0):
+    g = torch.Generator().manual_seed(seed)
+    return (torch.randn(*shape, generator=g) * scale).to(dtype).to(DEV)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("vocab,hidden", [(37, 24), (509, 100), (1000, 4096)])
+def test_embed(dtype, vocab, hidden):
+    table = rnd(vocab, hidden, dtype=dtype, seed=1)
+    ids = torch.tensor([0, vocab - 1, 5, 5, vocab // 2], dtype=torch.int32, device=DEV)
+    out = torch.empty((5, hidden), dtype=torch.float32, device=DEV)
+    ops().embed(table, ids, out)
+    assert torch.equal(out, table[ids.long()].float())
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("rows,hidden,eps", [(1, 16, 1e-6), (7, 100, 1e-5), (33, 2560, 1e-6), (3, 13000, 1e-3)])
+def test_add_rmsnorm(dtype, rows, hidden, eps):
+    resid = rnd(rows, hidden, seed=2)
+    delta = rnd(rows, hidden, dtype=dtype, seed=3)
+    weight = 1 + 0.1 * rnd(hidden, seed=4)
+    want_resid = resid + delta.float()
+    want = plain.rms_norm(want_resid.cpu(), weight.cpu(), eps).to(DEV)
+    out = torch.empty((rows, hidden), dtype=dtype, device=DEV)
+    got_resid = resid.clone()
+    ops().add_rmsnorm(got_resid, delta, weight, eps, out)
+    assert torch.equal(got_resid, want_resid)
+    tol = 2e-6 if dtype == torch.float32 else 8e-3
+    assert (out.float() - want).abs().max() <= tol * want.abs().max()
+    # no delta: the stream stays; chosen rows only: the stream stays too
+    keep = resid.clone()
+    ops().add_rmsnorm(keep, None, weight, eps, out)
+    assert torch.equal(keep, resid)
+    index = torch.tensor([rows - 1, 0], dtype=torch.int32, device=DEV)
+    picked = torch.empty((2, hidden), dtype=dtype, device=DEV)
+    ops().add_rmsnorm(keep, delta, weight, eps, picked, rows=index)
+    assert torch.equal(keep, resid)
+    assert (picked.float() - want[[rows - 1, 0]]).abs().max() <= tol * want.abs().max()
+
+
+@pytest.mark.parametrize("theta,half", [(10000.0, 8), (1e6, 64), (500000.0, 24)])
+def test_rotary_table(theta, half):
+    positions = torch.tensor([0, 1, 2, 777, 8191, 40000, -1], dtype=torch.int32, device=DEV)
+    inv = (torch.tensor(theta, dtype=torch.float64) ** (-torch.arange(half, dtype=torch.float64) / half)).to(DEV)
+    out = torch.empty((7, half, 2), dtype=torch.float32, device=DEV)
+    ops().rotary_table(positions, inv, out)
+    angle = positions[:6].double()[:, None] * inv[None, :]
+    assert (out[:6, :, 0] - angle.cos().float()).abs().max() <= 1.2e-7
+    assert (out[:6, :, 1] - angle.sin().float()).abs().max() <= 1.2e-7
+    assert torch.equal(out[6, :, 0], torch.ones(half, device=DEV)) and out[6, :, 1].abs().max() == 0
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("heads,kv_heads,head_dim,rotary_dim,page_size", [
+    (4, 2, 16, 16, 16), (6, 3, 32, 32, 8), (5, 5, 48, 24, 4), (8, 1, 128, 128, 16), (3, 1, 80, 80, 32)])
+def test_qk_norm_rope_cache(dtype, heads, kv_heads, head_dim, rotary_dim, page_size):
+    tokens, pages, eps, theta = 11, 9, 1e-5, 10000.0
+    width = (heads + 2 * kv_heads) * head_dim
+    qkv = rnd(tokens, width, dtype=dtype, seed=5)
+    qw, kw = 1 + 0.2 * rnd(head_dim, seed=6), 1 + 0.2 * rnd(head_dim, seed=7)
+    positions = torch.tensor([0, 1, 2, 3, 100, 101, 7, 8, 9, 4000, 31], dtype=torch.int32, device=DEV)
+    slots = torch.randperm(pages * page_size, generator=torch.Generator().manual_seed(8))[:tokens].int().to(DEV)
+    slots[3] = -1                                   # a token whose k/v must not be written
+    inv = (torch.tensor(theta, dtype=torch.float64) ** (-2.0 * torch.arange(rotary_dim // 2, dtype=torch.float64) / rotary_dim)).to(DEV)
+    rot = torch.empty((tokens, rotary_dim // 2, 2), dtype=torch.float32, device=DEV)
+    ops().rotary_table(positions, inv, rot)
+    k_cache = torch.full((pages, kv_heads, page_size, head_dim), 7.0, dtype=dtype, device=DEV)
+    v_cache = torch.full((pages, kv_heads, page_size, head_dim), 7.0, dtype=dtype, device=DEV)
+    src = qkv.float().cpu()
+    got = qkv.clone()
+    ops().qk_norm_rope_cache(got, heads, kv_heads, head_dim, qw, kw, eps, rot, rotary_dim, slots, k_cache,
+                             v_cache, page_size)
+    q = src[:, :heads * head_dim].view(tokens, heads, head_dim)
+    k = src[:, heads * head_dim:(heads + kv_heads) * head_dim].view(tokens, kv_heads, head_dim)
+    v = src[:, (heads + kv_heads) * head_dim:].view(tokens, kv_heads, head_dim)
+    pos = positions.cpu()
+    want_q = plain.rope(plain.rms_norm(q, qw.cpu(), eps), pos, theta, rotary_dim)
+    want_k = plain.rope(plain.rms_norm(k, kw.cpu(), eps), pos, theta, rotary_dim)
+    tol = 3e-6 if dtype == torch.float32 else 1.6e-2
+    got_q = got[:, :heads * head_dim].float().cpu().view(tokens, heads, head_dim)
+    assert (got_q - want_q).abs().max() <= tol * want_q.abs().max()
+    # k and v parts of the buffer are left alone
+    assert torch.equal(got[:, heads * head_dim:], qkv[:, heads * head_dim:])
+    kc, vc = k_cache.float().cpu(), v_cache.float().cpu()
+    written = torch.zeros(pages, page_size, dtype=torch.bool)
+    for t in range(tokens):
+        s = int(slots[t])
+        if s < 0:
+            continue
+        page, off = divmod(s, page_size)
+        written[page, off] = True
+        assert (kc[page, :, off] - want_k[t]).abs().max() <= tol * want_k.abs().max()
+        assert torch.equal(vc[page, :, off], v[t].to(dtype).float())
+    assert (kc.permute(0, 2, 1, 3)[~written] == 7.0).all() and (vc.permute(0, 2, 1, 3)[~written] == 7.0).all()
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("tokens,inter", [(1, 8), (5, 200), (17, 9728)])
+def test_swiglu(dtype, tokens, inter):
+    gate_up = rnd(tokens, 2 * inter, dtype=dtype, seed=9, scale=2.0)
+    out = torch.empty((tokens, inter), dtype=dtype, device=DEV)
+    ops().swiglu(gate_up, out)
+    g, u = gate_up[:, :inter].float(), gate_up[:, inter:].float()
+    want = g * torch.sigmoid(g) * u
+    tol = 2e-6 if dtype == torch.float32 else 8e-3
+    assert (out.float() - want).abs().max() <= tol * want.abs().max()
+
+
+@pytest.mark.parametrize("m,n,k", [(1, 7, 5), (3, 509, 96), (65, 130, 257), (128, 64, 64), (200, 1000, 333)])
+def test_gemm_f32(m, n, k):
+    x, w = rnd(m, k, seed=10), rnd(n, k, seed=11)
+    got = ops().gemm_f32_nt(x, w)
+    want = (x.double() @ w.double().T)
+    assert (got.double() - want).abs().max() <= 1e-6 * want.abs().max() * math.sqrt(k)
+    # a row's result does not depend on the other rows in the call
+    alone = ops().gemm_f32_nt(x[m // 2:m // 2 + 1].contiguous(), w)
+    assert torch.equal(alone[0], got[m // 2])
+    # strided input (a view into a wider buffer)
+    wide = rnd(m, k + 13, seed=12)
+    assert torch.equal(ops().gemm_f32_nt(wide[:, :k], w), ops().gemm_f32_nt(wide[:, :k].contiguous(), w))
+
+
+def test_linear_bf16_accumulates_in_32_bits():
+    x, w = rnd(9, 1024, dtype=torch.bfloat16, seed=13), rnd(77, 1024, dtype=torch.bfloat16, seed=14)
+    got = ops().linear(x, w, out_dtype=torch.float32)
+    want = x.float() @ w.float().T
+    assert got.dtype == torch.float32 and (got - want).abs().max() <= 1e-3 * want.abs().max()
+    assert ops().linear(x, w).dtype == torch.bfloat16
+
+
+# --------------------------------------------------------------------------- sampling
+
+@pytest.mark.parametrize("vocab", [7, 509, 151936])
+def test_sample_greedy_is_argmax_lowest_index(vocab):
+    logits = rnd(5, vocab, seed=15)
+    logits[2, 3] = logits[2, vocab - 1] = 50.0                       # a tie: the lower index wins
+    out = torch.empty(5, dtype=torch.int32, device=DEV)
+    ops().sample(logits, out)
+    want = [int(np.argmax(row)) for row in logits.cpu().numpy()]
+    assert out.tolist() == want and want[2] == 3
+
+
+@pytest.mark.parametrize("vocab", [64, 509, 50000])
+def test_sample_temperature_equals_plain_draw(vocab):
+    rows = 6
+    logits = rnd(rows, vocab, seed=16, scale=2.0)
+    temps = [0.8, 1.0, 0.3, 0.0, 1.7, 0.8]
+    keys = [plain.draw_key(99, n + 1) for n in range(rows)]
+    out = torch.empty(rows, dtype=torch.int32, device=DEV)
+    ops().sample(logits, out, temperature=torch.tensor(temps, device=DEV),
+                 keys=torch.from_numpy(np.array(keys, dtype=np.uint64).view(np.int64)).to(DEV))
+    host = logits.cpu().numpy()
+    assert out.tolist() == [plain.sample_token(host[i], temps[i], keys[i]) for i in range(rows)]
+
+
+def test_sample_filters_keep_the_plain_sets():
+    """top-k, top-p and min-p: over many draws every sampled token lies in the plain keep-set, and
+    the whole keep-set is reached when it is small."""
+    vocab, draws = 97, 400
+    row = rnd(1, vocab, seed=17, scale=2.5)
+    host = row.cpu().numpy()[0]
+    for kwargs in (dict(top_k=5), dict(top_p=0.6), dict(min_p=0.2), dict(top_p=0.9, top_k=8, min_p=0.05)):
+        keep = plain.filter_threshold(host, kwargs.get("top_p", 1.0), kwargs.get("top_k", 0), kwargs.get("min_p", 0.0))
+        logits = row.expand(draws, vocab).contiguous()
+        keys = np.array([plain.draw_key(5, n + 1) for n in range(draws)], dtype=np.uint64)
+        out = torch.empty(draws, dtype=torch.int32, device=DEV)
+        full = lambda v, dt: torch.full((draws,), v, dtype=dt, device=DEV)
+        ops().sample(logits, out, temperature=full(1.5, torch.float32), top_p=full(kwargs.get("top_p", 1.0), torch.float32),
+                     top_k=full(kwargs.get("top_k", 0), torch.int32), min_p=full(kwargs.get("min_p", 0.0), torch.float32),
+                     keys=torch.from_numpy(keys.view(np.int64)).to(DEV))
+        seen = set(out.tolist())
+        allowed = set(np.nonzero(keep)[0].tolist())
+        assert seen <= allowed, (kwargs, seen - allowed)
+        if len(allowed) <= 8:
+            assert seen == allowed, (kwargs, allowed - seen)
+        want = [plain.sample_token(host, 1.5, int(keys[n]), **kwargs) for n in range(20)]
+        assert out.tolist()[:20] == want
+
+
+def test_repetition_penalty():
+    logits = rnd(3, 50, seed=18)
+    before = logits.cpu().numpy().copy()
+    recent = torch.tensor([[1, 2, 2, -1], [-1, -1, -1, -1], [49, 0, 49, 7]], dtype=torch.int32, device=DEV)
+    penalty = torch.tensor([1.3, 1.3, 1.0], device=DEV)
+    ops().repetition_penalty(logits, recent, penalty)
+    want = before.copy()
+    want[0] = plain.apply_repetition_penalty(before[0], [1, 2, 2], 1.3)
+    assert np.allclose(logits.cpu().numpy(), want, rtol=1e-6, atol=0)
+
+
+def test_kernels_refuse_what_they_cannot_take():
+    from mrun_b200.kernels import KernelError
+    with pytest.raises(KernelError, match="CUDA"):
+        ops().swiglu(torch.zeros(2, 8), torch.zeros(2, 4))
+    with pytest.raises(KernelError, match="dtype"):
+        ops().swiglu(torch.zeros(2, 8, dtype=torch.float16, device=DEV), torch.zeros(2, 4, dtype=torch.float16, device=DEV))
+    with pytest.raises(KernelError, match="hidden"):
+        big = torch.zeros(1, 60000, device=DEV)
+        ops().add_rmsnorm(big, None, torch.ones(60000, device=DEV), 1e-6, torch.empty_like(big))
+    with pytest.raises(KernelError, match="rotary_dim"):
+        ops().qk_norm_rope_cache(torch.zeros(1, 48, device=DEV), 1, 1, 16, None, None, 0.0,
+                                 torch.zeros(1, 2, 2, device=DEV), 5, None, None, None, 4)
