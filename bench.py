@@ -143,6 +143,10 @@ def main() -> int:
     parser.add_argument("--layers", type=int, default=None,
                         help="run fewer layers than the configuration has (both numbers are reported)")
     parser.add_argument("--skip-points", action="store_true", help="only the batch-8 decode and the prefill")
+    parser.add_argument("--batches", default=None,
+                        help="decode batch sizes to run, comma separated (for profiling one point)")
+    parser.add_argument("--skip-prefill", action="store_true")
+    parser.add_argument("--skip-e2e", action="store_true")
     args = parser.parse_args()
 
     if args.impl == "reference":
@@ -169,6 +173,8 @@ def main() -> int:
     config = Qwen3Config(**sizes)
     page_size = 16
     batches = [8] if args.skip_points else [8, 1, 64]
+    if args.batches:
+        batches = [int(b) for b in args.batches.split(",")]
     slack = args.steps + args.warmup + 64
     capacity = max(max(batches) * (CONTEXT + slack), 8 * (CONTEXT + 2 * slack)) + PREFILL_TOKENS + 4 * 64
     engine = Engine.from_config(config, seed=0, dtype="bfloat16", page_size=page_size,
@@ -183,7 +189,7 @@ def main() -> int:
     from mrun_b200.engine import StepEntry
     prompt = seeded_tokens(vocab, PREFILL_TOKENS, 3)
     times = []
-    for i in range(2 + 3):
+    for i in range(0 if args.skip_prefill else 2 + 3):
         request = executor.admit(("prefill", i))
         torch.cuda.synchronize()
         begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -194,7 +200,7 @@ def main() -> int:
         executor.release(request)
         if i >= 2:
             times.append(begin.elapsed_time(end))
-    prefill_ms = statistics.median(times)
+    prefill_ms = statistics.median(times) if times else float("nan")
     h, d = config.hidden_size, config.head_dim
     linear_params = config.num_hidden_layers * ((config.num_attention_heads + 2 * config.num_key_value_heads) * d * h
                                                 + config.num_attention_heads * d * h
@@ -212,25 +218,31 @@ def main() -> int:
     for batch in batches:
         requests = fill_requests(executor, batch, CONTEXT, vocab, f"decode{batch}")
         sampler = ClockSampler()
-        if batch == 8:
+        if batch == batches[0]:
             sampler.start()
         ms, n_launch = time_decode(executor, requests, vocab, args.steps, args.warmup)
-        if batch == 8:
+        if batch == batches[0]:
             clocks = sampler.stop()
             launches = n_launch
         for r in requests:
             executor.release(r)
         results[batch] = ms
-    ms_per_step = results[8] / args.steps
-    value = 8 * args.steps / (results[8] * 1e-3)
+    main_batch = batches[0]
+    ms_per_step = results[main_batch] / args.steps
+    value = main_batch * args.steps / (results[main_batch] * 1e-3)
     context_mid = CONTEXT + args.warmup + args.steps / 2.0
-    step_bytes = weight_bytes + 8 * context_mid * kv_bytes + 8 * h * 2
+    step_bytes = weight_bytes + main_batch * context_mid * kv_bytes + main_batch * h * 2
     achieved = step_bytes / (ms_per_step * 1e-3) / 1e9
     roofline = {"bound": "hbm", "achieved": round(achieved, 1), "peak": peaks["hbm_gbs"], "unit": "GB/s",
                 "frac": round(achieved / peaks["hbm_gbs"], 4), "of": peaks["source"]}
-    points = {f"decode_b{b}": round(b * args.steps / (results[b] * 1e-3), 1) for b in batches if b != 8}
+    points = {f"decode_b{b}": round(b * args.steps / (results[b] * 1e-3), 1) for b in batches if b != main_batch}
 
     # ---------------------------------------------------------------- end to end, Engine.generate
+    if args.skip_e2e:
+        line = {"metric": f"decode tok/s at batch {main_batch}", "value": round(value, 1), "ms_per_step": round(ms_per_step, 4),
+                "roofline": roofline, "points": points, "gpu_launches": launches, "prefill_ms": prefill_ms}
+        print(json.dumps(line))
+        return 0
     out_tokens = args.steps + 1
     prompts = [seeded_tokens(vocab, CONTEXT, 50 + i) for i in range(8)]
     engine.generate(prompts[:2], max_tokens=4, ignore_eos=True)          # warm the mixed-step shapes
@@ -250,7 +262,7 @@ def main() -> int:
            "d2h_bytes_per_step": round((engine.stats.d2h_bytes - d2h_before) / n_steps, 1)}
 
     line = {
-        "metric": "decode tok/s at batch 8 (Qwen3-8B bf16, 1,024-token prompts)",
+        "metric": f"decode tok/s at batch {main_batch} (Qwen3-8B bf16, 1,024-token prompts)",
         "value": round(value, 1), "unit": "tok/s", "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": round(ms_per_step, 4), "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "bf16", "data": "synthetic (seeded uniform token ids, N(0,0.02) weights)",
@@ -260,7 +272,7 @@ def main() -> int:
             "hidden": h, "heads": config.num_attention_heads, "kv_heads": config.num_key_value_heads,
             "head_dim": d, "intermediate": config.intermediate_size, "vocab": vocab,
             "rope_theta": config.rope_theta, "rms_norm_eps": config.rms_norm_eps,
-            "tied": config.tie_word_embeddings, "global_batch": 8, "seq_len": CONTEXT,
+            "tied": config.tie_word_embeddings, "global_batch": main_batch, "seq_len": CONTEXT,
             "max_context": config.max_position_embeddings, "page_size": page_size,
             "parallelism": "single GPU", "l2": "inputs larger than L2 (15 GB of weights per step)",
         },

@@ -8,8 +8,8 @@
 //    group.  Keys are consumed 64 at a time in position order with an online softmax.
 //  * decode: one block per (token, kv head, split of the keys).  The rows are the group's query
 //    heads of one token (at most 16); the four warps take different 16-key slices of each
-//    64-key tile and are merged at the end; splits are merged by a second kernel through
-//    scratch memory (32-bit partial outputs with their running max and sum).
+//    64-key tile and are merged at the end; the split that finishes last merges all splits
+//    through scratch memory (32-bit partial outputs with their running max and sum).
 //
 // Both read keys and values from the pages (cache[page, kv_head, offset, :]) through the block
 // table of the token's state slot.  A token at position p sees keys lo..p, lo = 0 or
@@ -68,23 +68,53 @@ __device__ __forceinline__ unsigned pack_bf16(float lo, float hi) {
     return *reinterpret_cast<unsigned*>(&v);
 }
 
-// Loads keys key0 .. key0+63 of one kv head into a [64][LD] tile.  Rows whose key lies outside
-// [lo, hi] or whose page is not held are zero-filled.
-__device__ __forceinline__ void load_kv_tile(bf16* tile, const bf16* __restrict__ cache,
-                                             const int* __restrict__ table, int key0, int lo, int hi,
-                                             int kv_heads, int kvh, int page_size) {
-    for (int c = threadIdx.x; c < BLOCK_N * CHUNKS; c += THREADS) {
-        const int row = c / CHUNKS, chunk = c - row * CHUNKS;
-        const int key = key0 + row;
-        bool valid = key >= lo && key <= hi;
-        const bf16* src = cache;
-        if (valid) {
-            const int page = table[key / page_size];
-            valid = page >= 0;
-            if (valid)
-                src = cache + (((size_t)page * kv_heads + kvh) * page_size + key % page_size) * D + chunk * 8;
+// Loads keys key0 .. key0+63 of one kv head into a key tile and a value tile, both [64][LD].
+// Rows whose key lies outside [lo, hi] or whose page is not held are zero-filled.  A row's place
+// in the cache is worked out once and used for both tensors.  `page_shift` is log2(page_size)
+// when the page size is a power of two (shift and mask instead of a division), else -1.
+struct Paging {
+    const int* table;
+    int kv_heads, kvh, page_size, page_shift;
+};
+
+__device__ __forceinline__ long cache_row(const Paging& pg, int key, bool& valid) {
+    int block, off;
+    if (pg.page_shift >= 0) {
+        block = key >> pg.page_shift;
+        off = key & (pg.page_size - 1);
+    } else {
+        block = key / pg.page_size;
+        off = key - block * pg.page_size;
+    }
+    const int page = valid ? pg.table[block] : -1;
+    valid = page >= 0;
+    return ((long)(page * pg.kv_heads + pg.kvh) * pg.page_size + off) * D;
+}
+
+__device__ __forceinline__ void load_kv_tiles(bf16* k_tile, bf16* v_tile, const bf16* __restrict__ k_cache,
+                                              const bf16* __restrict__ v_cache, const Paging& pg, int key0,
+                                              int lo, int hi) {
+    if constexpr (THREADS % CHUNKS == 0) {
+        // a thread keeps its 16-byte column and walks down the rows
+        constexpr int STEP = THREADS / CHUNKS;
+        const int chunk = threadIdx.x % CHUNKS, r0 = threadIdx.x / CHUNKS;
+#pragma unroll
+        for (int row = r0; row < BLOCK_N; row += STEP) {
+            const int key = key0 + row;
+            bool valid = key >= lo && key <= hi;
+            const long at = cache_row(pg, key, valid) + chunk * 8;
+            cp_async_16(k_tile + row * LD + chunk * 8, valid ? k_cache + at : k_cache, valid);
+            cp_async_16(v_tile + row * LD + chunk * 8, valid ? v_cache + at : v_cache, valid);
         }
-        cp_async_16(tile + row * LD + chunk * 8, src, valid);
+    } else {
+        for (int c = threadIdx.x; c < BLOCK_N * CHUNKS; c += THREADS) {
+            const int row = c / CHUNKS, chunk = c - row * CHUNKS;
+            const int key = key0 + row;
+            bool valid = key >= lo && key <= hi;
+            const long at = cache_row(pg, key, valid) + chunk * 8;
+            cp_async_16(k_tile + row * LD + chunk * 8, valid ? k_cache + at : k_cache, valid);
+            cp_async_16(v_tile + row * LD + chunk * 8, valid ? v_cache + at : v_cache, valid);
+        }
     }
 }
 
@@ -186,7 +216,7 @@ prefill_kernel(const bf16* __restrict__ q, long q_stride, bf16* __restrict__ out
                const bf16* __restrict__ k_cache, const bf16* __restrict__ v_cache,
                const int* __restrict__ block_tables, int max_blocks, const int* __restrict__ token_slot,
                const int* __restrict__ positions, const int* __restrict__ tile_tok0,
-               const int* __restrict__ tile_ntok, int heads, int kv_heads, int page_size,
+               const int* __restrict__ tile_ntok, int heads, int kv_heads, int page_size, int page_shift,
                float scale_log2, int window) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
     bf16* q_tile = reinterpret_cast<bf16*>(smem_raw);           // [64][LD]
@@ -214,8 +244,8 @@ prefill_kernel(const bf16* __restrict__ q, long q_stride, bf16* __restrict__ out
             src = q + (size_t)(tok0 + row / group) * q_stride + (size_t)(kvh * group + row % group) * D + chunk * 8;
         cp_async_16(q_tile + row * LD + chunk * 8, src, valid);
     }
-    load_kv_tile(k_tiles, k_cache, table, first_block * BLOCK_N, lo_tile, pos_last, kv_heads, kvh, page_size);
-    load_kv_tile(v_tiles, v_cache, table, first_block * BLOCK_N, lo_tile, pos_last, kv_heads, kvh, page_size);
+    const Paging pg{table, kv_heads, kvh, page_size, page_shift};
+    load_kv_tiles(k_tiles, v_tiles, k_cache, v_cache, pg, first_block * BLOCK_N, lo_tile, pos_last);
     cp_async_commit();
 
     int row_pos[2], row_lo[2];
@@ -239,10 +269,8 @@ prefill_kernel(const bf16* __restrict__ q, long q_stride, bf16* __restrict__ out
     for (int block = first_block; block <= last_block; ++block) {
         const int stage = (block - first_block) & 1;
         if (block < last_block) {
-            load_kv_tile(k_tiles + (stage ^ 1) * BLOCK_N * LD, k_cache, table, (block + 1) * BLOCK_N, lo_tile,
-                         pos_last, kv_heads, kvh, page_size);
-            load_kv_tile(v_tiles + (stage ^ 1) * BLOCK_N * LD, v_cache, table, (block + 1) * BLOCK_N, lo_tile,
-                         pos_last, kv_heads, kvh, page_size);
+            load_kv_tiles(k_tiles + (stage ^ 1) * BLOCK_N * LD, v_tiles + (stage ^ 1) * BLOCK_N * LD, k_cache, v_cache,
+                          pg, (block + 1) * BLOCK_N, lo_tile, pos_last);
             cp_async_commit();
             cp_async_wait<1>();
         } else {
@@ -288,81 +316,101 @@ prefill_kernel(const bf16* __restrict__ q, long q_stride, bf16* __restrict__ out
 
 // ------------------------------------------------------------------------------------------
 // Decode: 16 rows = the group's heads of one token; grid (tokens, kv_heads, splits).
-// part_o: [tokens, heads, splits, D] f32 (unnormalised), part_ml: [tokens, heads, splits, 2].
-// With splits == 1 the output is written directly.
+//
+// The token's key tiles are dealt to the splits in runs of `per` tiles, at least `min_tiles`, so a
+// short context uses fewer splits than the grid offers; splits beyond the last run leave at once.  Every working split writes its unnormalised 32-bit result and its running
+// (max, sum) to scratch: part_o [tokens, heads, splits, D], part_ml [tokens, heads, splits, 2].
+// The split that arrives last at the (token, kv head) counter merges all of them in split order
+// and sets the counter back to zero, so no second kernel runs and the result does not depend on
+// which split came last.  With one working split the output is written directly.
 // ------------------------------------------------------------------------------------------
+#ifndef MRUN_DECODE_STAGES
+#define MRUN_DECODE_STAGES 2   // measured: three resident blocks with two tiles each beat deeper pipelines
+#endif
+constexpr int STAGES = MRUN_DECODE_STAGES;
+static_assert(STAGES >= 2 && STAGES <= 4, "2 to 4 key/value tiles in flight");
+
 __global__ void __launch_bounds__(THREADS)
 decode_kernel(const bf16* __restrict__ q, long q_stride, bf16* __restrict__ out,
               const bf16* __restrict__ k_cache, const bf16* __restrict__ v_cache,
               const int* __restrict__ block_tables, int max_blocks, const int* __restrict__ token_slot,
               const int* __restrict__ positions, float* __restrict__ part_o, float* __restrict__ part_ml,
-              int heads, int kv_heads, int page_size, float scale_log2, int window) {
+              int* __restrict__ counters, int min_tiles, int heads, int kv_heads, int page_size,
+              int page_shift, float scale_log2, int window) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
     bf16* q_tile = reinterpret_cast<bf16*>(smem_raw);           // [16][LD]
-    bf16* k_tiles = q_tile + 16 * LD;                           // [2][64][LD]
-    bf16* v_tiles = k_tiles + 2 * BLOCK_N * LD;                 // [2][64][LD]
+    bf16* k_tiles = q_tile + 16 * LD;                           // [STAGES][64][LD]
+    bf16* v_tiles = k_tiles + STAGES * BLOCK_N * LD;            // [STAGES][64][LD]
     float* merge = reinterpret_cast<float*>(k_tiles);           // reused after the loop
+    __shared__ int ticket_shared;
 
     const int tok = blockIdx.x, kvh = blockIdx.y, split = blockIdx.z, splits = gridDim.z;
     const int group = heads / kv_heads;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int pos = positions[tok];
 
-    int first_block = 0, last_block = -1, lo = 0;
-    const int* table = block_tables;
-    if (pos >= 0) {
-        table = block_tables + (size_t)token_slot[tok] * max_blocks;
-        lo = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
-        const int b0 = lo / BLOCK_N, b1 = pos / BLOCK_N;
-        const int per = (b1 - b0 + splits) / splits;            // ceil((b1 - b0 + 1) / splits)
-        first_block = b0 + split * per;
-        last_block = min(b1, first_block + per - 1);
+    if (pos < 0) {  // padding row: zeros, written by the first split
+        if (split == 0)
+            for (int i = threadIdx.x; i < group * D; i += THREADS)
+                out[((size_t)tok * heads + kvh * group) * D + i] = __float2bfloat16_rn(0.f);
+        return;
     }
+    const Paging pg{block_tables + (size_t)token_slot[tok] * max_blocks, kv_heads, kvh, page_size, page_shift};
+    const int lo = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
+    const int b0 = lo / BLOCK_N, b1 = pos / BLOCK_N;
+    const int n_blocks = b1 - b0 + 1;
+    const int per = max((n_blocks + splits - 1) / splits, min_tiles);
+    const int n_active = (n_blocks + per - 1) / per;
+    if (split >= n_active) return;
+    const int first_block = b0 + split * per;
+    const int last_block = min(b1, first_block + per - 1);
 
     float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
     float o[D / 8][4];
 #pragma unroll
     for (int dt = 0; dt < D / 8; ++dt) o[dt][0] = o[dt][1] = o[dt][2] = o[dt][3] = 0.f;
 
-    if (first_block <= last_block) {
-        for (int c = threadIdx.x; c < 16 * CHUNKS; c += THREADS) {
-            const int row = c / CHUNKS, chunk = c - row * CHUNKS;
-            const bool valid = row < group;
-            const bf16* src = valid ? q + (size_t)tok * q_stride + (size_t)(kvh * group + row) * D + chunk * 8 : q;
-            cp_async_16(q_tile + row * LD + chunk * 8, src, valid);
-        }
-        load_kv_tile(k_tiles, k_cache, table, first_block * BLOCK_N, lo, pos, kv_heads, kvh, page_size);
-        load_kv_tile(v_tiles, v_cache, table, first_block * BLOCK_N, lo, pos, kv_heads, kvh, page_size);
-        cp_async_commit();
-
-        int row_pos[2], row_lo[2];
-#pragma unroll
-        for (int r = 0; r < 2; ++r) {
-            const int row = (lane >> 2) + r * 8;
-            row_pos[r] = row < group ? pos : -1;
-            row_lo[r] = lo;
-        }
-        for (int block = first_block; block <= last_block; ++block) {
-            const int stage = (block - first_block) & 1;
-            if (block < last_block) {
-                load_kv_tile(k_tiles + (stage ^ 1) * BLOCK_N * LD, k_cache, table, (block + 1) * BLOCK_N, lo, pos,
-                             kv_heads, kvh, page_size);
-                load_kv_tile(v_tiles + (stage ^ 1) * BLOCK_N * LD, v_cache, table, (block + 1) * BLOCK_N, lo, pos,
-                             kv_heads, kvh, page_size);
-                cp_async_commit();
-                cp_async_wait<1>();
-            } else {
-                cp_async_wait<0>();
-            }
-            __syncthreads();
-            const int key_base = block * BLOCK_N;
-            // warp w takes keys 16w .. 16w+15 of the tile
-            if (key_base + warp * 16 <= pos && key_base + warp * 16 + 15 >= lo)
-                attend_tile<16>(q_tile, k_tiles + stage * BLOCK_N * LD, v_tiles + stage * BLOCK_N * LD, warp * 16,
-                                key_base, scale_log2, true, row_pos, row_lo, m, l, o);
-            __syncthreads();
-        }
+    for (int c = threadIdx.x; c < 16 * CHUNKS; c += THREADS) {
+        const int row = c / CHUNKS, chunk = c - row * CHUNKS;
+        const bool valid = row < group;
+        const bf16* src = valid ? q + (size_t)tok * q_stride + (size_t)(kvh * group + row) * D + chunk * 8 : q;
+        cp_async_16(q_tile + row * LD + chunk * 8, src, valid);
     }
+    // prologue: STAGES - 1 tiles in flight (an empty group keeps the counting uniform)
+#pragma unroll
+    for (int s = 0; s < STAGES - 1; ++s) {
+        if (first_block + s <= last_block)
+            load_kv_tiles(k_tiles + s * BLOCK_N * LD, v_tiles + s * BLOCK_N * LD, k_cache, v_cache, pg,
+                          (first_block + s) * BLOCK_N, lo, pos);
+        cp_async_commit();
+    }
+
+    int row_pos[2], row_lo[2];
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+        const int row = (lane >> 2) + r * 8;
+        row_pos[r] = row < group ? pos : -1;
+        row_lo[r] = lo;
+    }
+    for (int block = first_block; block <= last_block; ++block) {
+        const int it = block - first_block;
+        cp_async_wait<STAGES - 2>();        // tile `it` has landed
+        __syncthreads();                    // ... for every thread, and tile it-1 is no longer read
+        const int ahead = block + STAGES - 1;
+        if (ahead <= last_block) {
+            const int s = (it + STAGES - 1) % STAGES;
+            load_kv_tiles(k_tiles + s * BLOCK_N * LD, v_tiles + s * BLOCK_N * LD, k_cache, v_cache, pg,
+                          ahead * BLOCK_N, lo, pos);
+        }
+        cp_async_commit();
+        const int stage = it % STAGES;
+        const int key_base = block * BLOCK_N;
+        // warp w takes keys 16w .. 16w+15 of the tile
+        if (key_base + warp * 16 <= pos && key_base + warp * 16 + 15 >= lo)
+            attend_tile<16>(q_tile, k_tiles + stage * BLOCK_N * LD, v_tiles + stage * BLOCK_N * LD, warp * 16,
+                            key_base, scale_log2, true, row_pos, row_lo, m, l, o);
+    }
+    cp_async_wait<0>();
 #pragma unroll
     for (int r = 0; r < 2; ++r) {
         l[r] += __shfl_xor_sync(0xffffffffu, l[r], 1);
@@ -401,7 +449,7 @@ decode_kernel(const bf16* __restrict__ q, long q_stride, bf16* __restrict__ out,
             ll += src[D + 1] * c;
         }
         const int head = kvh * group + row;
-        if (splits == 1) {
+        if (n_active == 1) {
             out[((size_t)tok * heads + head) * D + d] = __float2bfloat16_rn(ll > 0.f ? acc / ll : 0.f);
         } else {
             const size_t at = ((size_t)tok * heads + head) * splits + split;
@@ -412,29 +460,43 @@ decode_kernel(const bf16* __restrict__ q, long q_stride, bf16* __restrict__ out,
             }
         }
     }
-}
+    if (n_active == 1) return;
 
-// Merges the splits of one (token, head): one block of D threads.
-__global__ void combine_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
-                               bf16* __restrict__ out, int splits) {
-    const size_t th = blockIdx.x;
-    const int d = threadIdx.x;
-    float mm = -INFINITY;
-    for (int s = 0; s < splits; ++s) mm = fmaxf(mm, part_ml[(th * splits + s) * 2]);
-    float acc = 0.f, ll = 0.f;
-    for (int s = 0; s < splits; ++s) {
-        const float ms = part_ml[(th * splits + s) * 2];
-        const float c = (ms == -INFINITY) ? 0.f : exp2f(ms - mm);
-        acc += part_o[(th * splits + s) * D + d] * c;
-        ll += part_ml[(th * splits + s) * 2 + 1] * c;
+    // the last split to arrive merges all of them
+    __threadfence();
+    __syncthreads();
+    if (threadIdx.x == 0) ticket_shared = atomicAdd(&counters[tok * kv_heads + kvh], 1);
+    __syncthreads();
+    if (ticket_shared != n_active - 1) return;
+    __threadfence();
+    for (int i = threadIdx.x; i < group * D; i += THREADS) {
+        const int row = i / D, d = i - row * D;
+        const size_t th = (size_t)tok * heads + kvh * group + row;
+        const float* ml = part_ml + th * splits * 2;
+        float mm = -INFINITY;
+        for (int s = 0; s < n_active; ++s) mm = fmaxf(mm, __ldcg(ml + 2 * s));
+        float acc = 0.f, ll = 0.f;
+        for (int s = 0; s < n_active; ++s) {
+            const float ms = __ldcg(ml + 2 * s);
+            const float c = (ms == -INFINITY) ? 0.f : exp2f(ms - mm);
+            acc += __ldcg(part_o + (th * splits + s) * D + d) * c;
+            ll += __ldcg(ml + 2 * s + 1) * c;
+        }
+        out[th * D + d] = __float2bfloat16_rn(ll > 0.f ? acc / ll : 0.f);
     }
-    out[th * D + d] = __float2bfloat16_rn(ll > 0.f ? acc / ll : 0.f);
+    if (threadIdx.x == 0) counters[tok * kv_heads + kvh] = 0;
 }
 
 constexpr size_t PREFILL_SMEM = (size_t)(64 + 4 * BLOCK_N) * LD * sizeof(bf16);
-constexpr size_t DECODE_SMEM = (size_t)(16 + 4 * BLOCK_N) * LD * sizeof(bf16);
-static_assert((size_t)4 * 16 * (D + 2) * sizeof(float) <= (size_t)4 * BLOCK_N * LD * sizeof(bf16),
+constexpr size_t DECODE_SMEM = (size_t)(16 + 2 * STAGES * BLOCK_N) * LD * sizeof(bf16);
+static_assert((size_t)4 * 16 * (D + 2) * sizeof(float) <= (size_t)2 * STAGES * BLOCK_N * LD * sizeof(bf16),
               "the warp merge area must fit in the key/value tiles");
+
+int shift_of(int page_size) {
+    for (int s = 0; s < 31; ++s)
+        if ((1 << s) == page_size) return s;
+    return -1;
+}
 
 int check_common(const char* name, int heads, int kv_heads, int head_dim, int page_size, int max_blocks,
                  int window, int max_group) {
@@ -470,21 +532,25 @@ MRUN_API int mrun_attn_prefill(const void* q, long q_stride, void* out, const vo
     }
     prefill_kernel<<<dim3(n_tiles, kv_heads), THREADS, PREFILL_SMEM, stream>>>(
         (const bf16*)q, q_stride, (bf16*)out, (const bf16*)k_cache, (const bf16*)v_cache, block_tables, max_blocks,
-        token_slot, positions, tile_tok0, tile_ntok, heads, kv_heads, page_size, scale * LOG2E, window);
+        token_slot, positions, tile_tok0, tile_ntok, heads, kv_heads, page_size, shift_of(page_size), scale * LOG2E,
+        window);
     MRUN_CHECK_LAUNCH("attn_prefill");
     return 0;
 }
 
 // Every token is a row of its own (positions[t] < 0 = padding, output zero).  part_o and part_ml
-// are scratch of tokens * heads * splits * (D and 2) floats; they may be null when splits == 1.
+// are scratch of tokens * heads * splits * (D and 2) floats; counters holds tokens * kv_heads
+// ints that are zero before the call and zero again after it.  All three may be null when
+// splits == 1.  Calls that share scratch must not overlap on the device.
 MRUN_API int mrun_attn_decode(const void* q, long q_stride, void* out, const void* k_cache, const void* v_cache,
                               const int* block_tables, int max_blocks, const int* token_slot,
-                              const int* positions, int tokens, float* part_o, float* part_ml, int splits,
-                              int heads, int kv_heads, int head_dim, int page_size, float scale, int window,
-                              cudaStream_t stream) {
+                              const int* positions, int tokens, float* part_o, float* part_ml, int* counters,
+                              int splits, int min_tiles, int heads, int kv_heads, int head_dim, int page_size, float scale,
+                              int window, cudaStream_t stream) {
     if (int rc = check_common("attn_decode", heads, kv_heads, head_dim, page_size, max_blocks, window, 16)) return rc;
-    MRUN_REQUIRE(tokens >= 0 && splits >= 1 && splits <= 65535, "attn_decode: tokens=%d splits=%d", tokens, splits);
-    MRUN_REQUIRE(splits == 1 || (part_o && part_ml), "attn_decode: %d splits need scratch memory", splits);
+    MRUN_REQUIRE(tokens >= 0 && splits >= 1 && splits <= 65535 && min_tiles >= 1,
+                 "attn_decode: tokens=%d splits=%d min_tiles=%d", tokens, splits, min_tiles);
+    MRUN_REQUIRE(splits == 1 || (part_o && part_ml && counters), "attn_decode: %d splits need scratch memory", splits);
     if (tokens == 0) return 0;
     static bool configured = false;
     if (!configured) {
@@ -494,11 +560,17 @@ MRUN_API int mrun_attn_decode(const void* q, long q_stride, void* out, const voi
     }
     decode_kernel<<<dim3(tokens, kv_heads, splits), THREADS, DECODE_SMEM, stream>>>(
         (const bf16*)q, q_stride, (bf16*)out, (const bf16*)k_cache, (const bf16*)v_cache, block_tables, max_blocks,
-        token_slot, positions, part_o, part_ml, heads, kv_heads, page_size, scale * LOG2E, window);
+        token_slot, positions, part_o, part_ml, counters, min_tiles, heads, kv_heads, page_size, shift_of(page_size),
+        scale * LOG2E, window);
     MRUN_CHECK_LAUNCH("attn_decode");
-    if (splits > 1) {
-        combine_kernel<<<tokens * heads, D, 0, stream>>>(part_o, part_ml, (bf16*)out, splits);
-        MRUN_CHECK_LAUNCH("attn_combine");
-    }
     return 0;
+}
+
+// Blocks of the decode kernel that fit on one multiprocessor (for choosing the number of splits).
+MRUN_API int mrun_attn_decode_occupancy() {
+    int blocks = 0;
+    cudaFuncSetAttribute(decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)DECODE_SMEM);
+    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&blocks, decode_kernel, THREADS, DECODE_SMEM) != cudaSuccess)
+        return -1;
+    return blocks;
 }

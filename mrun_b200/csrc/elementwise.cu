@@ -74,30 +74,115 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ resid, const TA* __restri
     }
 }
 
+// The same operation for widths that are a multiple of 8 and at most 8192: every thread keeps up
+// to four 8-element chunks in registers and moves them with 16-byte loads and stores, so a row
+// takes one pass and the latency of a few independent loads.  One block of 256 threads per row
+// whatever the batch: the order of additions depends on the width only.
+template <typename TA> struct Vec8;
+template <> struct Vec8<float> {
+    static __device__ __forceinline__ void load(const float* p, float (&v)[8]) {
+        const float4 a = *reinterpret_cast<const float4*>(p), b = *reinterpret_cast<const float4*>(p + 4);
+        v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+    }
+    static __device__ __forceinline__ void store(float* p, const float (&v)[8]) {
+        *reinterpret_cast<float4*>(p) = make_float4(v[0], v[1], v[2], v[3]);
+        *reinterpret_cast<float4*>(p + 4) = make_float4(v[4], v[5], v[6], v[7]);
+    }
+};
+template <> struct Vec8<__nv_bfloat16> {
+    static __device__ __forceinline__ void load(const __nv_bfloat16* p, float (&v)[8]) {
+        const uint4 raw = *reinterpret_cast<const uint4*>(p);
+        const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const float2 f = __bfloat1622float2(h[i]);
+            v[2 * i] = f.x; v[2 * i + 1] = f.y;
+        }
+    }
+    static __device__ __forceinline__ void store(__nv_bfloat16* p, const float (&v)[8]) {
+        uint4 raw;
+        __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&raw);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) h[i] = __floats2bfloat162_rn(v[2 * i], v[2 * i + 1]);
+        *reinterpret_cast<uint4*>(p) = raw;
+    }
+};
+
+template <typename TA>
+__global__ void __launch_bounds__(256)
+add_rmsnorm_vec_kernel(float* __restrict__ resid, const TA* __restrict__ delta,
+                       const float* __restrict__ weight, float eps, TA* __restrict__ out,
+                       const int* __restrict__ rows, int hidden) {
+    __shared__ float scratch[33];
+    const int r = blockIdx.x;
+    const size_t src = (size_t)(rows ? rows[r] : r) * hidden;
+    const int chunks = hidden >> 3;
+    float v[4][8];
+    float ss = 0.f;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const int c = threadIdx.x + i * 256;
+        if (c < chunks) {
+            Vec8<float>::load(resid + src + c * 8, v[i]);
+            if (delta) {
+                float d[8];
+                Vec8<TA>::load(delta + src + c * 8, d);
+#pragma unroll
+                for (int e = 0; e < 8; ++e) v[i][e] += d[e];
+            }
+#pragma unroll
+            for (int e = 0; e < 8; ++e) ss += v[i][e] * v[i][e];
+        }
+    }
+    ss = block_sum(ss, scratch);
+    const float inv = rsqrtf(ss / (float)hidden + eps);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const int c = threadIdx.x + i * 256;
+        if (c < chunks) {
+            if (!rows && delta) Vec8<float>::store(resid + src + c * 8, v[i]);
+            float w[8], y[8];
+            Vec8<float>::load(weight + c * 8, w);
+#pragma unroll
+            for (int e = 0; e < 8; ++e) y[e] = v[i][e] * inv * w[e];
+            Vec8<TA>::store(out + (size_t)r * hidden + c * 8, y);
+        }
+    }
+}
+
+template <typename TA>
+static int launch_add_rmsnorm(float* resid, const void* delta, const float* weight, float eps, void* out,
+                              const int* rows, int n_rows, int hidden, cudaStream_t stream) {
+    const bool aligned = (((uintptr_t)resid | (uintptr_t)delta | (uintptr_t)weight | (uintptr_t)out) & 15) == 0;
+    if (hidden % 8 == 0 && hidden <= 8192 && aligned) {
+        add_rmsnorm_vec_kernel<TA><<<n_rows, 256, 0, stream>>>(resid, (const TA*)delta, weight, eps, (TA*)out,
+                                                              rows, hidden);
+        return 0;
+    }
+    const size_t smem = (size_t)hidden * sizeof(float);
+    if (smem > 48 * 1024)
+        MRUN_CHECK_CUDA(cudaFuncSetAttribute(add_rmsnorm_kernel<TA>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                             (int)smem), "add_rmsnorm");
+    add_rmsnorm_kernel<TA><<<n_rows, 256, smem, stream>>>(resid, (const TA*)delta, weight, eps, (TA*)out, rows,
+                                                          hidden);
+    return 0;
+}
+
 MRUN_API int mrun_add_rmsnorm(float* resid, const void* delta, const float* weight, float eps, void* out,
                               int act_dtype, const int* rows, int n_rows, int hidden,
                               cudaStream_t stream) {
     MRUN_REQUIRE(n_rows >= 0 && hidden > 0, "add_rmsnorm: bad sizes rows=%d hidden=%d", n_rows, hidden);
-    const size_t smem = (size_t)hidden * sizeof(float);
-    MRUN_REQUIRE(smem <= 200 * 1024, "add_rmsnorm: hidden=%d exceeds the supported 51200", hidden);
+    MRUN_REQUIRE((size_t)hidden * sizeof(float) <= 200 * 1024, "add_rmsnorm: hidden=%d exceeds the supported 51200",
+                 hidden);
     if (n_rows == 0) return 0;
-    if (act_dtype == MRUN_F32) {
-        if (smem > 48 * 1024)
-            MRUN_CHECK_CUDA(cudaFuncSetAttribute(add_rmsnorm_kernel<float>,
-                                                 cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem),
-                            "add_rmsnorm");
-        add_rmsnorm_kernel<float><<<n_rows, 256, smem, stream>>>(resid, (const float*)delta, weight, eps,
-                                                                 (float*)out, rows, hidden);
-    } else if (act_dtype == MRUN_BF16) {
-        if (smem > 48 * 1024)
-            MRUN_CHECK_CUDA(cudaFuncSetAttribute(add_rmsnorm_kernel<__nv_bfloat16>,
-                                                 cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem),
-                            "add_rmsnorm");
-        add_rmsnorm_kernel<__nv_bfloat16><<<n_rows, 256, smem, stream>>>(
-            resid, (const __nv_bfloat16*)delta, weight, eps, (__nv_bfloat16*)out, rows, hidden);
-    } else {
+    int rc;
+    if (act_dtype == MRUN_F32)
+        rc = launch_add_rmsnorm<float>(resid, delta, weight, eps, out, rows, n_rows, hidden, stream);
+    else if (act_dtype == MRUN_BF16)
+        rc = launch_add_rmsnorm<__nv_bfloat16>(resid, delta, weight, eps, out, rows, n_rows, hidden, stream);
+    else
         return mrun_set_error("add_rmsnorm: unknown dtype code %d", act_dtype);
-    }
+    if (rc) return rc;
     MRUN_CHECK_LAUNCH("add_rmsnorm");
     return 0;
 }

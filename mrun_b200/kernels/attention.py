@@ -19,17 +19,53 @@ from . import lib as _lib
 from . import ops
 from .ops import _c_float, _c_int, _c_long, _ptr, _stream
 
-SM_COUNT_TARGET = 148 * 4      # blocks wanted in flight for the decode kernel
 MAX_SPLITS = 64
+COUNTER_CAPACITY = 1 << 16     # (token, kv head) pairs of one decode launch that may be split
+
+_counters = {}                 # device -> int32 zeros, handed to every split launch
+_slots = {}                    # head size -> blocks of the decode kernel resident on the device
+
+
+def _decode_slots(head_dim: int, library) -> int:
+    slots = _slots.get(head_dim)
+    if slots is None:
+        query = library._dll.mrun_attn_decode_occupancy
+        query.restype = ctypes.c_int
+        per_sm = max(1, query())
+        sms = torch.cuda.get_device_properties(torch.cuda.current_device()).multi_processor_count
+        slots = _slots[head_dim] = per_sm * sms
+    return slots
+
+
+def _split_counters(device: torch.device) -> torch.Tensor:
+    """Zeroed counters the decode kernel's splits meet at; the kernel leaves them zero.  One
+    buffer per device, never reallocated, so captured graphs may keep its address."""
+    counters = _counters.get(device)
+    if counters is None:
+        counters = _counters[device] = torch.zeros(COUNTER_CAPACITY, dtype=torch.int32, device=device)
+    return counters
 
 
 def supports_tensor_cores(dtype: torch.dtype, head_dim: int, group: int) -> bool:
     return dtype == torch.bfloat16 and head_dim % 16 == 0 and 16 <= head_dim <= 256 and group <= 64
 
 
-def decode_splits(tokens: int, kv_heads: int, max_kv_len: int) -> int:
+def decode_splits(tokens: int, kv_heads: int, max_kv_len: int, slots: int):
+    """(splits, min_tiles): how many ways the keys of a token may be split and the fewest 64-key
+    tiles a split takes.  Few (token, kv head) pairs: as many splits as fill the device once, four
+    tiles each at least.  More pairs than the device holds at a time: up to four rounds of blocks,
+    so that the last, partly filled round costs little, but only for contexts long enough to give
+    every split sixteen tiles.  (Measured on B200 at head size 128.)  The kernel applies
+    ``min_tiles`` to each token's own context, so short contexts use fewer splits."""
+    pairs = max(1, tokens * kv_heads)
     blocks = max(1, -(-max_kv_len // 64))
-    return max(1, min(-(-SM_COUNT_TARGET // max(1, tokens * kv_heads)), blocks, MAX_SPLITS))
+    if pairs > COUNTER_CAPACITY:
+        return 1, 1
+    if pairs < slots:
+        want, min_tiles = slots // pairs, 4
+    else:
+        want, min_tiles = -(-4 * slots // pairs), 16
+    return max(1, min(want, -(-blocks // min_tiles), MAX_SPLITS)), min_tiles
 
 
 def prefill_tiles(ctx, tokens_per_tile: int):
@@ -65,13 +101,14 @@ def paged_attention(q: torch.Tensor, q_stride: int, out: torch.Tensor, cache, gr
     tail = (_c_int(heads), _c_int(kv_heads), _c_int(head_dim), _c_int(page_size), _c_float(scale),
             _c_int(window), _stream())
     if ctx.all_decode and ratio <= 16:
-        splits = decode_splits(tokens, kv_heads, ctx.max_kv_len)
-        part_o = part_ml = None
+        splits, min_tiles = decode_splits(tokens, kv_heads, ctx.max_kv_len, _decode_slots(head_dim, library))
+        part_o = part_ml = counters = None
         if splits > 1:
             part_o = torch.empty((tokens, heads, splits, head_dim), dtype=torch.float32, device=q.device)
             part_ml = torch.empty((tokens, heads, splits, 2), dtype=torch.float32, device=q.device)
+            counters = _split_counters(q.device)
         library.call("mrun_attn_decode", _ptr(q), _c_long(q_stride), _ptr(out), *common, _c_int(tokens),
-                     _ptr(part_o), _ptr(part_ml), _c_int(splits), *tail)
+                     _ptr(part_o), _ptr(part_ml), _ptr(counters), _c_int(splits), _c_int(min_tiles), *tail)
         return out
     first, count, n_tiles = prefill_tiles(ctx, 64 // ratio)
     if tokens > ctx.real_tokens:

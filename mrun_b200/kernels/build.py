@@ -151,8 +151,12 @@ def build_attention(head_dim: int) -> str:
     """The tensor-core attention kernels specialised for one head size."""
     if head_dim % 16 or not 16 <= head_dim <= 256:
         raise BuildError(f"the tensor-core attention takes head sizes 16, 32, ... 256, not {head_dim}")
-    return build_library(f"mrun_attn_d{head_dim}", ("common.cu", "attention_mma.cu"),
-                         {"MRUN_HEAD_DIM": head_dim})
+    defines = {"MRUN_HEAD_DIM": head_dim}
+    stages = os.environ.get("MRUN_DECODE_STAGES")        # tuning knob: key/value tiles in flight
+    if stages:
+        defines["MRUN_DECODE_STAGES"] = int(stages)
+    return build_library(f"mrun_attn_d{head_dim}_s{stages}" if stages else f"mrun_attn_d{head_dim}",
+                         ("common.cu", "attention_mma.cu"), defines)
 
 
 # head sizes of the configurations this repository measures and tests

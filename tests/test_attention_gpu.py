@@ -125,10 +125,38 @@ def test_decode_batch_against_plain(heads, kv_heads, head_dim, page_size, window
     got = case.run(scale)
     assert (got[:case.tokens] - want[:case.tokens]).abs().max() <= 2e-2 * want.abs().max()
     assert got[case.tokens:].abs().max() == 0, "padding rows must come out as zeros"
-    # more splits than the heuristic picks: the context is cut at every 64 keys
-    case.ctx.max_kv_len = 64 * 64
+    # a captured step sizes its grid for the longest context the model allows: more splits offered
+    case.ctx.max_kv_len = 64 * 1024
     case.ctx.shared.clear()
     assert (case.run(scale)[:case.tokens] - want[:case.tokens]).abs().max() <= 2e-2 * want.abs().max()
+
+
+@pytest.mark.parametrize("splits,min_tiles", [(1, 1), (3, 1), (16, 1), (64, 1), (5, 2), (16, 4)])
+def test_decode_splits_of_every_kind(splits, min_tiles):
+    """The split-key kernel called directly with forced split counts, twice in a row (the counters
+    the splits meet at must be back at zero), against the CUDA-core kernel."""
+    import ctypes
+    from mrun_b200.kernels import lib as L, ops
+    from mrun_b200.kernels.ops import _c_float, _c_int, _c_long, _ptr, _stream
+    heads, kv_heads, head_dim, page_size = 8, 2, 64, 16
+    segments = [(0, 1), (63, 1), (64, 1), (700, 1), (1023, 1), (129, 1)]
+    case = Case(segments, heads, kv_heads, head_dim, page_size, torch.bfloat16, seed=21, pad=2)
+    scale = head_dim ** -0.5
+    want = case.run(scale, force_generic=True)
+    n = case.tokens + case.pad
+    part_o = torch.full((n, heads, splits, head_dim), float("nan"), device=DEV)
+    part_ml = torch.full((n, heads, splits, 2), float("nan"), device=DEV)
+    counters = torch.zeros(n * kv_heads, dtype=torch.int32, device=DEV)
+    for _ in range(2):
+        out = torch.full((n, heads * head_dim), 3.0, dtype=torch.bfloat16, device=DEV)
+        L.attention(head_dim).call(
+            "mrun_attn_decode", _ptr(case.qd), _c_long(case.qd.stride(0)), _ptr(out), _ptr(case.kd), _ptr(case.vd),
+            _ptr(case.table), _c_int(case.group.max_blocks), _ptr(case.ctx.token_slot), _ptr(case.ctx.positions),
+            _c_int(n), _ptr(part_o), _ptr(part_ml), _ptr(counters), _c_int(splits), _c_int(min_tiles), _c_int(heads),
+            _c_int(kv_heads), _c_int(head_dim), _c_int(page_size), _c_float(scale), _c_int(0), _stream())
+        got = out.float().cpu()
+        assert (got - want).abs().max() <= 2e-2 * want.abs().max()
+        assert int(counters.abs().sum()) == 0
 
 
 @pytest.mark.parametrize("far", [0, 15, 16, 63, 64, 65, 127, 255, 256, 400, 511])
