@@ -327,31 +327,40 @@ MRUN_API int mrun_qk_norm_rope_cache(void* qkv, int act_dtype, const float* q_we
 }
 
 // ------------------------------------------------------------------------------------------
-// Gated activation: out[t, i] = act(gate_up[t, i]) * gate_up[t, inter + i], act = SiLU
+// Gated activation: out[t, i] = act(gate_i) * up_i, act = SiLU
 // (z * sigmoid(z), crates/mrun-engine/src/models/activations.rs:46-59), in 32-bit.
+// Layout of gate_up[t, :]: block == 0: all gates, then all ups (gate_i at i, up_i at inter + i).
+// block == 8: runs of eight gates followed by the eight ups of the same outputs
+// (gate_i at 16 (i / 8) + i % 8, up_i eight further), the row order the decode GEMM's fused
+// epilogue wants of the stacked weight.
 // ------------------------------------------------------------------------------------------
 template <typename TA>
-__global__ void swiglu_kernel(const TA* __restrict__ gate_up, TA* __restrict__ out, long total, int inter) {
+__global__ void swiglu_kernel(const TA* __restrict__ gate_up, TA* __restrict__ out, long total, int inter,
+                              int block) {
     const long i = (long)blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= total) return;
     const long t = i / inter;
     const int c = (int)(i - t * inter);
-    const float g = to_float(gate_up[t * 2 * inter + c]);
-    const float u = to_float(gate_up[t * 2 * inter + inter + c]);
+    const long gi = block ? t * 2 * inter + 2 * (c & ~7) + (c & 7) : t * 2 * inter + c;
+    const long ui = block ? gi + 8 : gi + inter;
+    const float g = to_float(gate_up[gi]);
+    const float u = to_float(gate_up[ui]);
     out[i] = from_float<TA>(g / (1.f + expf(-g)) * u);
 }
 
-MRUN_API int mrun_swiglu(const void* gate_up, void* out, int act_dtype, int tokens, int inter,
+MRUN_API int mrun_swiglu(const void* gate_up, void* out, int act_dtype, int tokens, int inter, int block,
                          cudaStream_t stream) {
     MRUN_REQUIRE(tokens >= 0 && inter > 0, "swiglu: bad sizes tokens=%d inter=%d", tokens, inter);
+    MRUN_REQUIRE(block == 0 || (block == 8 && inter % 8 == 0),
+                 "swiglu: the interleaved layout has runs of 8 and needs inter=%d to be a multiple of 8", inter);
     if (tokens == 0) return 0;
     const long total = (long)tokens * inter;
     const unsigned blocks = (unsigned)((total + 255) / 256);
     if (act_dtype == MRUN_F32)
-        swiglu_kernel<float><<<blocks, 256, 0, stream>>>((const float*)gate_up, (float*)out, total, inter);
+        swiglu_kernel<float><<<blocks, 256, 0, stream>>>((const float*)gate_up, (float*)out, total, inter, block);
     else if (act_dtype == MRUN_BF16)
         swiglu_kernel<__nv_bfloat16><<<blocks, 256, 0, stream>>>((const __nv_bfloat16*)gate_up,
-                                                                 (__nv_bfloat16*)out, total, inter);
+                                                                 (__nv_bfloat16*)out, total, inter, block);
     else
         return mrun_set_error("swiglu: unknown dtype code %d", act_dtype);
     MRUN_CHECK_LAUNCH("swiglu");

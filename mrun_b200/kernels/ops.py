@@ -150,14 +150,41 @@ def paged_attention_generic(q: torch.Tensor, q_stride: int, out: torch.Tensor, k
     return out
 
 
-def swiglu(gate_up: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
-    """out = silu(gate_up[:, :I]) * gate_up[:, I:]."""
+def swiglu(gate_up: torch.Tensor, out: torch.Tensor, interleaved: bool = False) -> torch.Tensor:
+    """out = silu(gate) * up.  Plain layout: gate_up[:, :I] are the gates, gate_up[:, I:] the ups.
+    Interleaved: runs of eight gates followed by the eight ups of the same outputs."""
     _check(gate_up, "gate_up"); _check(out, "out", gate_up.dtype)
     tokens, inter = out.shape
     if gate_up.shape != (tokens, 2 * inter):
         raise KernelError(f"swiglu: gate_up {tuple(gate_up.shape)} vs out {tuple(out.shape)}")
     _lib.core().call("mrun_swiglu", _ptr(gate_up), _ptr(out), dtype_code(out.dtype), _c_int(tokens),
-                     _c_int(inter), _stream())
+                     _c_int(inter), _c_int(8 if interleaved else 0), _stream())
+    return out
+
+
+SKINNY_ROWS = 16      # the decode GEMM takes up to this many rows
+
+
+def skinny_ok(x: torch.Tensor, w: torch.Tensor) -> bool:
+    """Whether the decode GEMM takes this product: few rows, bf16, K a multiple of 32."""
+    return (x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and x.shape[0] <= SKINNY_ROWS
+            and x.shape[1] % 32 == 0 and x.stride(1) == 1 and x.stride(0) % 8 == 0
+            and x.data_ptr() % 16 == 0)
+
+
+def gemm_skinny(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype = torch.bfloat16,
+                swiglu_rows: bool = False) -> torch.Tensor:
+    """y = x @ w.T for at most 16 rows, reading w once at HBM speed.  ``swiglu_rows``: w holds gate
+    and up rows interleaved in runs of eight and y = silu(gate) * up has half as many columns."""
+    _check(x, "x", torch.bfloat16, dense=False); _check(w, "w", torch.bfloat16)
+    m, k = x.shape
+    n = w.shape[0]
+    if w.shape[1] != k:
+        raise KernelError(f"gemm_skinny: x {tuple(x.shape)} vs w {tuple(w.shape)}")
+    out = torch.empty((m, n // 2 if swiglu_rows else n), dtype=out_dtype, device=x.device)
+    _lib.core().call("mrun_gemm_skinny", _ptr(x), _ptr(w), _ptr(out), dtype_code(out_dtype),
+                     _c_int(1 if swiglu_rows else 0), _c_int(m), _c_int(n), _c_int(k),
+                     _c_long(x.stride(0) if m > 1 else max(k, x.stride(0))), _c_long(out.shape[1]), _stream())
     return out
 
 
@@ -179,12 +206,15 @@ def gemm_f32_nt(x: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] = 
 
 
 def linear(x: torch.Tensor, w: torch.Tensor, out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
-    """y = x @ w.T.  float32: this library's own IEEE kernel.  bfloat16: the vendor GEMM library
-    with 32-bit accumulation (the reference calls its array library's matmul for the same
-    products, crates/mrun-engine/src/load.rs:294-306)."""
+    """y = x @ w.T.  float32: this library's own IEEE kernel.  bfloat16 with at most 16 rows (decode):
+    this library's weight-streaming tensor-core kernel.  bfloat16 otherwise: the vendor GEMM
+    library with 32-bit accumulation (the reference calls its array library's matmul for the
+    same products, crates/mrun-engine/src/load.rs:294-306)."""
     if x.dtype == torch.float32:
         return gemm_f32_nt(x, w)
     _check(x, "x", torch.bfloat16, dense=False); _check(w, "w", torch.bfloat16)
+    if skinny_ok(x, w):
+        return gemm_skinny(x, w, out_dtype or torch.bfloat16)
     if out_dtype is None or out_dtype == torch.bfloat16:
         return torch.mm(x, w.t())
     return torch.mm(x, w.t(), out_dtype=out_dtype)

@@ -142,8 +142,41 @@ def test_gemm_f32(m, n, k):
     assert torch.equal(ops().gemm_f32_nt(wide[:, :k], w), ops().gemm_f32_nt(wide[:, :k].contiguous(), w))
 
 
+@pytest.mark.parametrize("m", [1, 3, 8, 9, 16])
+@pytest.mark.parametrize("n,k", [(16, 32), (509, 96), (6144, 4096), (1000, 12288), (24, 160)])
+def test_gemm_skinny(m, n, k):
+    x, w = rnd(m, k, dtype=torch.bfloat16, seed=20), rnd(n, k, dtype=torch.bfloat16, seed=21, scale=0.05)
+    want = x.float() @ w.float().T
+    for out_dtype, tol in ((torch.float32, 2e-5), (torch.bfloat16, 8e-3)):
+        got = ops().gemm_skinny(x, w, out_dtype=out_dtype)
+        assert got.dtype == out_dtype and got.shape == (m, n)
+        assert (got.float() - want).abs().max() <= tol * want.abs().max() * (4 if out_dtype == torch.float32 else 1)
+    # a row's result does not depend on the other rows, and a strided x is taken as it is
+    alone = ops().gemm_skinny(x[m // 2:m // 2 + 1], w, out_dtype=torch.float32)
+    assert torch.equal(alone[0], ops().gemm_skinny(x, w, out_dtype=torch.float32)[m // 2])
+    wide = rnd(m, k + 40, dtype=torch.bfloat16, seed=22)
+    assert torch.equal(ops().gemm_skinny(wide[:, :k], w), ops().gemm_skinny(wide[:, :k].contiguous(), w))
+
+
+@pytest.mark.parametrize("m,inter,k", [(1, 8, 32), (5, 200, 96), (16, 12288, 4096), (9, 9728, 2560)])
+def test_gemm_skinny_gated_epilogue(m, inter, k):
+    x = rnd(m, k, dtype=torch.bfloat16, seed=23)
+    gate, up = rnd(inter, k, dtype=torch.bfloat16, seed=24, scale=0.05), rnd(inter, k, dtype=torch.bfloat16, seed=25, scale=0.05)
+    w = torch.stack([gate.view(-1, 8, k), up.view(-1, 8, k)], dim=1).reshape(2 * inter, k).contiguous()
+    g = (x.float() @ gate.float().T).bfloat16().float()
+    u = (x.float() @ up.float().T).bfloat16().float()
+    want = g * torch.sigmoid(g) * u
+    got = ops().gemm_skinny(x, w, swiglu_rows=True)
+    assert got.shape == (m, inter)
+    assert (got.float() - want).abs().max() <= 1.2e-2 * want.abs().max()
+    # the unfused pair (product, then activation on the interleaved layout) agrees
+    act = torch.empty((m, inter), dtype=torch.bfloat16, device=DEV)
+    ops().swiglu(torch.mm(x, w.t()), act, interleaved=True)
+    assert (act.float() - want).abs().max() <= 1.2e-2 * want.abs().max()
+
+
 def test_linear_bf16_accumulates_in_32_bits():
-    x, w = rnd(9, 1024, dtype=torch.bfloat16, seed=13), rnd(77, 1024, dtype=torch.bfloat16, seed=14)
+    x, w = rnd(39, 1024, dtype=torch.bfloat16, seed=13), rnd(77, 1024, dtype=torch.bfloat16, seed=14)
     got = ops().linear(x, w, out_dtype=torch.float32)
     want = x.float() @ w.float().T
     assert got.dtype == torch.float32 and (got - want).abs().max() <= 1e-3 * want.abs().max()
