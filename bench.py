@@ -112,7 +112,7 @@ def fill_requests(executor, batch: int, context: int, vocab: int, tag: str):
     return requests
 
 
-def time_decode(executor, requests, vocab: int, steps: int, warmup: int):
+def time_decode(executor, requests, vocab: int, steps: int, warmup: int, profiler_range: bool = False):
     """Device time of ``steps`` decode steps: captured step + token read-back, as generation does."""
     import torch
     from mrun_b200.engine import StepEntry
@@ -126,11 +126,15 @@ def time_decode(executor, requests, vocab: int, steps: int, warmup: int):
     torch.cuda.synchronize()
     begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     launches = executor.launches.total
+    if profiler_range:                   # lets a profiler started with --profile-from-start off see only this
+        torch.cuda.profiler.start()
     begin.record()
     for _ in range(steps):
         one()
     end.record()
     torch.cuda.synchronize()
+    if profiler_range:
+        torch.cuda.profiler.stop()
     return begin.elapsed_time(end), executor.launches.total - launches
 
 
@@ -147,6 +151,8 @@ def main() -> int:
                         help="decode batch sizes to run, comma separated (for profiling one point)")
     parser.add_argument("--skip-prefill", action="store_true")
     parser.add_argument("--skip-e2e", action="store_true")
+    parser.add_argument("--profiler-range", action="store_true",
+                        help="bracket the timed decode steps with cudaProfilerStart/Stop")
     args = parser.parse_args()
 
     if args.impl == "reference":
@@ -220,7 +226,7 @@ def main() -> int:
         sampler = ClockSampler()
         if batch == batches[0]:
             sampler.start()
-        ms, n_launch = time_decode(executor, requests, vocab, args.steps, args.warmup)
+        ms, n_launch = time_decode(executor, requests, vocab, args.steps, args.warmup, args.profiler_range)
         if batch == batches[0]:
             clocks = sampler.stop()
             launches = n_launch

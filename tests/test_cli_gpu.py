@@ -1,0 +1,62 @@
+"""The command line: ``mrun random`` writes a folder, ``mrun run`` generates from token ids with the
+reference's option names, prints the ids, and refuses bad flags before loading anything."""
+from __future__ import annotations
+
+import json
+import os
+import subprocess
+import sys
+
+import pytest
+
+import plain_qwen3 as plain
+from tiny_models import TINY, random_tokens
+
+ROOT = os.path.normpath(os.path.join(os.path.dirname(os.path.abspath(__file__)), os.pardir))
+MRUN = os.path.join(ROOT, "bin", "mrun")
+
+
+def run(*args):
+    return subprocess.run([sys.executable, MRUN, *args], capture_output=True, text=True, timeout=600)
+
+
+def test_usage_errors_need_no_model():
+    for flags, text in ((["--max-tokens", "0"], "--max-tokens must be at least 1"),
+                        (["--temperature", "-1"], "temperature must be 0 or more"),
+                        (["--top-p", "0"], "top_p must be in (0, 1]")):
+        result = run("run", "/nonexistent", "--prompt", "1,2", *flags)
+        assert result.returncode == 2 and text in result.stderr
+    assert run("run", "/nonexistent", "--prompt", "").returncode == 2
+
+
+@pytest.mark.gpu
+def test_random_then_run(tmp_path):
+    config = dict(TINY["A"]["config"], model_type="qwen3", architectures=["Qwen3ForCausalLM"])
+    (tmp_path / "cfg.json").write_text(json.dumps(config))
+    folder = str(tmp_path / "model")
+    made = run("random", folder, "--config", str(tmp_path / "cfg.json"), "--seed", "11", "--std", "0.08")
+    assert made.returncode == 0, made.stderr
+    assert sorted(os.listdir(folder)) == ["config.json", "model.safetensors"]
+    cfg, weights = plain.load_folder(folder)
+    prompt = random_tokens(cfg["vocab_size"], 17, seed=1)
+    ids = tmp_path / "prompt.txt"
+    ids.write_text(" ".join(map(str, prompt)))
+
+    result = run("run", folder, "--prompt", str(ids), "--max-tokens", "8", "--dtype", "float32", "--ignore-eos")
+    assert result.returncode == 0, result.stderr
+    tokens = [int(t) for t in result.stdout.strip().split(",")]
+    assert tokens == plain.generate(cfg, weights, prompt, 8)
+    assert "prompt: 17 tokens" in result.stderr and "generation: 8 tokens" in result.stderr
+
+    inline = run("run", folder, "--prompt", ",".join(map(str, prompt)), "--max-tokens", "8", "--dtype", "float32",
+                 "--temperature", "0.8", "--seed", "5", "--ignore-eos")
+    again = run("run", folder, "--prompt", ",".join(map(str, prompt)), "--max-tokens", "8", "--dtype", "float32",
+                "--temperature", "0.8", "--seed", "5", "--ignore-eos")
+    assert inline.returncode == 0 and inline.stdout == again.stdout
+    assert [int(t) for t in inline.stdout.strip().split(",")] == plain.generate(cfg, weights, prompt, 8, temperature=0.8, seed=5)
+
+    info = run("run", folder, "--info", "--context", "1K")
+    assert info.returncode == 0 and json.loads(info.stdout)["capacity_tokens"] == 1024
+
+    bad = run("run", str(tmp_path), "--prompt", "1")
+    assert bad.returncode == 1 and "config.json" in bad.stderr

@@ -1,0 +1,226 @@
+"""Parts and arrangements that are not Qwen3's, defined here and run without a change to the
+framework: a mixer that keeps state of a fixed size per request (registered from this file), a
+rotary encoding with its own table, attention with a window, a layer that runs twice, and a layer
+that reads the cache another run wrote.  The toy model is compared with a plain whole-sequence
+implementation under several ways of cutting the work."""
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import ClassVar
+
+import pytest
+import torch
+
+import plain_qwen3 as plain
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+HIDDEN, HEADS, KV_HEADS, HEAD_DIM, INTER, VOCAB, EPS, THETA, WINDOW = 48, 4, 2, 16, 80, 101, 1e-5, 1e4, 9
+
+
+# ------------------------------------------------------------------ toy parts (test-side only)
+
+@dataclass(frozen=True)
+class DecaySpec:
+    """state_t = decay * state_{t-1} + W x_t ; y_t = state_t : one vector of state per request."""
+    kind: ClassVar[str] = "toy_decay"
+    hidden: int
+    decay: float
+
+
+@dataclass(frozen=True)
+class HalfStepRotarySpec:
+    """Rotary positions that advance half a step per token."""
+    kind: ClassVar[str] = "toy_half_step_rotary"
+    head_dim: int
+    rotary_dim: int
+    theta: float
+
+
+def register_toy_parts():
+    from mrun_b200.cache import FixedState
+    from mrun_b200.config import TensorSpec
+    from mrun_b200.parts import register_mixer, register_position
+
+    @register_mixer("toy_decay")
+    class DecayMixer:
+        graph_safe = False                     # walks the step's segments on the host
+
+        @staticmethod
+        def tensor_specs(spec, prefix):
+            return [TensorSpec(f"{prefix}.in_proj.weight", (spec.hidden, spec.hidden))]
+
+        def __init__(self, spec, tensors, runtime):
+            self.spec = spec
+            self.weight = tensors["in_proj.weight"].to(runtime.device, torch.float32)
+
+        def cache_need(self):
+            return FixedState((self.spec.hidden,), "float32")
+
+        def forward(self, x, ctx, cache):
+            out = torch.empty_like(x)
+            projected = x.float() @ self.weight.T
+            for seg in ctx.segments:
+                state = cache.state[seg.slot]
+                for row in range(seg.q_start, seg.q_start + seg.q_len):
+                    state.mul_(self.spec.decay).add_(projected[row])
+                    out[row] = state.to(x.dtype)
+            return out
+
+    @register_position("toy_half_step_rotary")
+    class HalfStepRotary:
+        @staticmethod
+        def tensor_specs(spec, prefix):
+            return []
+
+        def __init__(self, spec, tensors, runtime):
+            self.spec, self.rotary_dim = spec, spec.rotary_dim
+            half = spec.rotary_dim // 2
+            self.inv = (torch.tensor(spec.theta, dtype=torch.float64)
+                        ** (-2.0 * torch.arange(half, dtype=torch.float64) / spec.rotary_dim)).to(runtime.device)
+
+        def rotation(self, ctx):
+            key = ("toy_half_step_rotary", self.spec)
+            if key not in ctx.shared:
+                angle = ctx.positions.double()[:, None] * 0.5 * self.inv[None, :]
+                ctx.shared[key] = torch.stack([angle.cos(), angle.sin()], dim=-1).float().contiguous()
+            return ctx.shared[key]
+
+
+def toy_spec():
+    from mrun_b200.config import (AttentionSpec, GatedMLPSpec, LayerSpec, ModelSpec, RMSNormSpec, RotarySpec,
+                                  ScheduleEntry)
+    norm, mlp = RMSNormSpec(HIDDEN, EPS), GatedMLPSpec(HIDDEN, INTER)
+    full = AttentionSpec(HIDDEN, HEADS, KV_HEADS, HEAD_DIM, HEAD_DIM ** -0.5, RMSNormSpec(HEAD_DIM, EPS),
+                         RotarySpec(HEAD_DIM, HEAD_DIM, THETA), None)
+    windowed = AttentionSpec(HIDDEN, HEADS, KV_HEADS, HEAD_DIM, HEAD_DIM ** -0.5, None,
+                             HalfStepRotarySpec(HEAD_DIM, 8, THETA), WINDOW)
+    layers = (
+        LayerSpec("model.layers.0", full, mlp, norm, norm),
+        LayerSpec("model.layers.1", DecaySpec(HIDDEN, 0.9), mlp, norm, norm, mixer_prefix="decay"),
+        LayerSpec("model.layers.2", windowed, mlp, norm, norm),
+    )
+    schedule = (ScheduleEntry(0), ScheduleEntry(1), ScheduleEntry(2), ScheduleEntry(1), ScheduleEntry(0, cache_of=0))
+    return ModelSpec("ToyForCausalLM", VOCAB, HIDDEN, 512, layers, norm, tie_embeddings=False, schedule=schedule)
+
+
+# ------------------------------------------------------------------ the plain toy model
+
+def plain_attention(h, w, prefix, positions, qk_norm, rotary_dim, step, window, shared_kv=None):
+    L = h.shape[0]
+    q = (h @ w[f"{prefix}.q_proj.weight"].T).view(L, HEADS, HEAD_DIM)
+    k = (h @ w[f"{prefix}.k_proj.weight"].T).view(L, KV_HEADS, HEAD_DIM)
+    v = (h @ w[f"{prefix}.v_proj.weight"].T).view(L, KV_HEADS, HEAD_DIM)
+    if qk_norm:
+        q = plain.rms_norm(q, w[f"{prefix}.q_norm.weight"], EPS)
+        k = plain.rms_norm(k, w[f"{prefix}.k_norm.weight"], EPS)
+    scaled = positions.double() * step
+    q, k = plain.rope(q, scaled, THETA, rotary_dim), plain.rope(k, scaled, THETA, rotary_dim)
+    if shared_kv is not None:
+        k, v = shared_kv
+    o = plain.attention_scores_softmax_values(q, k, v, HEAD_DIM ** -0.5, positions, window)
+    return o.reshape(L, HEADS * HEAD_DIM) @ w[f"{prefix}.o_proj.weight"].T, (k, v)
+
+
+def plain_toy(w, tokens):
+    positions = torch.arange(len(tokens))
+    x = w["model.embed_tokens.weight"][torch.tensor(tokens)]
+    norm = lambda x, name: plain.rms_norm(x, w[name], EPS)
+
+    def feed_forward(x, i):
+        return x + plain.swiglu_mlp(norm(x, f"model.layers.{i}.post_attention_layernorm.weight"), w, f"model.layers.{i}.mlp")
+
+    def decay(x):
+        h = norm(x, "model.layers.1.input_layernorm.weight") @ w["model.layers.1.decay.in_proj.weight"].T
+        state, rows = torch.zeros(HIDDEN), []
+        for row in h:
+            state = 0.9 * state + row
+            rows.append(state)
+        return feed_forward(x + torch.stack(rows), 1)
+
+    a, kv0 = plain_attention(norm(x, "model.layers.0.input_layernorm.weight"), w, "model.layers.0.self_attn",
+                             positions, True, HEAD_DIM, 1.0, None)
+    x = feed_forward(x + a, 0)
+    x = decay(x)
+    a, _ = plain_attention(norm(x, "model.layers.2.input_layernorm.weight"), w, "model.layers.2.self_attn",
+                           positions, False, 8, 0.5, WINDOW)
+    x = feed_forward(x + a, 2)
+    x = decay(x)                                                   # the second run has state of its own
+    a, _ = plain_attention(norm(x, "model.layers.0.input_layernorm.weight"), w, "model.layers.0.self_attn",
+                           positions, True, HEAD_DIM, 1.0, None, shared_kv=kv0)
+    x = feed_forward(x + a, 0)
+    return norm(x, "model.norm.weight") @ w["lm_head.weight"].T
+
+
+# ------------------------------------------------------------------ the test
+
+@pytest.mark.parametrize("dtype,tolerance", [("float32", 3e-5), ("bfloat16", 4e-2)])
+def test_toy_model_with_parts_of_its_own(dtype, tolerance):
+    from mrun_b200.cache import FixedState, PagedKV
+    from mrun_b200.engine import Executor, StepEntry
+    from mrun_b200.weights import expected_tensors, random_tensors
+    register_toy_parts()
+    spec = toy_spec()
+    names = {t.name for t in expected_tensors(spec)}
+    assert "model.layers.1.decay.in_proj.weight" in names and "model.layers.2.self_attn.q_norm.weight" not in names
+    tensors = dict(random_tensors(spec, seed=3, std=0.08, norm_noise=0.1))
+    w = {k: v.float() for k, v in tensors.items()}
+    ex = Executor(spec, tensors, dtype=dtype, page_size=4, num_pages=80, max_requests=3)
+    assert not ex.model.graph_safe and not ex.use_graphs
+
+    needs = ex.model.cache_needs()
+    assert [type(n) for n in needs] == [PagedKV, FixedState, PagedKV, FixedState, type(None)]
+    assert set(ex.cache.groups) == {("paged", None), ("paged", WINDOW)}
+    assert ex.cache.entries[4].k is ex.cache.entries[0].k and not ex.cache.entries[4].writable
+    assert ex.cache.entries[1].state is not ex.cache.entries[3].state
+
+    gen = torch.Generator().manual_seed(9)
+    seqs = {name: torch.randint(0, VOCAB, (n,), generator=gen).tolist() for name, n in (("a", 61), ("b", 37), ("c", 50))}
+    want = {name: plain_toy(w, tokens) for name, tokens in seqs.items()}
+    scale = max(float(x.abs().max()) for x in want.values())
+
+    def check(name, start, logits):
+        got = logits.cpu()
+        error = float((got - want[name][start:start + got.shape[0]]).abs().max()) / scale
+        assert error <= tolerance, (name, start, error)
+
+    # whole
+    r = ex.admit("whole")
+    check("a", 0, ex.step([StepEntry(r, seqs["a"], range(61))]))
+    ex.release(r)
+    # portions of changing size, then token by token; the window gives pages back on the way
+    r = ex.admit("portions")
+    at = 0
+    for n in (2, 7, 3, 16, 5, 2, 9) + (1,) * 17:
+        check("a", at, ex.step([StepEntry(r, seqs["a"][at:at + n], range(n))]))
+        at += n
+    assert at == 61
+    held = len(r.pages_held(("paged", WINDOW)))
+    assert held <= -(-WINDOW // 4) + 1 and len(r.pages_held(("paged", None))) == 16
+    ex.release(r)
+    # mixed: three live requests, portions of some beside single tokens of others, slots reused
+    live = {name: ex.admit(name) for name in seqs}
+    fed = {name: 0 for name in seqs}
+    sizes = {"a": [30, 1, 1, 13, 1, 1, 14], "b": [1, 1, 20, 1, 14], "c": [5, 40, 1, 1, 1, 1, 1]}
+    for turn in range(7):
+        entries, names = [], []
+        for name in seqs:
+            if turn < len(sizes[name]):
+                n = sizes[name][turn]
+                entries.append(StepEntry(live[name], seqs[name][fed[name]:fed[name] + n], range(n)))
+                names.append((name, fed[name], n))
+                fed[name] += n
+        logits = ex.step(entries)
+        row = 0
+        for name, start, n in names:
+            check(name, start, logits[row:row + n])
+            row += n
+    assert fed == {name: len(tokens) for name, tokens in seqs.items()}
+    for request in live.values():
+        ex.release(request)
+    ex.cache.check_invariants()
+    assert ex.cache.free_pages(("paged", None)) == 80 and ex.cache.free_pages(("paged", WINDOW)) == 80
+    # a new request in a used slot starts from zero state
+    r = ex.admit("again")
+    check("b", 0, ex.step([StepEntry(r, seqs["b"], range(37))]))
+    ex.release(r)

@@ -1,0 +1,171 @@
+"""The scheduler's decisions, on the host with a scripted model in place of the GPU
+(as the reference tests its runtime on a scripted engine, crates/mrun/src/runtime/scripted.rs,
+crates/mrun/tests/admission.rs): refusals, admission with reservations, portions under the token
+budget, finishing, and what happens when pages run out."""
+from __future__ import annotations
+
+import pytest
+
+from mrun_b200.cache import CacheManager, OutOfPages, PagedKV
+from mrun_b200.engine.scheduler import Request, Scheduler, chunk_len, looping
+from mrun_b200.sampling import SamplingParams
+
+
+def cache(pages=64, page_size=4, requests=4):
+    return CacheManager([PagedKV(1, 8)], [None], page_size, pages, requests)
+
+
+def drive(scheduler, next_token=lambda r: len(r.output) + 100, max_steps=10000, on_plan=None):
+    """Runs plans against the cache manager the way the engine does; returns the plans."""
+    plans = []
+    for _ in range(max_steps):
+        if not scheduler.has_work():
+            break
+        plan = scheduler.schedule()
+        assert plan is not None
+        try:
+            append = scheduler.cache.plan_append([(e.request.cache, len(e.tokens)) for e in plan.entries])
+        except OutOfPages:
+            assert scheduler.preempt_newest() is not None
+            continue
+        scheduler.cache.commit(append)
+        scheduler.cache.check_invariants()
+        plans.append(plan)
+        if on_plan:
+            on_plan(plan)
+        scheduler.complete(plan, [next_token(r) for r in plan.sampled])
+    assert not scheduler.has_work()
+    return plans
+
+
+def test_chunk_len_follows_the_reference_table():
+    """crates/mrun-engine/src/engine.rs:481-486: clamp(2048 * 16384 / depth, 128, 2048)."""
+    assert chunk_len(0) == 2048 and chunk_len(16384) == 2048 and chunk_len(32768) == 1024
+    assert chunk_len(10 ** 7) == 128 and chunk_len(0, budget=64) == 64 and chunk_len(10 ** 7, budget=64) == 64
+
+
+def test_loop_guard():
+    assert not looping([1, 2, 3] * 100)
+    assert looping([1, 2, 3] * 171)                      # 513 tokens repeating with period 3
+    assert not looping(list(range(600)))
+    assert looping(list(range(256)) * 2)                 # the longest period still caught
+    assert not looping(list(range(257)) * 2)
+
+
+def test_refusals():
+    s = Scheduler(cache(pages=8, page_size=4), max_queue=1)
+    cases = [
+        (Request("empty", []), "invalid", "empty"),
+        (Request("zero", [1], max_tokens=0), "invalid", "at least 1"),
+        (Request("temp", [1], sampling=SamplingParams(temperature=-1.0)), "invalid", "temperature"),
+        (Request("topp", [1], sampling=SamplingParams(top_p=0.0)), "invalid", "top_p"),
+        (Request("long", list(range(32))), "too_long", "32 tokens"),
+    ]
+    for request, reason, text in cases:
+        assert s.submit(request) == reason
+        assert request.state == "finished" and request.finish_reason == reason and text in request.message
+    assert s.submit(Request("fits", list(range(31)), max_tokens=100)) is None
+    assert s.waiting[0].limit == 1                       # clamped to the room the prompt leaves
+    assert s.submit(Request("second", [1])) == "queue_full"
+
+
+def test_admission_reserves_prompt_plus_output():
+    s = Scheduler(cache(pages=10, page_size=4, requests=4), max_batch_tokens=64)
+    a = Request("a", list(range(10)), max_tokens=6)      # 16 tokens = 4 pages
+    b = Request("b", list(range(9)), max_tokens=8)       # 17 tokens = 5 pages
+    c = Request("c", list(range(3)), max_tokens=2)       # 5 tokens = 2 pages: does not fit beside a and b
+    for r in (a, b, c):
+        s.submit(r)
+    plan = s.schedule()
+    assert [e.request.request_id for e in plan.entries] == ["b", "a"]      # fewest prompt tokens left first
+    assert c.state == "waiting" and a.state == b.state == "running"
+    drive_rest = drive(s)
+    assert c.finish_reason == "length" and len(c.output) == 2
+    assert all(r.finish_reason == "length" for r in (a, b)) and s.preemptions == 0
+    assert s.cache.free_pages() == 10 and s.cache.free_slots == 4
+
+
+def test_portions_under_the_token_budget_beside_decodes():
+    s = Scheduler(cache(pages=256, page_size=4, requests=4), max_batch_tokens=16)
+    short = Request("short", list(range(5)), max_tokens=30)
+    long = Request("long", list(range(50)), max_tokens=3)
+    s.submit(short)
+    s.submit(long)
+    plans = drive(s)
+    sizes = [[(e.request.request_id, len(e.tokens), e.wants_logits) for e in p.entries] for p in plans]
+    assert sizes[0] == [("short", 5, True), ("long", 11, False)]           # shortest first, budget 16
+    assert sizes[1] == [("short", 1, True), ("long", 15, False)]           # a decode beside a portion
+    assert sizes[2] == [("short", 1, True), ("long", 15, False)]
+    assert sizes[3] == [("short", 1, True), ("long", 9, True)]             # the last portion wants logits
+    assert sizes[4] == [("short", 1, True), ("long", 1, True)]
+    assert all(sum(n for _, n, _ in step) <= 16 for step in sizes)
+    fed = {}
+    for p in plans:
+        for e in p.entries:
+            fed.setdefault(e.request.request_id, []).extend(e.tokens)
+    assert fed["long"] == long.prompt + long.output[:-1]                     # every token fed once, in order
+    assert fed["short"] == short.prompt + short.output[:-1]
+
+
+def test_finishing_reasons_and_eos():
+    s = Scheduler(cache(), eos_token_ids=[7], max_batch_tokens=8)
+    stop = Request("stop", [1, 2, 3], max_tokens=50)
+    ignore = Request("ignore", [1, 2, 3], max_tokens=5, ignore_eos=True)
+    s.submit(stop)
+    s.submit(ignore)
+    drive(s, next_token=lambda r: 7 if len(r.output) == 2 else 9)
+    assert stop.finish_reason == "stop" and stop.output == [9, 9, 7]
+    assert ignore.finish_reason == "length" and ignore.output == [9, 9, 7, 9, 9]
+    s = Scheduler(cache(pages=512), max_batch_tokens=8)
+    loop = Request("loop", [1], max_tokens=2000)
+    s.submit(loop)
+    drive(s, next_token=lambda r: len(r.output) % 5)
+    assert loop.finish_reason == "repetition" and len(loop.output) == 512
+
+
+def test_out_of_pages_preempts_the_newest_and_recomputes():
+    """Without reservations the pool runs out in mid-run: the request admitted last gives
+    everything back, waits at the head of the queue, and later feeds prompt + output again."""
+    s = Scheduler(cache(pages=12, page_size=4, requests=3), max_batch_tokens=32, reserve=False)
+    a = Request("a", list(range(12)), max_tokens=20)
+    b = Request("b", list(range(12)), max_tokens=20)
+    s.submit(a)
+    s.submit(b)
+    refed = []
+    def watch(plan):
+        for e in plan.entries:
+            if e.request is b and b.preemptions and e.request.fed == 0:
+                refed.append(list(e.tokens))
+    drive(s, on_plan=watch)
+    assert a.preemptions == 0 and b.preemptions >= 1 and s.preemptions == b.preemptions
+    assert a.finish_reason == b.finish_reason == "length" and len(a.output) == len(b.output) == 20
+    assert refed and refed[0][:12] == b.prompt and refed[0][12:] == b.output[:len(refed[0]) - 12]
+    assert s.cache.free_pages() == 12 and s.cache.free_slots == 3
+
+
+def test_a_lone_request_is_never_preempted():
+    s = Scheduler(cache(pages=4, page_size=4, requests=2), reserve=False)
+    only = Request("only", list(range(10)), max_tokens=100)
+    s.submit(only)
+    drive(s)
+    assert only.finish_reason == "length" and len(only.output) == 6 and only.preemptions == 0
+    assert s.preempt_newest() is None
+
+
+def test_abort_frees_everything():
+    s = Scheduler(cache())
+    r = Request("r", list(range(9)), max_tokens=5)
+    s.submit(r)
+    plan = s.schedule()
+    s.cache.commit(s.cache.plan_append([(r.cache, 9)]))
+    s.abort(r, "cancelled")
+    assert r.finish_reason == "aborted" and s.cache.free_pages() == 64 and not s.has_work()
+
+
+def test_seeds():
+    s = Scheduler(cache())
+    seeded = Request("s", [1], sampling=SamplingParams(temperature=1.0, seed=42))
+    free1, free2 = Request("f1", [1], sampling=SamplingParams(temperature=1.0)), Request("f2", [1])
+    for r in (seeded, free1, free2):
+        s.submit(r)
+    assert seeded.seed == 42 and free1.seed != free2.seed
