@@ -574,3 +574,77 @@ MRUN_API int mrun_attn_decode_occupancy() {
         return -1;
     return blocks;
 }
+
+// ------------------------------------------------------------------------------------------
+// The same decode kernel for callers that cannot allocate: its scratch is a fixed array in this
+// library (see attention_static.h for who needs that, the limits and the rules).
+// ------------------------------------------------------------------------------------------
+#include "attention_static.h"
+
+#include <mutex>
+
+namespace {
+
+constexpr size_t STATIC_PART_O = (size_t)MRUN_STATIC_MAX_PARTIALS * D;       // floats
+constexpr size_t STATIC_PART_ML = (size_t)MRUN_STATIC_MAX_PARTIALS * 2;      // floats
+constexpr size_t STATIC_COUNTERS = MRUN_STATIC_MAX_PAIRS;                    // ints, stored as 4-byte words
+
+// In host code this name is only a handle for cudaGetSymbolAddress, never a device pointer.
+static __device__ __align__(256) float g_static_scratch[STATIC_PART_O + STATIC_PART_ML + STATIC_COUNTERS];
+
+constexpr int STATIC_MAX_DEVICES = 64;
+float* g_static_address[STATIC_MAX_DEVICES] = {};
+std::mutex g_static_mutex;
+
+// The array's address on the current device, looked up at the first call on that device.
+int static_scratch_address(float** address) {
+    int device = -1;
+    MRUN_CHECK_CUDA(cudaGetDevice(&device), "attn_decode_static");
+    MRUN_REQUIRE(device >= 0 && device < STATIC_MAX_DEVICES, "attn_decode_static: device %d is outside 0..%d", device,
+                 STATIC_MAX_DEVICES - 1);
+    std::lock_guard<std::mutex> lock(g_static_mutex);
+    if (g_static_address[device] == nullptr) {
+        float* found = nullptr;
+        MRUN_CHECK_CUDA(cudaGetSymbolAddress((void**)&found, g_static_scratch), "attn_decode_static: scratch address");
+        MRUN_REQUIRE(found != nullptr, "attn_decode_static: the scratch array has no address on device %d", device);
+        MRUN_CHECK_CUDA(cudaFuncSetAttribute(decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                             (int)DECODE_SMEM), "attn_decode_static");
+        g_static_address[device] = found;
+    }
+    *address = g_static_address[device];
+    return 0;
+}
+
+}  // namespace
+
+MRUN_API int mrun_attn_decode_static(const void* q, long q_stride, void* out, const void* k_cache,
+                                     const void* v_cache, const int* block_tables, int max_blocks,
+                                     const int* token_slot, const int* positions, int tokens, int splits,
+                                     int min_tiles, int heads, int kv_heads, int head_dim, int page_size, float scale,
+                                     int window, cudaStream_t stream) {
+    if (int rc = check_common("attn_decode_static", heads, kv_heads, head_dim, page_size, max_blocks, window, 16))
+        return rc;
+    MRUN_REQUIRE(tokens >= 0 && splits >= 1 && splits <= 65535 && min_tiles >= 1,
+                 "attn_decode_static: tokens=%d splits=%d min_tiles=%d", tokens, splits, min_tiles);
+    MRUN_REQUIRE((long)tokens * heads * splits <= MRUN_STATIC_MAX_PARTIALS,
+                 "attn_decode_static: tokens * heads * splits = %ld exceeds the built-in scratch of %d partial results",
+                 (long)tokens * heads * splits, MRUN_STATIC_MAX_PARTIALS);
+    MRUN_REQUIRE((long)tokens * kv_heads <= MRUN_STATIC_MAX_PAIRS,
+                 "attn_decode_static: tokens * kv_heads = %ld exceeds the built-in scratch of %d counters",
+                 (long)tokens * kv_heads, MRUN_STATIC_MAX_PAIRS);
+    if (tokens == 0) return 0;
+    float* scratch = nullptr;
+    if (int rc = static_scratch_address(&scratch)) return rc;
+    float* part_o = scratch;
+    float* part_ml = scratch + STATIC_PART_O;
+    int* counters = reinterpret_cast<int*>(scratch + STATIC_PART_O + STATIC_PART_ML);
+    // the counters must start at zero whatever an earlier, possibly interrupted, call left
+    MRUN_CHECK_CUDA(cudaMemsetAsync(counters, 0, (size_t)tokens * kv_heads * sizeof(int), stream),
+                    "attn_decode_static: clearing the counters");
+    decode_kernel<<<dim3(tokens, kv_heads, splits), THREADS, DECODE_SMEM, stream>>>(
+        (const bf16*)q, q_stride, (bf16*)out, (const bf16*)k_cache, (const bf16*)v_cache, block_tables, max_blocks,
+        token_slot, positions, part_o, part_ml, counters, min_tiles, heads, kv_heads, page_size, shift_of(page_size),
+        scale * LOG2E, window);
+    MRUN_CHECK_LAUNCH("attn_decode_static");
+    return 0;
+}
