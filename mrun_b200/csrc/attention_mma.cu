@@ -347,9 +347,13 @@ decode_kernel(const bf16* __restrict__ q, long q_stride, bf16* __restrict__ out,
     const int tok = blockIdx.x, kvh = blockIdx.y, split = blockIdx.z, splits = gridDim.z;
     const int group = heads / kv_heads;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    // Positions, slots and block tables are written at the start of a step, not by the kernel
+    // before this one, so they are read before waiting for it.
+    mrun::pdl_launch_dependents();
     const int pos = positions[tok];
 
     if (pos < 0) {  // padding row: zeros, written by the first split
+        mrun::pdl_wait();
         if (split == 0)
             for (int i = threadIdx.x; i < group * D; i += THREADS)
                 out[((size_t)tok * heads + kvh * group) * D + i] = __float2bfloat16_rn(0.f);
@@ -361,7 +365,10 @@ decode_kernel(const bf16* __restrict__ q, long q_stride, bf16* __restrict__ out,
     const int n_blocks = b1 - b0 + 1;
     const int per = max((n_blocks + splits - 1) / splits, min_tiles);
     const int n_active = (n_blocks + per - 1) / per;
-    if (split >= n_active) return;
+    if (split >= n_active) {
+        mrun::pdl_wait();
+        return;
+    }
     const int first_block = b0 + split * per;
     const int last_block = min(b1, first_block + per - 1);
 
@@ -370,12 +377,11 @@ decode_kernel(const bf16* __restrict__ q, long q_stride, bf16* __restrict__ out,
 #pragma unroll
     for (int dt = 0; dt < D / 8; ++dt) o[dt][0] = o[dt][1] = o[dt][2] = o[dt][3] = 0.f;
 
-    for (int c = threadIdx.x; c < 16 * CHUNKS; c += THREADS) {
-        const int row = c / CHUNKS, chunk = c - row * CHUNKS;
-        const bool valid = row < group;
-        const bf16* src = valid ? q + (size_t)tok * q_stride + (size_t)(kvh * group + row) * D + chunk * 8 : q;
-        cp_async_16(q_tile + row * LD + chunk * 8, src, valid);
-    }
+    // The keys and values of earlier positions were written by earlier steps; only the tile that
+    // holds this step's own token (the last tile of the last run) and q come from the kernels
+    // just before.  Runs that do not hold that tile start their first loads before the wait.
+    const bool holds_new_token = last_block == b1 && first_block + (STAGES - 2) >= b1;
+    if (holds_new_token) mrun::pdl_wait();
     // prologue: STAGES - 1 tiles in flight (an empty group keeps the counting uniform)
 #pragma unroll
     for (int s = 0; s < STAGES - 1; ++s) {
@@ -383,6 +389,16 @@ decode_kernel(const bf16* __restrict__ q, long q_stride, bf16* __restrict__ out,
             load_kv_tiles(k_tiles + s * BLOCK_N * LD, v_tiles + s * BLOCK_N * LD, k_cache, v_cache, pg,
                           (first_block + s) * BLOCK_N, lo, pos);
         cp_async_commit();
+    }
+    if (!holds_new_token) mrun::pdl_wait();
+    // q with plain loads, so that the copy groups above stay one per tile; the first barrier of
+    // the loop publishes it
+    for (int c = threadIdx.x; c < 16 * CHUNKS; c += THREADS) {
+        const int row = c / CHUNKS, chunk = c - row * CHUNKS;
+        uint4 value = make_uint4(0, 0, 0, 0);
+        if (row < group)
+            value = *reinterpret_cast<const uint4*>(q + (size_t)tok * q_stride + (size_t)(kvh * group + row) * D + chunk * 8);
+        *reinterpret_cast<uint4*>(q_tile + row * LD + chunk * 8) = value;
     }
 
     int row_pos[2], row_lo[2];
@@ -558,11 +574,11 @@ MRUN_API int mrun_attn_decode(const void* q, long q_stride, void* out, const voi
                                              (int)DECODE_SMEM), "attn_decode");
         configured = true;
     }
-    decode_kernel<<<dim3(tokens, kv_heads, splits), THREADS, DECODE_SMEM, stream>>>(
-        (const bf16*)q, q_stride, (bf16*)out, (const bf16*)k_cache, (const bf16*)v_cache, block_tables, max_blocks,
-        token_slot, positions, part_o, part_ml, counters, min_tiles, heads, kv_heads, page_size, shift_of(page_size),
-        scale * LOG2E, window);
-    MRUN_CHECK_LAUNCH("attn_decode");
+    MRUN_CHECK_CUDA(mrun::launch_pdl(MRUN_PDL_ATTENTION, decode_kernel, dim3(tokens, kv_heads, splits), dim3(THREADS), DECODE_SMEM, stream,
+                                     (const bf16*)q, q_stride, (bf16*)out, (const bf16*)k_cache, (const bf16*)v_cache,
+                                     block_tables, max_blocks, token_slot, positions, part_o, part_ml, counters,
+                                     min_tiles, heads, kv_heads, page_size, shift_of(page_size), scale * LOG2E, window),
+                    "attn_decode");
     return 0;
 }
 

@@ -36,7 +36,38 @@ int mrun_set_error(const char* fmt, ...);
             return mrun_set_error("%s: %s", name, cudaGetErrorString(err__));           \
     } while (0)
 
+// Which kernel classes are launched so that their blocks may start while the kernel before them
+// in the stream is still running: a bit mask from the environment variable MRUN_PDL
+// (1 = norm/rotary/activation kernels, 2 = the decode GEMM, 4 = the decode attention).
+enum : int { MRUN_PDL_ELEMENTWISE = 1, MRUN_PDL_GEMM = 2, MRUN_PDL_ATTENTION = 4 };
+bool mrun_pdl_enabled(int kernel_class);
+
 namespace mrun {
+
+// Programmatic dependent launch.  A kernel launched with launch_pdl() may begin before the
+// previous kernel in its stream has finished; it must call pdl_wait() before it reads anything
+// that kernel wrote and before it writes anything at all.  What it does before the wait (index
+// arithmetic, loads of weights and of other data that no kernel of the step writes) overlaps the
+// previous kernel's tail.  pdl_launch_dependents() lets the *next* kernel's blocks be scheduled
+// once every block of this one has reached it.  Both are no-ops in a kernel launched normally.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;"); }
+
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_pdl(int kernel_class, void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem,
+                              cudaStream_t stream, Args... args) {
+    cudaLaunchConfig_t config = {};
+    config.gridDim = grid;
+    config.blockDim = block;
+    config.dynamicSmemBytes = smem;
+    config.stream = stream;
+    cudaLaunchAttribute attribute[1];
+    attribute[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attribute[0].val.programmaticStreamSerializationAllowed = 1;
+    config.attrs = attribute;
+    config.numAttrs = mrun_pdl_enabled(kernel_class) ? 1 : 0;
+    return cudaLaunchKernelEx(&config, kernel, KArgs(args)...);
+}
 
 __device__ __forceinline__ float to_float(float v) { return v; }
 __device__ __forceinline__ float to_float(__nv_bfloat16 v) { return __bfloat162float(v); }

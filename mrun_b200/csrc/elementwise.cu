@@ -114,6 +114,8 @@ add_rmsnorm_vec_kernel(float* __restrict__ resid, const TA* __restrict__ delta,
                        const float* __restrict__ weight, float eps, TA* __restrict__ out,
                        const int* __restrict__ rows, int hidden) {
     __shared__ float scratch[33];
+    pdl_launch_dependents();
+    pdl_wait();
     const int r = blockIdx.x;
     const size_t src = (size_t)(rows ? rows[r] : r) * hidden;
     const int chunks = hidden >> 3;
@@ -155,8 +157,8 @@ static int launch_add_rmsnorm(float* resid, const void* delta, const float* weig
                               const int* rows, int n_rows, int hidden, cudaStream_t stream) {
     const bool aligned = (((uintptr_t)resid | (uintptr_t)delta | (uintptr_t)weight | (uintptr_t)out) & 15) == 0;
     if (hidden % 8 == 0 && hidden <= 8192 && aligned) {
-        add_rmsnorm_vec_kernel<TA><<<n_rows, 256, 0, stream>>>(resid, (const TA*)delta, weight, eps, (TA*)out,
-                                                              rows, hidden);
+        MRUN_CHECK_CUDA(launch_pdl(MRUN_PDL_ELEMENTWISE, add_rmsnorm_vec_kernel<TA>, dim3(n_rows), dim3(256), 0, stream, resid,
+                                   (const TA*)delta, weight, eps, (TA*)out, rows, hidden), "add_rmsnorm");
         return 0;
     }
     const size_t smem = (size_t)hidden * sizeof(float);
@@ -237,6 +239,8 @@ __global__ void qk_norm_rope_cache_kernel(TA* __restrict__ qkv, const float* __r
                                           TA* __restrict__ v_cache, int tokens, int heads, int kv_heads,
                                           int head_dim, int page_size) {
     extern __shared__ float vec_buf[];
+    pdl_launch_dependents();
+    pdl_wait();
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int per_token = heads + 2 * kv_heads;
     const long item = (long)blockIdx.x * (blockDim.x >> 5) + warp;
@@ -313,13 +317,16 @@ MRUN_API int mrun_qk_norm_rope_cache(void* qkv, int act_dtype, const float* q_we
     const unsigned blocks = (unsigned)((items + warps - 1) / warps);
     const size_t smem = (size_t)warps * head_dim * sizeof(float);
     if (act_dtype == MRUN_F32)
-        qk_norm_rope_cache_kernel<float><<<blocks, warps * 32, smem, stream>>>(
-            (float*)qkv, q_weight, k_weight, eps, (const float2*)rot, rotary_dim, slots, (float*)k_cache,
-            (float*)v_cache, tokens, heads, kv_heads, head_dim, page_size);
+        MRUN_CHECK_CUDA(launch_pdl(MRUN_PDL_ELEMENTWISE, qk_norm_rope_cache_kernel<float>, dim3(blocks), dim3(warps * 32), smem, stream,
+                                   (float*)qkv, q_weight, k_weight, eps, (const float2*)rot, rotary_dim, slots,
+                                   (float*)k_cache, (float*)v_cache, tokens, heads, kv_heads, head_dim, page_size),
+                        "qk_norm_rope_cache");
     else if (act_dtype == MRUN_BF16)
-        qk_norm_rope_cache_kernel<__nv_bfloat16><<<blocks, warps * 32, smem, stream>>>(
-            (__nv_bfloat16*)qkv, q_weight, k_weight, eps, (const float2*)rot, rotary_dim, slots,
-            (__nv_bfloat16*)k_cache, (__nv_bfloat16*)v_cache, tokens, heads, kv_heads, head_dim, page_size);
+        MRUN_CHECK_CUDA(launch_pdl(MRUN_PDL_ELEMENTWISE, qk_norm_rope_cache_kernel<__nv_bfloat16>, dim3(blocks), dim3(warps * 32), smem,
+                                   stream, (__nv_bfloat16*)qkv, q_weight, k_weight, eps, (const float2*)rot,
+                                   rotary_dim, slots, (__nv_bfloat16*)k_cache, (__nv_bfloat16*)v_cache, tokens, heads,
+                                   kv_heads, head_dim, page_size),
+                        "qk_norm_rope_cache");
     else
         return mrun_set_error("qk_norm_rope_cache: unknown dtype code %d", act_dtype);
     MRUN_CHECK_LAUNCH("qk_norm_rope_cache");

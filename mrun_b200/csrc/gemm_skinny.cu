@@ -21,9 +21,22 @@
 namespace {
 
 using bf16 = __nv_bfloat16;
-constexpr int WARPS = 8;
+using mrun::pdl_launch_dependents;
+using mrun::pdl_wait;
+#ifndef MRUN_SKINNY_WARPS
+#define MRUN_SKINNY_WARPS 8
+#endif
+#ifndef MRUN_SKINNY_UNROLL
+#define MRUN_SKINNY_UNROLL 4        // chunks per batch with one row tile and one token tile per block
+#endif
+#ifndef MRUN_SKINNY_UNROLL_WIDE
+#define MRUN_SKINNY_UNROLL_WIDE 2   // ... with two row tiles or two token tiles (more registers per chunk)
+#endif
+#ifndef MRUN_SKINNY_WIDE_N
+#define MRUN_SKINNY_WIDE_N (32 * 148 * 4)
+#endif
+constexpr int WARPS = MRUN_SKINNY_WARPS;
 constexpr int THREADS = WARPS * 32;
-constexpr int UNROLL = 4;              // chunks a warp keeps in flight per batch
 
 __device__ __forceinline__ uint4 load_stream(const bf16* p) {
     uint4 v;
@@ -47,6 +60,7 @@ template <int NT, int MT, typename TOut, bool SWIGLU>
 __global__ void __launch_bounds__(THREADS)
 skinny_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w, TOut* __restrict__ y, int M, int N, int K,
               long ldx, long ldy) {
+    constexpr int UNROLL = (MT == 1 && NT == 1) ? MRUN_SKINNY_UNROLL : MRUN_SKINNY_UNROLL_WIDE;   // chunks per batch
     __shared__ float red[WARPS][MT * 16][NT * 8 + 1];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int g = lane >> 2, t = lane & 3;
@@ -77,7 +91,7 @@ skinny_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w, TOut* __re
 
     // two register sets: while one batch of chunks is multiplied the next is in flight
     uint4 wa[2][UNROLL][MT][2], xa[2][UNROLL][NT];
-    auto load_batch = [&](uint4 (&wb)[UNROLL][MT][2], uint4 (&xb)[UNROLL][NT], int c0) {
+    auto load_w = [&](uint4 (&wb)[UNROLL][MT][2], int c0) {
 #pragma unroll
         for (int u = 0; u < UNROLL; ++u) {
             const int c = c0 + u * WARPS;
@@ -88,6 +102,15 @@ skinny_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w, TOut* __re
                     wb[u][mt][0] = load_stream(w_rows[mt][0] + k);
                     wb[u][mt][1] = load_stream(w_rows[mt][1] + k);
                 }
+            }
+        }
+    };
+    auto load_x = [&](uint4 (&xb)[UNROLL][NT], int c0) {
+#pragma unroll
+        for (int u = 0; u < UNROLL; ++u) {
+            const int c = c0 + u * WARPS;
+            if (c < chunks) {
+                const int k = c << 5;
 #pragma unroll
                 for (int nt = 0; nt < NT; ++nt)
                     xb[u][nt] = x_valid[nt] ? __ldg(reinterpret_cast<const uint4*>(x_rows[nt] + k)) : make_uint4(0, 0, 0, 0);
@@ -110,17 +133,27 @@ skinny_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w, TOut* __re
             }
         }
     };
+    // The weights do not depend on the kernel before this one: their first two batches are
+    // requested before waiting for it, the rows of x after.
     constexpr int STRIDE = UNROLL * WARPS;
     int c0 = warp;
-    load_batch(wa[0], xa[0], c0);
+    pdl_launch_dependents();
+    load_w(wa[0], c0);
+    load_w(wa[1], c0 + STRIDE);
+    pdl_wait();
+    load_x(xa[0], c0);
+    load_x(xa[1], c0 + STRIDE);
     while (c0 < chunks) {
-        load_batch(wa[1], xa[1], c0 + STRIDE);
         compute_batch(wa[0], xa[0], c0);
         c0 += STRIDE;
         if (c0 >= chunks) break;
-        load_batch(wa[0], xa[0], c0 + STRIDE);
+        load_w(wa[0], c0 + STRIDE);
+        load_x(xa[0], c0 + STRIDE);
         compute_batch(wa[1], xa[1], c0);
         c0 += STRIDE;
+        if (c0 >= chunks) break;
+        load_w(wa[1], c0 + STRIDE);
+        load_x(xa[1], c0 + STRIDE);
     }
 
     // partial sums of the eight warps, added in warp order
@@ -169,13 +202,14 @@ skinny_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w, TOut* __re
 template <int NT, int MT, typename TOut, bool SWIGLU>
 void launch(const bf16* x, const bf16* w, TOut* y, int M, int N, int K, long ldx, long ldy, cudaStream_t stream) {
     const int blocks = (N + MT * 16 - 1) / (MT * 16);
-    skinny_kernel<NT, MT, TOut, SWIGLU><<<blocks, THREADS, 0, stream>>>(x, w, y, M, N, K, ldx, ldy);
+    mrun::launch_pdl(MRUN_PDL_GEMM, skinny_kernel<NT, MT, TOut, SWIGLU>, dim3(blocks), dim3(THREADS), 0, stream, x, w, y, M, N, K,
+                     ldx, ldy);
 }
 
 template <typename TOut, bool SWIGLU>
 void dispatch(const bf16* x, const bf16* w, TOut* y, int M, int N, int K, long ldx, long ldy, cudaStream_t stream) {
     // two row tiles per block halve the reads of x once there are plenty of blocks
-    const bool wide = N >= 32 * 148 * 4;
+    const bool wide = N >= MRUN_SKINNY_WIDE_N;
     if (M <= 8) {
         if (wide) launch<1, 2, TOut, SWIGLU>(x, w, y, M, N, K, ldx, ldy, stream);
         else launch<1, 1, TOut, SWIGLU>(x, w, y, M, N, K, ldx, ldy, stream);

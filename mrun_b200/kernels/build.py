@@ -145,7 +145,12 @@ CORE_SOURCES = ("common.cu", "elementwise.cu", "gemm_f32.cu", "gemm_skinny.cu", 
 
 
 def build_core() -> str:
-    return build_library("mrun_core", CORE_SOURCES)
+    defines = {}
+    for knob in ("MRUN_SKINNY_WARPS", "MRUN_SKINNY_UNROLL", "MRUN_SKINNY_UNROLL_WIDE", "MRUN_SKINNY_WIDE_N"):   # tuning knobs
+        if os.environ.get(knob):
+            defines[knob] = int(os.environ[knob])
+    tag = "_".join(f"{k[12:].lower()}{v}" for k, v in sorted(defines.items()))
+    return build_library(f"mrun_core_{tag}" if tag else "mrun_core", CORE_SOURCES, defines)
 
 
 def build_attention(head_dim: int) -> str:
