@@ -1,0 +1,416 @@
+// Linear layer on the fifth-generation tensor cores (tcgen05) for medium batches of rows
+// (decode with 17 .. 256 requests): y[M, N] = x[M, K] · W[N, K]^T, bf16 operands, 32-bit
+// accumulation in tensor memory, bf16 or 32-bit output, optional fused SiLU(gate) * up.
+//
+// The product is bound by reading W once from HBM, so the operands are swapped: the 128 lanes of
+// the MMA take 128 rows of W and the tokens are its N dimension (16 .. 256).  One block computes
+// one [128 weight rows x TOK tokens] tile over a range of k:
+//
+//   warp 0, one lane   TMA producer: per 64-wide k block one box of W [128 x 64] and one of x
+//                      [TOK x 64] into a ring of shared-memory stages (128-byte swizzle), each
+//                      stage guarded by a full/empty mbarrier pair;
+//   warp 1, one lane   MMA issuer: four tcgen05.mma (K = 16) per stage into the TMEM accumulator
+//                      [128 lanes x TOK columns], tcgen05.commit frees the stage and, after the
+//                      last k block, signals the epilogue;
+//   all four warps     epilogue: tcgen05.ld of the warp's 32 lanes, 16 columns at a time, then
+//                      either the output or a 32-bit partial tile.
+//
+// With several k ranges per tile (split K, so that 148 SMs have work when N / 128 is small) every
+// block writes its partial tile to scratch and the block that arrives last at the tile's counter
+// adds them in range order: the result does not depend on which block came last.
+//
+// Every wait on an mbarrier is bounded by a cycle budget.  When a wait runs out the block records
+// a code in the status word, stops issuing, lets its copies in flight land, frees its tensor
+// memory and returns; the host reads the status word after the step and raises.
+//
+// Reference call sites: crates/mrun-engine/src/load.rs:294-306 (x · Wᵀ),
+// crates/mrun-engine/src/models/common.rs:336-339 (the gated feed-forward).
+#include <cuda.h>
+
+#include "common.cuh"
+
+namespace {
+
+using bf16 = __nv_bfloat16;
+
+constexpr int BLOCK_ROWS = 128;      // weight rows per tile = MMA M
+constexpr int BLOCK_K = 64;          // bf16 per smem row = 128 bytes = one swizzle span
+constexpr int UMMA_K = 16;
+constexpr int THREADS = 128;
+constexpr long long WAIT_CYCLES = 3000000000LL;   // about 1.5 s at 2 GHz
+
+enum : int { STATUS_OK = 0, STATUS_PRODUCER_TIMEOUT = 1, STATUS_MMA_TIMEOUT = 2, STATUS_EPILOGUE_TIMEOUT = 3 };
+
+// ------------------------------------------------------------------------------------------ PTX
+__device__ __forceinline__ unsigned smem_u32(const void* p) { return (unsigned)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(unsigned long long* bar, int count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(unsigned long long* bar, unsigned bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(unsigned long long* bar, unsigned parity) {
+    unsigned done;
+    asm volatile(
+        "{\n.reg .pred p;\n"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+        "selp.u32 %0, 1, 0, p;\n}"
+        : "=r"(done) : "r"(smem_u32(bar)), "r"(parity) : "memory");
+    return done != 0;
+}
+// Bounded wait: false when the cycle budget ran out.
+__device__ __forceinline__ bool mbar_wait(unsigned long long* bar, unsigned parity) {
+    if (mbar_try_wait(bar, parity)) return true;
+    const long long start = clock64();
+    while (!mbar_try_wait(bar, parity))
+        if (clock64() - start > WAIT_CYCLES) return false;
+    return true;
+}
+__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, int c0, int c1, unsigned long long* bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+        ::"r"(smem_u32(dst)), "l"(map), "r"(smem_u32(bar)), "r"(c0), "r"(c1) : "memory");
+}
+__device__ __forceinline__ void tmem_alloc(unsigned* slot, unsigned columns) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(slot)), "r"(columns) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(unsigned address, unsigned columns) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(address), "r"(columns) : "memory");
+}
+__device__ __forceinline__ void umma_bf16(unsigned d_tmem, unsigned long long a_desc, unsigned long long b_desc,
+                                          unsigned idesc, unsigned accumulate) {
+    asm volatile(
+        "{\n.reg .pred p;\n"
+        "setp.ne.b32 p, %4, 0;\n"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}"
+        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void umma_commit(unsigned long long* bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tmem_load16(unsigned address, float (&v)[16]) {
+    unsigned r[16];
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];\n"
+        "tcgen05.wait::ld.sync.aligned;"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+        : "r"(address) : "memory");
+#pragma unroll
+    for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]);
+}
+
+// Shared-memory operand descriptor: K-major rows of 128 bytes, 128-byte swizzle, groups of eight
+// rows 1024 bytes apart (the layout a TMA box [rows x 64 bf16] with SWIZZLE_128B produces).
+__device__ __forceinline__ unsigned long long smem_descriptor(const void* tile) {
+    unsigned long long d = 0;
+    d |= (unsigned long long)((smem_u32(tile) & 0x3FFFF) >> 4);       // start address, 16-byte units
+    d |= (unsigned long long)(1024 >> 4) << 32;                        // stride between 8-row groups
+    d |= 1ull << 46;                                                   // descriptor version of sm_100
+    d |= 2ull << 61;                                                   // 128-byte swizzle
+    return d;
+}
+// Instruction descriptor: D f32, A and B bf16, both K-major, M = 128, N = tokens.
+__host__ __device__ constexpr unsigned instruction_descriptor(int n) {
+    return (1u << 4) | (1u << 7) | (1u << 10) | ((unsigned)(n >> 3) << 17) | ((unsigned)(BLOCK_ROWS >> 4) << 24);
+}
+
+template <typename T> __device__ __forceinline__ void store_out(T* p, float v);
+template <> __device__ __forceinline__ void store_out<bf16>(bf16* p, float v) { *p = __float2bfloat16_rn(v); }
+template <> __device__ __forceinline__ void store_out<float>(float* p, float v) { *p = v; }
+
+template <int TOK> constexpr int stages_for() {
+    // stage = 16 KB of W + TOK * 128 bytes of x; keep the ring under ~200 KB
+    return (200 * 1024) / (BLOCK_ROWS * BLOCK_K * 2 + TOK * BLOCK_K * 2) > 12
+               ? 12 : (200 * 1024) / (BLOCK_ROWS * BLOCK_K * 2 + TOK * BLOCK_K * 2);
+}
+
+// Writes one warp's 32 weight rows x 16 tokens of results.  `row` is the thread's weight row.
+template <typename TOut, bool SWIGLU>
+__device__ __forceinline__ void write_columns(TOut* __restrict__ y, long ldy, const float (&v)[16], int row, int tok0,
+                                              int M, int N) {
+    const int lane = threadIdx.x & 31;
+    if constexpr (!SWIGLU) {
+#pragma unroll
+        for (int j = 0; j < 16; ++j)
+            if (tok0 + j < M && row < N) store_out<TOut>(y + (size_t)(tok0 + j) * ldy + row, v[j]);
+    } else {
+        // rows 16q .. 16q+7 are gates, 16q+8 .. 16q+15 the ups of the same outputs
+        const bool is_gate = (lane & 8) == 0;
+        const int out_col = (row >> 4) * 8 + (row & 7);
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+            const float up_raw = __shfl_down_sync(0xffffffffu, v[j], 8);
+            if (is_gate && tok0 + j < M && row < N) {
+                const float gate = __bfloat162float(__float2bfloat16_rn(v[j]));
+                const float up = __bfloat162float(__float2bfloat16_rn(up_raw));
+                store_out<TOut>(y + (size_t)(tok0 + j) * ldy + out_col, gate / (1.f + expf(-gate)) * up);
+            }
+        }
+    }
+}
+
+// grid (row tiles, k splits).  partial: [tiles][splits][TOK][128] floats; counters: [tiles] ints, zero
+// before and after the call; status: one int.
+template <int TOK, typename TOut, bool SWIGLU>
+__global__ void __launch_bounds__(THREADS)
+gemm_tc5_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
+                TOut* __restrict__ y, long ldy, int M, int N, int k_blocks, float* __restrict__ partial,
+                int* __restrict__ counters, int* __restrict__ status) {
+    constexpr int STAGES = stages_for<TOK>();
+    constexpr int W_BYTES = BLOCK_ROWS * BLOCK_K * 2, X_BYTES = TOK * BLOCK_K * 2;
+    constexpr unsigned TMEM_COLS = TOK < 32 ? 32 : TOK;
+    extern __shared__ __align__(1024) unsigned char smem_raw[];
+    // stage s: W at s * (W_BYTES + X_BYTES), x right after it; both 1024-byte aligned
+    unsigned char* tiles = reinterpret_cast<unsigned char*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    __shared__ unsigned long long full_bar[STAGES], empty_bar[STAGES], done_bar;
+    __shared__ unsigned tmem_base_slot;
+    __shared__ int aborted, ticket_shared;
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int tile = blockIdx.x, split = blockIdx.y, splits = gridDim.y;
+    const int per = (k_blocks + splits - 1) / splits;
+    const int kb0 = split * per, kb1 = min(k_blocks, kb0 + per);     // this block's k blocks
+    const int n_kb = max(0, kb1 - kb0);
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; ++s) {
+            mbar_init(&full_bar[s], 1);
+            mbar_init(&empty_bar[s], 1);
+        }
+        mbar_init(&done_bar, 1);
+        aborted = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncwarp();
+    if (warp == 0) tmem_alloc(&tmem_base_slot, TMEM_COLS);
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const unsigned tmem_base = tmem_base_slot;
+
+    if (warp == 0 && lane == 0) {
+        // ---------------------------------------------------------------- TMA producer
+        for (int i = 0; i < n_kb; ++i) {
+            const int s = i % STAGES;
+            if (i >= STAGES && !mbar_wait(&empty_bar[s], ((i / STAGES) - 1) & 1)) {
+                atomicExch(status, STATUS_PRODUCER_TIMEOUT);
+                atomicExch(&aborted, 1);
+                break;
+            }
+            if (*(volatile int*)&aborted) break;
+            unsigned char* w_tile = tiles + (size_t)s * (W_BYTES + X_BYTES);
+            mbar_expect_tx(&full_bar[s], W_BYTES + X_BYTES);
+            tma_load_2d(w_tile, &map_w, (kb0 + i) * BLOCK_K, tile * BLOCK_ROWS, &full_bar[s]);
+            tma_load_2d(w_tile + W_BYTES, &map_x, (kb0 + i) * BLOCK_K, 0, &full_bar[s]);
+        }
+    } else if (warp == 1 && lane == 0) {
+        // ---------------------------------------------------------------- MMA issuer
+        constexpr unsigned idesc = instruction_descriptor(TOK);
+        bool ok = true;
+        for (int i = 0; i < n_kb && ok; ++i) {
+            const int s = i % STAGES;
+            if (!mbar_wait(&full_bar[s], (i / STAGES) & 1)) {
+                atomicExch(status, STATUS_MMA_TIMEOUT);
+                atomicExch(&aborted, 1);
+                ok = false;
+                break;
+            }
+            tc_fence_after();
+            const unsigned char* w_tile = tiles + (size_t)s * (W_BYTES + X_BYTES);
+            const unsigned long long a_desc = smem_descriptor(w_tile), b_desc = smem_descriptor(w_tile + W_BYTES);
+#pragma unroll
+            for (int k = 0; k < BLOCK_K / UMMA_K; ++k)   // 32 bytes further along k per instruction
+                umma_bf16(tmem_base, a_desc + (unsigned long long)(k * UMMA_K * 2 >> 4),
+                          b_desc + (unsigned long long)(k * UMMA_K * 2 >> 4), idesc, (i | k) != 0);
+            umma_commit(&empty_bar[s]);                  // the stage is free once these have read it
+        }
+        if (ok) umma_commit(&done_bar);                  // the accumulator is complete
+    }
+    __syncwarp();
+
+    // -------------------------------------------------------------------- epilogue, all warps
+    bool have = n_kb > 0;
+    if (have) {
+        if (!mbar_wait(&done_bar, 0)) {
+            if (lane == 0) {
+                atomicExch(status, STATUS_EPILOGUE_TIMEOUT);
+                atomicExch(&aborted, 1);
+            }
+            have = false;
+        }
+    }
+    tc_fence_after();
+    have = have && !*(volatile int*)&aborted;
+    const int row = tile * BLOCK_ROWS + warp * 32 + lane;             // the thread's weight row
+    const unsigned lane_base = tmem_base + ((unsigned)(warp * 32) << 16);
+
+    if (splits == 1) {
+        if (have) {
+#pragma unroll 1
+            for (int c = 0; c < TOK; c += 16) {
+                if (c >= M) break;
+                float v[16];
+                tmem_load16(lane_base + c, v);
+                write_columns<TOut, SWIGLU>(y, ldy, v, row, c, M, N);
+            }
+        }
+    } else {
+        float* mine = partial + ((size_t)tile * splits + split) * TOK * BLOCK_ROWS;
+#pragma unroll 1
+        for (int c = 0; c < TOK; c += 16) {
+            if (c >= M) break;
+            float v[16];
+            if (have) tmem_load16(lane_base + c, v);
+#pragma unroll
+            for (int j = 0; j < 16; ++j) mine[(size_t)(c + j) * BLOCK_ROWS + warp * 32 + lane] = have ? v[j] : 0.f;
+        }
+        __threadfence();
+        __syncthreads();
+        if (threadIdx.x == 0) ticket_shared = atomicAdd(&counters[tile], 1);
+        __syncthreads();
+        if (ticket_shared == splits - 1) {               // the last block of the tile adds the ranges in order
+            __threadfence();
+            const float* first = partial + (size_t)tile * splits * TOK * BLOCK_ROWS;
+#pragma unroll 1
+            for (int c = 0; c < TOK; c += 16) {
+                if (c >= M) break;
+                float v[16];
+#pragma unroll
+                for (int j = 0; j < 16; ++j) v[j] = 0.f;
+                for (int s = 0; s < splits; ++s) {
+                    const float* src = first + (size_t)s * TOK * BLOCK_ROWS + (size_t)c * BLOCK_ROWS + warp * 32 + lane;
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) v[j] += __ldcg(src + (size_t)j * BLOCK_ROWS);
+                }
+                write_columns<TOut, SWIGLU>(y, ldy, v, row, c, M, N);
+            }
+            if (threadIdx.x == 0) counters[tile] = 0;
+        }
+    }
+
+    // -------------------------------------------------------------------- teardown
+    tc_fence_before();
+    __syncthreads();
+    if (*(volatile int*)&aborted) {
+        // copies that were requested may still be landing in this block's shared memory
+        const long long start = clock64();
+        while (clock64() - start < 4000000LL) __nanosleep(1000);
+    }
+    if (warp == 0) tmem_dealloc(tmem_base, TMEM_COLS);
+}
+
+// ------------------------------------------------------------------------------------------ host
+
+typedef CUresult (*EncodeTiled)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiled encode_tiled() {
+    static EncodeTiled fn = [] {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult result;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &result) != cudaSuccess ||
+            result != cudaDriverEntryPointSuccess)
+            p = nullptr;
+        return (EncodeTiled)p;
+    }();
+    return fn;
+}
+
+// A [rows x cols] bf16 matrix with `ld` elements between rows, read in boxes of [box_rows x 64].
+int make_map(CUtensorMap* map, const void* base, long rows, long cols, long ld, int box_rows) {
+    EncodeTiled encode = encode_tiled();
+    MRUN_REQUIRE(encode != nullptr, "gemm_tc5: the driver does not offer cuTensorMapEncodeTiled");
+    const cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+    const cuuint64_t strides[1] = {(cuuint64_t)ld * sizeof(bf16)};
+    const cuuint32_t box[2] = {(cuuint32_t)BLOCK_K, (cuuint32_t)box_rows};
+    const cuuint32_t elem[2] = {1, 1};
+    const CUresult rc = encode(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box,
+                               elem, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                               CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    MRUN_REQUIRE(rc == CUDA_SUCCESS, "gemm_tc5: cuTensorMapEncodeTiled failed with code %d", (int)rc);
+    return 0;
+}
+
+template <int TOK, typename TOut, bool SWIGLU>
+int launch(const CUtensorMap& map_w, const CUtensorMap& map_x, TOut* y, long ldy, int M, int N, int K, int splits,
+           float* partial, int* counters, int* status, cudaStream_t stream) {
+    constexpr int STAGES = stages_for<TOK>();
+    constexpr size_t smem = (size_t)STAGES * (BLOCK_ROWS * BLOCK_K * 2 + TOK * BLOCK_K * 2) + 1024;
+    static bool configured = false;
+    if (!configured) {
+        MRUN_CHECK_CUDA(cudaFuncSetAttribute(gemm_tc5_kernel<TOK, TOut, SWIGLU>,
+                                             cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem), "gemm_tc5");
+        configured = true;
+    }
+    const dim3 grid((N + BLOCK_ROWS - 1) / BLOCK_ROWS, splits);
+    gemm_tc5_kernel<TOK, TOut, SWIGLU><<<grid, THREADS, smem, stream>>>(map_w, map_x, y, ldy, M, N, K / BLOCK_K,
+                                                                       partial, counters, status);
+    MRUN_CHECK_LAUNCH("gemm_tc5");
+    return 0;
+}
+
+template <typename TOut, bool SWIGLU>
+int dispatch(const CUtensorMap& map_w, const void* x, long ldx, TOut* y, long ldy, int M, int N, int K, int splits,
+             float* partial, int* counters, int* status, cudaStream_t stream, int tok) {
+    CUtensorMap map_x;
+    if (int rc = make_map(&map_x, x, M, K, ldx, tok)) return rc;
+    switch (tok) {
+        case 32: return launch<32, TOut, SWIGLU>(map_w, map_x, y, ldy, M, N, K, splits, partial, counters, status, stream);
+        case 64: return launch<64, TOut, SWIGLU>(map_w, map_x, y, ldy, M, N, K, splits, partial, counters, status, stream);
+        case 128: return launch<128, TOut, SWIGLU>(map_w, map_x, y, ldy, M, N, K, splits, partial, counters, status, stream);
+        case 256: return launch<256, TOut, SWIGLU>(map_w, map_x, y, ldy, M, N, K, splits, partial, counters, status, stream);
+    }
+    return mrun_set_error("gemm_tc5: no kernel for a token tile of %d", tok);
+}
+
+}  // namespace
+
+// The token tile (MMA N) this kernel uses for M rows, or 0 when it takes no such M.
+MRUN_API int mrun_gemm_tc5_token_tile(int M) {
+    if (M < 1 || M > 256) return 0;
+    return M <= 32 ? 32 : M <= 64 ? 64 : M <= 128 ? 128 : 256;
+}
+
+// Floats of scratch the call needs for `splits` k ranges (0 when splits == 1).
+MRUN_API long mrun_gemm_tc5_scratch_floats(int M, int N, int splits) {
+    const int tok = mrun_gemm_tc5_token_tile(M);
+    if (splits <= 1 || tok == 0) return 0;
+    return (long)((N + BLOCK_ROWS - 1) / BLOCK_ROWS) * splits * tok * BLOCK_ROWS;
+}
+
+// y[M, N] (or [M, N / 2] with swiglu) = x[M, K] · w[N, K]^T.  x rows ldx elements apart, y rows ldy.
+// partial: scratch of mrun_gemm_tc5_scratch_floats floats; counters: one zero int per 128 rows of w
+// (left zero); status: one int the kernel sets non-zero when a wait ran out.
+MRUN_API int mrun_gemm_tc5(const void* x, const void* w, void* y, int out_dtype, int swiglu, int M, int N, int K,
+                           long ldx, long ldy, int splits, float* partial, int* counters, int* status,
+                           cudaStream_t stream) {
+    MRUN_REQUIRE(M >= 1 && N > 0 && K > 0, "gemm_tc5: bad sizes M=%d N=%d K=%d", M, N, K);
+    const int tok = mrun_gemm_tc5_token_tile(M);
+    MRUN_REQUIRE(tok != 0, "gemm_tc5: M=%d exceeds the 256 rows this kernel takes", M);
+    MRUN_REQUIRE(K % BLOCK_K == 0, "gemm_tc5: K=%d is not a multiple of %d", K, BLOCK_K);
+    MRUN_REQUIRE(ldx >= K && ldx % 8 == 0, "gemm_tc5: ldx=%ld must be a multiple of 8 and at least K=%d", ldx, K);
+    MRUN_REQUIRE(((uintptr_t)x & 15) == 0 && ((uintptr_t)w & 15) == 0, "gemm_tc5: x and W must be 16-byte aligned");
+    MRUN_REQUIRE(!swiglu || N % 16 == 0, "gemm_tc5: the gated epilogue needs N=%d to be a multiple of 16", N);
+    MRUN_REQUIRE(ldy >= (swiglu ? N / 2 : N), "gemm_tc5: ldy=%ld is below the output width", ldy);
+    MRUN_REQUIRE(splits >= 1 && splits <= K / BLOCK_K, "gemm_tc5: splits=%d must be in 1..%d", splits, K / BLOCK_K);
+    MRUN_REQUIRE(splits == 1 || (partial && counters), "gemm_tc5: %d k ranges need scratch and counters", splits);
+    MRUN_REQUIRE(status != nullptr, "gemm_tc5: a status word is required");
+    CUtensorMap map_w;
+    if (int rc = make_map(&map_w, w, N, K, K, BLOCK_ROWS)) return rc;
+    if (out_dtype == MRUN_BF16) {
+        if (swiglu)
+            return dispatch<bf16, true>(map_w, x, ldx, (bf16*)y, ldy, M, N, K, splits, partial, counters, status, stream, tok);
+        return dispatch<bf16, false>(map_w, x, ldx, (bf16*)y, ldy, M, N, K, splits, partial, counters, status, stream, tok);
+    }
+    if (out_dtype == MRUN_F32) {
+        MRUN_REQUIRE(!swiglu, "gemm_tc5: the gated epilogue writes bfloat16");
+        return dispatch<float, false>(map_w, x, ldx, (float*)y, ldy, M, N, K, splits, partial, counters, status, stream, tok);
+    }
+    return mrun_set_error("gemm_tc5: unknown output dtype code %d", out_dtype);
+}

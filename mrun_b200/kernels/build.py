@@ -140,8 +140,8 @@ def build_library(name: str, source_names: Iterable[str],
         return target
 
 
-CORE_SOURCES = ("common.cu", "elementwise.cu", "gemm_f32.cu", "gemm_skinny.cu", "attention_generic.cu",
-                "sampling.cu")
+CORE_SOURCES = ("common.cu", "elementwise.cu", "gemm_f32.cu", "gemm_skinny.cu", "gemm_tc5.cu",
+                "attention_generic.cu", "sampling.cu")
 
 
 def build_core() -> str:

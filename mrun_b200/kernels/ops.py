@@ -205,9 +205,80 @@ def gemm_f32_nt(x: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] = 
     return out
 
 
+TC5_ROWS = 256            # the tcgen05 GEMM takes up to this many rows
+TC5_COUNTERS = 4096       # 128-row tiles of W that one call may split over k
+_tc5_state = {}           # device -> (counters, status)
+
+
+def _tc5_buffers(device: torch.device):
+    """Zeroed tile counters (the kernel leaves them zero) and the status word, one set per device,
+    never reallocated, so that captured graphs may keep their addresses."""
+    state = _tc5_state.get(device)
+    if state is None:
+        state = _tc5_state[device] = (torch.zeros(TC5_COUNTERS, dtype=torch.int32, device=device),
+                                      torch.zeros(1, dtype=torch.int32, device=device))
+    return state
+
+
+def tc5_ok(x: torch.Tensor, w: torch.Tensor) -> bool:
+    """Whether the tcgen05 GEMM takes this product: 17..256 rows, bf16, K a multiple of 64."""
+    return (x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and SKINNY_ROWS < x.shape[0] <= TC5_ROWS
+            and x.shape[1] % 64 == 0 and x.stride(1) == 1 and x.stride(0) % 8 == 0 and x.data_ptr() % 16 == 0
+            and w.shape[0] <= 128 * TC5_COUNTERS)
+
+
+def tc5_splits(n: int, k: int, sms: int = 148) -> int:
+    """Ranges of k per 128-row tile: enough blocks to fill the device once, each with at least
+    four 64-wide k blocks."""
+    tiles = -(-n // 128)
+    if tiles >= sms:
+        return 1
+    return max(1, min(sms // tiles, (k // 64) // 4))
+
+
+def gemm_tc5(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype = torch.bfloat16,
+             swiglu_rows: bool = False, splits: Optional[int] = None) -> torch.Tensor:
+    """y = x @ w.T for 1..256 rows on the tcgen05 tensor cores (TMA-fed, accumulator in tensor
+    memory).  ``swiglu_rows`` as in :func:`gemm_skinny`.  A wait inside the kernel that runs out
+    sets the status word that :func:`tc5_check` reads."""
+    _check(x, "x", torch.bfloat16, dense=False); _check(w, "w", torch.bfloat16)
+    m, k = x.shape
+    n = w.shape[0]
+    if w.shape[1] != k:
+        raise KernelError(f"gemm_tc5: x {tuple(x.shape)} vs w {tuple(w.shape)}")
+    if splits is None:
+        splits = tc5_splits(n, k)
+    out = torch.empty((m, n // 2 if swiglu_rows else n), dtype=out_dtype, device=x.device)
+    counters, status = _tc5_buffers(x.device)
+    core = _lib.core()
+    partial = None
+    if splits > 1:
+        query = core._dll.mrun_gemm_tc5_scratch_floats
+        query.restype = ctypes.c_long
+        partial = torch.empty(query(_c_int(m), _c_int(n), _c_int(splits)), dtype=torch.float32, device=x.device)
+    core.call("mrun_gemm_tc5", _ptr(x), _ptr(w), _ptr(out), dtype_code(out_dtype), _c_int(1 if swiglu_rows else 0),
+              _c_int(m), _c_int(n), _c_int(k), _c_long(x.stride(0) if m > 1 else max(k, x.stride(0))),
+              _c_long(out.shape[1]), _c_int(splits), _ptr(partial), _ptr(counters), _ptr(status), _stream())
+    return out
+
+
+def tc5_check(device: Optional[torch.device] = None) -> None:
+    """Raises if a tcgen05 GEMM on the device gave up on a wait (and clears the status word)."""
+    for dev, (_, status) in list(_tc5_state.items()):
+        if device is not None and dev != device:
+            continue
+        code = int(status.item())
+        if code:
+            status.zero_()
+            what = {1: "the TMA producer", 2: "the MMA issuer", 3: "the epilogue"}.get(code, "a role")
+            raise KernelError(f"gemm_tc5: {what} waited longer than its budget on {dev}; the results of that "
+                              f"call are invalid")
+
+
 def linear(x: torch.Tensor, w: torch.Tensor, out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
     """y = x @ w.T.  float32: this library's own IEEE kernel.  bfloat16 with at most 16 rows (decode):
-    this library's weight-streaming tensor-core kernel.  bfloat16 otherwise: the vendor GEMM
+    this library's weight-streaming tensor-core kernel; with 17 to 256 rows: this library's
+    tcgen05 kernel.  bfloat16 otherwise (prefill): the vendor GEMM
     library with 32-bit accumulation (the reference calls its array library's matmul for the
     same products, crates/mrun-engine/src/load.rs:294-306)."""
     if x.dtype == torch.float32:
@@ -215,6 +286,8 @@ def linear(x: torch.Tensor, w: torch.Tensor, out_dtype: Optional[torch.dtype] = 
     _check(x, "x", torch.bfloat16, dense=False); _check(w, "w", torch.bfloat16)
     if skinny_ok(x, w):
         return gemm_skinny(x, w, out_dtype or torch.bfloat16)
+    if tc5_ok(x, w):
+        return gemm_tc5(x, w, out_dtype or torch.bfloat16)
     if out_dtype is None or out_dtype == torch.bfloat16:
         return torch.mm(x, w.t())
     return torch.mm(x, w.t(), out_dtype=out_dtype)

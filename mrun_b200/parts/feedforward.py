@@ -39,6 +39,8 @@ class GatedMLP:
     def forward(self, x: torch.Tensor, ctx) -> torch.Tensor:
         if self.interleaved and ops.skinny_ok(x, self.w_gate_up):
             act = ops.gemm_skinny(x, self.w_gate_up, swiglu_rows=True)
+        elif self.interleaved and ops.tc5_ok(x, self.w_gate_up):
+            act = ops.gemm_tc5(x, self.w_gate_up, swiglu_rows=True)
         else:
             gate_up = ops.linear(x, self.w_gate_up)
             act = torch.empty((x.shape[0], self.spec.intermediate), dtype=x.dtype, device=x.device)
