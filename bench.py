@@ -113,16 +113,31 @@ def fill_requests(executor, batch: int, context: int, vocab: int, tag: str):
 
 
 def time_decode(executor, requests, vocab: int, steps: int, warmup: int, profiler_range: bool = False):
-    """Device time of ``steps`` decode steps: captured step + token read-back, as generation does."""
+    """Device time of ``steps`` decode steps the way generation runs them: a step is launched
+    with the tokens of the step before it taken on the device, then that step's tokens are read
+    back into pinned host memory."""
     import torch
     from mrun_b200.engine import StepEntry
-    tokens = seeded_tokens(vocab, len(requests), 7)
-    def one():
-        nonlocal tokens
-        out = executor.decode_step([StepEntry(r, [t], [0]) for r, t in zip(requests, tokens)])
-        tokens = out.to("cpu").tolist()
-    for _ in range(warmup):
-        one()
+    n = len(requests)
+    first = seeded_tokens(vocab, n, 7)
+    pinned = [torch.empty(n, dtype=torch.int32, pin_memory=True) for _ in range(2)]
+    state = {"event": None, "turn": 0}
+
+    def one(first_step: bool):
+        tokens = first if first_step else [0] * n
+        sources = None if first_step else list(range(n))
+        out = executor.decode_step([StepEntry(r, [t], [0]) for r, t in zip(requests, tokens)], None, sources)
+        pinned[state["turn"]].copy_(out, non_blocking=True)
+        event = torch.cuda.Event()
+        event.record()
+        if state["event"] is not None:
+            state["event"].synchronize()
+            pinned[state["turn"] ^ 1].tolist()          # the step before is read here
+        state["event"], state["turn"] = event, state["turn"] ^ 1
+
+    one(True)
+    for _ in range(warmup - 1):
+        one(False)
     torch.cuda.synchronize()
     begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     launches = executor.launches.total
@@ -130,7 +145,7 @@ def time_decode(executor, requests, vocab: int, steps: int, warmup: int, profile
         torch.cuda.profiler.start()
     begin.record()
     for _ in range(steps):
-        one()
+        one(False)
     end.record()
     torch.cuda.synchronize()
     if profiler_range:
@@ -249,20 +264,26 @@ def main() -> int:
                 "roofline": roofline, "points": points, "gpu_launches": launches, "prefill_ms": prefill_ms}
         print(json.dumps(line))
         return 0
+    # Token lists in, token lists out, through Engine.generate.  The token budget of this engine
+    # takes the eight prompts in one step, so all eight decode side by side for every step of
+    # the window that is timed: from the first token of each (read back on the host) to the last.
+    from mrun_b200.engine.engine import Engine as EngineClass
+    e2e_engine = EngineClass(executor, max_batch_tokens=main_batch * CONTEXT)
     out_tokens = args.steps + 1
-    prompts = [seeded_tokens(vocab, CONTEXT, 50 + i) for i in range(8)]
-    engine.generate(prompts[:2], max_tokens=4, ignore_eos=True)          # warm the mixed-step shapes
+    prompts = [seeded_tokens(vocab, CONTEXT, 50 + i) for i in range(main_batch)]
+    e2e_engine.generate(prompts, max_tokens=4, ignore_eos=True)         # warm the prompt step's shapes
     uploaded = executor.staging.bytes_uploaded
-    steps_before = engine.stats.steps
-    d2h_before = engine.stats.d2h_bytes
+    steps_before = e2e_engine.stats.steps
+    d2h_before = e2e_engine.stats.d2h_bytes
     torch.cuda.synchronize()
-    generations = engine.generate(prompts, max_tokens=out_tokens, ignore_eos=True)
+    generations = e2e_engine.generate(prompts, max_tokens=out_tokens, ignore_eos=True)
     torch.cuda.synchronize()
     last_first = max(g.first_token_time for g in generations)
     finished = max(g.finished_time for g in generations)
     decoded = sum(sum(1 for t in g.token_times if t > last_first) for g in generations)
     e2e_value = decoded / max(finished - last_first, 1e-9)
-    n_steps = max(1, engine.stats.steps - steps_before)
+    n_steps = max(1, e2e_engine.stats.steps - steps_before)
+    engine = e2e_engine
     e2e = {"value": round(e2e_value, 1), "unit": "tok/s",
            "h2d_bytes_per_step": round((executor.staging.bytes_uploaded - uploaded) / n_steps, 1),
            "d2h_bytes_per_step": round((engine.stats.d2h_bytes - d2h_before) / n_steps, 1)}

@@ -426,3 +426,26 @@ MRUN_API int mrun_scatter_i32(int* dst, const int* index, const int* value, int 
     MRUN_CHECK_LAUNCH("scatter_i32");
     return 0;
 }
+
+// ------------------------------------------------------------------------------------------
+// Token feedback: ids[r] = previous[source[r]] where source[r] >= 0.  Lets a decode step take the
+// tokens the step before it sampled straight from the device, before the host has read them
+// (the reference feeds a sampled token before reading it back too,
+// crates/mrun-engine/src/nuvec_engine.rs:1489-1500).
+// ------------------------------------------------------------------------------------------
+__global__ void select_tokens_kernel(int* __restrict__ ids, const int* __restrict__ previous,
+                                     const int* __restrict__ source, int rows, int previous_rows) {
+    const int r = blockIdx.x * blockDim.x + threadIdx.x;
+    if (r >= rows) return;
+    const int s = source[r];
+    if (s >= 0 && s < previous_rows) ids[r] = previous[s];
+}
+
+MRUN_API int mrun_select_tokens(int* ids, const int* previous, const int* source, int rows, int previous_rows,
+                                cudaStream_t stream) {
+    MRUN_REQUIRE(rows >= 0 && previous_rows >= 0, "select_tokens: bad sizes rows=%d previous=%d", rows, previous_rows);
+    if (rows == 0) return 0;
+    select_tokens_kernel<<<(rows + 255) / 256, 256, 0, stream>>>(ids, previous, source, rows, previous_rows);
+    MRUN_CHECK_LAUNCH("select_tokens");
+    return 0;
+}

@@ -105,14 +105,15 @@ RECENT = 20   # token ids per row that the repetition penalty looks at
 
 def layout(tokens: int, segments: int, groups: int, sampling_rows: int = 0) -> Dict[str, slice]:
     """Where each array sits in the step's int32 buffer.  With ``sampling_rows`` the buffer also
-    carries the per-row sampling settings (floats as their bit patterns, 64-bit keys as pairs on
-    an even offset)."""
+    carries, per row, where its token comes from (``token_src``: a row of the previous captured
+    step, or -1 for the id the host wrote) and the sampling settings (floats as their bit
+    patterns, 64-bit keys as pairs on an even offset)."""
     names = [("token_ids", tokens), ("positions", tokens), ("token_slot", tokens),
              ("seg_q_start", segments + 1), ("seg_kv_len", segments), ("seg_slot", segments)]
     names += [(f"slot_mapping{g}", tokens) for g in range(groups)]
     if sampling_rows:
         r = sampling_rows
-        names += [("temperature", r), ("top_p", r), ("min_p", r), ("penalty", r), ("top_k", r),
+        names += [("token_src", r), ("temperature", r), ("top_p", r), ("min_p", r), ("penalty", r), ("top_k", r),
                   ("recent", RECENT * r), ("keys", 2 * r)]
     out, at = {}, 0
     for name, n in names:
@@ -149,6 +150,7 @@ def build_context(entries: Sequence[StepEntry], manager: CacheManager, staging: 
     where = layout(total, n_seg, len(keys), total if sampling is not None else 0)
     host = np.zeros(where["_size"].stop, dtype=np.int32)
     if sampling is not None:
+        host[where["token_src"]] = -1
         sampling(host, where)
     token_ids, positions, token_slot = host[where["token_ids"]], host[where["positions"]], host[where["token_slot"]]
     seg_q_start, seg_kv_len, seg_slot = host[where["seg_q_start"]], host[where["seg_kv_len"]], host[where["seg_slot"]]
@@ -159,7 +161,28 @@ def build_context(entries: Sequence[StepEntry], manager: CacheManager, staging: 
 
     segments: List[SegmentInfo] = []
     row = 0
-    for s, entry in enumerate(entries):
+    if max(lengths) == 1:
+        # every entry brings one token (a decode step): plain lists, one conversion per array
+        n_real = len(entries)
+        starts = [e.request.length for e in entries]
+        slots = [e.request.slot for e in entries]
+        token_ids[:n_real] = [e.tokens[0] for e in entries]
+        positions[:n_real] = starts
+        token_slot[:n_real] = slots
+        seg_slot[:n_real] = slots
+        seg_q_start[:n_real] = range(n_real)
+        seg_kv_len[:n_real] = [p + 1 for p in starts]
+        for g, key in enumerate(keys):
+            values = []
+            for e, p in zip(entries, starts):
+                page = e.request.blocks[key][p // page_size]
+                values.append(-1 if page == FREED else page * page_size + p % page_size)
+            maps[g][:n_real] = values
+        segments = [SegmentInfo(slot, i, 1, p) for i, (slot, p) in enumerate(zip(slots, starts))]
+        entries_loop = ()
+    else:
+        entries_loop = entries
+    for s, entry in enumerate(entries_loop):
         n, start = lengths[s], entry.request.length
         token_ids[row:row + n] = np.asarray(entry.tokens, dtype=np.int64)
         pos = np.arange(start, start + n, dtype=np.int32)

@@ -38,6 +38,16 @@ class Generation:
 
 
 @dataclass
+class _Flying:
+    """A captured decode step whose tokens the host has not read yet."""
+    plan: StepPlan
+    rows: dict                     # id(request) -> row of the step
+    bucket: int
+    pinned: torch.Tensor           # where its tokens land on the host
+    event: torch.cuda.Event
+
+
+@dataclass
 class EngineStats:
     steps: int = 0
     tokens_in: int = 0
@@ -58,6 +68,9 @@ class Engine:
         self.eos_token_ids = tuple(executor.spec.eos_token_ids)
         self.stats = EngineStats()
         self._next_id = 0
+        rows = max(1, 2 * executor.cache.max_requests)
+        self._token_buffers = [torch.empty(rows, dtype=torch.int32, pin_memory=True) for _ in range(2)]
+        self._token_turn = 0
 
     # ------------------------------------------------------------------ construction
     @classmethod
@@ -110,51 +123,109 @@ class Engine:
                 for r in requests]
 
     def run(self, requests: Sequence[Request]) -> None:
-        """Runs the requests to their end through the scheduler and the step function."""
+        """Runs the requests to their end through the scheduler and the step function.
+
+        Pure decode steps are pipelined: step n+1 is launched with the tokens of step n taken on
+        the device, and only then are step n's tokens read back, so the host's work for a step
+        overlaps the device's work for the step before (the reference pipelines its decode the
+        same way, crates/mrun-engine/src/nuvec_engine.rs:1489-1517)."""
         scheduler = Scheduler(self.executor.cache, eos_token_ids=self.eos_token_ids,
                               max_batch_tokens=self.max_batch_tokens, reserve=self.reserve,
                               max_queue=self.max_queue, max_positions=self.executor.spec.max_positions)
         for request in requests:
             scheduler.submit(request)
+        flying: Optional[_Flying] = None
         try:
-            while scheduler.has_work():
-                plan = scheduler.schedule()
+            while scheduler.has_work() or flying is not None:
+                plan = scheduler.schedule() if scheduler.has_work() else None
+                if plan is not None and self._pipelinable(plan, flying):
+                    launched = self._launch_captured(scheduler, plan, flying)
+                    if launched is not None:
+                        if flying is not None:
+                            self._deliver(scheduler, flying)
+                        flying = launched
+                        continue
+                if flying is not None:          # read what is in flight, then plan with everything known
+                    self._deliver(scheduler, flying)
+                    flying = None
+                    continue
                 if plan is None:
                     raise RuntimeError("the scheduler has waiting requests and nothing to run")
-                tokens = self._run_plan(scheduler, plan)
-                if tokens is not None:
-                    scheduler.complete(plan, tokens)
+                self._run_plan(scheduler, plan)
+            if scheduler.unsettled():
+                raise RuntimeError("requests are left without a step to run")
         finally:
+            if flying is not None:
+                flying.event.synchronize()
             for request in list(scheduler.running):
+                request.inflight = 0
                 scheduler.abort(request, "generation was interrupted")
         self.stats.preemptions += scheduler.preemptions
+        from ..kernels import ops
+        ops.tc5_check(self.executor.device)
 
-    def _run_plan(self, scheduler: Scheduler, plan: StepPlan) -> Optional[List[int]]:
+    # ------------------------------------------------------------------ pipelined decode steps
+    def _pipelinable(self, plan: StepPlan, flying: Optional["_Flying"]) -> bool:
+        """A plan of single decode tokens that a captured step takes, whose unread tokens all sit
+        in the step in flight, and that needs no token history for a repetition penalty."""
+        if not all(len(e.tokens) == 1 and e.wants_logits for e in plan.entries):
+            return False
+        bucket = self.executor.decode_bucket(len(plan.entries))
+        if bucket is None:
+            return False
+        if any(e.request.sampling.repetition_penalty != 1.0 for e in plan.entries):
+            return flying is None and not any(e.from_device for e in plan.entries)
+        for entry in plan.entries:
+            if entry.from_device and (flying is None or flying.bucket != bucket
+                                      or id(entry.request) not in flying.rows):
+                return False
+        return True
+
+    def _launch_captured(self, scheduler: Scheduler, plan: StepPlan,
+                         flying: Optional["_Flying"]) -> Optional["_Flying"]:
+        sampled = plan.sampled
+        entries = [StepEntry(e.request.cache, e.tokens, [0]) for e in plan.entries]
+        sources = [flying.rows[id(e.request)] if e.from_device else -1 for e in plan.entries]
+        try:
+            tokens = self.executor.decode_step(
+                entries, lambda host, where: _fill_sampling(host, where, sampled), sources)
+        except OutOfPages:
+            return None                     # settle what is in flight, then the slow path decides
+        pinned = self._token_buffers[self._token_turn]
+        self._token_turn ^= 1
+        pinned[:len(entries)].copy_(tokens, non_blocking=True)
+        event = torch.cuda.Event()
+        event.record()
+        scheduler.launched(plan)
+        self.stats.steps += 1
+        self.stats.tokens_in += plan.num_tokens
+        return _Flying(plan, {id(e.request): row for row, e in enumerate(plan.entries)},
+                       self.executor.decode_bucket(len(entries)), pinned, event)
+
+    def _deliver(self, scheduler: Scheduler, flying: "_Flying") -> None:
+        flying.event.synchronize()
+        host = flying.pinned[:len(flying.plan.entries)].tolist()
+        self.stats.tokens_out += len(host)
+        self.stats.d2h_bytes += 4 * len(host)
+        scheduler.complete(flying.plan, host)
+
+    def _run_plan(self, scheduler: Scheduler, plan: StepPlan) -> None:
+        """A step with prompt portions in it (or one no captured step takes): run and read at once."""
         entries = [StepEntry(e.request.cache, e.tokens, [len(e.tokens) - 1] if e.wants_logits else [])
                    for e in plan.entries]
         sampled = plan.sampled
-        captured = (all(len(e.tokens) == 1 and e.wants_logits for e in plan.entries)
-                    and self.executor.decode_bucket(len(entries)) is not None)
         try:
-            if captured:
-                tokens = self.executor.decode_step(entries, lambda host, where: _fill_sampling(host, where, sampled))
-            else:
-                logits = self.executor.step(entries)
+            logits = self.executor.step(entries)
         except OutOfPages:
             if scheduler.preempt_newest() is None:
                 raise
-            return None          # plan again without the preempted request
-        if captured:
-            self.stats.steps += 1
-            self.stats.tokens_in += plan.num_tokens
-            host = tokens.to("cpu").tolist()
-            self.stats.tokens_out += len(host)
-            self.stats.d2h_bytes += 4 * len(host)
-            return host
+            return                          # plan again without the preempted request
+        scheduler.launched(plan)
         self.stats.steps += 1
         self.stats.tokens_in += plan.num_tokens
         if not sampled:
-            return []
+            scheduler.complete(plan, [])
+            return
         tokens = self.sampler.sample(
             logits, [r.sampling for r in sampled], [r.seed for r in sampled],
             [len(r.output) + 1 for r in sampled],
@@ -162,7 +233,7 @@ class Engine:
         host = tokens.to("cpu").tolist()
         self.stats.tokens_out += len(host)
         self.stats.d2h_bytes += 4 * len(host)
-        return host
+        scheduler.complete(plan, host)
 
     # ------------------------------------------------------------------ direct stepping
     def step(self, entries: Sequence[StepEntry]):
@@ -203,7 +274,7 @@ def _fill_sampling(host, where, requests: Sequence[Request]) -> None:
     keys = np.zeros(len(temperature), dtype=np.uint64)
     for i, r in enumerate(requests):
         if not r.sampling.greedy:
-            keys[i] = draw_key(r.seed, len(r.output) + 1)
+            keys[i] = draw_key(r.seed, len(r.output) + r.inflight + 1)
         if r.sampling.repetition_penalty != 1.0:
             ids = r.recent(RECENT)
             recent[i, :len(ids)] = ids

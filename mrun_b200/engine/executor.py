@@ -124,13 +124,23 @@ class Executor:
             bucket *= 2
         return bucket if bucket <= max(1, self.cache.max_requests) * 2 else None
 
-    def decode_step(self, entries: Sequence[StepEntry], sampling=None) -> torch.Tensor:
+    def decode_step(self, entries: Sequence[StepEntry], sampling=None,
+                    sources: Optional[Sequence[int]] = None) -> torch.Tensor:
         """One token for each entry (each brings exactly one token) through a captured graph,
         sampling included.  ``sampling(host, where)`` writes the rows' sampling settings into the
-        step's buffer (left at greedy when None).  Returns int32 device tokens, one per entry."""
-        self._validate(entries)
-        if any(len(e.tokens) != 1 for e in entries):
-            raise StepError("decode_step takes one token per request")
+        step's buffer (left at greedy when None).  ``sources[i] >= 0`` says that entry i's token
+        is row ``sources[i]`` of the previous captured step of the same size, still on the device
+        (the entry's own token value is then ignored).  Returns int32 device tokens, one per
+        entry; they stay valid until the next captured step of this size runs."""
+        vocab, limit = self.spec.vocab_size, self.spec.max_positions
+        for e in entries:
+            if len(e.tokens) != 1:
+                raise StepError("decode_step takes one token per request")
+            if not 0 <= e.tokens[0] < vocab:
+                raise StepError(f"request {e.request.request_id!r}: token id outside [0, {vocab})")
+            if e.request.length + 1 > limit:
+                raise StepError(f"request {e.request.request_id!r}: {e.request.length + 1} tokens exceed "
+                                f"max_position_embeddings={limit}")
         bucket = self.decode_bucket(len(entries))
         if bucket is None:
             raise StepError(f"no captured decode step takes {len(entries)} requests")
@@ -139,7 +149,12 @@ class Executor:
             graph = self._graphs[bucket] = DecodeGraph(self, bucket)
         plan = self.cache.plan_append([(e.request, 1) for e in entries])
         try:
-            fill = sampling if sampling is not None else _greedy_rows
+            base = sampling if sampling is not None else _greedy_rows
+
+            def fill(host, where):
+                base(host, where)
+                if sources is not None:
+                    host[where["token_src"]][:len(sources)] = sources
             build_context(entries, self.cache, self.staging, pad_tokens=bucket, out=graph.buffer,
                           sampling=fill)
             graph.replay()
@@ -181,6 +196,7 @@ class DecodeGraph:
         for g in range(len(keys)):
             buf[where[f"slot_mapping{g}"]] = -1
         buf[where["recent"]] = -1
+        buf[where["token_src"]] = -1
         f32 = lambda name: buf[where[name]].view(torch.float32)
         buf[where["top_p"]] = torch.ones(rows, dtype=torch.float32, device=device).view(torch.int32)
         buf[where["penalty"]] = torch.ones(rows, dtype=torch.float32, device=device).view(torch.int32)
@@ -197,6 +213,8 @@ class DecodeGraph:
 
         def run():
             self.ctx.shared.clear()
+            # rows whose token is still on the device take it from the previous replay's output
+            ops.select_tokens(buf[where["token_ids"]], self.tokens, buf[where["token_src"]])
             logits = model.forward(self.ctx, cache.entries, self.row_index)
             ops.repetition_penalty(logits, buf[where["recent"]].view(rows, RECENT), f32("penalty"))
             ops.sample(logits, self.tokens, temperature=f32("temperature"), top_p=f32("top_p"),

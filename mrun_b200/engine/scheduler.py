@@ -22,6 +22,12 @@ Decisions, with the reference's where it has one
   everything back and returns to the head of the queue; when it is admitted again it feeds its
   prompt and what it had generated as one prompt.  Requests admitted earlier are never touched,
   and a request that runs alone always fits because of the refusal above.
+* **Steps in flight**: a decode step may be launched before the tokens of the step before it have
+  been read back (they are taken from the device).  The scheduler then plans with
+  ``Request.inflight`` unread tokens; a request whose unread token will reach its output limit
+  is left out, and a request that turns out to have ended (an end token) while a later step was
+  already launched is marked ``retiring``: that step's token for it is dropped and its pages are
+  freed when the step is read.
 * **Finishing**: an end token (unless ``ignore_eos``) → ``stop``; the output limit → ``length``;
   the last 512 output tokens repeating with a period of at most 256, checked every 16 tokens →
   ``repetition`` (crates/mrun/src/runtime/generate.rs:27-33, 420-426, 866-919).
@@ -75,6 +81,8 @@ class Request:
     first_token_at: float = 0.0
     finished_at: float = 0.0
     token_times: List[float] = field(default_factory=list)   # when each output token was read back
+    inflight: int = 0                  # tokens sampled on the device that the host has not read yet
+    retiring: bool = False             # finished, but a step in flight still holds a row of it
 
     @property
     def sequence_len(self) -> int:
@@ -82,7 +90,8 @@ class Request:
 
     @property
     def remaining(self) -> int:
-        return self.sequence_len - self.fed
+        """Tokens still to feed, counting a sampled token that has not been read back yet."""
+        return self.sequence_len + self.inflight - self.fed
 
     def next_tokens(self, n: int) -> List[int]:
         start = self.fed
@@ -104,6 +113,7 @@ class PlannedEntry:
     request: Request
     tokens: List[int]
     wants_logits: bool
+    from_device: bool = False          # its one token is still on the device (sampled by the step before)
 
 
 @dataclass
@@ -174,6 +184,14 @@ class Scheduler:
         return None
 
     def has_work(self) -> bool:
+        """Whether a further step can be planned now (requests that only wait for tokens in flight
+        do not count)."""
+        if self.waiting:
+            return True
+        return any(not r.retiring and len(r.output) + r.inflight < r.limit for r in self.running)
+
+    def unsettled(self) -> bool:
+        """Whether any request is still admitted (running, or waiting for tokens in flight)."""
         return bool(self.waiting or self.running)
 
     # ------------------------------------------------------------------ admission
@@ -213,11 +231,18 @@ class Scheduler:
             return None
         budget = self.max_batch_tokens
         entries: List[PlannedEntry] = []
-        decoders = [r for r in self.running if r.remaining == 1 and r.fed > 0]
+        # a request whose unread token will be its last, or that finished while a step was in
+        # flight, takes no part any more
+        active = [r for r in self.running
+                  if not r.retiring and len(r.output) + r.inflight < r.limit]
+        decoders = [r for r in active if r.remaining == 1 and r.fed > 0]
         for request in decoders[:budget]:
-            entries.append(PlannedEntry(request, request.next_tokens(1), True))
+            if request.inflight:
+                entries.append(PlannedEntry(request, [0], True, from_device=True))
+            else:
+                entries.append(PlannedEntry(request, request.next_tokens(1), True))
         budget -= len(entries)
-        readers = sorted((r for r in self.running if not (r.remaining == 1 and r.fed > 0)),
+        readers = sorted((r for r in active if not (r.remaining == 1 and r.fed > 0) and not r.inflight),
                          key=lambda r: (r.remaining, r.order))
         for request in readers:
             if budget < 1:
@@ -227,9 +252,18 @@ class Scheduler:
             budget -= n
         return StepPlan(entries) if entries else None
 
+    def launched(self, plan: StepPlan) -> None:
+        """Records that the plan's step was handed to the device: its tokens count as fed, and
+        every entry that wanted logits has one sampled token on the way."""
+        for entry in plan.entries:
+            entry.request.fed += len(entry.tokens)
+            if entry.wants_logits:
+                entry.request.inflight += 1
+
     def complete(self, plan: StepPlan, sampled: Sequence[int]) -> List[Request]:
-        """Records a finished step: ``sampled`` holds one token per entry that wanted logits, in
-        order.  Returns the requests that finished."""
+        """Records the tokens of a launched step: ``sampled`` holds one per entry that wanted
+        logits, in order.  Returns the requests that finished.  The token of a request that
+        finished meanwhile (a later step was launched before its end token was read) is dropped."""
         now = time.perf_counter()
         done: List[Request] = []
         sampled = list(sampled)
@@ -238,11 +272,15 @@ class Scheduler:
         at = 0
         for entry in plan.entries:
             request = entry.request
-            request.fed += len(entry.tokens)
             if not entry.wants_logits:
                 continue
             token = int(sampled[at])
             at += 1
+            request.inflight -= 1
+            if request.retiring:
+                if request.inflight == 0:
+                    self._retire(request)
+                continue
             if not request.output:
                 request.first_token_at = now
             request.output.append(token)
@@ -255,7 +293,10 @@ class Scheduler:
             elif len(request.output) % LOOP_CHECK_EVERY == 0 and looping(request.output):
                 reason = "repetition"
             if reason is not None:
-                self._retire(request)
+                if request.inflight:
+                    request.retiring = True          # its row in the step in flight is dropped later
+                else:
+                    self._retire(request)
                 self._finish(request, reason)
                 done.append(request)
         return done
@@ -264,9 +305,12 @@ class Scheduler:
     def preempt_newest(self) -> Optional[Request]:
         """Gives back everything the running request admitted last holds and puts it at the head
         of the queue.  None when at most one request runs (it is never preempted)."""
-        if len(self.running) <= 1:
+        candidates = [r for r in self.running if not r.retiring]
+        if len(candidates) <= 1:
             return None
-        victim = max(self.running, key=lambda r: r.order)
+        if any(r.inflight for r in self.running):
+            raise RuntimeError("a request cannot be preempted while a step is in flight")
+        victim = max(candidates, key=lambda r: r.order)
         self._retire(victim)
         victim.state = "waiting"
         victim.fed = 0

@@ -4,6 +4,7 @@ pointers with the current CUDA stream.  Every function needs CUDA tensors; none 
 from __future__ import annotations
 
 import ctypes
+import os
 from typing import Optional
 
 import torch
@@ -220,9 +221,17 @@ def _tc5_buffers(device: torch.device):
     return state
 
 
+# Measured on B200 at the Qwen3-8B shapes with 64 rows (CUDA events, captured graph): the vendor
+# GEMM 11.6 / 10.1 / 39.6 / 22.7 us for QKV / O / gate-up / down, this kernel 23.3 / 23.3 / 77.8 /
+# 39.0 us: one block per 128-row tile streams at about 40 GB/s per SM, so it needs every SM busy
+# for the whole call (a stream-K schedule) to compete.  Until then it is used on request only.
+TC5_DEFAULT = os.environ.get("MRUN_TC5", "0") == "1"
+
+
 def tc5_ok(x: torch.Tensor, w: torch.Tensor) -> bool:
-    """Whether the tcgen05 GEMM takes this product: 17..256 rows, bf16, K a multiple of 64."""
-    return (x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and SKINNY_ROWS < x.shape[0] <= TC5_ROWS
+    """Whether the tcgen05 GEMM is to take this product: switched on (MRUN_TC5=1), 17..256 rows,
+    bf16, K a multiple of 64."""
+    return (TC5_DEFAULT and x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and SKINNY_ROWS < x.shape[0] <= TC5_ROWS
             and x.shape[1] % 64 == 0 and x.stride(1) == 1 and x.stride(0) % 8 == 0 and x.data_ptr() % 16 == 0
             and w.shape[0] <= 128 * TC5_COUNTERS)
 
@@ -331,3 +340,12 @@ def scatter_i32(dst: torch.Tensor, index: torch.Tensor, value: torch.Tensor) -> 
         raise KernelError("scatter_i32: index and value differ in length")
     _lib.core().call("mrun_scatter_i32", _ptr(dst), _ptr(index), _ptr(value), _c_int(index.numel()),
                      _c_long(dst.numel()), _stream())
+
+
+def select_tokens(ids: torch.Tensor, previous: torch.Tensor, source: torch.Tensor) -> None:
+    """ids[r] = previous[source[r]] where source[r] >= 0 (int32 tensors)."""
+    _check(ids, "ids", torch.int32); _check(previous, "previous", torch.int32); _check(source, "source", torch.int32)
+    if source.numel() != ids.numel():
+        raise KernelError("select_tokens: one source per row is needed")
+    _lib.core().call("mrun_select_tokens", _ptr(ids), _ptr(previous), _ptr(source), _c_int(ids.numel()),
+                     _c_int(previous.numel()), _stream())

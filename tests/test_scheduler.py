@@ -33,8 +33,9 @@ def drive(scheduler, next_token=lambda r: len(r.output) + 100, max_steps=10000, 
         plans.append(plan)
         if on_plan:
             on_plan(plan)
+        scheduler.launched(plan)
         scheduler.complete(plan, [next_token(r) for r in plan.sampled])
-    assert not scheduler.has_work()
+    assert not scheduler.has_work() and not scheduler.unsettled()
     return plans
 
 
