@@ -87,3 +87,60 @@ def test_long_decoding_stays_on_the_plain_logits(tiny):
         assert worst <= TOLERANCE[dtype], (dtype, worst)
         ex.release(request)
         ex.cache.check_invariants()
+
+
+def test_end_tokens_stop_requests_in_the_middle_of_pipelined_decoding(tiny):
+    """Decode steps are launched before the tokens of the step before them are read.  A request
+    that samples an end token has then already been given a row in the next step: that row's
+    token must be dropped, the other requests must go on unchanged, and everything must be freed."""
+    from mrun_b200 import Engine
+    name, folder, settings = tiny
+    cfg, weights = plain.load_folder(folder)
+    prompts = [random_tokens(cfg["vocab_size"], n, seed=200 + n) for n in (6, 11, 19, 25, 3)]
+    engine = Engine.from_folder(folder, dtype="float32", page_size=settings["page_size"], context=1024,
+                                max_batch_tokens=64, max_requests=8)
+    free = engine.generate(prompts, max_tokens=40, ignore_eos=True)
+    assert all(len(r.tokens) == 40 for r in free)
+    # an end token that stops some requests early and at different steps
+    counts = {}
+    for r in free:
+        for t in set(r.tokens[3:30]):
+            counts[t] = counts.get(t, 0) + 1
+    eos = max(counts, key=lambda t: (counts[t], t))
+    engine.eos_token_ids = (eos,)
+    stopped = engine.generate(prompts, max_tokens=40)
+    reasons = set()
+    for before, after in zip(free, stopped):
+        if eos in before.tokens:
+            cut = before.tokens.index(eos) + 1
+            assert after.tokens == before.tokens[:cut] and after.finish_reason == ("stop" if cut <= 40 else "length")
+        else:
+            assert after.tokens == before.tokens and after.finish_reason == "length"
+        reasons.add(after.finish_reason)
+    assert "stop" in reasons
+    engine.executor.cache.check_invariants()
+    assert not engine.executor.cache.live and engine.executor.cache.free_pages() == engine.executor.cache.num_pages
+    # different output limits: each request leaves the pipeline at its own step
+    limits = engine.generate(prompts[:3], max_tokens=7, ignore_eos=True) + engine.generate(prompts[3:], max_tokens=1, ignore_eos=True)
+    for before, after in zip(free, limits):
+        assert after.tokens == before.tokens[:len(after.tokens)] and after.finish_reason == "length"
+    assert [len(r.tokens) for r in limits] == [7, 7, 7, 1, 1]
+
+
+def test_repetition_penalty_and_filters_through_generate(tiny):
+    """Sampling settings that need the token history (the penalty) keep decoding correct: the
+    tokens equal a host-side replay of the same rule on the plain logits."""
+    from mrun_b200 import Engine, SamplingParams
+    name, folder, settings = tiny
+    cfg, weights = plain.load_folder(folder)
+    prompt = random_tokens(cfg["vocab_size"], 12, seed=5)
+    engine = Engine.from_folder(folder, dtype="float32", page_size=settings["page_size"], context=256, max_requests=2)
+    params = SamplingParams(temperature=0.9, top_k=12, top_p=0.95, min_p=0.01, seed=77, repetition_penalty=1.4)
+    got = engine.generate([prompt], max_tokens=10, sampling=[params], ignore_eos=True)[0].tokens
+    tokens = list(prompt)
+    for n, token in enumerate(got, start=1):
+        logits = plain.forward(cfg, weights, tokens)[-1].numpy()
+        logits = plain.apply_repetition_penalty(logits, tokens[-20:], 1.4)
+        want = plain.sample_token(logits, 0.9, plain.draw_key(77, n), top_p=0.95, top_k=12, min_p=0.01)
+        assert token == want, (n, token, want)
+        tokens.append(token)

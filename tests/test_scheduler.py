@@ -170,3 +170,36 @@ def test_seeds():
     for r in (seeded, free1, free2):
         s.submit(r)
     assert seeded.seed == 42 and free1.seed != free2.seed
+
+
+def test_steps_in_flight():
+    """A step may be planned while the tokens of the step before are unread: the request counts
+    its unread token, leaves out requests whose unread token is their last, and a request that
+    turns out to have ended keeps its pages until the step in flight has been read."""
+    s = Scheduler(cache(pages=64, page_size=4, requests=4), eos_token_ids=[7], max_batch_tokens=32)
+    a, b = Request("a", [1, 2, 3], max_tokens=3), Request("b", [4, 5], max_tokens=10)
+    s.submit(a)
+    s.submit(b)
+    def launch():
+        plan = s.schedule()
+        s.cache.commit(s.cache.plan_append([(e.request.cache, len(e.tokens)) for e in plan.entries]))
+        s.launched(plan)
+        return plan
+    def read(plan, tokens):                            # tokens by request id, in the plan's row order
+        return s.complete(plan, [tokens[e.request.request_id] for e in plan.entries if e.wants_logits])
+    first = launch()                                   # both prompts, logits wanted
+    assert a.inflight == b.inflight == 1 and a.fed == 3 and b.fed == 2
+    second = launch()                                  # planned before the first step is read
+    assert sorted((e.request.request_id, e.from_device) for e in second.entries) == [("a", True), ("b", True)]
+    assert a.inflight == 2 and a.remaining == 1          # the second unread token is still to be fed
+    read(first, {"a": 9, "b": 7})                    # b sampled an end token: it is in the second step already
+    assert b.finish_reason == "stop" and b.retiring and b.cache is not None and b.output == [7]
+    third = launch()                                   # a's third token will be its last: one more row, b is gone
+    assert [e.request.request_id for e in third.entries] == ["a"]
+    assert not s.has_work() and s.unsettled()          # nothing more to plan, tokens still on the way
+    read(second, {"a": 9, "b": 1})                   # b's token is dropped and b gives its pages back
+    assert b.output == [7] and b.cache is None and not b.retiring
+    read(third, {"a": 9})
+    assert a.finish_reason == "length" and a.output == [9, 9, 9] and not s.unsettled()
+    assert s.cache.free_pages() == 64 and s.cache.free_slots == 4
+    s.cache.check_invariants()
