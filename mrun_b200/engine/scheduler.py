@@ -330,6 +330,7 @@ class Scheduler:
     # ------------------------------------------------------------------ internals
     def _retire(self, request: Request) -> None:
         self.running.remove(request)
+        request.retiring = False
         if request.cache is not None:
             self.cache.release(request.cache)
             request.cache = None
