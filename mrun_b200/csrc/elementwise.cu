@@ -449,3 +449,4 @@ MRUN_API int mrun_select_tokens(int* ids, const int* previous, const int* source
     MRUN_CHECK_LAUNCH("select_tokens");
     return 0;
 }
+

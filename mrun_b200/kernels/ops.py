@@ -349,3 +349,4 @@ def select_tokens(ids: torch.Tensor, previous: torch.Tensor, source: torch.Tenso
         raise KernelError("select_tokens: one source per row is needed")
     _lib.core().call("mrun_select_tokens", _ptr(ids), _ptr(previous), _ptr(source), _c_int(ids.numel()),
                      _c_int(previous.numel()), _stream())
+
