@@ -146,10 +146,12 @@ CORE_SOURCES = ("common.cu", "elementwise.cu", "gemm_f32.cu", "gemm_skinny.cu", 
 
 def build_core() -> str:
     defines = {}
-    for knob in ("MRUN_SKINNY_WARPS", "MRUN_SKINNY_UNROLL", "MRUN_SKINNY_UNROLL_WIDE", "MRUN_SKINNY_WIDE_N"):   # tuning knobs
+    for knob in ("MRUN_SKINNY_WARPS", "MRUN_SKINNY_UNROLL", "MRUN_SKINNY_UNROLL_WIDE", "MRUN_SKINNY_WIDE_N",
+                 "MRUN_TC5_DEBUG_NO_X", "MRUN_TC5_DEBUG_NO_MMA", "MRUN_TC5_L2_PROMOTION"):   # tuning knobs
         if os.environ.get(knob):
-            defines[knob] = int(os.environ[knob])
-    tag = "_".join(f"{k[12:].lower()}{v}" for k, v in sorted(defines.items()))
+            value = os.environ[knob]
+            defines[knob] = int(value) if value.lstrip("-").isdigit() else value
+    tag = hashlib.sha256(repr(sorted(defines.items())).encode()).hexdigest()[:8] if defines else ""
     return build_library(f"mrun_core_{tag}" if tag else "mrun_core", CORE_SOURCES, defines)
 
 

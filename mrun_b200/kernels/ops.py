@@ -222,9 +222,11 @@ def _tc5_buffers(device: torch.device):
 
 
 # Measured on B200 at the Qwen3-8B shapes with 64 rows (CUDA events, captured graph): the vendor
-# GEMM 11.6 / 10.1 / 39.6 / 22.7 us for QKV / O / gate-up / down, this kernel 23.3 / 23.3 / 77.8 /
-# 39.0 us: one block per 128-row tile streams at about 40 GB/s per SM, so it needs every SM busy
-# for the whole call (a stream-K schedule) to compete.  Until then it is used on request only.
+# GEMM 11.7 / 9.9 / 39.6 / 22.9 us for QKV / O / gate-up / down and 209 us for the output head,
+# this kernel 27.9 / 28.3 / 54.8 / 40.7 / 250 us.  Its TMA stream runs at HBM speed (6.9 TB/s per
+# added byte), but a launch carries about 5 us of fixed latency (tensor-memory allocation, the
+# barrier hops from TMA to MMA to epilogue) and about 8 us of partial-tile epilogue where tiles
+# are shared between blocks: too much for products of 10 to 40 us.  It is used on request only.
 TC5_DEFAULT = os.environ.get("MRUN_TC5", "0") == "1"
 
 
@@ -236,38 +238,38 @@ def tc5_ok(x: torch.Tensor, w: torch.Tensor) -> bool:
             and w.shape[0] <= 128 * TC5_COUNTERS)
 
 
-def tc5_splits(n: int, k: int, sms: int = 148) -> int:
-    """Ranges of k per 128-row tile: enough blocks to fill the device once, each with at least
-    four 64-wide k blocks."""
-    tiles = -(-n // 128)
-    if tiles >= sms:
-        return 1
-    return max(1, min(sms // tiles, (k // 64) // 4))
+_sm_count = {}
+
+
+def sm_count(device: torch.device) -> int:
+    n = _sm_count.get(device)
+    if n is None:
+        n = _sm_count[device] = torch.cuda.get_device_properties(device).multi_processor_count
+    return n
 
 
 def gemm_tc5(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype = torch.bfloat16,
-             swiglu_rows: bool = False, splits: Optional[int] = None) -> torch.Tensor:
-    """y = x @ w.T for 1..256 rows on the tcgen05 tensor cores (TMA-fed, accumulator in tensor
-    memory).  ``swiglu_rows`` as in :func:`gemm_skinny`.  A wait inside the kernel that runs out
-    sets the status word that :func:`tc5_check` reads."""
+             swiglu_rows: bool = False, blocks: Optional[int] = None) -> torch.Tensor:
+    """y = x @ w.T for 1..256 rows on the tcgen05 tensor cores (TMA-fed, accumulators in tensor
+    memory, the work dealt evenly to ``blocks`` thread blocks, by default one per SM).
+    ``swiglu_rows`` as in :func:`gemm_skinny`.  A wait inside the kernel that runs out sets the
+    status word that :func:`tc5_check` reads."""
     _check(x, "x", torch.bfloat16, dense=False); _check(w, "w", torch.bfloat16)
     m, k = x.shape
     n = w.shape[0]
     if w.shape[1] != k:
         raise KernelError(f"gemm_tc5: x {tuple(x.shape)} vs w {tuple(w.shape)}")
-    if splits is None:
-        splits = tc5_splits(n, k)
+    if blocks is None:
+        blocks = sm_count(x.device)
     out = torch.empty((m, n // 2 if swiglu_rows else n), dtype=out_dtype, device=x.device)
     counters, status = _tc5_buffers(x.device)
     core = _lib.core()
-    partial = None
-    if splits > 1:
-        query = core._dll.mrun_gemm_tc5_scratch_floats
-        query.restype = ctypes.c_long
-        partial = torch.empty(query(_c_int(m), _c_int(n), _c_int(splits)), dtype=torch.float32, device=x.device)
+    query = core._dll.mrun_gemm_tc5_scratch_floats
+    query.restype = ctypes.c_long
+    partial = torch.empty(max(1, query(_c_int(m), _c_int(blocks))), dtype=torch.float32, device=x.device)
     core.call("mrun_gemm_tc5", _ptr(x), _ptr(w), _ptr(out), dtype_code(out_dtype), _c_int(1 if swiglu_rows else 0),
               _c_int(m), _c_int(n), _c_int(k), _c_long(x.stride(0) if m > 1 else max(k, x.stride(0))),
-              _c_long(out.shape[1]), _c_int(splits), _ptr(partial), _ptr(counters), _ptr(status), _stream())
+              _c_long(out.shape[1]), _c_int(blocks), _ptr(partial), _ptr(counters), _ptr(status), _stream())
     return out
 
 

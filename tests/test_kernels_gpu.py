@@ -176,35 +176,36 @@ def test_gemm_skinny_gated_epilogue(m, inter, k):
 
 
 @pytest.mark.parametrize("m", [1, 17, 32, 33, 64, 100, 128, 200, 256])
-@pytest.mark.parametrize("n,k,splits", [(128, 64, 1), (509, 192, 1), (6144, 4096, 3), (4096, 12288, 4), (1000, 2560, 5),
-                                        (24576, 4096, 1), (130, 128, 2)])
-def test_gemm_tc5(m, n, k, splits):
+@pytest.mark.parametrize("n,k,blocks", [(128, 64, 1), (509, 192, 5), (6144, 4096, 148), (4096, 12288, 148), (1000, 2560, 7),
+                                        (24576, 4096, 148), (130, 128, 3), (4096, 4096, 1000), (2000, 1024, 11)])
+def test_gemm_tc5(m, n, k, blocks):
     """The tcgen05 GEMM against a 32-bit product: every token tile, row counts that do not fill a
-    tile, widths that do not fill the last 128-row tile, one and several k ranges."""
+    tile, widths that do not fill the last 128-row tile, and the work dealt to one, a few, 148 and
+    more blocks than there are units of work per tile (tiles finished by one block or by several)."""
     x, w = rnd(m, k, dtype=torch.bfloat16, seed=30), rnd(n, k, dtype=torch.bfloat16, seed=31, scale=0.05)
     want = x.float() @ w.float().T
     for out_dtype, tol in ((torch.float32, 1e-4), (torch.bfloat16, 8e-3)):
-        got = ops().gemm_tc5(x, w, out_dtype=out_dtype, splits=splits)
+        got = ops().gemm_tc5(x, w, out_dtype=out_dtype, blocks=blocks)
         ops().tc5_check()
         assert got.dtype == out_dtype and got.shape == (m, n)
         assert (got.float() - want).abs().max() <= tol * want.abs().max()
-    # the same call again gives the same bits (the tile counters are back at zero, ranges add in order)
-    again = ops().gemm_tc5(x, w, out_dtype=torch.float32, splits=splits)
-    assert torch.equal(again, ops().gemm_tc5(x, w, out_dtype=torch.float32, splits=splits))
+    # the same call again gives the same bits (the tile counters are back at zero, partials add in order)
+    again = ops().gemm_tc5(x, w, out_dtype=torch.float32, blocks=blocks)
+    assert torch.equal(again, ops().gemm_tc5(x, w, out_dtype=torch.float32, blocks=blocks))
     wide = rnd(m, k + 72, dtype=torch.bfloat16, seed=32)
-    assert torch.equal(ops().gemm_tc5(wide[:, :k], w, splits=splits), ops().gemm_tc5(wide[:, :k].contiguous(), w, splits=splits))
+    assert torch.equal(ops().gemm_tc5(wide[:, :k], w, blocks=blocks), ops().gemm_tc5(wide[:, :k].contiguous(), w, blocks=blocks))
     ops().tc5_check()
 
 
-@pytest.mark.parametrize("m,inter,k,splits", [(17, 8, 64, 1), (64, 200, 128, 2), (64, 12288, 4096, 1), (130, 1024, 2560, 3)])
-def test_gemm_tc5_gated_epilogue(m, inter, k, splits):
+@pytest.mark.parametrize("m,inter,k,blocks", [(17, 8, 64, 1), (64, 200, 128, 3), (64, 12288, 4096, 148), (130, 1024, 2560, 37)])
+def test_gemm_tc5_gated_epilogue(m, inter, k, blocks):
     x = rnd(m, k, dtype=torch.bfloat16, seed=33)
     gate, up = rnd(inter, k, dtype=torch.bfloat16, seed=34, scale=0.05), rnd(inter, k, dtype=torch.bfloat16, seed=35, scale=0.05)
     w = torch.stack([gate.view(-1, 8, k), up.view(-1, 8, k)], dim=1).reshape(2 * inter, k).contiguous()
     g = (x.float() @ gate.float().T).bfloat16().float()
     u = (x.float() @ up.float().T).bfloat16().float()
     want = g * torch.sigmoid(g) * u
-    got = ops().gemm_tc5(x, w, swiglu_rows=True, splits=splits)
+    got = ops().gemm_tc5(x, w, swiglu_rows=True, blocks=blocks)
     ops().tc5_check()
     assert got.shape == (m, inter)
     assert (got.float() - want).abs().max() <= 1.2e-2 * want.abs().max()
