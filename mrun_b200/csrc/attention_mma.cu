@@ -324,6 +324,57 @@ prefill_kernel(const bf16* __restrict__ q, long q_stride, bf16* __restrict__ out
 // and sets the counter back to zero, so no second kernel runs and the result does not depend on
 // which split came last.  With one working split the output is written directly.
 // ------------------------------------------------------------------------------------------
+// What the decode kernel does itself when the step's q, k and v arrive raw from the projection:
+// per-head RMSNorm of q and k, rotation of both, and the write of the token's k and v into its
+// page (the same arithmetic, in the same order, as the stand-alone kernel that prefill uses:
+// norm, then rotation of pairs (j, j + rotary_dim / 2), v untouched).  `enabled` = 0: q is ready
+// and the cache already holds the token.
+struct FusedInput {
+    int enabled;
+    const float* q_weight;   // [D] or null: no norm
+    const float* k_weight;
+    float eps;
+    const float2* rot;       // [tokens, rotary_dim / 2] (cos, sin) or null: no rotation
+    int rotary_dim;
+    const int* slots;        // [tokens] page * page_size + offset, negative or null: nothing is written
+    bf16* k_cache;           // the pages, writable
+    bf16* v_cache;
+};
+
+// One head vector (D elements at `src`): norm with `weight` (may be null), rotation with the
+// token's table row `cs` (may be null), result as bf16 at `dst`.  One warp; `vec` holds D floats.
+__device__ __forceinline__ void norm_rotate_head(const bf16* __restrict__ src, const float* __restrict__ weight,
+                                                 float eps, const float2* __restrict__ cs, int rotary_dim,
+                                                 float* vec, bf16* dst) {
+    const int lane = threadIdx.x & 31;
+    float ss = 0.f;
+    for (int e = lane; e < D; e += 32) {
+        const float v = __bfloat162float(src[e]);
+        vec[e] = v;
+        ss += v * v;
+    }
+    if (weight) {
+        ss = mrun::warp_sum(ss);
+        const float inv = rsqrtf(ss / (float)D + eps);
+        __syncwarp();
+        for (int e = lane; e < D; e += 32) vec[e] = vec[e] * inv * weight[e];
+    }
+    __syncwarp();
+    const int half = rotary_dim >> 1;
+    if (cs) {
+        for (int j = lane; j < half; j += 32) {
+            const float x1 = vec[j], x2 = vec[j + half];
+            const float2 c = cs[j];
+            dst[j] = __float2bfloat16_rn(x1 * c.x - x2 * c.y);
+            dst[j + half] = __float2bfloat16_rn(x2 * c.x + x1 * c.y);
+        }
+        for (int e = rotary_dim + lane; e < D; e += 32) dst[e] = __float2bfloat16_rn(vec[e]);
+    } else {
+        for (int e = lane; e < D; e += 32) dst[e] = __float2bfloat16_rn(vec[e]);
+    }
+    __syncwarp();
+}
+
 #ifndef MRUN_DECODE_STAGES
 #define MRUN_DECODE_STAGES 2   // measured: three resident blocks with two tiles each beat deeper pipelines
 #endif
@@ -336,13 +387,15 @@ decode_kernel(const bf16* __restrict__ q, long q_stride, bf16* __restrict__ out,
               const int* __restrict__ block_tables, int max_blocks, const int* __restrict__ token_slot,
               const int* __restrict__ positions, float* __restrict__ part_o, float* __restrict__ part_ml,
               int* __restrict__ counters, int min_tiles, int heads, int kv_heads, int page_size,
-              int page_shift, float scale_log2, int window) {
+              int page_shift, float scale_log2, int window, const FusedInput fused) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
     bf16* q_tile = reinterpret_cast<bf16*>(smem_raw);           // [16][LD]
     bf16* k_tiles = q_tile + 16 * LD;                           // [STAGES][64][LD]
     bf16* v_tiles = k_tiles + STAGES * BLOCK_N * LD;            // [STAGES][64][LD]
     float* merge = reinterpret_cast<float*>(k_tiles);           // reused after the loop
     __shared__ int ticket_shared;
+    __shared__ float head_vec[THREADS / 32][D];                 // staging of a head vector per warp (fused input)
+    __shared__ __align__(16) bf16 new_k[D], new_v[D];           // this step's own key and value (fused input)
 
     const int tok = blockIdx.x, kvh = blockIdx.y, split = blockIdx.z, splits = gridDim.z;
     const int group = heads / kv_heads;
@@ -393,12 +446,47 @@ decode_kernel(const bf16* __restrict__ q, long q_stride, bf16* __restrict__ out,
     if (!holds_new_token) mrun::pdl_wait();
     // q with plain loads, so that the copy groups above stay one per tile; the first barrier of
     // the loop publishes it
-    for (int c = threadIdx.x; c < 16 * CHUNKS; c += THREADS) {
-        const int row = c / CHUNKS, chunk = c - row * CHUNKS;
-        uint4 value = make_uint4(0, 0, 0, 0);
-        if (row < group)
-            value = *reinterpret_cast<const uint4*>(q + (size_t)tok * q_stride + (size_t)(kvh * group + row) * D + chunk * 8);
-        *reinterpret_cast<uint4*>(q_tile + row * LD + chunk * 8) = value;
+    const bool owns_new_token = fused.enabled && last_block == b1;
+    if (!fused.enabled) {
+        for (int c = threadIdx.x; c < 16 * CHUNKS; c += THREADS) {
+            const int row = c / CHUNKS, chunk = c - row * CHUNKS;
+            uint4 value = make_uint4(0, 0, 0, 0);
+            if (row < group)
+                value = *reinterpret_cast<const uint4*>(q + (size_t)tok * q_stride + (size_t)(kvh * group + row) * D + chunk * 8);
+            *reinterpret_cast<uint4*>(q_tile + row * LD + chunk * 8) = value;
+        }
+    } else {
+        // q, k and v arrive raw: [q heads | k heads | v heads] of D elements each in the token's row
+        const bf16* token_row = q + (size_t)tok * q_stride;
+        const float2* cs = fused.rot ? fused.rot + (size_t)tok * (fused.rotary_dim >> 1) : nullptr;
+        for (int row = warp; row < 16; row += THREADS / 32) {
+            if (row < group)
+                norm_rotate_head(token_row + (size_t)(kvh * group + row) * D, fused.q_weight, fused.eps, cs,
+                                 fused.rotary_dim, head_vec[warp], q_tile + row * LD);
+            else
+                for (int e = lane; e < D; e += 32) q_tile[row * LD + e] = __float2bfloat16_rn(0.f);
+        }
+        if (owns_new_token) {
+            // the split that holds the last tile makes the token's own key and value: into the page
+            // for later steps, and into shared memory for this one
+            if (warp == 0)
+                norm_rotate_head(token_row + (size_t)(heads + kvh) * D, fused.k_weight, fused.eps, cs, fused.rotary_dim,
+                                 head_vec[0], new_k);
+            if (warp == 1)
+                for (int e = lane; e < D; e += 32) new_v[e] = token_row[(size_t)(heads + kv_heads + kvh) * D + e];
+            __syncthreads();
+            const int slot = fused.slots ? fused.slots[tok] : -1;
+            if (slot >= 0) {
+                const int page = slot / page_size, off = slot - page * page_size;
+                const size_t at = (((size_t)page * kv_heads + kvh) * page_size + off) * D;
+                for (int c = threadIdx.x; c < 2 * CHUNKS; c += THREADS) {
+                    const bool is_v = c >= CHUNKS;
+                    const int chunk = is_v ? c - CHUNKS : c;
+                    *reinterpret_cast<uint4*>((is_v ? fused.v_cache : fused.k_cache) + at + chunk * 8) =
+                        *reinterpret_cast<const uint4*>((is_v ? new_v : new_k) + chunk * 8);
+                }
+            }
+        }
     }
 
     int row_pos[2], row_lo[2];
@@ -421,6 +509,17 @@ decode_kernel(const bf16* __restrict__ q, long q_stride, bf16* __restrict__ out,
         cp_async_commit();
         const int stage = it % STAGES;
         const int key_base = block * BLOCK_N;
+        if (owns_new_token && block == b1) {
+            // the page row of this step's token was not written when the tile was requested
+            const int r = pos - key_base;
+            for (int c = threadIdx.x; c < 2 * CHUNKS; c += THREADS) {
+                const bool is_v = c >= CHUNKS;
+                const int chunk = is_v ? c - CHUNKS : c;
+                *reinterpret_cast<uint4*>((is_v ? v_tiles : k_tiles) + (stage * BLOCK_N + r) * LD + chunk * 8) =
+                    *reinterpret_cast<const uint4*>((is_v ? new_v : new_k) + chunk * 8);
+            }
+            __syncthreads();
+        }
         // warp w takes keys 16w .. 16w+15 of the tile
         if (key_base + warp * 16 <= pos && key_base + warp * 16 + 15 >= lo)
             attend_tile<16>(q_tile, k_tiles + stage * BLOCK_N * LD, v_tiles + stage * BLOCK_N * LD, warp * 16,
@@ -558,15 +657,28 @@ MRUN_API int mrun_attn_prefill(const void* q, long q_stride, void* out, const vo
 // are scratch of tokens * heads * splits * (D and 2) floats; counters holds tokens * kv_heads
 // ints that are zero before the call and zero again after it.  All three may be null when
 // splits == 1.  Calls that share scratch must not overlap on the device.
-MRUN_API int mrun_attn_decode(const void* q, long q_stride, void* out, const void* k_cache, const void* v_cache,
+//
+// fused != 0: `q` is the projection's raw output, rows of [heads | kv_heads | kv_heads] x D (q, k, v);
+// the kernel norms q and k with q_weight / k_weight (null: no norm) and eps, rotates them with
+// rot[token] (null: no rotation), writes the token's k and v to cache slot slots[token] (null or
+// negative: no write) and attends over the cache plus that token.  fused == 0: q is ready and the
+// cache holds the token already; the remaining fused arguments are ignored.
+MRUN_API int mrun_attn_decode(const void* q, long q_stride, void* out, void* k_cache, void* v_cache,
                               const int* block_tables, int max_blocks, const int* token_slot,
                               const int* positions, int tokens, float* part_o, float* part_ml, int* counters,
-                              int splits, int min_tiles, int heads, int kv_heads, int head_dim, int page_size, float scale,
-                              int window, cudaStream_t stream) {
+                              int splits, int min_tiles, int heads, int kv_heads, int head_dim, int page_size,
+                              float scale, int window, int fused, const float* q_weight, const float* k_weight,
+                              float eps, const float* rot, int rotary_dim, const int* slots, cudaStream_t stream) {
     if (int rc = check_common("attn_decode", heads, kv_heads, head_dim, page_size, max_blocks, window, 16)) return rc;
     MRUN_REQUIRE(tokens >= 0 && splits >= 1 && splits <= 65535 && min_tiles >= 1,
                  "attn_decode: tokens=%d splits=%d min_tiles=%d", tokens, splits, min_tiles);
     MRUN_REQUIRE(splits == 1 || (part_o && part_ml && counters), "attn_decode: %d splits need scratch memory", splits);
+    MRUN_REQUIRE(!fused || (rotary_dim >= 0 && rotary_dim <= head_dim && rotary_dim % 2 == 0),
+                 "attn_decode: rotary_dim=%d must be even and at most head_dim=%d", rotary_dim, head_dim);
+    MRUN_REQUIRE(!fused || (q_weight == nullptr) == (k_weight == nullptr),
+                 "attn_decode: q and k norm weights come together");
+    MRUN_REQUIRE(!fused || q_stride >= (long)(heads + 2 * kv_heads) * head_dim,
+                 "attn_decode: the raw rows must hold q, k and v (stride %ld)", q_stride);
     if (tokens == 0) return 0;
     static bool configured = false;
     if (!configured) {
@@ -574,10 +686,22 @@ MRUN_API int mrun_attn_decode(const void* q, long q_stride, void* out, const voi
                                              (int)DECODE_SMEM), "attn_decode");
         configured = true;
     }
+    FusedInput in = {};
+    if (fused) {
+        in.enabled = 1;
+        in.q_weight = q_weight;
+        in.k_weight = k_weight;
+        in.eps = eps;
+        in.rot = (const float2*)rot;
+        in.rotary_dim = rot ? rotary_dim : 0;
+        in.slots = slots;
+        in.k_cache = (bf16*)k_cache;
+        in.v_cache = (bf16*)v_cache;
+    }
     MRUN_CHECK_CUDA(mrun::launch_pdl(MRUN_PDL_ATTENTION, decode_kernel, dim3(tokens, kv_heads, splits), dim3(THREADS), DECODE_SMEM, stream,
                                      (const bf16*)q, q_stride, (bf16*)out, (const bf16*)k_cache, (const bf16*)v_cache,
                                      block_tables, max_blocks, token_slot, positions, part_o, part_ml, counters,
-                                     min_tiles, heads, kv_heads, page_size, shift_of(page_size), scale * LOG2E, window),
+                                     min_tiles, heads, kv_heads, page_size, shift_of(page_size), scale * LOG2E, window, in),
                     "attn_decode");
     return 0;
 }
@@ -660,7 +784,7 @@ MRUN_API int mrun_attn_decode_static(const void* q, long q_stride, void* out, co
     decode_kernel<<<dim3(tokens, kv_heads, splits), THREADS, DECODE_SMEM, stream>>>(
         (const bf16*)q, q_stride, (bf16*)out, (const bf16*)k_cache, (const bf16*)v_cache, block_tables, max_blocks,
         token_slot, positions, part_o, part_ml, counters, min_tiles, heads, kv_heads, page_size, shift_of(page_size),
-        scale * LOG2E, window);
+        scale * LOG2E, window, FusedInput{});
     MRUN_CHECK_LAUNCH("attn_decode_static");
     return 0;
 }

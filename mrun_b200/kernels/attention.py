@@ -85,10 +85,19 @@ def prefill_tiles(ctx, tokens_per_tile: int):
     return tiles
 
 
+def decode_fuses_input(ctx, dtype: torch.dtype, heads: int, kv_heads: int, head_dim: int) -> bool:
+    """Whether this step's attention takes q, k and v raw and norms, rotates and stores them itself
+    (every segment a single token, bfloat16, a group that the split-key kernel takes)."""
+    ratio = heads // kv_heads
+    return ctx.all_decode and ratio <= 16 and supports_tensor_cores(dtype, head_dim, ratio)
+
+
 def paged_attention(q: torch.Tensor, q_stride: int, out: torch.Tensor, cache, group, ctx,
-                    heads: int, scale: float, window: int) -> torch.Tensor:
+                    heads: int, scale: float, window: int, raw=None) -> torch.Tensor:
     """``q``: the step's queries (row t at ``q_stride * t``, heads contiguous); ``cache``: the
-    schedule entry's pages; ``group``: the step's view of the cache's group."""
+    schedule entry's pages; ``group``: the step's view of the cache's group.  ``raw``, only where
+    :func:`decode_fuses_input` holds: ``(q_weight, k_weight, eps, rot, rotary_dim, slots)`` for a
+    ``q`` that is the projection's raw [q | k | v] rows."""
     pages, kv_heads, page_size, head_dim = cache.k.shape
     ratio = heads // kv_heads
     if not supports_tensor_cores(q.dtype, head_dim, ratio):
@@ -107,9 +116,17 @@ def paged_attention(q: torch.Tensor, q_stride: int, out: torch.Tensor, cache, gr
             part_o = torch.empty((tokens, heads, splits, head_dim), dtype=torch.float32, device=q.device)
             part_ml = torch.empty((tokens, heads, splits, 2), dtype=torch.float32, device=q.device)
             counters = _split_counters(q.device)
+        fused = (_c_int(0), _ptr(None), _ptr(None), _c_float(0.0), _ptr(None), _c_int(0), _ptr(None))
+        if raw is not None:
+            q_weight, k_weight, eps, rot, rotary_dim, slots = raw
+            fused = (_c_int(1), _ptr(q_weight), _ptr(k_weight), _c_float(eps), _ptr(rot), _c_int(rotary_dim),
+                     _ptr(slots))
         library.call("mrun_attn_decode", _ptr(q), _c_long(q_stride), _ptr(out), *common, _c_int(tokens),
-                     _ptr(part_o), _ptr(part_ml), _ptr(counters), _c_int(splits), _c_int(min_tiles), *tail)
+                     _ptr(part_o), _ptr(part_ml), _ptr(counters), _c_int(splits), _c_int(min_tiles), *tail[:-1],
+                     *fused, tail[-1])
         return out
+    if raw is not None:
+        raise ValueError("raw q, k, v rows are taken by the decode kernel only")
     first, count, n_tiles = prefill_tiles(ctx, 64 // ratio)
     if tokens > ctx.real_tokens:
         out[ctx.real_tokens:].zero_()

@@ -13,7 +13,7 @@ import torch
 from ..cache.needs import PagedKV
 from ..config.spec import AttentionSpec, TensorSpec
 from ..kernels import ops
-from ..kernels.attention import paged_attention, supports_tensor_cores
+from ..kernels.attention import decode_fuses_input, paged_attention, supports_tensor_cores
 from .base import NORMS, POSITIONS, Runtime, register_mixer
 
 
@@ -68,10 +68,14 @@ class Attention:
         qkv = ops.linear(x, self.wqkv)
         rot = self.position.rotation(ctx) if self.position is not None else None
         rotary_dim = self.position.rotary_dim if self.position is not None else 0
-        ops.qk_norm_rope_cache(qkv, s.heads, s.kv_heads, s.head_dim, self.q_weight, self.k_weight,
-                               self.eps, rot, rotary_dim,
-                               group.slot_mapping if cache.writable else None,
-                               cache.k, cache.v, self.runtime.page_size)
+        slots = group.slot_mapping if cache.writable else None
         out = torch.empty((x.shape[0], s.heads * s.head_dim), dtype=x.dtype, device=x.device)
-        paged_attention(qkv, qkv.shape[1], out, cache, group, ctx, s.heads, s.softmax_scale, s.window or 0)
+        if decode_fuses_input(ctx, x.dtype, s.heads, s.kv_heads, s.head_dim):
+            # a pure decode step: the attention kernel norms, rotates and stores q, k, v itself
+            paged_attention(qkv, qkv.shape[1], out, cache, group, ctx, s.heads, s.softmax_scale, s.window or 0,
+                            raw=(self.q_weight, self.k_weight, self.eps, rot, rotary_dim, slots))
+        else:
+            ops.qk_norm_rope_cache(qkv, s.heads, s.kv_heads, s.head_dim, self.q_weight, self.k_weight,
+                                   self.eps, rot, rotary_dim, slots, cache.k, cache.v, self.runtime.page_size)
+            paged_attention(qkv, qkv.shape[1], out, cache, group, ctx, s.heads, s.softmax_scale, s.window or 0)
         return ops.linear(out, self.wo)

@@ -153,7 +153,8 @@ def test_decode_splits_of_every_kind(splits, min_tiles):
             "mrun_attn_decode", _ptr(case.qd), _c_long(case.qd.stride(0)), _ptr(out), _ptr(case.kd), _ptr(case.vd),
             _ptr(case.table), _c_int(case.group.max_blocks), _ptr(case.ctx.token_slot), _ptr(case.ctx.positions),
             _c_int(n), _ptr(part_o), _ptr(part_ml), _ptr(counters), _c_int(splits), _c_int(min_tiles), _c_int(heads),
-            _c_int(kv_heads), _c_int(head_dim), _c_int(page_size), _c_float(scale), _c_int(0), _stream())
+            _c_int(kv_heads), _c_int(head_dim), _c_int(page_size), _c_float(scale), _c_int(0),
+            _c_int(0), _ptr(None), _ptr(None), _c_float(0.0), _ptr(None), _c_int(0), _ptr(None), _stream())
         got = out.float().cpu()
         assert (got - want).abs().max() <= 2e-2 * want.abs().max()
         assert int(counters.abs().sum()) == 0

@@ -86,7 +86,7 @@ def test_rotary_part():
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("name", sorted(TINY))
-@pytest.mark.parametrize("chunks", [None, [5, 2, 30, 1, 12]])
+@pytest.mark.parametrize("chunks", [None, [5, 2, 30, 1, 12], [11] + [1] * 39, [1] * 50])
 def test_attention_part(dtype, name, chunks):
     from mrun_b200.parts import MIXERS
     from mrun_b200.parts.base import local
@@ -95,7 +95,7 @@ def test_attention_part(dtype, name, chunks):
     spec = config.to_spec().layers[0].mixer
     prefix = "model.layers.0.self_attn"
     mixer = MIXERS.build(spec, local(tensors, prefix), rt)
-    L = 50
+    L = 50                                              # every list of chunks adds up to it
     h = torch.randn(L, config.hidden_size).to(torch.bfloat16)
     want = plain.attention_block(h.float(), w, prefix, config.to_dict(), torch.arange(L))
     got = torch.empty(L, config.hidden_size)

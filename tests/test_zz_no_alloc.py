@@ -31,8 +31,10 @@ def call_decode(dll, name, case, out, splits, min_tiles, scratch=()):
     head = (_ptr(case.qd), _c_long(case.qd.stride(0)), _ptr(out), _ptr(case.kd), _ptr(case.vd), _ptr(case.table),
             _c_int(case.group.max_blocks), _ptr(case.ctx.token_slot), _ptr(case.ctx.positions), _c_int(n))
     tail = (_c_int(splits), _c_int(min_tiles), _c_int(case.heads), _c_int(case.kv_heads), _c_int(case.head_dim),
-            _c_int(case.page_size), _c_float(case.head_dim ** -0.5), _c_int(case.window), _stream())
-    return fn(*head, *[_ptr(s) for s in scratch], *tail)
+            _c_int(case.page_size), _c_float(case.head_dim ** -0.5), _c_int(case.window))
+    # the ordinary entry point also takes the description of raw q, k, v rows; here q is ready
+    ready = (_c_int(0), _ptr(None), _ptr(None), _c_float(0.0), _ptr(None), _c_int(0), _ptr(None)) if scratch else ()
+    return fn(*head, *[_ptr(s) for s in scratch], *tail, *ready, _stream())
 
 
 @pytest.mark.parametrize("head_dim,splits,min_tiles,window", [(64, 5, 1, 0), (128, 16, 2, 0), (32, 3, 1, 100)])
