@@ -6,10 +6,11 @@
 //  * prefill: one block per (tile of query tokens, kv head).  The tile's rows are (token, query
 //    head of the kv head's group) pairs, 64 rows, so a key/value tile read once serves the whole
 //    group.  Keys are consumed 64 at a time in position order with an online softmax.
-//  * decode: one block per (token, kv head, split of the keys).  The rows are the group's query
-//    heads of one token (at most 16); the four warps take different 16-key slices of each
-//    64-key tile and are merged at the end; the split that finishes last merges all splits
-//    through scratch memory (32-bit partial outputs with their running max and sum).
+//  * decode: the 64-key tiles of all (token, kv head) pairs are dealt evenly to the blocks.  The
+//    rows are the group's query heads of one token (at most 16); the four warps take different
+//    16-key slices of each tile and are merged at the end; a pair whose tiles fell to several
+//    blocks is merged by the block that finishes last, through scratch memory (32-bit partial
+//    outputs with their running max and sum).
 //
 // Both read keys and values from the pages (cache[page, kv_head, offset, :]) through the block
 // table of the token's state slot.  A token at position p sees keys lo..p, lo = 0 or
@@ -315,14 +316,18 @@ prefill_kernel(const bf16* __restrict__ q, long q_stride, bf16* __restrict__ out
 }
 
 // ------------------------------------------------------------------------------------------
-// Decode: 16 rows = the group's heads of one token; grid (tokens, kv_heads, splits).
+// Decode: 16 rows = the group's heads of one token.
 //
-// The token's key tiles are dealt to the splits in runs of `per` tiles, at least `min_tiles`, so a
-// short context uses fewer splits than the grid offers; splits beyond the last run leave at once.  Every working split writes its unnormalised 32-bit result and its running
-// (max, sum) to scratch: part_o [tokens, heads, splits, D], part_ml [tokens, heads, splits, 2].
-// The split that arrives last at the (token, kv head) counter merges all of them in split order
-// and sets the counter back to zero, so no second kernel runs and the result does not depend on
-// which split came last.  With one working split the output is written directly.
+// The work of a step is the list of 64-key tiles of every (token, kv head) pair, numbered kv head
+// by kv head and token by token.  Block b takes tiles [b * per, (b + 1) * per): every block streams
+// the same number of keys whatever the mix of context lengths, and a step of more pairs than the
+// device holds blocks does not run as one full round of blocks and a nearly empty one.  A
+// block's range is a sequence of segments, each a run of tiles of one pair; only its first and
+// its last segment can be part of a pair.  A partial segment writes its unnormalised 32-bit
+// result and its running (max, sum) to scratch (slot 0 if it is the block's first segment, else
+// slot 1): part_o [blocks, 2, 16, D], part_ml [blocks, 2, 16, 2].  The block that arrives last at
+// the pair's counter merges the pair's pieces in block order and sets the counter back to zero,
+// so no second kernel runs and the result does not depend on which block came last.
 // ------------------------------------------------------------------------------------------
 // What the decode kernel does itself when the step's q, k and v arrive raw from the projection:
 // per-head RMSNorm of q and k, rotation of both, and the write of the token's k and v into its
@@ -381,225 +386,341 @@ __device__ __forceinline__ void norm_rotate_head(const bf16* __restrict__ src, c
 constexpr int STAGES = MRUN_DECODE_STAGES;
 static_assert(STAGES >= 2 && STAGES <= 4, "2 to 4 key/value tiles in flight");
 
+// The plan of a decode step: tile_prefix[t] = number of 64-key tiles of tokens 0 .. t-1 (a
+// padding token has none), so tile_prefix[tokens] is the step's total per kv head.  One block.
+__global__ void decode_plan_kernel(const int* __restrict__ positions, int tokens, int window,
+                                   int* __restrict__ tile_prefix) {
+    __shared__ int carry;
+    __shared__ int scan[1024];
+    if (threadIdx.x == 0) {
+        carry = 0;
+        tile_prefix[0] = 0;
+    }
+    __syncthreads();
+    for (int base = 0; base < tokens; base += 1024) {
+        const int t = base + threadIdx.x;
+        int n = 0;
+        if (t < tokens) {
+            const int pos = positions[t];
+            if (pos >= 0) {
+                const int lo = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
+                n = pos / BLOCK_N - lo / BLOCK_N + 1;
+            }
+        }
+        scan[threadIdx.x] = n;
+        __syncthreads();
+        for (int step = 1; step < 1024; step <<= 1) {            // inclusive scan of the chunk
+            const int add = threadIdx.x >= step ? scan[threadIdx.x - step] : 0;
+            __syncthreads();
+            scan[threadIdx.x] += add;
+            __syncthreads();
+        }
+        if (t < tokens) tile_prefix[t + 1] = carry + scan[threadIdx.x];
+        __syncthreads();
+        if (threadIdx.x == 1023) carry += scan[1023];
+        __syncthreads();
+    }
+}
+
+// What block b of the decode kernel starts with, so that it needs one load and no search:
+// {first tile, end tile, kv head, token} and {tiles per kv head, tiles per block, splits per pair, -}.
+//
+// Two ways of dealing the tiles.  splits == 0, for steps with at least as many (token, kv head)
+// pairs as blocks: block b takes tiles [b * per, (b + 1) * per) of the flat list, across pairs.
+// splits > 0, for steps with few pairs: every pair is cut into up to `splits` equal runs of at
+// least min_tiles tiles, one block each (blocks = pairs * splits), so that no block pays the
+// start-up of two pairs for a handful of tiles.
+__global__ void decode_assign_kernel(const int* __restrict__ tile_prefix, int tokens, int kv_heads, int blocks,
+                                     int min_tiles, int splits, int4* __restrict__ assignment) {
+    const int b = blockIdx.x * blockDim.x + threadIdx.x;
+    if (b >= blocks) return;
+    const int tiles_per_head = tile_prefix[tokens];
+    const int total = tiles_per_head * kv_heads;
+    int u0 = 0, u1 = 0, kvh = 0, tok = 0, per = 0;
+    if (splits > 0) {
+        const int pair = b / splits, s = b - pair * splits;
+        kvh = pair / tokens;
+        tok = pair - kvh * tokens;
+        if (kvh < kv_heads) {
+            const int pair_tiles = tile_prefix[tok + 1] - tile_prefix[tok];
+            per = max((pair_tiles + splits - 1) / splits, min_tiles);
+            const int j0 = s * per;
+            if (j0 < pair_tiles) {
+                u0 = kvh * tiles_per_head + tile_prefix[tok] + j0;
+                u1 = u0 + min(per, pair_tiles - j0);
+            }
+        }
+    } else {
+        per = max((total + blocks - 1) / blocks, min_tiles);
+        u0 = min(total, b * per);
+        u1 = min(total, u0 + per);
+        if (u0 < u1) {
+            kvh = u0 / tiles_per_head;
+            const int r = u0 - kvh * tiles_per_head;
+            int lo_t = 0, hi_t = tokens - 1;                      // the last token t with prefix[t] <= r
+            while (lo_t < hi_t) {
+                const int mid = (lo_t + hi_t + 1) >> 1;
+                if (tile_prefix[mid] <= r) lo_t = mid; else hi_t = mid - 1;
+            }
+            tok = lo_t;
+        }
+    }
+    assignment[2 * b] = make_int4(u0, u1, kvh, tok);
+    assignment[2 * b + 1] = make_int4(tiles_per_head, per, splits, 0);
+}
+
+// grid: `blocks` blocks, the number the plan was made for.
+// part_o: [blocks][2][16][D] floats, part_ml: [blocks][2][16][2] floats, counters: [tokens * kv_heads]
+// ints, zero before the call and zero again after it.
 __global__ void __launch_bounds__(THREADS)
 decode_kernel(const bf16* __restrict__ q, long q_stride, bf16* __restrict__ out,
               const bf16* __restrict__ k_cache, const bf16* __restrict__ v_cache,
               const int* __restrict__ block_tables, int max_blocks, const int* __restrict__ token_slot,
-              const int* __restrict__ positions, float* __restrict__ part_o, float* __restrict__ part_ml,
-              int* __restrict__ counters, int min_tiles, int heads, int kv_heads, int page_size,
+              const int* __restrict__ positions, const int* __restrict__ tile_prefix,
+              const int4* __restrict__ assignment, int tokens, float* __restrict__ part_o,
+              float* __restrict__ part_ml, int* __restrict__ counters, int heads, int kv_heads, int page_size,
               int page_shift, float scale_log2, int window, const FusedInput fused) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
     bf16* q_tile = reinterpret_cast<bf16*>(smem_raw);           // [16][LD]
     bf16* k_tiles = q_tile + 16 * LD;                           // [STAGES][64][LD]
     bf16* v_tiles = k_tiles + STAGES * BLOCK_N * LD;            // [STAGES][64][LD]
-    float* merge = reinterpret_cast<float*>(k_tiles);           // reused after the loop
+    float* merge = reinterpret_cast<float*>(k_tiles);           // reused after a segment's loop
     __shared__ int ticket_shared;
-    __shared__ float head_vec[THREADS / 32][D];                 // staging of a head vector per warp (fused input)
     __shared__ __align__(16) bf16 new_k[D], new_v[D];           // this step's own key and value (fused input)
+    // Staging of a head vector per warp (fused input).  It lives in the value tile of the last
+    // stage, which no copy targets before the first tile of a segment has been consumed; shared
+    // memory is what limits the blocks per SM, and a static array here costs one of three.
+    float (*head_vec)[D] = reinterpret_cast<float (*)[D]>(v_tiles + (STAGES - 1) * BLOCK_N * LD);
+    constexpr int MS = D + 2;
 
-    const int tok = blockIdx.x, kvh = blockIdx.y, split = blockIdx.z, splits = gridDim.z;
+    const int block_id = blockIdx.x, n_blocks_grid = gridDim.x;
     const int group = heads / kv_heads;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    // Positions, slots and block tables are written at the start of a step, not by the kernel
-    // before this one, so they are read before waiting for it.
+    // Positions, slots, block tables and the plan are written at the start of a step, not by the
+    // kernel before this one, so they are read before waiting for it.
     mrun::pdl_launch_dependents();
-    const int pos = positions[tok];
+    const int4 mine = assignment[2 * block_id], shape = assignment[2 * block_id + 1];
+    int u = mine.x;
+    const int u_end = mine.y;
+    const int tiles_per_head = shape.x, per = shape.y, splits = shape.z;
+    mrun::pdl_wait();
+    const int* prefix = tile_prefix;
+    int kvh = mine.z, tok = mine.w;                             // the pair of the block's first tile
 
-    if (pos < 0) {  // padding row: zeros, written by the first split
-        mrun::pdl_wait();
-        if (split == 0)
-            for (int i = threadIdx.x; i < group * D; i += THREADS)
-                out[((size_t)tok * heads + kvh * group) * D + i] = __float2bfloat16_rn(0.f);
-        return;
-    }
-    const Paging pg{block_tables + (size_t)token_slot[tok] * max_blocks, kv_heads, kvh, page_size, page_shift};
-    const int lo = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
-    const int b0 = lo / BLOCK_N, b1 = pos / BLOCK_N;
-    const int n_blocks = b1 - b0 + 1;
-    const int per = max((n_blocks + splits - 1) / splits, min_tiles);
-    const int n_active = (n_blocks + per - 1) / per;
-    if (split >= n_active) {
-        mrun::pdl_wait();
-        return;
-    }
-    const int first_block = b0 + split * per;
-    const int last_block = min(b1, first_block + per - 1);
+    // padding rows come out as zeros
+    for (int t = block_id; t < tokens; t += n_blocks_grid)
+        if (positions[t] < 0)
+            for (int i = threadIdx.x; i < heads * D; i += THREADS) out[(size_t)t * heads * D + i] = __float2bfloat16_rn(0.f);
 
-    float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
-    float o[D / 8][4];
-#pragma unroll
-    for (int dt = 0; dt < D / 8; ++dt) o[dt][0] = o[dt][1] = o[dt][2] = o[dt][3] = 0.f;
-
-    // The keys and values of earlier positions were written by earlier steps; only the tile that
-    // holds this step's own token (the last tile of the last run) and q come from the kernels
-    // just before.  Runs that do not hold that tile start their first loads before the wait.
-    const bool holds_new_token = last_block == b1 && first_block + (STAGES - 2) >= b1;
-    if (holds_new_token) mrun::pdl_wait();
-    // prologue: STAGES - 1 tiles in flight (an empty group keeps the counting uniform)
-#pragma unroll
-    for (int s = 0; s < STAGES - 1; ++s) {
-        if (first_block + s <= last_block)
-            load_kv_tiles(k_tiles + s * BLOCK_N * LD, v_tiles + s * BLOCK_N * LD, k_cache, v_cache, pg,
-                          (first_block + s) * BLOCK_N, lo, pos);
-        cp_async_commit();
-    }
-    if (!holds_new_token) mrun::pdl_wait();
-    // q with plain loads, so that the copy groups above stay one per tile; the first barrier of
-    // the loop publishes it
-    const bool owns_new_token = fused.enabled && last_block == b1;
-    if (!fused.enabled) {
-        for (int c = threadIdx.x; c < 16 * CHUNKS; c += THREADS) {
-            const int row = c / CHUNKS, chunk = c - row * CHUNKS;
-            uint4 value = make_uint4(0, 0, 0, 0);
-            if (row < group)
-                value = *reinterpret_cast<const uint4*>(q + (size_t)tok * q_stride + (size_t)(kvh * group + row) * D + chunk * 8);
-            *reinterpret_cast<uint4*>(q_tile + row * LD + chunk * 8) = value;
+    for (int seg = 0; u < u_end; ++seg) {
+        // ---------------------------------------------------------------- which pair, which tiles
+        // after the first segment the next pair follows: the next token with tiles, or the first
+        // one of the next kv head
+        if (seg > 0) {
+            ++tok;
+            if (u - kvh * tiles_per_head >= tiles_per_head) {
+                ++kvh;
+                tok = 0;
+            }
         }
-    } else {
-        // q, k and v arrive raw: [q heads | k heads | v heads] of D elements each in the token's row
-        const bf16* token_row = q + (size_t)tok * q_stride;
-        const float2* cs = fused.rot ? fused.rot + (size_t)tok * (fused.rotary_dim >> 1) : nullptr;
-        for (int row = warp; row < 16; row += THREADS / 32) {
-            if (row < group)
-                norm_rotate_head(token_row + (size_t)(kvh * group + row) * D, fused.q_weight, fused.eps, cs,
-                                 fused.rotary_dim, head_vec[warp], q_tile + row * LD);
-            else
-                for (int e = lane; e < D; e += 32) q_tile[row * LD + e] = __float2bfloat16_rn(0.f);
+        const int r = u - kvh * tiles_per_head;
+        while (prefix[tok + 1] <= r) ++tok;                      // skip tokens without tiles (padding)
+        const int pair_tiles = prefix[tok + 1] - prefix[tok];
+        const int j0 = r - prefix[tok];
+        const int len = min(u_end - u, pair_tiles - j0);
+        const bool complete = j0 == 0 && len == pair_tiles;
+        const int pair_start = kvh * tiles_per_head + prefix[tok];
+
+        const int pos = positions[tok];
+        const Paging pg{block_tables + (size_t)token_slot[tok] * max_blocks, kv_heads, kvh, page_size, page_shift};
+        const int lo = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
+        const int b1 = pos / BLOCK_N;
+        const int first_block = lo / BLOCK_N + j0;
+        const int last_block = first_block + len - 1;
+
+        float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
+        float o[D / 8][4];
+#pragma unroll
+        for (int dt = 0; dt < D / 8; ++dt) o[dt][0] = o[dt][1] = o[dt][2] = o[dt][3] = 0.f;
+
+        // prologue: STAGES - 1 tiles in flight (an empty group keeps the counting uniform)
+#pragma unroll
+        for (int s = 0; s < STAGES - 1; ++s) {
+            if (first_block + s <= last_block)
+                load_kv_tiles(k_tiles + s * BLOCK_N * LD, v_tiles + s * BLOCK_N * LD, k_cache, v_cache, pg,
+                              (first_block + s) * BLOCK_N, lo, pos);
+            cp_async_commit();
         }
-        if (owns_new_token) {
-            // the split that holds the last tile makes the token's own key and value: into the page
-            // for later steps, and into shared memory for this one
-            if (warp == 0)
-                norm_rotate_head(token_row + (size_t)(heads + kvh) * D, fused.k_weight, fused.eps, cs, fused.rotary_dim,
-                                 head_vec[0], new_k);
-            if (warp == 1)
-                for (int e = lane; e < D; e += 32) new_v[e] = token_row[(size_t)(heads + kv_heads + kvh) * D + e];
-            __syncthreads();
-            const int slot = fused.slots ? fused.slots[tok] : -1;
-            if (slot >= 0) {
-                const int page = slot / page_size, off = slot - page * page_size;
-                const size_t at = (((size_t)page * kv_heads + kvh) * page_size + off) * D;
-                for (int c = threadIdx.x; c < 2 * CHUNKS; c += THREADS) {
-                    const bool is_v = c >= CHUNKS;
-                    const int chunk = is_v ? c - CHUNKS : c;
-                    *reinterpret_cast<uint4*>((is_v ? fused.v_cache : fused.k_cache) + at + chunk * 8) =
-                        *reinterpret_cast<const uint4*>((is_v ? new_v : new_k) + chunk * 8);
+        // q with plain loads, so that the copy groups above stay one per tile; the first barrier of
+        // the loop publishes it
+        const bool owns_new_token = fused.enabled && last_block == b1;
+        if (!fused.enabled) {
+            for (int c = threadIdx.x; c < 16 * CHUNKS; c += THREADS) {
+                const int row = c / CHUNKS, chunk = c - row * CHUNKS;
+                uint4 value = make_uint4(0, 0, 0, 0);
+                if (row < group)
+                    value = *reinterpret_cast<const uint4*>(q + (size_t)tok * q_stride + (size_t)(kvh * group + row) * D + chunk * 8);
+                *reinterpret_cast<uint4*>(q_tile + row * LD + chunk * 8) = value;
+            }
+        } else {
+            // q, k and v arrive raw: [q heads | k heads | v heads] of D elements each in the token's row
+            const bf16* token_row = q + (size_t)tok * q_stride;
+            const float2* cs = fused.rot ? fused.rot + (size_t)tok * (fused.rotary_dim >> 1) : nullptr;
+            for (int row = warp; row < 16; row += THREADS / 32) {
+                if (row < group)
+                    norm_rotate_head(token_row + (size_t)(kvh * group + row) * D, fused.q_weight, fused.eps, cs,
+                                     fused.rotary_dim, head_vec[warp], q_tile + row * LD);
+                else
+                    for (int e = lane; e < D; e += 32) q_tile[row * LD + e] = __float2bfloat16_rn(0.f);
+            }
+            if (owns_new_token) {
+                // the block that holds the pair's last tile makes the token's own key and value: into
+                // the page for later steps, and into shared memory for this one
+                if (warp == 0)
+                    norm_rotate_head(token_row + (size_t)(heads + kvh) * D, fused.k_weight, fused.eps, cs,
+                                     fused.rotary_dim, head_vec[0], new_k);
+                if (warp == 1)
+                    for (int e = lane; e < D; e += 32) new_v[e] = token_row[(size_t)(heads + kv_heads + kvh) * D + e];
+                __syncthreads();
+                const int slot = fused.slots ? fused.slots[tok] : -1;
+                if (slot >= 0) {
+                    const int page = slot / page_size, off = slot - page * page_size;
+                    const size_t at = (((size_t)page * kv_heads + kvh) * page_size + off) * D;
+                    for (int c = threadIdx.x; c < 2 * CHUNKS; c += THREADS) {
+                        const bool is_v = c >= CHUNKS;
+                        const int chunk = is_v ? c - CHUNKS : c;
+                        *reinterpret_cast<uint4*>((is_v ? fused.v_cache : fused.k_cache) + at + chunk * 8) =
+                            *reinterpret_cast<const uint4*>((is_v ? new_v : new_k) + chunk * 8);
+                    }
                 }
             }
         }
-    }
 
-    int row_pos[2], row_lo[2];
+        int row_pos[2], row_lo[2];
 #pragma unroll
-    for (int r = 0; r < 2; ++r) {
-        const int row = (lane >> 2) + r * 8;
-        row_pos[r] = row < group ? pos : -1;
-        row_lo[r] = lo;
-    }
-    for (int block = first_block; block <= last_block; ++block) {
-        const int it = block - first_block;
-        cp_async_wait<STAGES - 2>();        // tile `it` has landed
-        __syncthreads();                    // ... for every thread, and tile it-1 is no longer read
-        const int ahead = block + STAGES - 1;
-        if (ahead <= last_block) {
-            const int s = (it + STAGES - 1) % STAGES;
-            load_kv_tiles(k_tiles + s * BLOCK_N * LD, v_tiles + s * BLOCK_N * LD, k_cache, v_cache, pg,
-                          ahead * BLOCK_N, lo, pos);
+        for (int rr = 0; rr < 2; ++rr) {
+            const int row = (lane >> 2) + rr * 8;
+            row_pos[rr] = row < group ? pos : -1;
+            row_lo[rr] = lo;
         }
-        cp_async_commit();
-        const int stage = it % STAGES;
-        const int key_base = block * BLOCK_N;
-        if (owns_new_token && block == b1) {
-            // the page row of this step's token was not written when the tile was requested
-            const int r = pos - key_base;
-            for (int c = threadIdx.x; c < 2 * CHUNKS; c += THREADS) {
-                const bool is_v = c >= CHUNKS;
-                const int chunk = is_v ? c - CHUNKS : c;
-                *reinterpret_cast<uint4*>((is_v ? v_tiles : k_tiles) + (stage * BLOCK_N + r) * LD + chunk * 8) =
-                    *reinterpret_cast<const uint4*>((is_v ? new_v : new_k) + chunk * 8);
+        for (int block = first_block; block <= last_block; ++block) {
+            const int it = block - first_block;
+            cp_async_wait<STAGES - 2>();        // tile `it` has landed
+            __syncthreads();                    // ... for every thread, and tile it-1 is no longer read
+            const int ahead = block + STAGES - 1;
+            if (ahead <= last_block) {
+                const int s = (it + STAGES - 1) % STAGES;
+                load_kv_tiles(k_tiles + s * BLOCK_N * LD, v_tiles + s * BLOCK_N * LD, k_cache, v_cache, pg,
+                              ahead * BLOCK_N, lo, pos);
             }
+            cp_async_commit();
+            const int stage = it % STAGES;
+            const int key_base = block * BLOCK_N;
+            if (owns_new_token && block == b1) {
+                // the page row of this step's token was not written when the tile was requested
+                const int row = pos - key_base;
+                for (int c = threadIdx.x; c < 2 * CHUNKS; c += THREADS) {
+                    const bool is_v = c >= CHUNKS;
+                    const int chunk = is_v ? c - CHUNKS : c;
+                    *reinterpret_cast<uint4*>((is_v ? v_tiles : k_tiles) + (stage * BLOCK_N + row) * LD + chunk * 8) =
+                        *reinterpret_cast<const uint4*>((is_v ? new_v : new_k) + chunk * 8);
+                }
+                __syncthreads();
+            }
+            // warp w takes keys 16w .. 16w+15 of the tile
+            if (key_base + warp * 16 <= pos && key_base + warp * 16 + 15 >= lo)
+                attend_tile<16>(q_tile, k_tiles + stage * BLOCK_N * LD, v_tiles + stage * BLOCK_N * LD, warp * 16,
+                                key_base, scale_log2, true, row_pos, row_lo, m, l, o);
+        }
+        cp_async_wait<0>();
+#pragma unroll
+        for (int rr = 0; rr < 2; ++rr) {
+            l[rr] += __shfl_xor_sync(0xffffffffu, l[rr], 1);
+            l[rr] += __shfl_xor_sync(0xffffffffu, l[rr], 2);
+        }
+
+        // merge the four warps: merge[warp][16 rows][D + 2]
+        __syncthreads();
+#pragma unroll
+        for (int rr = 0; rr < 2; ++rr) {
+            const int row = (lane >> 2) + rr * 8;
+            float* dst = merge + (warp * 16 + row) * MS;
+#pragma unroll
+            for (int dt = 0; dt < D / 8; ++dt) {
+                dst[dt * 8 + (lane & 3) * 2] = o[dt][2 * rr];
+                dst[dt * 8 + (lane & 3) * 2 + 1] = o[dt][2 * rr + 1];
+            }
+            if ((lane & 3) == 0) {
+                dst[D] = m[rr];
+                dst[D + 1] = l[rr];
+            }
+        }
+        __syncthreads();
+        const size_t my_slot = (size_t)block_id * 2 + (seg == 0 ? 0 : 1);
+        for (int i = threadIdx.x; i < group * D; i += THREADS) {
+            const int row = i / D, d = i - row * D;
+            float mm = -INFINITY;
+#pragma unroll
+            for (int w = 0; w < 4; ++w) mm = fmaxf(mm, merge[(w * 16 + row) * MS + D]);
+            float acc = 0.f, ll = 0.f;
+#pragma unroll
+            for (int w = 0; w < 4; ++w) {
+                const float* src = merge + (w * 16 + row) * MS;
+                const float c = (src[D] == -INFINITY) ? 0.f : exp2f(src[D] - mm);
+                acc += src[d] * c;
+                ll += src[D + 1] * c;
+            }
+            if (complete) {
+                out[((size_t)tok * heads + kvh * group + row) * D + d] = __float2bfloat16_rn(ll > 0.f ? acc / ll : 0.f);
+            } else {
+                part_o[(my_slot * 16 + row) * D + d] = acc;
+                if (d == 0) {
+                    part_ml[(my_slot * 16 + row) * 2] = mm;
+                    part_ml[(my_slot * 16 + row) * 2 + 1] = ll;
+                }
+            }
+        }
+        if (!complete) {
+            // the blocks that share this pair are p_first .. p_last; the last to arrive merges their
+            // pieces in block order
+            int p_first, p_last;
+            if (splits > 0) {            // the pair's own run of blocks, as many as have tiles
+                p_first = (kvh * tokens + tok) * splits;
+                p_last = p_first + (pair_tiles + per - 1) / per - 1;
+            } else {
+                p_first = pair_start / per;
+                p_last = (pair_start + pair_tiles - 1) / per;
+            }
+            __threadfence();
             __syncthreads();
-        }
-        // warp w takes keys 16w .. 16w+15 of the tile
-        if (key_base + warp * 16 <= pos && key_base + warp * 16 + 15 >= lo)
-            attend_tile<16>(q_tile, k_tiles + stage * BLOCK_N * LD, v_tiles + stage * BLOCK_N * LD, warp * 16,
-                            key_base, scale_log2, true, row_pos, row_lo, m, l, o);
-    }
-    cp_async_wait<0>();
-#pragma unroll
-    for (int r = 0; r < 2; ++r) {
-        l[r] += __shfl_xor_sync(0xffffffffu, l[r], 1);
-        l[r] += __shfl_xor_sync(0xffffffffu, l[r], 2);
-    }
-
-    // merge the four warps: merge[warp][16 rows][D + 2]
-    constexpr int MS = D + 2;
-    __syncthreads();
-#pragma unroll
-    for (int r = 0; r < 2; ++r) {
-        const int row = (lane >> 2) + r * 8;
-        float* dst = merge + (warp * 16 + row) * MS;
-#pragma unroll
-        for (int dt = 0; dt < D / 8; ++dt) {
-            dst[dt * 8 + (lane & 3) * 2] = o[dt][2 * r];
-            dst[dt * 8 + (lane & 3) * 2 + 1] = o[dt][2 * r + 1];
-        }
-        if ((lane & 3) == 0) {
-            dst[D] = m[r];
-            dst[D + 1] = l[r];
-        }
-    }
-    __syncthreads();
-    for (int i = threadIdx.x; i < group * D; i += THREADS) {
-        const int row = i / D, d = i - row * D;
-        float mm = -INFINITY;
-#pragma unroll
-        for (int w = 0; w < 4; ++w) mm = fmaxf(mm, merge[(w * 16 + row) * MS + D]);
-        float acc = 0.f, ll = 0.f;
-#pragma unroll
-        for (int w = 0; w < 4; ++w) {
-            const float* src = merge + (w * 16 + row) * MS;
-            const float c = (src[D] == -INFINITY) ? 0.f : exp2f(src[D] - mm);
-            acc += src[d] * c;
-            ll += src[D + 1] * c;
-        }
-        const int head = kvh * group + row;
-        if (n_active == 1) {
-            out[((size_t)tok * heads + head) * D + d] = __float2bfloat16_rn(ll > 0.f ? acc / ll : 0.f);
-        } else {
-            const size_t at = ((size_t)tok * heads + head) * splits + split;
-            part_o[at * D + d] = acc;
-            if (d == 0) {
-                part_ml[at * 2] = mm;
-                part_ml[at * 2 + 1] = ll;
+            if (threadIdx.x == 0) ticket_shared = atomicAdd(&counters[tok * kv_heads + kvh], 1);
+            __syncthreads();
+            if (ticket_shared == p_last - p_first) {
+                __threadfence();
+                for (int i = threadIdx.x; i < group * D; i += THREADS) {
+                    const int row = i / D, d = i - row * D;
+                    float mm = -INFINITY;
+                    for (int p = p_first; p <= p_last; ++p) {
+                        // block p's piece of this pair is its first segment iff its range starts inside the pair
+                        const size_t slot = (size_t)p * 2 + ((splits > 0 || p * per >= pair_start) ? 0 : 1);
+                        mm = fmaxf(mm, __ldcg(part_ml + (slot * 16 + row) * 2));
+                    }
+                    float acc = 0.f, ll = 0.f;
+                    for (int p = p_first; p <= p_last; ++p) {
+                        const size_t slot = (size_t)p * 2 + ((splits > 0 || p * per >= pair_start) ? 0 : 1);
+                        const float ms = __ldcg(part_ml + (slot * 16 + row) * 2);
+                        const float c = (ms == -INFINITY) ? 0.f : exp2f(ms - mm);
+                        acc += __ldcg(part_o + (slot * 16 + row) * D + d) * c;
+                        ll += __ldcg(part_ml + (slot * 16 + row) * 2 + 1) * c;
+                    }
+                    out[((size_t)tok * heads + kvh * group + row) * D + d] = __float2bfloat16_rn(ll > 0.f ? acc / ll : 0.f);
+                }
+                if (threadIdx.x == 0) counters[tok * kv_heads + kvh] = 0;
             }
         }
+        __syncthreads();            // the merge area and ticket_shared are reused by the next segment
+        u += len;
     }
-    if (n_active == 1) return;
-
-    // the last split to arrive merges all of them
-    __threadfence();
-    __syncthreads();
-    if (threadIdx.x == 0) ticket_shared = atomicAdd(&counters[tok * kv_heads + kvh], 1);
-    __syncthreads();
-    if (ticket_shared != n_active - 1) return;
-    __threadfence();
-    for (int i = threadIdx.x; i < group * D; i += THREADS) {
-        const int row = i / D, d = i - row * D;
-        const size_t th = (size_t)tok * heads + kvh * group + row;
-        const float* ml = part_ml + th * splits * 2;
-        float mm = -INFINITY;
-        for (int s = 0; s < n_active; ++s) mm = fmaxf(mm, __ldcg(ml + 2 * s));
-        float acc = 0.f, ll = 0.f;
-        for (int s = 0; s < n_active; ++s) {
-            const float ms = __ldcg(ml + 2 * s);
-            const float c = (ms == -INFINITY) ? 0.f : exp2f(ms - mm);
-            acc += __ldcg(part_o + (th * splits + s) * D + d) * c;
-            ll += __ldcg(ml + 2 * s + 1) * c;
-        }
-        out[th * D + d] = __float2bfloat16_rn(ll > 0.f ? acc / ll : 0.f);
-    }
-    if (threadIdx.x == 0) counters[tok * kv_heads + kvh] = 0;
 }
 
 constexpr size_t PREFILL_SMEM = (size_t)(64 + 4 * BLOCK_N) * LD * sizeof(bf16);
@@ -653,10 +774,35 @@ MRUN_API int mrun_attn_prefill(const void* q, long q_stride, void* out, const vo
     return 0;
 }
 
-// Every token is a row of its own (positions[t] < 0 = padding, output zero).  part_o and part_ml
-// are scratch of tokens * heads * splits * (D and 2) floats; counters holds tokens * kv_heads
-// ints that are zero before the call and zero again after it.  All three may be null when
-// splits == 1.  Calls that share scratch must not overlap on the device.
+// The plan of a decode step for a window (0 = none) and a launch of `blocks` blocks that take at
+// least min_tiles tiles each: tile_prefix gets tokens + 1 ints, assignment 8 ints per block.
+// splits == 0: the tiles of all pairs are dealt evenly across the blocks; splits > 0: every pair
+// has `splits` blocks of its own (blocks = tokens * kv_heads * splits).  The plan is the same for
+// every layer with that window and those sizes, so a step computes it once.
+MRUN_API int mrun_attn_decode_plan(const int* positions, int tokens, int window, int kv_heads, int blocks,
+                                   int min_tiles, int splits, int* tile_prefix, int* assignment,
+                                   cudaStream_t stream) {
+    MRUN_REQUIRE(tokens >= 0 && window >= 0 && kv_heads >= 1 && blocks >= 1 && min_tiles >= 1 && splits >= 0,
+                 "attn_decode_plan: tokens=%d window=%d kv_heads=%d blocks=%d min_tiles=%d splits=%d", tokens, window,
+                 kv_heads, blocks, min_tiles, splits);
+    MRUN_REQUIRE(splits == 0 || blocks == tokens * kv_heads * splits,
+                 "attn_decode_plan: with %d splits per pair the launch has tokens * kv_heads * splits = %d blocks, not %d",
+                 splits, tokens * kv_heads * splits, blocks);
+    MRUN_REQUIRE(((uintptr_t)assignment & 15) == 0, "attn_decode_plan: the assignment must be 16-byte aligned");
+    decode_plan_kernel<<<1, 1024, 0, stream>>>(positions, tokens, window, tile_prefix);
+    MRUN_CHECK_LAUNCH("attn_decode_plan");
+    decode_assign_kernel<<<(blocks + 127) / 128, 128, 0, stream>>>(tile_prefix, tokens, kv_heads, blocks, min_tiles,
+                                                                  splits, (int4*)assignment);
+    MRUN_CHECK_LAUNCH("attn_decode_plan: assignment");
+    return 0;
+}
+
+// Every token is a row of its own (positions[t] < 0 = padding, output zero).  tile_prefix and
+// assignment: the plan from mrun_attn_decode_plan for the same positions, window, kv_heads and
+// blocks.  blocks: how many blocks share the tiles (as many as the device holds at once is best).
+// part_o and part_ml are scratch of blocks * 2 * 16 * (D and 2) floats; counters holds
+// tokens * kv_heads ints that are zero before the call and zero again after it.  Calls that share
+// scratch must not overlap on the device.
 //
 // fused != 0: `q` is the projection's raw output, rows of [heads | kv_heads | kv_heads] x D (q, k, v);
 // the kernel norms q and k with q_weight / k_weight (null: no norm) and eps, rotates them with
@@ -665,14 +811,15 @@ MRUN_API int mrun_attn_prefill(const void* q, long q_stride, void* out, const vo
 // cache holds the token already; the remaining fused arguments are ignored.
 MRUN_API int mrun_attn_decode(const void* q, long q_stride, void* out, void* k_cache, void* v_cache,
                               const int* block_tables, int max_blocks, const int* token_slot,
-                              const int* positions, int tokens, float* part_o, float* part_ml, int* counters,
-                              int splits, int min_tiles, int heads, int kv_heads, int head_dim, int page_size,
-                              float scale, int window, int fused, const float* q_weight, const float* k_weight,
-                              float eps, const float* rot, int rotary_dim, const int* slots, cudaStream_t stream) {
+                              const int* positions, const int* tile_prefix, const int* assignment, int tokens,
+                              float* part_o, float* part_ml, int* counters, int blocks, int heads, int kv_heads,
+                              int head_dim, int page_size, float scale, int window, int fused,
+                              const float* q_weight, const float* k_weight, float eps, const float* rot,
+                              int rotary_dim, const int* slots, cudaStream_t stream) {
     if (int rc = check_common("attn_decode", heads, kv_heads, head_dim, page_size, max_blocks, window, 16)) return rc;
-    MRUN_REQUIRE(tokens >= 0 && splits >= 1 && splits <= 65535 && min_tiles >= 1,
-                 "attn_decode: tokens=%d splits=%d min_tiles=%d", tokens, splits, min_tiles);
-    MRUN_REQUIRE(splits == 1 || (part_o && part_ml && counters), "attn_decode: %d splits need scratch memory", splits);
+    MRUN_REQUIRE(tokens >= 0 && blocks >= 1 && blocks <= 65535, "attn_decode: tokens=%d blocks=%d", tokens, blocks);
+    MRUN_REQUIRE(tile_prefix && assignment && part_o && part_ml && counters,
+                 "attn_decode: the plan and the scratch are required");
     MRUN_REQUIRE(!fused || (rotary_dim >= 0 && rotary_dim <= head_dim && rotary_dim % 2 == 0),
                  "attn_decode: rotary_dim=%d must be even and at most head_dim=%d", rotary_dim, head_dim);
     MRUN_REQUIRE(!fused || (q_weight == nullptr) == (k_weight == nullptr),
@@ -698,10 +845,11 @@ MRUN_API int mrun_attn_decode(const void* q, long q_stride, void* out, void* k_c
         in.k_cache = (bf16*)k_cache;
         in.v_cache = (bf16*)v_cache;
     }
-    MRUN_CHECK_CUDA(mrun::launch_pdl(MRUN_PDL_ATTENTION, decode_kernel, dim3(tokens, kv_heads, splits), dim3(THREADS), DECODE_SMEM, stream,
+    MRUN_CHECK_CUDA(mrun::launch_pdl(MRUN_PDL_ATTENTION, decode_kernel, dim3(blocks), dim3(THREADS), DECODE_SMEM, stream,
                                      (const bf16*)q, q_stride, (bf16*)out, (const bf16*)k_cache, (const bf16*)v_cache,
-                                     block_tables, max_blocks, token_slot, positions, part_o, part_ml, counters,
-                                     min_tiles, heads, kv_heads, page_size, shift_of(page_size), scale * LOG2E, window, in),
+                                     block_tables, max_blocks, token_slot, positions, tile_prefix,
+                                     (const int4*)assignment, tokens, part_o, part_ml, counters, heads, kv_heads,
+                                     page_size, shift_of(page_size), scale * LOG2E, window, in),
                     "attn_decode");
     return 0;
 }
@@ -725,12 +873,15 @@ MRUN_API int mrun_attn_decode_occupancy() {
 
 namespace {
 
-constexpr size_t STATIC_PART_O = (size_t)MRUN_STATIC_MAX_PARTIALS * D;       // floats
-constexpr size_t STATIC_PART_ML = (size_t)MRUN_STATIC_MAX_PARTIALS * 2;      // floats
-constexpr size_t STATIC_COUNTERS = MRUN_STATIC_MAX_PAIRS;                    // ints, stored as 4-byte words
+constexpr size_t STATIC_PART_O = (size_t)MRUN_STATIC_MAX_BLOCKS * 2 * 16 * D;      // floats
+constexpr size_t STATIC_PART_ML = (size_t)MRUN_STATIC_MAX_BLOCKS * 2 * 16 * 2;     // floats
+constexpr size_t STATIC_COUNTERS = MRUN_STATIC_MAX_PAIRS;                          // ints, stored as 4-byte words
+constexpr size_t STATIC_ASSIGNMENT = (size_t)MRUN_STATIC_MAX_BLOCKS * 8;            // ints, 16-byte aligned
+constexpr size_t STATIC_PREFIX = MRUN_STATIC_MAX_TOKENS + 1;                       // ints
 
 // In host code this name is only a handle for cudaGetSymbolAddress, never a device pointer.
-static __device__ __align__(256) float g_static_scratch[STATIC_PART_O + STATIC_PART_ML + STATIC_COUNTERS];
+static __device__ __align__(256) float g_static_scratch[STATIC_PART_O + STATIC_PART_ML + STATIC_COUNTERS +
+                                                        STATIC_ASSIGNMENT + STATIC_PREFIX];
 
 constexpr int STATIC_MAX_DEVICES = 64;
 float* g_static_address[STATIC_MAX_DEVICES] = {};
@@ -759,16 +910,19 @@ int static_scratch_address(float** address) {
 
 MRUN_API int mrun_attn_decode_static(const void* q, long q_stride, void* out, const void* k_cache,
                                      const void* v_cache, const int* block_tables, int max_blocks,
-                                     const int* token_slot, const int* positions, int tokens, int splits,
+                                     const int* token_slot, const int* positions, int tokens, int blocks,
                                      int min_tiles, int heads, int kv_heads, int head_dim, int page_size, float scale,
                                      int window, cudaStream_t stream) {
     if (int rc = check_common("attn_decode_static", heads, kv_heads, head_dim, page_size, max_blocks, window, 16))
         return rc;
-    MRUN_REQUIRE(tokens >= 0 && splits >= 1 && splits <= 65535 && min_tiles >= 1,
-                 "attn_decode_static: tokens=%d splits=%d min_tiles=%d", tokens, splits, min_tiles);
-    MRUN_REQUIRE((long)tokens * heads * splits <= MRUN_STATIC_MAX_PARTIALS,
-                 "attn_decode_static: tokens * heads * splits = %ld exceeds the built-in scratch of %d partial results",
-                 (long)tokens * heads * splits, MRUN_STATIC_MAX_PARTIALS);
+    MRUN_REQUIRE(tokens >= 0 && blocks >= 1 && min_tiles >= 1, "attn_decode_static: tokens=%d blocks=%d min_tiles=%d",
+                 tokens, blocks, min_tiles);
+    MRUN_REQUIRE(blocks <= MRUN_STATIC_MAX_BLOCKS,
+                 "attn_decode_static: blocks = %d exceeds the built-in scratch of %d blocks", blocks,
+                 MRUN_STATIC_MAX_BLOCKS);
+    MRUN_REQUIRE(tokens <= MRUN_STATIC_MAX_TOKENS,
+                 "attn_decode_static: tokens = %d exceeds the built-in scratch of %d tokens", tokens,
+                 MRUN_STATIC_MAX_TOKENS);
     MRUN_REQUIRE((long)tokens * kv_heads <= MRUN_STATIC_MAX_PAIRS,
                  "attn_decode_static: tokens * kv_heads = %ld exceeds the built-in scratch of %d counters",
                  (long)tokens * kv_heads, MRUN_STATIC_MAX_PAIRS);
@@ -778,13 +932,20 @@ MRUN_API int mrun_attn_decode_static(const void* q, long q_stride, void* out, co
     float* part_o = scratch;
     float* part_ml = scratch + STATIC_PART_O;
     int* counters = reinterpret_cast<int*>(scratch + STATIC_PART_O + STATIC_PART_ML);
+    int* assignment = counters + STATIC_COUNTERS;
+    int* tile_prefix = assignment + STATIC_ASSIGNMENT;
     // the counters must start at zero whatever an earlier, possibly interrupted, call left
     MRUN_CHECK_CUDA(cudaMemsetAsync(counters, 0, (size_t)tokens * kv_heads * sizeof(int), stream),
                     "attn_decode_static: clearing the counters");
-    decode_kernel<<<dim3(tokens, kv_heads, splits), THREADS, DECODE_SMEM, stream>>>(
+    decode_plan_kernel<<<1, 1024, 0, stream>>>(positions, tokens, window, tile_prefix);
+    MRUN_CHECK_LAUNCH("attn_decode_static: plan");
+    decode_assign_kernel<<<(blocks + 127) / 128, 128, 0, stream>>>(tile_prefix, tokens, kv_heads, blocks, min_tiles,
+                                                                  0, (int4*)assignment);
+    MRUN_CHECK_LAUNCH("attn_decode_static: assignment");
+    decode_kernel<<<dim3(blocks), THREADS, DECODE_SMEM, stream>>>(
         (const bf16*)q, q_stride, (bf16*)out, (const bf16*)k_cache, (const bf16*)v_cache, block_tables, max_blocks,
-        token_slot, positions, part_o, part_ml, counters, min_tiles, heads, kv_heads, page_size, shift_of(page_size),
-        scale * LOG2E, window, FusedInput{});
+        token_slot, positions, tile_prefix, (const int4*)assignment, tokens, part_o, part_ml, counters, heads, kv_heads,
+        page_size, shift_of(page_size), scale * LOG2E, window, FusedInput{});
     MRUN_CHECK_LAUNCH("attn_decode_static");
     return 0;
 }

@@ -12,10 +12,11 @@
 // for inputs and outputs, but the scratch for the splits' partial results and their meeting
 // counters lives in a fixed array inside the library instead of in caller-provided buffers.
 //
-// Limits: tokens * heads * splits <= MRUN_STATIC_MAX_PARTIALS (16384) and
+// Limits: blocks <= MRUN_STATIC_MAX_BLOCKS (512), tokens <= MRUN_STATIC_MAX_TOKENS (4096) and
 // tokens * kv_heads <= MRUN_STATIC_MAX_PAIRS (4096); larger calls are refused with a message.
-// The array takes 16384 * (head size + 2) * 4 + 4096 * 4 bytes of device memory (about 8.1 MiB
+// The array takes 512 * 32 * (head size + 2) * 4 + 12289 * 4 bytes of device memory (about 8.2 MiB
 // at head size 128) on every GPU that loads the library, from load until the process exits.
+// It also holds the step's plan (tiles per token), which this entry point computes itself.
 //
 // Rules for callers:
 //  * The first call on a device looks up the array's device address (cudaGetSymbolAddress, once
@@ -32,7 +33,8 @@
 
 #include <cuda_runtime.h>
 
-#define MRUN_STATIC_MAX_PARTIALS 16384
+#define MRUN_STATIC_MAX_BLOCKS 512
+#define MRUN_STATIC_MAX_TOKENS 4096
 #define MRUN_STATIC_MAX_PAIRS 4096
 
 #ifdef __cplusplus
@@ -41,7 +43,7 @@ extern "C" {
 
 int mrun_attn_decode_static(const void* q, long q_stride, void* out, const void* k_cache, const void* v_cache,
                             const int* block_tables, int max_blocks, const int* token_slot, const int* positions,
-                            int tokens, int splits, int min_tiles, int heads, int kv_heads, int head_dim,
+                            int tokens, int blocks, int min_tiles, int heads, int kv_heads, int head_dim,
                             int page_size, float scale, int window, cudaStream_t stream);
 
 #ifdef __cplusplus

@@ -4,8 +4,9 @@ Every kernel reads keys and values from the pages; the tokens of the step were w
 the fused norm/rotary/cache kernel just before.
 
 * float32, or a shape the tensor-core kernels refuse: the CUDA-core kernel in 32-bit arithmetic.
-* bfloat16, every segment a single token: the split-key decode kernel (scratch for the partial
-  results of the splits, merged by a second kernel).
+* bfloat16, every segment a single token: the decode kernel, which deals the key tiles of all
+  (token, kv head) pairs evenly to as many blocks as the device holds (scratch for the partial
+  results of pairs shared between blocks, merged by the block that finishes last).
 * bfloat16 otherwise: the tiled prefill kernel over (tokens x group heads) row tiles.
 """
 from __future__ import annotations
@@ -19,7 +20,6 @@ from . import lib as _lib
 from . import ops
 from .ops import _c_float, _c_int, _c_long, _ptr, _stream
 
-MAX_SPLITS = 64
 COUNTER_CAPACITY = 1 << 16     # (token, kv head) pairs of one decode launch that may be split
 
 _counters = {}                 # device -> int32 zeros, handed to every split launch
@@ -50,22 +50,37 @@ def supports_tensor_cores(dtype: torch.dtype, head_dim: int, group: int) -> bool
     return dtype == torch.bfloat16 and head_dim % 16 == 0 and 16 <= head_dim <= 256 and group <= 64
 
 
-def decode_splits(tokens: int, kv_heads: int, max_kv_len: int, slots: int):
-    """(splits, min_tiles): how many ways the keys of a token may be split and the fewest 64-key
-    tiles a split takes.  Few (token, kv head) pairs: as many splits as fill the device once, four
-    tiles each at least.  More pairs than the device holds at a time: up to four rounds of blocks,
-    so that the last, partly filled round costs little, but only for contexts long enough to give
-    every split sixteen tiles.  (Measured on B200 at head size 128.)  The kernel applies
-    ``min_tiles`` to each token's own context, so short contexts use fewer splits."""
-    pairs = max(1, tokens * kv_heads)
-    blocks = max(1, -(-max_kv_len // 64))
-    if pairs > COUNTER_CAPACITY:
-        return 1, 1
-    if pairs < slots:
-        want, min_tiles = slots // pairs, 4
-    else:
-        want, min_tiles = -(-4 * slots // pairs), 16
-    return max(1, min(want, -(-blocks // min_tiles), MAX_SPLITS)), min_tiles
+MIN_TILES = 4      # the fewest 64-key tiles a block of the decode kernel takes (measured on B200)
+
+
+MAX_SPLITS = 32    # blocks per (token, kv head) pair when a step has few pairs
+
+
+def decode_launch(tokens: int, kv_heads: int, slots: int):
+    """(blocks, splits) of a decode step.  At least as many (token, kv head) pairs as the device
+    holds blocks: all its blocks, the tiles dealt evenly across pairs (splits = 0).  Fewer: every
+    pair gets as many blocks of its own as fill the device once."""
+    pairs = tokens * kv_heads
+    if pairs >= slots:
+        return slots, 0
+    splits = max(1, min(slots // pairs, MAX_SPLITS))
+    return pairs * splits, splits
+
+
+def decode_plan(ctx, library, window: int, kv_heads: int, blocks: int, splits: int):
+    """The step's plan for the decode kernel: tiles per token as a prefix sum (int32, tokens + 1)
+    and what each of ``blocks`` blocks starts with (int32, 8 per block).  Made once per step for
+    a window, a number of kv heads and a launch shape."""
+    key = ("decode_plan", window, kv_heads, blocks, splits)
+    plan = ctx.shared.get(key)
+    if plan is None:
+        prefix = torch.empty(ctx.num_tokens + 1, dtype=torch.int32, device=ctx.positions.device)
+        assignment = torch.empty(blocks * 8, dtype=torch.int32, device=ctx.positions.device)
+        library.call("mrun_attn_decode_plan", _ptr(ctx.positions), _c_int(ctx.num_tokens), _c_int(window),
+                     _c_int(kv_heads), _c_int(blocks), _c_int(MIN_TILES), _c_int(splits), _ptr(prefix),
+                     _ptr(assignment), _stream())
+        plan = ctx.shared[key] = (prefix, assignment)
+    return plan
 
 
 def prefill_tiles(ctx, tokens_per_tile: int):
@@ -110,20 +125,20 @@ def paged_attention(q: torch.Tensor, q_stride: int, out: torch.Tensor, cache, gr
     tail = (_c_int(heads), _c_int(kv_heads), _c_int(head_dim), _c_int(page_size), _c_float(scale),
             _c_int(window), _stream())
     if ctx.all_decode and ratio <= 16:
-        splits, min_tiles = decode_splits(tokens, kv_heads, ctx.max_kv_len, _decode_slots(head_dim, library))
-        part_o = part_ml = counters = None
-        if splits > 1:
-            part_o = torch.empty((tokens, heads, splits, head_dim), dtype=torch.float32, device=q.device)
-            part_ml = torch.empty((tokens, heads, splits, 2), dtype=torch.float32, device=q.device)
-            counters = _split_counters(q.device)
+        if tokens * kv_heads > COUNTER_CAPACITY:
+            raise ValueError(f"a decode step of {tokens} tokens x {kv_heads} kv heads exceeds {COUNTER_CAPACITY} pairs")
+        blocks, splits = decode_launch(tokens, kv_heads, _decode_slots(head_dim, library))
+        part_o = torch.empty((blocks, 2, 16, head_dim), dtype=torch.float32, device=q.device)
+        part_ml = torch.empty((blocks, 2, 16, 2), dtype=torch.float32, device=q.device)
         fused = (_c_int(0), _ptr(None), _ptr(None), _c_float(0.0), _ptr(None), _c_int(0), _ptr(None))
         if raw is not None:
             q_weight, k_weight, eps, rot, rotary_dim, slots = raw
             fused = (_c_int(1), _ptr(q_weight), _ptr(k_weight), _c_float(eps), _ptr(rot), _c_int(rotary_dim),
                      _ptr(slots))
-        library.call("mrun_attn_decode", _ptr(q), _c_long(q_stride), _ptr(out), *common, _c_int(tokens),
-                     _ptr(part_o), _ptr(part_ml), _ptr(counters), _c_int(splits), _c_int(min_tiles), *tail[:-1],
-                     *fused, tail[-1])
+        prefix, assignment = decode_plan(ctx, library, window, kv_heads, blocks, splits)
+        library.call("mrun_attn_decode", _ptr(q), _c_long(q_stride), _ptr(out), *common, _ptr(prefix),
+                     _ptr(assignment), _c_int(tokens), _ptr(part_o), _ptr(part_ml),
+                     _ptr(_split_counters(q.device)), _c_int(blocks), *tail[:-1], *fused, tail[-1])
         return out
     if raw is not None:
         raise ValueError("raw q, k, v rows are taken by the decode kernel only")

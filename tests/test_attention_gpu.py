@@ -125,16 +125,19 @@ def test_decode_batch_against_plain(heads, kv_heads, head_dim, page_size, window
     got = case.run(scale)
     assert (got[:case.tokens] - want[:case.tokens]).abs().max() <= 2e-2 * want.abs().max()
     assert got[case.tokens:].abs().max() == 0, "padding rows must come out as zeros"
-    # a captured step sizes its grid for the longest context the model allows: more splits offered
-    case.ctx.max_kv_len = 64 * 1024
+    # the same step again: the plan is made anew and the counters are back at zero
     case.ctx.shared.clear()
     assert (case.run(scale)[:case.tokens] - want[:case.tokens]).abs().max() <= 2e-2 * want.abs().max()
 
 
-@pytest.mark.parametrize("splits,min_tiles", [(1, 1), (3, 1), (16, 1), (64, 1), (5, 2), (16, 4)])
-def test_decode_splits_of_every_kind(splits, min_tiles):
-    """The split-key kernel called directly with forced split counts, twice in a row (the counters
-    the splits meet at must be back at zero), against the CUDA-core kernel."""
+@pytest.mark.parametrize("blocks,min_tiles,splits", [(1, 1, 0), (3, 1, 0), (16, 1, 0), (64, 1, 0), (444, 1, 0), (5, 2, 0),
+                                                     (16, 4, 0), (1000, 3, 0), (7, 40, 0),
+                                                     (16, 1, 1), (48, 1, 3), (256, 2, 16), (512, 4, 32)])
+def test_decode_tiles_dealt_to_any_number_of_blocks(blocks, min_tiles, splits):
+    """The decode kernel called directly with forced launch shapes (one block takes every pair,
+    several blocks share pairs, more blocks than tiles; tiles dealt across pairs, or every pair
+    split between blocks of its own), twice in a row (the counters the blocks meet at must be
+    back at zero), against the CUDA-core kernel."""
     import ctypes
     from mrun_b200.kernels import lib as L, ops
     from mrun_b200.kernels.ops import _c_float, _c_int, _c_long, _ptr, _stream
@@ -144,19 +147,31 @@ def test_decode_splits_of_every_kind(splits, min_tiles):
     scale = head_dim ** -0.5
     want = case.run(scale, force_generic=True)
     n = case.tokens + case.pad
-    part_o = torch.full((n, heads, splits, head_dim), float("nan"), device=DEV)
-    part_ml = torch.full((n, heads, splits, 2), float("nan"), device=DEV)
+    library = L.attention(head_dim)
+    plan = torch.empty(n + 1, dtype=torch.int32, device=DEV)
+    assignment = torch.empty(blocks * 8, dtype=torch.int32, device=DEV)
+    library.call("mrun_attn_decode_plan", _ptr(case.ctx.positions), _c_int(n), _c_int(0), _c_int(kv_heads),
+                 _c_int(blocks), _c_int(min_tiles), _c_int(splits), _ptr(plan), _ptr(assignment), _stream())
+    assert plan.tolist() == [0, 1, 2, 4, 15, 31, 34, 34, 34]
+    starts = assignment.view(blocks, 2, 4)[:, 0].tolist()
+    if splits == 0:
+        per = max(-(-68 // blocks), min_tiles)
+        assert [s[0] for s in starts] == [min(68, b * per) for b in range(blocks)]    # 34 tiles x 2 kv heads
+    assert sum(s[1] - s[0] for s in starts) == 68                                      # every tile dealt once
+    part_o = torch.full((blocks, 2, 16, head_dim), float("nan"), device=DEV)
+    part_ml = torch.full((blocks, 2, 16, 2), float("nan"), device=DEV)
     counters = torch.zeros(n * kv_heads, dtype=torch.int32, device=DEV)
     for _ in range(2):
         out = torch.full((n, heads * head_dim), 3.0, dtype=torch.bfloat16, device=DEV)
-        L.attention(head_dim).call(
+        library.call(
             "mrun_attn_decode", _ptr(case.qd), _c_long(case.qd.stride(0)), _ptr(out), _ptr(case.kd), _ptr(case.vd),
             _ptr(case.table), _c_int(case.group.max_blocks), _ptr(case.ctx.token_slot), _ptr(case.ctx.positions),
-            _c_int(n), _ptr(part_o), _ptr(part_ml), _ptr(counters), _c_int(splits), _c_int(min_tiles), _c_int(heads),
-            _c_int(kv_heads), _c_int(head_dim), _c_int(page_size), _c_float(scale), _c_int(0),
+            _ptr(plan), _ptr(assignment), _c_int(n), _ptr(part_o), _ptr(part_ml), _ptr(counters), _c_int(blocks),
+            _c_int(heads), _c_int(kv_heads), _c_int(head_dim), _c_int(page_size), _c_float(scale), _c_int(0),
             _c_int(0), _ptr(None), _ptr(None), _c_float(0.0), _ptr(None), _c_int(0), _ptr(None), _stream())
         got = out.float().cpu()
         assert (got - want).abs().max() <= 2e-2 * want.abs().max()
+        assert got[case.tokens:].abs().max() == 0
         assert int(counters.abs().sum()) == 0
 
 
