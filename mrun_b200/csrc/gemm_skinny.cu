@@ -55,12 +55,11 @@ template <typename T> __device__ __forceinline__ void store_out(T* p, float v);
 template <> __device__ __forceinline__ void store_out<bf16>(bf16* p, float v) { *p = __float2bfloat16_rn(v); }
 template <> __device__ __forceinline__ void store_out<float>(float* p, float v) { *p = v; }
 
-// NT: token tiles of 8 (M <= 8 NT).  MT: 16-row tiles of W per block.
-template <int NT, int MT, typename TOut, bool SWIGLU>
+// NT: token tiles of 8 (M <= 8 NT).  MT: 16-row tiles of W per block.  UNROLL: chunks per batch.
+template <int NT, int MT, int UNROLL, typename TOut, bool SWIGLU>
 __global__ void __launch_bounds__(THREADS)
 skinny_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w, TOut* __restrict__ y, int M, int N, int K,
               long ldx, long ldy) {
-    constexpr int UNROLL = (MT == 1 && NT == 1) ? MRUN_SKINNY_UNROLL : MRUN_SKINNY_UNROLL_WIDE;   // chunks per batch
     __shared__ float red[WARPS][MT * 16][NT * 8 + 1];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int g = lane >> 2, t = lane & 3;
@@ -199,23 +198,28 @@ skinny_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w, TOut* __re
     }
 }
 
-template <int NT, int MT, typename TOut, bool SWIGLU>
+template <int NT, int MT, int UNROLL, typename TOut, bool SWIGLU>
 void launch(const bf16* x, const bf16* w, TOut* y, int M, int N, int K, long ldx, long ldy, cudaStream_t stream) {
     const int blocks = (N + MT * 16 - 1) / (MT * 16);
-    mrun::launch_pdl(MRUN_PDL_GEMM, skinny_kernel<NT, MT, TOut, SWIGLU>, dim3(blocks), dim3(THREADS), 0, stream, x, w, y, M, N, K,
-                     ldx, ldy);
+    mrun::launch_pdl(MRUN_PDL_GEMM, skinny_kernel<NT, MT, UNROLL, TOut, SWIGLU>, dim3(blocks), dim3(THREADS), 0,
+                     stream, x, w, y, M, N, K, ldx, ldy);
 }
 
 template <typename TOut, bool SWIGLU>
 void dispatch(const bf16* x, const bf16* w, TOut* y, int M, int N, int K, long ldx, long ldy, cudaStream_t stream) {
     // two row tiles per block halve the reads of x once there are plenty of blocks
     const bool wide = N >= MRUN_SKINNY_WIDE_N;
+    constexpr int DEEP = MRUN_SKINNY_UNROLL, SHALLOW = MRUN_SKINNY_UNROLL_WIDE;
     if (M <= 8) {
-        if (wide) launch<1, 2, TOut, SWIGLU>(x, w, y, M, N, K, ldx, ldy, stream);
-        else launch<1, 1, TOut, SWIGLU>(x, w, y, M, N, K, ldx, ldy, stream);
+        // With the deep batches two blocks fit on an SM (registers), with the shallow ones three.
+        // More than two rounds' worth of 16-row blocks (N = 6144: 384 blocks on 148 SMs) run in
+        // one round with the shallow kind; fewer blocks are faster with the deep kind.
+        if (wide) launch<1, 2, SHALLOW, TOut, SWIGLU>(x, w, y, M, N, K, ldx, ldy, stream);
+        else if ((N + 15) / 16 > 2 * 148) launch<1, 1, SHALLOW, TOut, SWIGLU>(x, w, y, M, N, K, ldx, ldy, stream);
+        else launch<1, 1, DEEP, TOut, SWIGLU>(x, w, y, M, N, K, ldx, ldy, stream);
     } else {
-        if (wide) launch<2, 2, TOut, SWIGLU>(x, w, y, M, N, K, ldx, ldy, stream);
-        else launch<2, 1, TOut, SWIGLU>(x, w, y, M, N, K, ldx, ldy, stream);
+        if (wide) launch<2, 2, SHALLOW, TOut, SWIGLU>(x, w, y, M, N, K, ldx, ldy, stream);
+        else launch<2, 1, SHALLOW, TOut, SWIGLU>(x, w, y, M, N, K, ldx, ldy, stream);
     }
 }
 
