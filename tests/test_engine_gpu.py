@@ -144,3 +144,43 @@ def test_repetition_penalty_and_filters_through_generate(tiny):
         want = plain.sample_token(logits, 0.9, plain.draw_key(77, n), top_p=0.95, top_k=12, min_p=0.01)
         assert token == want, (n, token, want)
         tokens.append(token)
+
+
+def test_many_requests_through_few_slots_and_few_pages(tiny):
+    """Continuous batching under pressure: more requests than state slots, a pool so small that
+    pages are reused many times, and (without reservations) requests that are preempted and fed
+    again.  Greedy tokens must not depend on any of it."""
+    from mrun_b200 import Engine
+    name, folder, settings = tiny
+    cfg, weights = plain.load_folder(folder)
+    lengths = [3, 47, 12, 80, 5, 33, 64, 9, 21, 70, 2, 55]
+    prompts = [random_tokens(cfg["vocab_size"], n, seed=300 + i) for i, n in enumerate(lengths)]
+    roomy = Engine.from_folder(folder, dtype="float32", page_size=settings["page_size"], context=4096,
+                               max_batch_tokens=64, max_requests=16)
+    want = [r.tokens for r in roomy.generate(prompts, max_tokens=10, ignore_eos=True)]
+    for prompt, tokens in list(zip(prompts, want))[:3]:
+        assert tokens == plain.generate(cfg, weights, prompt, 10)
+
+    page = settings["page_size"]
+    tight = Engine.from_folder(folder, dtype="float32", page_size=page, num_pages=-(-200 // page),
+                               max_batch_tokens=24, max_requests=3)
+    got = tight.generate(prompts, max_tokens=10, ignore_eos=True)
+    assert [r.tokens for r in got] == want and all(r.finish_reason == "length" for r in got)
+    tight.executor.cache.check_invariants()
+    assert tight.executor.cache.free_pages() == tight.executor.cache.num_pages
+
+    # without reservations: four requests are admitted on what their prompts need, then grow by
+    # 40 tokens each until the pool of 160 tokens runs out
+    growing = [random_tokens(cfg["vocab_size"], n, seed=400 + n) for n in (20, 25, 30, 18)]
+    want_long = [r.tokens for r in roomy.generate(growing, max_tokens=40, ignore_eos=True)]
+    greedy_pool = Engine.from_folder(folder, dtype="float32", page_size=page, num_pages=-(-160 // page),
+                                     max_batch_tokens=32, max_requests=4, reserve=False)
+    got = greedy_pool.generate(growing, max_tokens=40, ignore_eos=True)
+    assert [r.tokens for r in got] == want_long
+    assert greedy_pool.stats.preemptions > 0 and sum(r.preemptions for r in got) == greedy_pool.stats.preemptions, \
+        "the pool was meant to run out"
+    greedy_pool.executor.cache.check_invariants()
+    assert greedy_pool.executor.cache.free_pages() == greedy_pool.executor.cache.num_pages
+
+    too_long = tight.generate([random_tokens(cfg["vocab_size"], 400, seed=1)], max_tokens=4)[0]
+    assert too_long.finish_reason == "too_long" and too_long.tokens == []
