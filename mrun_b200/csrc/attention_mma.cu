@@ -498,12 +498,12 @@ decode_kernel(const bf16* __restrict__ q, long q_stride, bf16* __restrict__ out,
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     // Positions, slots, block tables and the plan are written at the start of a step, not by the
     // kernel before this one, so they are read before waiting for it.
-    mrun::pdl_launch_dependents();
     const int4 mine = assignment[2 * block_id], shape = assignment[2 * block_id + 1];
     int u = mine.x;
     const int u_end = mine.y;
     const int tiles_per_head = shape.x, per = shape.y, splits = shape.z;
     mrun::pdl_wait();
+    mrun::pdl_launch_dependents();
     const int* prefix = tile_prefix;
     int kvh = mine.z, tok = mine.w;                             // the pair of the block's first tile
 

@@ -49,7 +49,10 @@ namespace mrun {
 // that kernel wrote and before it writes anything at all.  What it does before the wait (index
 // arithmetic, loads of weights and of other data that no kernel of the step writes) overlaps the
 // previous kernel's tail.  pdl_launch_dependents() lets the *next* kernel's blocks be scheduled
-// once every block of this one has reached it.  Both are no-ops in a kernel launched normally.
+// once every block of this one has reached it.  It is called after pdl_wait(), never before: a
+// kernel that released its successor before waiting itself would let a whole chain of kernels
+// pile up on the SMs, each holding block slots while it waits for the one before it.  Both are
+// no-ops in a kernel launched normally.
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;"); }
 

@@ -114,8 +114,8 @@ add_rmsnorm_vec_kernel(float* __restrict__ resid, const TA* __restrict__ delta,
                        const float* __restrict__ weight, float eps, TA* __restrict__ out,
                        const int* __restrict__ rows, int hidden) {
     __shared__ float scratch[33];
-    pdl_launch_dependents();
     pdl_wait();
+    pdl_launch_dependents();
     const int r = blockIdx.x;
     const size_t src = (size_t)(rows ? rows[r] : r) * hidden;
     const int chunks = hidden >> 3;
@@ -239,8 +239,8 @@ __global__ void qk_norm_rope_cache_kernel(TA* __restrict__ qkv, const float* __r
                                           TA* __restrict__ v_cache, int tokens, int heads, int kv_heads,
                                           int head_dim, int page_size) {
     extern __shared__ float vec_buf[];
-    pdl_launch_dependents();
     pdl_wait();
+    pdl_launch_dependents();
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int per_token = heads + 2 * kv_heads;
     const long item = (long)blockIdx.x * (blockDim.x >> 5) + warp;

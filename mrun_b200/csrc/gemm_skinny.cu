@@ -136,10 +136,10 @@ skinny_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w, TOut* __re
     // requested before waiting for it, the rows of x after.
     constexpr int STRIDE = UNROLL * WARPS;
     int c0 = warp;
-    pdl_launch_dependents();
     load_w(wa[0], c0);
     load_w(wa[1], c0 + STRIDE);
     pdl_wait();
+    pdl_launch_dependents();
     load_x(xa[0], c0);
     load_x(xa[1], c0 + STRIDE);
     while (c0 < chunks) {
