@@ -83,6 +83,27 @@ class EntryCache:
         self.k, self.v, self.state = k, v, state
 
 
+def token_bytes(needs: Sequence[object], shares: Sequence[Optional[int]], element_size: int) -> Tuple[int, int]:
+    """(bytes one token holds in the pages of every owning schedule entry, bytes of fixed-size
+    state one request slot holds), from the needs alone: what a memory budget needs before any
+    tensor exists.  A windowed group is counted like a full one (an upper bound)."""
+    per_token = per_slot = 0
+    for need, share in zip(needs, shares):
+        if share is not None or need is None:
+            continue
+        if isinstance(need, PagedKV):
+            per_token += 2 * need.kv_heads * need.head_dim * element_size
+        elif isinstance(need, FixedState):
+            count = 1
+            for extent in need.shape:
+                count *= extent
+            per_slot += count * _STATE_BYTES.get(need.dtype, 4)
+    return per_token, per_slot
+
+
+_STATE_BYTES = {"float32": 4, "float16": 2, "bfloat16": 2, "int32": 4, "float64": 8}
+
+
 class CacheManager:
     def __init__(self, needs: Sequence[object], shares: Sequence[Optional[int]], page_size: int,
                  num_pages: int, max_requests: int, device=None, dtype=None,

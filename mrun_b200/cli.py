@@ -2,7 +2,7 @@
 reference's token-ids-in example (crates/mrun-engine/examples/generate.rs:1-13).
 
     mrun run MODEL --prompt IDS [--max-tokens N] [--temperature T] [--top-p P] [--top-k K]
-                   [--min-p P] [--seed S] [--context TOKENS] [--info]
+                   [--min-p P] [--seed S] [--budget-gib GIB | --context TOKENS] [--info]
     mrun random MODEL_DIR --config CONFIG.json --seed S
 
 ``MODEL`` is a folder with config.json and safetensors.  ``--prompt`` takes token ids, inline or
@@ -46,6 +46,17 @@ def parse_tokens(text: str) -> int:
     return int(text) * scale
 
 
+def parse_budget_gib(text: str) -> int:
+    """Whole GiB, at least 1 (crates/mrun/src/cli/model.rs: ``parse_budget_gib``)."""
+    try:
+        value = int(text)
+    except ValueError:
+        raise argparse.ArgumentTypeError(f"{text!r} is not a whole number of GiB") from None
+    if value < 1:
+        raise argparse.ArgumentTypeError("the budget must be at least 1 GiB")
+    return value
+
+
 def generation_defaults(model_dir: str) -> dict:
     defaults = dict(temperature=0.0, top_p=1.0, top_k=0, min_p=0.0)
     path = os.path.join(model_dir, "generation_config.json")
@@ -78,7 +89,10 @@ def build_parser() -> argparse.ArgumentParser:
     run.add_argument("--min-p", type=float, default=None)
     run.add_argument("--seed", type=int, default=None)
     run.add_argument("--max-tokens", type=int, default=2048)
-    run.add_argument("--context", type=parse_tokens, default=None,
+    run.add_argument("--budget-gib", type=parse_budget_gib, default=os.environ.get("MRUN_BUDGET_GIB"),
+                     help="lower the memory budget to this many GiB [default: the GPU's memory less 2 GiB, "
+                          "at most what is free less a margin]; it cannot raise it (MRUN_BUDGET_GIB)")
+    run.add_argument("--context", type=parse_tokens, default=os.environ.get("MRUN_CONTEXT"),
                      help="memory for this many tokens of context (64K)")
     run.add_argument("--info", action="store_true", help="print the memory breakdown after loading and exit")
     run.add_argument("--dtype", choices=["bfloat16", "float32"], default="bfloat16")
@@ -101,6 +115,10 @@ def check_run_args(args) -> Optional[str]:
     from .sampling.params import SamplingParams
     if args.max_tokens < 1:
         return "--max-tokens must be at least 1"
+    if args.budget_gib is not None and args.context is not None:
+        return "--context cannot be used with --budget-gib"
+    if args.context is not None and args.context < 1:
+        return "--context must be at least 1 token"
     try:
         SamplingParams(temperature=args.temperature if args.temperature is not None else 0.0,
                        top_p=args.top_p if args.top_p is not None else 1.0,
@@ -121,15 +139,24 @@ def command_run(args) -> int:
     if not prompt and not args.info:
         print("error: the prompt is empty", file=sys.stderr)
         return 2
+    from .engine import budget
     from .engine.engine import Engine
     loaded = time.perf_counter()
-    engine = Engine.from_folder(args.model, dtype=args.dtype, page_size=args.page_size,
-                                context=args.context or max(4096, len(prompt) + args.max_tokens),
-                                max_batch_tokens=args.max_batch_tokens)
+    try:
+        # one request at a time: the cache holds at most the model's longest sequence
+        memory = budget.plan(budget.read_device(), args.budget_gib)
+        engine = Engine.from_folder(args.model, dtype=args.dtype, page_size=args.page_size,
+                                    context=args.context, max_requests=1,
+                                    max_batch_tokens=args.max_batch_tokens, memory=memory)
+    except budget.BudgetError as error:
+        print(f"error: {error}", file=sys.stderr)
+        return 4
     info = engine.info()
     gib = lambda b: b / float(1 << 30)
-    print(f"loaded {info['architecture']} in {time.perf_counter() - loaded:.1f} s: weights "
-          f"{gib(info['weights_bytes']):.2f} GiB + cache {gib(info['cache_bytes']):.2f} GiB "
+    print(f"loaded {info['architecture']} in {time.perf_counter() - loaded:.1f} s: budget "
+          f"{gib(info['memory']['budget_bytes']):.2f} GiB ({info['memory']['binding']}) = weights "
+          f"{gib(info['weights_bytes']):.2f} GiB + scratch {gib(info['memory']['scratch_bytes']):.2f} GiB + "
+          f"cache {gib(info['cache_bytes']):.2f} GiB "
           f"({info['capacity_tokens']} tokens in {info['num_pages']} pages of {info['page_size']})",
           file=sys.stderr)
     if args.info:

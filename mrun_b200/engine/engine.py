@@ -14,10 +14,13 @@ from typing import List, Optional, Sequence, Union
 import numpy as np
 import torch
 
+from ..cache.manager import token_bytes
 from ..cache.pages import OutOfPages
 from ..sampling.params import REPETITION_CONTEXT, SamplingParams, draw_key
 from ..sampling.sampler import Sampler
+from . import budget
 from .batch import RECENT, StepEntry
+from .budget import MemoryBudget
 from .executor import Executor
 from .loading import executor_from_config, executor_from_folder
 from .scheduler import Request, Scheduler, StepPlan
@@ -77,21 +80,31 @@ class Engine:
     def from_folder(cls, model_dir: str, dtype: str = "bfloat16", page_size: int = 16,
                     num_pages: Optional[int] = None, context: Optional[int] = None,
                     max_requests: int = 64, max_batch_tokens: int = 2048, reserve: bool = True,
-                    device: str = "cuda:0", **kw) -> "Engine":
+                    device: str = "cuda:0", memory: Optional[MemoryBudget] = None, **kw) -> "Engine":
+        """``num_pages`` or ``context`` size the cache directly.  With ``memory`` (a budget from
+        :func:`mrun_b200.engine.budget.plan`) the cache is what the budget leaves beside the
+        weights and the step's scratch, or exactly ``context`` tokens if that fits."""
+        sizing = None
+        if memory is not None and num_pages is None:
+            sizing = _sizing(memory, context, page_size, max_requests, max_batch_tokens)
         pages = _pages_for(num_pages, context, page_size)
         executor = executor_from_folder(model_dir, dtype=dtype, page_size=page_size, num_pages=pages,
-                                        max_requests=max_requests, device=device)
+                                        max_requests=max_requests, device=device, sizing=sizing)
         return cls(executor, max_batch_tokens=max_batch_tokens, reserve=reserve, **kw)
 
     @classmethod
     def from_config(cls, config, seed: int = 0, dtype: str = "bfloat16", std: float = 0.02,
                     norm_noise: float = 0.0, page_size: int = 16, num_pages: Optional[int] = None,
                     context: Optional[int] = None, max_requests: int = 64, max_batch_tokens: int = 2048,
-                    reserve: bool = True, device: str = "cuda:0", **kw) -> "Engine":
+                    reserve: bool = True, device: str = "cuda:0", memory: Optional[MemoryBudget] = None,
+                    **kw) -> "Engine":
+        sizing = None
+        if memory is not None and num_pages is None:
+            sizing = _sizing(memory, context, page_size, max_requests, max_batch_tokens)
         pages = _pages_for(num_pages, context, page_size)
         executor = executor_from_config(config, seed, dtype=dtype, std=std, norm_noise=norm_noise,
                                         page_size=page_size, num_pages=pages, max_requests=max_requests,
-                                        device=device)
+                                        device=device, sizing=sizing)
         return cls(executor, max_batch_tokens=max_batch_tokens, reserve=reserve, **kw)
 
     # ------------------------------------------------------------------ generation
@@ -253,6 +266,7 @@ class Engine:
             "max_requests": ex.cache.max_requests,
             "max_batch_tokens": self.max_batch_tokens,
             "eos_token_ids": list(self.eos_token_ids),
+            "memory": ex.memory.breakdown() if ex.memory is not None else None,
         }
 
 
@@ -279,6 +293,27 @@ def _fill_sampling(host, where, requests: Sequence[Request]) -> None:
             ids = r.recent(RECENT)
             recent[i, :len(ids)] = ids
     host[where["keys"]] = keys.view(np.int32)
+
+
+def _sizing(memory: MemoryBudget, context: Optional[int], page_size: int, max_requests: int,
+            max_batch_tokens: int):
+    """The executor's page count from a memory budget, once the model is on the device."""
+    def sizing(model):
+        spec, precision = model.spec, model.runtime.precision
+        element = 2 if precision.act == torch.bfloat16 else 4
+        per_token, per_slot = token_bytes(model.cache_needs(), model.cache_shares(), element)
+        scratch = budget.scratch_estimate(spec.hidden_size, model.activation_elements(), spec.vocab_size,
+                                          max_batch_tokens, max_requests, element)
+        weights = model.weight_bytes()
+        most = spec.max_positions * max_requests
+        if context is not None:
+            done = budget.for_context(memory, context, weights, scratch, max(1, per_token), most,
+                                      per_slot * max_requests)
+        else:
+            done = budget.with_capacity(memory, weights, scratch, max(1, per_token), most,
+                                        per_slot * max_requests)
+        return max(1, -(-done.capacity_tokens // page_size)), done
+    return sizing
 
 
 def _pages_for(num_pages: Optional[int], context: Optional[int], page_size: int) -> int:

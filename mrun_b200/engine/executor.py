@@ -44,7 +44,10 @@ class LaunchCounter:
 class Executor:
     def __init__(self, spec: ModelSpec, tensors: Dict[str, torch.Tensor], dtype: str = "bfloat16",
                  page_size: int = 16, num_pages: int = 256, max_requests: int = 8,
-                 device: str = "cuda:0"):
+                 device: str = "cuda:0", sizing=None):
+        """``sizing(model) -> (num_pages, memory)`` replaces ``num_pages`` once the weights are
+        on the device: the memory budget needs their size and the parts' needs to say how many
+        pages fit; ``memory`` is kept for :meth:`Engine.info`."""
         if not torch.cuda.is_available():
             raise RuntimeError("mrun_b200 runs on a CUDA device only: no GPU is visible and there "
                                "is no CPU path")
@@ -54,6 +57,9 @@ class Executor:
         self.runtime = Runtime(self.device, self.precision, page_size)
         self.spec = spec
         self.model = Model(spec, tensors, self.runtime)
+        self.memory = None
+        if sizing is not None:
+            num_pages, self.memory = sizing(self.model)
         self.cache = CacheManager(self.model.cache_needs(), self.model.cache_shares(), page_size,
                                   num_pages, max_requests, device=self.device, dtype=self.precision.act,
                                   max_blocks_per_request=-(-spec.max_positions // page_size))

@@ -43,6 +43,17 @@ class Model:
     def cache_shares(self) -> List[Optional[int]]:
         return [entry.cache_of for entry in self.order]
 
+    def activation_elements(self) -> int:
+        """The widest set of per-token temporaries any part declares (parts without the hint
+        count as nothing); the memory budget sizes the step's scratch from it."""
+        widest = 0
+        for block in self.blocks:
+            for part in (getattr(block, "mixer", None), getattr(block, "feed_forward", None)):
+                hint = getattr(part, "activation_elements", None)
+                if hint is not None:
+                    widest = max(widest, int(hint()))
+        return widest
+
     @property
     def graph_safe(self) -> bool:
         return all(getattr(block.mixer, "graph_safe", False) for block in self.blocks)

@@ -62,6 +62,10 @@ class Attention:
     def cache_need(self):
         return PagedKV(self.spec.kv_heads, self.spec.head_dim, self.spec.window)
 
+    def activation_elements(self) -> int:
+        """Elements per token of the temporaries alive at once (q, k, v and the heads' output)."""
+        return (2 * self.spec.heads + 2 * self.spec.kv_heads) * self.spec.head_dim
+
     def forward(self, x: torch.Tensor, ctx, cache) -> torch.Tensor:
         s = self.spec
         group = ctx.group(cache.group_key)

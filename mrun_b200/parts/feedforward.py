@@ -36,6 +36,10 @@ class GatedMLP:
             self.w_gate_up = runtime.matrix(torch.cat([gate, up], dim=0))
         self.w_down = runtime.matrix(tensors["down_proj.weight"])
 
+    def activation_elements(self) -> int:
+        """Elements per token of the temporaries alive at once (gate, up and their product)."""
+        return 3 * self.spec.intermediate
+
     def forward(self, x: torch.Tensor, ctx) -> torch.Tensor:
         if self.interleaved and ops.skinny_ok(x, self.w_gate_up):
             act = ops.gemm_skinny(x, self.w_gate_up, swiglu_rows=True)

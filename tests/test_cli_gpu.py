@@ -23,7 +23,9 @@ def run(*args):
 def test_usage_errors_need_no_model():
     for flags, text in ((["--max-tokens", "0"], "--max-tokens must be at least 1"),
                         (["--temperature", "-1"], "temperature must be 0 or more"),
-                        (["--top-p", "0"], "top_p must be in (0, 1]")):
+                        (["--top-p", "0"], "top_p must be in (0, 1]"),
+                        (["--budget-gib", "8", "--context", "4K"], "--context cannot be used with --budget-gib"),
+                        (["--budget-gib", "0"], "at least 1 GiB")):
         result = run("run", "/nonexistent", "--prompt", "1,2", *flags)
         assert result.returncode == 2 and text in result.stderr
     assert run("run", "/nonexistent", "--prompt", "").returncode == 2
@@ -57,6 +59,18 @@ def test_random_then_run(tmp_path):
 
     info = run("run", folder, "--info", "--context", "1K")
     assert info.returncode == 0 and json.loads(info.stdout)["capacity_tokens"] == 1024
+    memory = json.loads(info.stdout)["memory"]
+    assert memory["binding"] == "context"
+    assert memory["budget_bytes"] == memory["weights_bytes"] + memory["scratch_bytes"] + memory["cache_bytes"]
+
+    # without --context: the most that fits, at most the model's longest sequence
+    most = json.loads(run("run", folder, "--info", "--budget-gib", "1").stdout)
+    assert most["capacity_tokens"] == cfg["max_position_embeddings"] and most["memory"]["binding"] == "budget-gib"
+    # a budget above the automatic one and a context beyond the model are refused with the figures
+    above = run("run", folder, "--info", "--budget-gib", "100000")
+    assert above.returncode == 4 and "above the automatic budget" in above.stderr
+    beyond = run("run", folder, "--info", "--context", "1M")
+    assert beyond.returncode == 4 and "beyond the 1024 tokens" in beyond.stderr
 
     bad = run("run", str(tmp_path), "--prompt", "1")
     assert bad.returncode == 1 and "config.json" in bad.stderr
