@@ -22,6 +22,7 @@
 // product, as the tensor cores take bf16 operands.
 #include <mma.h>
 
+#include "attention_paging.cuh"
 #include "common.cuh"
 
 #ifndef MRUN_HEAD_DIM
@@ -73,25 +74,6 @@ __device__ __forceinline__ unsigned pack_bf16(float lo, float hi) {
 // Rows whose key lies outside [lo, hi] or whose page is not held are zero-filled.  A row's place
 // in the cache is worked out once and used for both tensors.  `page_shift` is log2(page_size)
 // when the page size is a power of two (shift and mask instead of a division), else -1.
-struct Paging {
-    const int* table;
-    int kv_heads, kvh, page_size, page_shift;
-};
-
-__device__ __forceinline__ long cache_row(const Paging& pg, int key, bool& valid) {
-    int block, off;
-    if (pg.page_shift >= 0) {
-        block = key >> pg.page_shift;
-        off = key & (pg.page_size - 1);
-    } else {
-        block = key / pg.page_size;
-        off = key - block * pg.page_size;
-    }
-    const int page = valid ? pg.table[block] : -1;
-    valid = page >= 0;
-    return ((long)(page * pg.kv_heads + pg.kvh) * pg.page_size + off) * D;
-}
-
 __device__ __forceinline__ void load_kv_tiles(bf16* k_tile, bf16* v_tile, const bf16* __restrict__ k_cache,
                                               const bf16* __restrict__ v_cache, const Paging& pg, int key0,
                                               int lo, int hi) {
@@ -103,7 +85,7 @@ __device__ __forceinline__ void load_kv_tiles(bf16* k_tile, bf16* v_tile, const 
         for (int row = r0; row < BLOCK_N; row += STEP) {
             const int key = key0 + row;
             bool valid = key >= lo && key <= hi;
-            const long at = cache_row(pg, key, valid) + chunk * 8;
+            const long at = cache_row<D>(pg, key, valid) + chunk * 8;
             cp_async_16(k_tile + row * LD + chunk * 8, valid ? k_cache + at : k_cache, valid);
             cp_async_16(v_tile + row * LD + chunk * 8, valid ? v_cache + at : v_cache, valid);
         }
@@ -112,7 +94,7 @@ __device__ __forceinline__ void load_kv_tiles(bf16* k_tile, bf16* v_tile, const 
             const int row = c / CHUNKS, chunk = c - row * CHUNKS;
             const int key = key0 + row;
             bool valid = key >= lo && key <= hi;
-            const long at = cache_row(pg, key, valid) + chunk * 8;
+            const long at = cache_row<D>(pg, key, valid) + chunk * 8;
             cp_async_16(k_tile + row * LD + chunk * 8, valid ? k_cache + at : k_cache, valid);
             cp_async_16(v_tile + row * LD + chunk * 8, valid ? v_cache + at : v_cache, valid);
         }
@@ -728,12 +710,6 @@ constexpr size_t DECODE_SMEM = (size_t)(16 + 2 * STAGES * BLOCK_N) * LD * sizeof
 static_assert((size_t)4 * 16 * (D + 2) * sizeof(float) <= (size_t)2 * STAGES * BLOCK_N * LD * sizeof(bf16),
               "the warp merge area must fit in the key/value tiles");
 
-int shift_of(int page_size) {
-    for (int s = 0; s < 31; ++s)
-        if ((1 << s) == page_size) return s;
-    return -1;
-}
-
 int check_common(const char* name, int heads, int kv_heads, int head_dim, int page_size, int max_blocks,
                  int window, int max_group) {
     MRUN_REQUIRE(head_dim == D, "%s: this library was built for head_dim=%d, got %d", name, D, head_dim);
@@ -768,7 +744,7 @@ MRUN_API int mrun_attn_prefill(const void* q, long q_stride, void* out, const vo
     }
     prefill_kernel<<<dim3(n_tiles, kv_heads), THREADS, PREFILL_SMEM, stream>>>(
         (const bf16*)q, q_stride, (bf16*)out, (const bf16*)k_cache, (const bf16*)v_cache, block_tables, max_blocks,
-        token_slot, positions, tile_tok0, tile_ntok, heads, kv_heads, page_size, shift_of(page_size), scale * LOG2E,
+        token_slot, positions, tile_tok0, tile_ntok, heads, kv_heads, page_size, page_shift_of(page_size), scale * LOG2E,
         window);
     MRUN_CHECK_LAUNCH("attn_prefill");
     return 0;
@@ -849,7 +825,7 @@ MRUN_API int mrun_attn_decode(const void* q, long q_stride, void* out, void* k_c
                                      (const bf16*)q, q_stride, (bf16*)out, (const bf16*)k_cache, (const bf16*)v_cache,
                                      block_tables, max_blocks, token_slot, positions, tile_prefix,
                                      (const int4*)assignment, tokens, part_o, part_ml, counters, heads, kv_heads,
-                                     page_size, shift_of(page_size), scale * LOG2E, window, in),
+                                     page_size, page_shift_of(page_size), scale * LOG2E, window, in),
                     "attn_decode");
     return 0;
 }
@@ -945,7 +921,7 @@ MRUN_API int mrun_attn_decode_static(const void* q, long q_stride, void* out, co
     decode_kernel<<<dim3(blocks), THREADS, DECODE_SMEM, stream>>>(
         (const bf16*)q, q_stride, (bf16*)out, (const bf16*)k_cache, (const bf16*)v_cache, block_tables, max_blocks,
         token_slot, positions, tile_prefix, (const int4*)assignment, tokens, part_o, part_ml, counters, heads, kv_heads,
-        page_size, shift_of(page_size), scale * LOG2E, window, FusedInput{});
+        page_size, page_shift_of(page_size), scale * LOG2E, window, FusedInput{});
     MRUN_CHECK_LAUNCH("attn_decode_static");
     return 0;
 }

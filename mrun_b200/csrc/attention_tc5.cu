@@ -1,0 +1,530 @@
+// Paged grouped-query attention for prompt portions on the fifth-generation tensor cores
+// (tcgen05, accumulators in tensor memory), compiled for one head size that is a multiple of 64
+// and at most 128: -DMRUN_HEAD_DIM=<64 | 128>.
+//
+// One thread block per (tile of query tokens, kv head).  The tile's 128 rows are (token, query
+// head of the kv head's group) pairs, so a key/value tile read once serves the whole group.  Keys
+// are consumed 128 at a time in position order with an online softmax:
+//
+//   warps 0..3   softmax: thread r owns row r.  It reads its row of S = Q·Kᵀ from tensor memory
+//                (tcgen05.ld), scales and masks it, keeps the running maximum and sum in 32-bit,
+//                writes P = exp2(s - max) as bf16 into one of two shared-memory buffers in the
+//                swizzled operand layout, and rescales its row of O in tensor memory when the maximum has grown
+//                by more than 2^8 since the last rescale (until then P is taken against the
+//                older maximum, which is exact: the final division uses the same maximum);
+//   warp 4       one lane issues the products: S[j+1] = Q·K[j+1]ᵀ into the other of two S
+//                accumulators while the softmax of tile j runs, then O += P[j]·V[j]
+//                (V as the MN-major operand: its rows are keys, as the cache stores them);
+//   warp 5       brings K tiles from the pages into a ring of two stages by TMA: a lane per page
+//                of the tile looks the page up in the block table and copies its rows as
+//                [rows x 64] boxes with the 128-byte swizzle; warp 6 the V tiles likewise.
+//
+// The roles hand tiles to one another through mbarriers; every wait is bounded by a cycle budget.
+// When a wait runs out the block records a code in the status word, every role stops, the block
+// frees its tensor memory and returns; the host reads the status word after the step and raises.
+//
+// A token at position p sees keys lo..p, lo = 0 or p - window + 1.  Pages that lie wholly
+// outside the tile's range, or that were given back, are never dereferenced; their rows of a
+// stage keep what an earlier tile left there (the V stages start as zeros), and every key outside
+// a row's range is masked.  The page size must be a power of two (pages of 1 .. 128 keys divide
+// a tile, larger pages hold whole tiles).
+// Math as in the other attention kernels: s = scale * q·k, softmax in 32-bit, o = p·v
+// (crates/mrun-engine/src/models/common.rs:129,199-205); P is rounded to bf16 for the second
+// product, as the tensor cores take bf16 operands.
+#include <cstdio>
+
+#include "attention_paging.cuh"
+#include "common.cuh"
+#include "tcgen05.cuh"
+
+#ifndef MRUN_HEAD_DIM
+#error "compile with -DMRUN_HEAD_DIM=<head size>"
+#endif
+
+#if MRUN_HEAD_DIM % 64 == 0 && MRUN_HEAD_DIM <= 128
+#define MRUN_ATTN_TC5 1
+#else
+#define MRUN_ATTN_TC5 0
+#endif
+
+#if MRUN_ATTN_TC5
+
+namespace {
+
+using bf16 = __nv_bfloat16;
+using namespace tc5;
+
+constexpr int D = MRUN_HEAD_DIM;
+constexpr int ROWS = 128;                    // query rows per block = MMA M
+constexpr int KEYS = 128;                    // keys per tile = N of the first product, K of the second
+constexpr int SPANS_D = D / 64;              // 64-wide spans of the head dimension
+constexpr int SPAN_BYTES = 128 * 128;        // one swizzled tile of 128 rows x 64 bf16
+constexpr int Q_BYTES = SPANS_D * SPAN_BYTES;
+constexpr int KV_BYTES = SPANS_D * SPAN_BYTES;          // one stage of K (or V): 128 keys x D
+constexpr int P_BYTES = 2 * SPAN_BYTES;                 // 128 rows x 128 keys
+constexpr int SMEM_BYTES = Q_BYTES + 4 * KV_BYTES + 2 * P_BYTES + 1024;      // two stages of K, V and P
+constexpr int SOFTMAX_THREADS = 128;
+constexpr int THREADS = SOFTMAX_THREADS + 32 + 2 * 32;                  // 224
+constexpr unsigned TMEM_COLS = 512;          // S0 [0,128) S1 [128,256) O [256, 256 + D)
+constexpr unsigned O_COL = 256;
+constexpr float LOG2E = 1.4426950408889634f;
+constexpr float RESCALE_STEP = 8.f;          // log2 of the growth of a row maximum that forces a rescale
+constexpr long long WAIT_CYCLES = 3000000000LL;         // about 1.5 s at 2 GHz
+
+enum : int { STATUS_OK = 0, STATUS_LOADER = 1, STATUS_MMA = 2, STATUS_SOFTMAX = 3 };
+
+// -DMRUN_ATTN_TC5_TIMING: the first block prints where each role's cycles went (a tuning aid).
+#ifdef MRUN_ATTN_TC5_TIMING
+#define TIMING_DECL(n) long long tacc[n] = {}; long long tlast = clock64();
+#define TIMING_MARK(i) { const long long tnow = clock64(); tacc[i] += tnow - tlast; tlast = tnow; }
+#else
+#define TIMING_DECL(n)
+#define TIMING_MARK(i)
+#endif
+
+__device__ __forceinline__ void cp_async_16(void* dst, const void* src, bool valid) {
+    const int bytes = valid ? 16 : 0;        // 0: the destination is zero-filled, the source not read
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(smem_u32(dst)), "l"(src), "r"(bytes));
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::: "memory"); }
+template <int N> __device__ __forceinline__ void cp_async_wait() {
+    asm volatile("cp.async.wait_group %0;\n" ::"n"(N) : "memory");
+}
+__device__ __forceinline__ unsigned pack_bf16(float lo, float hi) {
+    __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<unsigned*>(&v);
+}
+
+// 2^x by the special-function unit (two units in the last place; P is rounded to bf16 after it).
+__device__ __forceinline__ float fast_exp2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+
+// A thread's row of 128 consecutive 32-bit columns: four loads in flight, one wait.  The empty
+// statements after the wait keep the compiler from using a value before the wait.
+__device__ __forceinline__ void tmem_load_row128(unsigned address, float (&v)[128]) {
+    unsigned r[128];
+#pragma unroll
+    for (int c = 0; c < 128; c += 32)
+        asm volatile(
+            "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,"
+            "%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+            : "=r"(r[c + 0]), "=r"(r[c + 1]), "=r"(r[c + 2]), "=r"(r[c + 3]), "=r"(r[c + 4]), "=r"(r[c + 5]),
+              "=r"(r[c + 6]), "=r"(r[c + 7]), "=r"(r[c + 8]), "=r"(r[c + 9]), "=r"(r[c + 10]), "=r"(r[c + 11]),
+              "=r"(r[c + 12]), "=r"(r[c + 13]), "=r"(r[c + 14]), "=r"(r[c + 15]), "=r"(r[c + 16]), "=r"(r[c + 17]),
+              "=r"(r[c + 18]), "=r"(r[c + 19]), "=r"(r[c + 20]), "=r"(r[c + 21]), "=r"(r[c + 22]), "=r"(r[c + 23]),
+              "=r"(r[c + 24]), "=r"(r[c + 25]), "=r"(r[c + 26]), "=r"(r[c + 27]), "=r"(r[c + 28]), "=r"(r[c + 29]),
+              "=r"(r[c + 30]), "=r"(r[c + 31])
+            : "r"(address + c) : "memory");
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+    for (int i = 0; i < 128; ++i) {
+        asm volatile("" : "+r"(r[i]));
+        v[i] = __uint_as_float(r[i]);
+    }
+}
+
+struct Barriers {
+    unsigned long long q_full;
+    unsigned long long k_full[2], k_empty[2], v_full[2], v_empty[2];
+    unsigned long long s_full[2], s_empty[2];
+    unsigned long long p_full[2], pv_done;
+};
+
+__global__ void __launch_bounds__(THREADS, 1)
+prefill_tc5_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
+                   const bf16* __restrict__ q, long q_stride, bf16* __restrict__ out,
+                   const int* __restrict__ block_tables, int max_blocks, const int* __restrict__ token_slot,
+                   const int* __restrict__ positions, const int* __restrict__ tile_tok0,
+                   const int* __restrict__ tile_ntok, int heads, int kv_heads, int page_size, int page_shift,
+                   float scale_log2, int window, int* __restrict__ status) {
+    extern __shared__ __align__(1024) unsigned char smem_raw[];
+    unsigned char* base = reinterpret_cast<unsigned char*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    unsigned char* q_tile = base;
+    unsigned char* k_stages = q_tile + Q_BYTES;
+    unsigned char* v_stages = k_stages + 2 * KV_BYTES;
+    unsigned char* p_tile = v_stages + 2 * KV_BYTES;
+    __shared__ Barriers bars;
+    __shared__ unsigned tmem_base_slot;
+    __shared__ int aborted;
+
+    // the longest tiles (latest positions) first
+    const int tile = gridDim.x - 1 - blockIdx.x, kvh = blockIdx.y;
+    const int group = heads / kv_heads;
+    const int tok0 = tile_tok0[tile], ntok = tile_ntok[tile];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int n_rows = ntok * group;
+    // tokens of a tile are consecutive positions of one request
+    const int pos_first = positions[tok0], pos_last = pos_first + ntok - 1;
+    const int lo_tile = (window > 0 && pos_first - window + 1 > 0) ? pos_first - window + 1 : 0;
+    const int first_block = lo_tile / KEYS, last_block = pos_last / KEYS;
+    const int n_tiles = last_block - first_block + 1;
+
+    if (threadIdx.x == 0) {
+        mbar_init(&bars.q_full, SOFTMAX_THREADS / 32);
+        for (int s = 0; s < 2; ++s) {
+            mbar_init(&bars.k_full[s], 32);                         // every lane of the loader warp arrives
+            mbar_init(&bars.v_full[s], 32);
+            mbar_init(&bars.k_empty[s], 1);
+            mbar_init(&bars.v_empty[s], 1);
+            mbar_init(&bars.s_full[s], 1);
+            mbar_init(&bars.s_empty[s], SOFTMAX_THREADS / 32);      // one arrival per softmax warp
+        }
+        mbar_init(&bars.p_full[0], SOFTMAX_THREADS / 32);
+        mbar_init(&bars.p_full[1], SOFTMAX_THREADS / 32);
+        mbar_init(&bars.pv_done, 1);
+        aborted = 0;
+        mbar_init_fence();
+    }
+    // rows of a V stage that no copy ever fills must not hold NaN patterns: 0 * NaN is NaN
+    for (int i = threadIdx.x; i < 2 * KV_BYTES / 16; i += THREADS)
+        reinterpret_cast<uint4*>(v_stages)[i] = make_uint4(0, 0, 0, 0);
+    fence_async_smem();
+    __syncwarp();
+    if (warp == 0) tmem_alloc(&tmem_base_slot, TMEM_COLS);
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const unsigned tmem_base = tmem_base_slot;
+
+    if (warp < 4) {
+        // ------------------------------------------------------------------------ softmax, rows
+        const int row = threadIdx.x;                                  // 0..127
+        const unsigned lane_base = tmem_base + ((unsigned)(warp * 32) << 16);
+        // q rows: row r = (token r / group, head kvh * group + r % group); rows past n_rows are zero
+        for (int c = threadIdx.x; c < ROWS * (D / 8); c += SOFTMAX_THREADS) {
+            const int r = c / (D / 8), chunk = c - r * (D / 8);
+            const bool valid = r < n_rows;
+            const bf16* src = q;
+            if (valid)
+                src = q + (size_t)(tok0 + r / group) * q_stride + (size_t)(kvh * group + r % group) * D + chunk * 8;
+            cp_async_16(q_tile + (chunk >> 3) * SPAN_BYTES + swizzled_offset(r, chunk & 7), src, valid);
+        }
+        cp_async_commit();
+        cp_async_wait<0>();
+        fence_async_smem();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&bars.q_full);
+
+        const int row_pos = row < n_rows ? pos_first + row / group : -1;      // -1: padding row
+        const int row_lo = (window > 0 && row_pos - window + 1 > 0) ? row_pos - window + 1 : 0;
+        // the tile's last row sees the most recent keys, its first row the oldest
+        const int lo_last = (window > 0 && pos_last - window + 1 > 0) ? pos_last - window + 1 : 0;
+        float m_used = -INFINITY, l = 0.f;
+        bool alive = true;
+        TIMING_DECL(6)
+        for (int j = 0; j < n_tiles; ++j) {
+            const int buf = j & 1;
+            TIMING_MARK(5)
+            if (!__all_sync(0xffffffffu, mbar_wait(&bars.s_full[buf], (j >> 1) & 1, WAIT_CYCLES, &aborted))) { alive = false; break; }
+            tc_fence_after();
+            TIMING_MARK(0)
+            const int key_base = (first_block + j) * KEYS;
+            // every row of the block sees every key of the tile: no comparisons
+            const bool need_mask = key_base + KEYS - 1 > pos_first || key_base < lo_last || n_rows < ROWS;
+            const unsigned s_addr = lane_base + buf * KEYS;
+            // the row's 128 scores, read once; visible keys are lo_rel .. hi_rel of the tile
+            float sc[KEYS];
+            tmem_load_row128(s_addr, sc);
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&bars.s_empty[buf]);          // the next but one S may overwrite it
+            // the largest raw score first (the scale is positive, so it scales the maximum alike);
+            // masked scores become -inf and later give p = 0
+            float mx = -INFINITY;
+            if (need_mask) {
+                const int lo_rel = row_lo - key_base, hi_rel = row_pos - key_base;
+#pragma unroll
+                for (int i = 0; i < KEYS; ++i) {
+                    if (i > hi_rel || i < lo_rel) sc[i] = -INFINITY;
+                    mx = fmaxf(mx, sc[i]);
+                }
+            } else {
+                float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+#pragma unroll
+                for (int i = 0; i < KEYS; i += 4) {
+                    mx4[0] = fmaxf(mx4[0], sc[i]); mx4[1] = fmaxf(mx4[1], sc[i + 1]);
+                    mx4[2] = fmaxf(mx4[2], sc[i + 2]); mx4[3] = fmaxf(mx4[3], sc[i + 3]);
+                }
+                mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
+            }
+            mx *= scale_log2;
+            // the maximum the probabilities are taken against moves only by large steps
+            float m_new = m_used;
+            if (mx > m_used + RESCALE_STEP || (m_used == -INFINITY && mx > -INFINITY)) m_new = mx;
+            const bool moved = m_new != m_used && m_used != -INFINITY;       // O holds something to rescale
+            const bool warp_moved = __any_sync(0xffffffffu, moved);
+            TIMING_MARK(1)
+            // The P buffer of this tile was read by the second product of the tile before last.
+            if (j >= 2) {
+                if (!__all_sync(0xffffffffu, mbar_wait(&bars.v_empty[buf], ((j >> 1) - 1) & 1, WAIT_CYCLES, &aborted))) { alive = false; break; }
+            }
+            TIMING_MARK(2)
+            if (warp_moved) {
+                // O belongs to the second product of the tile before until that has finished
+                if (j > 0) {
+                    if (!__all_sync(0xffffffffu, mbar_wait(&bars.pv_done, (j - 1) & 1, WAIT_CYCLES, &aborted))) { alive = false; break; }
+                    tc_fence_after();
+                }
+                const float corr = moved ? exp2f(m_used - m_new) : 1.f;
+#pragma unroll 1
+                for (int c = 0; c < D; c += 32) {
+                    float v[32];
+                    tmem_load32(lane_base + O_COL + c, v);
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) v[i] *= corr;
+                    tmem_store32(lane_base + O_COL + c, v);
+                }
+                l *= corr;
+            }
+            m_used = m_new;
+            TIMING_MARK(3)
+            // p = 2^(s * scale - m): one fused multiply-add and one special-function call a score.
+            // Masked scores are -inf and give 0; a row that has seen nothing yet keeps m_used = -inf.
+            const float m_sub = m_used == -INFINITY ? 0.f : -m_used;
+            float sum0 = 0.f, sum1 = 0.f;
+#pragma unroll
+            for (int c = 0; c < KEYS; c += 8) {
+                unsigned packed[4];
+#pragma unroll
+                for (int i = 0; i < 8; i += 2) {
+                    const float p0 = fast_exp2(fmaf(sc[c + i], scale_log2, m_sub));
+                    const float p1 = fast_exp2(fmaf(sc[c + i + 1], scale_log2, m_sub));
+                    sum0 += p0;
+                    sum1 += p1;
+                    packed[i >> 1] = pack_bf16(p0, p1);
+                }
+                // eight keys = one 16-byte chunk of the row's 128-byte line in span c / 64
+                *reinterpret_cast<uint4*>(p_tile + buf * P_BYTES + (c >> 6) * SPAN_BYTES + swizzled_offset(row, (c & 63) >> 3)) =
+                    make_uint4(packed[0], packed[1], packed[2], packed[3]);
+            }
+            l += sum0 + sum1;
+            tc_fence_before();
+            fence_async_smem();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&bars.p_full[buf]);
+            TIMING_MARK(4)
+        }
+#ifdef MRUN_ATTN_TC5_TIMING
+        if (blockIdx.x == 0 && blockIdx.y == 0 && threadIdx.x == 0)
+            printf("softmax  tiles %d: wait S %lld, max pass %lld, wait PV %lld, rescale %lld, P pass %lld, other %lld\n",
+                   n_tiles, tacc[0], tacc[1], tacc[2], tacc[3], tacc[4], tacc[5]);
+#endif
+        // a warp leaves the loop as a whole, so every lane takes part in what follows
+        if (alive && !__all_sync(0xffffffffu, mbar_wait(&bars.pv_done, (n_tiles - 1) & 1, WAIT_CYCLES, &aborted))) alive = false;
+        if (!alive) {
+            if (!*(volatile int*)&aborted) atomicExch(status, STATUS_SOFTMAX);
+            atomicExch(&aborted, 1);
+        } else {
+            tc_fence_after();
+            const float inv = l > 0.f ? 1.f / l : 0.f;
+            bf16* dst = out + ((size_t)(tok0 + row / group) * heads + kvh * group + row % group) * D;
+#pragma unroll 1
+            for (int c = 0; c < D; c += 32) {
+                float v[32];
+                tmem_load32(lane_base + O_COL + c, v);         // every lane of the warp takes part
+                if (row < n_rows) {
+#pragma unroll
+                    for (int k = 0; k < 4; ++k)
+                        *reinterpret_cast<uint4*>(dst + c + 8 * k) =
+                            make_uint4(pack_bf16(v[8 * k] * inv, v[8 * k + 1] * inv),
+                                       pack_bf16(v[8 * k + 2] * inv, v[8 * k + 3] * inv),
+                                       pack_bf16(v[8 * k + 4] * inv, v[8 * k + 5] * inv),
+                                       pack_bf16(v[8 * k + 6] * inv, v[8 * k + 7] * inv));
+                }
+            }
+        }
+    } else if (warp == 4) {
+        // ---------------------------------------------------------------------------- MMA issuer
+        if (lane == 0) {
+            constexpr unsigned idesc_qk = instruction_descriptor(ROWS, KEYS);
+            constexpr unsigned idesc_pv = instruction_descriptor(ROWS, D, true);
+            TIMING_DECL(6)
+            bool alive = mbar_wait(&bars.q_full, 0, WAIT_CYCLES, &aborted);
+            auto issue_qk = [&](int j) -> bool {
+                const int s = j & 1;
+                TIMING_MARK(5)
+                if (!mbar_wait(&bars.k_full[s], (j >> 1) & 1, WAIT_CYCLES, &aborted)) return false;
+                TIMING_MARK(0)
+                if (j >= 2 && !mbar_wait(&bars.s_empty[s], ((j >> 1) - 1) & 1, WAIT_CYCLES, &aborted)) return false;
+                TIMING_MARK(1)
+                tc_fence_after();
+                const unsigned char* k_tile = k_stages + s * KV_BYTES;
+#pragma unroll
+                for (int kk = 0; kk < D / 16; ++kk) {
+                    const int off = (kk >> 2) * SPAN_BYTES + (kk & 3) * 32;
+                    umma_bf16(tmem_base + s * KEYS, smem_descriptor(q_tile + off), smem_descriptor(k_tile + off),
+                              idesc_qk, kk > 0 ? 1u : 0u);
+                }
+                umma_commit(&bars.s_full[s]);
+                umma_commit(&bars.k_empty[s]);
+                return true;
+            };
+            if (alive) alive = issue_qk(0);
+            for (int j = 0; alive && j < n_tiles; ++j) {
+                if (j + 1 < n_tiles && !issue_qk(j + 1)) { alive = false; break; }
+                const int s = j & 1;
+                TIMING_MARK(5)
+                if (!mbar_wait(&bars.v_full[s], (j >> 1) & 1, WAIT_CYCLES, &aborted)) { alive = false; break; }
+                TIMING_MARK(2)
+                if (!mbar_wait(&bars.p_full[s], (j >> 1) & 1, WAIT_CYCLES, &aborted)) { alive = false; break; }
+                TIMING_MARK(3)
+                tc_fence_after();
+                const unsigned char* v_tile = v_stages + s * KV_BYTES;
+#pragma unroll
+                for (int kk = 0; kk < KEYS / 16; ++kk) {
+                    // P: 32 bytes further along the keys per step; V: sixteen rows (two groups) further
+                    const unsigned long long a_desc = smem_descriptor(p_tile + s * P_BYTES + (kk >> 2) * SPAN_BYTES + (kk & 3) * 32);
+                    const unsigned long long b_desc = smem_descriptor(v_tile + kk * 2048, SPAN_BYTES, 1024);
+                    umma_bf16(tmem_base + O_COL, a_desc, b_desc, idesc_pv, (j > 0 || kk > 0) ? 1u : 0u);
+                }
+                umma_commit(&bars.v_empty[s]);
+                umma_commit(&bars.pv_done);
+            }
+#ifdef MRUN_ATTN_TC5_TIMING
+            if (blockIdx.x == 0 && blockIdx.y == 0)
+                printf("products tiles %d: wait K %lld, wait S free %lld, wait V %lld, wait P %lld, issue %lld\n", n_tiles,
+                       tacc[0], tacc[1], tacc[2], tacc[3], tacc[5]);
+#endif
+            if (!alive) {
+                if (!*(volatile int*)&aborted) atomicExch(status, STATUS_MMA);
+                atomicExch(&aborted, 1);
+            }
+        }
+    } else {
+        // ------------------------------------------------------------------------------- loaders
+        const bool keys_role = warp == 5;                             // warp 5: K; warp 6: V
+        const CUtensorMap* map = keys_role ? &map_k : &map_v;
+        unsigned char* stages = keys_role ? k_stages : v_stages;
+        unsigned long long* full = keys_role ? bars.k_full : bars.v_full;
+        unsigned long long* empty = keys_role ? bars.k_empty : bars.v_empty;
+        const int* table = block_tables + (size_t)token_slot[tok0] * max_blocks;
+        // pages of up to 128 keys: 128 / page_size boxes of page_size rows; larger pages: one box
+        const int box_rows = page_size < KEYS ? page_size : KEYS;
+        const int boxes = KEYS / box_rows;
+        bool alive = true;
+        TIMING_DECL(6)
+        for (int j = 0; j < n_tiles; ++j) {
+            const int s = j & 1;
+            TIMING_MARK(5)
+            const bool free_now = j < 2 || mbar_wait(&empty[s], ((j >> 1) - 1) & 1, WAIT_CYCLES, &aborted);
+            if (!__all_sync(0xffffffffu, free_now)) { alive = false; break; }
+            TIMING_MARK(0)
+            const int key0 = (first_block + j) * KEYS;
+            unsigned char* stage = stages + s * KV_BYTES;
+            // a lane's boxes: lane, lane + 32, ...  It announces their bytes, then copies them.
+            unsigned bytes = 0;
+            for (int b = lane; b < boxes; b += 32) {
+                const int first_key = key0 + b * box_rows;
+                if (first_key <= pos_last && first_key + box_rows - 1 >= lo_tile && table[first_key >> page_shift] >= 0)
+                    bytes += (unsigned)(box_rows * D * 2);
+            }
+            if (bytes) mbar_expect_tx(&full[s], bytes);
+            else mbar_arrive(&full[s]);
+            for (int b = lane; b < boxes; b += 32) {
+                const int first_key = key0 + b * box_rows;
+                if (first_key > pos_last || first_key + box_rows - 1 < lo_tile) continue;
+                const int page = table[first_key >> page_shift];
+                if (page < 0) continue;
+#pragma unroll
+                for (int h = 0; h < SPANS_D; ++h)
+                    tma_load_4d(stage + h * SPAN_BYTES + b * box_rows * 128, map, h * 64,
+                                first_key & (page_size - 1), kvh, page, &full[s]);
+            }
+            TIMING_MARK(1)
+        }
+#ifdef MRUN_ATTN_TC5_TIMING
+        if (blockIdx.x == 0 && blockIdx.y == 0 && lane == 0)
+            printf("loader %c tiles %d: wait free %lld, issue %lld\n", keys_role ? 'K' : 'V', n_tiles, tacc[0], tacc[1]);
+#endif
+        if (!alive) {
+            if (!*(volatile int*)&aborted) atomicExch(status, STATUS_LOADER);
+            atomicExch(&aborted, 1);
+        }
+    }
+
+    // ---------------------------------------------------------------------------------- teardown
+    tc_fence_before();
+    __syncthreads();
+    if (*(volatile int*)&aborted) {
+        // copies that were requested may still be landing in this block's shared memory
+        const long long start = clock64();
+        while (clock64() - start < 4000000LL) __nanosleep(1000);
+    }
+    if (warp == 0) tmem_dealloc(tmem_base, TMEM_COLS);
+}
+
+// The cache [pages, kv_heads, page_size, D] as a rank-4 tensor read in boxes of [box_rows x 64].
+int make_cache_map(CUtensorMap* map, const void* cache, long pages, int kv_heads, int page_size, int box_rows) {
+    EncodeTiled encode = encode_tiled();
+    MRUN_REQUIRE(encode != nullptr, "attn_prefill_tc5: the driver does not offer cuTensorMapEncodeTiled");
+    const cuuint64_t dims[4] = {(cuuint64_t)D, (cuuint64_t)page_size, (cuuint64_t)kv_heads, (cuuint64_t)pages};
+    const cuuint64_t strides[3] = {(cuuint64_t)D * 2, (cuuint64_t)page_size * D * 2,
+                                   (cuuint64_t)kv_heads * page_size * D * 2};
+    const cuuint32_t box[4] = {64, (cuuint32_t)box_rows, 1, 1};
+    const cuuint32_t elem[4] = {1, 1, 1, 1};
+    const CUresult rc = encode(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void*>(cache), dims, strides, box,
+                               elem, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                               CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    MRUN_REQUIRE(rc == CUDA_SUCCESS, "attn_prefill_tc5: cuTensorMapEncodeTiled failed with code %d", (int)rc);
+    return 0;
+}
+
+}  // namespace
+
+#endif  // MRUN_ATTN_TC5
+
+// 1 when this library holds the tcgen05 prefill kernel (head sizes 64 and 128).
+MRUN_API int mrun_attn_prefill_tc5_available() { return MRUN_ATTN_TC5; }
+
+// Rows per tile of the tcgen05 kernel: a tile holds at most 128 / (heads / kv_heads) tokens.
+MRUN_API int mrun_attn_prefill_tc5_rows() { return 128; }
+
+// As mrun_attn_prefill, with tiles of at most 128 / (heads / kv_heads) tokens, a page size that is
+// a power of two, and `pages` the number of pages of the two cache tensors.  `status` is one
+// int on the device, zero before the first call; a non-zero value afterwards names the role whose
+// wait ran out (1 loader, 2 products, 3 softmax) and the outputs of that launch are void.
+MRUN_API int mrun_attn_prefill_tc5(const void* q, long q_stride, void* out, const void* k_cache,
+                                   const void* v_cache, const int* block_tables, int max_blocks,
+                                   const int* token_slot, const int* positions, const int* tile_tok0,
+                                   const int* tile_ntok, int n_tiles, int heads, int kv_heads, int head_dim,
+                                   int page_size, float scale, int window, long pages, int* status,
+                                   cudaStream_t stream) {
+#if MRUN_ATTN_TC5
+    MRUN_REQUIRE(head_dim == D, "attn_prefill_tc5: this library was built for head_dim=%d, got %d", D, head_dim);
+    MRUN_REQUIRE(heads > 0 && kv_heads > 0 && heads % kv_heads == 0,
+                 "attn_prefill_tc5: heads=%d must be a positive multiple of kv_heads=%d", heads, kv_heads);
+    MRUN_REQUIRE(heads / kv_heads <= ROWS, "attn_prefill_tc5: %d query heads per kv head exceed the supported %d",
+                 heads / kv_heads, ROWS);
+    MRUN_REQUIRE(page_size > 0 && max_blocks > 0 && window >= 0, "attn_prefill_tc5: bad page_size/max_blocks/window");
+    MRUN_REQUIRE(kv_heads <= 65535, "attn_prefill_tc5: kv_heads=%d exceeds 65535", kv_heads);
+    MRUN_REQUIRE(n_tiles >= 0, "attn_prefill_tc5: n_tiles=%d", n_tiles);
+    MRUN_REQUIRE(q_stride % 8 == 0 && ((uintptr_t)q & 15) == 0 && ((uintptr_t)out & 15) == 0 &&
+                 ((uintptr_t)k_cache & 15) == 0 && ((uintptr_t)v_cache & 15) == 0,
+                 "attn_prefill_tc5: q, out and the caches must be 16-byte aligned, q_stride a multiple of 8");
+    MRUN_REQUIRE(status != nullptr, "attn_prefill_tc5: the status word is missing");
+    MRUN_REQUIRE(page_shift_of(page_size) >= 0, "attn_prefill_tc5: page_size=%d is not a power of two", page_size);
+    MRUN_REQUIRE(pages > 0 && pages < (1L << 31), "attn_prefill_tc5: pages=%ld", pages);
+    if (n_tiles == 0) return 0;
+    CUtensorMap map_k, map_v;
+    const int box_rows = page_size < KEYS ? page_size : KEYS;
+    if (int rc = make_cache_map(&map_k, k_cache, pages, kv_heads, page_size, box_rows)) return rc;
+    if (int rc = make_cache_map(&map_v, v_cache, pages, kv_heads, page_size, box_rows)) return rc;
+    static bool configured = false;
+    if (!configured) {
+        MRUN_CHECK_CUDA(cudaFuncSetAttribute(prefill_tc5_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                             SMEM_BYTES), "attn_prefill_tc5");
+        configured = true;
+    }
+    prefill_tc5_kernel<<<dim3(n_tiles, kv_heads), THREADS, SMEM_BYTES, stream>>>(
+        map_k, map_v, (const bf16*)q, q_stride, (bf16*)out, block_tables, max_blocks,
+        token_slot, positions, tile_tok0, tile_ntok, heads, kv_heads, page_size, page_shift_of(page_size),
+        scale * LOG2E, window, status);
+    MRUN_CHECK_LAUNCH("attn_prefill_tc5");
+    return 0;
+#else
+    return mrun_set_error("attn_prefill_tc5: not built for head_dim=%d (head sizes 64 and 128 only)", MRUN_HEAD_DIM);
+#endif
+}

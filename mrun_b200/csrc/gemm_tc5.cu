@@ -31,6 +31,7 @@
 #include <cuda.h>
 
 #include "common.cuh"
+#include "tcgen05.cuh"
 
 #ifndef MRUN_TC5_L2_PROMOTION
 #define MRUN_TC5_L2_PROMOTION CU_TENSOR_MAP_L2_PROMOTION_L2_256B
@@ -47,82 +48,14 @@ constexpr long long WAIT_CYCLES = 3000000000LL;   // about 1.5 s at 2 GHz
 
 enum : int { STATUS_OK = 0, STATUS_PRODUCER_TIMEOUT = 1, STATUS_MMA_TIMEOUT = 2, STATUS_EPILOGUE_TIMEOUT = 3 };
 
-// ------------------------------------------------------------------------------------------ PTX
-__device__ __forceinline__ unsigned smem_u32(const void* p) { return (unsigned)__cvta_generic_to_shared(p); }
+using namespace tc5;
 
-__device__ __forceinline__ void mbar_init(unsigned long long* bar, int count) {
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
-}
-__device__ __forceinline__ void mbar_expect_tx(unsigned long long* bar, unsigned bytes) {
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ bool mbar_try_wait(unsigned long long* bar, unsigned parity) {
-    unsigned done;
-    asm volatile(
-        "{\n.reg .pred p;\n"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
-        "selp.u32 %0, 1, 0, p;\n}"
-        : "=r"(done) : "r"(smem_u32(bar)), "r"(parity) : "memory");
-    return done != 0;
-}
-// Bounded wait: false when the cycle budget ran out.
 __device__ __forceinline__ bool mbar_wait(unsigned long long* bar, unsigned parity) {
-    if (mbar_try_wait(bar, parity)) return true;
-    const long long start = clock64();
-    while (!mbar_try_wait(bar, parity))
-        if (clock64() - start > WAIT_CYCLES) return false;
-    return true;
-}
-__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, int c0, int c1, unsigned long long* bar) {
-    asm volatile(
-        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
-        ::"r"(smem_u32(dst)), "l"(map), "r"(smem_u32(bar)), "r"(c0), "r"(c1) : "memory");
-}
-__device__ __forceinline__ void tmem_alloc(unsigned* slot, unsigned columns) {
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(slot)), "r"(columns) : "memory");
-    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
-}
-__device__ __forceinline__ void tmem_dealloc(unsigned address, unsigned columns) {
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(address), "r"(columns) : "memory");
-}
-__device__ __forceinline__ void umma_bf16(unsigned d_tmem, unsigned long long a_desc, unsigned long long b_desc,
-                                          unsigned idesc, unsigned accumulate) {
-    asm volatile(
-        "{\n.reg .pred p;\n"
-        "setp.ne.b32 p, %4, 0;\n"
-        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}"
-        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
-}
-__device__ __forceinline__ void umma_commit(unsigned long long* bar) {
-    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
-}
-__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tmem_load16(unsigned address, float (&v)[16]) {
-    unsigned r[16];
-    asm volatile(
-        "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];\n"
-        "tcgen05.wait::ld.sync.aligned;"
-        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
-          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
-        : "r"(address) : "memory");
-#pragma unroll
-    for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]);
-}
-
-// Shared-memory operand descriptor: K-major rows of 128 bytes, 128-byte swizzle, groups of eight
-// rows 1024 bytes apart (the layout a TMA box [rows x 64 bf16] with SWIZZLE_128B produces).
-__device__ __forceinline__ unsigned long long smem_descriptor(const void* tile) {
-    unsigned long long d = 0;
-    d |= (unsigned long long)((smem_u32(tile) & 0x3FFFF) >> 4);       // start address, 16-byte units
-    d |= (unsigned long long)(1024 >> 4) << 32;                        // stride between 8-row groups
-    d |= 1ull << 46;                                                   // descriptor version of sm_100
-    d |= 2ull << 61;                                                   // 128-byte swizzle
-    return d;
+    return tc5::mbar_wait(bar, parity, WAIT_CYCLES);
 }
 // Instruction descriptor: D f32, A and B bf16, both K-major, M = 128, N = tokens.
 __host__ __device__ constexpr unsigned instruction_descriptor(int n) {
-    return (1u << 4) | (1u << 7) | (1u << 10) | ((unsigned)(n >> 3) << 17) | ((unsigned)(BLOCK_ROWS >> 4) << 24);
+    return tc5::instruction_descriptor(BLOCK_ROWS, n);
 }
 
 template <typename T> __device__ __forceinline__ void store_out(T* p, float v);
@@ -199,7 +132,7 @@ gemm_tc5_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
             mbar_init(&acc_empty[a], 4);                         // one arrival per epilogue warp
         }
         aborted = 0;
-        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        mbar_init_fence();
     }
     __syncwarp();
     if (warp == 0) tmem_alloc(&tmem_base_slot, TMEM_COLS);
@@ -306,7 +239,7 @@ gemm_tc5_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
                 }
                 tc_fence_before();
                 __syncwarp();
-                if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(&acc_empty[acc])) : "memory");
+                if (lane == 0) mbar_arrive(&acc_empty[acc]);
             } else {
                 float* mine = partial + (((size_t)blockIdx.x * 2 + (seg == 0 ? 0 : 1)) * BLOCK_ROWS + row_in_tile) * TOK;
 #pragma unroll 1
@@ -321,7 +254,7 @@ gemm_tc5_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
                 }
                 tc_fence_before();
                 __syncwarp();
-                if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(&acc_empty[acc])) : "memory");
+                if (lane == 0) mbar_arrive(&acc_empty[acc]);
                 // the blocks that share this tile: p_first .. p_last
                 const int p_first = (tile * k_blocks) / per, p_last = ((tile + 1) * k_blocks - 1) / per;
                 __threadfence();
@@ -369,22 +302,6 @@ gemm_tc5_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
 }
 
 // ------------------------------------------------------------------------------------------ host
-
-typedef CUresult (*EncodeTiled)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
-                                const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
-                                CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-EncodeTiled encode_tiled() {
-    static EncodeTiled fn = [] {
-        void* p = nullptr;
-        cudaDriverEntryPointQueryResult result;
-        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &result) != cudaSuccess ||
-            result != cudaDriverEntryPointSuccess)
-            p = nullptr;
-        return (EncodeTiled)p;
-    }();
-    return fn;
-}
 
 // A [rows x cols] bf16 matrix with `ld` elements between rows, read in boxes of [box_rows x 64].
 int make_map(CUtensorMap* map, const void* base, long rows, long cols, long ld, int box_rows) {

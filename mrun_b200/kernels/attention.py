@@ -7,11 +7,15 @@ the fused norm/rotary/cache kernel just before.
 * bfloat16, every segment a single token: the decode kernel, which deals the key tiles of all
   (token, kv head) pairs evenly to as many blocks as the device holds (scratch for the partial
   results of pairs shared between blocks, merged by the block that finishes last).
-* bfloat16 otherwise: the tiled prefill kernel over (tokens x group heads) row tiles.
+* bfloat16 otherwise: prompt portions.  Head sizes 64 and 128: the tcgen05 kernel (128-row tiles
+  of tokens x group heads, accumulators in tensor memory) for every segment with more rows than
+  one tile of the older kernel; the mma.sync kernel (64-row tiles) for the rest of the step (the
+  single decode tokens of a mixed step, short tails) and for the other head sizes.
 """
 from __future__ import annotations
 
 import ctypes
+import os
 
 import numpy as np
 import torch
@@ -83,14 +87,17 @@ def decode_plan(ctx, library, window: int, kv_heads: int, blocks: int, splits: i
     return plan
 
 
-def prefill_tiles(ctx, tokens_per_tile: int):
-    """(first token row, token count) of every row tile, as device int32 arrays; made once per
-    step and group size."""
-    key = ("attention_tiles", tokens_per_tile)
+def prefill_tiles(ctx, tokens_per_tile: int, longer_than: int = 0, up_to: int = 1 << 30):
+    """(first token row, token count) of every row tile of the segments with more than
+    ``longer_than`` and at most ``up_to`` tokens, as device int32 arrays; made once per step and
+    choice of sizes."""
+    key = ("attention_tiles", tokens_per_tile, longer_than, up_to)
     tiles = ctx.shared.get(key)
     if tiles is None:
         first, count = [], []
         for seg in ctx.segments:
+            if not longer_than < seg.q_len <= up_to:
+                continue
             for t0 in range(0, seg.q_len, tokens_per_tile):
                 first.append(seg.q_start + t0)
                 count.append(min(tokens_per_tile, seg.q_len - t0))
@@ -142,9 +149,35 @@ def paged_attention(q: torch.Tensor, q_stride: int, out: torch.Tensor, cache, gr
         return out
     if raw is not None:
         raise ValueError("raw q, k, v rows are taken by the decode kernel only")
-    first, count, n_tiles = prefill_tiles(ctx, 64 // ratio)
     if tokens > ctx.real_tokens:
         out[ctx.real_tokens:].zero_()
-    library.call("mrun_attn_prefill", _ptr(q), _c_long(q_stride), _ptr(out), *common, _ptr(first),
-                 _ptr(count), _c_int(n_tiles), *tail)
+    short_up_to = 1 << 30
+    if prefill_uses_tcgen05(library, head_dim, ratio, page_size):
+        # segments with more rows than a 64-row tile go to the 128-row tcgen05 kernel
+        short_up_to = (64 // ratio) if ratio <= 64 else 0
+        first, count, n_tiles = prefill_tiles(ctx, 128 // ratio, longer_than=short_up_to)
+        if n_tiles:
+            status = ops.status_word(q.device, "attn_prefill_tc5",
+                                     {1: "a key/value loader", 2: "the MMA issuer", 3: "the softmax warps"})
+            library.call("mrun_attn_prefill_tc5", _ptr(q), _c_long(q_stride), _ptr(out), *common, _ptr(first),
+                         _ptr(count), _c_int(n_tiles), *tail[:-1], _c_long(pages), _ptr(status), tail[-1])
+    if short_up_to:
+        first, count, n_tiles = prefill_tiles(ctx, 64 // ratio, up_to=short_up_to)
+        if n_tiles:
+            library.call("mrun_attn_prefill", _ptr(q), _c_long(q_stride), _ptr(out), *common, _ptr(first),
+                         _ptr(count), _c_int(n_tiles), *tail)
     return out
+
+
+TC5_PREFILL = os.environ.get("MRUN_ATTN_TC5", "1") != "0"      # 0: the mma.sync kernel for every prompt portion
+_tc5_prefill = {}
+
+
+def prefill_uses_tcgen05(library, head_dim: int, ratio: int, page_size: int) -> bool:
+    """Head sizes 64 and 128, pages of a power-of-two size (the kernel copies whole pages by TMA)."""
+    if not TC5_PREFILL or ratio > 128 or page_size & (page_size - 1):
+        return False
+    have = _tc5_prefill.get(head_dim)
+    if have is None:
+        have = _tc5_prefill[head_dim] = bool(library._dll.mrun_attn_prefill_tc5_available())
+    return have

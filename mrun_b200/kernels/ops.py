@@ -217,7 +217,8 @@ def _tc5_buffers(device: torch.device):
     state = _tc5_state.get(device)
     if state is None:
         state = _tc5_state[device] = (torch.zeros(TC5_COUNTERS, dtype=torch.int32, device=device),
-                                      torch.zeros(1, dtype=torch.int32, device=device))
+                                      status_word(device, "gemm_tc5", {1: "the TMA producer", 2: "the MMA issuer",
+                                                                       3: "the epilogue"}))
     return state
 
 
@@ -273,17 +274,28 @@ def gemm_tc5(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype = torch.bf
     return out
 
 
+_status_words = {}       # (device, kernel name) -> (int32[1] on the device, {code: role})
+
+
+def status_word(device: torch.device, kernel: str, roles: dict) -> torch.Tensor:
+    """The word a kernel with bounded waits reports into (zero = fine), one per device and kernel,
+    never reallocated, so that captured graphs may keep its address.  :func:`tc5_check` reads it."""
+    entry = _status_words.get((device, kernel))
+    if entry is None:
+        entry = _status_words[(device, kernel)] = (torch.zeros(1, dtype=torch.int32, device=device), dict(roles))
+    return entry[0]
+
+
 def tc5_check(device: Optional[torch.device] = None) -> None:
-    """Raises if a tcgen05 GEMM on the device gave up on a wait (and clears the status word)."""
-    for dev, (_, status) in list(_tc5_state.items()):
+    """Raises if a tcgen05 kernel on the device gave up on a wait (and clears its status word)."""
+    for (dev, kernel), (status, roles) in list(_status_words.items()):
         if device is not None and dev != device:
             continue
         code = int(status.item())
         if code:
             status.zero_()
-            what = {1: "the TMA producer", 2: "the MMA issuer", 3: "the epilogue"}.get(code, "a role")
-            raise KernelError(f"gemm_tc5: {what} waited longer than its budget on {dev}; the results of that "
-                              f"call are invalid")
+            raise KernelError(f"{kernel}: {roles.get(code, 'a role')} waited longer than its budget on {dev}; "
+                              f"the results of that call are invalid")
 
 
 def linear(x: torch.Tensor, w: torch.Tensor, out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:

@@ -74,7 +74,8 @@ def test_rotary_table(theta, half):
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("heads,kv_heads,head_dim,rotary_dim,page_size", [
-    (4, 2, 16, 16, 16), (6, 3, 32, 32, 8), (5, 5, 48, 24, 4), (8, 1, 128, 128, 16), (3, 1, 80, 80, 32)])
+    (4, 2, 16, 16, 16), (6, 3, 32, 32, 8), (5, 5, 48, 24, 4), (8, 1, 128, 128, 16), (3, 1, 80, 80, 32),
+    (12, 4, 64, 64, 16), (5, 2, 256, 256, 8), (33, 3, 128, 128, 16), (7, 7, 128, 64, 16)])
 def test_qk_norm_rope_cache(dtype, heads, kv_heads, head_dim, rotary_dim, page_size):
     tokens, pages, eps, theta = 11, 9, 1e-5, 10000.0
     width = (heads + 2 * kv_heads) * head_dim
