@@ -6,18 +6,24 @@
 // head of the kv head's group) pairs, so a key/value tile read once serves the whole group.  Keys
 // are consumed 128 at a time in position order with an online softmax:
 //
-//   warps 0..3   softmax: thread r owns row r.  It reads its row of S = Q·Kᵀ from tensor memory
-//                (tcgen05.ld), scales and masks it, keeps the running maximum and sum in 32-bit,
-//                writes P = exp2(s - max) as bf16 into one of two shared-memory buffers in the
-//                swizzled operand layout, and rescales its row of O in tensor memory when the maximum has grown
-//                by more than 2^8 since the last rescale (until then P is taken against the
-//                older maximum, which is exact: the final division uses the same maximum);
-//   warp 4       one lane issues the products: S[j+1] = Q·K[j+1]ᵀ into the other of two S
-//                accumulators while the softmax of tile j runs, then O += P[j]·V[j]
-//                (V as the MN-major operand: its rows are keys, as the cache stores them);
-//   warp 5       brings K tiles from the pages into a ring of two stages by TMA: a lane per page
+//   warps 0..7   softmax.  Tensor-memory lane r is row r; warp w and warp w + 4 share the lanes
+//                32 (w % 4) .., the first takes the row's keys 0..63 of a tile, the second keys
+//                64..127.  A thread reads its half row of S = Q·Kᵀ (tcgen05.ld), masks it, meets
+//                its partner for the row's maximum (through shared memory and a barrier of the
+//                two warps), keeps the running maximum and its half of the sum in 32-bit, and
+//                writes P = exp2(s - max) as packed bf16 into tensor memory (tcgen05.st, one of
+//                two P buffers).  It rescales its half of the row of O when the
+//                maximum has grown by more than 2^8 since the last rescale (until then P is
+//                taken against the older maximum, which is exact: the final division uses the
+//                same maximum);
+//   warp 8       one lane issues the products: S = Q·Kᵀ into one of two S accumulators, up to two
+//                tiles ahead of the softmax (an accumulator is free again once the softmax has
+//                its scores in registers), and O += P[j]·V[j] as soon as P[j] is written.  P is
+//                read from tensor memory, Q, K and V from shared memory, V as the MN-major
+//                operand (its rows are keys, as the cache stores them);
+//   warp 9       brings K tiles from the pages into a ring of two stages by TMA: a lane per page
 //                of the tile looks the page up in the block table and copies its rows as
-//                [rows x 64] boxes with the 128-byte swizzle; warp 6 the V tiles likewise.
+//                [rows x 64] boxes with the 128-byte swizzle; warp 10 the V tiles likewise.
 //
 // The roles hand tiles to one another through mbarriers; every wait is bounded by a cycle budget.
 // When a wait runs out the block records a code in the status word, every role stops, the block
@@ -59,14 +65,15 @@ constexpr int ROWS = 128;                    // query rows per block = MMA M
 constexpr int KEYS = 128;                    // keys per tile = N of the first product, K of the second
 constexpr int SPANS_D = D / 64;              // 64-wide spans of the head dimension
 constexpr int SPAN_BYTES = 128 * 128;        // one swizzled tile of 128 rows x 64 bf16
-constexpr int Q_BYTES = SPANS_D * SPAN_BYTES;
 constexpr int KV_BYTES = SPANS_D * SPAN_BYTES;          // one stage of K (or V): 128 keys x D
-constexpr int P_BYTES = 2 * SPAN_BYTES;                 // 128 rows x 128 keys
-constexpr int SMEM_BYTES = Q_BYTES + 4 * KV_BYTES + 2 * P_BYTES + 1024;      // two stages of K, V and P
-constexpr int SOFTMAX_THREADS = 128;
-constexpr int THREADS = SOFTMAX_THREADS + 32 + 2 * 32;                  // 224
-constexpr unsigned TMEM_COLS = 512;          // S0 [0,128) S1 [128,256) O [256, 256 + D)
-constexpr unsigned O_COL = 256;
+constexpr int Q_BYTES = SPANS_D * SPAN_BYTES;
+constexpr int SMEM_BYTES = Q_BYTES + 4 * KV_BYTES + 1024;                // Q, two stages of K and of V
+constexpr int SOFTMAX_WARPS = 8, SOFTMAX_THREADS = SOFTMAX_WARPS * 32;
+constexpr int MMA_WARP = 8, K_WARP = 9, V_WARP = 10;
+constexpr int THREADS = SOFTMAX_THREADS + 3 * 32;                        // 352
+constexpr unsigned TMEM_COLS = 512;          // S0 [0,128) S1 [128,256) P0 [256,320) P1 [320,384) O [384, 384 + D)
+constexpr unsigned P_COL = 256, O_COL = 384;
+constexpr int O_HALF = D / 2;                // columns of O a thread of a pair looks after
 constexpr float LOG2E = 1.4426950408889634f;
 constexpr float RESCALE_STEP = 8.f;          // log2 of the growth of a row maximum that forces a rescale
 constexpr long long WAIT_CYCLES = 3000000000LL;         // about 1.5 s at 2 GHz
@@ -74,6 +81,9 @@ constexpr long long WAIT_CYCLES = 3000000000LL;         // about 1.5 s at 2 GHz
 enum : int { STATUS_OK = 0, STATUS_LOADER = 1, STATUS_MMA = 2, STATUS_SOFTMAX = 3 };
 
 // -DMRUN_ATTN_TC5_TIMING: the first block prints where each role's cycles went (a tuning aid).
+#ifndef MRUN_ATTN_TC5_EXPERIMENT
+#define MRUN_ATTN_TC5_EXPERIMENT 0
+#endif
 #ifdef MRUN_ATTN_TC5_TIMING
 #define TIMING_DECL(n) long long tacc[n] = {}; long long tlast = clock64();
 #define TIMING_MARK(i) { const long long tnow = clock64(); tacc[i] += tnow - tlast; tlast = tnow; }
@@ -94,43 +104,21 @@ __device__ __forceinline__ unsigned pack_bf16(float lo, float hi) {
     __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
     return *reinterpret_cast<unsigned*>(&v);
 }
-
 // 2^x by the special-function unit (two units in the last place; P is rounded to bf16 after it).
 __device__ __forceinline__ float fast_exp2(float x) {
     float y;
     asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
     return y;
 }
-
-// A thread's row of 128 consecutive 32-bit columns: four loads in flight, one wait.  The empty
-// statements after the wait keep the compiler from using a value before the wait.
-__device__ __forceinline__ void tmem_load_row128(unsigned address, float (&v)[128]) {
-    unsigned r[128];
-#pragma unroll
-    for (int c = 0; c < 128; c += 32)
-        asm volatile(
-            "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,"
-            "%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
-            : "=r"(r[c + 0]), "=r"(r[c + 1]), "=r"(r[c + 2]), "=r"(r[c + 3]), "=r"(r[c + 4]), "=r"(r[c + 5]),
-              "=r"(r[c + 6]), "=r"(r[c + 7]), "=r"(r[c + 8]), "=r"(r[c + 9]), "=r"(r[c + 10]), "=r"(r[c + 11]),
-              "=r"(r[c + 12]), "=r"(r[c + 13]), "=r"(r[c + 14]), "=r"(r[c + 15]), "=r"(r[c + 16]), "=r"(r[c + 17]),
-              "=r"(r[c + 18]), "=r"(r[c + 19]), "=r"(r[c + 20]), "=r"(r[c + 21]), "=r"(r[c + 22]), "=r"(r[c + 23]),
-              "=r"(r[c + 24]), "=r"(r[c + 25]), "=r"(r[c + 26]), "=r"(r[c + 27]), "=r"(r[c + 28]), "=r"(r[c + 29]),
-              "=r"(r[c + 30]), "=r"(r[c + 31])
-            : "r"(address + c) : "memory");
-    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-#pragma unroll
-    for (int i = 0; i < 128; ++i) {
-        asm volatile("" : "+r"(r[i]));
-        v[i] = __uint_as_float(r[i]);
-    }
+// The two warps that share a quarter of the rows meet here (barrier 1 + quarter, 64 threads).
+__device__ __forceinline__ void pair_sync(int quarter) {
+    asm volatile("bar.sync %0, 64;" ::"r"(1 + quarter) : "memory");
 }
 
 struct Barriers {
     unsigned long long q_full;
     unsigned long long k_full[2], k_empty[2], v_full[2], v_empty[2];
-    unsigned long long s_full[2], s_empty[2];
-    unsigned long long p_full[2], pv_done;
+    unsigned long long s_full[2], s_empty[2], p_full[2], pv_done;
 };
 
 __global__ void __launch_bounds__(THREADS, 1)
@@ -145,10 +133,11 @@ prefill_tc5_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_const
     unsigned char* q_tile = base;
     unsigned char* k_stages = q_tile + Q_BYTES;
     unsigned char* v_stages = k_stages + 2 * KV_BYTES;
-    unsigned char* p_tile = v_stages + 2 * KV_BYTES;
     __shared__ Barriers bars;
     __shared__ unsigned tmem_base_slot;
     __shared__ int aborted;
+    __shared__ float pair_max[2][2][ROWS];               // [tile parity][half][row]: the halves' maxima
+    __shared__ float pair_sum[2][ROWS];                  // [half][row]: the halves' sums, at the end
 
     // the longest tiles (latest positions) first
     const int tile = gridDim.x - 1 - blockIdx.x, kvh = blockIdx.y;
@@ -163,17 +152,16 @@ prefill_tc5_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_const
     const int n_tiles = last_block - first_block + 1;
 
     if (threadIdx.x == 0) {
-        mbar_init(&bars.q_full, SOFTMAX_THREADS / 32);
+        mbar_init(&bars.q_full, SOFTMAX_WARPS);                     // one arrival per softmax warp
         for (int s = 0; s < 2; ++s) {
             mbar_init(&bars.k_full[s], 32);                         // every lane of the loader warp arrives
             mbar_init(&bars.v_full[s], 32);
             mbar_init(&bars.k_empty[s], 1);
             mbar_init(&bars.v_empty[s], 1);
             mbar_init(&bars.s_full[s], 1);
-            mbar_init(&bars.s_empty[s], SOFTMAX_THREADS / 32);      // one arrival per softmax warp
+            mbar_init(&bars.s_empty[s], SOFTMAX_WARPS);
+            mbar_init(&bars.p_full[s], SOFTMAX_WARPS);
         }
-        mbar_init(&bars.p_full[0], SOFTMAX_THREADS / 32);
-        mbar_init(&bars.p_full[1], SOFTMAX_THREADS / 32);
         mbar_init(&bars.pv_done, 1);
         aborted = 0;
         mbar_init_fence();
@@ -189,10 +177,11 @@ prefill_tc5_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_const
     tc_fence_after();
     const unsigned tmem_base = tmem_base_slot;
 
-    if (warp < 4) {
-        // ------------------------------------------------------------------------ softmax, rows
-        const int row = threadIdx.x;                                  // 0..127
-        const unsigned lane_base = tmem_base + ((unsigned)(warp * 32) << 16);
+    if (warp < SOFTMAX_WARPS) {
+        // ------------------------------------------------------------------ softmax, half rows
+        const int quarter = warp & 3, half = warp >> 2;
+        const int row = quarter * 32 + lane;                          // 0..127
+        const unsigned lane_base = tmem_base + ((unsigned)(quarter * 32) << 16);
         // q rows: row r = (token r / group, head kvh * group + r % group); rows past n_rows are zero
         for (int c = threadIdx.x; c < ROWS * (D / 8); c += SOFTMAX_THREADS) {
             const int r = c / (D / 8), chunk = c - r * (D / 8);
@@ -212,70 +201,88 @@ prefill_tc5_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_const
         const int row_lo = (window > 0 && row_pos - window + 1 > 0) ? row_pos - window + 1 : 0;
         // the tile's last row sees the most recent keys, its first row the oldest
         const int lo_last = (window > 0 && pos_last - window + 1 > 0) ? pos_last - window + 1 : 0;
-        float m_used = -INFINITY, l = 0.f;
+        float m_used = -INFINITY, l = 0.f;                           // l: this half's share of the row's sum
         bool alive = true;
         TIMING_DECL(6)
+        // A warp that gave up on a wait still walks through the remaining tiles, doing nothing but
+        // meeting its partner at every barrier, so that no warp is left waiting at one.
         for (int j = 0; j < n_tiles; ++j) {
             const int buf = j & 1;
             TIMING_MARK(5)
-            if (!__all_sync(0xffffffffu, mbar_wait(&bars.s_full[buf], (j >> 1) & 1, WAIT_CYCLES, &aborted))) { alive = false; break; }
-            tc_fence_after();
+            if (alive && !__all_sync(0xffffffffu, mbar_wait(&bars.s_full[buf], (j >> 1) & 1, WAIT_CYCLES, &aborted))) alive = false;
             TIMING_MARK(0)
-            const int key_base = (first_block + j) * KEYS;
+            const int key_base = (first_block + j) * KEYS + half * 64;        // of this thread's first score
             // every row of the block sees every key of the tile: no comparisons
-            const bool need_mask = key_base + KEYS - 1 > pos_first || key_base < lo_last || n_rows < ROWS;
-            const unsigned s_addr = lane_base + buf * KEYS;
-            // the row's 128 scores, read once; visible keys are lo_rel .. hi_rel of the tile
-            float sc[KEYS];
-            tmem_load_row128(s_addr, sc);
-            tc_fence_before();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(&bars.s_empty[buf]);          // the next but one S may overwrite it
-            // the largest raw score first (the scale is positive, so it scales the maximum alike);
-            // masked scores become -inf and later give p = 0
+            const bool need_mask = (first_block + j) * KEYS + KEYS - 1 > pos_first || (first_block + j) * KEYS < lo_last ||
+                                   n_rows < ROWS;
+            float sc[64];
             float mx = -INFINITY;
-            if (need_mask) {
-                const int lo_rel = row_lo - key_base, hi_rel = row_pos - key_base;
-#pragma unroll
-                for (int i = 0; i < KEYS; ++i) {
-                    if (i > hi_rel || i < lo_rel) sc[i] = -INFINITY;
-                    mx = fmaxf(mx, sc[i]);
+            if (alive) {
+                tc_fence_after();
+                // the half row's 64 scores, read once
+                unsigned raw[64];
+                {
+                    unsigned (&lo32)[32] = *reinterpret_cast<unsigned (*)[32]>(&raw[0]);
+                    unsigned (&hi32)[32] = *reinterpret_cast<unsigned (*)[32]>(&raw[32]);
+                    tmem_load32_start(lane_base + buf * KEYS + half * 64, lo32);
+                    tmem_load32_start(lane_base + buf * KEYS + half * 64 + 32, hi32);
+                    tmem_load_wait();
                 }
-            } else {
-                float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+                // the scores are in registers: the product after next may overwrite the accumulator
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&bars.s_empty[buf]);
 #pragma unroll
-                for (int i = 0; i < KEYS; i += 4) {
-                    mx4[0] = fmaxf(mx4[0], sc[i]); mx4[1] = fmaxf(mx4[1], sc[i + 1]);
-                    mx4[2] = fmaxf(mx4[2], sc[i + 2]); mx4[3] = fmaxf(mx4[3], sc[i + 3]);
+                for (int i = 0; i < 64; ++i) {
+                    pin(raw[i]);
+                    sc[i] = __uint_as_float(raw[i]);
                 }
-                mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
+                // the largest raw score first (the scale is positive, so it scales the maximum
+                // alike); masked scores become -inf and later give p = 0
+                if (need_mask) {
+                    const int lo_rel = row_lo - key_base, hi_rel = row_pos - key_base;
+#pragma unroll
+                    for (int i = 0; i < 64; ++i) {
+                        if (i > hi_rel || i < lo_rel) sc[i] = -INFINITY;
+                        mx = fmaxf(mx, sc[i]);
+                    }
+                } else {
+                    float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+#pragma unroll
+                    for (int i = 0; i < 64; i += 4) {
+                        mx4[0] = fmaxf(mx4[0], sc[i]); mx4[1] = fmaxf(mx4[1], sc[i + 1]);
+                        mx4[2] = fmaxf(mx4[2], sc[i + 2]); mx4[3] = fmaxf(mx4[3], sc[i + 3]);
+                    }
+                    mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
+                }
             }
-            mx *= scale_log2;
-            // the maximum the probabilities are taken against moves only by large steps
+            // the other half of the row
+            pair_max[buf][half][row] = mx;
+            pair_sync(quarter);
+            if (!alive) continue;
+            mx = fmaxf(mx, pair_max[buf][half ^ 1][row]) * scale_log2;
+            // the maximum the probabilities are taken against moves only by large steps; both
+            // halves of a row decide alike, from the same numbers
             float m_new = m_used;
             if (mx > m_used + RESCALE_STEP || (m_used == -INFINITY && mx > -INFINITY)) m_new = mx;
             const bool moved = m_new != m_used && m_used != -INFINITY;       // O holds something to rescale
             const bool warp_moved = __any_sync(0xffffffffu, moved);
             TIMING_MARK(1)
-            // The P buffer of this tile was read by the second product of the tile before last.
-            if (j >= 2) {
-                if (!__all_sync(0xffffffffu, mbar_wait(&bars.v_empty[buf], ((j >> 1) - 1) & 1, WAIT_CYCLES, &aborted))) { alive = false; break; }
-            }
-            TIMING_MARK(2)
             if (warp_moved) {
                 // O belongs to the second product of the tile before until that has finished
-                if (j > 0) {
-                    if (!__all_sync(0xffffffffu, mbar_wait(&bars.pv_done, (j - 1) & 1, WAIT_CYCLES, &aborted))) { alive = false; break; }
-                    tc_fence_after();
+                if (j > 0 && !__all_sync(0xffffffffu, mbar_wait(&bars.pv_done, (j - 1) & 1, WAIT_CYCLES, &aborted))) {
+                    alive = false;
+                    continue;
                 }
+                tc_fence_after();
                 const float corr = moved ? exp2f(m_used - m_new) : 1.f;
 #pragma unroll 1
-                for (int c = 0; c < D; c += 32) {
+                for (int c = 0; c < O_HALF; c += 32) {
                     float v[32];
-                    tmem_load32(lane_base + O_COL + c, v);
+                    tmem_load32(lane_base + O_COL + half * O_HALF + c, v);
 #pragma unroll
                     for (int i = 0; i < 32; ++i) v[i] *= corr;
-                    tmem_store32(lane_base + O_COL + c, v);
+                    tmem_store32(lane_base + O_COL + half * O_HALF + c, v);
                 }
                 l *= corr;
             }
@@ -285,46 +292,50 @@ prefill_tc5_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_const
             // Masked scores are -inf and give 0; a row that has seen nothing yet keeps m_used = -inf.
             const float m_sub = m_used == -INFINITY ? 0.f : -m_used;
             float sum0 = 0.f, sum1 = 0.f;
+            float packed[32];                                         // two bf16 a word, even key low
 #pragma unroll
-            for (int c = 0; c < KEYS; c += 8) {
-                unsigned packed[4];
-#pragma unroll
-                for (int i = 0; i < 8; i += 2) {
-                    const float p0 = fast_exp2(fmaf(sc[c + i], scale_log2, m_sub));
-                    const float p1 = fast_exp2(fmaf(sc[c + i + 1], scale_log2, m_sub));
-                    sum0 += p0;
-                    sum1 += p1;
-                    packed[i >> 1] = pack_bf16(p0, p1);
-                }
-                // eight keys = one 16-byte chunk of the row's 128-byte line in span c / 64
-                *reinterpret_cast<uint4*>(p_tile + buf * P_BYTES + (c >> 6) * SPAN_BYTES + swizzled_offset(row, (c & 63) >> 3)) =
-                    make_uint4(packed[0], packed[1], packed[2], packed[3]);
+            for (int i = 0; i < 64; i += 2) {
+                const float p0 = fast_exp2(fmaf(sc[i], scale_log2, m_sub));
+                const float p1 = fast_exp2(fmaf(sc[i + 1], scale_log2, m_sub));
+                sum0 += p0;
+                sum1 += p1;
+                packed[i >> 1] = __uint_as_float(pack_bf16(p0, p1));
             }
             l += sum0 + sum1;
+            // the P buffer of this tile was read by the second product of the tile before last
+            if (j >= 2 && !__all_sync(0xffffffffu, mbar_wait(&bars.v_empty[buf], ((j >> 1) - 1) & 1, WAIT_CYCLES, &aborted))) {
+                alive = false;
+                continue;
+            }
+            tmem_store32(lane_base + P_COL + buf * 64 + half * 32, packed);       // this half's keys: words 32 half ..
             tc_fence_before();
-            fence_async_smem();
             __syncwarp();
             if (lane == 0) mbar_arrive(&bars.p_full[buf]);
             TIMING_MARK(4)
         }
 #ifdef MRUN_ATTN_TC5_TIMING
         if (blockIdx.x == 0 && blockIdx.y == 0 && threadIdx.x == 0)
-            printf("softmax  tiles %d: wait S %lld, max pass %lld, wait PV %lld, rescale %lld, P pass %lld, other %lld\n",
-                   n_tiles, tacc[0], tacc[1], tacc[2], tacc[3], tacc[4], tacc[5]);
+            printf("softmax  tiles %d: wait S %lld, max pass %lld, rescale %lld, P pass %lld, other %lld\n",
+                   n_tiles, tacc[0], tacc[1], tacc[3], tacc[4], tacc[5]);
 #endif
         // a warp leaves the loop as a whole, so every lane takes part in what follows
         if (alive && !__all_sync(0xffffffffu, mbar_wait(&bars.pv_done, (n_tiles - 1) & 1, WAIT_CYCLES, &aborted))) alive = false;
         if (!alive) {
             if (!*(volatile int*)&aborted) atomicExch(status, STATUS_SOFTMAX);
             atomicExch(&aborted, 1);
-        } else {
+        }
+        // the row's sum is the two halves' (the partner may have given up: it still comes here)
+        pair_sum[half][row] = l;
+        pair_sync(quarter);
+        if (alive) {
             tc_fence_after();
-            const float inv = l > 0.f ? 1.f / l : 0.f;
-            bf16* dst = out + ((size_t)(tok0 + row / group) * heads + kvh * group + row % group) * D;
+            const float total = l + pair_sum[half ^ 1][row];
+            const float inv = total > 0.f ? 1.f / total : 0.f;
+            bf16* dst = out + ((size_t)(tok0 + row / group) * heads + kvh * group + row % group) * D + half * O_HALF;
 #pragma unroll 1
-            for (int c = 0; c < D; c += 32) {
+            for (int c = 0; c < O_HALF; c += 32) {
                 float v[32];
-                tmem_load32(lane_base + O_COL + c, v);         // every lane of the warp takes part
+                tmem_load32(lane_base + O_COL + half * O_HALF + c, v);       // every lane of the warp takes part
                 if (row < n_rows) {
 #pragma unroll
                     for (int k = 0; k < 4; ++k)
@@ -336,12 +347,26 @@ prefill_tc5_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_const
                 }
             }
         }
-    } else if (warp == 4) {
+    } else if (warp == MMA_WARP) {
         // ---------------------------------------------------------------------------- MMA issuer
         if (lane == 0) {
             constexpr unsigned idesc_qk = instruction_descriptor(ROWS, KEYS);
             constexpr unsigned idesc_pv = instruction_descriptor(ROWS, D, true);
-            TIMING_DECL(6)
+            // The operand descriptors of stage 0, made once: this warp shares its scheduler with
+            // two softmax warps, so every instruction it spends between two products delays them.
+            // Stage 1 lies KV_BYTES further (the address field counts 16-byte units).
+            unsigned long long q_desc[D / 16], k_desc[D / 16], v_desc[KEYS / 16];
+#pragma unroll
+            for (int kk = 0; kk < D / 16; ++kk) {
+                const int off = (kk >> 2) * SPAN_BYTES + (kk & 3) * 32;       // 32 bytes further along d per step
+                q_desc[kk] = smem_descriptor(q_tile + off);
+                k_desc[kk] = smem_descriptor(k_stages + off);
+            }
+#pragma unroll
+            for (int kk = 0; kk < KEYS / 16; ++kk)                            // sixteen rows (two groups) further per step
+                v_desc[kk] = smem_descriptor(v_stages + kk * 2048, SPAN_BYTES, 1024);
+            constexpr unsigned long long STAGE_STEP = KV_BYTES >> 4;
+            TIMING_DECL(9)
             bool alive = mbar_wait(&bars.q_full, 0, WAIT_CYCLES, &aborted);
             auto issue_qk = [&](int j) -> bool {
                 const int s = j & 1;
@@ -351,20 +376,19 @@ prefill_tc5_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_const
                 if (j >= 2 && !mbar_wait(&bars.s_empty[s], ((j >> 1) - 1) & 1, WAIT_CYCLES, &aborted)) return false;
                 TIMING_MARK(1)
                 tc_fence_after();
-                const unsigned char* k_tile = k_stages + s * KV_BYTES;
+                const unsigned long long step = s * STAGE_STEP;
 #pragma unroll
-                for (int kk = 0; kk < D / 16; ++kk) {
-                    const int off = (kk >> 2) * SPAN_BYTES + (kk & 3) * 32;
-                    umma_bf16(tmem_base + s * KEYS, smem_descriptor(q_tile + off), smem_descriptor(k_tile + off),
-                              idesc_qk, kk > 0 ? 1u : 0u);
-                }
+                for (int kk = 0; kk < D / 16; ++kk)
+                    umma_bf16(tmem_base + s * KEYS, q_desc[kk], k_desc[kk] + step, idesc_qk, kk > 0 ? 1u : 0u);
                 umma_commit(&bars.s_full[s]);
                 umma_commit(&bars.k_empty[s]);
+                TIMING_MARK(4)
                 return true;
             };
+            // the first products run two tiles ahead of the softmax, the second follow it
             if (alive) alive = issue_qk(0);
+            if (alive && n_tiles > 1) alive = issue_qk(1);
             for (int j = 0; alive && j < n_tiles; ++j) {
-                if (j + 1 < n_tiles && !issue_qk(j + 1)) { alive = false; break; }
                 const int s = j & 1;
                 TIMING_MARK(5)
                 if (!mbar_wait(&bars.v_full[s], (j >> 1) & 1, WAIT_CYCLES, &aborted)) { alive = false; break; }
@@ -372,21 +396,39 @@ prefill_tc5_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_const
                 if (!mbar_wait(&bars.p_full[s], (j >> 1) & 1, WAIT_CYCLES, &aborted)) { alive = false; break; }
                 TIMING_MARK(3)
                 tc_fence_after();
-                const unsigned char* v_tile = v_stages + s * KV_BYTES;
+                TIMING_MARK(6)
+                const unsigned long long step = s * STAGE_STEP;
+#if MRUN_ATTN_TC5_EXPERIMENT == 1      // timing only: B read as a K-major tile
 #pragma unroll
-                for (int kk = 0; kk < KEYS / 16; ++kk) {
-                    // P: 32 bytes further along the keys per step; V: sixteen rows (two groups) further
-                    const unsigned long long a_desc = smem_descriptor(p_tile + s * P_BYTES + (kk >> 2) * SPAN_BYTES + (kk & 3) * 32);
-                    const unsigned long long b_desc = smem_descriptor(v_tile + kk * 2048, SPAN_BYTES, 1024);
-                    umma_bf16(tmem_base + O_COL, a_desc, b_desc, idesc_pv, (j > 0 || kk > 0) ? 1u : 0u);
-                }
+                for (int kk = 0; kk < KEYS / 16; ++kk)
+                    umma_bf16_a_tmem(tmem_base + O_COL, tmem_base + P_COL + s * 64 + kk * 8, k_desc[kk] + step, idesc_qk,
+                                     (j > 0 || kk > 0) ? 1u : 0u);
+#elif MRUN_ATTN_TC5_EXPERIMENT == 2    // timing only: A read from shared memory
+#pragma unroll
+                for (int kk = 0; kk < KEYS / 16; ++kk)
+                    umma_bf16(tmem_base + O_COL, q_desc[kk], v_desc[kk] + step, idesc_pv, (j > 0 || kk > 0) ? 1u : 0u);
+#elif MRUN_ATTN_TC5_EXPERIMENT == 3    // timing only: the products of a tile written to the S accumulator
+#pragma unroll
+                for (int kk = 0; kk < KEYS / 16; ++kk)
+                    umma_bf16_a_tmem(tmem_base + s * KEYS, tmem_base + P_COL + s * 64 + kk * 8, v_desc[kk] + step, idesc_pv,
+                                     kk > 0 ? 1u : 0u);
+#else
+#pragma unroll
+                for (int kk = 0; kk < KEYS / 16; ++kk)                        // P: eight columns (16 keys) further per step
+                    umma_bf16_a_tmem(tmem_base + O_COL, tmem_base + P_COL + s * 64 + kk * 8, v_desc[kk] + step, idesc_pv,
+                                     (j > 0 || kk > 0) ? 1u : 0u);
+#endif
+                TIMING_MARK(7)
                 umma_commit(&bars.v_empty[s]);
                 umma_commit(&bars.pv_done);
+                TIMING_MARK(8)
+                if (j + 2 < n_tiles && !issue_qk(j + 2)) { alive = false; break; }
             }
 #ifdef MRUN_ATTN_TC5_TIMING
             if (blockIdx.x == 0 && blockIdx.y == 0)
-                printf("products tiles %d: wait K %lld, wait S free %lld, wait V %lld, wait P %lld, issue %lld\n", n_tiles,
-                       tacc[0], tacc[1], tacc[2], tacc[3], tacc[5]);
+                printf("products tiles %d: wait K %lld, wait S free %lld, wait V %lld, wait P %lld, issue QK %lld, other %lld, "
+                       "fence %lld, issue PV %lld, commits %lld\n",
+                       n_tiles, tacc[0], tacc[1], tacc[2], tacc[3], tacc[4], tacc[5], tacc[6], tacc[7], tacc[8]);
 #endif
             if (!alive) {
                 if (!*(volatile int*)&aborted) atomicExch(status, STATUS_MMA);
@@ -395,7 +437,7 @@ prefill_tc5_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_const
         }
     } else {
         // ------------------------------------------------------------------------------- loaders
-        const bool keys_role = warp == 5;                             // warp 5: K; warp 6: V
+        const bool keys_role = warp == K_WARP;                        // one warp for K, one for V
         const CUtensorMap* map = keys_role ? &map_k : &map_v;
         unsigned char* stages = keys_role ? k_stages : v_stages;
         unsigned long long* full = keys_role ? bars.k_full : bars.v_full;

@@ -110,6 +110,22 @@ __device__ __forceinline__ void tmem_load32(unsigned address, float (&v)[32]) {
 #pragma unroll
     for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
 }
+// Starts a load of 32 columns; the values may be used after tmem_load_wait() and pin() of each.
+__device__ __forceinline__ void tmem_load32_start(unsigned address, unsigned (&r)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,"
+        "%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+          "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+          "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(address) : "memory");
+}
+__device__ __forceinline__ void tmem_load_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+// An empty statement that the compiler cannot move a use of `x` across: placed after
+// tmem_load_wait() it keeps the value from being read before the wait.
+__device__ __forceinline__ void pin(unsigned& x) { asm volatile("" : "+r"(x)); }
+
 __device__ __forceinline__ void tmem_store32(unsigned address, const float (&v)[32]) {
     asm volatile(
         "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,"
@@ -137,6 +153,17 @@ __device__ __forceinline__ void umma_bf16(unsigned d_tmem, unsigned long long a_
         "setp.ne.b32 p, %4, 0;\n"
         "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}"
         ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
+}
+// The same with the A operand in tensor memory: lane = row, one 32-bit column per two
+// consecutive values of k (the even one in the low half), so an instruction (k = 16) reads eight
+// columns starting at `a_tmem`.
+__device__ __forceinline__ void umma_bf16_a_tmem(unsigned d_tmem, unsigned a_tmem, unsigned long long b_desc,
+                                                 unsigned idesc, unsigned accumulate) {
+    asm volatile(
+        "{\n.reg .pred p;\n"
+        "setp.ne.b32 p, %4, 0;\n"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n}"
+        ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
 }
 // Arrives on the barrier once every tcgen05.mma issued so far by this thread has finished.
 __device__ __forceinline__ void umma_commit(unsigned long long* bar) {

@@ -244,6 +244,8 @@ class Engine:
             [len(r.output) + 1 for r in sampled],
             [r.recent(REPETITION_CONTEXT) for r in sampled])
         host = tokens.to("cpu").tolist()
+        if plan.num_tokens > len(plan.entries):          # a step with prompt portions: its kernels wait on one another
+            self.executor.check()
         self.stats.tokens_out += len(host)
         self.stats.d2h_bytes += 4 * len(host)
         scheduler.complete(plan, host)

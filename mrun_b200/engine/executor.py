@@ -120,6 +120,12 @@ class Executor:
         self.steps_run += 1
         return logits
 
+    def check(self) -> None:
+        """Raises if a kernel with bounded waits gave up on one since the last check (reads a
+        word from the device, so it waits for the work queued so far)."""
+        from ..kernels import ops
+        ops.tc5_check(self.device)
+
     # ------------------------------------------------------------------ captured decode step
     def decode_bucket(self, rows: int) -> Optional[int]:
         """The captured step size that takes ``rows`` decoding requests, or None."""
