@@ -81,9 +81,6 @@ constexpr long long WAIT_CYCLES = 3000000000LL;         // about 1.5 s at 2 GHz
 enum : int { STATUS_OK = 0, STATUS_LOADER = 1, STATUS_MMA = 2, STATUS_SOFTMAX = 3 };
 
 // -DMRUN_ATTN_TC5_TIMING: the first block prints where each role's cycles went (a tuning aid).
-#ifndef MRUN_ATTN_TC5_EXPERIMENT
-#define MRUN_ATTN_TC5_EXPERIMENT 0
-#endif
 #ifdef MRUN_ATTN_TC5_TIMING
 #define TIMING_DECL(n) long long tacc[n] = {}; long long tlast = clock64();
 #define TIMING_MARK(i) { const long long tnow = clock64(); tacc[i] += tnow - tlast; tlast = tnow; }
@@ -398,26 +395,10 @@ prefill_tc5_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_const
                 tc_fence_after();
                 TIMING_MARK(6)
                 const unsigned long long step = s * STAGE_STEP;
-#if MRUN_ATTN_TC5_EXPERIMENT == 1      // timing only: B read as a K-major tile
-#pragma unroll
-                for (int kk = 0; kk < KEYS / 16; ++kk)
-                    umma_bf16_a_tmem(tmem_base + O_COL, tmem_base + P_COL + s * 64 + kk * 8, k_desc[kk] + step, idesc_qk,
-                                     (j > 0 || kk > 0) ? 1u : 0u);
-#elif MRUN_ATTN_TC5_EXPERIMENT == 2    // timing only: A read from shared memory
-#pragma unroll
-                for (int kk = 0; kk < KEYS / 16; ++kk)
-                    umma_bf16(tmem_base + O_COL, q_desc[kk], v_desc[kk] + step, idesc_pv, (j > 0 || kk > 0) ? 1u : 0u);
-#elif MRUN_ATTN_TC5_EXPERIMENT == 3    // timing only: the products of a tile written to the S accumulator
-#pragma unroll
-                for (int kk = 0; kk < KEYS / 16; ++kk)
-                    umma_bf16_a_tmem(tmem_base + s * KEYS, tmem_base + P_COL + s * 64 + kk * 8, v_desc[kk] + step, idesc_pv,
-                                     kk > 0 ? 1u : 0u);
-#else
 #pragma unroll
                 for (int kk = 0; kk < KEYS / 16; ++kk)                        // P: eight columns (16 keys) further per step
                     umma_bf16_a_tmem(tmem_base + O_COL, tmem_base + P_COL + s * 64 + kk * 8, v_desc[kk] + step, idesc_pv,
                                      (j > 0 || kk > 0) ? 1u : 0u);
-#endif
                 TIMING_MARK(7)
                 umma_commit(&bars.v_empty[s]);
                 umma_commit(&bars.pv_done);

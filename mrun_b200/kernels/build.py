@@ -165,8 +165,7 @@ def build_attention(head_dim: int) -> str:
         defines["MRUN_DECODE_STAGES"] = int(stages)
     if os.environ.get("MRUN_ATTN_TC5_TIMING"):           # tuning aid: the first block prints its roles' cycles
         defines["MRUN_ATTN_TC5_TIMING"] = 1
-        defines["MRUN_ATTN_TC5_EXPERIMENT"] = int(os.environ.get("MRUN_ATTN_TC5_EXPERIMENT", "0"))
-        return build_library(f"mrun_attn_d{head_dim}_timing{defines['MRUN_ATTN_TC5_EXPERIMENT']}", ("common.cu", "attention_mma.cu", "attention_tc5.cu"), defines)
+        return build_library(f"mrun_attn_d{head_dim}_timing", ("common.cu", "attention_mma.cu", "attention_tc5.cu"), defines)
     return build_library(f"mrun_attn_d{head_dim}_s{stages}" if stages else f"mrun_attn_d{head_dim}",
                          ("common.cu", "attention_mma.cu", "attention_tc5.cu"), defines)
 
