@@ -166,8 +166,9 @@ def main() -> int:
                         help="decode batch sizes to run, comma separated (for profiling one point)")
     parser.add_argument("--skip-prefill", action="store_true")
     parser.add_argument("--skip-e2e", action="store_true")
-    parser.add_argument("--profiler-range", action="store_true",
-                        help="bracket the timed decode steps with cudaProfilerStart/Stop")
+    parser.add_argument("--profiler-range", nargs="?", const="decode", default=None, choices=["decode", "prefill"],
+                        help="bracket the timed decode steps (or the last timed prefill) with "
+                             "cudaProfilerStart/Stop, for a profiler started with --profile-from-start off")
     args = parser.parse_args()
 
     if args.impl == "reference":
@@ -214,10 +215,15 @@ def main() -> int:
         request = executor.admit(("prefill", i))
         torch.cuda.synchronize()
         begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        ranged = args.profiler_range == "prefill" and i == 4
+        if ranged:
+            torch.cuda.profiler.start()
         begin.record()
         executor.step([StepEntry(request, prompt, [PREFILL_TOKENS - 1])])
         end.record()
         torch.cuda.synchronize()
+        if ranged:
+            torch.cuda.profiler.stop()
         executor.release(request)
         if i >= 2:
             times.append(begin.elapsed_time(end))
@@ -241,7 +247,7 @@ def main() -> int:
         sampler = ClockSampler()
         if batch == batches[0]:
             sampler.start()
-        ms, n_launch = time_decode(executor, requests, vocab, args.steps, args.warmup, args.profiler_range)
+        ms, n_launch = time_decode(executor, requests, vocab, args.steps, args.warmup, args.profiler_range == "decode")
         if batch == batches[0]:
             clocks = sampler.stop()
             launches = n_launch
