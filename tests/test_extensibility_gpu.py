@@ -1,7 +1,8 @@
 """Parts and arrangements that are not Qwen3's, defined here and run without a change to the
 framework: a mixer that keeps state of a fixed size per request (registered from this file), a
-rotary encoding with its own table, attention with a window, a layer that runs twice, and a layer
-that reads the cache another run wrote.  The toy model is compared with a plain whole-sequence
+rotary encoding with its own table, attention with a window, a layer that runs twice, a layer
+that reads the cache another run wrote, and a feed-forward that routes each token to two of five
+experts.  The toy model is compared with a plain whole-sequence
 implementation under several ways of cutting the work."""
 from __future__ import annotations
 
@@ -224,3 +225,133 @@ def test_toy_model_with_parts_of_its_own(dtype, tolerance):
     r = ex.admit("again")
     check("b", 0, ex.step([StepEntry(r, seqs["b"], range(37))]))
     ex.release(r)
+
+
+# ------------------------------------------------------------------ a feed-forward with routing
+
+EXPERTS, TOP = 5, 2
+
+
+@dataclass(frozen=True)
+class RoutedSpec:
+    """y = sum over the token's TOP experts of gate_e * down_e(silu(gate_proj_e x) * up_proj_e x);
+    gates = softmax of the router's logits over the chosen experts, in 32-bit."""
+    kind: ClassVar[str] = "toy_routed"
+    hidden: int
+    intermediate: int
+    experts: int
+    top: int
+
+
+def register_routed():
+    from mrun_b200.config import TensorSpec
+    from mrun_b200.parts import register_feed_forward
+
+    @register_feed_forward("toy_routed")
+    class RoutedFeedForward:
+        @staticmethod
+        def tensor_specs(spec, prefix):
+            specs = [TensorSpec(f"{prefix}.router.weight", (spec.experts, spec.hidden))]
+            for e in range(spec.experts):
+                specs += [TensorSpec(f"{prefix}.experts.{e}.gate_proj.weight", (spec.intermediate, spec.hidden)),
+                          TensorSpec(f"{prefix}.experts.{e}.up_proj.weight", (spec.intermediate, spec.hidden)),
+                          TensorSpec(f"{prefix}.experts.{e}.down_proj.weight", (spec.hidden, spec.intermediate))]
+            return specs
+
+        def __init__(self, spec, tensors, runtime):
+            self.spec = spec
+            act = runtime.precision.act
+            self.router = tensors["router.weight"].to(runtime.device, torch.float32)
+            take = lambda name: torch.stack([tensors[f"experts.{e}.{name}.weight"] for e in range(spec.experts)]).to(runtime.device, act)
+            self.gate, self.up, self.down = take("gate_proj"), take("up_proj"), take("down_proj")
+
+        def forward(self, x, ctx):
+            # the step's flat token batch is the domain the tokens are sorted by expert in
+            logits = x.float() @ self.router.T
+            top_logits, chosen = logits.topk(self.spec.top, dim=-1)
+            gates = torch.softmax(top_logits, dim=-1)
+            out = torch.zeros(x.shape, dtype=torch.float32, device=x.device)
+            for e in range(self.spec.experts):
+                rows, which = (chosen == e).nonzero(as_tuple=True)
+                if rows.numel() == 0:
+                    continue
+                h = x[rows]
+                act = torch.nn.functional.silu((h @ self.gate[e].T).float()).to(x.dtype) * (h @ self.up[e].T)
+                out.index_add_(0, rows, (act @ self.down[e].T).float() * gates[rows, which][:, None])
+            return out.to(x.dtype)
+
+
+def plain_routed(h, w, prefix):
+    logits = h @ w[f"{prefix}.router.weight"].T
+    top_logits, chosen = logits.topk(TOP, dim=-1)
+    gates = torch.softmax(top_logits, dim=-1)
+    out = torch.zeros_like(h)
+    for t in range(h.shape[0]):
+        for j in range(TOP):
+            out[t] += gates[t, j] * plain.swiglu_mlp(h[t:t + 1], w, f"{prefix}.experts.{int(chosen[t, j])}")[0]
+    return out
+
+
+@pytest.mark.parametrize("dtype,tolerance", [("float32", 3e-5), ("bfloat16", 4e-2)])
+def test_toy_model_with_a_routed_feed_forward(dtype, tolerance):
+    from mrun_b200.config import AttentionSpec, GatedMLPSpec, LayerSpec, ModelSpec, RMSNormSpec, RotarySpec
+    from mrun_b200.engine import Executor, StepEntry
+    from mrun_b200.weights import expected_tensors, random_tensors
+    register_routed()
+    norm = RMSNormSpec(HIDDEN, EPS)
+    attention = AttentionSpec(HIDDEN, HEADS, KV_HEADS, HEAD_DIM, HEAD_DIM ** -0.5, RMSNormSpec(HEAD_DIM, EPS),
+                              RotarySpec(HEAD_DIM, HEAD_DIM, THETA), None)
+    layers = (LayerSpec("model.layers.0", attention, RoutedSpec(HIDDEN, 24, EXPERTS, TOP), norm, norm),
+              LayerSpec("model.layers.1", attention, GatedMLPSpec(HIDDEN, INTER), norm, norm))
+    spec = ModelSpec("ToyRoutedForCausalLM", VOCAB, HIDDEN, 512, layers, norm, tie_embeddings=True)
+    names = {t.name for t in expected_tensors(spec)}
+    assert "model.layers.0.mlp.experts.4.down_proj.weight" in names and "model.layers.1.mlp.gate_proj.weight" in names
+    tensors = dict(random_tensors(spec, seed=5, std=0.08, norm_noise=0.1))
+    w = {k: v.float() for k, v in tensors.items()}
+    ex = Executor(spec, tensors, dtype=dtype, page_size=4, num_pages=64, max_requests=3)
+
+    def plain_model(tokens):
+        positions = torch.arange(len(tokens))
+        x = w["model.embed_tokens.weight"][torch.tensor(tokens)]
+        rms = lambda x, name: plain.rms_norm(x, w[name], EPS)
+        for i in range(2):
+            a, _ = plain_attention(rms(x, f"model.layers.{i}.input_layernorm.weight"), w, f"model.layers.{i}.self_attn",
+                                   positions, True, HEAD_DIM, 1.0, None)
+            x = x + a
+            h = rms(x, f"model.layers.{i}.post_attention_layernorm.weight")
+            x = x + (plain_routed(h, w, "model.layers.0.mlp") if i == 0 else plain.swiglu_mlp(h, w, "model.layers.1.mlp"))
+        return rms(x, "model.norm.weight") @ w["model.embed_tokens.weight"].T
+
+    gen = torch.Generator().manual_seed(4)
+    seqs = {name: torch.randint(0, VOCAB, (n,), generator=gen).tolist() for name, n in (("a", 45), ("b", 23))}
+    want = {name: plain_model(tokens) for name, tokens in seqs.items()}
+    scale = max(float(x.abs().max()) for x in want.values())
+
+    def check(name, start, logits):
+        got = logits.cpu()
+        # a near-tie between two experts may fall the other way in bfloat16: such rows are rare
+        # and would show as a large error in one row, which the tolerance does not hide
+        error = float((got - want[name][start:start + got.shape[0]]).abs().max()) / scale
+        assert error <= tolerance, (name, start, error)
+
+    r = ex.admit("whole")
+    check("a", 0, ex.step([StepEntry(r, seqs["a"], range(45))]))
+    ex.release(r)
+    live = {name: ex.admit(name) for name in seqs}
+    fed = {name: 0 for name in seqs}
+    sizes = {"a": [20, 1, 1, 2, 21], "b": [1, 1, 19, 1, 1]}
+    for turn in range(5):
+        entries, parts = [], []
+        for name in seqs:
+            n = sizes[name][turn]
+            entries.append(StepEntry(live[name], seqs[name][fed[name]:fed[name] + n], range(n)))
+            parts.append((name, fed[name], n))
+            fed[name] += n
+        logits = ex.step(entries)
+        row = 0
+        for name, start, n in parts:
+            check(name, start, logits[row:row + n])
+            row += n
+    for request in live.values():
+        ex.release(request)
+    ex.cache.check_invariants()
