@@ -165,6 +165,10 @@ def main() -> int:
     parser.add_argument("--batches", default=None,
                         help="decode batch sizes to run, comma separated (for profiling one point)")
     parser.add_argument("--skip-prefill", action="store_true")
+    parser.add_argument("--context", type=int, default=CONTEXT,
+                        help="tokens each request holds when decoding is timed (the default is the baseline's)")
+    parser.add_argument("--prefill-depth", type=int, default=0,
+                        help="tokens already in the cache before the timed portion of 2,048 (0: a fresh prompt)")
     parser.add_argument("--skip-e2e", action="store_true")
     parser.add_argument("--profiler-range", nargs="?", const="decode", default=None, choices=["decode", "prefill"],
                         help="bracket the timed decode steps (or the last timed prefill) with "
@@ -198,10 +202,14 @@ def main() -> int:
     if args.batches:
         batches = [int(b) for b in args.batches.split(",")]
     slack = args.steps + args.warmup + 64
-    capacity = max(max(batches) * (CONTEXT + slack), 8 * (CONTEXT + 2 * slack)) + PREFILL_TOKENS + 4 * 64
+    context = args.context
+    capacity = max(max(batches) * (context + slack), 8 * (context + 2 * slack)) + args.prefill_depth + PREFILL_TOKENS + 4 * 64
+    sizes["max_position_embeddings"] = max(sizes["max_position_embeddings"], context + slack + 64,
+                                           args.prefill_depth + PREFILL_TOKENS + 64)
+    config = Qwen3Config(**sizes)
     engine = Engine.from_config(config, seed=0, dtype="bfloat16", page_size=page_size,
                                 num_pages=-(-capacity // page_size), max_requests=max(64, max(batches)),
-                                max_batch_tokens=PREFILL_TOKENS)
+                                max_batch_tokens=max(PREFILL_TOKENS, args.prefill_depth))
     executor = engine.executor
     vocab = config.vocab_size
     kv_bytes = config.kv_bytes_per_token(2)
@@ -213,6 +221,8 @@ def main() -> int:
     times = []
     for i in range(0 if args.skip_prefill else 2 + 3):
         request = executor.admit(("prefill", i))
+        for start in range(0, args.prefill_depth, 4 * PREFILL_TOKENS):        # the depth, untimed
+            executor.step([StepEntry(request, seeded_tokens(vocab, min(4 * PREFILL_TOKENS, args.prefill_depth - start), 5), [])])
         torch.cuda.synchronize()
         begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         ranged = args.profiler_range == "prefill" and i == 4
@@ -233,9 +243,10 @@ def main() -> int:
                                                 + config.num_attention_heads * d * h
                                                 + 3 * h * config.intermediate_size)
     prefill_flops = 2.0 * PREFILL_TOKENS * linear_params + 2.0 * vocab * h \
-        + config.num_hidden_layers * 2.0 * PREFILL_TOKENS ** 2 * config.num_attention_heads * d
+        + config.num_hidden_layers * (2.0 * PREFILL_TOKENS ** 2 + 4.0 * PREFILL_TOKENS * args.prefill_depth) \
+        * config.num_attention_heads * d
     prefill = {"value": round(PREFILL_TOKENS / prefill_ms * 1e3, 1), "tokens": PREFILL_TOKENS,
-               "ms": round(prefill_ms, 3),
+               "ms": round(prefill_ms, 3), **({"depth": args.prefill_depth} if args.prefill_depth else {}),
                "frac": round(prefill_flops / (prefill_ms * 1e-3) / (peaks["bf16_tflops"] * 1e12), 4)}
 
     # ---------------------------------------------------------------- decode at batch 8 / 1 / 64
@@ -243,7 +254,7 @@ def main() -> int:
     clocks = {}
     launches = 0
     for batch in batches:
-        requests = fill_requests(executor, batch, CONTEXT, vocab, f"decode{batch}")
+        requests = fill_requests(executor, batch, context, vocab, f"decode{batch}")
         sampler = ClockSampler()
         if batch == batches[0]:
             sampler.start()
@@ -257,7 +268,7 @@ def main() -> int:
     main_batch = batches[0]
     ms_per_step = results[main_batch] / args.steps
     value = main_batch * args.steps / (results[main_batch] * 1e-3)
-    context_mid = CONTEXT + args.warmup + args.steps / 2.0
+    context_mid = context + args.warmup + args.steps / 2.0
     step_bytes = weight_bytes + main_batch * context_mid * kv_bytes + main_batch * h * 2
     achieved = step_bytes / (ms_per_step * 1e-3) / 1e9
     roofline = {"bound": "hbm", "achieved": round(achieved, 1), "peak": peaks["hbm_gbs"], "unit": "GB/s",
@@ -274,9 +285,9 @@ def main() -> int:
     # takes the eight prompts in one step, so all eight decode side by side for every step of
     # the window that is timed: from the first token of each (read back on the host) to the last.
     from mrun_b200.engine.engine import Engine as EngineClass
-    e2e_engine = EngineClass(executor, max_batch_tokens=main_batch * CONTEXT)
+    e2e_engine = EngineClass(executor, max_batch_tokens=main_batch * context)
     out_tokens = args.steps + 1
-    prompts = [seeded_tokens(vocab, CONTEXT, 50 + i) for i in range(main_batch)]
+    prompts = [seeded_tokens(vocab, context, 50 + i) for i in range(main_batch)]
     e2e_engine.generate(prompts, max_tokens=4, ignore_eos=True)         # warm the prompt step's shapes
     uploaded = executor.staging.bytes_uploaded
     steps_before = e2e_engine.stats.steps
@@ -295,7 +306,7 @@ def main() -> int:
            "d2h_bytes_per_step": round((engine.stats.d2h_bytes - d2h_before) / n_steps, 1)}
 
     line = {
-        "metric": f"decode tok/s at batch {main_batch} (Qwen3-8B bf16, 1,024-token prompts)",
+        "metric": f"decode tok/s at batch {main_batch} (Qwen3-8B bf16, {context:,}-token prompts)",
         "value": round(value, 1), "unit": "tok/s", "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": round(ms_per_step, 4), "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "bf16", "data": "synthetic (seeded uniform token ids, N(0,0.02) weights)",
@@ -305,7 +316,7 @@ def main() -> int:
             "hidden": h, "heads": config.num_attention_heads, "kv_heads": config.num_key_value_heads,
             "head_dim": d, "intermediate": config.intermediate_size, "vocab": vocab,
             "rope_theta": config.rope_theta, "rms_norm_eps": config.rms_norm_eps,
-            "tied": config.tie_word_embeddings, "global_batch": main_batch, "seq_len": CONTEXT,
+            "tied": config.tie_word_embeddings, "global_batch": main_batch, "seq_len": context,
             "max_context": config.max_position_embeddings, "page_size": page_size,
             "parallelism": "single GPU", "l2": "inputs larger than L2 (15 GB of weights per step)",
         },

@@ -1,0 +1,548 @@
+// Paged grouped-query attention for decode steps, keys and values brought by TMA: the same work
+// list, plan, scratch and merge as the decode kernel of attention_mma.cu (a step's 64-key tiles of
+// all (token, kv head) pairs dealt to the blocks; a pair shared between blocks is merged by the one
+// that arrives last), with another way of moving the tiles:
+//
+//   warp 4       the producer.  It walks the block's tiles ahead of the others; for every tile a
+//                lane per page looks the page up in the block table and copies its rows of K and
+//                of V as [rows x 64] boxes (cp.async.bulk.tensor, 128-byte swizzle) into a ring
+//                of two or three stages, each guarded by a full/empty pair of mbarriers.  It
+//                does not stop at the end of a pair: while the other warps merge and write a
+//                pair's result, the first tiles of the next pair are already on their way;
+//   warps 0..3   the consumers: per pair the queries (ready, or normed and rotated here from the
+//                raw projection rows), then per tile each warp takes 16 of the 64 keys with
+//                mma.sync over ldmatrix fragments read through the swizzle, online softmax in
+//                32-bit; the four warps' results meet in a small buffer of their own, so the
+//                ring is never drained.
+//
+// A stage is 2 x 64 x D x 2 bytes without padding (the swizzle keeps ldmatrix free of bank
+// conflicts), so two blocks with three stages each fit a multiprocessor at D = 128 and up to five
+// tiles a multiprocessor are in flight.  Head sizes 64 and 128, page sizes that are powers of
+// two, at most 16 query heads per kv head.  Every mbarrier wait is bounded; a wait that runs out
+// sets the status word (the host reads it after the step and raises) and the block runs to its
+// end without waiting again.
+//
+// Math as in the other attention kernels (crates/mrun-engine/src/models/common.rs:129,199-205).
+#include "attention_frag.cuh"
+#include "tcgen05.cuh"
+
+#if MRUN_HEAD_DIM % 64 == 0 && MRUN_HEAD_DIM <= 128
+#define MRUN_DECODE_TMA 1
+#else
+#define MRUN_DECODE_TMA 0
+#endif
+
+#if MRUN_DECODE_TMA
+
+namespace {
+
+using namespace tc5;
+
+constexpr int SPANS = D / 64;                        // 64-wide spans of the head dimension
+constexpr int SPAN_BYTES = BLOCK_N * 128;            // 64 rows x 128 bytes
+constexpr int TILE_BYTES = SPANS * SPAN_BYTES;       // one K (or V) tile
+constexpr int STAGE_BYTES = 2 * TILE_BYTES;          // K then V
+constexpr int CONSUMERS = 128, TMA_THREADS = CONSUMERS + 32;
+constexpr int MS = D + 2;                            // a merged row: D values, maximum, sum
+constexpr long long WAIT_CYCLES = 3000000000LL;      // about 1.5 s at 2 GHz
+
+enum : int { STATUS_PRODUCER = 1, STATUS_CONSUMER = 2 };
+
+__host__ __device__ constexpr size_t tma_smem_bytes(int ring, int group) {
+    return (size_t)ring * STAGE_BYTES + 1024                           // the ring, 1024-byte aligned
+           + (size_t)16 * LD * sizeof(bf16)                             // q rows
+           + (size_t)4 * group * MS * sizeof(float)                     // the four warps' results
+           + (size_t)4 * D * sizeof(float) + 2 * D * sizeof(bf16);      // head staging, the step's own k and v
+}
+
+// Address of the 16-byte chunk `chunk` (0 .. D/8 - 1) of row `row` of a swizzled tile.
+__device__ __forceinline__ const unsigned char* swz(const unsigned char* tile, int row, int chunk) {
+    return tile + (chunk >> 3) * SPAN_BYTES + row * 128 + (((chunk & 7) ^ (row & 7)) << 4);
+}
+
+__device__ __forceinline__ void consumer_sync() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
+
+// One 16-row warp tile against the 16 keys krow0 .. krow0+15 of a swizzled K and V tile: the same
+// arithmetic as attend_tile<16>, with the fragments fetched through the swizzle.
+__device__ __forceinline__ void attend_slice(const bf16* q_tile, const unsigned char* k_tile, const unsigned char* v_tile,
+                                             int krow0, int key_base, float scale_log2, const int (&row_pos)[2],
+                                             const int (&row_lo)[2], float (&m)[2], float (&l)[2], float (&o)[D / 8][4]) {
+    const int lane = threadIdx.x & 31;
+    float s[2][4];
+#pragma unroll
+    for (int i = 0; i < 2; ++i) s[i][0] = s[i][1] = s[i][2] = s[i][3] = 0.f;
+#pragma unroll
+    for (int kk = 0; kk < D / 16; ++kk) {
+        unsigned a[4], b[4];
+        ldmatrix_x4(a, q_tile + ((lane & 7) + ((lane >> 3) & 1) * 8) * LD + kk * 16 + (lane >> 4) * 8);
+        ldmatrix_x4(b, swz(k_tile, krow0 + (lane & 7) + (lane >> 4) * 8, kk * 2 + ((lane >> 3) & 1)));
+        mma_bf16(s[0], a, b[0], b[1]);
+        mma_bf16(s[1], a, b[2], b[3]);
+    }
+    float mx[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+    for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            const int r = e >> 1;
+            float v = s[nt][e] * scale_log2;
+            const int key = key_base + krow0 + nt * 8 + (lane & 3) * 2 + (e & 1);
+            if (key > row_pos[r] || key < row_lo[r]) v = -INFINITY;
+            s[nt][e] = v;
+            mx[r] = fmaxf(mx[r], v);
+        }
+    float corr[2];
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+        mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 1));
+        mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 2));
+        const float m_new = fmaxf(m[r], mx[r]);
+        corr[r] = (m[r] == -INFINITY) ? 0.f : exp2f(m[r] - m_new);
+        m[r] = m_new;
+    }
+    float sum[2] = {0.f, 0.f};
+#pragma unroll
+    for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            const int r = e >> 1;
+            const float p = (m[r] == -INFINITY) ? 0.f : exp2f(s[nt][e] - m[r]);
+            s[nt][e] = p;
+            sum[r] += p;
+        }
+#pragma unroll
+    for (int r = 0; r < 2; ++r) l[r] = l[r] * corr[r] + sum[r];       // per-thread partial; reduced at the end
+#pragma unroll
+    for (int dt = 0; dt < D / 8; ++dt) {
+        o[dt][0] *= corr[0]; o[dt][1] *= corr[0];
+        o[dt][2] *= corr[1]; o[dt][3] *= corr[1];
+    }
+    unsigned a[4];
+    a[0] = pack_bf16(s[0][0], s[0][1]);
+    a[1] = pack_bf16(s[0][2], s[0][3]);
+    a[2] = pack_bf16(s[1][0], s[1][1]);
+    a[3] = pack_bf16(s[1][2], s[1][3]);
+#pragma unroll
+    for (int dt = 0; dt < D / 8; dt += 2) {
+        unsigned b[4];
+        ldmatrix_x4_trans(b, swz(v_tile, krow0 + (lane & 7) + ((lane >> 3) & 1) * 8, dt + (lane >> 4)));
+        mma_bf16(o[dt], a, b[0], b[1]);
+        mma_bf16(o[dt + 1], a, b[2], b[3]);
+    }
+}
+
+// The pair that tile `u` of the flat list belongs to, found as the consumers and the producer walk
+// the block's range: `tok`/`kvh` come in as the pair of the tile before (or the plan's start).
+struct Segment {
+    int kvh, tok, j0, len, pair_tiles, pair_start, pos, lo, first_block, last_block;
+    bool complete;
+};
+
+__device__ __forceinline__ Segment next_segment(int seg, int u, int u_end, int& kvh, int& tok, int tiles_per_head,
+                                                const int* __restrict__ prefix, const int* __restrict__ positions,
+                                                int window) {
+    if (seg > 0) {
+        ++tok;
+        if (u - kvh * tiles_per_head >= tiles_per_head) {
+            ++kvh;
+            tok = 0;
+        }
+    }
+    const int r = u - kvh * tiles_per_head;
+    while (prefix[tok + 1] <= r) ++tok;                          // skip tokens without tiles (padding)
+    Segment sg;
+    sg.kvh = kvh;
+    sg.tok = tok;
+    sg.pair_tiles = prefix[tok + 1] - prefix[tok];
+    sg.j0 = r - prefix[tok];
+    sg.len = min(u_end - u, sg.pair_tiles - sg.j0);
+    sg.complete = sg.j0 == 0 && sg.len == sg.pair_tiles;
+    sg.pair_start = kvh * tiles_per_head + prefix[tok];
+    sg.pos = positions[tok];
+    sg.lo = (window > 0 && sg.pos - window + 1 > 0) ? sg.pos - window + 1 : 0;
+    sg.first_block = sg.lo / BLOCK_N + sg.j0;
+    sg.last_block = sg.first_block + sg.len - 1;
+    return sg;
+}
+
+// grid: `blocks` blocks, the number the plan was made for.  Scratch as for decode_kernel.
+template <int RING>
+__global__ void __launch_bounds__(TMA_THREADS)
+decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
+                  const bf16* __restrict__ q, long q_stride, bf16* __restrict__ out,
+                  const int* __restrict__ block_tables, int max_blocks, const int* __restrict__ token_slot,
+                  const int* __restrict__ positions, const int* __restrict__ tile_prefix,
+                  const int4* __restrict__ assignment, int tokens, float* __restrict__ part_o,
+                  float* __restrict__ part_ml, int* __restrict__ counters, int heads, int kv_heads, int page_size,
+                  int page_shift, float scale_log2, int window, const FusedInput fused, int* __restrict__ status) {
+    extern __shared__ __align__(1024) unsigned char smem_raw[];
+    unsigned char* ring = reinterpret_cast<unsigned char*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    const int group = heads / kv_heads;
+    bf16* q_tile = reinterpret_cast<bf16*>(ring + RING * STAGE_BYTES);                   // [16][LD]
+    float* merge = reinterpret_cast<float*>(q_tile + 16 * LD);                            // [4][group][MS]
+    float (*head_vec)[D] = reinterpret_cast<float (*)[D]>(merge + 4 * group * MS);        // [4][D]
+    bf16* new_k = reinterpret_cast<bf16*>(head_vec + 4);                                  // this step's own key, value
+    bf16* new_v = new_k + D;
+    __shared__ unsigned long long full_bar[RING], empty_bar[RING];
+    __shared__ int ticket_shared, aborted;
+
+    const int block_id = blockIdx.x, n_blocks_grid = gridDim.x;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int4 mine = assignment[2 * block_id], shape = assignment[2 * block_id + 1];
+    const int u_begin = mine.x, u_end = mine.y;
+    const int tiles_per_head = shape.x, per = shape.y, splits = shape.z;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < RING; ++s) {
+            mbar_init(&full_bar[s], 32);                 // every lane of the producer arrives
+            mbar_init(&empty_bar[s], 4);                 // one arrival per consumer warp
+        }
+        aborted = 0;
+        mbar_init_fence();
+    }
+    // rows of a V tile that no copy fills must not hold NaN patterns: 0 * NaN is NaN
+    for (int s = 0; s < RING; ++s)
+        for (int i = threadIdx.x; i < TILE_BYTES / 16; i += TMA_THREADS)
+            reinterpret_cast<uint4*>(ring + s * STAGE_BYTES + TILE_BYTES)[i] = make_uint4(0, 0, 0, 0);
+    fence_async_smem();
+    __syncthreads();
+
+    if (warp == 4) {
+        // ------------------------------------------------------------------------------ producer
+        const int box_rows = page_size < BLOCK_N ? page_size : BLOCK_N;
+        const int boxes = BLOCK_N / box_rows;
+        int kvh = mine.z, tok = mine.w, u = u_begin, it = 0;
+        bool alive = true;
+        for (int seg = 0; alive && u < u_end; ++seg) {
+            const Segment sg = next_segment(seg, u, u_end, kvh, tok, tiles_per_head, tile_prefix, positions, window);
+            const int* table = block_tables + (size_t)token_slot[sg.tok] * max_blocks;
+            for (int block = sg.first_block; block <= sg.last_block; ++block, ++it) {
+                const int s = it % RING, use = it / RING;
+                const bool free_now = use == 0 || mbar_wait(&empty_bar[s], (use - 1) & 1, WAIT_CYCLES, &aborted);
+                if (!__all_sync(0xffffffffu, free_now)) { alive = false; break; }
+                unsigned char* stage = ring + s * STAGE_BYTES;
+                const int key0 = block * BLOCK_N;
+                // a lane's boxes: lane, lane + 32, ...  It announces their bytes, then copies them.
+                unsigned bytes = 0;
+                for (int b = lane; b < boxes; b += 32) {
+                    const int first_key = key0 + b * box_rows;
+                    if (first_key <= sg.pos && first_key + box_rows - 1 >= sg.lo && table[first_key >> page_shift] >= 0)
+                        bytes += (unsigned)(2 * box_rows * D * 2);
+                }
+                if (bytes) mbar_expect_tx(&full_bar[s], bytes);
+                else mbar_arrive(&full_bar[s]);
+                for (int b = lane; b < boxes; b += 32) {
+                    const int first_key = key0 + b * box_rows;
+                    if (first_key > sg.pos || first_key + box_rows - 1 < sg.lo) continue;
+                    const int page = table[first_key >> page_shift];
+                    if (page < 0) continue;
+#pragma unroll
+                    for (int h = 0; h < SPANS; ++h) {
+                        tma_load_4d(stage + h * SPAN_BYTES + b * box_rows * 128, &map_k, h * 64,
+                                    first_key & (page_size - 1), sg.kvh, page, &full_bar[s]);
+                        tma_load_4d(stage + TILE_BYTES + h * SPAN_BYTES + b * box_rows * 128, &map_v, h * 64,
+                                    first_key & (page_size - 1), sg.kvh, page, &full_bar[s]);
+                    }
+                }
+            }
+            u += sg.len;
+        }
+        if (!alive) {
+            if (!*(volatile int*)&aborted) atomicExch(status, STATUS_PRODUCER);
+            atomicExch(&aborted, 1);
+        }
+    } else {
+        // ----------------------------------------------------------------------------- consumers
+        // padding rows come out as zeros
+        for (int t = block_id; t < tokens; t += n_blocks_grid)
+            if (positions[t] < 0)
+                for (int i = threadIdx.x; i < heads * D; i += CONSUMERS) out[(size_t)t * heads * D + i] = __float2bfloat16_rn(0.f);
+
+        // A warp whose wait ran out sets the flag and keeps walking (its later waits return at once,
+        // its numbers are void), so that every barrier of the four warps is still met by all.
+        int kvh = mine.z, tok = mine.w, u = u_begin, it = 0;
+        bool alive = true;
+        for (int seg = 0; u < u_end; ++seg) {
+            const Segment sg = next_segment(seg, u, u_end, kvh, tok, tiles_per_head, tile_prefix, positions, window);
+            const int pos = sg.pos, lo = sg.lo;
+            const int b1 = pos / BLOCK_N;
+            float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
+            float o[D / 8][4];
+#pragma unroll
+            for (int dt = 0; dt < D / 8; ++dt) o[dt][0] = o[dt][1] = o[dt][2] = o[dt][3] = 0.f;
+
+            const bool owns_new_token = fused.enabled && sg.last_block == b1;
+            if (!fused.enabled) {
+                for (int c = threadIdx.x; c < 16 * CHUNKS; c += CONSUMERS) {
+                    const int row = c / CHUNKS, chunk = c - row * CHUNKS;
+                    uint4 value = make_uint4(0, 0, 0, 0);
+                    if (row < group)
+                        value = *reinterpret_cast<const uint4*>(q + (size_t)sg.tok * q_stride + (size_t)(sg.kvh * group + row) * D + chunk * 8);
+                    *reinterpret_cast<uint4*>(q_tile + row * LD + chunk * 8) = value;
+                }
+            } else {
+                // q, k and v arrive raw: [q heads | k heads | v heads] of D elements each in the token's row
+                const bf16* token_row = q + (size_t)sg.tok * q_stride;
+                const float2* cs = fused.rot ? fused.rot + (size_t)sg.tok * (fused.rotary_dim >> 1) : nullptr;
+                for (int row = warp; row < 16; row += 4) {
+                    if (row < group)
+                        norm_rotate_head(token_row + (size_t)(sg.kvh * group + row) * D, fused.q_weight, fused.eps, cs,
+                                         fused.rotary_dim, head_vec[warp], q_tile + row * LD);
+                    else
+                        for (int e = lane; e < D; e += 32) q_tile[row * LD + e] = __float2bfloat16_rn(0.f);
+                }
+                if (owns_new_token) {
+                    // the block that holds the pair's last tile makes the token's own key and value: into
+                    // the page for later steps, and into shared memory for this one
+                    if (warp == 0)
+                        norm_rotate_head(token_row + (size_t)(heads + sg.kvh) * D, fused.k_weight, fused.eps, cs,
+                                         fused.rotary_dim, head_vec[0], new_k);
+                    if (warp == 1)
+                        for (int e = lane; e < D; e += 32) new_v[e] = token_row[(size_t)(heads + kv_heads + sg.kvh) * D + e];
+                    consumer_sync();
+                    const int slot = fused.slots ? fused.slots[sg.tok] : -1;
+                    if (slot >= 0) {
+                        const int page = slot / page_size, off = slot - page * page_size;
+                        const size_t at = (((size_t)page * kv_heads + sg.kvh) * page_size + off) * D;
+                        for (int c = threadIdx.x; c < 2 * CHUNKS; c += CONSUMERS) {
+                            const bool is_v = c >= CHUNKS;
+                            const int chunk = is_v ? c - CHUNKS : c;
+                            *reinterpret_cast<uint4*>((is_v ? fused.v_cache : fused.k_cache) + at + chunk * 8) =
+                                *reinterpret_cast<const uint4*>((is_v ? new_v : new_k) + chunk * 8);
+                        }
+                    }
+                }
+            }
+            consumer_sync();                                    // q (and the new key and value) are in place
+
+            int row_pos[2], row_lo[2];
+#pragma unroll
+            for (int rr = 0; rr < 2; ++rr) {
+                const int row = (lane >> 2) + rr * 8;
+                row_pos[rr] = row < group ? pos : -1;
+                row_lo[rr] = lo;
+            }
+            for (int block = sg.first_block; block <= sg.last_block; ++block, ++it) {
+                const int s = it % RING, use = it / RING;
+                if (!__all_sync(0xffffffffu, mbar_wait(&full_bar[s], use & 1, WAIT_CYCLES, &aborted)) && alive) {
+                    alive = false;
+                    if (lane == 0) {
+                        if (!*(volatile int*)&aborted) atomicExch(status, STATUS_CONSUMER);
+                        atomicExch(&aborted, 1);
+                    }
+                }
+                unsigned char* k_tile = ring + s * STAGE_BYTES;
+                unsigned char* v_tile = k_tile + TILE_BYTES;
+                const int key_base = block * BLOCK_N;
+                if (owns_new_token && block == b1) {
+                    // the page row of this step's token was not written when the tile was requested
+                    const int row = pos - key_base;
+                    for (int c = threadIdx.x; c < 2 * CHUNKS; c += CONSUMERS) {
+                        const bool is_v = c >= CHUNKS;
+                        const int chunk = is_v ? c - CHUNKS : c;
+                        *reinterpret_cast<uint4*>(const_cast<unsigned char*>(swz(is_v ? v_tile : k_tile, row, chunk))) =
+                            *reinterpret_cast<const uint4*>((is_v ? new_v : new_k) + chunk * 8);
+                    }
+                    consumer_sync();
+                }
+                // warp w takes keys 16w .. 16w+15 of the tile
+                if (key_base + warp * 16 <= pos && key_base + warp * 16 + 15 >= lo)
+                    attend_slice(q_tile, k_tile, v_tile, warp * 16, key_base, scale_log2, row_pos, row_lo, m, l, o);
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&empty_bar[s]);
+            }
+#pragma unroll
+            for (int rr = 0; rr < 2; ++rr) {
+                l[rr] += __shfl_xor_sync(0xffffffffu, l[rr], 1);
+                l[rr] += __shfl_xor_sync(0xffffffffu, l[rr], 2);
+            }
+            // the four warps meet: merge[warp][row < group][D + 2]
+#pragma unroll
+            for (int rr = 0; rr < 2; ++rr) {
+                const int row = (lane >> 2) + rr * 8;
+                if (row < group) {
+                    float* dst = merge + (warp * group + row) * MS;
+#pragma unroll
+                    for (int dt = 0; dt < D / 8; ++dt) {
+                        dst[dt * 8 + (lane & 3) * 2] = o[dt][2 * rr];
+                        dst[dt * 8 + (lane & 3) * 2 + 1] = o[dt][2 * rr + 1];
+                    }
+                    if ((lane & 3) == 0) {
+                        dst[D] = m[rr];
+                        dst[D + 1] = l[rr];
+                    }
+                }
+            }
+            consumer_sync();
+            const size_t my_slot = (size_t)block_id * 2 + (seg == 0 ? 0 : 1);
+            for (int i = threadIdx.x; i < group * D; i += CONSUMERS) {
+                const int row = i / D, d = i - row * D;
+                float mm = -INFINITY;
+#pragma unroll
+                for (int w = 0; w < 4; ++w) mm = fmaxf(mm, merge[(w * group + row) * MS + D]);
+                float acc = 0.f, ll = 0.f;
+#pragma unroll
+                for (int w = 0; w < 4; ++w) {
+                    const float* src = merge + (w * group + row) * MS;
+                    const float c = (src[D] == -INFINITY) ? 0.f : exp2f(src[D] - mm);
+                    acc += src[d] * c;
+                    ll += src[D + 1] * c;
+                }
+                if (sg.complete) {
+                    out[((size_t)sg.tok * heads + sg.kvh * group + row) * D + d] = __float2bfloat16_rn(ll > 0.f ? acc / ll : 0.f);
+                } else {
+                    part_o[(my_slot * 16 + row) * D + d] = acc;
+                    if (d == 0) {
+                        part_ml[(my_slot * 16 + row) * 2] = mm;
+                        part_ml[(my_slot * 16 + row) * 2 + 1] = ll;
+                    }
+                }
+            }
+            if (!sg.complete) {
+                // the blocks that share this pair are p_first .. p_last; the last to arrive merges their
+                // pieces in block order
+                int p_first, p_last;
+                if (splits > 0) {            // the pair's own run of blocks, as many as have tiles
+                    p_first = (sg.kvh * tokens + sg.tok) * splits;
+                    p_last = p_first + (sg.pair_tiles + per - 1) / per - 1;
+                } else {
+                    p_first = sg.pair_start / per;
+                    p_last = (sg.pair_start + sg.pair_tiles - 1) / per;
+                }
+                __threadfence();
+                consumer_sync();
+                if (threadIdx.x == 0) ticket_shared = atomicAdd(&counters[sg.tok * kv_heads + sg.kvh], 1);
+                consumer_sync();
+                if (ticket_shared == p_last - p_first) {
+                    __threadfence();
+                    for (int i = threadIdx.x; i < group * D; i += CONSUMERS) {
+                        const int row = i / D, d = i - row * D;
+                        float mm = -INFINITY;
+                        for (int p = p_first; p <= p_last; ++p) {
+                            // block p's piece of this pair is its first segment iff its range starts inside the pair
+                            const size_t slot = (size_t)p * 2 + ((splits > 0 || p * per >= sg.pair_start) ? 0 : 1);
+                            mm = fmaxf(mm, __ldcg(part_ml + (slot * 16 + row) * 2));
+                        }
+                        float acc = 0.f, ll = 0.f;
+                        for (int p = p_first; p <= p_last; ++p) {
+                            const size_t slot = (size_t)p * 2 + ((splits > 0 || p * per >= sg.pair_start) ? 0 : 1);
+                            const float ms = __ldcg(part_ml + (slot * 16 + row) * 2);
+                            const float c = (ms == -INFINITY) ? 0.f : exp2f(ms - mm);
+                            acc += __ldcg(part_o + (slot * 16 + row) * D + d) * c;
+                            ll += __ldcg(part_ml + (slot * 16 + row) * 2 + 1) * c;
+                        }
+                        out[((size_t)sg.tok * heads + sg.kvh * group + row) * D + d] = __float2bfloat16_rn(ll > 0.f ? acc / ll : 0.f);
+                    }
+                    if (threadIdx.x == 0) counters[sg.tok * kv_heads + sg.kvh] = 0;
+                }
+            }
+            consumer_sync();            // the merge area, q and ticket_shared are reused by the next segment
+            u += sg.len;
+        }
+    }
+    __syncthreads();
+    if (*(volatile int*)&aborted) {
+        // copies that were requested may still be landing in this block's shared memory
+        const long long start = clock64();
+        while (clock64() - start < 4000000LL) __nanosleep(1000);
+    }
+}
+
+// Three stages where two blocks of them fit a multiprocessor, else two.
+int ring_for(int group) { return 2 * (tma_smem_bytes(3, group) + 1024) <= 227 * 1024 ? 3 : 2; }
+
+template <int RING>
+int configure(int group, int* per_sm) {
+    const size_t smem = tma_smem_bytes(RING, group);
+    MRUN_CHECK_CUDA(cudaFuncSetAttribute(decode_tma_kernel<RING>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem),
+                    "attn_decode_tma");
+    if (per_sm)
+        MRUN_CHECK_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(per_sm, decode_tma_kernel<RING>, TMA_THREADS, smem),
+                        "attn_decode_tma");
+    return 0;
+}
+
+}  // namespace
+
+#endif  // MRUN_DECODE_TMA
+
+// 1 when this library holds the TMA decode kernel (head sizes 64 and 128).
+MRUN_API int mrun_attn_decode_tma_available() { return MRUN_DECODE_TMA; }
+
+// Blocks of the TMA decode kernel that fit on one multiprocessor with `group` query heads per kv
+// head (for choosing the number of blocks of a launch); 0 when the kernel is not available.
+MRUN_API int mrun_attn_decode_tma_occupancy(int group) {
+#if MRUN_DECODE_TMA
+    if (group < 1 || group > 16) return 0;
+    int per_sm = 0;
+    const int rc = ring_for(group) == 3 ? configure<3>(group, &per_sm) : configure<2>(group, &per_sm);
+    return rc == 0 ? per_sm : 0;
+#else
+    (void)group;
+    return 0;
+#endif
+}
+
+// As mrun_attn_decode, with a page size that is a power of two, `pages` the number of pages of the
+// two cache tensors, and `status` one int on the device, zero before the first call; a non-zero
+// value afterwards names the role whose wait ran out (1 producer, 2 consumers) and the outputs of
+// that launch are void.
+MRUN_API int mrun_attn_decode_tma(const void* q, long q_stride, void* out, void* k_cache, void* v_cache,
+                                  const int* block_tables, int max_blocks, const int* token_slot,
+                                  const int* positions, const int* tile_prefix, const int* assignment, int tokens,
+                                  float* part_o, float* part_ml, int* counters, int blocks, int heads, int kv_heads,
+                                  int head_dim, int page_size, float scale, int window, int fused,
+                                  const float* q_weight, const float* k_weight, float eps, const float* rot,
+                                  int rotary_dim, const int* slots, long pages, int* status, cudaStream_t stream) {
+#if MRUN_DECODE_TMA
+    if (int rc = check_common("attn_decode_tma", heads, kv_heads, head_dim, page_size, max_blocks, window, 16)) return rc;
+    MRUN_REQUIRE(tokens >= 0 && blocks >= 1 && blocks <= 65535, "attn_decode_tma: tokens=%d blocks=%d", tokens, blocks);
+    MRUN_REQUIRE(tile_prefix && assignment && part_o && part_ml && counters && status,
+                 "attn_decode_tma: the plan, the scratch and the status word are required");
+    MRUN_REQUIRE(page_shift_of(page_size) >= 0, "attn_decode_tma: page_size=%d is not a power of two", page_size);
+    MRUN_REQUIRE(pages > 0 && pages < (1L << 31), "attn_decode_tma: pages=%ld", pages);
+    MRUN_REQUIRE(((uintptr_t)k_cache & 15) == 0 && ((uintptr_t)v_cache & 15) == 0 && ((uintptr_t)q & 15) == 0 &&
+                 q_stride % 8 == 0, "attn_decode_tma: q and the caches must be 16-byte aligned, q_stride a multiple of 8");
+    MRUN_REQUIRE(!fused || (rotary_dim >= 0 && rotary_dim <= head_dim && rotary_dim % 2 == 0),
+                 "attn_decode_tma: rotary_dim=%d must be even and at most head_dim=%d", rotary_dim, head_dim);
+    MRUN_REQUIRE(!fused || (q_weight == nullptr) == (k_weight == nullptr),
+                 "attn_decode_tma: q and k norm weights come together");
+    MRUN_REQUIRE(!fused || q_stride >= (long)(heads + 2 * kv_heads) * head_dim,
+                 "attn_decode_tma: the raw rows must hold q, k and v (stride %ld)", q_stride);
+    if (tokens == 0) return 0;
+    const int group = heads / kv_heads;
+    const int ring = ring_for(group);
+    if (int rc = ring == 3 ? configure<3>(group, nullptr) : configure<2>(group, nullptr)) return rc;
+    CUtensorMap map_k, map_v;
+    const int box_rows = page_size < BLOCK_N ? page_size : BLOCK_N;
+    if (int rc = paged_cache_map(&map_k, k_cache, pages, kv_heads, page_size, D, box_rows, "attn_decode_tma")) return rc;
+    if (int rc = paged_cache_map(&map_v, v_cache, pages, kv_heads, page_size, D, box_rows, "attn_decode_tma")) return rc;
+    FusedInput in = {};
+    if (fused) {
+        in.enabled = 1;
+        in.q_weight = q_weight;
+        in.k_weight = k_weight;
+        in.eps = eps;
+        in.rot = (const float2*)rot;
+        in.rotary_dim = rot ? rotary_dim : 0;
+        in.slots = slots;
+        in.k_cache = (bf16*)k_cache;
+        in.v_cache = (bf16*)v_cache;
+    }
+    const size_t smem = tma_smem_bytes(ring, group);
+    if (ring == 3)
+        decode_tma_kernel<3><<<dim3(blocks), TMA_THREADS, smem, stream>>>(
+            map_k, map_v, (const bf16*)q, q_stride, (bf16*)out, block_tables, max_blocks, token_slot, positions,
+            tile_prefix, (const int4*)assignment, tokens, part_o, part_ml, counters, heads, kv_heads, page_size,
+            page_shift_of(page_size), scale * LOG2E, window, in, status);
+    else
+        decode_tma_kernel<2><<<dim3(blocks), TMA_THREADS, smem, stream>>>(
+            map_k, map_v, (const bf16*)q, q_stride, (bf16*)out, block_tables, max_blocks, token_slot, positions,
+            tile_prefix, (const int4*)assignment, tokens, part_o, part_ml, counters, heads, kv_heads, page_size,
+            page_shift_of(page_size), scale * LOG2E, window, in, status);
+    MRUN_CHECK_LAUNCH("attn_decode_tma");
+    return 0;
+#else
+    return mrun_set_error("attn_decode_tma: not built for head_dim=%d (head sizes 64 and 128 only)", MRUN_HEAD_DIM);
+#endif
+}

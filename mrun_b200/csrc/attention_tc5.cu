@@ -479,22 +479,6 @@ prefill_tc5_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_const
     if (warp == 0) tmem_dealloc(tmem_base, TMEM_COLS);
 }
 
-// The cache [pages, kv_heads, page_size, D] as a rank-4 tensor read in boxes of [box_rows x 64].
-int make_cache_map(CUtensorMap* map, const void* cache, long pages, int kv_heads, int page_size, int box_rows) {
-    EncodeTiled encode = encode_tiled();
-    MRUN_REQUIRE(encode != nullptr, "attn_prefill_tc5: the driver does not offer cuTensorMapEncodeTiled");
-    const cuuint64_t dims[4] = {(cuuint64_t)D, (cuuint64_t)page_size, (cuuint64_t)kv_heads, (cuuint64_t)pages};
-    const cuuint64_t strides[3] = {(cuuint64_t)D * 2, (cuuint64_t)page_size * D * 2,
-                                   (cuuint64_t)kv_heads * page_size * D * 2};
-    const cuuint32_t box[4] = {64, (cuuint32_t)box_rows, 1, 1};
-    const cuuint32_t elem[4] = {1, 1, 1, 1};
-    const CUresult rc = encode(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void*>(cache), dims, strides, box,
-                               elem, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
-                               CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-    MRUN_REQUIRE(rc == CUDA_SUCCESS, "attn_prefill_tc5: cuTensorMapEncodeTiled failed with code %d", (int)rc);
-    return 0;
-}
-
 }  // namespace
 
 #endif  // MRUN_ATTN_TC5
@@ -533,8 +517,8 @@ MRUN_API int mrun_attn_prefill_tc5(const void* q, long q_stride, void* out, cons
     if (n_tiles == 0) return 0;
     CUtensorMap map_k, map_v;
     const int box_rows = page_size < KEYS ? page_size : KEYS;
-    if (int rc = make_cache_map(&map_k, k_cache, pages, kv_heads, page_size, box_rows)) return rc;
-    if (int rc = make_cache_map(&map_v, v_cache, pages, kv_heads, page_size, box_rows)) return rc;
+    if (int rc = paged_cache_map(&map_k, k_cache, pages, kv_heads, page_size, D, box_rows, "attn_prefill_tc5")) return rc;
+    if (int rc = paged_cache_map(&map_v, v_cache, pages, kv_heads, page_size, D, box_rows, "attn_prefill_tc5")) return rc;
     static bool configured = false;
     if (!configured) {
         MRUN_CHECK_CUDA(cudaFuncSetAttribute(prefill_tc5_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,

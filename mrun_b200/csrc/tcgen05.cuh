@@ -212,4 +212,22 @@ inline EncodeTiled encode_tiled() {
     return fn;
 }
 
+// A paged cache [pages, kv_heads, page_size, head_dim] of bf16 as a rank-4 tensor read in boxes of
+// [box_rows x 64 values] with the 128-byte swizzle: coordinates (value, row in page, kv head, page).
+inline int paged_cache_map(CUtensorMap* map, const void* cache, long pages, int kv_heads, int page_size, int head_dim,
+                           int box_rows, const char* who) {
+    EncodeTiled encode = encode_tiled();
+    MRUN_REQUIRE(encode != nullptr, "%s: the driver does not offer cuTensorMapEncodeTiled", who);
+    const cuuint64_t dims[4] = {(cuuint64_t)head_dim, (cuuint64_t)page_size, (cuuint64_t)kv_heads, (cuuint64_t)pages};
+    const cuuint64_t strides[3] = {(cuuint64_t)head_dim * 2, (cuuint64_t)page_size * head_dim * 2,
+                                   (cuuint64_t)kv_heads * page_size * head_dim * 2};
+    const cuuint32_t box[4] = {64, (cuuint32_t)box_rows, 1, 1};
+    const cuuint32_t elem[4] = {1, 1, 1, 1};
+    const CUresult rc = encode(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void*>(cache), dims, strides, box,
+                               elem, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                               CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    MRUN_REQUIRE(rc == CUDA_SUCCESS, "%s: cuTensorMapEncodeTiled failed with code %d", who, (int)rc);
+    return 0;
+}
+
 }  // namespace tc5

@@ -4,9 +4,11 @@ Every kernel reads keys and values from the pages; the tokens of the step were w
 the fused norm/rotary/cache kernel just before.
 
 * float32, or a shape the tensor-core kernels refuse: the CUDA-core kernel in 32-bit arithmetic.
-* bfloat16, every segment a single token: the decode kernel, which deals the key tiles of all
+* bfloat16, every segment a single token: a decode kernel, which deals the key tiles of all
   (token, kv head) pairs evenly to as many blocks as the device holds (scratch for the partial
-  results of pairs shared between blocks, merged by the block that finishes last).
+  results of pairs shared between blocks, merged by the block that finishes last).  Head sizes 64
+  and 128 with power-of-two pages: the kernel whose tiles a producer warp brings by TMA into a
+  ring; else the kernel that copies them with cp.async.
 * bfloat16 otherwise: prompt portions.  Head sizes 64 and 128: the tcgen05 kernel (128-row tiles
   of tokens x group heads, accumulators in tensor memory) for every segment with more rows than
   one tile of the older kernel; the mma.sync kernel (64-row tiles) for the rest of the step (the
@@ -30,15 +32,39 @@ _counters = {}                 # device -> int32 zeros, handed to every split la
 _slots = {}                    # head size -> blocks of the decode kernel resident on the device
 
 
-def _decode_slots(head_dim: int, library) -> int:
-    slots = _slots.get(head_dim)
+def _decode_slots(head_dim: int, library, tma_group: int = 0) -> int:
+    """Blocks of the decode kernel that the device holds at once: the cp.async kernel's, or, with
+    ``tma_group`` query heads per kv head, the TMA kernel's."""
+    slots = _slots.get((head_dim, tma_group))
     if slots is None:
-        query = library._dll.mrun_attn_decode_occupancy
-        query.restype = ctypes.c_int
-        per_sm = max(1, query())
+        if tma_group:
+            per_sm = max(1, int(library._dll.mrun_attn_decode_tma_occupancy(_c_int(tma_group))))
+        else:
+            query = library._dll.mrun_attn_decode_occupancy
+            query.restype = ctypes.c_int
+            per_sm = max(1, query())
         sms = torch.cuda.get_device_properties(torch.cuda.current_device()).multi_processor_count
-        slots = _slots[head_dim] = per_sm * sms
+        slots = _slots[(head_dim, tma_group)] = per_sm * sms
     return slots
+
+
+TMA_DECODE = os.environ.get("MRUN_DECODE_TMA", "1") != "0"       # 0: the cp.async kernel for every decode step
+_tma_decode = {}
+
+
+def decode_uses_tma(library, head_dim: int, ratio: int, page_size: int) -> bool:
+    """Head sizes 64 and 128, pages of a power-of-two size (the kernel copies whole pages by TMA)."""
+    if not TMA_DECODE or ratio > 16 or page_size & (page_size - 1):
+        return False
+    have = _tma_decode.get(head_dim)
+    if have is None:
+        have = _tma_decode[head_dim] = bool(library._dll.mrun_attn_decode_tma_available())
+    return have
+
+
+def decode_slots(head_dim: int, ratio: int, page_size: int) -> int:
+    library = _lib.attention(head_dim)
+    return _decode_slots(head_dim, library, ratio if decode_uses_tma(library, head_dim, ratio, page_size) else 0)
 
 
 def _split_counters(device: torch.device) -> torch.Tensor:
@@ -61,11 +87,13 @@ MAX_SPLITS = 32    # blocks per (token, kv head) pair when a step has few pairs
 
 
 def decode_launch(tokens: int, kv_heads: int, slots: int):
-    """(blocks, splits) of a decode step.  At least as many (token, kv head) pairs as the device
-    holds blocks: all its blocks, the tiles dealt evenly across pairs (splits = 0).  Fewer: every
-    pair gets as many blocks of its own as fill the device once."""
+    """(blocks, splits) of a decode step.  More (token, kv head) pairs than the device holds
+    blocks: all its blocks, the tiles dealt evenly across pairs (splits = 0).  Else every pair gets
+    as many blocks of its own as fill the device once: a block that never changes pair has no
+    partial result to hand over (measured with the TMA kernel at 1,024-token contexts: 288 pairs
+    on 288 blocks 28 us, 5.3 TB/s; 320 pairs dealt to 296 blocks 41 us, 4.1 TB/s)."""
     pairs = tokens * kv_heads
-    if pairs >= slots:
+    if pairs > slots:
         return slots, 0
     splits = max(1, min(slots // pairs, MAX_SPLITS))
     return pairs * splits, splits
@@ -107,16 +135,16 @@ def prefill_tiles(ctx, tokens_per_tile: int, longer_than: int = 0, up_to: int = 
     return tiles
 
 
-def decode_fuses_input(ctx, dtype: torch.dtype, heads: int, kv_heads: int, head_dim: int) -> bool:
+def decode_fuses_input(ctx, dtype: torch.dtype, heads: int, kv_heads: int, head_dim: int, page_size: int = 16) -> bool:
     """Whether this step's attention takes q, k and v raw and norms, rotates and stores them itself:
-    every segment a single token, bfloat16, a group that the split-key kernel takes, and fewer
+    every segment a single token, bfloat16, a group that the split-key kernel takes, and no more
     (token, kv head) pairs than resident blocks.  With more pairs the blocks walk from pair to
     pair and would redo the input work at every change (measured at 64 requests of the 8B shape:
     82.6 us a layer fused against 67.7 + 4 us with the stand-alone kernel first)."""
     ratio = heads // kv_heads
     if not (ctx.all_decode and ratio <= 16 and supports_tensor_cores(dtype, head_dim, ratio)):
         return False
-    return ctx.num_tokens * kv_heads < _decode_slots(head_dim, _lib.attention(head_dim))
+    return ctx.num_tokens * kv_heads <= decode_slots(head_dim, ratio, page_size)
 
 
 def paged_attention(q: torch.Tensor, q_stride: int, out: torch.Tensor, cache, group, ctx,
@@ -139,7 +167,8 @@ def paged_attention(q: torch.Tensor, q_stride: int, out: torch.Tensor, cache, gr
     if ctx.all_decode and ratio <= 16:
         if tokens * kv_heads > COUNTER_CAPACITY:
             raise ValueError(f"a decode step of {tokens} tokens x {kv_heads} kv heads exceeds {COUNTER_CAPACITY} pairs")
-        blocks, splits = decode_launch(tokens, kv_heads, _decode_slots(head_dim, library))
+        tma = decode_uses_tma(library, head_dim, ratio, page_size)
+        blocks, splits = decode_launch(tokens, kv_heads, decode_slots(head_dim, ratio, page_size))
         part_o = torch.empty((blocks, 2, 16, head_dim), dtype=torch.float32, device=q.device)
         part_ml = torch.empty((blocks, 2, 16, 2), dtype=torch.float32, device=q.device)
         fused = (_c_int(0), _ptr(None), _ptr(None), _c_float(0.0), _ptr(None), _c_int(0), _ptr(None))
@@ -148,9 +177,13 @@ def paged_attention(q: torch.Tensor, q_stride: int, out: torch.Tensor, cache, gr
             fused = (_c_int(1), _ptr(q_weight), _ptr(k_weight), _c_float(eps), _ptr(rot), _c_int(rotary_dim),
                      _ptr(slots))
         prefix, assignment = decode_plan(ctx, library, window, kv_heads, blocks, splits)
-        library.call("mrun_attn_decode", _ptr(q), _c_long(q_stride), _ptr(out), *common, _ptr(prefix),
-                     _ptr(assignment), _c_int(tokens), _ptr(part_o), _ptr(part_ml),
-                     _ptr(_split_counters(q.device)), _c_int(blocks), *tail[:-1], *fused, tail[-1])
+        extra = ()
+        if tma:
+            status = ops.status_word(q.device, "attn_decode_tma", {1: "the TMA producer", 2: "the consumer warps"})
+            extra = (_c_long(pages), _ptr(status))
+        library.call("mrun_attn_decode_tma" if tma else "mrun_attn_decode", _ptr(q), _c_long(q_stride), _ptr(out),
+                     *common, _ptr(prefix), _ptr(assignment), _c_int(tokens), _ptr(part_o), _ptr(part_ml),
+                     _ptr(_split_counters(q.device)), _c_int(blocks), *tail[:-1], *fused, *extra, tail[-1])
         return out
     if raw is not None:
         raise ValueError("raw q, k, v rows are taken by the decode kernel only")

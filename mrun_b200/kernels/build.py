@@ -155,6 +155,9 @@ def build_core() -> str:
     return build_library(f"mrun_core_{tag}" if tag else "mrun_core", CORE_SOURCES, defines)
 
 
+ATTENTION_SOURCES = ("common.cu", "attention_mma.cu", "attention_decode_tma.cu", "attention_tc5.cu")
+
+
 def build_attention(head_dim: int) -> str:
     """The tensor-core attention kernels specialised for one head size."""
     if head_dim % 16 or not 16 <= head_dim <= 256:
@@ -165,9 +168,9 @@ def build_attention(head_dim: int) -> str:
         defines["MRUN_DECODE_STAGES"] = int(stages)
     if os.environ.get("MRUN_ATTN_TC5_TIMING"):           # tuning aid: the first block prints its roles' cycles
         defines["MRUN_ATTN_TC5_TIMING"] = 1
-        return build_library(f"mrun_attn_d{head_dim}_timing", ("common.cu", "attention_mma.cu", "attention_tc5.cu"), defines)
+        return build_library(f"mrun_attn_d{head_dim}_timing", ATTENTION_SOURCES, defines)
     return build_library(f"mrun_attn_d{head_dim}_s{stages}" if stages else f"mrun_attn_d{head_dim}",
-                         ("common.cu", "attention_mma.cu", "attention_tc5.cu"), defines)
+                         ATTENTION_SOURCES, defines)
 
 
 # head sizes of the configurations this repository measures and tests

@@ -74,7 +74,7 @@ class Attention:
         rotary_dim = self.position.rotary_dim if self.position is not None else 0
         slots = group.slot_mapping if cache.writable else None
         out = torch.empty((x.shape[0], s.heads * s.head_dim), dtype=x.dtype, device=x.device)
-        if decode_fuses_input(ctx, x.dtype, s.heads, s.kv_heads, s.head_dim):
+        if decode_fuses_input(ctx, x.dtype, s.heads, s.kv_heads, s.head_dim, self.runtime.page_size):
             # a pure decode step: the attention kernel norms, rotates and stores q, k, v itself
             paged_attention(qkv, qkv.shape[1], out, cache, group, ctx, s.heads, s.softmax_scale, s.window or 0,
                             raw=(self.q_weight, self.k_weight, self.eps, rot, rotary_dim, slots))

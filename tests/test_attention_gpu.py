@@ -97,7 +97,7 @@ class Case:
 
 SHAPES = [  # heads, kv_heads, head_dim, page_size
     (4, 2, 16, 16), (6, 3, 32, 8), (7, 1, 48, 4), (8, 8, 64, 32), (10, 2, 80, 16), (32, 8, 128, 16), (2, 1, 256, 16),
-    (3, 1, 96, 1), (40, 2, 64, 16)]
+    (3, 1, 96, 1), (40, 2, 64, 16), (16, 1, 128, 4), (12, 4, 64, 128), (6, 2, 128, 1), (8, 2, 128, 24)]
 
 
 @pytest.mark.parametrize("heads,kv_heads,head_dim,page_size", SHAPES)
@@ -133,8 +133,9 @@ def test_decode_batch_against_plain(heads, kv_heads, head_dim, page_size, window
 @pytest.mark.parametrize("blocks,min_tiles,splits", [(1, 1, 0), (3, 1, 0), (16, 1, 0), (64, 1, 0), (444, 1, 0), (5, 2, 0),
                                                      (16, 4, 0), (1000, 3, 0), (7, 40, 0),
                                                      (16, 1, 1), (48, 1, 3), (256, 2, 16), (512, 4, 32)])
-def test_decode_tiles_dealt_to_any_number_of_blocks(blocks, min_tiles, splits):
-    """The decode kernel called directly with forced launch shapes (one block takes every pair,
+@pytest.mark.parametrize("entry", ["mrun_attn_decode", "mrun_attn_decode_tma"])
+def test_decode_tiles_dealt_to_any_number_of_blocks(blocks, min_tiles, splits, entry):
+    """The decode kernels (tiles copied by cp.async, tiles brought by TMA into a ring) called directly with forced launch shapes (one block takes every pair,
     several blocks share pairs, more blocks than tiles; tiles dealt across pairs, or every pair
     split between blocks of its own), twice in a row (the counters the blocks meet at must be
     back at zero), against the CUDA-core kernel."""
@@ -161,15 +162,18 @@ def test_decode_tiles_dealt_to_any_number_of_blocks(blocks, min_tiles, splits):
     part_o = torch.full((blocks, 2, 16, head_dim), float("nan"), device=DEV)
     part_ml = torch.full((blocks, 2, 16, 2), float("nan"), device=DEV)
     counters = torch.zeros(n * kv_heads, dtype=torch.int32, device=DEV)
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    extra = (_c_long(case.kd.shape[0]), _ptr(status)) if entry.endswith("tma") else ()
     for _ in range(2):
         out = torch.full((n, heads * head_dim), 3.0, dtype=torch.bfloat16, device=DEV)
         library.call(
-            "mrun_attn_decode", _ptr(case.qd), _c_long(case.qd.stride(0)), _ptr(out), _ptr(case.kd), _ptr(case.vd),
+            entry, _ptr(case.qd), _c_long(case.qd.stride(0)), _ptr(out), _ptr(case.kd), _ptr(case.vd),
             _ptr(case.table), _c_int(case.group.max_blocks), _ptr(case.ctx.token_slot), _ptr(case.ctx.positions),
             _ptr(plan), _ptr(assignment), _c_int(n), _ptr(part_o), _ptr(part_ml), _ptr(counters), _c_int(blocks),
             _c_int(heads), _c_int(kv_heads), _c_int(head_dim), _c_int(page_size), _c_float(scale), _c_int(0),
-            _c_int(0), _ptr(None), _ptr(None), _c_float(0.0), _ptr(None), _c_int(0), _ptr(None), _stream())
+            _c_int(0), _ptr(None), _ptr(None), _c_float(0.0), _ptr(None), _c_int(0), _ptr(None), *extra, _stream())
         got = out.float().cpu()
+        assert int(status.item()) == 0
         assert (got - want).abs().max() <= 2e-2 * want.abs().max()
         assert got[case.tokens:].abs().max() == 0
         assert int(counters.abs().sum()) == 0
