@@ -256,7 +256,8 @@ decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_consta
         // padding rows come out as zeros
         for (int t = block_id; t < tokens; t += n_blocks_grid)
             if (positions[t] < 0)
-                for (int i = threadIdx.x; i < heads * D; i += CONSUMERS) out[(size_t)t * heads * D + i] = __float2bfloat16_rn(0.f);
+                for (int i = threadIdx.x; i < heads * D; i += CONSUMERS)
+                    out[(size_t)(fused.rows ? fused.rows[t] : t) * heads * D + i] = __float2bfloat16_rn(0.f);
 
         // A warp whose wait ran out sets the flag and keeps walking (its later waits return at once,
         // its numbers are void), so that every barrier of the four warps is still met by all.
@@ -272,12 +273,13 @@ decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_consta
             for (int dt = 0; dt < D / 8; ++dt) o[dt][0] = o[dt][1] = o[dt][2] = o[dt][3] = 0.f;
 
             const bool owns_new_token = fused.enabled && sg.last_block == b1;
+            const int q_row = fused.rows ? fused.rows[sg.tok] : sg.tok;        // the row of q and out
             if (!fused.enabled) {
                 for (int c = threadIdx.x; c < 16 * CHUNKS; c += CONSUMERS) {
                     const int row = c / CHUNKS, chunk = c - row * CHUNKS;
                     uint4 value = make_uint4(0, 0, 0, 0);
                     if (row < group)
-                        value = *reinterpret_cast<const uint4*>(q + (size_t)sg.tok * q_stride + (size_t)(sg.kvh * group + row) * D + chunk * 8);
+                        value = *reinterpret_cast<const uint4*>(q + (size_t)q_row * q_stride + (size_t)(sg.kvh * group + row) * D + chunk * 8);
                     *reinterpret_cast<uint4*>(q_tile + row * LD + chunk * 8) = value;
                 }
             } else {
@@ -389,7 +391,7 @@ decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_consta
                     ll += src[D + 1] * c;
                 }
                 if (sg.complete) {
-                    out[((size_t)sg.tok * heads + sg.kvh * group + row) * D + d] = __float2bfloat16_rn(ll > 0.f ? acc / ll : 0.f);
+                    out[((size_t)q_row * heads + sg.kvh * group + row) * D + d] = __float2bfloat16_rn(ll > 0.f ? acc / ll : 0.f);
                 } else {
                     part_o[(my_slot * 16 + row) * D + d] = acc;
                     if (d == 0) {
@@ -431,7 +433,7 @@ decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_consta
                             acc += __ldcg(part_o + (slot * 16 + row) * D + d) * c;
                             ll += __ldcg(part_ml + (slot * 16 + row) * 2 + 1) * c;
                         }
-                        out[((size_t)sg.tok * heads + sg.kvh * group + row) * D + d] = __float2bfloat16_rn(ll > 0.f ? acc / ll : 0.f);
+                        out[((size_t)q_row * heads + sg.kvh * group + row) * D + d] = __float2bfloat16_rn(ll > 0.f ? acc / ll : 0.f);
                     }
                     if (threadIdx.x == 0) counters[sg.tok * kv_heads + sg.kvh] = 0;
                 }
@@ -484,7 +486,8 @@ MRUN_API int mrun_attn_decode_tma_occupancy(int group) {
 }
 
 // As mrun_attn_decode, with a page size that is a power of two, `pages` the number of pages of the
-// two cache tensors, and `status` one int on the device, zero before the first call; a non-zero
+// two cache tensors, `rows` null or, for each of the `tokens` tokens (whose positions and state
+// slots the arrays of that length give), the row of q and of out it stands for, and `status` one int on the device, zero before the first call; a non-zero
 // value afterwards names the role whose wait ran out (1 producer, 2 consumers) and the outputs of
 // that launch are void.
 MRUN_API int mrun_attn_decode_tma(const void* q, long q_stride, void* out, void* k_cache, void* v_cache,
@@ -493,7 +496,8 @@ MRUN_API int mrun_attn_decode_tma(const void* q, long q_stride, void* out, void*
                                   float* part_o, float* part_ml, int* counters, int blocks, int heads, int kv_heads,
                                   int head_dim, int page_size, float scale, int window, int fused,
                                   const float* q_weight, const float* k_weight, float eps, const float* rot,
-                                  int rotary_dim, const int* slots, long pages, int* status, cudaStream_t stream) {
+                                  int rotary_dim, const int* slots, const int* rows, long pages, int* status,
+                                  cudaStream_t stream) {
 #if MRUN_DECODE_TMA
     if (int rc = check_common("attn_decode_tma", heads, kv_heads, head_dim, page_size, max_blocks, window, 16)) return rc;
     MRUN_REQUIRE(tokens >= 0 && blocks >= 1 && blocks <= 65535, "attn_decode_tma: tokens=%d blocks=%d", tokens, blocks);
@@ -509,6 +513,7 @@ MRUN_API int mrun_attn_decode_tma(const void* q, long q_stride, void* out, void*
                  "attn_decode_tma: q and k norm weights come together");
     MRUN_REQUIRE(!fused || q_stride >= (long)(heads + 2 * kv_heads) * head_dim,
                  "attn_decode_tma: the raw rows must hold q, k and v (stride %ld)", q_stride);
+    MRUN_REQUIRE(!(fused && rows), "attn_decode_tma: a selection of rows does not go with raw q, k, v input");
     if (tokens == 0) return 0;
     const int group = heads / kv_heads;
     const int ring = ring_for(group);
@@ -529,6 +534,7 @@ MRUN_API int mrun_attn_decode_tma(const void* q, long q_stride, void* out, void*
         in.k_cache = (bf16*)k_cache;
         in.v_cache = (bf16*)v_cache;
     }
+    in.rows = rows;
     const size_t smem = tma_smem_bytes(ring, group);
     if (ring == 3)
         decode_tma_kernel<3><<<dim3(blocks), TMA_THREADS, smem, stream>>>(

@@ -66,6 +66,10 @@ struct FusedInput {
     const int* slots;        // [tokens] page * page_size + offset, negative or null: nothing is written
     bf16* k_cache;           // the pages, writable
     bf16* v_cache;
+    // Not part of the raw input: when the kernel's tokens are a selection of the step's rows (the
+    // single decode tokens of a step that also carries prompt portions), rows[t] is the row of q
+    // and of out that token t stands for; null: token t is row t.  Only without raw input.
+    const int* rows;
 };
 
 // One head vector (D elements at `src`): norm with `weight` (may be null), rotation with the

@@ -9,7 +9,9 @@ the fused norm/rotary/cache kernel just before.
   results of pairs shared between blocks, merged by the block that finishes last).  Head sizes 64
   and 128 with power-of-two pages: the kernel whose tiles a producer warp brings by TMA into a
   ring; else the kernel that copies them with cp.async.
-* bfloat16 otherwise: prompt portions.  Head sizes 64 and 128: the tcgen05 kernel (128-row tiles
+* bfloat16 otherwise: a step with prompt portions.  Its single-token segments (the decoding
+  requests beside the prompts) go through the TMA decode kernel as a selection of the step's rows
+  where that kernel takes the shape; the rest as follows.  Head sizes 64 and 128: the tcgen05 kernel (128-row tiles
   of tokens x group heads, accumulators in tensor memory) for every segment with more rows than
   one tile of the older kernel; the mma.sync kernel (64-row tiles) for the rest of the step (the
   single decode tokens of a mixed step, short tails) and for the other head sizes.
@@ -99,16 +101,20 @@ def decode_launch(tokens: int, kv_heads: int, slots: int):
     return pairs * splits, splits
 
 
-def decode_plan(ctx, library, window: int, kv_heads: int, blocks: int, splits: int):
+def decode_plan(ctx, library, window: int, kv_heads: int, blocks: int, splits: int, positions=None):
     """The step's plan for the decode kernel: tiles per token as a prefix sum (int32, tokens + 1)
     and what each of ``blocks`` blocks starts with (int32, 8 per block).  Made once per step for
-    a window, a number of kv heads and a launch shape."""
-    key = ("decode_plan", window, kv_heads, blocks, splits)
+    a window, a number of kv heads and a launch shape.  ``positions``: those of a selection of the
+    step's tokens instead of all of them."""
+    key = ("decode_plan", window, kv_heads, blocks, splits, positions is not None)
     plan = ctx.shared.get(key)
     if plan is None:
-        prefix = torch.empty(ctx.num_tokens + 1, dtype=torch.int32, device=ctx.positions.device)
-        assignment = torch.empty(blocks * 8, dtype=torch.int32, device=ctx.positions.device)
-        library.call("mrun_attn_decode_plan", _ptr(ctx.positions), _c_int(ctx.num_tokens), _c_int(window),
+        if positions is None:
+            positions = ctx.positions
+        n = positions.shape[0]
+        prefix = torch.empty(n + 1, dtype=torch.int32, device=positions.device)
+        assignment = torch.empty(blocks * 8, dtype=torch.int32, device=positions.device)
+        library.call("mrun_attn_decode_plan", _ptr(positions), _c_int(n), _c_int(window),
                      _c_int(kv_heads), _c_int(blocks), _c_int(MIN_TILES), _c_int(splits), _ptr(prefix),
                      _ptr(assignment), _stream())
         plan = ctx.shared[key] = (prefix, assignment)
@@ -133,6 +139,23 @@ def prefill_tiles(ctx, tokens_per_tile: int, longer_than: int = 0, up_to: int = 
         both = ctx.upload(np.asarray(first + count, dtype=np.int32))
         tiles = ctx.shared[key] = (both[:n], both[n:], n)
     return tiles
+
+
+def single_tokens(ctx):
+    """The single-token segments of a step that also carries prompt portions, as device int32
+    arrays (rows, positions, state slots) and their number; made once per step."""
+    found = ctx.shared.get("single_tokens")
+    if found is None:
+        singles = [seg for seg in ctx.segments if seg.q_len == 1]
+        n = len(singles)
+        if n:
+            packed = ctx.upload(np.asarray([seg.q_start for seg in singles] + [seg.pos_start for seg in singles]
+                                           + [seg.slot for seg in singles], dtype=np.int32))
+            found = (packed[:n], packed[n:2 * n], packed[2 * n:], n)
+        else:
+            found = (None, None, None, 0)
+        ctx.shared["single_tokens"] = found
+    return found
 
 
 def decode_fuses_input(ctx, dtype: torch.dtype, heads: int, kv_heads: int, head_dim: int, page_size: int = 16) -> bool:
@@ -180,7 +203,7 @@ def paged_attention(q: torch.Tensor, q_stride: int, out: torch.Tensor, cache, gr
         extra = ()
         if tma:
             status = ops.status_word(q.device, "attn_decode_tma", {1: "the TMA producer", 2: "the consumer warps"})
-            extra = (_c_long(pages), _ptr(status))
+            extra = (_ptr(None), _c_long(pages), _ptr(status))
         library.call("mrun_attn_decode_tma" if tma else "mrun_attn_decode", _ptr(q), _c_long(q_stride), _ptr(out),
                      *common, _ptr(prefix), _ptr(assignment), _c_int(tokens), _ptr(part_o), _ptr(part_ml),
                      _ptr(_split_counters(q.device)), _c_int(blocks), *tail[:-1], *fused, *extra, tail[-1])
@@ -189,18 +212,36 @@ def paged_attention(q: torch.Tensor, q_stride: int, out: torch.Tensor, cache, gr
         raise ValueError("raw q, k, v rows are taken by the decode kernel only")
     if tokens > ctx.real_tokens:
         out[ctx.real_tokens:].zero_()
+    # The single tokens of a step that also carries prompt portions: the decode kernel over that
+    # selection of rows (split keys, every block busy), not one 64-row tile a token and kv head.
+    shortest = 0
+    if ratio <= 16 and decode_uses_tma(library, head_dim, ratio, page_size):
+        rows, row_positions, row_slots, n_single = single_tokens(ctx)
+        if n_single and n_single * kv_heads <= COUNTER_CAPACITY:
+            blocks, splits = decode_launch(n_single, kv_heads, decode_slots(head_dim, ratio, page_size))
+            part_o = torch.empty((blocks, 2, 16, head_dim), dtype=torch.float32, device=q.device)
+            part_ml = torch.empty((blocks, 2, 16, 2), dtype=torch.float32, device=q.device)
+            prefix, assignment = decode_plan(ctx, library, window, kv_heads, blocks, splits, positions=row_positions)
+            status = ops.status_word(q.device, "attn_decode_tma", {1: "the TMA producer", 2: "the consumer warps"})
+            library.call("mrun_attn_decode_tma", _ptr(q), _c_long(q_stride), _ptr(out), _ptr(cache.k), _ptr(cache.v),
+                         _ptr(group.block_tables), _c_int(group.max_blocks), _ptr(row_slots), _ptr(row_positions),
+                         _ptr(prefix), _ptr(assignment), _c_int(n_single), _ptr(part_o), _ptr(part_ml),
+                         _ptr(_split_counters(q.device)), _c_int(blocks), *tail[:-1],
+                         _c_int(0), _ptr(None), _ptr(None), _c_float(0.0), _ptr(None), _c_int(0), _ptr(None),
+                         _ptr(rows), _c_long(pages), _ptr(status), tail[-1])
+            shortest = 1
     short_up_to = 1 << 30
     if prefill_uses_tcgen05(library, head_dim, ratio, page_size):
         # segments with more rows than a 64-row tile go to the 128-row tcgen05 kernel
         short_up_to = (64 // ratio) if ratio <= 64 else 0
-        first, count, n_tiles = prefill_tiles(ctx, 128 // ratio, longer_than=short_up_to)
+        first, count, n_tiles = prefill_tiles(ctx, 128 // ratio, longer_than=max(short_up_to, shortest))
         if n_tiles:
             status = ops.status_word(q.device, "attn_prefill_tc5",
                                      {1: "a key/value loader", 2: "the MMA issuer", 3: "the softmax warps"})
             library.call("mrun_attn_prefill_tc5", _ptr(q), _c_long(q_stride), _ptr(out), *common, _ptr(first),
                          _ptr(count), _c_int(n_tiles), *tail[:-1], _c_long(pages), _ptr(status), tail[-1])
-    if short_up_to:
-        first, count, n_tiles = prefill_tiles(ctx, 64 // ratio, up_to=short_up_to)
+    if short_up_to > shortest:
+        first, count, n_tiles = prefill_tiles(ctx, 64 // ratio, longer_than=shortest, up_to=short_up_to)
         if n_tiles:
             library.call("mrun_attn_prefill", _ptr(q), _c_long(q_stride), _ptr(out), *common, _ptr(first),
                          _ptr(count), _c_int(n_tiles), *tail)

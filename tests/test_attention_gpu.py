@@ -163,7 +163,7 @@ def test_decode_tiles_dealt_to_any_number_of_blocks(blocks, min_tiles, splits, e
     part_ml = torch.full((blocks, 2, 16, 2), float("nan"), device=DEV)
     counters = torch.zeros(n * kv_heads, dtype=torch.int32, device=DEV)
     status = torch.zeros(1, dtype=torch.int32, device=DEV)
-    extra = (_c_long(case.kd.shape[0]), _ptr(status)) if entry.endswith("tma") else ()
+    extra = (_ptr(None), _c_long(case.kd.shape[0]), _ptr(status)) if entry.endswith("tma") else ()
     for _ in range(2):
         out = torch.full((n, heads * head_dim), 3.0, dtype=torch.bfloat16, device=DEV)
         library.call(

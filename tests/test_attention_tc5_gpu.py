@@ -130,3 +130,27 @@ def test_given_back_pages_are_not_read():
     got = case.run(scale)
     check_status()
     assert (got - want).abs().max() <= 2e-2 * want.abs().max()
+
+
+def test_single_tokens_beside_portions_take_the_decode_kernel(monkeypatch):
+    """A step of prompt portions and single decode tokens at long contexts: the single tokens go
+    through the split-key decode kernel as a selection of the step's rows, the portions through
+    the prefill kernels, and every row agrees with plain attention either way."""
+    from mrun_b200.kernels import attention
+    heads, kv_heads, head_dim, page_size = 32, 8, 128, 16
+    scale = head_dim ** -0.5
+    segments = [(0, 300), (2000, 1), (513, 1), (64, 1), (100, 40), (4095, 1), (7, 2)]
+    case = Case(segments, heads, kv_heads, head_dim, page_size, torch.bfloat16, seed=13)
+    want = reference(case, scale)
+    got = case.run(scale)
+    check_status()
+    rows, positions, slots, n = case.ctx.shared["single_tokens"]
+    assert n == 4 and rows.tolist() == [300, 301, 302, 343] and positions.tolist() == [2000, 513, 64, 4095]
+    assert any(key[0] == "decode_plan" and key[-1] for key in case.ctx.shared if isinstance(key, tuple))
+    assert (got - want).abs().max() <= 2e-2 * want.abs().max()
+    # the same step with the decode kernel switched off: the 64-row tiles take the single tokens
+    monkeypatch.setattr(attention, "TMA_DECODE", False)
+    case.ctx.shared.clear()
+    other = case.run(scale)
+    assert "single_tokens" not in case.ctx.shared
+    assert (other - want).abs().max() <= 2e-2 * want.abs().max()
