@@ -456,8 +456,12 @@ int ring_for(int group) { return 2 * (tma_smem_bytes(3, group) + 1024) <= 227 * 
 template <int RING>
 int configure(int group, int* per_sm) {
     const size_t smem = tma_smem_bytes(RING, group);
-    MRUN_CHECK_CUDA(cudaFuncSetAttribute(decode_tma_kernel<RING>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem),
-                    "attn_decode_tma");
+    static size_t allowed = 0;                   // the attribute is raised once per size, not per launch
+    if (smem > allowed) {
+        MRUN_CHECK_CUDA(cudaFuncSetAttribute(decode_tma_kernel<RING>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem),
+                        "attn_decode_tma");
+        allowed = smem;
+    }
     if (per_sm)
         MRUN_CHECK_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(per_sm, decode_tma_kernel<RING>, TMA_THREADS, smem),
                         "attn_decode_tma");
