@@ -172,7 +172,53 @@ __global__ void repetition_penalty_kernel(float* __restrict__ logits, int vocab,
     *v = *v >= 0.f ? *v / pen : *v * pen;
 }
 
+// The n most likely tokens of a row with their log-probabilities, most likely first, ties by the
+// smaller id (crates/mrun-engine/src/sample.rs:134-156).  lp_i = x_i - logsumexp(x), 32-bit.
+// One block per row: the row's maximum and sum, then n selection rounds, each the argmax over the
+// tokens that come after the one chosen in the round before.
+__global__ void __launch_bounds__(THREADS)
+top_logprobs_kernel(const float* __restrict__ logits, int vocab, int n, int* __restrict__ ids,
+                    float* __restrict__ values) {
+    __shared__ float scratch[33];
+    __shared__ ArgMax arg_scratch[33];
+    const int row = blockIdx.x, tid = threadIdx.x;
+    const float* x = logits + (size_t)row * vocab;
+    float mx = -INFINITY;
+    for (int i = tid; i < vocab; i += THREADS) mx = fmaxf(mx, x[i]);
+    mx = block_max(mx, scratch);
+    float total = 0.f;
+    for (int i = tid; i < vocab; i += THREADS) total += expf(x[i] - mx);
+    total = block_sum(total, scratch);
+    const float lse = mx + logf(total);
+    ArgMax last{INFINITY, -1};                   // everything comes after this
+    for (int round = 0; round < n; ++round) {
+        ArgMax best{-INFINITY, 0x7fffffff};
+        for (int i = tid; i < vocab; i += THREADS) {
+            const float v = x[i];
+            // after `last` in the order (value descending, id ascending)
+            if (v < last.value || (v == last.value && i > last.index)) best = better(best, ArgMax{v, i});
+        }
+        best = block_argmax(best, arg_scratch);
+        if (tid == 0) {
+            ids[(size_t)row * n + round] = best.index;
+            values[(size_t)row * n + round] = best.value - lse;
+        }
+        last = best;
+    }
+}
+
 }  // namespace
+
+// ids, values: [rows, n]; n at most the vocabulary.
+MRUN_API int mrun_top_logprobs(const float* logits, int rows, int vocab, int n, int* ids, float* values,
+                               cudaStream_t stream) {
+    MRUN_REQUIRE(rows >= 0 && vocab > 0, "top_logprobs: bad sizes rows=%d vocab=%d", rows, vocab);
+    MRUN_REQUIRE(n >= 1 && n <= vocab && n <= 1024, "top_logprobs: n=%d must be 1 .. min(vocab, 1024)", n);
+    if (rows == 0) return 0;
+    top_logprobs_kernel<<<rows, THREADS, 0, stream>>>(logits, vocab, n, ids, values);
+    MRUN_CHECK_LAUNCH("top_logprobs");
+    return 0;
+}
 
 // temperature/top_p/top_k/min_p/keys are per-row device arrays; a null array means the neutral
 // value (0, 1, 0, 0).  temperature 0 = greedy (keys may then be null).

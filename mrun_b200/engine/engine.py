@@ -38,6 +38,9 @@ class Generation:
     first_token_time: float = 0.0                 # host clock (perf_counter) readings
     finished_time: float = 0.0
     token_times: List[float] = field(default_factory=list)
+    # with ``logprobs=n``: per output token the n most likely tokens at that place as
+    # (id, log-probability), most likely first (crates/mrun-engine/src/engine.rs:740-741)
+    top_logprobs: List[list] = field(default_factory=list)
 
 
 @dataclass
@@ -111,10 +114,15 @@ class Engine:
     def generate(self, prompts: Sequence[Sequence[int]], max_tokens: int = 2048, temperature: float = 0.0,
                  top_p: float = 1.0, top_k: int = 0, min_p: float = 0.0, seed: Optional[int] = None,
                  repetition_penalty: float = 1.0, ignore_eos: bool = False,
-                 sampling: Optional[Sequence[SamplingParams]] = None) -> List[Generation]:
+                 sampling: Optional[Sequence[SamplingParams]] = None, logprobs: int = 0) -> List[Generation]:
         """Generates for every prompt (lists of token ids) and returns the results in order.
         ``sampling`` gives each prompt settings of its own; otherwise all share the keyword
-        values, prompt i drawing with ``seed + i`` when a seed is given."""
+        values, prompt i drawing with ``seed + i`` when a seed is given.  ``logprobs`` = n > 0
+        also reports, for every output token, the n most likely tokens at its place with their
+        log-probabilities (of the logits as the model gave them, before any penalty); such
+        requests are read back step by step, not pipelined."""
+        if not 0 <= logprobs <= 1024:
+            raise ValueError(f"logprobs must be 0 .. 1024, got {logprobs}")
         requests = []
         for i, prompt in enumerate(prompts):
             if sampling is not None:
@@ -124,7 +132,8 @@ class Engine:
                                         seed=None if seed is None else seed + i,
                                         repetition_penalty=repetition_penalty)
             requests.append(Request(request_id=("gen", self._next_id), prompt=list(map(int, prompt)),
-                                    max_tokens=max_tokens, sampling=params, ignore_eos=ignore_eos))
+                                    max_tokens=max_tokens, sampling=params, ignore_eos=ignore_eos,
+                                    logprobs=logprobs))
             self._next_id += 1
         self.run(requests)
         return [Generation(tokens=r.output, finish_reason=r.finish_reason, message=r.message,
@@ -132,7 +141,7 @@ class Engine:
                            time_to_first_token_s=max(0.0, r.first_token_at - r.submitted_at) if r.output else 0.0,
                            total_s=r.finished_at - r.submitted_at, preemptions=r.preemptions,
                            first_token_time=r.first_token_at, finished_time=r.finished_at,
-                           token_times=r.token_times)
+                           token_times=r.token_times, top_logprobs=r.top_logprobs)
                 for r in requests]
 
     def run(self, requests: Sequence[Request]) -> None:
@@ -183,6 +192,8 @@ class Engine:
         in the step in flight, and that needs no token history for a repetition penalty."""
         if not all(len(e.tokens) == 1 and e.wants_logits for e in plan.entries):
             return False
+        if any(e.request.logprobs for e in plan.entries):
+            return False                    # the logits themselves are wanted on the host side
         bucket = self.executor.decode_bucket(len(plan.entries))
         if bucket is None:
             return False
@@ -239,6 +250,12 @@ class Engine:
         if not sampled:
             scheduler.complete(plan, [])
             return
+        wanted = [(row, r) for row, r in enumerate(sampled) if r.logprobs]
+        if wanted:                          # before the sampler, which applies penalties in place
+            ids, values = self.sampler.top_logprobs(logits, max(r.logprobs for _, r in wanted))
+            ids, values = ids.to("cpu").tolist(), values.to("cpu").tolist()
+            for row, r in wanted:
+                r.top_logprobs.append(list(zip(ids[row][:r.logprobs], values[row][:r.logprobs])))
         tokens = self.sampler.sample(
             logits, [r.sampling for r in sampled], [r.seed for r in sampled],
             [len(r.output) + 1 for r in sampled],

@@ -65,6 +65,7 @@ class Request:
     max_tokens: int = 2048
     sampling: SamplingParams = GREEDY
     ignore_eos: bool = False
+    logprobs: int = 0                  # how many of the most likely tokens to report beside each output token
     # ---- run state
     state: str = "new"                 # new | waiting | running | finished
     output: List[int] = field(default_factory=list)
@@ -81,6 +82,7 @@ class Request:
     first_token_at: float = 0.0
     finished_at: float = 0.0
     token_times: List[float] = field(default_factory=list)   # when each output token was read back
+    top_logprobs: List[list] = field(default_factory=list)   # per output token: [(id, log-probability), ...]
     inflight: int = 0                  # tokens sampled on the device that the host has not read yet
     retiring: bool = False             # finished, but a step in flight still holds a row of it
 

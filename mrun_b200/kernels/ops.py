@@ -336,6 +336,19 @@ def sample(logits: torch.Tensor, out: torch.Tensor, temperature: Optional[torch.
     return out
 
 
+def top_logprobs(logits: torch.Tensor, n: int):
+    """(ids int32 [rows, n], log-probabilities float32 [rows, n]) of the n most likely tokens of
+    each row of float32 logits, most likely first, ties by the smaller id."""
+    _check(logits, "logits", torch.float32)
+    rows, vocab = logits.shape
+    n = max(1, min(int(n), vocab))
+    ids = torch.empty((rows, n), dtype=torch.int32, device=logits.device)
+    values = torch.empty((rows, n), dtype=torch.float32, device=logits.device)
+    _lib.core().call("mrun_top_logprobs", _ptr(logits), _c_int(rows), _c_int(vocab), _c_int(n), _ptr(ids),
+                     _ptr(values), _stream())
+    return ids, values
+
+
 def repetition_penalty(logits: torch.Tensor, recent: torch.Tensor, penalty: torch.Tensor) -> None:
     """In place: the logits of the ids in recent[row] (negative = empty) are penalised."""
     _check(logits, "logits", torch.float32); _check(recent, "recent", torch.int32)

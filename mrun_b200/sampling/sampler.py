@@ -41,3 +41,8 @@ class Sampler:
             top_k=torch.tensor([p.top_k for p in params], dtype=torch.int32).to(self.device),
             min_p=f32([p.min_p for p in params]),
             keys=torch.from_numpy(keys.view(np.int64)).to(self.device))
+
+    def top_logprobs(self, logits: torch.Tensor, n: int):
+        """(ids int32 [rows, n], log-probabilities float32 [rows, n]) of each row's n most likely
+        tokens, most likely first, ties by the smaller id; on the device."""
+        return ops.top_logprobs(logits, n)

@@ -214,6 +214,15 @@ def sample_token(logits: np.ndarray, temperature: float, key: int = 0, top_p: fl
     return int(np.argmax(score))
 
 
+def top_logprobs(logits: np.ndarray, n: int) -> List[tuple]:
+    """crates/mrun-engine/src/sample.rs:134-156: the n most likely tokens with lp = logits -
+    logsumexp(logits) (sample.rs:10-13), most likely first, ties by the smaller id."""
+    logits = np.asarray(logits, dtype=np.float64)
+    lp = logits - (logits.max() + np.log(np.exp(logits - logits.max()).sum()))
+    order = sorted(range(len(lp)), key=lambda i: (-lp[i], i))[:max(1, min(n, len(lp)))]
+    return [(i, float(lp[i])) for i in order]
+
+
 def apply_repetition_penalty(logits: np.ndarray, recent: Sequence[int], penalty: float) -> np.ndarray:
     """crates/mrun-engine/src/sample.rs:23-36: logits of recent ids divided by the penalty when
     >= 0, multiplied when negative."""

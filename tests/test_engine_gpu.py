@@ -184,3 +184,23 @@ def test_many_requests_through_few_slots_and_few_pages(tiny):
 
     too_long = tight.generate([random_tokens(cfg["vocab_size"], 400, seed=1)], max_tokens=4)[0]
     assert too_long.finish_reason == "too_long" and too_long.tokens == []
+
+
+def test_top_logprobs_beside_every_output_token(tiny):
+    """``logprobs=n`` reports the n most likely tokens at every generated place: the same ids and
+    values as the plain implementation, the chosen (greedy) token first, and the tokens unchanged."""
+    from mrun_b200 import Engine
+    name, folder, settings = tiny
+    cfg, weights = plain.load_folder(folder)
+    engine = Engine.from_folder(folder, dtype="float32", page_size=settings["page_size"], num_pages=64, max_requests=4)
+    prompts = [random_tokens(cfg["vocab_size"], n, seed=40 + n) for n in (5, 19)]
+    plain_runs = engine.generate(prompts, max_tokens=6, ignore_eos=True)
+    runs = engine.generate(prompts, max_tokens=6, ignore_eos=True, logprobs=3)
+    for prompt, run, base in zip(prompts, runs, plain_runs):
+        assert run.tokens == base.tokens and len(run.top_logprobs) == len(run.tokens) and not base.top_logprobs
+        tokens = list(prompt)
+        for token, top in zip(run.tokens, run.top_logprobs):
+            want = plain.top_logprobs(plain.forward(cfg, weights, tokens)[-1].numpy(), 3)
+            assert [i for i, _ in top] == [i for i, _ in want] and top[0][0] == token
+            assert max(abs(a - b) for (_, a), (_, b) in zip(top, want)) <= 1e-4
+            tokens.append(token)

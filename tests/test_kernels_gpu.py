@@ -292,3 +292,16 @@ def test_kernels_refuse_what_they_cannot_take():
     with pytest.raises(KernelError, match="rotary_dim"):
         ops().qk_norm_rope_cache(torch.zeros(1, 48, device=DEV), 1, 1, 16, None, None, 0.0,
                                  torch.zeros(1, 2, 2, device=DEV), 5, None, None, None, 4)
+
+
+@pytest.mark.parametrize("rows,vocab,n", [(1, 7, 3), (3, 509, 5), (2, 151936, 2), (4, 1000, 1000), (2, 33, 40)])
+def test_top_logprobs(rows, vocab, n):
+    logits = rnd(rows, vocab, seed=vocab + n) * 3.0
+    logits[0, min(5, vocab - 1)] = logits[0, 0]                  # a tie: the smaller id comes first
+    ids, values = ops().top_logprobs(logits, n)
+    n_eff = min(n, vocab)
+    assert ids.shape == (rows, n_eff) and values.shape == (rows, n_eff)
+    for row in range(rows):
+        want = plain.top_logprobs(logits[row].cpu().numpy(), n)
+        assert ids[row].tolist() == [i for i, _ in want]
+        assert np.abs(values[row].cpu().numpy() - np.array([v for _, v in want])).max() <= 2e-5
