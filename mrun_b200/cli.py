@@ -165,7 +165,14 @@ def command_run(args) -> int:
     defaults = generation_defaults(args.model)
     pick = lambda value, key: defaults[key] if value is None else value
     start = time.perf_counter()
-    result = engine.generate([prompt], max_tokens=args.max_tokens,
+    streamed = []
+
+    def show(_, token):                     # ids go out as they are read back, as `mrun run` streams text
+        sys.stdout.write(("," if streamed else "") + str(token))
+        sys.stdout.flush()
+        streamed.append(token)
+
+    result = engine.generate([prompt], max_tokens=args.max_tokens, on_token=show,
                              temperature=pick(args.temperature, "temperature"),
                              top_p=pick(args.top_p, "top_p"), top_k=pick(args.top_k, "top_k"),
                              min_p=pick(args.min_p, "min_p"), seed=args.seed,
@@ -174,7 +181,7 @@ def command_run(args) -> int:
     if result.finish_reason in ("invalid", "too_long", "queue_full"):
         print(f"error: {result.message}", file=sys.stderr)
         return 1
-    print(",".join(map(str, result.tokens)))
+    print("" if streamed == result.tokens else "\n" + ",".join(map(str, result.tokens)))
     ttft = result.time_to_first_token_s
     print(f"prompt: {len(prompt)} tokens, {len(prompt) / max(ttft, 1e-9):.1f} tokens-per-sec", file=sys.stderr)
     print(f"generation: {len(result.tokens)} tokens, "

@@ -114,13 +114,16 @@ class Engine:
     def generate(self, prompts: Sequence[Sequence[int]], max_tokens: int = 2048, temperature: float = 0.0,
                  top_p: float = 1.0, top_k: int = 0, min_p: float = 0.0, seed: Optional[int] = None,
                  repetition_penalty: float = 1.0, ignore_eos: bool = False,
-                 sampling: Optional[Sequence[SamplingParams]] = None, logprobs: int = 0) -> List[Generation]:
+                 sampling: Optional[Sequence[SamplingParams]] = None, logprobs: int = 0,
+                 on_token=None) -> List[Generation]:
         """Generates for every prompt (lists of token ids) and returns the results in order.
         ``sampling`` gives each prompt settings of its own; otherwise all share the keyword
         values, prompt i drawing with ``seed + i`` when a seed is given.  ``logprobs`` = n > 0
         also reports, for every output token, the n most likely tokens at its place with their
         log-probabilities (of the logits as the model gave them, before any penalty); such
-        requests are read back step by step, not pipelined."""
+        requests are read back step by step, not pipelined.  ``on_token(i, token)`` is called as
+        each output token of prompt i reaches the host (with pipelined decoding one step after it
+        was sampled), the way the reference streams a generation to its client."""
         if not 0 <= logprobs <= 1024:
             raise ValueError(f"logprobs must be 0 .. 1024, got {logprobs}")
         requests = []
@@ -133,7 +136,8 @@ class Engine:
                                         repetition_penalty=repetition_penalty)
             requests.append(Request(request_id=("gen", self._next_id), prompt=list(map(int, prompt)),
                                     max_tokens=max_tokens, sampling=params, ignore_eos=ignore_eos,
-                                    logprobs=logprobs))
+                                    logprobs=logprobs,
+                                    on_token=None if on_token is None else (lambda r, t, i=i: on_token(i, t))))
             self._next_id += 1
         self.run(requests)
         return [Generation(tokens=r.output, finish_reason=r.finish_reason, message=r.message,

@@ -66,6 +66,7 @@ class Request:
     sampling: SamplingParams = GREEDY
     ignore_eos: bool = False
     logprobs: int = 0                  # how many of the most likely tokens to report beside each output token
+    on_token: Optional[object] = None  # called with (request, token) as each output token is read back
     # ---- run state
     state: str = "new"                 # new | waiting | running | finished
     output: List[int] = field(default_factory=list)
@@ -287,6 +288,8 @@ class Scheduler:
                 request.first_token_at = now
             request.output.append(token)
             request.token_times.append(now)
+            if request.on_token is not None:
+                request.on_token(request, token)
             reason = None
             if token in self.eos and not request.ignore_eos:
                 reason = "stop"

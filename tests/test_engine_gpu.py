@@ -39,8 +39,11 @@ def test_greedy_generation_matches_plain(tiny, dtype):
     prompts = [random_tokens(cfg["vocab_size"], n, seed=n) for n in (1, 9, 40, 71)]
     engine = Engine.from_folder(folder, dtype=dtype, page_size=settings["page_size"], context=1024,
                                 max_batch_tokens=7, max_requests=4)
-    results = engine.generate(prompts, max_tokens=12, ignore_eos=True)
+    streamed = {i: [] for i in range(len(prompts))}
+    results = engine.generate(prompts, max_tokens=12, ignore_eos=True,
+                              on_token=lambda i, token: streamed[i].append(token))
     assert engine.executor._graphs, "decode steps should have gone through a captured graph"
+    assert [streamed[i] for i in range(len(prompts))] == [r.tokens for r in results]
     for prompt, result in zip(prompts, results):
         assert result.finish_reason == "length" and len(result.tokens) == 12
         margin = 1e-3 if dtype == "float32" else 0.05
