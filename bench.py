@@ -203,12 +203,13 @@ def main() -> int:
         batches = [int(b) for b in args.batches.split(",")]
     slack = args.steps + args.warmup + 64
     context = args.context
-    capacity = max(max(batches) * (context + slack), 8 * (context + 2 * slack)) + args.prefill_depth + PREFILL_TOKENS + 4 * 64
+    # the requests of every batch size are alive together, so that the clocks can be sampled over all of them
+    capacity = max(sum(batches) * (context + slack), 8 * (context + 2 * slack)) + args.prefill_depth + PREFILL_TOKENS + 4 * 64
     sizes["max_position_embeddings"] = max(sizes["max_position_embeddings"], context + slack + 64,
                                            args.prefill_depth + PREFILL_TOKENS + 64)
     config = Qwen3Config(**sizes)
     engine = Engine.from_config(config, seed=0, dtype="bfloat16", page_size=page_size,
-                                num_pages=-(-capacity // page_size), max_requests=max(64, max(batches)),
+                                num_pages=-(-capacity // page_size), max_requests=max(64, sum(batches)),
                                 max_batch_tokens=max(PREFILL_TOKENS, args.prefill_depth))
     executor = engine.executor
     vocab = config.vocab_size
@@ -251,20 +252,20 @@ def main() -> int:
 
     # ---------------------------------------------------------------- decode at batch 8 / 1 / 64
     results = {}
-    clocks = {}
     launches = 0
+    all_requests = {batch: fill_requests(executor, batch, context, vocab, f"decode{batch}") for batch in batches}
+    sampler = ClockSampler()             # clocks and throttle reasons over every timed decode region
+    sampler.start()
     for batch in batches:
-        requests = fill_requests(executor, batch, context, vocab, f"decode{batch}")
-        sampler = ClockSampler()
+        ms, n_launch = time_decode(executor, all_requests[batch], vocab, args.steps, args.warmup,
+                                   args.profiler_range == "decode")
         if batch == batches[0]:
-            sampler.start()
-        ms, n_launch = time_decode(executor, requests, vocab, args.steps, args.warmup, args.profiler_range == "decode")
-        if batch == batches[0]:
-            clocks = sampler.stop()
             launches = n_launch
+        results[batch] = ms
+    clocks = sampler.stop()
+    for requests in all_requests.values():
         for r in requests:
             executor.release(r)
-        results[batch] = ms
     main_batch = batches[0]
     ms_per_step = results[main_batch] / args.steps
     value = main_batch * args.steps / (results[main_batch] * 1e-3)
