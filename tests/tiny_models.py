@@ -1,6 +1,7 @@
 """The tiny configurations the tests run on.  They differ in every size and option: head counts and
 groups, sizes that are no power of two, number of layers, vocabulary, the norms' eps, rope base,
-tied or untied head, norm weights, page size."""
+tied or untied head, norm weights, page size.  A and B have small heads (the mma.sync attention
+kernels), C has heads of 64 (the TMA and tcgen05 attention kernels)."""
 from __future__ import annotations
 
 import numpy as np
@@ -16,6 +17,12 @@ TINY = {
                     head_dim=32, intermediate_size=200, vocab_size=509, max_position_embeddings=2048,
                     rms_norm_eps=1e-5, rope_theta=1000000.0, tie_word_embeddings=False),
         seed=23, std=0.06, norm_noise=0.1, page_size=8),
+    # heads of 64: the sizes the TMA decode attention and the tcgen05 prefill attention take
+    "C": dict(
+        config=dict(num_hidden_layers=2, hidden_size=160, num_attention_heads=4, num_key_value_heads=2,
+                    head_dim=64, intermediate_size=224, vocab_size=300, max_position_embeddings=4096,
+                    rms_norm_eps=3e-6, rope_theta=500000.0, tie_word_embeddings=False),
+        seed=37, std=0.07, norm_noise=0.05, page_size=16),
 }
 
 
