@@ -18,27 +18,53 @@ the layers need, and slots for per-request state of fixed size.
 """
 from __future__ import annotations
 
-from dataclasses import dataclass, field
+import ctypes
+from dataclasses import dataclass
 from typing import Dict, List, Optional, Sequence, Tuple
 
 import numpy as np
 
+from . import native
 from .needs import FixedState, PagedKV
-from .pages import OutOfPages, PagePool
+from .pages import OutOfPages
 
 FREED = -1  # block-table entry of a logical block whose page was given back (or never taken)
 
 
-@dataclass
 class RequestCache:
-    """What one live request holds."""
+    """What one live request holds: a view of the native books through its state slot."""
 
-    request_id: object
-    slot: int
-    length: int = 0                       # tokens committed
-    pending: int = 0                      # tokens of a planned, uncommitted step
-    blocks: Dict[tuple, List[int]] = field(default_factory=dict)   # group key -> page per logical block
-    released: bool = False
+    def __init__(self, manager: "CacheManager", request_id: object, slot: int):
+        self._manager = manager
+        self.request_id = request_id
+        self.slot = slot
+        self.released = False
+
+    @property
+    def length(self) -> int:
+        """Tokens committed."""
+        return 0 if self.released else self._manager._lib.mrun_cache_length(self._manager._core, self.slot)
+
+    @property
+    def pending(self) -> int:
+        """Tokens of a planned, uncommitted step."""
+        return 0 if self.released else self._manager._lib.mrun_cache_pending(self._manager._core, self.slot)
+
+    @property
+    def blocks(self) -> Dict[tuple, List[int]]:
+        """Group key -> page per logical block (FREED where a window has passed)."""
+        m = self._manager
+        out = {}
+        for g, (key, group) in enumerate(m.groups.items()):
+            n = 0 if self.released else m._lib.mrun_cache_blocks(m._core, self.slot, g)
+            out[key] = group.table[self.slot, :n].tolist()
+        return out
+
+    def block_row(self, key: tuple) -> np.ndarray:
+        """The request's pages of one group as a view of the host block table."""
+        m = self._manager
+        n = m._lib.mrun_cache_blocks(m._core, self.slot, m._group_index[key])
+        return m.groups[key].table[self.slot, :n]
 
     def pages_held(self, key: tuple) -> List[int]:
         return [p for p in self.blocks.get(key, ()) if p != FREED]
@@ -47,30 +73,40 @@ class RequestCache:
 @dataclass
 class AppendPlan:
     items: List[Tuple[RequestCache, int]]
-    taken: List[Tuple[RequestCache, tuple, int, List[int]]]   # (request, group, first block, pages)
+    plan_id: int
     done: bool = False
+
+
+class _PoolView:
+    """The page pool of a group as the tests and the scheduler look at it."""
+
+    def __init__(self, manager: "CacheManager", index: int, what: str):
+        self._manager, self._index, self.what = manager, index, what
+        self.num_pages = manager.num_pages
+
+    @property
+    def free_count(self) -> int:
+        return self._manager._lib.mrun_cache_free_pages(self._manager._core, self._index)
+
+    def is_held(self, page: int) -> bool:
+        return bool(self._manager._lib.mrun_cache_is_held(self._manager._core, self._index, page))
 
 
 class PagedGroup:
     """One pool of pages and the block table of every state slot: ``table[slot, block]`` is the
     page of logical block ``block`` of the request in ``slot`` (FREED where it holds none).  The
-    host copy is authoritative; changes are queued and reach the device copy in one scatter at
-    the start of the next step (:meth:`CacheManager.drain_table_updates`)."""
+    host copy (a view of the native library's memory) is authoritative; changes are queued and
+    reach the device copy in one scatter at the start of the next step
+    (:meth:`CacheManager.drain_table_updates`)."""
 
-    def __init__(self, key: tuple, window: Optional[int], num_pages: int, max_requests: int,
-                 max_blocks: int):
+    def __init__(self, key: tuple, window: Optional[int], max_blocks: int):
         self.key = key
         self.window = window
-        self.pool = PagePool(num_pages, what=f"pages of group {key}")
         self.entries: List[int] = []
         self.max_blocks = max_blocks
-        self.table = np.full((max_requests, max_blocks), FREED, dtype=np.int32)
+        self.table: np.ndarray = np.empty((0, 0), dtype=np.int32)      # set once the books exist
         self.table_device = None
-        self.updates: List[Tuple[int, int]] = []        # (flat index, page)
-
-    def set(self, slot: int, block: int, page: int) -> None:
-        self.table[slot, block] = page
-        self.updates.append((slot * self.max_blocks + block, page))
+        self.pool: Optional[_PoolView] = None
 
 
 class EntryCache:
@@ -123,7 +159,6 @@ class CacheManager:
         self.max_blocks = max(1, min(max_blocks_per_request or num_pages, max(num_pages, 1)))
         self.groups: Dict[tuple, PagedGroup] = {}
         self.entries: List[Optional[EntryCache]] = []
-        self._slots = PagePool(max_requests, what="state slots")
         self._live: Dict[object, RequestCache] = {}
         self._state_tensors = []
 
@@ -142,8 +177,7 @@ class CacheManager:
                 key = need.group_key()
                 group = self.groups.get(key)
                 if group is None:
-                    group = self.groups[key] = PagedGroup(key, need.window, num_pages, max_requests,
-                                                          self.max_blocks)
+                    group = self.groups[key] = PagedGroup(key, need.window, self.max_blocks)
                     if device is not None:
                         import torch
                         group.table_device = torch.full((max_requests, self.max_blocks), FREED,
@@ -167,6 +201,31 @@ class CacheManager:
             else:
                 raise TypeError(f"schedule entry {i}: unknown cache need {need!r}")
 
+        # the books: pools, block tables, lengths, plans (csrc/host/cache_core.cpp)
+        self._lib = native.library()
+        windows = [-1 if g.window is None else g.window for g in self.groups.values()]
+        self._core = self._lib.mrun_cache_create(len(windows), native.int_array(windows), page_size, num_pages,
+                                                 max_requests, self.max_blocks)
+        if not self._core:
+            raise ValueError(f"bad cache sizes: page_size={page_size} num_pages={num_pages} "
+                             f"max_requests={max_requests}")
+        self._group_index = {key: g for g, key in enumerate(self.groups)}
+        for g, (key, group) in enumerate(self.groups.items()):
+            pointer = self._lib.mrun_cache_table(self._core, g)
+            group.table = np.ctypeslib.as_array(pointer, shape=(max_requests, self.max_blocks))
+            group.pool = _PoolView(self, g, f"pages of group {key}")
+        self._by_slot: Dict[int, RequestCache] = {}
+
+    def __del__(self):
+        core, self._core = getattr(self, "_core", None), None
+        if core:
+            for group in self.groups.values():          # the views must not outlive the memory
+                group.table = np.empty((0, 0), dtype=np.int32)
+            self._lib.mrun_cache_destroy(core)
+
+    def _message(self) -> str:
+        return self._lib.mrun_cache_error(self._core).decode()
+
     # ------------------------------------------------------------------ sizes
     def blocks_for(self, tokens: int) -> int:
         return -(-tokens // self.page_size)
@@ -178,7 +237,7 @@ class CacheManager:
 
     @property
     def free_slots(self) -> int:
-        return self._slots.free_count
+        return self._lib.mrun_cache_free_slots(self._core)
 
     @property
     def live(self) -> List[RequestCache]:
@@ -195,9 +254,12 @@ class CacheManager:
     def admit(self, request_id: object) -> RequestCache:
         if request_id in self._live:
             raise ValueError(f"request {request_id!r} is already live")
-        (slot,) = self._slots.alloc(1)
-        request = RequestCache(request_id, slot, blocks={key: [] for key in self.groups})
+        slot = self._lib.mrun_cache_admit(self._core)
+        if slot < 0:
+            raise OutOfPages("state slots", 1, 0)
+        request = RequestCache(self, request_id, slot)
         self._live[request_id] = request
+        self._by_slot[slot] = request
         for state in self._state_tensors:
             state[slot].zero_()
         return request
@@ -210,24 +272,20 @@ class CacheManager:
             raise ValueError(f"request {request.request_id!r} is released twice")
         if request.pending:
             raise ValueError(f"request {request.request_id!r} has an uncommitted step")
-        for key, group in self.groups.items():
-            group.pool.free(request.pages_held(key))
-            for block, page in enumerate(request.blocks[key]):
-                if page != FREED:
-                    group.set(request.slot, block, FREED)
-            request.blocks[key] = []
-        self._slots.free([request.slot])
+        if self._lib.mrun_cache_release(self._core, request.slot):
+            raise ValueError(f"request {request.request_id!r}: {self._message()}")
         request.released = True
         del self._live[request.request_id]
+        del self._by_slot[request.slot]
 
     # ------------------------------------------------------------------ appending
     def pages_needed(self, request: RequestCache, tokens: int) -> Dict[tuple, int]:
         """Pages each group must add so that ``request`` can take ``tokens`` more."""
         target = self.blocks_for(request.length + request.pending + tokens)
-        return {key: max(0, target - len(request.blocks[key])) for key in self.groups}
+        return {key: max(0, target - self._lib.mrun_cache_blocks(self._core, request.slot, g))
+                for key, g in self._group_index.items()}
 
     def plan_append(self, items: Sequence[Tuple[RequestCache, int]]) -> AppendPlan:
-        wanted: Dict[tuple, int] = {key: 0 for key in self.groups}
         seen = set()
         for request, tokens in items:
             if request.released:
@@ -239,100 +297,75 @@ class CacheManager:
                 raise ValueError(f"request {request.request_id!r}: a step brings at least one token")
             if request.pending:
                 raise ValueError(f"request {request.request_id!r} has an uncommitted step")
-            if self.groups and self.blocks_for(request.length + tokens) > self.max_blocks:
-                raise OutOfPages(f"blocks of request {request.request_id!r}",
-                                 self.blocks_for(request.length + tokens), self.max_blocks)
-            for key, n in self.pages_needed(request, tokens).items():
-                wanted[key] += n
-        for key, n in wanted.items():
-            free = self.groups[key].pool.free_count
-            if n > free:
-                raise OutOfPages(self.groups[key].pool.what, n, free)
-        taken = []
-        for request, tokens in items:
-            for key, n in self.pages_needed(request, tokens).items():
-                if n:
-                    group = self.groups[key]
-                    pages = group.pool.alloc(n)
-                    first = len(request.blocks[key])
-                    taken.append((request, key, first, pages))
-                    request.blocks[key].extend(pages)
-                    for i, page in enumerate(pages):
-                        group.set(request.slot, first + i, page)
-            request.pending = tokens
-        return AppendPlan(list(items), taken)
+        n = len(items)
+        plan_id = self._lib.mrun_cache_plan(self._core, n, native.int_array(r.slot for r, _ in items),
+                                            native.int_array(t for _, t in items))
+        if plan_id < 0:
+            raise ValueError(self._message())
+        if plan_id == 0:
+            group, wanted, free, slot = (ctypes.c_int() for _ in range(4))
+            self._lib.mrun_cache_shortage(self._core, ctypes.byref(group), ctypes.byref(wanted), ctypes.byref(free),
+                                          ctypes.byref(slot))
+            if group.value == -2:
+                raise OutOfPages(f"blocks of request {self._by_slot[slot.value].request_id!r}", wanted.value, free.value)
+            key = list(self.groups)[group.value]
+            raise OutOfPages(self.groups[key].pool.what, wanted.value, free.value)
+        return AppendPlan(list(items), plan_id)
 
     def commit(self, plan: AppendPlan) -> None:
         if plan.done:
             raise ValueError("the plan was already committed or rolled back")
         plan.done = True
-        for request, tokens in plan.items:
-            request.length += tokens
-            request.pending = 0
-            for key, group in self.groups.items():
-                if group.window is None:
-                    continue
-                # the next token sits at position >= length and sees keys >= length - window + 1
-                first_needed = max(0, request.length - group.window + 1) // self.page_size
-                blocks = request.blocks[key]
-                passed = [b for b in range(min(first_needed, len(blocks))) if blocks[b] != FREED]
-                if passed:
-                    group.pool.free([blocks[b] for b in passed])
-                    for b in passed:
-                        blocks[b] = FREED
-                        group.set(request.slot, b, FREED)
+        if self._lib.mrun_cache_commit(self._core, plan.plan_id):
+            raise ValueError(self._message())
 
     def rollback(self, plan: AppendPlan) -> None:
         if plan.done:
             raise ValueError("the plan was already committed or rolled back")
         plan.done = True
-        for request, key, first, pages in reversed(plan.taken):
-            blocks = request.blocks[key]
-            assert blocks[first:first + len(pages)] == pages and len(blocks) == first + len(pages)
-            del blocks[first:]
-            self.groups[key].pool.free(pages)
-            for i in range(len(pages)):
-                self.groups[key].set(request.slot, first + i, FREED)
-        for request, _ in plan.items:
-            request.pending = 0
+        if self._lib.mrun_cache_rollback(self._core, plan.plan_id):
+            raise ValueError(self._message())
+
+    def layout_step(self, slots: Sequence[int], counts: Sequence[int], positions: np.ndarray,
+                    token_slot: np.ndarray, seg_q_start: np.ndarray, seg_kv_len: np.ndarray,
+                    seg_slot: np.ndarray, maps: Sequence[np.ndarray]) -> int:
+        """Fills the per-token arrays of a step (int32 views of the step's host buffer): entry s
+        brings ``counts[s]`` tokens of the request in ``slots[s]``.  ``maps[g]`` gets each token's
+        place in the pages of group g.  Returns the number of tokens."""
+        as_ints = lambda a: a.ctypes.data_as(ctypes.POINTER(ctypes.c_int))
+        pointers = (ctypes.POINTER(ctypes.c_int) * max(1, len(maps)))(*[as_ints(m) for m in maps])
+        n = self._lib.mrun_cache_layout_step(self._core, len(slots), native.int_array(slots), native.int_array(counts),
+                                             as_ints(positions), as_ints(token_slot), as_ints(seg_q_start),
+                                             as_ints(seg_kv_len), as_ints(seg_slot), pointers)
+        if n < 0:
+            raise ValueError(self._message())
+        return n
 
     # ------------------------------------------------------------------ device tables
     def drain_table_updates(self) -> Dict[tuple, Tuple[np.ndarray, np.ndarray]]:
         """The queued block-table changes per group as (flat indices, pages), oldest first with
         only the last change of an index kept; the queues are emptied."""
         out = {}
-        for key, group in self.groups.items():
-            if group.updates:
-                last = dict(group.updates)          # later entries overwrite earlier ones
-                out[key] = (np.fromiter(last.keys(), dtype=np.int32, count=len(last)),
-                            np.fromiter(last.values(), dtype=np.int32, count=len(last)))
-                group.updates = []
+        for key, g in self._group_index.items():
+            queued = self._lib.mrun_cache_pending_updates(self._core, g)
+            if not queued:
+                continue
+            index = np.empty(queued, dtype=np.int32)
+            value = np.empty(queued, dtype=np.int32)
+            as_ints = lambda a: a.ctypes.data_as(ctypes.POINTER(ctypes.c_int))
+            n = self._lib.mrun_cache_drain(self._core, g, as_ints(index), as_ints(value), queued)
+            out[key] = (index[:n].copy(), value[:n].copy())
         return out
 
     # ------------------------------------------------------------------ checks
     def check_invariants(self) -> None:
-        """No page lost, held by two requests, or free while held."""
-        self._slots.check()
+        """No page lost, held by two requests, or free while held; the block tables agree with
+        what the live requests hold."""
+        problem = self._lib.mrun_cache_check(self._core).decode()
+        if problem:
+            raise AssertionError(problem)
         slots = [r.slot for r in self._live.values()]
         if len(set(slots)) != len(slots):
             raise AssertionError("two live requests share a state slot")
-        if self._slots.free_count + len(slots) != self.max_requests:
+        if self.free_slots + len(slots) != self.max_requests:
             raise AssertionError("a state slot is lost")
-        for key, group in self.groups.items():
-            group.pool.check()
-            held: List[int] = []
-            for request in self._live.values():
-                held.extend(request.pages_held(key))
-            if len(set(held)) != len(held):
-                raise AssertionError(f"group {key}: a page is held twice")
-            for page in held:
-                if not group.pool.is_held(page):
-                    raise AssertionError(f"group {key}: page {page} is in a block table and free")
-            for request in self._live.values():
-                row = self.groups[key].table[request.slot]
-                blocks = request.blocks[key]
-                if list(row[:len(blocks)]) != blocks or (row[len(blocks):] != FREED).any():
-                    raise AssertionError(f"group {key}: the block table of slot {request.slot} differs "
-                                         f"from request {request.request_id!r}'s pages")
-            if len(held) + group.pool.free_count != group.pool.num_pages:
-                raise AssertionError(f"group {key}: {group.pool.num_pages - len(held) - group.pool.free_count} pages lost")

@@ -1,4 +1,5 @@
-"""A pool of equally sized pages with a free list.
+"""A pool of equally sized pages with a free list (the books are kept by the host runtime library,
+``csrc/host/cache_core.cpp``).
 
 Freed pages go on top of the list and are handed out first, so a page that one request gave back
 is soon written by another without being cleared; the tests rely on that to show that nothing
@@ -6,7 +7,10 @@ reads stale contents.
 """
 from __future__ import annotations
 
+import ctypes
 from typing import Iterable, List
+
+from . import native
 
 
 class OutOfPages(RuntimeError):
@@ -23,41 +27,39 @@ class PagePool:
             raise ValueError(f"num_pages must not be negative, got {num_pages}")
         self.num_pages = num_pages
         self.what = what
-        self._free: List[int] = list(range(num_pages - 1, -1, -1))
-        self._held = [False] * num_pages
+        self._lib = native.library()
+        self._handle = self._lib.mrun_pool_create(num_pages)
+
+    def __del__(self):
+        handle, self._handle = getattr(self, "_handle", None), None
+        if handle:
+            self._lib.mrun_pool_destroy(handle)
 
     @property
     def free_count(self) -> int:
-        return len(self._free)
+        return self._lib.mrun_pool_free_count(self._handle)
 
     def alloc(self, n: int) -> List[int]:
         """All ``n`` pages or :class:`OutOfPages` with nothing taken."""
-        if n > len(self._free):
-            raise OutOfPages(self.what, n, len(self._free))
-        taken = [self._free.pop() for _ in range(n)]
-        for page in taken:
-            self._held[page] = True
-        return taken
+        out = (ctypes.c_int * max(1, n))()
+        if self._lib.mrun_pool_alloc(self._handle, n, out):
+            raise OutOfPages(self.what, n, self.free_count)
+        return list(out[:n])
 
     def free(self, pages: Iterable[int]) -> None:
-        pages = list(pages)
-        for page in pages:
-            if not 0 <= page < self.num_pages:
-                raise ValueError(f"{self.what}: page {page} is outside the pool")
-            if not self._held[page]:
-                raise ValueError(f"{self.what}: page {page} is freed twice")
-            self._held[page] = False
-        self._free.extend(pages)
+        pages = [int(p) for p in pages]
+        bad = ctypes.c_int(0)
+        status = self._lib.mrun_pool_free(self._handle, native.int_array(pages), len(pages), ctypes.byref(bad))
+        if status == 1:
+            raise ValueError(f"{self.what}: page {bad.value} is outside the pool")
+        if status == 2:
+            raise ValueError(f"{self.what}: page {bad.value} is freed twice")
 
     def is_held(self, page: int) -> bool:
-        return self._held[page]
+        return bool(self._lib.mrun_pool_is_held(self._handle, page))
 
     def check(self) -> None:
         """Raises if a page is lost, listed twice, or both free and held."""
-        if len(set(self._free)) != len(self._free):
-            raise AssertionError(f"{self.what}: a page is on the free list twice")
-        for page in self._free:
-            if self._held[page]:
-                raise AssertionError(f"{self.what}: page {page} is free and held")
-        if len(self._free) + sum(self._held) != self.num_pages:
-            raise AssertionError(f"{self.what}: {self.num_pages - len(self._free) - sum(self._held)} pages lost")
+        problem = self._lib.mrun_pool_check(self._handle).decode()
+        if problem:
+            raise AssertionError(f"{self.what}: {problem}")

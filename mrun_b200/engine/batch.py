@@ -159,44 +159,16 @@ def build_context(entries: Sequence[StepEntry], manager: CacheManager, staging: 
     for m in maps:
         m[real:] = -1
 
-    segments: List[SegmentInfo] = []
-    row = 0
+    # positions, slots, segment bounds and every token's place in the pages: the native books know them
+    slots = [e.request.slot for e in entries]
+    manager.layout_step(slots, lengths, positions, token_slot, seg_q_start, seg_kv_len, seg_slot, maps)
     if max(lengths) == 1:
-        # every entry brings one token (a decode step): plain lists, one conversion per array
-        n_real = len(entries)
-        starts = [e.request.length for e in entries]
-        slots = [e.request.slot for e in entries]
-        token_ids[:n_real] = [e.tokens[0] for e in entries]
-        positions[:n_real] = starts
-        token_slot[:n_real] = slots
-        seg_slot[:n_real] = slots
-        seg_q_start[:n_real] = range(n_real)
-        seg_kv_len[:n_real] = [p + 1 for p in starts]
-        for g, key in enumerate(keys):
-            values = []
-            for e, p in zip(entries, starts):
-                page = e.request.blocks[key][p // page_size]
-                values.append(-1 if page == FREED else page * page_size + p % page_size)
-            maps[g][:n_real] = values
-        segments = [SegmentInfo(slot, i, 1, p) for i, (slot, p) in enumerate(zip(slots, starts))]
-        entries_loop = ()
+        token_ids[:len(entries)] = [e.tokens[0] for e in entries]
     else:
-        entries_loop = entries
-    for s, entry in enumerate(entries_loop):
-        n, start = lengths[s], entry.request.length
-        token_ids[row:row + n] = np.asarray(entry.tokens, dtype=np.int64)
-        pos = np.arange(start, start + n, dtype=np.int32)
-        positions[row:row + n] = pos
-        token_slot[row:row + n] = entry.request.slot
-        seg_q_start[s] = row
-        seg_kv_len[s] = start + n
-        seg_slot[s] = entry.request.slot
-        for g, key in enumerate(keys):
-            blocks = np.asarray(entry.request.blocks[key], dtype=np.int32)
-            pages = blocks[pos // page_size]
-            maps[g][row:row + n] = np.where(pages == FREED, -1, pages * page_size + pos % page_size)
-        segments.append(SegmentInfo(entry.request.slot, row, n, start))
-        row += n
+        token_ids[:real] = np.concatenate([np.asarray(e.tokens, dtype=np.int64) for e in entries])
+    starts = seg_kv_len[:len(entries)] - np.asarray(lengths, dtype=np.int32)
+    segments = [SegmentInfo(slot, int(q0), n, int(p))
+                for slot, q0, n, p in zip(slots, seg_q_start[:len(entries)].tolist(), lengths, starts.tolist())]
     seg_q_start[len(entries):] = real
 
     push_table_updates(manager, staging)

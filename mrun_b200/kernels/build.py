@@ -140,6 +140,48 @@ def build_library(name: str, source_names: Iterable[str],
         return target
 
 
+HOST_SOURCES = ("host/cache_core.cpp",)
+CXX_FLAGS = ["-O2", "-std=c++17", "-shared", "-fPIC", "-fvisibility=hidden"]
+
+
+def find_cxx() -> str:
+    for candidate in (os.environ.get("CXX"), shutil.which("g++"), shutil.which("c++"), shutil.which("clang++")):
+        if candidate and (os.path.exists(candidate) or shutil.which(candidate)):
+            return candidate
+    raise BuildError("no C++ compiler was found (looked at $CXX, g++, c++, clang++); the host runtime library "
+                     "cannot be built")
+
+
+def build_host() -> str:
+    """The host-side runtime library (the cache manager's bookkeeping): plain C++, no CUDA."""
+    sources = [os.path.join(CSRC, n) for n in HOST_SOURCES]
+    h = hashlib.sha256()
+    for path in sources:
+        with open(path, "rb") as f:
+            h.update(f.read())
+    h.update(" ".join(CXX_FLAGS).encode())
+    with _lock:
+        target = os.path.join(build_dir(), f"libmrun_host_{h.hexdigest()[:16]}.so")
+        if os.path.exists(target):
+            return target
+        cxx = find_cxx()
+        _say(f"building {os.path.basename(target)} from {len(sources)} file(s) ...")
+        tmp = target + f".{os.getpid()}.tmp"
+        proc = subprocess.run([cxx, *CXX_FLAGS, "-o", tmp, *sources], stdout=subprocess.PIPE,
+                              stderr=subprocess.STDOUT, text=True)
+        if proc.returncode != 0:
+            raise BuildError(f"{cxx} failed on the host runtime library:\n{proc.stdout}")
+        os.replace(tmp, target)
+        _say(f"built {os.path.basename(target)}")
+        for other in os.listdir(os.path.dirname(target)):
+            if other.startswith("libmrun_host_") and other.endswith(".so") and other != os.path.basename(target):
+                try:
+                    os.remove(os.path.join(os.path.dirname(target), other))
+                except OSError:
+                    pass
+        return target
+
+
 CORE_SOURCES = ("common.cu", "elementwise.cu", "gemm_f32.cu", "gemm_skinny.cu", "gemm_tc5.cu",
                 "attention_generic.cu", "sampling.cu")
 
@@ -180,4 +222,4 @@ COMMON_HEAD_DIMS = (16, 32, 64, 128)
 def build_all() -> list[str]:
     """Every library the package loads for the configurations it measures and tests; other head
     sizes are built when a model with them is first run."""
-    return [build_core()] + [build_attention(d) for d in COMMON_HEAD_DIMS]
+    return [build_host(), build_core()] + [build_attention(d) for d in COMMON_HEAD_DIMS]
