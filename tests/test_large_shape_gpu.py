@@ -108,3 +108,60 @@ def test_greedy_tokens_agree_between_the_precisions(engines):
     assert half._graphs and all(len(x.tokens) == 12 for x in a + b)
     agree = sum(x.tokens[0] == y.tokens[0] for x, y in zip(a, b))
     assert agree >= len(prompts) - 1, [(x.tokens[:3], y.tokens[:3]) for x, y in zip(a, b)]
+
+
+OTHER_SHAPES = {
+    # Qwen3-4B: heads x head size (4096) is not the width (2560), tied head
+    "4b": dict(num_hidden_layers=2, hidden_size=2560, num_attention_heads=32, num_key_value_heads=8, head_dim=128,
+               intermediate_size=9728, vocab_size=151936, max_position_embeddings=8192, rms_norm_eps=1e-6,
+               rope_theta=1e6, tie_word_embeddings=True),
+    # Qwen3-32B: eight query heads per kv head (the attention kernels' 16-token tiles and two-stage ring)
+    "32b": dict(num_hidden_layers=2, hidden_size=5120, num_attention_heads=64, num_key_value_heads=8, head_dim=128,
+                intermediate_size=25600, vocab_size=151936, max_position_embeddings=8192, rms_norm_eps=1e-6,
+                rope_theta=1e6, tie_word_embeddings=False),
+}
+
+
+@pytest.mark.parametrize("shape", sorted(OTHER_SHAPES))
+def test_other_layer_shapes_follow_the_32_bit_path(shape):
+    """Two layers of the Qwen3-4B and Qwen3-32B shapes: a prompt whole, then tokens one by one
+    through the captured step, then a mixed step, bfloat16 against the engine's 32-bit path."""
+    from mrun_b200.config import Qwen3Config
+    from mrun_b200.engine import Executor, StepEntry
+    from mrun_b200.weights import random_tensors
+    if torch.cuda.get_device_properties(0).total_memory < 60 * 2 ** 30:
+        pytest.skip("needs about 20 GB of device memory")
+    config = Qwen3Config(**OTHER_SHAPES[shape])
+    spec = config.to_spec()
+    tensors = dict(random_tensors(spec, seed=2, std=0.02, norm_noise=0.1, dtype=torch.bfloat16, device="cuda:0"))
+    half = Executor(spec, tensors, dtype="bfloat16", page_size=16, num_pages=128, max_requests=4)
+    full = Executor(spec, tensors, dtype="float32", page_size=16, num_pages=128, max_requests=4)
+    del tensors
+    rng = np.random.default_rng(6)
+    tokens = rng.integers(0, config.vocab_size, size=330).tolist()
+    other = rng.integers(0, config.vocab_size, size=90).tolist()
+    head = 300
+
+    def run(ex, captured):
+        rows = []
+        r = ex.admit("a")
+        rows.append(ex.step([StepEntry(r, tokens[:head], [0, 17, head - 1])]).float().cpu().numpy())
+        for i in range(head, head + 8):                               # token by token
+            if captured:
+                ex.decode_step([StepEntry(r, [tokens[i]], [0])])
+                rows.append(ex.decode_logits([None]).float().cpu().numpy())
+            else:
+                rows.append(ex.step([StepEntry(r, [tokens[i]], [0])]).float().cpu().numpy())
+        s = ex.admit("b")                                             # a portion beside a single token
+        rows.append(ex.step([StepEntry(s, other, [0, 89]), StepEntry(r, [tokens[head + 8]], [0])]).float().cpu().numpy())
+        ex.release(r)
+        ex.release(s)
+        return np.concatenate(rows)
+
+    want, got = run(full, False), run(half, True)
+    assert half._graphs
+    from mrun_b200.kernels import ops
+    ops.tc5_check()
+    assert got.shape == want.shape == (3 + 8 + 3, config.vocab_size)
+    error = np.abs(got - want).max() / np.abs(want).max()
+    assert error <= 4e-2, error
