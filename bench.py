@@ -3,6 +3,7 @@
 random weights and seeded synthetic token ids.
 
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--layers L] [--impl ours|reference]
+                    [--shape 8b|4b|32b] [--serve]
 
 A *step* is one decode step of a batch of 8 requests that each hold 1,024 tokens of context.
 ``value`` is decoded tokens per second over exactly K steps, timed on the device with CUDA events
@@ -10,6 +11,8 @@ after W warm-up steps, through the same captured step and host loop that generat
 ``e2e`` is the same quantity through ``Engine.generate`` with host token lists in and out.
 The line also carries a 2,048-token prefill, the decode step's HBM roofline, and decode at batch
 1 and 64.  Weights (15 GB) are far larger than L2, so every step reads them from HBM.
+``--shape`` runs the same at the 4B or 32B layer sizes (the 32B at 2,048 tokens of context and
+batch 1, 8 and 32), and ``--serve`` times a mixed workload of 16 requests through the scheduler.
 """
 from __future__ import annotations
 
@@ -29,6 +32,14 @@ FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "source": "fallback"
 QWEN3_8B = dict(num_hidden_layers=36, hidden_size=4096, num_attention_heads=32, num_key_value_heads=8,
                 head_dim=128, intermediate_size=12288, vocab_size=151936, max_position_embeddings=8192,
                 rms_norm_eps=1e-6, rope_theta=1000000.0, tie_word_embeddings=False)
+# the other layer shapes the baseline names, for --shape (the default run is the 8B shape)
+SHAPES = {
+    "8b": ("Qwen3-8B", QWEN3_8B, 1024),
+    "4b": ("Qwen3-4B", dict(QWEN3_8B, hidden_size=2560, intermediate_size=9728, max_position_embeddings=32768,
+                            tie_word_embeddings=True), 1024),
+    "32b": ("Qwen3-32B", dict(QWEN3_8B, num_hidden_layers=64, hidden_size=5120, num_attention_heads=64,
+                              intermediate_size=25600), 2048),
+}
 CONTEXT = 1024
 PREFILL_TOKENS = 2048
 
@@ -153,6 +164,64 @@ def time_decode(executor, requests, vocab: int, steps: int, warmup: int, profile
     return begin.elapsed_time(end), executor.launches.total - launches
 
 
+def serve(args, config, model_name: str, full_layers: int, page_size: int, peaks: dict) -> int:
+    """The baseline's mixed workload: 16 requests whose prompts hold 64 to 16,384 seeded tokens,
+    prompts cut into portions under a budget of 2,048 tokens a step beside the decoding of the
+    others, 256 tokens decoded for each.  Everything goes through ``Engine.generate``; the times
+    are the host's clock around that one call (it ends when the last token is on the host)."""
+    import numpy as np
+    import torch
+    from mrun_b200 import Engine
+    from mrun_b200.kernels import lib as kernel_lib
+
+    requests, decode_tokens = 16, 256
+    lengths = np.random.default_rng(11).integers(64, 16384 + 1, size=requests).tolist()
+    prompts = [seeded_tokens(config.vocab_size, n, 200 + i) for i, n in enumerate(lengths)]
+    capacity = sum(-(-(n + decode_tokens) // page_size) for n in lengths) + 64
+    engine = Engine.from_config(config, seed=0, dtype="bfloat16", page_size=page_size, num_pages=capacity,
+                                max_requests=requests, max_batch_tokens=PREFILL_TOKENS)
+    engine.generate([p[:300] for p in prompts[:4]], max_tokens=8, ignore_eos=True)       # warm-up: shapes, graphs
+    engine.generate(prompts[:2], max_tokens=4, ignore_eos=True)
+    sampler = ClockSampler()
+    sampler.start()
+    steps_before, launches = engine.stats.steps, engine.executor.launches.total
+    torch.cuda.synchronize()
+    begin = time.perf_counter()
+    generations = engine.generate(prompts, max_tokens=decode_tokens, ignore_eos=True)
+    torch.cuda.synchronize()
+    seconds = time.perf_counter() - begin
+    clocks = sampler.stop()
+    decoded = sum(len(g.tokens) for g in generations)
+    last_first = max(g.first_token_time for g in generations)
+    finished = max(g.finished_time for g in generations)
+    tail = sum(sum(1 for t in g.token_times if t > last_first) for g in generations)
+    steps = engine.stats.steps - steps_before
+    line = {
+        "metric": f"tokens/s, prompts and decoded, {requests} mixed requests ({model_name} bf16)",
+        "value": round((sum(lengths) + decoded) / seconds, 1), "unit": "tok/s", "n_gpus": 1,
+        "steps": steps, "warmup": 2, "ms_per_step": round(seconds * 1e3 / max(1, steps), 4),
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
+        "data": "synthetic (seeded uniform token ids, N(0,0.02) weights)", "impl": "ours",
+        "config": {"model": f"{model_name} shape", "layers": config.num_hidden_layers, "layers_of_config": full_layers,
+                   "hidden": config.hidden_size, "heads": config.num_attention_heads,
+                   "kv_heads": config.num_key_value_heads, "head_dim": config.head_dim,
+                   "intermediate": config.intermediate_size, "vocab": config.vocab_size,
+                   "tied": config.tie_word_embeddings, "global_batch": requests, "prompt_tokens": sum(lengths),
+                   "longest_prompt": max(lengths), "decoded_per_request": decode_tokens,
+                   "max_batch_tokens": PREFILL_TOKENS, "page_size": page_size, "parallelism": "single GPU"},
+        "seconds": round(seconds, 3), "decoded": decoded,
+        "time_to_first_token_s": {"median": round(statistics.median(g.time_to_first_token_s for g in generations), 3),
+                                  "max": round(max(g.time_to_first_token_s for g in generations), 3)},
+        "decode_tail": {"value": round(tail / max(finished - last_first, 1e-9), 1), "unit": "tok/s",
+                        "note": "all 16 decoding side by side, after the last prompt ended"},
+        "preemptions": sum(g.preemptions for g in generations),
+        "gpu_launches": engine.executor.launches.total - launches, "clocks": clocks, "peaks": peaks,
+        "kernel_entry_calls": kernel_lib.call_count(),
+    }
+    print(json.dumps(line))
+    return 0
+
+
 def main() -> int:
     parser = argparse.ArgumentParser()
     parser.add_argument("--gpus", type=int, default=1)
@@ -165,7 +234,12 @@ def main() -> int:
     parser.add_argument("--batches", default=None,
                         help="decode batch sizes to run, comma separated (for profiling one point)")
     parser.add_argument("--skip-prefill", action="store_true")
-    parser.add_argument("--context", type=int, default=CONTEXT,
+    parser.add_argument("--shape", choices=sorted(SHAPES), default="8b",
+                        help="layer sizes: the baseline's 8B shape, or its 4B and 32B shapes")
+    parser.add_argument("--serve", action="store_true",
+                        help="instead of the decode step: 16 requests with prompts of 64 to 16,384 tokens and "
+                             "256 decoded tokens each through Engine.generate, prompts cut at 2,048 tokens")
+    parser.add_argument("--context", type=int, default=None,
                         help="tokens each request holds when decoding is timed (the default is the baseline's)")
     parser.add_argument("--prefill-depth", type=int, default=0,
                         help="tokens already in the cache before the timed portion of 2,048 (0: a fresh prompt)")
@@ -192,13 +266,20 @@ def main() -> int:
     from mrun_b200.kernels import lib as kernel_lib
 
     peaks = load_peaks()
-    sizes = dict(QWEN3_8B)
+    model_name, shape_sizes, shape_context = SHAPES[args.shape]
+    sizes = dict(shape_sizes)
+    if args.context is None:
+        args.context = shape_context
     full_layers = sizes["num_hidden_layers"]
     if args.layers is not None:
         sizes["num_hidden_layers"] = args.layers
+    if args.serve:
+        sizes["max_position_embeddings"] = max(sizes["max_position_embeddings"], 16384 + 256 + 64)
     config = Qwen3Config(**sizes)
     page_size = 16
-    batches = [8] if args.skip_points else [8, 1, 64]
+    if args.serve:
+        return serve(args, config, model_name, full_layers, page_size, peaks)
+    batches = [8] if args.skip_points else [8, 1, 32 if args.shape == "32b" else 64]
     if args.batches:
         batches = [int(b) for b in args.batches.split(",")]
     slack = args.steps + args.warmup + 64
@@ -307,19 +388,19 @@ def main() -> int:
            "d2h_bytes_per_step": round((engine.stats.d2h_bytes - d2h_before) / n_steps, 1)}
 
     line = {
-        "metric": f"decode tok/s at batch {main_batch} (Qwen3-8B bf16, {context:,}-token prompts)",
+        "metric": f"decode tok/s at batch {main_batch} ({model_name} bf16, {context:,}-token prompts)",
         "value": round(value, 1), "unit": "tok/s", "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": round(ms_per_step, 4), "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "bf16", "data": "synthetic (seeded uniform token ids, N(0,0.02) weights)",
         "impl": "ours",
         "config": {
-            "model": "Qwen3-8B shape", "layers": config.num_hidden_layers, "layers_of_config": full_layers,
+            "model": f"{model_name} shape", "layers": config.num_hidden_layers, "layers_of_config": full_layers,
             "hidden": h, "heads": config.num_attention_heads, "kv_heads": config.num_key_value_heads,
             "head_dim": d, "intermediate": config.intermediate_size, "vocab": vocab,
             "rope_theta": config.rope_theta, "rms_norm_eps": config.rms_norm_eps,
             "tied": config.tie_word_embeddings, "global_batch": main_batch, "seq_len": context,
             "max_context": config.max_position_embeddings, "page_size": page_size,
-            "parallelism": "single GPU", "l2": "inputs larger than L2 (15 GB of weights per step)",
+            "parallelism": "single GPU", "l2": f"inputs larger than L2 ({weight_bytes / 1e9:.0f} GB of weights per step)",
         },
         "e2e": e2e, "gpu_launches": launches, "clocks": clocks,
         "prefill": prefill, "roofline": roofline, "points": points,

@@ -404,8 +404,8 @@ decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_consta
                 // the blocks that share this pair are p_first .. p_last; the last to arrive merges their
                 // pieces in block order
                 int p_first, p_last;
-                if (splits > 0) {            // the pair's own run of blocks, as many as have tiles
-                    p_first = (sg.kvh * tokens + sg.tok) * splits;
+                if (splits > 0) {            // the pair's own run of blocks: `splits` blocks a kv head
+                    p_first = sg.kvh * splits + tile_prefix[tokens + 1 + sg.tok];
                     p_last = p_first + (sg.pair_tiles + per - 1) / per - 1;
                 } else {
                     p_first = sg.pair_start / per;

@@ -273,28 +273,41 @@ prefill_kernel(const bf16* __restrict__ q, long q_stride, bf16* __restrict__ out
 constexpr int STAGES = MRUN_DECODE_STAGES;
 static_assert(STAGES >= 2 && STAGES <= 4, "2 to 4 key/value tiles in flight");
 
-// The plan of a decode step: tile_prefix[t] = number of 64-key tiles of tokens 0 .. t-1 (a
-// padding token has none), so tile_prefix[tokens] is the step's total per kv head.  One block.
-__global__ void decode_plan_kernel(const int* __restrict__ positions, int tokens, int window,
-                                   int* __restrict__ tile_prefix) {
-    __shared__ int carry;
-    __shared__ int scan[1024];
+// Sum and maximum over the block's 1024 threads; every thread gets the result.
+__device__ __forceinline__ int plan_reduce(int v, bool take_max, int* scratch) {
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) {
+        const int other = __shfl_xor_sync(0xffffffffu, v, off);
+        v = take_max ? max(v, other) : v + other;
+    }
+    if ((threadIdx.x & 31) == 0) scratch[threadIdx.x >> 5] = v;
+    __syncthreads();
+    if (threadIdx.x < 32) {
+        v = scratch[threadIdx.x];
+#pragma unroll
+        for (int off = 16; off > 0; off >>= 1) {
+            const int other = __shfl_xor_sync(0xffffffffu, v, off);
+            v = take_max ? max(v, other) : v + other;
+        }
+        if (threadIdx.x == 0) scratch[32] = v;
+    }
+    __syncthreads();
+    v = scratch[32];
+    __syncthreads();
+    return v;
+}
+
+// prefix[0] = 0, prefix[t + 1] = value(0) + .. + value(t) for t < tokens.  One block of 1024 threads.
+template <typename F>
+__device__ __forceinline__ void plan_prefix(F value, int tokens, int* __restrict__ prefix, int* scan, int* carry) {
     if (threadIdx.x == 0) {
-        carry = 0;
-        tile_prefix[0] = 0;
+        *carry = 0;
+        prefix[0] = 0;
     }
     __syncthreads();
     for (int base = 0; base < tokens; base += 1024) {
         const int t = base + threadIdx.x;
-        int n = 0;
-        if (t < tokens) {
-            const int pos = positions[t];
-            if (pos >= 0) {
-                const int lo = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
-                n = pos / BLOCK_N - lo / BLOCK_N + 1;
-            }
-        }
-        scan[threadIdx.x] = n;
+        scan[threadIdx.x] = t < tokens ? value(t) : 0;
         __syncthreads();
         for (int step = 1; step < 1024; step <<= 1) {            // inclusive scan of the chunk
             const int add = threadIdx.x >= step ? scan[threadIdx.x - step] : 0;
@@ -302,40 +315,86 @@ __global__ void decode_plan_kernel(const int* __restrict__ positions, int tokens
             scan[threadIdx.x] += add;
             __syncthreads();
         }
-        if (t < tokens) tile_prefix[t + 1] = carry + scan[threadIdx.x];
+        if (t < tokens) prefix[t + 1] = *carry + scan[threadIdx.x];
         __syncthreads();
-        if (threadIdx.x == 1023) carry += scan[1023];
+        if (threadIdx.x == 1023) *carry += scan[1023];
         __syncthreads();
     }
 }
 
-// What block b of the decode kernel starts with, so that it needs one load and no search:
-// {first tile, end tile, kv head, token} and {tiles per kv head, tiles per block, splits per pair, -}.
+// The plan of a decode step: tile_prefix[t] = number of 64-key tiles of tokens 0 .. t-1 (a
+// padding token has none), so tile_prefix[tokens] is the step's total per kv head.  One block.
 //
-// Two ways of dealing the tiles.  splits == 0, for steps with at least as many (token, kv head)
-// pairs as blocks: block b takes tiles [b * per, (b + 1) * per) of the flat list, across pairs.
-// splits > 0, for steps with few pairs: every pair is cut into up to `splits` equal runs of at
-// least min_tiles tiles, one block each (blocks = pairs * splits), so that no block pays the
-// start-up of two pairs for a handful of tiles.
+// blocks_per_head > 0 (steps with few pairs, every block stays with one pair): the step's tiles
+// per block `per` is the smallest number, at least min_tiles, with which the pairs of one kv head
+// need no more than blocks_per_head blocks and no pair more than max_pieces: a long context gets
+// many blocks and a short one a single block, and the longest run of tiles any block streams is as
+// short as the launch allows.  Then tile_prefix[tokens + 1 + t] = blocks of tokens 0 .. t-1 and
+// tile_prefix[2 * (tokens + 1)] = per.
+__global__ void decode_plan_kernel(const int* __restrict__ positions, int tokens, int window,
+                                   int* __restrict__ tile_prefix, int blocks_per_head, int min_tiles,
+                                   int max_pieces) {
+    __shared__ int carry;
+    __shared__ int scan[1024];
+    __shared__ int scratch[33];
+    plan_prefix([&](int t) {
+        const int pos = positions[t];
+        if (pos < 0) return 0;
+        const int lo = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
+        return pos / BLOCK_N - lo / BLOCK_N + 1;
+    }, tokens, tile_prefix, scan, &carry);
+    if (blocks_per_head <= 0) return;
+    int longest = 0;
+    for (int t = threadIdx.x; t < tokens; t += 1024) longest = max(longest, tile_prefix[t + 1] - tile_prefix[t]);
+    longest = plan_reduce(longest, true, scratch);
+    int lo = max(min_tiles, (longest + max_pieces - 1) / max_pieces);
+    int hi = max(lo, longest);                 // with `longest` tiles a block every pair takes one block
+    while (lo < hi) {
+        const int mid = (lo + hi) >> 1;
+        int need = 0;
+        for (int t = threadIdx.x; t < tokens; t += 1024)
+            need += (tile_prefix[t + 1] - tile_prefix[t] + mid - 1) / mid;
+        need = plan_reduce(need, false, scratch);
+        if (need <= blocks_per_head) hi = mid; else lo = mid + 1;
+    }
+    const int per = lo;
+    int* block_prefix = tile_prefix + tokens + 1;
+    plan_prefix([&](int t) { return (tile_prefix[t + 1] - tile_prefix[t] + per - 1) / per; }, tokens, block_prefix,
+                scan, &carry);
+    if (threadIdx.x == 0) block_prefix[tokens + 1] = per;
+}
+
+// What block b of the decode kernel starts with, so that it needs one load and no search:
+// {first tile, end tile, kv head, token} and {tiles per kv head, tiles per block, blocks per kv head, -}.
+//
+// Two ways of dealing the tiles.  blocks_per_head == 0, for steps with more (token, kv head)
+// pairs than blocks: block b takes tiles [b * per, (b + 1) * per) of the flat list, across pairs.
+// blocks_per_head > 0, for steps with few pairs: block i of a kv head belongs to the token whose
+// run of blocks (the plan's second prefix) holds i and takes that pair's next `per` tiles, so
+// that no block pays the start-up of two pairs for a handful of tiles.
 __global__ void decode_assign_kernel(const int* __restrict__ tile_prefix, int tokens, int kv_heads, int blocks,
-                                     int min_tiles, int splits, int4* __restrict__ assignment) {
+                                     int min_tiles, int blocks_per_head, int4* __restrict__ assignment) {
     const int b = blockIdx.x * blockDim.x + threadIdx.x;
     if (b >= blocks) return;
     const int tiles_per_head = tile_prefix[tokens];
     const int total = tiles_per_head * kv_heads;
     int u0 = 0, u1 = 0, kvh = 0, tok = 0, per = 0;
-    if (splits > 0) {
-        const int pair = b / splits, s = b - pair * splits;
-        kvh = pair / tokens;
-        tok = pair - kvh * tokens;
-        if (kvh < kv_heads) {
-            const int pair_tiles = tile_prefix[tok + 1] - tile_prefix[tok];
-            per = max((pair_tiles + splits - 1) / splits, min_tiles);
-            const int j0 = s * per;
-            if (j0 < pair_tiles) {
-                u0 = kvh * tiles_per_head + tile_prefix[tok] + j0;
-                u1 = u0 + min(per, pair_tiles - j0);
+    if (blocks_per_head > 0) {
+        const int* block_prefix = tile_prefix + tokens + 1;
+        per = block_prefix[tokens + 1];
+        kvh = b / blocks_per_head;
+        const int i = b - kvh * blocks_per_head;
+        if (kvh < kv_heads && i < block_prefix[tokens]) {
+            int lo_t = 0, hi_t = tokens - 1;                          // the last token t with block_prefix[t] <= i
+            while (lo_t < hi_t) {
+                const int mid = (lo_t + hi_t + 1) >> 1;
+                if (block_prefix[mid] <= i) lo_t = mid; else hi_t = mid - 1;
             }
+            tok = lo_t;
+            const int pair_tiles = tile_prefix[tok + 1] - tile_prefix[tok];
+            const int j0 = (i - block_prefix[tok]) * per;
+            u0 = kvh * tiles_per_head + tile_prefix[tok] + j0;
+            u1 = u0 + min(per, pair_tiles - j0);
         }
     } else {
         per = max((total + blocks - 1) / blocks, min_tiles);
@@ -353,7 +412,7 @@ __global__ void decode_assign_kernel(const int* __restrict__ tile_prefix, int to
         }
     }
     assignment[2 * b] = make_int4(u0, u1, kvh, tok);
-    assignment[2 * b + 1] = make_int4(tiles_per_head, per, splits, 0);
+    assignment[2 * b + 1] = make_int4(tiles_per_head, per, blocks_per_head, 0);
 }
 
 // grid: `blocks` blocks, the number the plan was made for.
@@ -571,8 +630,8 @@ decode_kernel(const bf16* __restrict__ q, long q_stride, bf16* __restrict__ out,
             // the blocks that share this pair are p_first .. p_last; the last to arrive merges their
             // pieces in block order
             int p_first, p_last;
-            if (splits > 0) {            // the pair's own run of blocks, as many as have tiles
-                p_first = (kvh * tokens + tok) * splits;
+            if (splits > 0) {            // the pair's own run of blocks: `splits` blocks a kv head
+                p_first = kvh * splits + prefix[tokens + 1 + tok];
                 p_last = p_first + (pair_tiles + per - 1) / per - 1;
             } else {
                 p_first = pair_start / per;
@@ -644,24 +703,28 @@ MRUN_API int mrun_attn_prefill(const void* q, long q_stride, void* out, const vo
 }
 
 // The plan of a decode step for a window (0 = none) and a launch of `blocks` blocks that take at
-// least min_tiles tiles each: tile_prefix gets tokens + 1 ints, assignment 8 ints per block.
-// splits == 0: the tiles of all pairs are dealt evenly across the blocks; splits > 0: every pair
-// has `splits` blocks of its own (blocks = tokens * kv_heads * splits).  The plan is the same for
-// every layer with that window and those sizes, so a step computes it once.
+// least min_tiles tiles each: assignment gets 8 ints per block.
+// splits == 0: the tiles of all pairs are dealt evenly across the blocks; tile_prefix gets
+// tokens + 1 ints.  splits > 0: every block stays with one pair; each kv head has blocks / kv_heads
+// blocks (a multiple, and at least `tokens`), dealt to its pairs by their length, at most `splits`
+// to one pair; tile_prefix gets 2 * (tokens + 1) + 1 ints.  The plan is the same for every layer
+// with that window and those sizes, so a step computes it once.
 MRUN_API int mrun_attn_decode_plan(const int* positions, int tokens, int window, int kv_heads, int blocks,
                                    int min_tiles, int splits, int* tile_prefix, int* assignment,
                                    cudaStream_t stream) {
     MRUN_REQUIRE(tokens >= 0 && window >= 0 && kv_heads >= 1 && blocks >= 1 && min_tiles >= 1 && splits >= 0,
                  "attn_decode_plan: tokens=%d window=%d kv_heads=%d blocks=%d min_tiles=%d splits=%d", tokens, window,
                  kv_heads, blocks, min_tiles, splits);
-    MRUN_REQUIRE(splits == 0 || blocks == tokens * kv_heads * splits,
-                 "attn_decode_plan: with %d splits per pair the launch has tokens * kv_heads * splits = %d blocks, not %d",
-                 splits, tokens * kv_heads * splits, blocks);
+    MRUN_REQUIRE(splits == 0 || (blocks % kv_heads == 0 && blocks / kv_heads >= tokens),
+                 "attn_decode_plan: blocks that stay with one pair need a multiple of kv_heads = %d blocks and at "
+                 "least one for each of %d tokens a kv head, not %d", kv_heads, tokens, blocks);
     MRUN_REQUIRE(((uintptr_t)assignment & 15) == 0, "attn_decode_plan: the assignment must be 16-byte aligned");
-    decode_plan_kernel<<<1, 1024, 0, stream>>>(positions, tokens, window, tile_prefix);
+    const int blocks_per_head = splits > 0 ? blocks / kv_heads : 0;
+    decode_plan_kernel<<<1, 1024, 0, stream>>>(positions, tokens, window, tile_prefix, blocks_per_head, min_tiles,
+                                               splits);
     MRUN_CHECK_LAUNCH("attn_decode_plan");
     decode_assign_kernel<<<(blocks + 127) / 128, 128, 0, stream>>>(tile_prefix, tokens, kv_heads, blocks, min_tiles,
-                                                                  splits, (int4*)assignment);
+                                                                  blocks_per_head, (int4*)assignment);
     MRUN_CHECK_LAUNCH("attn_decode_plan: assignment");
     return 0;
 }
@@ -806,7 +869,7 @@ MRUN_API int mrun_attn_decode_static(const void* q, long q_stride, void* out, co
     // the counters must start at zero whatever an earlier, possibly interrupted, call left
     MRUN_CHECK_CUDA(cudaMemsetAsync(counters, 0, (size_t)tokens * kv_heads * sizeof(int), stream),
                     "attn_decode_static: clearing the counters");
-    decode_plan_kernel<<<1, 1024, 0, stream>>>(positions, tokens, window, tile_prefix);
+    decode_plan_kernel<<<1, 1024, 0, stream>>>(positions, tokens, window, tile_prefix, 0, min_tiles, 1);
     MRUN_CHECK_LAUNCH("attn_decode_static: plan");
     decode_assign_kernel<<<(blocks + 127) / 128, 128, 0, stream>>>(tile_prefix, tokens, kv_heads, blocks, min_tiles,
                                                                   0, (int4*)assignment);

@@ -218,7 +218,11 @@ void dispatch(const bf16* x, const bf16* w, TOut* y, int M, int N, int K, long l
         else if ((N + 15) / 16 > 2 * 148) launch<1, 1, SHALLOW, TOut, SWIGLU>(x, w, y, M, N, K, ldx, ldy, stream);
         else launch<1, 1, DEEP, TOut, SWIGLU>(x, w, y, M, N, K, ldx, ldy, stream);
     } else {
-        if (wide) launch<2, 2, SHALLOW, TOut, SWIGLU>(x, w, y, M, N, K, ldx, ldy, stream);
+        // 9 to 16 rows of x: every chunk carries twice the x, so one row tile a block, and with
+        // more than two rounds' worth of blocks one chunk per batch (measured at 16 rows, us:
+        // QKV 6144x4096 17.6 -> 12.7, gate/up 24576x4096 53.9 -> 37.7 with one chunk; O 4096x4096
+        // 10.4 and down 4096x12288 24.3 with two chunks, 11.2 and 28.2 with one)
+        if ((N + 15) / 16 > 2 * 148) launch<2, 1, 1, TOut, SWIGLU>(x, w, y, M, N, K, ldx, ldy, stream);
         else launch<2, 1, SHALLOW, TOut, SWIGLU>(x, w, y, M, N, K, ldx, ldy, stream);
     }
 }

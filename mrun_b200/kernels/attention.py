@@ -85,15 +85,17 @@ def supports_tensor_cores(dtype: torch.dtype, head_dim: int, group: int) -> bool
 MIN_TILES = 4      # the fewest 64-key tiles a block of the decode kernel takes (measured on B200)
 
 
-MAX_SPLITS = 32    # blocks per (token, kv head) pair when a step has few pairs
+MAX_SPLITS = 32    # the most blocks one (token, kv head) pair is cut into when a step has few pairs
 
 
 def decode_launch(tokens: int, kv_heads: int, slots: int):
     """(blocks, splits) of a decode step.  More (token, kv head) pairs than the device holds
-    blocks: all its blocks, the tiles dealt evenly across pairs (splits = 0).  Else every pair gets
-    as many blocks of its own as fill the device once: a block that never changes pair has no
-    partial result to hand over (measured with the TMA kernel at 1,024-token contexts: 288 pairs
-    on 288 blocks 28 us, 5.3 TB/s; 320 pairs dealt to 296 blocks 41 us, 4.1 TB/s)."""
+    blocks: all its blocks, the tiles dealt evenly across pairs (splits = 0).  Else every block
+    stays with one pair, since a block that never changes pair has no partial result to hand over
+    (measured with the TMA kernel at 1,024-token contexts: 288 pairs on 288 blocks 28 us,
+    5.3 TB/s; 320 pairs dealt to 296 blocks 41 us, 4.1 TB/s): the launch fills the device once,
+    every kv head has the same number of blocks, and the plan deals them to the head's pairs by
+    their length, at most ``splits`` to one pair."""
     pairs = tokens * kv_heads
     if pairs > slots:
         # k pairs a block where that leaves at least four fifths of the blocks busy: with equal
@@ -102,13 +104,14 @@ def decode_launch(tokens: int, kv_heads: int, slots: int):
         k = -(-pairs // slots)
         aligned = -(-pairs // k)
         return (aligned if 5 * aligned >= 4 * slots else slots), 0
-    splits = max(1, min(slots // pairs, MAX_SPLITS))
-    return pairs * splits, splits
+    per_head = max(tokens, min(slots // kv_heads, tokens * MAX_SPLITS))
+    return per_head * kv_heads, MAX_SPLITS
 
 
 def decode_plan(ctx, library, window: int, kv_heads: int, blocks: int, splits: int, positions=None):
-    """The step's plan for the decode kernel: tiles per token as a prefix sum (int32, tokens + 1)
-    and what each of ``blocks`` blocks starts with (int32, 8 per block).  Made once per step for
+    """The step's plan for the decode kernel: tiles per token as a prefix sum (int32, tokens + 1;
+    with ``splits`` also the blocks per token as a prefix sum and the tiles a block takes) and
+    what each of ``blocks`` blocks starts with (int32, 8 per block).  Made once per step for
     a window, a number of kv heads and a launch shape.  ``positions``: those of a selection of the
     step's tokens instead of all of them."""
     key = ("decode_plan", window, kv_heads, blocks, splits, positions is not None)
@@ -117,7 +120,7 @@ def decode_plan(ctx, library, window: int, kv_heads: int, blocks: int, splits: i
         if positions is None:
             positions = ctx.positions
         n = positions.shape[0]
-        prefix = torch.empty(n + 1, dtype=torch.int32, device=positions.device)
+        prefix = torch.empty(2 * (n + 1) + 1, dtype=torch.int32, device=positions.device)
         assignment = torch.empty(blocks * 8, dtype=torch.int32, device=positions.device)
         library.call("mrun_attn_decode_plan", _ptr(positions), _c_int(n), _c_int(window),
                      _c_int(kv_heads), _c_int(blocks), _c_int(MIN_TILES), _c_int(splits), _ptr(prefix),

@@ -132,12 +132,13 @@ def test_decode_batch_against_plain(heads, kv_heads, head_dim, page_size, window
 
 @pytest.mark.parametrize("blocks,min_tiles,splits", [(1, 1, 0), (3, 1, 0), (16, 1, 0), (64, 1, 0), (444, 1, 0), (5, 2, 0),
                                                      (16, 4, 0), (1000, 3, 0), (7, 40, 0),
-                                                     (16, 1, 1), (48, 1, 3), (256, 2, 16), (512, 4, 32)])
+                                                     (16, 1, 1), (48, 1, 3), (256, 2, 16), (512, 4, 32),
+                                                     (26, 1, 32), (40, 1, 2), (64, 3, 32)])
 @pytest.mark.parametrize("entry", ["mrun_attn_decode", "mrun_attn_decode_tma"])
 def test_decode_tiles_dealt_to_any_number_of_blocks(blocks, min_tiles, splits, entry):
     """The decode kernels (tiles copied by cp.async, tiles brought by TMA into a ring) called directly with forced launch shapes (one block takes every pair,
-    several blocks share pairs, more blocks than tiles; tiles dealt across pairs, or every pair
-    split between blocks of its own), twice in a row (the counters the blocks meet at must be
+    several blocks share pairs, more blocks than tiles; tiles dealt across pairs, or every block
+    with one pair and the blocks dealt to the pairs by their length), twice in a row (the counters the blocks meet at must be
     back at zero), against the CUDA-core kernel."""
     import ctypes
     from mrun_b200.kernels import lib as L, ops
@@ -149,15 +150,30 @@ def test_decode_tiles_dealt_to_any_number_of_blocks(blocks, min_tiles, splits, e
     want = case.run(scale, force_generic=True)
     n = case.tokens + case.pad
     library = L.attention(head_dim)
-    plan = torch.empty(n + 1, dtype=torch.int32, device=DEV)
+    plan = torch.full((2 * (n + 1) + 1,), -7, dtype=torch.int32, device=DEV)
     assignment = torch.empty(blocks * 8, dtype=torch.int32, device=DEV)
     library.call("mrun_attn_decode_plan", _ptr(case.ctx.positions), _c_int(n), _c_int(0), _c_int(kv_heads),
                  _c_int(blocks), _c_int(min_tiles), _c_int(splits), _ptr(plan), _ptr(assignment), _stream())
-    assert plan.tolist() == [0, 1, 2, 4, 15, 31, 34, 34, 34]
+    tiles = [1, 1, 2, 11, 16, 3, 0, 0]
+    assert plan[:n + 1].tolist() == [0, 1, 2, 4, 15, 31, 34, 34, 34]
     starts = assignment.view(blocks, 2, 4)[:, 0].tolist()
     if splits == 0:
         per = max(-(-68 // blocks), min_tiles)
         assert [s[0] for s in starts] == [min(68, b * per) for b in range(blocks)]    # 34 tiles x 2 kv heads
+        assert plan[n + 1:].tolist() == [-7] * (n + 2), "the flat plan writes tokens + 1 numbers"
+    else:
+        # the fewest tiles a block, at least min_tiles, with which a kv head's pairs fit its blocks
+        per_head = blocks // kv_heads
+        per = next(p for p in range(max(min_tiles, -(-16 // splits)), 17)
+                   if p == 16 or sum(-(-t // p) for t in tiles) <= per_head)
+        assert int(plan[2 * (n + 1)]) == per
+        pieces = [-(-t // per) for t in tiles]
+        assert plan[n + 1:2 * (n + 1)].tolist() == [sum(pieces[:i]) for i in range(n + 1)]
+        assert max(s[1] - s[0] for s in starts) <= per
+        for b, s in enumerate(starts):                # a block's tiles lie in its own pair
+            if s[1] > s[0]:
+                first = s[2] * 34 + sum(tiles[:s[3]])
+                assert first <= s[0] and s[1] <= first + tiles[s[3]] and s[2] == b // per_head
     assert sum(s[1] - s[0] for s in starts) == 68                                      # every tile dealt once
     part_o = torch.full((blocks, 2, 16, head_dim), float("nan"), device=DEV)
     part_ml = torch.full((blocks, 2, 16, 2), float("nan"), device=DEV)
@@ -177,6 +193,85 @@ def test_decode_tiles_dealt_to_any_number_of_blocks(blocks, min_tiles, splits, e
         assert (got - want).abs().max() <= 2e-2 * want.abs().max()
         assert got[case.tokens:].abs().max() == 0
         assert int(counters.abs().sum()) == 0
+
+
+UNEQUAL = [5000, 100, 3000, 64, 9000, 17]       # 79, 2, 47, 2, 141 and 1 tiles of 64 keys
+
+
+@pytest.mark.parametrize("contexts,blocks,min_tiles,splits,flat", [
+    ([0, 63, 64, 700, 1023, 129], 5, 1, 0, True), ([0, 63, 64, 700, 1023, 129], 64, 1, 0, True),
+    ([0, 63, 64, 700, 1023, 129], 48, 1, 3, False), ([0, 63, 64, 700, 1023, 129], 26, 1, 32, False),
+    (UNEQUAL, 7, 4, 0, True), (UNEQUAL, 296, 4, 0, True),
+    (UNEQUAL, 64, 4, 32, False), (UNEQUAL, 16, 4, 32, False), (UNEQUAL, 592, 4, 32, False),
+    (UNEQUAL, 16, 1, 2, False)])
+@pytest.mark.parametrize("raw", [False, True])
+@pytest.mark.parametrize("entry", ["mrun_attn_decode", "mrun_attn_decode_tma"])
+def test_decode_contexts_of_unequal_length_and_raw_input(contexts, blocks, min_tiles, splits, flat, raw, entry):
+    """The decode kernels called directly over contexts of equal and of very unequal length with
+    forced launch shapes; with ``raw`` they take the projection's q, k and v rows and norm, rotate
+    and store them themselves, compared with the stand-alone kernel doing that first."""
+    from mrun_b200.kernels import lib as L, ops
+    from mrun_b200.kernels.ops import _c_float, _c_int, _c_long, _ptr, _stream
+    heads, kv_heads, head_dim, page_size, eps, rotary = 8, 2, 64, 16, 1e-5, 48
+    case = Case([(c, 1) for c in contexts], heads, kv_heads, head_dim, page_size, torch.bfloat16, seed=5, pad=2)
+    scale = head_dim ** -0.5
+    n = case.tokens + case.pad
+    g = torch.Generator().manual_seed(17)
+    width = (heads + 2 * kv_heads) * head_dim
+    qkv = torch.randn(n, width, generator=g).to(torch.bfloat16).to(DEV)
+    q_weight = (1 + 0.2 * torch.randn(head_dim, generator=g)).to(DEV)
+    k_weight = (1 + 0.2 * torch.randn(head_dim, generator=g)).to(DEV)
+    angle = torch.rand(n, rotary // 2, generator=g) * 6.28
+    rot = torch.stack([angle.cos(), angle.sin()], dim=-1).contiguous().to(DEV)
+    slots = [case.seg_pages[s][c // page_size] * page_size + c % page_size for s, c in enumerate(contexts)] + [-1] * case.pad
+    slots = torch.tensor(slots, dtype=torch.int32, device=DEV)
+    library = L.attention(head_dim)
+
+    # what is wanted: the stand-alone kernel norms, rotates and stores, the CUDA-core kernel attends
+    k_want, v_want = case.kd.clone(), case.vd.clone()
+    if raw:
+        q_want = qkv.clone()
+        ops.qk_norm_rope_cache(q_want, heads, kv_heads, head_dim, q_weight, k_weight, eps, rot, rotary, slots,
+                               k_want, v_want, page_size)
+    else:
+        q_want = case.qd
+    want = torch.zeros((n, heads * head_dim), dtype=torch.bfloat16, device=DEV)
+    ops.paged_attention_generic(q_want, q_want.stride(0), want, k_want, v_want, case.table, case.ctx.token_slot,
+                                case.ctx.positions, heads, scale, 0)
+    want = want.float().cpu()
+
+    plan = torch.empty(2 * (n + 1) + 1, dtype=torch.int32, device=DEV)
+    assignment = torch.empty(blocks * 8, dtype=torch.int32, device=DEV)
+    library.call("mrun_attn_decode_plan", _ptr(case.ctx.positions), _c_int(n), _c_int(0), _c_int(kv_heads),
+                 _c_int(blocks), _c_int(min_tiles), _c_int(splits), _ptr(plan), _ptr(assignment), _stream())
+    shape = assignment.view(blocks, 2, 4)[:, 1].tolist()
+    assert all((row[2] == 0) == flat for row in shape)
+    tiles = sum(c // 64 + 1 for c in contexts) * kv_heads
+    assert sum(row[1] - row[0] for row in assignment.view(blocks, 2, 4)[:, 0].tolist()) == tiles
+    part_o = torch.full((blocks, 2, 16, head_dim), float("nan"), device=DEV)
+    part_ml = torch.full((blocks, 2, 16, 2), float("nan"), device=DEV)
+    counters = torch.zeros(n * kv_heads, dtype=torch.int32, device=DEV)
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    extra = (_ptr(None), _c_long(case.kd.shape[0]), _ptr(status)) if entry.endswith("tma") else ()
+    for _ in range(2):
+        k_got, v_got = case.kd.clone(), case.vd.clone()
+        q_in = qkv if raw else case.qd
+        out = torch.full((n, heads * head_dim), 3.0, dtype=torch.bfloat16, device=DEV)
+        fused = ((_c_int(1), _ptr(q_weight), _ptr(k_weight), _c_float(eps), _ptr(rot), _c_int(rotary), _ptr(slots)) if raw
+                 else (_c_int(0), _ptr(None), _ptr(None), _c_float(0.0), _ptr(None), _c_int(0), _ptr(None)))
+        library.call(
+            entry, _ptr(q_in), _c_long(q_in.stride(0)), _ptr(out), _ptr(k_got), _ptr(v_got),
+            _ptr(case.table), _c_int(case.group.max_blocks), _ptr(case.ctx.token_slot), _ptr(case.ctx.positions),
+            _ptr(plan), _ptr(assignment), _c_int(n), _ptr(part_o), _ptr(part_ml), _ptr(counters), _c_int(blocks),
+            _c_int(heads), _c_int(kv_heads), _c_int(head_dim), _c_int(page_size), _c_float(scale), _c_int(0),
+            *fused, *extra, _stream())
+        got = out.float().cpu()
+        assert int(status.item()) == 0
+        assert (got - want).abs().max() <= 2e-2 * want.abs().max()
+        assert got[case.tokens:].abs().max() == 0
+        assert int(counters.abs().sum()) == 0
+        assert (k_got.float() - k_want.float()).abs().max() <= 2e-2 * k_want.float().abs().max()
+        assert torch.equal(v_got, v_want)
 
 
 @pytest.mark.parametrize("far", [0, 15, 16, 63, 64, 65, 127, 255, 256, 400, 511])
