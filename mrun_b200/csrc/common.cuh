@@ -125,4 +125,14 @@ __device__ __forceinline__ float block_max(float v, float* scratch) {
     return scratch[32];
 }
 
+// SiLU(gate) * up.  The 32-bit path divides and takes the exponential exactly; the bfloat16
+// kernels (the stand-alone SwiGLU and the GEMM epilogues alike, so that a decode step and a prompt
+// step give the same number) use the special-function unit for both: a relative error near
+// 2^-21, far inside bfloat16's rounding, and a sixth of the instructions.
+template <bool EXACT>
+__device__ __forceinline__ float silu_mul(float gate, float up) {
+    if constexpr (EXACT) return gate / (1.f + expf(-gate)) * up;
+    else return __fdividef(gate, 1.f + __expf(-gate)) * up;
+}
+
 }  // namespace mrun

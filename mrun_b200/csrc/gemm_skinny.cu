@@ -192,7 +192,7 @@ skinny_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w, TOut* __re
                 // the activation sees the gate as the layer would have stored it
                 gate = __bfloat162float(__float2bfloat16_rn(gate));
                 up = __bfloat162float(__float2bfloat16_rn(up));
-                store_out<TOut>(y + (size_t)token * ldy + out_col, gate / (1.f + expf(-gate)) * up);
+                store_out<TOut>(y + (size_t)token * ldy + out_col, mrun::silu_mul<false>(gate, up));
             }
         }
     }

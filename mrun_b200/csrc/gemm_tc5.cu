@@ -87,7 +87,7 @@ __device__ __forceinline__ void write_columns(TOut* __restrict__ y, long ldy, co
             if (is_gate && tok0 + j < M && row < N) {
                 const float gate = __bfloat162float(__float2bfloat16_rn(v[j]));
                 const float up = __bfloat162float(__float2bfloat16_rn(up_raw));
-                store_out<TOut>(y + (size_t)(tok0 + j) * ldy + out_col, gate / (1.f + expf(-gate)) * up);
+                store_out<TOut>(y + (size_t)(tok0 + j) * ldy + out_col, mrun::silu_mul<false>(gate, up));
             }
         }
     }
