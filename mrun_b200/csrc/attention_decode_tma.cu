@@ -23,6 +23,8 @@
 // end without waiting again.
 //
 // Math as in the other attention kernels (crates/mrun-engine/src/models/common.rs:129,199-205).
+#include <cstdio>
+
 #include "attention_frag.cuh"
 #include "tcgen05.cuh"
 
@@ -165,6 +167,15 @@ __device__ __forceinline__ Segment next_segment(int seg, int u, int u_end, int& 
     return sg;
 }
 
+// -DMRUN_ATTN_TC5_TIMING: the first blocks print where a consumer's cycles went (a tuning aid).
+#ifdef MRUN_ATTN_TC5_TIMING
+#define DT_DECL long long dt_acc[8] = {}; long long dt_last = clock64();
+#define DT_MARK(i) { const long long dt_now = clock64(); dt_acc[i] += dt_now - dt_last; dt_last = dt_now; }
+#else
+#define DT_DECL
+#define DT_MARK(i)
+#endif
+
 // grid: `blocks` blocks, the number the plan was made for.  Scratch as for decode_kernel.
 template <int RING>
 __global__ void __launch_bounds__(TMA_THREADS)
@@ -188,6 +199,7 @@ decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_consta
 
     const int block_id = blockIdx.x, n_blocks_grid = gridDim.x;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    DT_DECL
     const int4 mine = assignment[2 * block_id], shape = assignment[2 * block_id + 1];
     const int u_begin = mine.x, u_end = mine.y;
     const int tiles_per_head = shape.x, per = shape.y, splits = shape.z;
@@ -200,21 +212,30 @@ decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_consta
         aborted = 0;
         mbar_init_fence();
     }
+    // The producer looks its first run of tiles up (plan, positions: dependent loads from global
+    // memory) while the block prepares its shared memory.  (Also reading the block-table entries
+    // of the first tiles and prefetching the tensor maps here made the kernel slower, 12.7 -> 13.5 us.)
+    Segment first_sg = {};
+    int first_kvh = mine.z, first_tok = mine.w;
+    if (warp == 4 && u_begin < u_end)
+        first_sg = next_segment(0, u_begin, u_end, first_kvh, first_tok, tiles_per_head, tile_prefix, positions, window);
     // rows of a V tile that no copy fills must not hold NaN patterns: 0 * NaN is NaN
     for (int s = 0; s < RING; ++s)
         for (int i = threadIdx.x; i < TILE_BYTES / 16; i += TMA_THREADS)
             reinterpret_cast<uint4*>(ring + s * STAGE_BYTES + TILE_BYTES)[i] = make_uint4(0, 0, 0, 0);
     fence_async_smem();
     __syncthreads();
+    DT_MARK(0)
 
     if (warp == 4) {
         // ------------------------------------------------------------------------------ producer
         const int box_rows = page_size < BLOCK_N ? page_size : BLOCK_N;
         const int boxes = BLOCK_N / box_rows;
-        int kvh = mine.z, tok = mine.w, u = u_begin, it = 0;
+        int kvh = first_kvh, tok = first_tok, u = u_begin, it = 0;
         bool alive = true;
         for (int seg = 0; alive && u < u_end; ++seg) {
-            const Segment sg = next_segment(seg, u, u_end, kvh, tok, tiles_per_head, tile_prefix, positions, window);
+            const Segment sg = seg == 0 ? first_sg
+                                        : next_segment(seg, u, u_end, kvh, tok, tiles_per_head, tile_prefix, positions, window);
             const int* table = block_tables + (size_t)token_slot[sg.tok] * max_blocks;
             for (int block = sg.first_block; block <= sg.last_block; ++block, ++it) {
                 const int s = it % RING, use = it / RING;
@@ -316,6 +337,7 @@ decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_consta
                 }
             }
             consumer_sync();                                    // q (and the new key and value) are in place
+            DT_MARK(1)
 
             int row_pos[2], row_lo[2];
 #pragma unroll
@@ -353,6 +375,7 @@ decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_consta
                 __syncwarp();
                 if (lane == 0) mbar_arrive(&empty_bar[s]);
             }
+            DT_MARK(2)
 #pragma unroll
             for (int rr = 0; rr < 2; ++rr) {
                 l[rr] += __shfl_xor_sync(0xffffffffu, l[rr], 1);
@@ -377,29 +400,36 @@ decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_consta
             }
             consumer_sync();
             const size_t my_slot = (size_t)block_id * 2 + (seg == 0 ? 0 : 1);
-            for (int i = threadIdx.x; i < group * D; i += CONSUMERS) {
-                const int row = i / D, d = i - row * D;
+            // a thread takes four values of a row: the warps' maxima and sums are read once for them
+            for (int i = threadIdx.x; i < group * (D / 4); i += CONSUMERS) {
+                const int row = i / (D / 4), d = (i - row * (D / 4)) * 4;
                 float mm = -INFINITY;
 #pragma unroll
                 for (int w = 0; w < 4; ++w) mm = fmaxf(mm, merge[(w * group + row) * MS + D]);
-                float acc = 0.f, ll = 0.f;
+                float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+                float ll = 0.f;
 #pragma unroll
                 for (int w = 0; w < 4; ++w) {
                     const float* src = merge + (w * group + row) * MS;
                     const float c = (src[D] == -INFINITY) ? 0.f : exp2f(src[D] - mm);
-                    acc += src[d] * c;
+                    const float2 lo2 = *reinterpret_cast<const float2*>(src + d), hi2 = *reinterpret_cast<const float2*>(src + d + 2);
+                    acc.x += lo2.x * c; acc.y += lo2.y * c; acc.z += hi2.x * c; acc.w += hi2.y * c;
                     ll += src[D + 1] * c;
                 }
                 if (sg.complete) {
-                    out[((size_t)q_row * heads + sg.kvh * group + row) * D + d] = __float2bfloat16_rn(ll > 0.f ? acc / ll : 0.f);
+                    const float inv = ll > 0.f ? 1.f / ll : 0.f;
+                    __nv_bfloat162 lo2 = __floats2bfloat162_rn(acc.x * inv, acc.y * inv);
+                    __nv_bfloat162 hi2 = __floats2bfloat162_rn(acc.z * inv, acc.w * inv);
+                    uint2 packed;
+                    packed.x = *reinterpret_cast<unsigned*>(&lo2);
+                    packed.y = *reinterpret_cast<unsigned*>(&hi2);
+                    *reinterpret_cast<uint2*>(out + ((size_t)q_row * heads + sg.kvh * group + row) * D + d) = packed;
                 } else {
-                    part_o[(my_slot * 16 + row) * D + d] = acc;
-                    if (d == 0) {
-                        part_ml[(my_slot * 16 + row) * 2] = mm;
-                        part_ml[(my_slot * 16 + row) * 2 + 1] = ll;
-                    }
+                    *reinterpret_cast<float4*>(part_o + (my_slot * 16 + row) * D + d) = acc;
+                    if (d == 0) *reinterpret_cast<float2*>(part_ml + (my_slot * 16 + row) * 2) = make_float2(mm, ll);
                 }
             }
+            DT_MARK(3)
             if (!sg.complete) {
                 // the blocks that share this pair are p_first .. p_last; the last to arrive merges their
                 // pieces in block order
@@ -415,30 +445,67 @@ decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_consta
                 consumer_sync();
                 if (threadIdx.x == 0) ticket_shared = atomicAdd(&counters[sg.tok * kv_heads + sg.kvh], 1);
                 consumer_sync();
+                DT_MARK(4)
                 if (ticket_shared == p_last - p_first) {
                     __threadfence();
-                    for (int i = threadIdx.x; i < group * D; i += CONSUMERS) {
-                        const int row = i / D, d = i - row * D;
+                    // A thread takes four values of a row.  The pieces are read four at a time, all
+                    // loads of a round requested before any is used (one piece after the other the
+                    // merge of four pieces took 3.9 us of a 13 us block).
+                    for (int i = threadIdx.x; i < group * (D / 4); i += CONSUMERS) {
+                        const int row = i / (D / 4), d = (i - row * (D / 4)) * 4;
+                        // block p's piece of this pair is its first segment iff its range starts inside the pair
+                        auto slot_of = [&](int p) -> size_t {
+                            return (size_t)p * 2 + ((splits > 0 || p * per >= sg.pair_start) ? 0 : 1);
+                        };
                         float mm = -INFINITY;
-                        for (int p = p_first; p <= p_last; ++p) {
-                            // block p's piece of this pair is its first segment iff its range starts inside the pair
-                            const size_t slot = (size_t)p * 2 + ((splits > 0 || p * per >= sg.pair_start) ? 0 : 1);
-                            mm = fmaxf(mm, __ldcg(part_ml + (slot * 16 + row) * 2));
+                        for (int p0 = p_first; p0 <= p_last; p0 += 4) {
+                            float ms[4];
+#pragma unroll
+                            for (int k = 0; k < 4; ++k)
+                                ms[k] = p0 + k <= p_last ? __ldcg(part_ml + (slot_of(p0 + k) * 16 + row) * 2) : -INFINITY;
+#pragma unroll
+                            for (int k = 0; k < 4; ++k) mm = fmaxf(mm, ms[k]);
                         }
-                        float acc = 0.f, ll = 0.f;
-                        for (int p = p_first; p <= p_last; ++p) {
-                            const size_t slot = (size_t)p * 2 + ((splits > 0 || p * per >= sg.pair_start) ? 0 : 1);
-                            const float ms = __ldcg(part_ml + (slot * 16 + row) * 2);
-                            const float c = (ms == -INFINITY) ? 0.f : exp2f(ms - mm);
-                            acc += __ldcg(part_o + (slot * 16 + row) * D + d) * c;
-                            ll += __ldcg(part_ml + (slot * 16 + row) * 2 + 1) * c;
+                        float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+                        float ll = 0.f;
+                        for (int p0 = p_first; p0 <= p_last; p0 += 4) {
+                            float2 ml[4];
+                            float4 po[4];
+#pragma unroll
+                            for (int k = 0; k < 4; ++k) {
+                                ml[k] = make_float2(-INFINITY, 0.f);
+                                po[k] = make_float4(0.f, 0.f, 0.f, 0.f);
+                                if (p0 + k <= p_last) {
+                                    const size_t at = slot_of(p0 + k) * 16 + row;
+                                    ml[k] = __ldcg(reinterpret_cast<const float2*>(part_ml + at * 2));
+                                    po[k] = __ldcg(reinterpret_cast<const float4*>(part_o + at * D + d));
+                                }
+                            }
+#pragma unroll
+                            for (int k = 0; k < 4; ++k) {
+                                const float c = (ml[k].x == -INFINITY) ? 0.f : exp2f(ml[k].x - mm);
+                                acc.x += po[k].x * c; acc.y += po[k].y * c; acc.z += po[k].z * c; acc.w += po[k].w * c;
+                                ll += ml[k].y * c;
+                            }
                         }
-                        out[((size_t)q_row * heads + sg.kvh * group + row) * D + d] = __float2bfloat16_rn(ll > 0.f ? acc / ll : 0.f);
+                        const float inv = ll > 0.f ? 1.f / ll : 0.f;
+                        __nv_bfloat162 lo2 = __floats2bfloat162_rn(acc.x * inv, acc.y * inv);
+                        __nv_bfloat162 hi2 = __floats2bfloat162_rn(acc.z * inv, acc.w * inv);
+                        uint2 packed;
+                        packed.x = *reinterpret_cast<unsigned*>(&lo2);
+                        packed.y = *reinterpret_cast<unsigned*>(&hi2);
+                        *reinterpret_cast<uint2*>(out + ((size_t)q_row * heads + sg.kvh * group + row) * D + d) = packed;
                     }
                     if (threadIdx.x == 0) counters[sg.tok * kv_heads + sg.kvh] = 0;
                 }
             }
             consumer_sync();            // the merge area, q and ticket_shared are reused by the next segment
+            DT_MARK(5)
+#ifdef MRUN_ATTN_TC5_TIMING
+            if (block_id < 4 && threadIdx.x == 0)
+                printf("decode block %d: start %lld, q ready %lld, tiles %lld (%d), warp merge and piece out %lld, ticket %lld, "
+                       "final merge %lld\n", block_id, dt_acc[0], dt_acc[1], dt_acc[2], sg.len, dt_acc[3], dt_acc[4], dt_acc[5]);
+#endif
             u += sg.len;
         }
     }

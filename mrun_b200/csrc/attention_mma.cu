@@ -643,23 +643,52 @@ decode_kernel(const bf16* __restrict__ q, long q_stride, bf16* __restrict__ out,
             __syncthreads();
             if (ticket_shared == p_last - p_first) {
                 __threadfence();
-                for (int i = threadIdx.x; i < group * D; i += THREADS) {
-                    const int row = i / D, d = i - row * D;
+                // A thread takes four values of a row; the pieces are read four at a time, all loads
+                // of a round requested before any is used.
+                for (int i = threadIdx.x; i < group * (D / 4); i += THREADS) {
+                    const int row = i / (D / 4), d = (i - row * (D / 4)) * 4;
+                    // block p's piece of this pair is its first segment iff its range starts inside the pair
+                    auto slot_of = [&](int p) -> size_t {
+                        return (size_t)p * 2 + ((splits > 0 || p * per >= pair_start) ? 0 : 1);
+                    };
                     float mm = -INFINITY;
-                    for (int p = p_first; p <= p_last; ++p) {
-                        // block p's piece of this pair is its first segment iff its range starts inside the pair
-                        const size_t slot = (size_t)p * 2 + ((splits > 0 || p * per >= pair_start) ? 0 : 1);
-                        mm = fmaxf(mm, __ldcg(part_ml + (slot * 16 + row) * 2));
+                    for (int p0 = p_first; p0 <= p_last; p0 += 4) {
+                        float ms[4];
+#pragma unroll
+                        for (int k = 0; k < 4; ++k)
+                            ms[k] = p0 + k <= p_last ? __ldcg(part_ml + (slot_of(p0 + k) * 16 + row) * 2) : -INFINITY;
+#pragma unroll
+                        for (int k = 0; k < 4; ++k) mm = fmaxf(mm, ms[k]);
                     }
-                    float acc = 0.f, ll = 0.f;
-                    for (int p = p_first; p <= p_last; ++p) {
-                        const size_t slot = (size_t)p * 2 + ((splits > 0 || p * per >= pair_start) ? 0 : 1);
-                        const float ms = __ldcg(part_ml + (slot * 16 + row) * 2);
-                        const float c = (ms == -INFINITY) ? 0.f : exp2f(ms - mm);
-                        acc += __ldcg(part_o + (slot * 16 + row) * D + d) * c;
-                        ll += __ldcg(part_ml + (slot * 16 + row) * 2 + 1) * c;
+                    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+                    float ll = 0.f;
+                    for (int p0 = p_first; p0 <= p_last; p0 += 4) {
+                        float2 ml[4];
+                        float4 po[4];
+#pragma unroll
+                        for (int k = 0; k < 4; ++k) {
+                            ml[k] = make_float2(-INFINITY, 0.f);
+                            po[k] = make_float4(0.f, 0.f, 0.f, 0.f);
+                            if (p0 + k <= p_last) {
+                                const size_t at = slot_of(p0 + k) * 16 + row;
+                                ml[k] = __ldcg(reinterpret_cast<const float2*>(part_ml + at * 2));
+                                po[k] = __ldcg(reinterpret_cast<const float4*>(part_o + at * D + d));
+                            }
+                        }
+#pragma unroll
+                        for (int k = 0; k < 4; ++k) {
+                            const float c = (ml[k].x == -INFINITY) ? 0.f : exp2f(ml[k].x - mm);
+                            acc.x += po[k].x * c; acc.y += po[k].y * c; acc.z += po[k].z * c; acc.w += po[k].w * c;
+                            ll += ml[k].y * c;
+                        }
                     }
-                    out[((size_t)tok * heads + kvh * group + row) * D + d] = __float2bfloat16_rn(ll > 0.f ? acc / ll : 0.f);
+                    const float inv = ll > 0.f ? 1.f / ll : 0.f;
+                    __nv_bfloat162 lo2 = __floats2bfloat162_rn(acc.x * inv, acc.y * inv);
+                    __nv_bfloat162 hi2 = __floats2bfloat162_rn(acc.z * inv, acc.w * inv);
+                    uint2 packed;
+                    packed.x = *reinterpret_cast<unsigned*>(&lo2);
+                    packed.y = *reinterpret_cast<unsigned*>(&hi2);
+                    *reinterpret_cast<uint2*>(out + ((size_t)tok * heads + kvh * group + row) * D + d) = packed;
                 }
                 if (threadIdx.x == 0) counters[tok * kv_heads + kvh] = 0;
             }
