@@ -307,6 +307,8 @@ decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_consta
                 // q, k and v arrive raw: [q heads | k heads | v heads] of D elements each in the token's row
                 const bf16* token_row = q + (size_t)sg.tok * q_stride;
                 const float2* cs = fused.rot ? fused.rot + (size_t)sg.tok * (fused.rotary_dim >> 1) : nullptr;
+                // where the token's own key and value go: asked for now, used after the heads are made
+                const int slot = (owns_new_token && fused.slots) ? fused.slots[sg.tok] : -1;
                 for (int row = warp; row < 16; row += 4) {
                     if (row < group)
                         norm_rotate_head(token_row + (size_t)(sg.kvh * group + row) * D, fused.q_weight, fused.eps, cs,
@@ -323,7 +325,6 @@ decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_consta
                     if (warp == 1)
                         for (int e = lane; e < D; e += 32) new_v[e] = token_row[(size_t)(heads + kv_heads + sg.kvh) * D + e];
                     consumer_sync();
-                    const int slot = fused.slots ? fused.slots[sg.tok] : -1;
                     if (slot >= 0) {
                         const int page = slot / page_size, off = slot - page * page_size;
                         const size_t at = (((size_t)page * kv_heads + sg.kvh) * page_size + off) * D;

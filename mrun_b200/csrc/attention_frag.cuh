@@ -78,6 +78,44 @@ __device__ __forceinline__ void norm_rotate_head(const bf16* __restrict__ src, c
                                                  float eps, const float2* __restrict__ cs, int rotary_dim,
                                                  float* vec, bf16* dst) {
     const int lane = threadIdx.x & 31;
+    if constexpr (D % 64 == 0) {
+        // Rotation over the whole head (or none): element e = lane + 32 i and its partner
+        // e + D / 2 belong to the same lane, so nothing travels through shared memory, and the
+        // head, the weight and the table row are requested together: one trip to memory, not three.
+        if (cs == nullptr || rotary_dim == D) {
+            constexpr int N = D % 64 == 0 ? D / 32 : 2, H = N / 2;      // (sizes that compile for every D)
+            float v[N], w[N];
+            float2 c[H];
+#pragma unroll
+            for (int i = 0; i < N; ++i) v[i] = __bfloat162float(src[lane + 32 * i]);
+#pragma unroll
+            for (int i = 0; i < N; ++i) w[i] = weight ? weight[lane + 32 * i] : 1.f;
+#pragma unroll
+            for (int i = 0; i < H; ++i) c[i] = cs ? cs[lane + 32 * i] : make_float2(1.f, 0.f);
+            if (weight) {
+                float ss = 0.f;
+#pragma unroll
+                for (int i = 0; i < N; ++i) ss += v[i] * v[i];
+                ss = mrun::warp_sum(ss);
+                const float inv = rsqrtf(ss / (float)D + eps);
+#pragma unroll
+                for (int i = 0; i < N; ++i) v[i] = v[i] * inv * w[i];
+            }
+            if (cs) {
+#pragma unroll
+                for (int i = 0; i < H; ++i) {
+                    const float x1 = v[i], x2 = v[i + H];
+                    dst[lane + 32 * i] = __float2bfloat16_rn(x1 * c[i].x - x2 * c[i].y);
+                    dst[lane + 32 * i + D / 2] = __float2bfloat16_rn(x2 * c[i].x + x1 * c[i].y);
+                }
+            } else {
+#pragma unroll
+                for (int i = 0; i < N; ++i) dst[lane + 32 * i] = __float2bfloat16_rn(v[i]);
+            }
+            __syncwarp();
+            return;
+        }
+    }
     float ss = 0.f;
     for (int e = lane; e < D; e += 32) {
         const float v = __bfloat162float(src[e]);
