@@ -1,5 +1,6 @@
-"""The host runtime library (``csrc/host/cache_core.cpp``) loaded through ctypes: page pools and the
-cache manager's books in C++.  Built with the system's C++ compiler at first use."""
+"""The host runtime library (``csrc/host/*.cpp``) loaded through ctypes: page pools, the cache
+manager's books and the scheduler's decisions in C++.  Built with the system's C++ compiler at
+first use."""
 from __future__ import annotations
 
 import ctypes
@@ -15,6 +16,7 @@ def library() -> ctypes.CDLL:
         dll = ctypes.CDLL(build_host())
         P, I = ctypes.c_void_p, ctypes.c_int
         IP = ctypes.POINTER(ctypes.c_int)
+        L, LP = ctypes.c_int64, ctypes.POINTER(ctypes.c_int64)
         signatures = {
             "mrun_pool_create": (P, [I]), "mrun_pool_destroy": (None, [P]), "mrun_pool_free_count": (I, [P]),
             "mrun_pool_alloc": (I, [P, I, IP]), "mrun_pool_free": (I, [P, IP, I, IP]),
@@ -29,6 +31,13 @@ def library() -> ctypes.CDLL:
             "mrun_cache_rollback": (I, [P, I]), "mrun_cache_drain": (I, [P, I, IP, IP, I]),
             "mrun_cache_pending_updates": (I, [P, I]), "mrun_cache_check": (ctypes.c_char_p, [P]),
             "mrun_cache_layout_step": (I, [P, I, IP, IP, IP, IP, IP, IP, IP, ctypes.POINTER(IP)]),
+            "mrun_sched_chunk_len": (I, [L, I]), "mrun_sched_looping": (I, [IP, L]),
+            "mrun_sched_loop_check_every": (I, []),
+            "mrun_sched_submit_check": (I, [L, L, L, L, L, LP]),
+            "mrun_sched_can_admit": (I, [I, I, I, I, L, L, I, L, L, L, I, LP, LP]),
+            "mrun_sched_plan": (I, [I, LP, LP, IP, LP, LP, IP, LP, I, IP, IP, IP, IP]),
+            "mrun_sched_end_reason": (I, [I, I, L, L, IP, L]),
+            "mrun_sched_preemption_victim": (I, [I, IP, LP]),
         }
         for name, (restype, argtypes) in signatures.items():
             fn = getattr(dll, name)
@@ -40,3 +49,8 @@ def library() -> ctypes.CDLL:
 def int_array(values) -> ctypes.Array:
     values = list(values)
     return (ctypes.c_int * max(1, len(values)))(*values)
+
+
+def long_array(values) -> ctypes.Array:
+    values = list(values)
+    return (ctypes.c_int64 * max(1, len(values)))(*values)

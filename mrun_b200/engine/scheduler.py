@@ -1,6 +1,9 @@
 """The scheduler: admits requests, cuts prompts into portions under a token budget, lets every
 running request decode, finishes requests and frees what they hold.  Host-side only; it decides,
-the executor computes.
+the executor computes.  The decisions themselves (refusal and clamped limit at submission, the
+admission test, what a step holds, the length of a portion, why a request ends, who gives way when
+pages run out) are computed by the host runtime library (``csrc/host/sched_core.cpp``, C++); this
+class keeps the request objects and the queues and hands their numbers over.
 
 Decisions, with the reference's where it has one
 ------------------------------------------------
@@ -34,28 +37,31 @@ Decisions, with the reference's where it has one
 """
 from __future__ import annotations
 
+import ctypes
 import time
 from collections import deque
 from dataclasses import dataclass, field
 from typing import Deque, Dict, List, Optional, Sequence, Tuple
 
+from ..cache import native
 from ..cache.manager import CacheManager, RequestCache
 from ..sampling.params import GREEDY, SamplingParams, fresh_seed
 
-LOOP_WINDOW, LOOP_MAX_PERIOD, LOOP_CHECK_EVERY = 512, 256, 16
+LOOP_WINDOW, LOOP_MAX_PERIOD = 512, 256
+END_REASONS = (None, "stop", "length", "repetition")
 
 
 def chunk_len(depth: int, budget: int = 2048) -> int:
     """Longest prompt portion at ``depth`` tokens already in the cache."""
-    return max(min(128, budget), min(budget, budget * 16384 // max(depth, 1)))
+    return int(native.library().mrun_sched_chunk_len(int(depth), int(budget)))
 
 
 def looping(output: Sequence[int]) -> bool:
+    """Whether the last 512 tokens repeat with a period of at most 256."""
     if len(output) < LOOP_WINDOW:
         return False
-    window = output[-LOOP_WINDOW:]
-    return any(all(window[i] == window[i - p] for i in range(p, LOOP_WINDOW))
-               for p in range(1, LOOP_MAX_PERIOD + 1))
+    window = native.int_array(output[-LOOP_WINDOW:])
+    return bool(native.library().mrun_sched_looping(window, LOOP_WINDOW))
 
 
 @dataclass
@@ -153,6 +159,8 @@ class Scheduler:
         self._admitted = 0
         self._reserved = 0
         self.preemptions = 0
+        self._core = native.library()
+        self._loop_check_every = int(self._core.mrun_sched_loop_check_every())
 
     # ------------------------------------------------------------------ submission
     def submit(self, request: Request) -> Optional[str]:
@@ -169,15 +177,17 @@ class Scheduler:
             except ValueError as error:
                 reason, request.message = "invalid", str(error)
         if reason is None:
-            room = self.capacity_tokens - len(request.prompt)
-            if room < 1:
+            limit = ctypes.c_int64(0)
+            code = self._core.mrun_sched_submit_check(len(request.prompt), int(request.max_tokens), self.capacity_tokens,
+                                                      len(self.waiting), -1 if self.max_queue is None else self.max_queue,
+                                                      ctypes.byref(limit))
+            request.limit = int(limit.value)
+            if code == 1:
                 reason = "too_long"
                 request.message = (f"prompt is too long: {len(request.prompt)} tokens, the cache holds "
                                    f"{self.capacity_tokens}")
-            else:
-                request.limit = min(request.max_tokens, room)
-        if reason is None and self.max_queue is not None and len(self.waiting) >= self.max_queue:
-            reason, request.message = "queue_full", f"{len(self.waiting)} requests are waiting already"
+            elif code == 2:
+                reason, request.message = "queue_full", f"{len(self.waiting)} requests are waiting already"
         if reason is not None:
             self._finish(request, reason)
             return reason
@@ -202,16 +212,15 @@ class Scheduler:
         return self.cache.blocks_for(len(request.prompt) + request.limit)
 
     def _can_admit(self, request: Request) -> bool:
-        if len(self.running) >= self.max_running or self.cache.free_slots < 1:
-            return False
-        if self.reserve:
-            return self._reserved + self._need_pages(request) <= self.cache.num_pages
-        # on demand: room for its whole sequence and one more page, beside what the running
-        # requests still have to bring in
-        outstanding = sum(self.cache.blocks_for(r.sequence_len) - self.cache.blocks_for(r.fed)
-                          for r in self.running)
-        return self.cache.free_pages() - outstanding >= self.cache.blocks_for(request.sequence_len) + 1 \
-            or not self.running
+        # with reservations: pages for prompt + clamped output beside what is reserved; on demand:
+        # room for its whole sequence and one more page, beside what the running requests still
+        # have to bring in
+        running = self.running
+        return bool(self._core.mrun_sched_can_admit(
+            len(running), self.max_running, self.cache.free_slots, 1 if self.reserve else 0, self._reserved,
+            self.cache.num_pages, self.cache.page_size, self.cache.free_pages(), len(request.prompt) + request.limit,
+            request.sequence_len, len(running), native.long_array(r.sequence_len for r in running),
+            native.long_array(r.fed for r in running)))
 
     def _admit(self) -> None:
         while self.waiting and self._can_admit(self.waiting[0]):
@@ -232,27 +241,22 @@ class Scheduler:
         self._admit()
         if not self.running:
             return None
-        budget = self.max_batch_tokens
+        running = self.running
+        n = len(running)
+        which, tokens = native.int_array([0] * n), native.int_array([0] * n)
+        wants, from_device = native.int_array([0] * n), native.int_array([0] * n)
+        made = self._core.mrun_sched_plan(
+            n, native.long_array(r.sequence_len for r in running), native.long_array(r.fed for r in running),
+            native.int_array(r.inflight for r in running), native.long_array(len(r.output) for r in running),
+            native.long_array(r.limit for r in running), native.int_array(1 if r.retiring else 0 for r in running),
+            native.long_array(r.order for r in running), self.max_batch_tokens, which, tokens, wants, from_device)
         entries: List[PlannedEntry] = []
-        # a request whose unread token will be its last, or that finished while a step was in
-        # flight, takes no part any more
-        active = [r for r in self.running
-                  if not r.retiring and len(r.output) + r.inflight < r.limit]
-        decoders = [r for r in active if r.remaining == 1 and r.fed > 0]
-        for request in decoders[:budget]:
-            if request.inflight:
+        for e in range(made):
+            request = running[which[e]]
+            if from_device[e]:
                 entries.append(PlannedEntry(request, [0], True, from_device=True))
             else:
-                entries.append(PlannedEntry(request, request.next_tokens(1), True))
-        budget -= len(entries)
-        readers = sorted((r for r in active if not (r.remaining == 1 and r.fed > 0) and not r.inflight),
-                         key=lambda r: (r.remaining, r.order))
-        for request in readers:
-            if budget < 1:
-                break
-            n = min(request.remaining, budget, chunk_len(request.fed, self.max_batch_tokens))
-            entries.append(PlannedEntry(request, request.next_tokens(n), n == request.remaining))
-            budget -= n
+                entries.append(PlannedEntry(request, request.next_tokens(tokens[e]), bool(wants[e])))
         return StepPlan(entries) if entries else None
 
     def launched(self, plan: StepPlan) -> None:
@@ -290,13 +294,12 @@ class Scheduler:
             request.token_times.append(now)
             if request.on_token is not None:
                 request.on_token(request, token)
-            reason = None
-            if token in self.eos and not request.ignore_eos:
-                reason = "stop"
-            elif len(request.output) >= request.limit:
-                reason = "length"
-            elif len(request.output) % LOOP_CHECK_EVERY == 0 and looping(request.output):
-                reason = "repetition"
+            count = len(request.output)
+            recent, recent_len = None, 0             # the loop guard looks every few tokens only
+            if count % self._loop_check_every == 0 and count >= LOOP_WINDOW:
+                recent, recent_len = native.int_array(request.output[-LOOP_WINDOW:]), LOOP_WINDOW
+            reason = END_REASONS[self._core.mrun_sched_end_reason(
+                1 if token in self.eos else 0, 1 if request.ignore_eos else 0, count, request.limit, recent, recent_len)]
             if reason is not None:
                 if request.inflight:
                     request.retiring = True          # its row in the step in flight is dropped later
@@ -310,12 +313,14 @@ class Scheduler:
     def preempt_newest(self) -> Optional[Request]:
         """Gives back everything the running request admitted last holds and puts it at the head
         of the queue.  None when at most one request runs (it is never preempted)."""
-        candidates = [r for r in self.running if not r.retiring]
-        if len(candidates) <= 1:
+        running = self.running
+        at = self._core.mrun_sched_preemption_victim(len(running), native.int_array(1 if r.retiring else 0 for r in running),
+                                                     native.long_array(r.order for r in running))
+        if at < 0:
             return None
-        if any(r.inflight for r in self.running):
+        if any(r.inflight for r in running):
             raise RuntimeError("a request cannot be preempted while a step is in flight")
-        victim = max(candidates, key=lambda r: r.order)
+        victim = running[at]
         self._retire(victim)
         victim.state = "waiting"
         victim.fed = 0

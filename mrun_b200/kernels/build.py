@@ -140,7 +140,7 @@ def build_library(name: str, source_names: Iterable[str],
         return target
 
 
-HOST_SOURCES = ("host/cache_core.cpp",)
+HOST_SOURCES = ("host/cache_core.cpp", "host/sched_core.cpp")
 CXX_FLAGS = ["-O2", "-std=c++17", "-shared", "-fPIC", "-fvisibility=hidden"]
 
 
@@ -153,7 +153,8 @@ def find_cxx() -> str:
 
 
 def build_host() -> str:
-    """The host-side runtime library (the cache manager's bookkeeping): plain C++, no CUDA."""
+    """The host-side runtime library (the cache manager's bookkeeping, the scheduler's decisions):
+    plain C++, no CUDA."""
     sources = [os.path.join(CSRC, n) for n in HOST_SOURCES]
     h = hashlib.sha256()
     for path in sources:

@@ -203,3 +203,67 @@ def test_steps_in_flight():
     assert a.finish_reason == "length" and a.output == [9, 9, 9] and not s.unsettled()
     assert s.cache.free_pages() == 64 and s.cache.free_slots == 4
     s.cache.check_invariants()
+
+
+def test_native_plan_follows_the_rule_under_random_states():
+    """The step the host library plans (csrc/host/sched_core.cpp) against the rule restated here:
+    one token for every request past its prompt (while the budget lasts), then portions, fewest
+    tokens left first, ties by admission order, each at most chunk_len(depth) and the budget."""
+    import random
+    from mrun_b200.cache import native
+    core = native.library()
+    rng = random.Random(5)
+    for _ in range(300):
+        n = rng.randint(1, 12)
+        budget_all = rng.choice([1, 3, 16, 64, 2048])
+        prompt = [rng.randint(1, 5000) for _ in range(n)]
+        out = [rng.choice([0, 0, 1, 7]) for _ in range(n)]
+        limit = [o + rng.choice([0, 1, 5]) for o in out]
+        inflight = [rng.choice([0, 0, 1]) if o > 0 or rng.random() < 0.2 else 0 for o in out]
+        retiring = [1 if rng.random() < 0.1 else 0 for _ in range(n)]
+        order = rng.sample(range(100), n)
+        seq = [p + o for p, o in zip(prompt, out)]
+        fed = []
+        for i in range(n):
+            if inflight[i]:
+                fed.append(seq[i])                        # everything read so far is in the cache
+            elif out[i] > 0:
+                fed.append(seq[i] - 1)                    # the last token read is still to be fed
+            else:
+                fed.append(rng.choice([0, rng.randint(0, prompt[i] - 1)]))
+        # the rule
+        want, budget = [], budget_all
+        active = [i for i in range(n) if not retiring[i] and out[i] + inflight[i] < limit[i]]
+        decoding = [i for i in active if seq[i] + inflight[i] - fed[i] == 1 and fed[i] > 0]
+        for i in decoding[:budget]:
+            want.append((i, 1, 1, 1 if inflight[i] else 0))
+        budget -= len(want)
+        readers = sorted((i for i in active if i not in decoding and not inflight[i]),
+                         key=lambda i: (seq[i] - fed[i], order[i]))
+        for i in readers:
+            if budget < 1:
+                break
+            take = min(seq[i] - fed[i], budget, chunk_len(fed[i], budget_all))
+            want.append((i, take, 1 if take == seq[i] - fed[i] else 0, 0))
+            budget -= take
+        which, tokens = native.int_array([0] * n), native.int_array([0] * n)
+        wants, from_device = native.int_array([0] * n), native.int_array([0] * n)
+        made = core.mrun_sched_plan(n, native.long_array(seq), native.long_array(fed), native.int_array(inflight),
+                                    native.long_array(out), native.long_array(limit), native.int_array(retiring),
+                                    native.long_array(order), budget_all, which, tokens, wants, from_device)
+        got = [(which[e], tokens[e], wants[e], from_device[e]) for e in range(made)]
+        assert got == want
+        assert sum(t for _, t, _, _ in got) <= budget_all
+
+
+def test_native_end_reason_and_victim():
+    from mrun_b200.cache import native
+    core = native.library()
+    assert core.mrun_sched_end_reason(1, 0, 3, 10, None, 0) == 1 and core.mrun_sched_end_reason(1, 1, 3, 10, None, 0) == 0
+    assert core.mrun_sched_end_reason(0, 0, 10, 10, None, 0) == 2 and core.mrun_sched_end_reason(1, 1, 10, 10, None, 0) == 2
+    loop = native.int_array([4, 9] * 256)
+    assert core.mrun_sched_end_reason(0, 0, 512, 9999, loop, 512) == 3
+    assert core.mrun_sched_end_reason(0, 0, 513, 9999, loop, 512) == 0          # not a multiple of the interval
+    assert core.mrun_sched_preemption_victim(3, native.int_array([0, 0, 0]), native.long_array([5, 9, 2])) == 1
+    assert core.mrun_sched_preemption_victim(3, native.int_array([0, 1, 0]), native.long_array([5, 9, 2])) == 0
+    assert core.mrun_sched_preemption_victim(2, native.int_array([0, 1]), native.long_array([5, 9])) == -1
