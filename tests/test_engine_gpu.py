@@ -77,7 +77,7 @@ def test_long_decoding_stays_on_the_plain_logits(tiny):
     tokens = random_tokens(cfg["vocab_size"], 330, seed=77)
     want = plain.forward(cfg, weights, tokens).numpy()
     for dtype in ("float32", "bfloat16"):
-        ex = executor_from_folder(folder, dtype=dtype, page_size=settings["page_size"], num_pages=64,
+        ex = executor_from_folder(folder, dtype=dtype, page_size=settings["page_size"], num_pages=max(64, 352 // settings["page_size"]),
                                   max_requests=2)
         request = ex.admit("long")
         first = ex.step([StepEntry(request, tokens[:30], [0, 1, 2, 29])]).cpu().numpy()

@@ -1,7 +1,8 @@
 """The tiny configurations the tests run on.  They differ in every size and option: head counts and
 groups, sizes that are no power of two, number of layers, vocabulary, the norms' eps, rope base,
 tied or untied head, norm weights, page size.  A and B have small heads (the mma.sync attention
-kernels), C has heads of 64 (the TMA and tcgen05 attention kernels)."""
+kernels), C has heads of 64 (the TMA and tcgen05 attention kernels), D sizes that are no
+multiple of 8."""
 from __future__ import annotations
 
 import numpy as np
@@ -23,6 +24,13 @@ TINY = {
                     head_dim=64, intermediate_size=224, vocab_size=300, max_position_embeddings=4096,
                     rms_norm_eps=3e-6, rope_theta=500000.0, tie_word_embeddings=False),
         seed=37, std=0.07, norm_noise=0.05, page_size=16),
+    # sizes that fit no vector width: a width and an intermediate size that are no multiple of 8, one
+    # kv head for eight query heads, heads of 48, an odd vocabulary, pages of four tokens
+    "D": dict(
+        config=dict(num_hidden_layers=2, hidden_size=100, num_attention_heads=8, num_key_value_heads=1,
+                    head_dim=48, intermediate_size=150, vocab_size=301, max_position_embeddings=1024,
+                    rms_norm_eps=2e-5, rope_theta=50000.0, tie_word_embeddings=True),
+        seed=41, std=0.08, norm_noise=0.1, page_size=4),
 }
 
 
