@@ -217,7 +217,7 @@ def build_attention(head_dim: int) -> str:
 
 
 # head sizes of the configurations this repository measures and tests
-COMMON_HEAD_DIMS = (16, 32, 64, 128)
+COMMON_HEAD_DIMS = (16, 32, 48, 64, 80, 96, 128, 256)      # the head sizes the tests and the measured shapes use
 
 
 def build_all() -> list[str]:
