@@ -23,12 +23,15 @@ class TensorSpec:
     """One tensor a part expects in the checkpoint.
 
     ``init`` tells the random-weights mode how to fill it: ``"normal"`` (matrices and tables),
-    ``"norm"`` (scale vectors: ones, or ones plus noise).
+    ``"norm"`` (scale vectors: ones, or ones plus noise).  An ``optional`` tensor is bound when
+    the checkpoint has it and is neither missed nor made by the random-weights mode otherwise
+    (the reference takes a linear layer's ``.bias`` that way, crates/mrun-engine/src/load.rs:281).
     """
 
     name: str
     shape: Tuple[int, ...]
     init: str = "normal"
+    optional: bool = False
 
 
 # --------------------------------------------------------------------------- norms
@@ -126,10 +129,23 @@ class ModelSpec:
     final_norm_prefix: str = "model.norm"
     head_name: str = "lm_head.weight"
     eos_token_ids: Tuple[int, ...] = ()
-    # tensors that may be present in a checkpoint and are dropped unread
+    # optional transform specs (kinds of the ``TRANSFORMS`` registry; a spec that binds tensors
+    # carries their ``prefix``): applied to the 32-bit stream right after the embedding, and to
+    # the float32 logits of the wanted rows
+    embedding_transform: Any = None
+    logits_transform: Any = None
+    # tensors that may be present in a checkpoint and are dropped unread: the vision tower, heads
+    # for multi-token prediction and rotary frequency tables
     # (crates/mrun-engine/src/load.rs:168-173, crates/mrun-engine/src/models/qwen3.rs:107)
-    ignored_suffixes: Tuple[str, ...] = ("rotary_emb.inv_freq",)
+    ignored_suffixes: Tuple[str, ...] = ()
+    ignored_prefixes: Tuple[str, ...] = ("vision_tower", "model.visual")
+    ignored_containing: Tuple[str, ...] = ("mtp.", "rotary_emb.inv_freq")
     extra: dict = field(default_factory=dict, compare=False, hash=False)
+
+    def ignores(self, name: str) -> bool:
+        """Whether a checkpoint tensor of this name is left unread."""
+        return (name.startswith(tuple(self.ignored_prefixes)) or name.endswith(tuple(self.ignored_suffixes))
+                or any(part in name for part in self.ignored_containing))
 
     def run_order(self) -> Tuple[ScheduleEntry, ...]:
         if self.schedule:

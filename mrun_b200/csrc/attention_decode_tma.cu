@@ -167,15 +167,6 @@ __device__ __forceinline__ Segment next_segment(int seg, int u, int u_end, int& 
     return sg;
 }
 
-// -DMRUN_ATTN_TC5_TIMING: the first blocks print where a consumer's cycles went (a tuning aid).
-#ifdef MRUN_ATTN_TC5_TIMING
-#define DT_DECL long long dt_acc[8] = {}; long long dt_last = clock64();
-#define DT_MARK(i) { const long long dt_now = clock64(); dt_acc[i] += dt_now - dt_last; dt_last = dt_now; }
-#else
-#define DT_DECL
-#define DT_MARK(i)
-#endif
-
 // grid: `blocks` blocks, the number the plan was made for.  Scratch as for decode_kernel.
 template <int RING>
 __global__ void __launch_bounds__(TMA_THREADS)
@@ -199,7 +190,6 @@ decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_consta
 
     const int block_id = blockIdx.x, n_blocks_grid = gridDim.x;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    DT_DECL
     const int4 mine = assignment[2 * block_id], shape = assignment[2 * block_id + 1];
     const int u_begin = mine.x, u_end = mine.y;
     const int tiles_per_head = shape.x, per = shape.y, splits = shape.z;
@@ -225,7 +215,6 @@ decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_consta
             reinterpret_cast<uint4*>(ring + s * STAGE_BYTES + TILE_BYTES)[i] = make_uint4(0, 0, 0, 0);
     fence_async_smem();
     __syncthreads();
-    DT_MARK(0)
 
     if (warp == 4) {
         // ------------------------------------------------------------------------------ producer
@@ -338,7 +327,6 @@ decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_consta
                 }
             }
             consumer_sync();                                    // q (and the new key and value) are in place
-            DT_MARK(1)
 
             int row_pos[2], row_lo[2];
 #pragma unroll
@@ -376,7 +364,6 @@ decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_consta
                 __syncwarp();
                 if (lane == 0) mbar_arrive(&empty_bar[s]);
             }
-            DT_MARK(2)
 #pragma unroll
             for (int rr = 0; rr < 2; ++rr) {
                 l[rr] += __shfl_xor_sync(0xffffffffu, l[rr], 1);
@@ -430,7 +417,6 @@ decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_consta
                     if (d == 0) *reinterpret_cast<float2*>(part_ml + (my_slot * 16 + row) * 2) = make_float2(mm, ll);
                 }
             }
-            DT_MARK(3)
             if (!sg.complete) {
                 // the blocks that share this pair are p_first .. p_last; the last to arrive merges their
                 // pieces in block order
@@ -446,7 +432,6 @@ decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_consta
                 consumer_sync();
                 if (threadIdx.x == 0) ticket_shared = atomicAdd(&counters[sg.tok * kv_heads + sg.kvh], 1);
                 consumer_sync();
-                DT_MARK(4)
                 if (ticket_shared == p_last - p_first) {
                     __threadfence();
                     // A thread takes four values of a row.  The pieces are read four at a time, all
@@ -501,12 +486,6 @@ decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_consta
                 }
             }
             consumer_sync();            // the merge area, q and ticket_shared are reused by the next segment
-            DT_MARK(5)
-#ifdef MRUN_ATTN_TC5_TIMING
-            if (block_id < 4 && threadIdx.x == 0)
-                printf("decode block %d: start %lld, q ready %lld, tiles %lld (%d), warp merge and piece out %lld, ticket %lld, "
-                       "final merge %lld\n", block_id, dt_acc[0], dt_acc[1], dt_acc[2], sg.len, dt_acc[3], dt_acc[4], dt_acc[5]);
-#endif
             u += sg.len;
         }
     }

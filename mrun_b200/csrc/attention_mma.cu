@@ -267,11 +267,7 @@ prefill_kernel(const bf16* __restrict__ q, long q_stride, bf16* __restrict__ out
 // the pair's counter merges the pair's pieces in block order and sets the counter back to zero,
 // so no second kernel runs and the result does not depend on which block came last.
 // ------------------------------------------------------------------------------------------
-#ifndef MRUN_DECODE_STAGES
-#define MRUN_DECODE_STAGES 2   // measured: three resident blocks with two tiles each beat deeper pipelines
-#endif
-constexpr int STAGES = MRUN_DECODE_STAGES;
-static_assert(STAGES >= 2 && STAGES <= 4, "2 to 4 key/value tiles in flight");
+constexpr int STAGES = 2;      // key/value tiles in flight: three resident blocks with two tiles each beat deeper pipelines
 
 // Sum and maximum over the block's 1024 threads; every thread gets the result.
 __device__ __forceinline__ int plan_reduce(int v, bool take_max, int* scratch) {
@@ -442,14 +438,10 @@ decode_kernel(const bf16* __restrict__ q, long q_stride, bf16* __restrict__ out,
     const int block_id = blockIdx.x, n_blocks_grid = gridDim.x;
     const int group = heads / kv_heads;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    // Positions, slots, block tables and the plan are written at the start of a step, not by the
-    // kernel before this one, so they are read before waiting for it.
     const int4 mine = assignment[2 * block_id], shape = assignment[2 * block_id + 1];
     int u = mine.x;
     const int u_end = mine.y;
     const int tiles_per_head = shape.x, per = shape.y, splits = shape.z;
-    mrun::pdl_wait();
-    mrun::pdl_launch_dependents();
     const int* prefix = tile_prefix;
     int kvh = mine.z, tok = mine.w;                             // the pair of the block's first tile
 
@@ -806,7 +798,7 @@ MRUN_API int mrun_attn_decode(const void* q, long q_stride, void* out, void* k_c
         in.k_cache = (bf16*)k_cache;
         in.v_cache = (bf16*)v_cache;
     }
-    MRUN_CHECK_CUDA(mrun::launch_pdl(MRUN_PDL_ATTENTION, decode_kernel, dim3(blocks), dim3(THREADS), DECODE_SMEM, stream,
+    MRUN_CHECK_CUDA(mrun::launch_kernel(decode_kernel, dim3(blocks), dim3(THREADS), DECODE_SMEM, stream,
                                      (const bf16*)q, q_stride, (bf16*)out, (const bf16*)k_cache, (const bf16*)v_cache,
                                      block_tables, max_blocks, token_slot, positions, tile_prefix,
                                      (const int4*)assignment, tokens, part_o, part_ml, counters, heads, kv_heads,

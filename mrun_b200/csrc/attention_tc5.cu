@@ -80,14 +80,6 @@ constexpr long long WAIT_CYCLES = 3000000000LL;         // about 1.5 s at 2 GHz
 
 enum : int { STATUS_OK = 0, STATUS_LOADER = 1, STATUS_MMA = 2, STATUS_SOFTMAX = 3 };
 
-// -DMRUN_ATTN_TC5_TIMING: the first block prints where each role's cycles went (a tuning aid).
-#ifdef MRUN_ATTN_TC5_TIMING
-#define TIMING_DECL(n) long long tacc[n] = {}; long long tlast = clock64();
-#define TIMING_MARK(i) { const long long tnow = clock64(); tacc[i] += tnow - tlast; tlast = tnow; }
-#else
-#define TIMING_DECL(n)
-#define TIMING_MARK(i)
-#endif
 
 __device__ __forceinline__ void cp_async_16(void* dst, const void* src, bool valid) {
     const int bytes = valid ? 16 : 0;        // 0: the destination is zero-filled, the source not read
@@ -200,14 +192,11 @@ prefill_tc5_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_const
         const int lo_last = (window > 0 && pos_last - window + 1 > 0) ? pos_last - window + 1 : 0;
         float m_used = -INFINITY, l = 0.f;                           // l: this half's share of the row's sum
         bool alive = true;
-        TIMING_DECL(6)
         // A warp that gave up on a wait still walks through the remaining tiles, doing nothing but
         // meeting its partner at every barrier, so that no warp is left waiting at one.
         for (int j = 0; j < n_tiles; ++j) {
             const int buf = j & 1;
-            TIMING_MARK(5)
             if (alive && !__all_sync(0xffffffffu, mbar_wait(&bars.s_full[buf], (j >> 1) & 1, WAIT_CYCLES, &aborted))) alive = false;
-            TIMING_MARK(0)
             const int key_base = (first_block + j) * KEYS + half * 64;        // of this thread's first score
             // every row of the block sees every key of the tile: no comparisons
             const bool need_mask = (first_block + j) * KEYS + KEYS - 1 > pos_first || (first_block + j) * KEYS < lo_last ||
@@ -264,7 +253,6 @@ prefill_tc5_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_const
             if (mx > m_used + RESCALE_STEP || (m_used == -INFINITY && mx > -INFINITY)) m_new = mx;
             const bool moved = m_new != m_used && m_used != -INFINITY;       // O holds something to rescale
             const bool warp_moved = __any_sync(0xffffffffu, moved);
-            TIMING_MARK(1)
             if (warp_moved) {
                 // O belongs to the second product of the tile before until that has finished
                 if (j > 0 && !__all_sync(0xffffffffu, mbar_wait(&bars.pv_done, (j - 1) & 1, WAIT_CYCLES, &aborted))) {
@@ -284,7 +272,6 @@ prefill_tc5_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_const
                 l *= corr;
             }
             m_used = m_new;
-            TIMING_MARK(3)
             // p = 2^(s * scale - m): one fused multiply-add and one special-function call a score.
             // Masked scores are -inf and give 0; a row that has seen nothing yet keeps m_used = -inf.
             const float m_sub = m_used == -INFINITY ? 0.f : -m_used;
@@ -308,13 +295,7 @@ prefill_tc5_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_const
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(&bars.p_full[buf]);
-            TIMING_MARK(4)
         }
-#ifdef MRUN_ATTN_TC5_TIMING
-        if (blockIdx.x == 0 && blockIdx.y == 0 && threadIdx.x == 0)
-            printf("softmax  tiles %d: wait S %lld, max pass %lld, rescale %lld, P pass %lld, other %lld\n",
-                   n_tiles, tacc[0], tacc[1], tacc[3], tacc[4], tacc[5]);
-#endif
         // a warp leaves the loop as a whole, so every lane takes part in what follows
         if (alive && !__all_sync(0xffffffffu, mbar_wait(&bars.pv_done, (n_tiles - 1) & 1, WAIT_CYCLES, &aborted))) alive = false;
         if (!alive) {
@@ -363,15 +344,11 @@ prefill_tc5_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_const
             for (int kk = 0; kk < KEYS / 16; ++kk)                            // sixteen rows (two groups) further per step
                 v_desc[kk] = smem_descriptor(v_stages + kk * 2048, SPAN_BYTES, 1024);
             constexpr unsigned long long STAGE_STEP = KV_BYTES >> 4;
-            TIMING_DECL(9)
             bool alive = mbar_wait(&bars.q_full, 0, WAIT_CYCLES, &aborted);
             auto issue_qk = [&](int j) -> bool {
                 const int s = j & 1;
-                TIMING_MARK(5)
                 if (!mbar_wait(&bars.k_full[s], (j >> 1) & 1, WAIT_CYCLES, &aborted)) return false;
-                TIMING_MARK(0)
                 if (j >= 2 && !mbar_wait(&bars.s_empty[s], ((j >> 1) - 1) & 1, WAIT_CYCLES, &aborted)) return false;
-                TIMING_MARK(1)
                 tc_fence_after();
                 const unsigned long long step = s * STAGE_STEP;
 #pragma unroll
@@ -379,7 +356,6 @@ prefill_tc5_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_const
                     umma_bf16(tmem_base + s * KEYS, q_desc[kk], k_desc[kk] + step, idesc_qk, kk > 0 ? 1u : 0u);
                 umma_commit(&bars.s_full[s]);
                 umma_commit(&bars.k_empty[s]);
-                TIMING_MARK(4)
                 return true;
             };
             // the first products run two tiles ahead of the softmax, the second follow it
@@ -387,30 +363,18 @@ prefill_tc5_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_const
             if (alive && n_tiles > 1) alive = issue_qk(1);
             for (int j = 0; alive && j < n_tiles; ++j) {
                 const int s = j & 1;
-                TIMING_MARK(5)
                 if (!mbar_wait(&bars.v_full[s], (j >> 1) & 1, WAIT_CYCLES, &aborted)) { alive = false; break; }
-                TIMING_MARK(2)
                 if (!mbar_wait(&bars.p_full[s], (j >> 1) & 1, WAIT_CYCLES, &aborted)) { alive = false; break; }
-                TIMING_MARK(3)
                 tc_fence_after();
-                TIMING_MARK(6)
                 const unsigned long long step = s * STAGE_STEP;
 #pragma unroll
                 for (int kk = 0; kk < KEYS / 16; ++kk)                        // P: eight columns (16 keys) further per step
                     umma_bf16_a_tmem(tmem_base + O_COL, tmem_base + P_COL + s * 64 + kk * 8, v_desc[kk] + step, idesc_pv,
                                      (j > 0 || kk > 0) ? 1u : 0u);
-                TIMING_MARK(7)
                 umma_commit(&bars.v_empty[s]);
                 umma_commit(&bars.pv_done);
-                TIMING_MARK(8)
                 if (j + 2 < n_tiles && !issue_qk(j + 2)) { alive = false; break; }
             }
-#ifdef MRUN_ATTN_TC5_TIMING
-            if (blockIdx.x == 0 && blockIdx.y == 0)
-                printf("products tiles %d: wait K %lld, wait S free %lld, wait V %lld, wait P %lld, issue QK %lld, other %lld, "
-                       "fence %lld, issue PV %lld, commits %lld\n",
-                       n_tiles, tacc[0], tacc[1], tacc[2], tacc[3], tacc[4], tacc[5], tacc[6], tacc[7], tacc[8]);
-#endif
             if (!alive) {
                 if (!*(volatile int*)&aborted) atomicExch(status, STATUS_MMA);
                 atomicExch(&aborted, 1);
@@ -428,13 +392,10 @@ prefill_tc5_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_const
         const int box_rows = page_size < KEYS ? page_size : KEYS;
         const int boxes = KEYS / box_rows;
         bool alive = true;
-        TIMING_DECL(6)
         for (int j = 0; j < n_tiles; ++j) {
             const int s = j & 1;
-            TIMING_MARK(5)
             const bool free_now = j < 2 || mbar_wait(&empty[s], ((j >> 1) - 1) & 1, WAIT_CYCLES, &aborted);
             if (!__all_sync(0xffffffffu, free_now)) { alive = false; break; }
-            TIMING_MARK(0)
             const int key0 = (first_block + j) * KEYS;
             unsigned char* stage = stages + s * KV_BYTES;
             // a lane's boxes: lane, lane + 32, ...  It announces their bytes, then copies them.
@@ -456,12 +417,7 @@ prefill_tc5_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_const
                     tma_load_4d(stage + h * SPAN_BYTES + b * box_rows * 128, map, h * 64,
                                 first_key & (page_size - 1), kvh, page, &full[s]);
             }
-            TIMING_MARK(1)
         }
-#ifdef MRUN_ATTN_TC5_TIMING
-        if (blockIdx.x == 0 && blockIdx.y == 0 && lane == 0)
-            printf("loader %c tiles %d: wait free %lld, issue %lld\n", keys_role ? 'K' : 'V', n_tiles, tacc[0], tacc[1]);
-#endif
         if (!alive) {
             if (!*(volatile int*)&aborted) atomicExch(status, STATUS_LOADER);
             atomicExch(&aborted, 1);

@@ -3,7 +3,6 @@
 
 #include <stdarg.h>
 #include <stdio.h>
-#include <stdlib.h>
 
 static thread_local char g_error[512] = "";
 
@@ -13,18 +12,6 @@ int mrun_set_error(const char* fmt, ...) {
     vsnprintf(g_error, sizeof(g_error), fmt, args);
     va_end(args);
     return 1;
-}
-
-#ifndef MRUN_PDL_DEFAULT
-#define MRUN_PDL_DEFAULT 0
-#endif
-
-bool mrun_pdl_enabled(int kernel_class) {
-    static const int mask = [] {
-        const char* value = getenv("MRUN_PDL");
-        return value ? atoi(value) : MRUN_PDL_DEFAULT;
-    }();
-    return (mask & kernel_class) != 0;
 }
 
 // The message of the last failed call on this thread.

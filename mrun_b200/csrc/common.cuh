@@ -13,6 +13,10 @@
 
 // dtype codes of the C ABI
 enum : int { MRUN_F32 = 0, MRUN_BF16 = 1 };
+// gate functions of a gated feed-forward (0 = the product has no gated epilogue)
+enum : int { MRUN_GATE_NONE = 0, MRUN_GATE_SILU = 1, MRUN_GATE_GELU_TANH = 2 };
+#define MRUN_REQUIRE_GATE(act, name) \
+    MRUN_REQUIRE((act) == MRUN_GATE_SILU || (act) == MRUN_GATE_GELU_TANH, "%s: unknown gate function code %d", name, act)
 
 // Stores a printf-style message for the calling thread and returns a non-zero code.
 int mrun_set_error(const char* fmt, ...);
@@ -36,39 +40,18 @@ int mrun_set_error(const char* fmt, ...);
             return mrun_set_error("%s: %s", name, cudaGetErrorString(err__));           \
     } while (0)
 
-// Which kernel classes are launched so that their blocks may start while the kernel before them
-// in the stream is still running: a bit mask from the environment variable MRUN_PDL
-// (1 = norm/rotary/activation kernels, 2 = the decode GEMM, 4 = the decode attention).
-enum : int { MRUN_PDL_ELEMENTWISE = 1, MRUN_PDL_GEMM = 2, MRUN_PDL_ATTENTION = 4 };
-bool mrun_pdl_enabled(int kernel_class);
-
 namespace mrun {
 
-// Programmatic dependent launch.  A kernel launched with launch_pdl() may begin before the
-// previous kernel in its stream has finished; it must call pdl_wait() before it reads anything
-// that kernel wrote and before it writes anything at all.  What it does before the wait (index
-// arithmetic, loads of weights and of other data that no kernel of the step writes) overlaps the
-// previous kernel's tail.  pdl_launch_dependents() lets the *next* kernel's blocks be scheduled
-// once every block of this one has reached it.  It is called after pdl_wait(), never before: a
-// kernel that released its successor before waiting itself would let a whole chain of kernels
-// pile up on the SMs, each holding block slots while it waits for the one before it.  Both are
-// no-ops in a kernel launched normally.
-__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
-__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;"); }
-
+// Launches a kernel whose arguments are given with the caller's types (they are converted to the
+// kernel's parameter types) and returns the launch's error code.
 template <typename... KArgs, typename... Args>
-inline cudaError_t launch_pdl(int kernel_class, void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem,
-                              cudaStream_t stream, Args... args) {
+inline cudaError_t launch_kernel(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                          Args... args) {
     cudaLaunchConfig_t config = {};
     config.gridDim = grid;
     config.blockDim = block;
     config.dynamicSmemBytes = smem;
     config.stream = stream;
-    cudaLaunchAttribute attribute[1];
-    attribute[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-    attribute[0].val.programmaticStreamSerializationAllowed = 1;
-    config.attrs = attribute;
-    config.numAttrs = mrun_pdl_enabled(kernel_class) ? 1 : 0;
     return cudaLaunchKernelEx(&config, kernel, KArgs(args)...);
 }
 
@@ -125,12 +108,21 @@ __device__ __forceinline__ float block_max(float v, float* scratch) {
     return scratch[32];
 }
 
-// SiLU(gate) * up.  The 32-bit path divides and takes the exponential exactly; the bfloat16
-// kernels (the stand-alone SwiGLU and the GEMM epilogues alike, so that a decode step and a prompt
-// step give the same number) use the special-function unit for both: a relative error near
-// 2^-21, far inside bfloat16's rounding, and a sixth of the instructions.
+// act(gate) * up, the gate's function named by a code of the C ABI.  The 32-bit path divides and
+// takes the exponential exactly; the bfloat16 kernels (the stand-alone kernel and the GEMM
+// epilogues alike, so that a decode step and a prompt step give the same number) use the
+// special-function unit: a relative error near 2^-21 for SiLU, far inside bfloat16's rounding,
+// and a sixth of the instructions.  Another gate function is one more case here and one more
+// name in the Python table; no kernel changes.
 template <bool EXACT>
-__device__ __forceinline__ float silu_mul(float gate, float up) {
+__device__ __forceinline__ float gated_mul(int act, float gate, float up) {
+    if (act == MRUN_GATE_GELU_TANH) {
+        const float inner = 0.7978845608028654f * (gate + 0.044715f * gate * gate * gate);
+        float th;
+        if constexpr (EXACT) th = tanhf(inner);
+        else asm("tanh.approx.f32 %0, %1;" : "=f"(th) : "f"(inner));
+        return 0.5f * gate * (1.f + th) * up;
+    }
     if constexpr (EXACT) return gate / (1.f + expf(-gate)) * up;
     else return __fdividef(gate, 1.f + __expf(-gate)) * up;
 }

@@ -114,8 +114,6 @@ add_rmsnorm_vec_kernel(float* __restrict__ resid, const TA* __restrict__ delta,
                        const float* __restrict__ weight, float eps, TA* __restrict__ out,
                        const int* __restrict__ rows, int hidden) {
     __shared__ float scratch[33];
-    pdl_wait();
-    pdl_launch_dependents();
     const int r = blockIdx.x;
     const size_t src = (size_t)(rows ? rows[r] : r) * hidden;
     const int chunks = hidden >> 3;
@@ -157,7 +155,7 @@ static int launch_add_rmsnorm(float* resid, const void* delta, const float* weig
                               const int* rows, int n_rows, int hidden, cudaStream_t stream) {
     const bool aligned = (((uintptr_t)resid | (uintptr_t)delta | (uintptr_t)weight | (uintptr_t)out) & 15) == 0;
     if (hidden % 8 == 0 && hidden <= 8192 && aligned) {
-        MRUN_CHECK_CUDA(launch_pdl(MRUN_PDL_ELEMENTWISE, add_rmsnorm_vec_kernel<TA>, dim3(n_rows), dim3(256), 0, stream, resid,
+        MRUN_CHECK_CUDA(launch_kernel(add_rmsnorm_vec_kernel<TA>, dim3(n_rows), dim3(256), 0, stream, resid,
                                    (const TA*)delta, weight, eps, (TA*)out, rows, hidden), "add_rmsnorm");
         return 0;
     }
@@ -239,8 +237,6 @@ __global__ void qk_norm_rope_cache_kernel(TA* __restrict__ qkv, const float* __r
                                           TA* __restrict__ v_cache, int tokens, int heads, int kv_heads,
                                           int head_dim, int page_size) {
     extern __shared__ float vec_buf[];
-    pdl_wait();
-    pdl_launch_dependents();
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int per_token = heads + 2 * kv_heads;
     const long item = (long)blockIdx.x * (blockDim.x >> 5) + warp;
@@ -314,8 +310,6 @@ qk_norm_rope_cache_vec_kernel(__nv_bfloat16* __restrict__ qkv, const float* __re
                               __nv_bfloat16* __restrict__ v_cache, int tokens, int heads, int kv_heads,
                               int page_size) {
     constexpr int HEAD_DIM = LANES * 8, HALF = HEAD_DIM / 2;
-    pdl_wait();
-    pdl_launch_dependents();
     const int per_token = heads + 2 * kv_heads;
     const int groups_per_token = (per_token + QK_HEADS_PER_GROUP - 1) / QK_HEADS_PER_GROUP;
     const long group = ((long)blockIdx.x * blockDim.x + threadIdx.x) / LANES;
@@ -408,7 +402,7 @@ cudaError_t launch_qk_vec(__nv_bfloat16* qkv, const float* q_weight, const float
     const int per_token = heads + 2 * kv_heads;
     const long groups = (long)tokens * ((per_token + QK_HEADS_PER_GROUP - 1) / QK_HEADS_PER_GROUP);
     const long threads = groups * LANES;
-    return launch_pdl(MRUN_PDL_ELEMENTWISE, qk_norm_rope_cache_vec_kernel<LANES>, dim3((unsigned)((threads + 255) / 256)),
+    return launch_kernel(qk_norm_rope_cache_vec_kernel<LANES>, dim3((unsigned)((threads + 255) / 256)),
                       dim3(256), 0, stream, qkv, q_weight, k_weight, eps, rot, slots, k_cache, v_cache, tokens, heads,
                       kv_heads, page_size);
 }
@@ -446,12 +440,12 @@ MRUN_API int mrun_qk_norm_rope_cache(void* qkv, int act_dtype, const float* q_we
     const unsigned blocks = (unsigned)((items + warps - 1) / warps);
     const size_t smem = (size_t)warps * head_dim * sizeof(float);
     if (act_dtype == MRUN_F32)
-        MRUN_CHECK_CUDA(launch_pdl(MRUN_PDL_ELEMENTWISE, qk_norm_rope_cache_kernel<float>, dim3(blocks), dim3(warps * 32), smem, stream,
+        MRUN_CHECK_CUDA(launch_kernel(qk_norm_rope_cache_kernel<float>, dim3(blocks), dim3(warps * 32), smem, stream,
                                    (float*)qkv, q_weight, k_weight, eps, (const float2*)rot, rotary_dim, slots,
                                    (float*)k_cache, (float*)v_cache, tokens, heads, kv_heads, head_dim, page_size),
                         "qk_norm_rope_cache");
     else if (act_dtype == MRUN_BF16)
-        MRUN_CHECK_CUDA(launch_pdl(MRUN_PDL_ELEMENTWISE, qk_norm_rope_cache_kernel<__nv_bfloat16>, dim3(blocks), dim3(warps * 32), smem,
+        MRUN_CHECK_CUDA(launch_kernel(qk_norm_rope_cache_kernel<__nv_bfloat16>, dim3(blocks), dim3(warps * 32), smem,
                                    stream, (__nv_bfloat16*)qkv, q_weight, k_weight, eps, (const float2*)rot,
                                    rotary_dim, slots, (__nv_bfloat16*)k_cache, (__nv_bfloat16*)v_cache, tokens, heads,
                                    kv_heads, head_dim, page_size),
@@ -463,8 +457,8 @@ MRUN_API int mrun_qk_norm_rope_cache(void* qkv, int act_dtype, const float* q_we
 }
 
 // ------------------------------------------------------------------------------------------
-// Gated activation: out[t, i] = act(gate_i) * up_i, act = SiLU
-// (z * sigmoid(z), crates/mrun-engine/src/models/activations.rs:46-59), in 32-bit.
+// Gated activation: out[t, i] = act(gate_i) * up_i in 32-bit; act by code: SiLU
+// (z * sigmoid(z), crates/mrun-engine/src/models/activations.rs:46-59) or tanh-GELU.
 // Layout of gate_up[t, :]: block == 0: all gates, then all ups (gate_i at i, up_i at inter + i).
 // block == 8: runs of eight gates followed by the eight ups of the same outputs
 // (gate_i at 16 (i / 8) + i % 8, up_i eight further), the row order the decode GEMM's fused
@@ -472,7 +466,7 @@ MRUN_API int mrun_qk_norm_rope_cache(void* qkv, int act_dtype, const float* q_we
 // ------------------------------------------------------------------------------------------
 template <typename TA>
 __global__ void swiglu_kernel(const TA* __restrict__ gate_up, TA* __restrict__ out, long total, int inter,
-                              int block) {
+                              int block, int act) {
     const long i = (long)blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= total) return;
     const long t = i / inter;
@@ -481,7 +475,7 @@ __global__ void swiglu_kernel(const TA* __restrict__ gate_up, TA* __restrict__ o
     const long ui = block ? gi + 8 : gi + inter;
     const float g = to_float(gate_up[gi]);
     const float u = to_float(gate_up[ui]);
-    out[i] = from_float<TA>(mrun::silu_mul<sizeof(TA) == 4>(g, u));
+    out[i] = from_float<TA>(mrun::gated_mul<sizeof(TA) == 4>(act, g, u));
 }
 
 // Eight outputs per thread with 16-byte loads and stores, for widths that are a multiple of 8.
@@ -489,7 +483,7 @@ __global__ void swiglu_kernel(const TA* __restrict__ gate_up, TA* __restrict__ o
 // (2,048 x 12,288 outputs, bfloat16: 24.8 us, 6.1 TB/s with one; 27 to 29 us with two; 37 us with four).
 template <typename TA>
 __global__ void __launch_bounds__(256)
-swiglu_vec_kernel(const TA* __restrict__ gate_up, TA* __restrict__ out, long total8, int inter, int block) {
+swiglu_vec_kernel(const TA* __restrict__ gate_up, TA* __restrict__ out, long total8, int inter, int block, int act) {
     const long i = (long)blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= total8) return;
     const int per_row = inter >> 3;
@@ -501,12 +495,13 @@ swiglu_vec_kernel(const TA* __restrict__ gate_up, TA* __restrict__ out, long tot
     Vec8<TA>::load(g_ptr, g);
     Vec8<TA>::load(u_ptr, u);
 #pragma unroll
-    for (int e = 0; e < 8; ++e) y[e] = mrun::silu_mul<sizeof(TA) == 4>(g[e], u[e]);
+    for (int e = 0; e < 8; ++e) y[e] = mrun::gated_mul<sizeof(TA) == 4>(act, g[e], u[e]);
     Vec8<TA>::store(out + t * inter + c, y);
 }
 
 MRUN_API int mrun_swiglu(const void* gate_up, void* out, int act_dtype, int tokens, int inter, int block,
-                         cudaStream_t stream) {
+                         int act, cudaStream_t stream) {
+    MRUN_REQUIRE_GATE(act, "swiglu");
     MRUN_REQUIRE(tokens >= 0 && inter > 0, "swiglu: bad sizes tokens=%d inter=%d", tokens, inter);
     MRUN_REQUIRE(block == 0 || (block == 8 && inter % 8 == 0),
                  "swiglu: the interleaved layout has runs of 8 and needs inter=%d to be a multiple of 8", inter);
@@ -518,22 +513,48 @@ MRUN_API int mrun_swiglu(const void* gate_up, void* out, int act_dtype, int toke
         const unsigned vblocks = (unsigned)((total8 + 255) / 256);
         if (act_dtype == MRUN_F32)
             swiglu_vec_kernel<float><<<vblocks, 256, 0, stream>>>((const float*)gate_up, (float*)out, total8, inter,
-                                                                block);
+                                                                block, act);
         else
             swiglu_vec_kernel<__nv_bfloat16><<<vblocks, 256, 0, stream>>>(
-                (const __nv_bfloat16*)gate_up, (__nv_bfloat16*)out, total8, inter, block);
+                (const __nv_bfloat16*)gate_up, (__nv_bfloat16*)out, total8, inter, block, act);
         MRUN_CHECK_LAUNCH("swiglu");
         return 0;
     }
     const unsigned blocks = (unsigned)((total + 255) / 256);
     if (act_dtype == MRUN_F32)
-        swiglu_kernel<float><<<blocks, 256, 0, stream>>>((const float*)gate_up, (float*)out, total, inter, block);
+        swiglu_kernel<float><<<blocks, 256, 0, stream>>>((const float*)gate_up, (float*)out, total, inter, block, act);
     else if (act_dtype == MRUN_BF16)
         swiglu_kernel<__nv_bfloat16><<<blocks, 256, 0, stream>>>((const __nv_bfloat16*)gate_up,
-                                                                 (__nv_bfloat16*)out, total, inter, block);
+                                                                 (__nv_bfloat16*)out, total, inter, block, act);
     else
         return mrun_set_error("swiglu: unknown dtype code %d", act_dtype);
     MRUN_CHECK_LAUNCH("swiglu");
+    return 0;
+}
+
+// ------------------------------------------------------------------------------------------
+// Bias of a linear layer: y[t, n] += bias[n], the sum in 32-bit and rounded once to y's type
+// (crates/mrun-engine/src/load.rs:302-305 adds an optional bias after the product).
+// ------------------------------------------------------------------------------------------
+template <typename TA>
+__global__ void add_bias_kernel(TA* __restrict__ y, const float* __restrict__ bias, long total, int n) {
+    const long i = (long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= total) return;
+    y[i] = from_float<TA>(to_float(y[i]) + bias[(int)(i % n)]);
+}
+
+MRUN_API int mrun_add_bias(void* y, int act_dtype, const float* bias, int tokens, int n, cudaStream_t stream) {
+    MRUN_REQUIRE(tokens >= 0 && n > 0, "add_bias: bad sizes tokens=%d n=%d", tokens, n);
+    if (tokens == 0) return 0;
+    const long total = (long)tokens * n;
+    const unsigned blocks = (unsigned)((total + 255) / 256);
+    if (act_dtype == MRUN_F32)
+        add_bias_kernel<float><<<blocks, 256, 0, stream>>>((float*)y, bias, total, n);
+    else if (act_dtype == MRUN_BF16)
+        add_bias_kernel<__nv_bfloat16><<<blocks, 256, 0, stream>>>((__nv_bfloat16*)y, bias, total, n);
+    else
+        return mrun_set_error("add_bias: unknown dtype code %d", act_dtype);
+    MRUN_CHECK_LAUNCH("add_bias");
     return 0;
 }
 

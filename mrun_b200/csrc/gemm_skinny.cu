@@ -11,8 +11,16 @@
 //    Inside a 32-wide chunk thread t of a quad owns k = 8t .. 8t+7 of *both* operands, which is a
 //    permutation of the instruction's k order applied to both sides alike, so the sum is the same;
 //  * the eight partial sums are added in shared memory in warp order (fixed, so a row's result
-//    does not depend on the batch), and the epilogue writes y, or SiLU(gate) * up when W holds
+//    does not depend on the batch), and the epilogue writes y, or act(gate) * up when W holds
 //    gate and up rows interleaved in runs of eight (rows 16j..16j+7 gate, 16j+8..16j+15 up).
+//
+// A decode step is a chain of such products with a residual sum and an RMSNorm between them, and
+// at a handful of rows a stand-alone norm kernel is all launch latency.  So the norm is split
+// over the two products around it.  The product *before* it (epilogue RESIDUAL) adds its result
+// to the 32-bit residual stream in place, writes xw = bf16(stream * norm weight) and, per block,
+// the sum of squares of its 16 stream columns per row.  The product *after* it reads xw as its x
+// and multiplies its sums by rsqrt(sum of all blocks' squares / width + eps), which it adds up
+// itself in a fixed order: RMSNorm(x) · Wᵀ = rsqrt(mean(x²) + eps) · ((x ⊙ w_norm) · Wᵀ).
 //
 // Reference call sites: crates/mrun-engine/src/load.rs:294-306 (x · Wᵀ),
 // crates/mrun-engine/src/models/common.rs:336-339 (the gated feed-forward).
@@ -21,22 +29,27 @@
 namespace {
 
 using bf16 = __nv_bfloat16;
-using mrun::pdl_launch_dependents;
-using mrun::pdl_wait;
-#ifndef MRUN_SKINNY_WARPS
-#define MRUN_SKINNY_WARPS 8
-#endif
-#ifndef MRUN_SKINNY_UNROLL
-#define MRUN_SKINNY_UNROLL 4        // chunks per batch with one row tile and one token tile per block
-#endif
-#ifndef MRUN_SKINNY_UNROLL_WIDE
-#define MRUN_SKINNY_UNROLL_WIDE 2   // ... with two row tiles or two token tiles (more registers per chunk)
-#endif
-#ifndef MRUN_SKINNY_WIDE_N
-#define MRUN_SKINNY_WIDE_N (32 * 148 * 4)
-#endif
-constexpr int WARPS = MRUN_SKINNY_WARPS;
+constexpr int WARPS = 8;
 constexpr int THREADS = WARPS * 32;
+constexpr int UNROLL_DEEP = 4;      // chunks per batch with one row tile and one token tile per block
+constexpr int UNROLL_SHALLOW = 2;   // ... with two row tiles or two token tiles (more registers per chunk)
+enum : int { EPI_PLAIN = 0, EPI_GATED = 1, EPI_RESIDUAL = 2 };
+constexpr int MAX_IN_BLOCKS = 512;  // sums of squares a product takes in: a stream of up to 8,192 columns
+
+// What a launch does beside the product itself.
+struct Fusion {
+    int act;                     // EPI_GATED: the gate's function (MRUN_GATE_*)
+    // x is the xw of a product before: the row's scale is rsqrt(sum of in_partials / width + eps)
+    const float* in_partials;    // [in_blocks][16] sums of squares, or null: x is taken as it is
+    int in_blocks;
+    float in_eps, in_inv_width;
+    // EPI_RESIDUAL: resid[M, ldr] += y; xw_out[M, N] = bf16(resid * norm_w); out_partials[block][16]
+    float* resid;
+    long ldr;
+    const float* norm_w;
+    bf16* xw_out;
+    float* out_partials;
+};
 
 __device__ __forceinline__ uint4 load_stream(const bf16* p) {
     uint4 v;
@@ -56,11 +69,18 @@ template <> __device__ __forceinline__ void store_out<bf16>(bf16* p, float v) { 
 template <> __device__ __forceinline__ void store_out<float>(float* p, float v) { *p = v; }
 
 // NT: token tiles of 8 (M <= 8 NT).  MT: 16-row tiles of W per block.  UNROLL: chunks per batch.
-template <int NT, int MT, int UNROLL, typename TOut, bool SWIGLU>
-__global__ void __launch_bounds__(THREADS)
+// Blocks a multiprocessor is to hold: three of the kinds with one register set of weights a chunk
+// (85 registers a thread), two of the others (128).
+constexpr int resident_blocks(int nt, int mt, int unroll) { return nt * mt * unroll <= 2 ? 3 : 2; }
+
+template <int NT, int MT, int UNROLL, typename TOut, int EPI>
+__global__ void __launch_bounds__(THREADS, resident_blocks(NT, MT, UNROLL))
 skinny_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w, TOut* __restrict__ y, int M, int N, int K,
-              long ldx, long ldy) {
+              long ldx, long ldy, const Fusion f) {
+    static_assert(EPI != EPI_RESIDUAL || MT == 1, "the residual epilogue sums 16 columns per block");
     __shared__ float red[WARPS][MT * 16][NT * 8 + 1];
+    __shared__ float row_scale[NT * 8];
+    __shared__ __align__(16) float in_sums[MAX_IN_BLOCKS * 16];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int g = lane >> 2, t = lane & 3;
     const int n0 = blockIdx.x * (MT * 16);
@@ -132,16 +152,21 @@ skinny_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w, TOut* __re
             }
         }
     };
-    // The weights do not depend on the kernel before this one: their first two batches are
-    // requested before waiting for it, the rows of x after.
     constexpr int STRIDE = UNROLL * WARPS;
     int c0 = warp;
     load_w(wa[0], c0);
     load_w(wa[1], c0 + STRIDE);
-    pdl_wait();
-    pdl_launch_dependents();
     load_x(xa[0], c0);
     load_x(xa[1], c0 + STRIDE);
+    // The blocks' sums of squares of the rows of x travel to shared memory beside the weight
+    // stream (asynchronous copies: no registers, nothing waits for them before the last chunk).
+    if (f.in_partials != nullptr) {
+        for (int i = threadIdx.x; i < f.in_blocks * 4; i += THREADS) {
+            const unsigned dst = (unsigned)__cvta_generic_to_shared(in_sums + 4 * i);
+            asm volatile("cp.async.ca.shared.global [%0], [%1], 16;\n" ::"r"(dst), "l"(f.in_partials + 4 * i));
+        }
+    }
+    asm volatile("cp.async.commit_group;\n" ::);
     while (c0 < chunks) {
         compute_batch(wa[0], xa[0], c0);
         c0 += STRIDE;
@@ -155,6 +180,19 @@ skinny_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w, TOut* __re
         load_x(xa[1], c0 + STRIDE);
     }
 
+    // The scale of each row of x: the blocks' sums added lane-strided and then across the warp,
+    // an order that depends on in_blocks only.
+    asm volatile("cp.async.wait_all;\n" ::: "memory");
+    __syncthreads();
+    for (int token = warp; token < NT * 8; token += WARPS) {
+        float scale = 1.f;
+        if (f.in_partials != nullptr) {
+            float sum = 0.f;
+            for (int b = lane; b < f.in_blocks; b += 32) sum += in_sums[b * 16 + token];
+            scale = rsqrtf(mrun::warp_sum(sum) * f.in_inv_width + f.in_eps);
+        }
+        if (lane == 0) row_scale[token] = scale;
+    }
     // partial sums of the eight warps, added in warp order
 #pragma unroll
     for (int mt = 0; mt < MT; ++mt)
@@ -166,17 +204,17 @@ skinny_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w, TOut* __re
             red[warp][mt * 16 + g + 8][nt * 8 + 2 * t + 1] = acc[mt][nt][3];
         }
     __syncthreads();
-    if constexpr (!SWIGLU) {
+    if constexpr (EPI == EPI_PLAIN) {
         for (int i = threadIdx.x; i < MT * 16 * NT * 8; i += THREADS) {
             const int row = i % (MT * 16), token = i / (MT * 16);
             if (token < M && n0 + row < N) {
                 float s = 0.f;
 #pragma unroll
                 for (int wi = 0; wi < WARPS; ++wi) s += red[wi][row][token];
-                store_out<TOut>(y + (size_t)token * ldy + n0 + row, s);
+                store_out<TOut>(y + (size_t)token * ldy + n0 + row, s * row_scale[token]);
             }
         }
-    } else {
+    } else if constexpr (EPI == EPI_GATED) {
         // rows 16j .. 16j+7 are gate rows, 16j+8 .. 16j+15 the up rows of the same outputs
         for (int i = threadIdx.x; i < MT * 8 * NT * 8; i += THREADS) {
             const int col = i % (MT * 8), token = i / (MT * 8);
@@ -190,68 +228,163 @@ skinny_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w, TOut* __re
                     up += red[wi][tile * 16 + 8 + r][token];
                 }
                 // the activation sees the gate as the layer would have stored it
-                gate = __bfloat162float(__float2bfloat16_rn(gate));
-                up = __bfloat162float(__float2bfloat16_rn(up));
-                store_out<TOut>(y + (size_t)token * ldy + out_col, mrun::silu_mul<false>(gate, up));
+                gate = __bfloat162float(__float2bfloat16_rn(gate * row_scale[token]));
+                up = __bfloat162float(__float2bfloat16_rn(up * row_scale[token]));
+                store_out<TOut>(y + (size_t)token * ldy + out_col, mrun::gated_mul<false>(f.act, gate, up));
             }
+        }
+    } else {
+        // 16 consecutive threads hold the block's 16 columns of one row: the stream gets the sum,
+        // the next product its x, and the 16 squares meet in the group's first lane
+        for (int i = threadIdx.x; i < 16 * NT * 8; i += THREADS) {
+            const int row = i & 15, token = i >> 4;
+            float v = 0.f;
+            if (token < M && n0 + row < N) {
+                float s = 0.f;
+#pragma unroll
+                for (int wi = 0; wi < WARPS; ++wi) s += red[wi][row][token];
+                float* r = f.resid + (size_t)token * f.ldr + n0 + row;
+                v = *r + s * row_scale[token];
+                *r = v;
+                f.xw_out[(size_t)token * N + n0 + row] = __float2bfloat16_rn(v * f.norm_w[n0 + row]);
+            }
+            float q = v * v;
+#pragma unroll
+            for (int o = 8; o > 0; o >>= 1) q += __shfl_xor_sync(0xffffffffu, q, o);
+            if (row == 0 && token < M) f.out_partials[(size_t)blockIdx.x * 16 + token] = q;
         }
     }
 }
 
-template <int NT, int MT, int UNROLL, typename TOut, bool SWIGLU>
-void launch(const bf16* x, const bf16* w, TOut* y, int M, int N, int K, long ldx, long ldy, cudaStream_t stream) {
+template <int NT, int MT, int UNROLL, typename TOut, int EPI>
+void launch(const bf16* x, const bf16* w, TOut* y, int M, int N, int K, long ldx, long ldy, const Fusion& f,
+            cudaStream_t stream) {
     const int blocks = (N + MT * 16 - 1) / (MT * 16);
-    mrun::launch_pdl(MRUN_PDL_GEMM, skinny_kernel<NT, MT, UNROLL, TOut, SWIGLU>, dim3(blocks), dim3(THREADS), 0,
-                     stream, x, w, y, M, N, K, ldx, ldy);
+    skinny_kernel<NT, MT, UNROLL, TOut, EPI><<<blocks, THREADS, 0, stream>>>(x, w, y, M, N, K, ldx, ldy, f);
 }
 
-template <typename TOut, bool SWIGLU>
-void dispatch(const bf16* x, const bf16* w, TOut* y, int M, int N, int K, long ldx, long ldy, cudaStream_t stream) {
-    // two row tiles per block halve the reads of x once there are plenty of blocks
-    const bool wide = N >= MRUN_SKINNY_WIDE_N;
-    constexpr int DEEP = MRUN_SKINNY_UNROLL, SHALLOW = MRUN_SKINNY_UNROLL_WIDE;
+int sm_count() {
+    static int count = 0;          // of the current device at the first call; a tuning input only
+    if (count == 0) {
+        int device = 0;
+        if (cudaGetDevice(&device) != cudaSuccess ||
+            cudaDeviceGetAttribute(&count, cudaDevAttrMultiProcessorCount, device) != cudaSuccess || count < 1)
+            count = 148;
+    }
+    return count;
+}
+
+template <typename TOut, int EPI>
+void dispatch(const bf16* x, const bf16* w, TOut* y, int M, int N, int K, long ldx, long ldy, const Fusion& f,
+              cudaStream_t stream) {
+    const int sms = sm_count();
+    const bool two_rounds = (N + 15) / 16 > 2 * sms;      // more 16-row blocks than two a multiprocessor
     if (M <= 8) {
-        // With the deep batches two blocks fit on an SM (registers), with the shallow ones three.
-        // More than two rounds' worth of 16-row blocks (N = 6144: 384 blocks on 148 SMs) run in
-        // one round with the shallow kind; fewer blocks are faster with the deep kind.
-        if (wide) launch<1, 2, SHALLOW, TOut, SWIGLU>(x, w, y, M, N, K, ldx, ldy, stream);
-        else if ((N + 15) / 16 > 2 * 148) launch<1, 1, SHALLOW, TOut, SWIGLU>(x, w, y, M, N, K, ldx, ldy, stream);
-        else launch<1, 1, DEEP, TOut, SWIGLU>(x, w, y, M, N, K, ldx, ldy, stream);
+        // With the deep batches two blocks fit on a multiprocessor (registers), with the shallow
+        // ones three.  Plenty of blocks: two row tiles a block halve the reads of x.  More than
+        // two rounds' worth of 16-row blocks run in one round with the shallow kind; fewer blocks
+        // are faster with the deep kind.
+        if constexpr (EPI != EPI_RESIDUAL) {
+            if (N >= 32 * sms * 4) return launch<1, 2, UNROLL_SHALLOW, TOut, EPI>(x, w, y, M, N, K, ldx, ldy, f, stream);
+        }
+        if (two_rounds) launch<1, 1, UNROLL_SHALLOW, TOut, EPI>(x, w, y, M, N, K, ldx, ldy, f, stream);
+        else launch<1, 1, UNROLL_DEEP, TOut, EPI>(x, w, y, M, N, K, ldx, ldy, f, stream);
     } else {
         // 9 to 16 rows of x: every chunk carries twice the x, so one row tile a block, and with
-        // more than two rounds' worth of blocks one chunk per batch (measured at 16 rows, us:
-        // QKV 6144x4096 17.6 -> 12.7, gate/up 24576x4096 53.9 -> 37.7 with one chunk; O 4096x4096
-        // 10.4 and down 4096x12288 24.3 with two chunks, 11.2 and 28.2 with one)
-        if ((N + 15) / 16 > 2 * 148) launch<2, 1, 1, TOut, SWIGLU>(x, w, y, M, N, K, ldx, ldy, stream);
-        else launch<2, 1, SHALLOW, TOut, SWIGLU>(x, w, y, M, N, K, ldx, ldy, stream);
+        // more than two rounds' worth of blocks one chunk per batch
+        if (two_rounds) launch<2, 1, 1, TOut, EPI>(x, w, y, M, N, K, ldx, ldy, f, stream);
+        else launch<2, 1, UNROLL_SHALLOW, TOut, EPI>(x, w, y, M, N, K, ldx, ldy, f, stream);
     }
 }
 
 }  // namespace
 
-// out_dtype: MRUN_BF16 or MRUN_F32.  swiglu != 0: W holds gate/up rows interleaved in runs of
-// eight and y gets N / 2 columns of SiLU(gate) * up.  x rows are ldx elements apart, y rows ldy.
-MRUN_API int mrun_gemm_skinny(const void* x, const void* w, void* y, int out_dtype, int swiglu, int M, int N,
-                              int K, long ldx, long ldy, cudaStream_t stream) {
+// y[M, N] = x[M, K] · w[N, K]^T for M <= 16.  out_dtype: MRUN_BF16 or MRUN_F32.  gate != 0
+// (MRUN_GATE_*): W holds gate/up rows interleaved in runs of eight and y gets N / 2 columns of
+// act(gate) * up.  x rows are ldx elements apart, y rows ldy.
+// in_partials != null: x is the xw that a call with `resid` made, and every row's sums are
+// multiplied by rsqrt(sum over in_blocks of in_partials[b][row] / K + in_eps).
+// resid != null: nothing is written to y; instead resid[M, N] (32-bit, dense) += the product,
+// xw_out[M, N] = bf16(resid * norm_w) and out_partials[(N + 15) / 16][16] gets every block's sums
+// of squares of its 16 columns of resid, per row.
+MRUN_API int mrun_gemm_skinny(const void* x, const void* w, void* y, int out_dtype, int gate, int M, int N,
+                              int K, long ldx, long ldy, const float* in_partials, int in_blocks, float in_eps,
+                              float* resid, const float* norm_w, void* xw_out, float* out_partials,
+                              cudaStream_t stream) {
     MRUN_REQUIRE(M >= 0 && N > 0 && K > 0, "gemm_skinny: bad sizes M=%d N=%d K=%d", M, N, K);
     MRUN_REQUIRE(M <= 16, "gemm_skinny: M=%d exceeds the 16 rows this kernel takes", M);
     MRUN_REQUIRE(K % 32 == 0, "gemm_skinny: K=%d is not a multiple of 32", K);
     MRUN_REQUIRE(ldx >= K && ldx % 8 == 0, "gemm_skinny: ldx=%ld must be a multiple of 8 and at least K=%d", ldx, K);
     MRUN_REQUIRE(((uintptr_t)x & 15) == 0 && ((uintptr_t)w & 15) == 0, "gemm_skinny: x and W must be 16-byte aligned");
-    MRUN_REQUIRE(!swiglu || N % 16 == 0, "gemm_skinny: the gated epilogue needs N=%d to be a multiple of 16", N);
-    MRUN_REQUIRE(ldy >= (swiglu ? N / 2 : N), "gemm_skinny: ldy=%ld is below the output width", ldy);
-    if (M == 0) return 0;
+    MRUN_REQUIRE(in_partials == nullptr || (in_blocks > 0 && in_blocks <= MAX_IN_BLOCKS && ((uintptr_t)in_partials & 15) == 0),
+                 "gemm_skinny: a row scale from in_blocks=%d sums (1..%d, 16-byte aligned) cannot be applied", in_blocks,
+                 MAX_IN_BLOCKS);
+    Fusion f = {};
+    f.act = gate;
+    f.in_partials = in_partials;
+    f.in_blocks = in_blocks;
+    f.in_eps = in_eps;
+    f.in_inv_width = 1.f / (float)K;
     const bf16* xp = (const bf16*)x;
     const bf16* wp = (const bf16*)w;
+    if (resid != nullptr) {
+        MRUN_REQUIRE(!gate, "gemm_skinny: the residual epilogue has no gate");
+        MRUN_REQUIRE(norm_w != nullptr && xw_out != nullptr && out_partials != nullptr,
+                     "gemm_skinny: the residual epilogue needs norm_w, xw_out and out_partials");
+        if (M == 0) return 0;
+        f.resid = resid;
+        f.ldr = N;
+        f.norm_w = norm_w;
+        f.xw_out = (bf16*)xw_out;
+        f.out_partials = out_partials;
+        dispatch<bf16, EPI_RESIDUAL>(xp, wp, (bf16*)nullptr, M, N, K, ldx, ldy, f, stream);
+        MRUN_CHECK_LAUNCH("gemm_skinny");
+        return 0;
+    }
+    if (gate) MRUN_REQUIRE_GATE(gate, "gemm_skinny");
+    MRUN_REQUIRE(!gate || N % 16 == 0, "gemm_skinny: the gated epilogue needs N=%d to be a multiple of 16", N);
+    MRUN_REQUIRE(ldy >= (gate ? N / 2 : N), "gemm_skinny: ldy=%ld is below the output width", ldy);
+    if (M == 0) return 0;
     if (out_dtype == MRUN_BF16) {
-        if (swiglu) dispatch<bf16, true>(xp, wp, (bf16*)y, M, N, K, ldx, ldy, stream);
-        else dispatch<bf16, false>(xp, wp, (bf16*)y, M, N, K, ldx, ldy, stream);
+        if (gate) dispatch<bf16, EPI_GATED>(xp, wp, (bf16*)y, M, N, K, ldx, ldy, f, stream);
+        else dispatch<bf16, EPI_PLAIN>(xp, wp, (bf16*)y, M, N, K, ldx, ldy, f, stream);
     } else if (out_dtype == MRUN_F32) {
-        MRUN_REQUIRE(!swiglu, "gemm_skinny: the gated epilogue writes bfloat16");
-        dispatch<float, false>(xp, wp, (float*)y, M, N, K, ldx, ldy, stream);
+        MRUN_REQUIRE(!gate, "gemm_skinny: the gated epilogue writes bfloat16");
+        dispatch<float, EPI_PLAIN>(xp, wp, (float*)y, M, N, K, ldx, ldy, f, stream);
     } else {
         return mrun_set_error("gemm_skinny: unknown output dtype code %d", out_dtype);
     }
     MRUN_CHECK_LAUNCH("gemm_skinny");
+    return 0;
+}
+
+// out[t, k] = bf16(xw[t, k] * rsqrt(sum over blocks of partials[b][t] / width + eps)): the rows a
+// product with `resid` left as xw, finished into plain RMSNorm output for a consumer that is not
+// one of these products.  The sums are added in the order the products use.
+namespace {
+__global__ void norm_finish_kernel(const bf16* __restrict__ xw, const float* __restrict__ partials, int blocks,
+                                   float eps, float inv_width, bf16* __restrict__ out, int width) {
+    __shared__ float scale;
+    const int token = blockIdx.x;
+    if (threadIdx.x < 32) {
+        float sum = 0.f;
+        for (int b = threadIdx.x; b < blocks; b += 32) sum += partials[b * 16 + token];
+        sum = mrun::warp_sum(sum);
+        if (threadIdx.x == 0) scale = rsqrtf(sum * inv_width + eps);
+    }
+    __syncthreads();
+    for (int k = threadIdx.x; k < width; k += blockDim.x)
+        out[(size_t)token * width + k] = __float2bfloat16_rn(__bfloat162float(xw[(size_t)token * width + k]) * scale);
+}
+}  // namespace
+
+MRUN_API int mrun_norm_finish(const void* xw, const float* partials, int blocks, float eps, void* out, int tokens,
+                              int width, cudaStream_t stream) {
+    MRUN_REQUIRE(tokens >= 0 && tokens <= 16 && width > 0 && blocks > 0,
+                 "norm_finish: bad sizes tokens=%d width=%d blocks=%d", tokens, width, blocks);
+    if (tokens == 0) return 0;
+    norm_finish_kernel<<<tokens, 256, 0, stream>>>((const bf16*)xw, partials, blocks, eps, 1.f / (float)width,
+                                                   (bf16*)out, width);
+    MRUN_CHECK_LAUNCH("norm_finish");
     return 0;
 }

@@ -33,10 +33,6 @@
 #include "common.cuh"
 #include "tcgen05.cuh"
 
-#ifndef MRUN_TC5_L2_PROMOTION
-#define MRUN_TC5_L2_PROMOTION CU_TENSOR_MAP_L2_PROMOTION_L2_256B
-#endif
-
 namespace {
 
 using bf16 = __nv_bfloat16;
@@ -71,7 +67,7 @@ template <int TOK> constexpr int stages_for() {
 // Writes one warp's 32 weight rows x 16 tokens of results.  `row` is the thread's weight row.
 template <typename TOut, bool SWIGLU>
 __device__ __forceinline__ void write_columns(TOut* __restrict__ y, long ldy, const float (&v)[16], int row, int tok0,
-                                              int M, int N) {
+                                              int M, int N, int act) {
     const int lane = threadIdx.x & 31;
     if constexpr (!SWIGLU) {
 #pragma unroll
@@ -87,7 +83,7 @@ __device__ __forceinline__ void write_columns(TOut* __restrict__ y, long ldy, co
             if (is_gate && tok0 + j < M && row < N) {
                 const float gate = __bfloat162float(__float2bfloat16_rn(v[j]));
                 const float up = __bfloat162float(__float2bfloat16_rn(up_raw));
-                store_out<TOut>(y + (size_t)(tok0 + j) * ldy + out_col, mrun::silu_mul<false>(gate, up));
+                store_out<TOut>(y + (size_t)(tok0 + j) * ldy + out_col, mrun::gated_mul<false>(act, gate, up));
             }
         }
     }
@@ -107,7 +103,7 @@ template <int TOK, typename TOut, bool SWIGLU>
 __global__ void __launch_bounds__(192)
 gemm_tc5_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
                 TOut* __restrict__ y, long ldy, int M, int N, int k_blocks, int per, int total_units,
-                float* __restrict__ partial, int* __restrict__ counters, int* __restrict__ status) {
+                float* __restrict__ partial, int* __restrict__ counters, int* __restrict__ status, int act) {
     constexpr int STAGES = stages_for<TOK>();
     constexpr int W_BYTES = BLOCK_ROWS * BLOCK_K * 2, X_BYTES = TOK * BLOCK_K * 2;
     constexpr unsigned ACC_COLS = TOK < 32 ? 32 : TOK;
@@ -154,14 +150,9 @@ gemm_tc5_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
                 if (*(volatile int*)&aborted) break;
                 const int u = u0 + i, tile = u / k_blocks, kb = u - tile * k_blocks;
                 unsigned char* w_tile = tiles + (size_t)s * (W_BYTES + X_BYTES);
-#ifdef MRUN_TC5_DEBUG_NO_X
-                mbar_expect_tx(&full_bar[s], W_BYTES);
-                tma_load_2d(w_tile, &map_w, kb * BLOCK_K, tile * BLOCK_ROWS, &full_bar[s]);
-#else
                 mbar_expect_tx(&full_bar[s], W_BYTES + X_BYTES);
                 tma_load_2d(w_tile, &map_w, kb * BLOCK_K, tile * BLOCK_ROWS, &full_bar[s]);
                 tma_load_2d(w_tile + W_BYTES, &map_x, kb * BLOCK_K, 0, &full_bar[s]);
-#endif
             }
         }
     } else if (warp == 1) {
@@ -194,13 +185,11 @@ gemm_tc5_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
                 const unsigned char* w_tile = tiles + (size_t)s * (W_BYTES + X_BYTES);
                 const unsigned long long a_desc = smem_descriptor(w_tile), b_desc = smem_descriptor(w_tile + W_BYTES);
                 const unsigned d_tmem = tmem_base + acc * ACC_COLS;
-#ifndef MRUN_TC5_DEBUG_NO_MMA
 #pragma unroll
                 for (int k = 0; k < BLOCK_K / UMMA_K; ++k)       // 32 bytes further along k per instruction
                     umma_bf16(d_tmem, a_desc + (unsigned long long)(k * UMMA_K * 2 >> 4),
                               b_desc + (unsigned long long)(k * UMMA_K * 2 >> 4), idesc,
                               (first_of_segment && k == 0) ? 0u : 1u);
-#endif
                 umma_commit(&empty_bar[s]);                      // the stage is free once these have read it
                 const bool last_of_segment = i == n_units - 1 || kb == k_blocks - 1;
                 if (last_of_segment) umma_commit(&acc_full[acc]);
@@ -234,7 +223,7 @@ gemm_tc5_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
                         if (c >= M) break;
                         float v[16];
                         tmem_load16(lane_base + c, v);
-                        write_columns<TOut, SWIGLU>(y, ldy, v, row, c, M, N);
+                        write_columns<TOut, SWIGLU>(y, ldy, v, row, c, M, N, act);
                     }
                 }
                 tc_fence_before();
@@ -279,7 +268,7 @@ gemm_tc5_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
                                 v[4 * w4] += t.x; v[4 * w4 + 1] += t.y; v[4 * w4 + 2] += t.z; v[4 * w4 + 3] += t.w;
                             }
                         }
-                        write_columns<TOut, SWIGLU>(y, ldy, v, row, c, M, N);
+                        write_columns<TOut, SWIGLU>(y, ldy, v, row, c, M, N, act);
                     }
                     if (tid == 0) counters[tile] = 0;
                 }
@@ -313,14 +302,14 @@ int make_map(CUtensorMap* map, const void* base, long rows, long cols, long ld, 
     const cuuint32_t elem[2] = {1, 1};
     const CUresult rc = encode(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box,
                                elem, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
-                               MRUN_TC5_L2_PROMOTION, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+                               CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     MRUN_REQUIRE(rc == CUDA_SUCCESS, "gemm_tc5: cuTensorMapEncodeTiled failed with code %d", (int)rc);
     return 0;
 }
 
 template <int TOK, typename TOut, bool SWIGLU>
 int launch(const CUtensorMap& map_w, const CUtensorMap& map_x, TOut* y, long ldy, int M, int N, int K, int blocks,
-           float* partial, int* counters, int* status, cudaStream_t stream) {
+           float* partial, int* counters, int* status, cudaStream_t stream, int act) {
     constexpr int STAGES = stages_for<TOK>();
     constexpr size_t smem = (size_t)STAGES * (BLOCK_ROWS * BLOCK_K * 2 + TOK * BLOCK_K * 2) + 1024;
     static bool configured = false;
@@ -334,21 +323,21 @@ int launch(const CUtensorMap& map_w, const CUtensorMap& map_x, TOut* y, long ldy
     const int per = (total + blocks - 1) / blocks;
     const int grid = (total + per - 1) / per;
     gemm_tc5_kernel<TOK, TOut, SWIGLU><<<grid, 192, smem, stream>>>(map_w, map_x, y, ldy, M, N, k_blocks, per, total,
-                                                                   partial, counters, status);
+                                                                   partial, counters, status, act);
     MRUN_CHECK_LAUNCH("gemm_tc5");
     return 0;
 }
 
 template <typename TOut, bool SWIGLU>
 int dispatch(const CUtensorMap& map_w, const void* x, long ldx, TOut* y, long ldy, int M, int N, int K, int blocks,
-             float* partial, int* counters, int* status, cudaStream_t stream, int tok) {
+             float* partial, int* counters, int* status, cudaStream_t stream, int tok, int act) {
     CUtensorMap map_x;
     if (int rc = make_map(&map_x, x, M, K, ldx, tok)) return rc;
     switch (tok) {
-        case 32: return launch<32, TOut, SWIGLU>(map_w, map_x, y, ldy, M, N, K, blocks, partial, counters, status, stream);
-        case 64: return launch<64, TOut, SWIGLU>(map_w, map_x, y, ldy, M, N, K, blocks, partial, counters, status, stream);
-        case 128: return launch<128, TOut, SWIGLU>(map_w, map_x, y, ldy, M, N, K, blocks, partial, counters, status, stream);
-        case 256: return launch<256, TOut, SWIGLU>(map_w, map_x, y, ldy, M, N, K, blocks, partial, counters, status, stream);
+        case 32: return launch<32, TOut, SWIGLU>(map_w, map_x, y, ldy, M, N, K, blocks, partial, counters, status, stream, act);
+        case 64: return launch<64, TOut, SWIGLU>(map_w, map_x, y, ldy, M, N, K, blocks, partial, counters, status, stream, act);
+        case 128: return launch<128, TOut, SWIGLU>(map_w, map_x, y, ldy, M, N, K, blocks, partial, counters, status, stream, act);
+        case 256: return launch<256, TOut, SWIGLU>(map_w, map_x, y, ldy, M, N, K, blocks, partial, counters, status, stream, act);
     }
     return mrun_set_error("gemm_tc5: no kernel for a token tile of %d", tok);
 }
@@ -368,11 +357,11 @@ MRUN_API long mrun_gemm_tc5_scratch_floats(int M, int blocks) {
     return (long)blocks * 2 * BLOCK_ROWS * tok;
 }
 
-// y[M, N] (or [M, N / 2] with swiglu) = x[M, K] · w[N, K]^T.  x rows ldx elements apart, y rows ldy.
+// y[M, N] (or, with gate = MRUN_GATE_*, [M, N / 2] of act(gate) * up) = x[M, K] · w[N, K]^T.  x rows ldx elements apart, y rows ldy.
 // blocks: how many blocks share the work (the number of SMs); partial: scratch of
 // mrun_gemm_tc5_scratch_floats floats; counters: one zero int per 128 rows of w (left zero);
 // status: one int the kernel sets non-zero when a wait ran out.
-MRUN_API int mrun_gemm_tc5(const void* x, const void* w, void* y, int out_dtype, int swiglu, int M, int N, int K,
+MRUN_API int mrun_gemm_tc5(const void* x, const void* w, void* y, int out_dtype, int gate, int M, int N, int K,
                            long ldx, long ldy, int blocks, float* partial, int* counters, int* status,
                            cudaStream_t stream) {
     MRUN_REQUIRE(M >= 1 && N > 0 && K > 0, "gemm_tc5: bad sizes M=%d N=%d K=%d", M, N, K);
@@ -381,6 +370,8 @@ MRUN_API int mrun_gemm_tc5(const void* x, const void* w, void* y, int out_dtype,
     MRUN_REQUIRE(K % BLOCK_K == 0, "gemm_tc5: K=%d is not a multiple of %d", K, BLOCK_K);
     MRUN_REQUIRE(ldx >= K && ldx % 8 == 0, "gemm_tc5: ldx=%ld must be a multiple of 8 and at least K=%d", ldx, K);
     MRUN_REQUIRE(((uintptr_t)x & 15) == 0 && ((uintptr_t)w & 15) == 0, "gemm_tc5: x and W must be 16-byte aligned");
+    if (gate) MRUN_REQUIRE_GATE(gate, "gemm_tc5");
+    const int swiglu = gate;
     MRUN_REQUIRE(!swiglu || N % 16 == 0, "gemm_tc5: the gated epilogue needs N=%d to be a multiple of 16", N);
     MRUN_REQUIRE(ldy >= (swiglu ? N / 2 : N), "gemm_tc5: ldy=%ld is below the output width", ldy);
     MRUN_REQUIRE(blocks >= 1 && blocks <= 4096, "gemm_tc5: blocks=%d must be in 1..4096", blocks);
@@ -389,12 +380,12 @@ MRUN_API int mrun_gemm_tc5(const void* x, const void* w, void* y, int out_dtype,
     if (int rc = make_map(&map_w, w, N, K, K, BLOCK_ROWS)) return rc;
     if (out_dtype == MRUN_BF16) {
         if (swiglu)
-            return dispatch<bf16, true>(map_w, x, ldx, (bf16*)y, ldy, M, N, K, blocks, partial, counters, status, stream, tok);
-        return dispatch<bf16, false>(map_w, x, ldx, (bf16*)y, ldy, M, N, K, blocks, partial, counters, status, stream, tok);
+            return dispatch<bf16, true>(map_w, x, ldx, (bf16*)y, ldy, M, N, K, blocks, partial, counters, status, stream, tok, gate);
+        return dispatch<bf16, false>(map_w, x, ldx, (bf16*)y, ldy, M, N, K, blocks, partial, counters, status, stream, tok, gate);
     }
     if (out_dtype == MRUN_F32) {
         MRUN_REQUIRE(!swiglu, "gemm_tc5: the gated epilogue writes bfloat16");
-        return dispatch<float, false>(map_w, x, ldx, (float*)y, ldy, M, N, K, blocks, partial, counters, status, stream, tok);
+        return dispatch<float, false>(map_w, x, ldx, (float*)y, ldy, M, N, K, blocks, partial, counters, status, stream, tok, gate);
     }
     return mrun_set_error("gemm_tc5: unknown output dtype code %d", out_dtype);
 }

@@ -137,15 +137,17 @@ HOST_API int mrun_sched_plan(int n, const int64_t* sequence_len, const int64_t* 
     return made;
 }
 
-// Why a request ends after the token that brought its output to output_len tokens: 0 it goes on,
-// 1 an end token, 2 the output limit, 3 repetition.  `recent` holds the last recent_len tokens of
+// Why a request ends at a sampled token: 0 it goes on, 1 an end token (the token is not part of
+// the output: output_len is the output's length without it), 2 the output limit, 3 repetition
+// (output_len counts the token).  The loop guard is off with ignore_eos: runs of a forced length
+// go to their limit on purpose (crates/mrun/src/runtime/generate.rs:908-913).  `recent` holds the last recent_len tokens of
 // the output (the loop guard wants the last 512); it is looked at only when output_len is a
 // multiple of the loop guard's interval and may be null otherwise.
 HOST_API int mrun_sched_end_reason(int is_end_token, int ignore_eos, int64_t output_len, int64_t limit,
                                    const int* recent, int64_t recent_len) {
     if (is_end_token && !ignore_eos) return 1;
     if (output_len >= limit) return 2;
-    if (recent != nullptr && output_len % LOOP_CHECK_EVERY == 0 && mrun_sched_looping(recent, recent_len)) return 3;
+    if (!ignore_eos && recent != nullptr && output_len % LOOP_CHECK_EVERY == 0 && mrun_sched_looping(recent, recent_len)) return 3;
     return 0;
 }
 

@@ -123,7 +123,11 @@ class Engine:
         log-probabilities (of the logits as the model gave them, before any penalty); such
         requests are read back step by step, not pipelined.  ``on_token(i, token)`` is called as
         each output token of prompt i reaches the host (with pipelined decoding one step after it
-        was sampled), the way the reference streams a generation to its client."""
+        was sampled), the way the reference streams a generation to its client; when it returns
+        False, prompt i is cancelled: it ends with finish reason ``cancelled`` and the tokens read
+        so far, and the other prompts go on unchanged (the reference's cancel flag,
+        crates/mrun-engine/src/engine.rs:463-479).  An end token finishes a prompt with ``stop``
+        and is itself not part of the output (crates/mrun/src/runtime/generate.rs:868-874)."""
         if not 0 <= logprobs <= 1024:
             raise ValueError(f"logprobs must be 0 .. 1024, got {logprobs}")
         requests = []

@@ -13,7 +13,7 @@ import torch
 
 from ..config.spec import ModelSpec
 from ..kernels import ops
-from ..parts import ARRANGEMENTS, NORMS, Runtime
+from ..parts import ARRANGEMENTS, NORMS, TRANSFORMS, Runtime
 from ..parts.base import local
 from .batch import StepContext
 
@@ -30,6 +30,13 @@ class Model:
         self.blocks = [ARRANGEMENTS.get(layer.arrangement)(layer, tensors, runtime) for layer in spec.layers]
         self.final_norm = NORMS.build(spec.final_norm, local(tensors, spec.final_norm_prefix), runtime)
         self.order = spec.run_order()
+        self.embedding_transform = self.logits_transform = None
+        if spec.embedding_transform is not None:
+            t = spec.embedding_transform
+            self.embedding_transform = TRANSFORMS.build(t, local(tensors, getattr(t, "prefix", "")), runtime)
+        if spec.logits_transform is not None:
+            t = spec.logits_transform
+            self.logits_transform = TRANSFORMS.build(t, local(tensors, getattr(t, "prefix", "")), runtime)
 
     # ------------------------------------------------------------------ cache layout
     def cache_needs(self) -> List[object]:
@@ -86,15 +93,25 @@ class Model:
         resid = torch.empty((ctx.num_tokens, self.spec.hidden_size), dtype=torch.float32,
                             device=self.runtime.device)
         ops.embed(self.embedding, ctx.token_ids, resid)
+        if self.embedding_transform is not None:
+            resid = self.embedding_transform.forward(resid)
         delta = None
         for at, entry in enumerate(self.order):
-            delta = self.blocks[entry.layer].forward(resid, delta, ctx, caches[at])
+            block = self.blocks[entry.layer]
+            if isinstance(delta, ops.PendingLinear) and not getattr(block, "accepts_pending", False):
+                delta = delta.compute()
+            delta = block.forward(resid, delta, ctx, caches[at])
         return resid, delta
 
     def logits(self, resid: torch.Tensor, delta: Optional[torch.Tensor], rows: torch.Tensor) -> torch.Tensor:
         """float32 ``[len(rows), vocab]``: final norm and head at the wanted rows only."""
+        if isinstance(delta, ops.PendingLinear):
+            delta = delta.compute()
         h = self.final_norm.rows_forward(resid, delta, rows)
-        return ops.linear(h, self.head, out_dtype=torch.float32)
+        logits = ops.linear(h, self.head, out_dtype=torch.float32)
+        if self.logits_transform is not None:
+            logits = self.logits_transform.forward(logits)
+        return logits
 
     def forward(self, ctx: StepContext, caches, rows: Optional[torch.Tensor]) -> Optional[torch.Tensor]:
         resid, delta = self.hidden_states(ctx, caches)

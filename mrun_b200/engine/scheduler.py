@@ -31,9 +31,14 @@ Decisions, with the reference's where it has one
   is left out, and a request that turns out to have ended (an end token) while a later step was
   already launched is marked ``retiring``: that step's token for it is dropped and its pages are
   freed when the step is read.
-* **Finishing**: an end token (unless ``ignore_eos``) → ``stop``; the output limit → ``length``;
-  the last 512 output tokens repeating with a period of at most 256, checked every 16 tokens →
-  ``repetition`` (crates/mrun/src/runtime/generate.rs:27-33, 420-426, 866-919).
+* **Finishing**: an end token (unless ``ignore_eos``) → ``stop``, the end token itself being left
+  out of the output; the output limit → ``length``; the last 512 output tokens repeating with a
+  period of at most 256, checked every 16 tokens and never with ``ignore_eos`` → ``repetition``
+  (crates/mrun/src/runtime/generate.rs:27-33, 420-426, 866-919).
+* **Cancelling**: ``on_token`` returning False, or ``Request.cancel_requested`` set by the caller,
+  ends the request with ``cancelled`` when its next token is read: the tokens read so far stay,
+  a token still in flight for it is dropped, its pages go back, and the other requests of the
+  step go on unchanged (the reference's cancel flag, crates/mrun-engine/src/engine.rs:463-479).
 """
 from __future__ import annotations
 
@@ -90,6 +95,7 @@ class Request:
     finished_at: float = 0.0
     token_times: List[float] = field(default_factory=list)   # when each output token was read back
     top_logprobs: List[list] = field(default_factory=list)   # per output token: [(id, log-probability), ...]
+    cancel_requested: bool = False     # set from outside (or by on_token returning False): end at the next token read
     inflight: int = 0                  # tokens sampled on the device that the host has not read yet
     retiring: bool = False             # finished, but a step in flight still holds a row of it
 
@@ -288,18 +294,27 @@ class Scheduler:
                 if request.inflight == 0:
                     self._retire(request)
                 continue
-            if not request.output:
-                request.first_token_at = now
-            request.output.append(token)
-            request.token_times.append(now)
-            if request.on_token is not None:
-                request.on_token(request, token)
-            count = len(request.output)
+            # The end token itself is not part of the output: it is neither counted, streamed nor
+            # returned (crates/mrun/src/runtime/generate.rs:868-874 returns Stop before pushing).
+            count = len(request.output) + 1
             recent, recent_len = None, 0             # the loop guard looks every few tokens only
-            if count % self._loop_check_every == 0 and count >= LOOP_WINDOW:
-                recent, recent_len = native.int_array(request.output[-LOOP_WINDOW:]), LOOP_WINDOW
+            if count % self._loop_check_every == 0 and count >= LOOP_WINDOW and not request.ignore_eos:
+                recent = native.int_array(request.output[-(LOOP_WINDOW - 1):] + [token])
+                recent_len = LOOP_WINDOW
             reason = END_REASONS[self._core.mrun_sched_end_reason(
                 1 if token in self.eos else 0, 1 if request.ignore_eos else 0, count, request.limit, recent, recent_len)]
+            if request.first_token_at == 0.0:
+                request.first_token_at = now
+            cancelled = False
+            if reason != "stop":
+                request.output.append(token)
+                request.token_times.append(now)
+                if request.on_token is not None:
+                    cancelled = request.on_token(request, token) is False
+            else:
+                del request.top_logprobs[len(request.output):]       # the end token's row goes with it
+            if reason is None and (cancelled or request.cancel_requested):
+                reason = "cancelled"
             if reason is not None:
                 if request.inflight:
                     request.retiring = True          # its row in the step in flight is dropped later

@@ -19,7 +19,6 @@ the fused norm/rotary/cache kernel just before.
 from __future__ import annotations
 
 import ctypes
-import os
 
 import numpy as np
 import torch
@@ -50,7 +49,7 @@ def _decode_slots(head_dim: int, library, tma_group: int = 0) -> int:
     return slots
 
 
-TMA_DECODE = os.environ.get("MRUN_DECODE_TMA", "1") != "0"       # 0: the cp.async kernel for every decode step
+TMA_DECODE = True        # False: the cp.async kernel for every decode step (tests compare the two)
 _tma_decode = {}
 
 
@@ -82,7 +81,7 @@ def supports_tensor_cores(dtype: torch.dtype, head_dim: int, group: int) -> bool
     return dtype == torch.bfloat16 and head_dim % 16 == 0 and 16 <= head_dim <= 256 and group <= 64
 
 
-MIN_TILES = 2      # the fewest 64-key tiles a block of the decode kernel takes (batch 1 at 1,024 tokens: 287 / 293 / 290 tok/s with 1 / 2 / 4)
+MIN_TILES = 2      # the fewest 64-key tiles a block of the decode kernel takes
 
 
 MAX_SPLITS = 32    # the most blocks one (token, kv head) pair is cut into when a step has few pairs
@@ -170,8 +169,7 @@ def decode_fuses_input(ctx, dtype: torch.dtype, heads: int, kv_heads: int, head_
     """Whether this step's attention takes q, k and v raw and norms, rotates and stores them itself:
     every segment a single token, bfloat16 and a group that the split-key kernel takes.  A block
     that walks from pair to pair redoes the input work at every change, which costs less than the
-    stand-alone kernel's launch (measured at the 8B shape, tok/s with and without: 64 requests
-    11,846 / 11,760, 40 requests 7,894 / 7,798, 128 requests 16,855 / 16,789)."""
+    stand-alone kernel's launch."""
     ratio = heads // kv_heads
     return ctx.all_decode and ratio <= 16 and supports_tensor_cores(dtype, head_dim, ratio)
 
@@ -254,7 +252,7 @@ def paged_attention(q: torch.Tensor, q_stride: int, out: torch.Tensor, cache, gr
     return out
 
 
-TC5_PREFILL = os.environ.get("MRUN_ATTN_TC5", "1") != "0"      # 0: the mma.sync kernel for every prompt portion
+TC5_PREFILL = True       # False: the mma.sync kernel for every prompt portion (tests compare the two)
 _tc5_prefill = {}
 
 

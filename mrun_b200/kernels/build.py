@@ -188,14 +188,7 @@ CORE_SOURCES = ("common.cu", "elementwise.cu", "gemm_f32.cu", "gemm_skinny.cu", 
 
 
 def build_core() -> str:
-    defines = {}
-    for knob in ("MRUN_SKINNY_WARPS", "MRUN_SKINNY_UNROLL", "MRUN_SKINNY_UNROLL_WIDE", "MRUN_SKINNY_WIDE_N",
-                 "MRUN_TC5_DEBUG_NO_X", "MRUN_TC5_DEBUG_NO_MMA", "MRUN_TC5_L2_PROMOTION"):   # tuning knobs
-        if os.environ.get(knob):
-            value = os.environ[knob]
-            defines[knob] = int(value) if value.lstrip("-").isdigit() else value
-    tag = hashlib.sha256(repr(sorted(defines.items())).encode()).hexdigest()[:8] if defines else ""
-    return build_library(f"mrun_core_{tag}" if tag else "mrun_core", CORE_SOURCES, defines)
+    return build_library("mrun_core", CORE_SOURCES, {})
 
 
 ATTENTION_SOURCES = ("common.cu", "attention_mma.cu", "attention_decode_tma.cu", "attention_tc5.cu")
@@ -205,15 +198,7 @@ def build_attention(head_dim: int) -> str:
     """The tensor-core attention kernels specialised for one head size."""
     if head_dim % 16 or not 16 <= head_dim <= 256:
         raise BuildError(f"the tensor-core attention takes head sizes 16, 32, ... 256, not {head_dim}")
-    defines = {"MRUN_HEAD_DIM": head_dim}
-    stages = os.environ.get("MRUN_DECODE_STAGES")        # tuning knob: key/value tiles in flight
-    if stages:
-        defines["MRUN_DECODE_STAGES"] = int(stages)
-    if os.environ.get("MRUN_ATTN_TC5_TIMING"):           # tuning aid: the first block prints its roles' cycles
-        defines["MRUN_ATTN_TC5_TIMING"] = 1
-        return build_library(f"mrun_attn_d{head_dim}_timing", ATTENTION_SOURCES, defines)
-    return build_library(f"mrun_attn_d{head_dim}_s{stages}" if stages else f"mrun_attn_d{head_dim}",
-                         ATTENTION_SOURCES, defines)
+    return build_library(f"mrun_attn_d{head_dim}", ATTENTION_SOURCES, {"MRUN_HEAD_DIM": head_dim})
 
 
 # head sizes of the configurations this repository measures and tests

@@ -151,32 +151,109 @@ def paged_attention_generic(q: torch.Tensor, q_stride: int, out: torch.Tensor, k
     return out
 
 
-def swiglu(gate_up: torch.Tensor, out: torch.Tensor, interleaved: bool = False) -> torch.Tensor:
-    """out = silu(gate) * up.  Plain layout: gate_up[:, :I] are the gates, gate_up[:, I:] the ups.
+GATE_FUNCTIONS = {"silu": 1, "gelu_tanh": 2}      # codes of the C ABI (MRUN_GATE_*); 0 = no gated epilogue
+
+
+def gate_code(activation: str) -> int:
+    try:
+        return GATE_FUNCTIONS[activation]
+    except KeyError:
+        raise KernelError(f"no kernel has the gate function {activation!r} "
+                          f"(known: {', '.join(sorted(GATE_FUNCTIONS))})") from None
+
+
+def swiglu(gate_up: torch.Tensor, out: torch.Tensor, interleaved: bool = False, activation: str = "silu") -> torch.Tensor:
+    """out = act(gate) * up.  Plain layout: gate_up[:, :I] are the gates, gate_up[:, I:] the ups.
     Interleaved: runs of eight gates followed by the eight ups of the same outputs."""
     _check(gate_up, "gate_up"); _check(out, "out", gate_up.dtype)
     tokens, inter = out.shape
     if gate_up.shape != (tokens, 2 * inter):
         raise KernelError(f"swiglu: gate_up {tuple(gate_up.shape)} vs out {tuple(out.shape)}")
     _lib.core().call("mrun_swiglu", _ptr(gate_up), _ptr(out), dtype_code(out.dtype), _c_int(tokens),
-                     _c_int(inter), _c_int(8 if interleaved else 0), _stream())
+                     _c_int(inter), _c_int(8 if interleaved else 0), _c_int(gate_code(activation)), _stream())
     return out
+
+
+def add_bias(y: torch.Tensor, bias: torch.Tensor) -> torch.Tensor:
+    """y[t, n] += bias[n] in place; bias is float32."""
+    _check(y, "y"); _check(bias, "bias", torch.float32)
+    if y.dim() != 2 or bias.numel() != y.shape[1]:
+        raise KernelError(f"add_bias: y {tuple(y.shape)} vs bias {tuple(bias.shape)}")
+    _lib.core().call("mrun_add_bias", _ptr(y), dtype_code(y.dtype), _ptr(bias), _c_int(y.shape[0]),
+                     _c_int(y.shape[1]), _stream())
+    return y
 
 
 SKINNY_ROWS = 16      # the decode GEMM takes up to this many rows
 
 
-def skinny_ok(x: torch.Tensor, w: torch.Tensor) -> bool:
+def skinny_ok(x, w: torch.Tensor) -> bool:
     """Whether the decode GEMM takes this product: few rows, bf16, K a multiple of 32."""
+    if isinstance(x, NormedRows):
+        x = x.xw
     return (x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and x.shape[0] <= SKINNY_ROWS
             and x.shape[1] % 32 == 0 and x.stride(1) == 1 and x.stride(0) % 8 == 0
             and x.data_ptr() % 16 == 0)
 
 
-def gemm_skinny(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype = torch.bfloat16,
-                swiglu_rows: bool = False) -> torch.Tensor:
+class NormedRows:
+    """The output of an RMSNorm whose row scale has not been applied yet: ``xw`` holds
+    bf16(stream * norm weight) and ``partials`` [blocks, 16] the sums of squares of the stream's
+    columns, block by block, per row.  The decode GEMM takes it as its x and applies
+    rsqrt(sum / width + eps) to its own sums; :meth:`finish` makes the plain normed rows."""
+
+    def __init__(self, xw: torch.Tensor, partials: torch.Tensor, eps: float):
+        self.xw, self.partials, self.eps = xw, partials, float(eps)
+
+    @property
+    def shape(self):
+        return self.xw.shape
+
+    @property
+    def dtype(self):
+        return self.xw.dtype
+
+    @property
+    def device(self):
+        return self.xw.device
+
+    def finish(self) -> torch.Tensor:
+        tokens, width = self.xw.shape
+        out = torch.empty_like(self.xw)
+        _lib.core().call("mrun_norm_finish", _ptr(self.xw), _ptr(self.partials), _c_int(self.partials.shape[0]),
+                         _c_float(self.eps), _ptr(out), _c_int(tokens), _c_int(width), _stream())
+        return out
+
+
+class PendingLinear:
+    """A product ``x @ w.T`` that has not run yet: a part returns it as its output where the norm
+    that follows can run it with the residual sum and the norm folded into its epilogue
+    (:func:`linear_into_norm`).  :meth:`compute` runs it as an ordinary product."""
+
+    def __init__(self, x: torch.Tensor, w: torch.Tensor):
+        self.x, self.w = x, w
+
+    @property
+    def shape(self):
+        return (self.x.shape[0], self.w.shape[0])
+
+    def compute(self) -> torch.Tensor:
+        return linear(self.x, self.w)
+
+
+def _normed(x):
+    """(rows, partials pointer, blocks, eps) of a product's x, which may be :class:`NormedRows`."""
+    if isinstance(x, NormedRows):
+        return x.xw, _ptr(x.partials), _c_int(x.partials.shape[0]), _c_float(x.eps)
+    return x, _ptr(None), _c_int(0), _c_float(0.0)
+
+
+def gemm_skinny(x, w: torch.Tensor, out_dtype: torch.dtype = torch.bfloat16,
+                swiglu_rows: bool = False, activation: str = "silu") -> torch.Tensor:
     """y = x @ w.T for at most 16 rows, reading w once at HBM speed.  ``swiglu_rows``: w holds gate
-    and up rows interleaved in runs of eight and y = silu(gate) * up has half as many columns."""
+    and up rows interleaved in runs of eight and y = act(gate) * up has half as many columns.
+    ``x`` may be :class:`NormedRows`."""
+    x, partials, blocks, eps = _normed(x)
     _check(x, "x", torch.bfloat16, dense=False); _check(w, "w", torch.bfloat16)
     m, k = x.shape
     n = w.shape[0]
@@ -184,9 +261,41 @@ def gemm_skinny(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype = torch
         raise KernelError(f"gemm_skinny: x {tuple(x.shape)} vs w {tuple(w.shape)}")
     out = torch.empty((m, n // 2 if swiglu_rows else n), dtype=out_dtype, device=x.device)
     _lib.core().call("mrun_gemm_skinny", _ptr(x), _ptr(w), _ptr(out), dtype_code(out_dtype),
-                     _c_int(1 if swiglu_rows else 0), _c_int(m), _c_int(n), _c_int(k),
-                     _c_long(x.stride(0) if m > 1 else max(k, x.stride(0))), _c_long(out.shape[1]), _stream())
+                     _c_int(gate_code(activation) if swiglu_rows else 0), _c_int(m), _c_int(n), _c_int(k),
+                     _c_long(x.stride(0) if m > 1 else max(k, x.stride(0))), _c_long(out.shape[1]),
+                     partials, blocks, eps, _ptr(None), _ptr(None), _ptr(None), _ptr(None), _stream())
     return out
+
+
+NORM_FUSION_WIDTH = 8192      # the widest stream whose sums of squares the decode GEMM takes in
+
+
+def norm_fusable(pending, resid: torch.Tensor, weight: torch.Tensor) -> bool:
+    """Whether :func:`linear_into_norm` takes this pending product and residual stream."""
+    return (isinstance(pending, PendingLinear) and skinny_ok(pending.x, pending.w)
+            and resid.dtype == torch.float32 and resid.is_contiguous() and resid.shape == pending.shape
+            and resid.shape[1] % 32 == 0 and resid.shape[1] <= NORM_FUSION_WIDTH and weight.numel() == resid.shape[1])
+
+
+def linear_into_norm(pending: PendingLinear, resid: torch.Tensor, weight: torch.Tensor, eps: float) -> NormedRows:
+    """resid += pending.x @ pending.w.T (32-bit, in place) and the RMSNorm of the new rows with
+    ``weight``, as :class:`NormedRows`: one kernel, at most 16 rows."""
+    x, partials, blocks, in_eps = _normed(pending.x)
+    w = pending.w
+    _check(x, "x", torch.bfloat16, dense=False); _check(w, "w", torch.bfloat16)
+    _check(resid, "resid", torch.float32); _check(weight, "weight", torch.float32)
+    m, k = x.shape
+    n = w.shape[0]
+    if w.shape[1] != k or resid.shape != (m, n) or weight.numel() != n:
+        raise KernelError(f"linear_into_norm: x {tuple(x.shape)}, w {tuple(w.shape)}, resid {tuple(resid.shape)}, "
+                          f"weight {tuple(weight.shape)}")
+    xw = torch.empty((m, n), dtype=torch.bfloat16, device=x.device)
+    out_partials = torch.empty((-(-n // 16), 16), dtype=torch.float32, device=x.device)
+    _lib.core().call("mrun_gemm_skinny", _ptr(x), _ptr(w), _ptr(None), dtype_code(torch.bfloat16), _c_int(0),
+                     _c_int(m), _c_int(n), _c_int(k), _c_long(x.stride(0) if m > 1 else max(k, x.stride(0))),
+                     _c_long(n), partials, blocks, in_eps, _ptr(resid), _ptr(weight), _ptr(xw), _ptr(out_partials),
+                     _stream())
+    return NormedRows(xw, out_partials, eps)
 
 
 def gemm_f32_nt(x: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
@@ -222,19 +331,14 @@ def _tc5_buffers(device: torch.device):
     return state
 
 
-# Measured on B200 at the Qwen3-8B shapes with 64 rows (CUDA events, captured graph): the vendor
-# GEMM 11.7 / 9.9 / 39.6 / 22.9 us for QKV / O / gate-up / down and 209 us for the output head,
-# this kernel 27.9 / 28.3 / 54.8 / 40.7 / 250 us.  Its TMA stream runs at HBM speed (6.9 TB/s per
-# added byte), but a launch carries about 5 us of fixed latency (tensor-memory allocation, the
-# barrier hops from TMA to MMA to epilogue) and about 8 us of partial-tile epilogue where tiles
-# are shared between blocks: too much for products of 10 to 40 us.  It is used on request only.
+# The tcgen05 GEMM is used on request only (MRUN_TC5=1): at 17 to 256 rows the vendor GEMM is faster.
 TC5_DEFAULT = os.environ.get("MRUN_TC5", "0") == "1"
 
 
 def tc5_ok(x: torch.Tensor, w: torch.Tensor) -> bool:
     """Whether the tcgen05 GEMM is to take this product: switched on (MRUN_TC5=1), 17..256 rows,
     bf16, K a multiple of 64."""
-    return (TC5_DEFAULT and x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and SKINNY_ROWS < x.shape[0] <= TC5_ROWS
+    return (TC5_DEFAULT and isinstance(x, torch.Tensor) and x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and SKINNY_ROWS < x.shape[0] <= TC5_ROWS
             and x.shape[1] % 64 == 0 and x.stride(1) == 1 and x.stride(0) % 8 == 0 and x.data_ptr() % 16 == 0
             and w.shape[0] <= 128 * TC5_COUNTERS)
 
@@ -250,7 +354,7 @@ def sm_count(device: torch.device) -> int:
 
 
 def gemm_tc5(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype = torch.bfloat16,
-             swiglu_rows: bool = False, blocks: Optional[int] = None) -> torch.Tensor:
+             swiglu_rows: bool = False, blocks: Optional[int] = None, activation: str = "silu") -> torch.Tensor:
     """y = x @ w.T for 1..256 rows on the tcgen05 tensor cores (TMA-fed, accumulators in tensor
     memory, the work dealt evenly to ``blocks`` thread blocks, by default one per SM).
     ``swiglu_rows`` as in :func:`gemm_skinny`.  A wait inside the kernel that runs out sets the
@@ -268,7 +372,8 @@ def gemm_tc5(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype = torch.bf
     query = core._dll.mrun_gemm_tc5_scratch_floats
     query.restype = ctypes.c_long
     partial = torch.empty(max(1, query(_c_int(m), _c_int(blocks))), dtype=torch.float32, device=x.device)
-    core.call("mrun_gemm_tc5", _ptr(x), _ptr(w), _ptr(out), dtype_code(out_dtype), _c_int(1 if swiglu_rows else 0),
+    core.call("mrun_gemm_tc5", _ptr(x), _ptr(w), _ptr(out), dtype_code(out_dtype),
+              _c_int(gate_code(activation) if swiglu_rows else 0),
               _c_int(m), _c_int(n), _c_int(k), _c_long(x.stride(0) if m > 1 else max(k, x.stride(0))),
               _c_long(out.shape[1]), _c_int(blocks), _ptr(partial), _ptr(counters), _ptr(status), _stream())
     return out
@@ -298,22 +403,37 @@ def tc5_check(device: Optional[torch.device] = None) -> None:
                               f"the results of that call are invalid")
 
 
-def linear(x: torch.Tensor, w: torch.Tensor, out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
-    """y = x @ w.T.  float32: this library's own IEEE kernel.  bfloat16 with at most 16 rows (decode):
-    this library's weight-streaming tensor-core kernel; with 17 to 256 rows: this library's
-    tcgen05 kernel.  bfloat16 otherwise (prefill): the vendor GEMM
-    library with 32-bit accumulation (the reference calls its array library's matmul for the
-    same products, crates/mrun-engine/src/load.rs:294-306)."""
+def linear(x, w: torch.Tensor, out_dtype: Optional[torch.dtype] = None,
+           bias: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """y = x @ w.T (+ bias).  float32: this library's own IEEE kernel.  bfloat16 with at most 16
+    rows (decode): this library's weight-streaming tensor-core kernel (``x`` may then be
+    :class:`NormedRows`).  bfloat16 otherwise (prefill): the vendor GEMM library with 32-bit
+    accumulation (the reference calls its array library's matmul for the same products and adds
+    an optional bias after it, crates/mrun-engine/src/load.rs:294-306)."""
+    if isinstance(x, NormedRows) and not skinny_ok(x, w):
+        x = x.finish()
     if x.dtype == torch.float32:
-        return gemm_f32_nt(x, w)
-    _check(x, "x", torch.bfloat16, dense=False); _check(w, "w", torch.bfloat16)
-    if skinny_ok(x, w):
-        return gemm_skinny(x, w, out_dtype or torch.bfloat16)
-    if tc5_ok(x, w):
-        return gemm_tc5(x, w, out_dtype or torch.bfloat16)
-    if out_dtype is None or out_dtype == torch.bfloat16:
-        return torch.mm(x, w.t())
-    return torch.mm(x, w.t(), out_dtype=out_dtype)
+        y = gemm_f32_nt(x, w)
+    else:
+        _check(x, "x", torch.bfloat16, dense=False); _check(w, "w", torch.bfloat16)
+        if skinny_ok(x, w):
+            y = gemm_skinny(x, w, out_dtype or torch.bfloat16)
+        elif tc5_ok(x, w):
+            y = gemm_tc5(x, w, out_dtype or torch.bfloat16)
+        elif out_dtype is None or out_dtype == torch.bfloat16:
+            y = torch.mm(x, w.t())
+        else:
+            y = torch.mm(x, w.t(), out_dtype=out_dtype)
+    return y if bias is None else add_bias(y, bias)
+
+
+def linear_or_pending(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = None):
+    """The last product of a part whose caller accepts a :class:`PendingLinear`: left pending where
+    the decode GEMM would take it (the norm after it then runs it with its epilogue), computed
+    otherwise."""
+    if bias is None and skinny_ok(x, w):
+        return PendingLinear(x, w)
+    return linear(x, w, bias=bias)
 
 
 def sample(logits: torch.Tensor, out: torch.Tensor, temperature: Optional[torch.Tensor] = None,

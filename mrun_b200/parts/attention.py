@@ -5,6 +5,8 @@ concatenation; the reference keeps three products, crates/mrun-engine/src/models
 per-head RMSNorm of q and k, then rotation, then k and v into the pages
 (crates/mrun-engine/src/models/common.rs:183,194-198); softmax attention of each token over the
 keys of its request up to itself; output projection (crates/mrun-engine/src/models/common.rs:137,206).
+A projection's ``.bias`` is bound and added when the checkpoint has one
+(crates/mrun-engine/src/load.rs:281,302-305); Qwen3's have none.
 """
 from __future__ import annotations
 
@@ -19,6 +21,8 @@ from .base import NORMS, POSITIONS, Runtime, register_mixer
 
 @register_mixer("attention")
 class Attention:
+    accepts_normed_rows = True      # its first product takes ``ops.NormedRows`` as x
+    can_defer_output = True         # ``forward(..., defer_output=True)`` may return ``ops.PendingLinear``
 
     @staticmethod
     def tensor_specs(spec: AttentionSpec, prefix: str):
@@ -28,6 +32,10 @@ class Attention:
             TensorSpec(f"{prefix}.k_proj.weight", (spec.kv_heads * d, spec.hidden)),
             TensorSpec(f"{prefix}.v_proj.weight", (spec.kv_heads * d, spec.hidden)),
             TensorSpec(f"{prefix}.o_proj.weight", (spec.hidden, spec.heads * d)),
+            TensorSpec(f"{prefix}.q_proj.bias", (spec.heads * d,), optional=True),
+            TensorSpec(f"{prefix}.k_proj.bias", (spec.kv_heads * d,), optional=True),
+            TensorSpec(f"{prefix}.v_proj.bias", (spec.kv_heads * d,), optional=True),
+            TensorSpec(f"{prefix}.o_proj.bias", (spec.hidden,), optional=True),
         ]
         if spec.qk_norm is not None:
             out += NORMS.tensor_specs(spec.qk_norm, f"{prefix}.q_norm")
@@ -46,6 +54,14 @@ class Attention:
         self.wqkv = runtime.matrix(torch.cat(
             [tensors["q_proj.weight"], tensors["k_proj.weight"], tensors["v_proj.weight"]], dim=0))
         self.wo = runtime.matrix(tensors["o_proj.weight"])
+        biases = [tensors.get(f"{name}_proj.bias") for name in "qkv"]
+        self.bqkv = None
+        if any(b is not None for b in biases):
+            widths = (spec.heads * spec.head_dim, spec.kv_heads * spec.head_dim, spec.kv_heads * spec.head_dim)
+            self.bqkv = runtime.vector_f32(torch.cat(
+                [torch.zeros(n, dtype=torch.float32) if b is None else b.to(torch.float32)
+                 for b, n in zip(biases, widths)]))
+        self.bo = runtime.vector_f32(tensors["o_proj.bias"]) if "o_proj.bias" in tensors else None
         self.q_weight = self.k_weight = None
         self.eps = 0.0
         if spec.qk_norm is not None:
@@ -66,10 +82,10 @@ class Attention:
         """Elements per token of the temporaries alive at once (q, k, v and the heads' output)."""
         return (2 * self.spec.heads + 2 * self.spec.kv_heads) * self.spec.head_dim
 
-    def forward(self, x: torch.Tensor, ctx, cache) -> torch.Tensor:
+    def forward(self, x, ctx, cache, defer_output: bool = False):
         s = self.spec
         group = ctx.group(cache.group_key)
-        qkv = ops.linear(x, self.wqkv)
+        qkv = ops.linear(x, self.wqkv, bias=self.bqkv)
         rot = self.position.rotation(ctx) if self.position is not None else None
         rotary_dim = self.position.rotary_dim if self.position is not None else 0
         slots = group.slot_mapping if cache.writable else None
@@ -82,4 +98,6 @@ class Attention:
             ops.qk_norm_rope_cache(qkv, s.heads, s.kv_heads, s.head_dim, self.q_weight, self.k_weight,
                                    self.eps, rot, rotary_dim, slots, cache.k, cache.v, self.runtime.page_size)
             paged_attention(qkv, qkv.shape[1], out, cache, group, ctx, s.heads, s.softmax_scale, s.window or 0)
-        return ops.linear(out, self.wo)
+        if defer_output:
+            return ops.linear_or_pending(out, self.wo, self.bo)
+        return ops.linear(out, self.wo, bias=self.bo)

@@ -26,6 +26,17 @@ feed-forward    ``forward(x, ctx) -> y``.
 arrangement     a block class built from a :class:`LayerSpec`; ``forward(resid, delta, ctx,
                 cache) -> delta`` takes the stream and the branch output not yet added to it and
                 returns the next pending branch output.
+transform       ``forward(x) -> x`` on the 32-bit stream right after the embedding
+                (``ModelSpec.embedding_transform``: a scale, an added table) or on the float32
+                logits of the wanted rows (``ModelSpec.logits_transform``: a soft cap, a bias);
+                may work in place.
+
+Optional capabilities (class attributes, all off when absent), which let a step of a handful of
+rows fold the residual sum and the norm into the products around them:
+``can_defer_output`` on a mixer or feed-forward (``forward(..., defer_output=True)`` may return its
+last product unrun, ``kernels.ops.PendingLinear``); ``accepts_pending`` on a norm or arrangement
+(``delta`` may be such a product; a norm may answer with ``kernels.ops.NormedRows``);
+``accepts_normed_rows`` on a mixer or feed-forward (``x`` may be ``NormedRows``).
 """
 from __future__ import annotations
 
@@ -98,12 +109,14 @@ POSITIONS = Registry("position encoding")
 MIXERS = Registry("mixer")
 FEED_FORWARDS = Registry("feed-forward")
 ARRANGEMENTS = Registry("arrangement")
+TRANSFORMS = Registry("transform")
 
 register_norm = NORMS.register
 register_position = POSITIONS.register
 register_mixer = MIXERS.register
 register_feed_forward = FEED_FORWARDS.register
 register_arrangement = ARRANGEMENTS.register
+register_transform = TRANSFORMS.register
 
 
 def local(tensors: Mapping[str, torch.Tensor], prefix: str) -> Dict[str, torch.Tensor]:

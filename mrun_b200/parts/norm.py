@@ -18,17 +18,27 @@ class RMSNorm:
     def tensor_specs(spec: RMSNormSpec, prefix: str):
         return [TensorSpec(f"{prefix}.weight", (spec.size,), "norm")]
 
+    # ``delta`` may be a product that has not run yet (``ops.PendingLinear``): with a handful
+    # of rows it runs with the residual sum and this norm folded into its epilogue, and what
+    # comes back is ``ops.NormedRows`` (the row scale is applied by the product that reads it).
+    accepts_pending = True
+
     def __init__(self, spec: RMSNormSpec, tensors, runtime: Runtime):
         self.size, self.eps = spec.size, float(spec.eps)
         self.weight = runtime.vector_f32(tensors["weight"])
         self.act = runtime.precision.act
 
-    def add_forward(self, resid: torch.Tensor, delta: Optional[torch.Tensor]) -> torch.Tensor:
+    def add_forward(self, resid: torch.Tensor, delta):
+        if isinstance(delta, ops.PendingLinear):
+            if ops.norm_fusable(delta, resid, self.weight):
+                return ops.linear_into_norm(delta, resid, self.weight, self.eps)
+            delta = delta.compute()
         out = torch.empty(resid.shape, dtype=self.act, device=resid.device)
         return ops.add_rmsnorm(resid, delta, self.weight, self.eps, out)
 
-    def rows_forward(self, resid: torch.Tensor, delta: Optional[torch.Tensor],
-                     rows: torch.Tensor) -> torch.Tensor:
+    def rows_forward(self, resid: torch.Tensor, delta, rows: torch.Tensor) -> torch.Tensor:
+        if isinstance(delta, ops.PendingLinear):
+            delta = delta.compute()
         out = torch.empty((rows.numel(), self.size), dtype=self.act, device=resid.device)
         return ops.add_rmsnorm(resid, delta, self.weight, self.eps, out, rows=rows)
 

@@ -6,8 +6,13 @@ the wrong shape (the reference fails on the first missing name and on leftovers,
 crates/mrun-engine/src/load.rs:202-206, crates/mrun-engine/src/models/common.rs:433-438).
 
 Storage dtypes are kept: bfloat16 stays bfloat16, a tensor stored in 32-bit stays 32-bit, float16
-is widened to bfloat16's range by conversion, integer tables become int32.  A stored output head of
-a model with tied embeddings is dropped (crates/mrun-engine/src/models/common.rs:367-369).
+is widened to 32-bit (exactly; the run's precision decides later whether a matrix is narrowed to
+bfloat16, so a float16 checkpoint run in 32-bit computes with the stored values), integer tables
+become int32.  A stored output head of a model with tied embeddings is dropped
+(crates/mrun-engine/src/models/common.rs:367-369).  Tensors whose names the spec ignores (vision
+tower, multi-token-prediction heads, rotary frequency tables) are never read
+(crates/mrun-engine/src/load.rs:168-173); a part's optional tensors (a linear layer's ``.bias``)
+are bound when the checkpoint has them (crates/mrun-engine/src/load.rs:281).
 """
 from __future__ import annotations
 
@@ -33,13 +38,16 @@ class WeightsError(ValueError):
 
 def expected_tensors(spec: ModelSpec) -> List[TensorSpec]:
     """Every tensor the model binds, in a fixed order (embedding, head, layers, final norm)."""
-    from ..parts import ARRANGEMENTS, NORMS
+    from ..parts import ARRANGEMENTS, NORMS, TRANSFORMS
     out = [TensorSpec(spec.embedding_name, (spec.vocab_size, spec.hidden_size))]
     if not spec.tie_embeddings:
         out.append(TensorSpec(spec.head_name, (spec.vocab_size, spec.hidden_size)))
     for layer in spec.layers:
         out += ARRANGEMENTS.get(layer.arrangement).tensor_specs(layer)
     out += NORMS.tensor_specs(spec.final_norm, spec.final_norm_prefix)
+    for transform in (spec.embedding_transform, spec.logits_transform):
+        if transform is not None:
+            out += TRANSFORMS.tensor_specs(transform, getattr(transform, "prefix", ""))
     names = [t.name for t in out]
     if len(set(names)) != len(names):
         raise ValueError("two parts of the model bind the same tensor name")
@@ -50,7 +58,7 @@ def _keep_dtype(tensor: torch.Tensor) -> torch.Tensor:
     if tensor.dtype in (torch.bfloat16, torch.float32):
         return tensor
     if tensor.dtype == torch.float16:
-        return tensor.to(torch.bfloat16)
+        return tensor.to(torch.float32)
     if tensor.dtype == torch.float64:
         return tensor.to(torch.float32)
     if tensor.dtype in (torch.int64, torch.int16, torch.int8, torch.uint8, torch.int32):
@@ -67,16 +75,17 @@ def bind(spec: ModelSpec, available: Dict[str, object], where: str, fetch) -> Di
     missing, wrong = [], []
     for t in expected:
         if t.name not in available:
-            missing.append(t.name)
+            if not t.optional:
+                missing.append(t.name)
         elif tuple(available[t.name]) != tuple(t.shape):
             wrong.append(f"{t.name}: file {list(available[t.name])}, expected {list(t.shape)}")
     unexpected = sorted(
         n for n in available
-        if n not in names and not any(n.endswith(s) for s in spec.ignored_suffixes)
+        if n not in names and not spec.ignores(n)
         and not (spec.tie_embeddings and (n in dropped_head or n.startswith(head_stem))))
     if missing or unexpected or wrong:
         raise WeightsError(where, spec.architecture, missing, unexpected, wrong)
-    return {t.name: _keep_dtype(fetch(t.name)) for t in expected}
+    return {t.name: _keep_dtype(fetch(t.name)) for t in expected if t.name in available}
 
 
 def load_tensors(model_dir: str, spec: ModelSpec) -> Dict[str, torch.Tensor]:

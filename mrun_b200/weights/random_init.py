@@ -51,6 +51,8 @@ def random_tensors(spec: ModelSpec, seed: int, std: float = 0.02, norm_noise: fl
                    dtype: torch.dtype = torch.bfloat16, device: str = "cpu"
                    ) -> Iterator[Tuple[str, torch.Tensor]]:
     for t in expected_tensors(spec):
+        if t.optional:
+            continue
         yield t.name, random_tensor(t, seed, std, norm_noise, dtype, device)
 
 

@@ -92,15 +92,17 @@ def test_long_decoding_stays_on_the_plain_logits(tiny):
         ex.cache.check_invariants()
 
 
-def test_end_tokens_stop_requests_in_the_middle_of_pipelined_decoding(tiny):
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_end_tokens_stop_requests_in_the_middle_of_pipelined_decoding(tiny, dtype):
     """Decode steps are launched before the tokens of the step before them are read.  A request
     that samples an end token has then already been given a row in the next step: that row's
-    token must be dropped, the other requests must go on unchanged, and everything must be freed."""
+    token must be dropped, the other requests must go on unchanged, and everything must be freed.
+    The end token itself is not part of the output."""
     from mrun_b200 import Engine
     name, folder, settings = tiny
     cfg, weights = plain.load_folder(folder)
     prompts = [random_tokens(cfg["vocab_size"], n, seed=200 + n) for n in (6, 11, 19, 25, 3)]
-    engine = Engine.from_folder(folder, dtype="float32", page_size=settings["page_size"], context=1024,
+    engine = Engine.from_folder(folder, dtype=dtype, page_size=settings["page_size"], context=1024,
                                 max_batch_tokens=64, max_requests=8)
     free = engine.generate(prompts, max_tokens=40, ignore_eos=True)
     assert all(len(r.tokens) == 40 for r in free)
@@ -113,21 +115,54 @@ def test_end_tokens_stop_requests_in_the_middle_of_pipelined_decoding(tiny):
     engine.eos_token_ids = (eos,)
     stopped = engine.generate(prompts, max_tokens=40)
     reasons = set()
-    for before, after in zip(free, stopped):
-        if eos in before.tokens:
-            cut = before.tokens.index(eos) + 1
-            assert after.tokens == before.tokens[:cut] and after.finish_reason == ("stop" if cut <= 40 else "length")
-        else:
-            assert after.tokens == before.tokens and after.finish_reason == "length"
+    for prompt, before, after in zip(prompts, free, stopped):
+        assert eos not in after.tokens
+        if dtype == "float32":                      # 32-bit logits do not depend on the batch: the same tokens
+            if eos in before.tokens:
+                cut = before.tokens.index(eos)
+                assert after.tokens == before.tokens[:cut] and after.finish_reason == "stop"
+            else:
+                assert after.tokens == before.tokens and after.finish_reason == "length"
+        else:                                       # bfloat16: the plain tokens up to near-ties, the end token last
+            ended = [eos] if after.finish_reason == "stop" else []
+            plain_tokens_match(cfg, weights, prompt, after.tokens + ended, margin=0.05)
+            assert after.finish_reason == "stop" or len(after.tokens) == 40
         reasons.add(after.finish_reason)
     assert "stop" in reasons
     engine.executor.cache.check_invariants()
     assert not engine.executor.cache.live and engine.executor.cache.free_pages() == engine.executor.cache.num_pages
     # different output limits: each request leaves the pipeline at its own step
     limits = engine.generate(prompts[:3], max_tokens=7, ignore_eos=True) + engine.generate(prompts[3:], max_tokens=1, ignore_eos=True)
-    for before, after in zip(free, limits):
-        assert after.tokens == before.tokens[:len(after.tokens)] and after.finish_reason == "length"
+    for prompt, before, after in zip(prompts, free, limits):
+        if dtype == "float32":
+            assert after.tokens == before.tokens[:len(after.tokens)]
+        else:
+            plain_tokens_match(cfg, weights, prompt, after.tokens, margin=0.05)
+        assert after.finish_reason == "length"
     assert [len(r.tokens) for r in limits] == [7, 7, 7, 1, 1]
+
+
+def test_cancelling_one_request_leaves_the_others_as_they_were(tiny):
+    """``on_token`` returning False cancels that prompt in the middle of pipelined decoding: it
+    keeps what it had, the token in flight for it is dropped, and the other prompts' tokens are
+    those of an undisturbed run (crates/mrun-engine/tests/tiny_qwen3.rs:193-211)."""
+    from mrun_b200 import Engine
+    name, folder, settings = tiny
+    cfg, weights = plain.load_folder(folder)
+    prompts = [random_tokens(cfg["vocab_size"], n, seed=600 + n) for n in (14, 5, 30)]
+    engine = Engine.from_folder(folder, dtype="float32", page_size=settings["page_size"], context=512,
+                                max_batch_tokens=32, max_requests=4)
+    free = engine.generate(prompts, max_tokens=20, ignore_eos=True)
+    seen = []
+    def on_token(i, token):
+        seen.append((i, token))
+        return not (i == 1 and sum(1 for j, _ in seen if j == 1) == 6)
+    cut = engine.generate(prompts, max_tokens=20, ignore_eos=True, on_token=on_token)
+    assert cut[1].finish_reason == "cancelled" and cut[1].tokens == free[1].tokens[:6]
+    assert cut[0].tokens == free[0].tokens and cut[2].tokens == free[2].tokens
+    assert cut[0].finish_reason == cut[2].finish_reason == "length"
+    engine.executor.cache.check_invariants()
+    assert not engine.executor.cache.live and engine.executor.cache.free_pages() == engine.executor.cache.num_pages
 
 
 def test_repetition_penalty_and_filters_through_generate(tiny):

@@ -176,6 +176,113 @@ def test_gemm_skinny_gated_epilogue(m, inter, k):
     assert (act.float() - want).abs().max() <= 1.2e-2 * want.abs().max()
 
 
+@pytest.mark.parametrize("m", [1, 5, 8, 9, 16])
+@pytest.mark.parametrize("hidden,k,n_next", [(32, 64, 48), (96, 192, 200), (4096, 4096, 6144), (2560, 4096, 9728),
+                                             (5120, 1024, 64), (8192, 96, 32)])
+def test_gemm_skinny_with_the_residual_sum_and_the_norm_around_it(m, hidden, k, n_next):
+    """Three kernels as a decode step chains them: a product whose epilogue adds its result to
+    the 32-bit stream and leaves stream * norm weight with per-block sums of squares; the product
+    that reads those rows and applies rsqrt(mean + eps) to its own sums; and the same rows
+    finished into plain RMSNorm output.  Against x + a W1^T, rmsnorm, · W2^T in 64-bit."""
+    o = ops()
+    eps = 1e-5
+    a = rnd(m, k, dtype=torch.bfloat16, seed=30)
+    w1 = rnd(hidden, k, dtype=torch.bfloat16, seed=31, scale=0.05)
+    w2 = rnd(n_next, hidden, dtype=torch.bfloat16, seed=32, scale=0.05)
+    norm_w = 1 + 0.1 * rnd(hidden, seed=33)
+    stream = rnd(m, hidden, seed=34, scale=3.0)                        # far from unit scale on purpose
+    want_stream = stream.double() + a.double() @ w1.double().T
+    normed = want_stream * torch.rsqrt((want_stream ** 2).mean(-1, keepdim=True) + eps) * norm_w.double()
+    want = normed @ w2.double().T
+
+    got_stream = stream.clone()
+    rows = o.linear_into_norm(o.PendingLinear(a, w1), got_stream, norm_w, eps)
+    assert (got_stream.double() - want_stream).abs().max() <= 2e-5 * want_stream.abs().max()
+    assert rows.partials.shape == (-(-hidden // 16), 16)
+    sums = rows.partials[:, :m].double().sum(0)
+    assert ((sums - (want_stream ** 2).sum(-1)).abs() <= 1e-4 * sums).all()
+    finished = rows.finish()
+    assert (finished.double() - normed).abs().max() <= 1.2e-2 * normed.abs().max()       # rounded to bfloat16 twice
+    for out_dtype, tol in ((torch.float32, 8e-3), (torch.bfloat16, 1.2e-2)):
+        got = o.gemm_skinny(rows, w2, out_dtype=out_dtype)
+        assert (got.double() - want).abs().max() <= tol * want.abs().max()
+    # a row's result depends neither on the other rows nor on how many there are
+    alone_stream = stream[m // 2:m // 2 + 1].clone()
+    alone = o.linear_into_norm(o.PendingLinear(a[m // 2:m // 2 + 1], w1), alone_stream, norm_w, eps)
+    assert torch.equal(alone_stream[0], got_stream[m // 2])
+    assert torch.equal(o.gemm_skinny(alone, w2, out_dtype=torch.float32)[0],
+                       o.gemm_skinny(rows, w2, out_dtype=torch.float32)[m // 2])
+    # chained: the next product's x may itself carry a pending scale
+    w3 = rnd(hidden, hidden, dtype=torch.bfloat16, seed=35, scale=0.05)
+    again = got_stream.clone()
+    o.linear_into_norm(o.PendingLinear(rows, w3), again, norm_w, eps)
+    want_again = want_stream + normed @ w3.double().T
+    assert (again.double() - want_again).abs().max() <= 8e-3 * want_again.abs().max()
+    # the gated epilogue applies the scale before the activation
+    if n_next % 16 == 0:
+        inter = n_next // 2
+        gate, up = w2[:inter], w2[inter:]
+        stacked = torch.stack([gate.reshape(-1, 8, hidden), up.reshape(-1, 8, hidden)], dim=1).reshape(n_next, hidden).contiguous()
+        g, u = normed @ gate.double().T, normed @ up.double().T
+        want_act = g * torch.sigmoid(g) * u
+        got_act = o.gemm_skinny(rows, stacked, swiglu_rows=True)
+        assert (got_act.double() - want_act).abs().max() <= 2e-2 * want_act.abs().max()
+
+
+def test_norm_fusion_is_refused_where_it_does_not_fit():
+    o = ops()
+    a, w1 = rnd(20, 64, dtype=torch.bfloat16), rnd(64, 64, dtype=torch.bfloat16)
+    assert not o.norm_fusable(o.PendingLinear(a, w1), rnd(20, 64), rnd(64))              # more than 16 rows
+    a = rnd(4, 64, dtype=torch.bfloat16)
+    assert o.norm_fusable(o.PendingLinear(a, w1), rnd(4, 64), rnd(64))
+    assert not o.norm_fusable(o.PendingLinear(a, rnd(48, 64, dtype=torch.bfloat16)), rnd(4, 48), rnd(48))   # width % 32
+    assert not o.norm_fusable(a, rnd(4, 64), rnd(64))                                     # a plain tensor is no pending product
+    wide = rnd(16416, 64, dtype=torch.bfloat16)
+    assert not o.norm_fusable(o.PendingLinear(a, wide), rnd(4, 16416), rnd(16416))        # wider than the kernel's sums
+    assert torch.equal(o.PendingLinear(a, w1).compute(), o.linear(a, w1))
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("tokens,inter", [(1, 8), (5, 200), (3, 1001)])
+def test_gate_functions(dtype, tokens, inter):
+    """The gate's function is a code of the kernels: SiLU and tanh-GELU, stand-alone and in the
+    decode GEMM's epilogue; an unknown name is refused."""
+    o = ops()
+    gate_up = rnd(tokens, 2 * inter, dtype=dtype, seed=9, scale=2.0)
+    g, u = gate_up[:, :inter].double(), gate_up[:, inter:].double()
+    want = {"silu": g * torch.sigmoid(g) * u,
+            "gelu_tanh": 0.5 * g * (1 + torch.tanh(math.sqrt(2 / math.pi) * (g + 0.044715 * g ** 3))) * u}
+    tol = 2e-6 if dtype == torch.float32 else 8e-3
+    for name, expected in want.items():
+        out = torch.empty((tokens, inter), dtype=dtype, device=DEV)
+        o.swiglu(gate_up, out, activation=name)
+        assert (out.double() - expected).abs().max() <= tol * expected.abs().max(), name
+    with pytest.raises(o.KernelError, match="gate function"):
+        o.swiglu(gate_up, torch.empty((tokens, inter), dtype=dtype, device=DEV), activation="relu6")
+    if dtype == torch.bfloat16 and inter % 8 == 0:
+        k = 96
+        x = rnd(tokens, k, dtype=dtype, seed=1)
+        wg, wu = rnd(inter, k, dtype=dtype, seed=2, scale=0.1), rnd(inter, k, dtype=dtype, seed=3, scale=0.1)
+        stacked = torch.stack([wg.view(-1, 8, k), wu.view(-1, 8, k)], dim=1).reshape(2 * inter, k).contiguous()
+        g = (x.float() @ wg.float().T).bfloat16().double()
+        u = (x.float() @ wu.float().T).bfloat16().double()
+        expected = 0.5 * g * (1 + torch.tanh(math.sqrt(2 / math.pi) * (g + 0.044715 * g ** 3))) * u
+        got = o.gemm_skinny(x, stacked, swiglu_rows=True, activation="gelu_tanh")
+        assert (got.double() - expected).abs().max() <= 1.2e-2 * expected.abs().max()
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_linear_with_a_bias(dtype):
+    o = ops()
+    for m, n, k in ((3, 40, 64), (40, 509, 96)):
+        x, w = rnd(m, k, dtype=dtype, seed=1), rnd(n, k, dtype=dtype, seed=2, scale=0.1)
+        bias = rnd(n, seed=3)
+        want = x.double() @ w.double().T + bias.double()
+        got = o.linear(x, w, bias=bias)
+        tol = 2e-6 * math.sqrt(k) if dtype == torch.float32 else 1.2e-2
+        assert got.dtype == dtype and (got.double() - want).abs().max() <= tol * want.abs().max()
+
+
 @pytest.mark.parametrize("m", [1, 17, 32, 33, 64, 100, 128, 200, 256])
 @pytest.mark.parametrize("n,k,blocks", [(128, 64, 1), (509, 192, 5), (6144, 4096, 148), (4096, 12288, 148), (1000, 2560, 7),
                                         (24576, 4096, 148), (130, 128, 3), (4096, 4096, 1000), (2000, 1024, 11)])

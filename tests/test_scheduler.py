@@ -115,13 +115,46 @@ def test_finishing_reasons_and_eos():
     s.submit(stop)
     s.submit(ignore)
     drive(s, next_token=lambda r: 7 if len(r.output) == 2 else 9)
-    assert stop.finish_reason == "stop" and stop.output == [9, 9, 7]
+    # the end token is not part of the output (crates/mrun/src/runtime/generate.rs:868-874)
+    assert stop.finish_reason == "stop" and stop.output == [9, 9]
     assert ignore.finish_reason == "length" and ignore.output == [9, 9, 7, 9, 9]
     s = Scheduler(cache(pages=512), max_batch_tokens=8)
     loop = Request("loop", [1], max_tokens=2000)
     s.submit(loop)
     drive(s, next_token=lambda r: len(r.output) % 5)
     assert loop.finish_reason == "repetition" and len(loop.output) == 512
+    # a run of a forced length goes to its limit however it repeats
+    # (crates/mrun/src/runtime/generate.rs:908-913)
+    s = Scheduler(cache(pages=512), max_batch_tokens=8)
+    forced = Request("forced", [1], max_tokens=700, ignore_eos=True)
+    s.submit(forced)
+    drive(s, next_token=lambda r: len(r.output) % 5)
+    assert forced.finish_reason == "length" and len(forced.output) == 700
+
+
+def test_cancelling_from_the_token_callback_and_from_outside():
+    """on_token returning False ends that request at once with what it has; the others go on
+    (crates/mrun-engine/src/engine.rs:463-479, crates/mrun-engine/tests/tiny_qwen3.rs:193-211)."""
+    s = Scheduler(cache(pages=64), max_batch_tokens=16)
+    seen = []
+    def stop_after_three(request, token):
+        seen.append(token)
+        return len(request.output) < 3
+    a = Request("a", [1, 2, 3], max_tokens=20, on_token=stop_after_three)
+    b = Request("b", [4, 5], max_tokens=6, on_token=lambda r, t: None)         # None is no cancellation
+    c = Request("c", [6], max_tokens=20)
+    for r in (a, b, c):
+        s.submit(r)
+    def tokens(r):
+        if r is c and len(c.output) == 4:
+            c.cancel_requested = True                     # asked from outside: it ends with its next token
+        return 100 + len(r.output)
+    drive(s, next_token=tokens)
+    assert a.finish_reason == "cancelled" and a.output == [100, 101, 102] and seen == a.output
+    assert b.finish_reason == "length" and b.output == [100 + i for i in range(6)]
+    assert c.finish_reason == "cancelled" and c.output == [100 + i for i in range(5)]
+    assert s.cache.free_pages() == 64 and s.cache.free_slots == 4
+    s.cache.check_invariants()
 
 
 def test_out_of_pages_preempts_the_newest_and_recomputes():
@@ -193,12 +226,12 @@ def test_steps_in_flight():
     assert sorted((e.request.request_id, e.from_device) for e in second.entries) == [("a", True), ("b", True)]
     assert a.inflight == 2 and a.remaining == 1          # the second unread token is still to be fed
     read(first, {"a": 9, "b": 7})                    # b sampled an end token: it is in the second step already
-    assert b.finish_reason == "stop" and b.retiring and b.cache is not None and b.output == [7]
+    assert b.finish_reason == "stop" and b.retiring and b.cache is not None and b.output == []
     third = launch()                                   # a's third token will be its last: one more row, b is gone
     assert [e.request.request_id for e in third.entries] == ["a"]
     assert not s.has_work() and s.unsettled()          # nothing more to plan, tokens still on the way
     read(second, {"a": 9, "b": 1})                   # b's token is dropped and b gives its pages back
-    assert b.output == [7] and b.cache is None and not b.retiring
+    assert b.output == [] and b.cache is None and not b.retiring
     read(third, {"a": 9})
     assert a.finish_reason == "length" and a.output == [9, 9, 9] and not s.unsettled()
     assert s.cache.free_pages() == 64 and s.cache.free_slots == 4
@@ -264,6 +297,7 @@ def test_native_end_reason_and_victim():
     loop = native.int_array([4, 9] * 256)
     assert core.mrun_sched_end_reason(0, 0, 512, 9999, loop, 512) == 3
     assert core.mrun_sched_end_reason(0, 0, 513, 9999, loop, 512) == 0          # not a multiple of the interval
+    assert core.mrun_sched_end_reason(0, 1, 512, 9999, loop, 512) == 0          # the guard is off with ignore_eos
     assert core.mrun_sched_preemption_victim(3, native.int_array([0, 0, 0]), native.long_array([5, 9, 2])) == 1
     assert core.mrun_sched_preemption_victim(3, native.int_array([0, 1, 0]), native.long_array([5, 9, 2])) == 0
     assert core.mrun_sched_preemption_victim(2, native.int_array([0, 1]), native.long_array([5, 9])) == -1

@@ -28,7 +28,7 @@ def test_names_and_shapes_follow_the_reference():
     assert shapes[f"{p}.mlp.gate_proj.weight"] == (200, 96) == shapes[f"{p}.mlp.up_proj.weight"]
     assert shapes[f"{p}.mlp.down_proj.weight"] == (96, 200)
     assert shapes[f"{p}.input_layernorm.weight"] == (96,) == shapes[f"{p}.post_attention_layernorm.weight"]
-    assert len(shapes) == 2 + 1 + 3 * 11
+    assert len([n for n in shapes if not n.endswith('.bias')]) == 2 + 1 + 3 * 11
     tied = {t.name for t in expected_tensors(tiny_config("A").to_spec())}
     assert "lm_head.weight" not in tied
 
@@ -38,13 +38,13 @@ def test_one_error_lists_missing_unexpected_and_wrong_shapes():
     tensors = dict(random_tensors(spec, seed=1))
     del tensors["model.layers.1.mlp.up_proj.weight"]
     del tensors["model.norm.weight"]
-    tensors["model.layers.0.self_attn.q_proj.bias"] = torch.zeros(192)
+    tensors["model.layers.0.self_attn.q_proj.scales"] = torch.zeros(192)
     tensors["model.layers.0.self_attn.o_proj.weight"] = torch.zeros(96, 100)
     with pytest.raises(WeightsError) as error:
         bind_tensors(spec, tensors, "a test")
     e = error.value
     assert e.missing == ["model.layers.1.mlp.up_proj.weight", "model.norm.weight"]
-    assert e.unexpected == ["model.layers.0.self_attn.q_proj.bias"]
+    assert e.unexpected == ["model.layers.0.self_attn.q_proj.scales"]
     assert len(e.wrong_shape) == 1 and "o_proj" in e.wrong_shape[0] and "[96, 100]" in e.wrong_shape[0]
     text = str(e)
     assert "missing (2)" in text and "unexpected (1)" in text and "wrong shape (1)" in text and "a test" in text
@@ -57,8 +57,48 @@ def test_dropped_and_ignored_tensors():
     tensors = dict(random_tensors(spec, seed=2))
     tensors["lm_head.weight"] = torch.zeros(256, 64)
     tensors["model.layers.0.self_attn.rotary_emb.inv_freq"] = torch.zeros(8)
+    # the vision tower and heads for multi-token prediction, too (crates/mrun-engine/src/load.rs:168-173)
+    tensors["vision_tower.blocks.0.attn.qkv.weight"] = torch.zeros(3, 3)
+    tensors["model.visual.merger.weight"] = torch.zeros(2)
+    tensors["model.layers.1.mtp.proj.weight"] = torch.zeros(4, 4)
     bound = bind_tensors(spec, tensors)
-    assert "lm_head.weight" not in bound and len(bound) == len(expected_tensors(spec))
+    required = [t for t in expected_tensors(spec) if not t.optional]
+    assert "lm_head.weight" not in bound and sorted(bound) == sorted(t.name for t in required)
+
+
+def test_ignored_tensors_are_never_read(tmp_path):
+    spec = tiny_config("A").to_spec()
+    tensors = dict(random_tensors(spec, seed=2))
+    tensors["vision_tower.huge.weight"] = torch.zeros(5, 5)
+    write_safetensors(str(tmp_path / "model.safetensors"), tensors.items())
+    read = []
+    original = SafetensorsFile.tensor
+    def spy(self, name):
+        read.append(name)
+        return original(self, name)
+    SafetensorsFile.tensor = spy
+    try:
+        load_tensors(str(tmp_path), spec)
+    finally:
+        SafetensorsFile.tensor = original
+    assert "vision_tower.huge.weight" not in read and "model.norm.weight" in read
+
+
+def test_an_optional_bias_is_bound_when_the_file_has_it():
+    """crates/mrun-engine/src/load.rs:281: a linear layer takes ``<path>.bias`` if it is there."""
+    spec = tiny_config("B").to_spec()
+    tensors = dict(random_tensors(spec, seed=1))
+    assert not any(name.endswith(".bias") for name in tensors)            # the random mode makes none
+    assert not any(name.endswith(".bias") for name in bind_tensors(spec, tensors))
+    tensors["model.layers.0.self_attn.q_proj.bias"] = torch.zeros(192)
+    tensors["model.layers.2.mlp.down_proj.bias"] = torch.ones(96)
+    bound = bind_tensors(spec, tensors)
+    assert torch.equal(bound["model.layers.2.mlp.down_proj.bias"], torch.ones(96))
+    assert "model.layers.0.self_attn.q_proj.bias" in bound and "model.layers.0.self_attn.k_proj.bias" not in bound
+    tensors["model.layers.0.self_attn.q_proj.bias"] = torch.zeros(191)
+    with pytest.raises(WeightsError) as error:
+        bind_tensors(spec, tensors)
+    assert "q_proj.bias" in error.value.wrong_shape[0] and not error.value.missing
 
 
 def test_storage_dtypes_are_kept(tmp_path):
@@ -71,7 +111,9 @@ def test_storage_dtypes_are_kept(tmp_path):
     write_safetensors(str(tmp_path / "model.safetensors"), tensors.items())
     loaded = load_tensors(str(tmp_path), spec)
     assert loaded[name32].dtype == torch.float32                 # stored in 32-bit, stays so
-    assert loaded[name16].dtype == torch.bfloat16                # half precision is kept as bfloat16
+    # float16 is widened to 32-bit, exactly: a 32-bit run computes with the stored values, a
+    # bfloat16 run narrows the matrix when it goes to the device
+    assert loaded[name16].dtype == torch.float32 and torch.equal(loaded[name16], tensors[name16].float())
     assert loaded["model.embed_tokens.weight"].dtype == torch.bfloat16
     assert torch.equal(loaded["model.embed_tokens.weight"], tensors["model.embed_tokens.weight"])
 
