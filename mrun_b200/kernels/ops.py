@@ -410,7 +410,10 @@ def linear(x, w: torch.Tensor, out_dtype: Optional[torch.dtype] = None,
     :class:`NormedRows`).  bfloat16 otherwise (prefill): the vendor GEMM library with 32-bit
     accumulation (the reference calls its array library's matmul for the same products and adds
     an optional bias after it, crates/mrun-engine/src/load.rs:294-306)."""
-    if isinstance(x, NormedRows) and not skinny_ok(x, w):
+    if isinstance(x, NormedRows):
+        if skinny_ok(x, w):
+            y = gemm_skinny(x, w, out_dtype or torch.bfloat16)
+            return y if bias is None else add_bias(y, bias)
         x = x.finish()
     if x.dtype == torch.float32:
         y = gemm_f32_nt(x, w)

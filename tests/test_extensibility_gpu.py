@@ -355,3 +355,167 @@ def test_toy_model_with_a_routed_feed_forward(dtype, tolerance):
     for request in live.values():
         ex.release(request)
     ex.cache.check_invariants()
+
+
+# ------------------------------------------------------------------ hooks of the model, biases, another gate function
+
+@dataclass(frozen=True)
+class ScaleSpec:
+    """x * factor (a scale of the embedding)."""
+    kind: ClassVar[str] = "toy_scale"
+    factor: float
+
+
+@dataclass(frozen=True)
+class SoftCapSpec:
+    """cap * tanh(x / cap) + bias (a soft cap and a bias of the logits; the bias is a checkpoint tensor)."""
+    kind: ClassVar[str] = "toy_soft_cap"
+    cap: float
+    size: int
+    prefix: str = "logits_cap"
+
+
+@dataclass(frozen=True)
+class TokenLinearSpec:
+    """y = x W^T, token by token: a mixer without a cache that knows nothing of pending products."""
+    kind: ClassVar[str] = "toy_token_linear"
+    hidden: int
+
+
+def register_hooks():
+    from mrun_b200.config import TensorSpec
+    from mrun_b200.parts import TRANSFORMS, register_mixer, register_transform
+    if "toy_scale" in TRANSFORMS.kinds():
+        return
+
+    @register_transform("toy_scale")
+    class Scale:
+        @staticmethod
+        def tensor_specs(spec, prefix):
+            return []
+
+        def __init__(self, spec, tensors, runtime):
+            self.factor = spec.factor
+
+        def forward(self, x):
+            return x.mul_(self.factor)
+
+    @register_transform("toy_soft_cap")
+    class SoftCap:
+        @staticmethod
+        def tensor_specs(spec, prefix):
+            return [TensorSpec(f"{prefix}.bias", (spec.size,))]
+
+        def __init__(self, spec, tensors, runtime):
+            self.cap = spec.cap
+            self.bias = tensors["bias"].to(runtime.device, torch.float32)
+
+        def forward(self, logits):
+            return torch.tanh(logits / self.cap) * self.cap + self.bias
+
+    @register_mixer("toy_token_linear")
+    class TokenLinear:
+        graph_safe = True
+
+        @staticmethod
+        def tensor_specs(spec, prefix):
+            return [TensorSpec(f"{prefix}.proj.weight", (spec.hidden, spec.hidden))]
+
+        def __init__(self, spec, tensors, runtime):
+            self.weight = runtime.matrix(tensors["proj.weight"])
+
+        def cache_need(self):
+            return None
+
+        def forward(self, x, ctx, cache):
+            assert isinstance(x, torch.Tensor)            # normed rows are finished for a part like this one
+            return (x.float() @ self.weight.float().T).to(x.dtype)
+
+
+@pytest.mark.parametrize("dtype,tolerance", [("float32", 3e-5), ("bfloat16", 4e-2)])
+def test_model_hooks_biases_and_another_gate_function(dtype, tolerance):
+    """An embedding scale and a logit soft cap with a bias as transforms of the model spec, linear
+    layers with biases in the checkpoint, a tanh-GELU gate, and a toy mixer between product norms
+    (it gets plain tensors where a product part would get rows with a pending scale): nothing of
+    it edits the framework.  Whole, in portions, and token by token through the captured step."""
+    import math
+    from mrun_b200.config import (AttentionSpec, GatedMLPSpec, LayerSpec, ModelSpec, RMSNormSpec, RotarySpec)
+    from mrun_b200.engine import Executor, StepEntry
+    from mrun_b200.weights import bind_tensors, random_tensors
+    register_hooks()
+    hidden, heads, kv_heads, head_dim, inter, vocab, eps, theta = 64, 4, 2, 32, 96, 211, 1e-5, 1e4
+    norm = RMSNormSpec(hidden, eps)
+    mlp = GatedMLPSpec(hidden, inter, activation="gelu_tanh")
+    attn = AttentionSpec(hidden, heads, kv_heads, head_dim, head_dim ** -0.5, RMSNormSpec(head_dim, eps),
+                         RotarySpec(head_dim, head_dim, theta), None)
+    layers = (LayerSpec("model.layers.0", attn, mlp, norm, norm),
+              LayerSpec("model.layers.1", TokenLinearSpec(hidden), mlp, norm, norm, mixer_prefix="mix"),
+              LayerSpec("model.layers.2", attn, mlp, norm, norm))
+    spec = ModelSpec("ToyHooksForCausalLM", vocab, hidden, 512, layers, norm, tie_embeddings=True,
+                     embedding_transform=ScaleSpec(math.sqrt(hidden)), logits_transform=SoftCapSpec(4.0, vocab))
+    tensors = dict(random_tensors(spec, seed=5, std=0.08, norm_noise=0.1))
+    assert "logits_cap.bias" in tensors and not any(n.endswith("proj.bias") for n in tensors)
+    gen = torch.Generator().manual_seed(2)
+    bias = lambda n: (torch.randn(n, generator=gen) * 0.3).to(torch.bfloat16)
+    for i in (0, 2):
+        p = f"model.layers.{i}"
+        tensors[f"{p}.self_attn.q_proj.bias"] = bias(heads * head_dim)
+        tensors[f"{p}.self_attn.v_proj.bias"] = bias(kv_heads * head_dim)
+        tensors[f"{p}.self_attn.o_proj.bias"] = bias(hidden)
+        tensors[f"{p}.mlp.up_proj.bias"] = bias(inter)
+    tensors["model.layers.1.mlp.down_proj.bias"] = bias(hidden)
+    tensors = bind_tensors(spec, tensors)
+    w = {k: v.float() for k, v in tensors.items()}
+
+    def plain_model(tokens):
+        positions = torch.arange(len(tokens))
+        x = w["model.embed_tokens.weight"][torch.tensor(tokens)] * math.sqrt(hidden)
+        n = lambda t, name: plain.rms_norm(t, w[name], eps)
+        b = lambda name, size: w.get(name, torch.zeros(size))
+        for i in range(3):
+            p = f"model.layers.{i}"
+            h = n(x, f"{p}.input_layernorm.weight")
+            if i == 1:
+                a = h @ w[f"{p}.mix.proj.weight"].T
+            else:
+                q = (h @ w[f"{p}.self_attn.q_proj.weight"].T + b(f"{p}.self_attn.q_proj.bias", 1)).view(-1, heads, head_dim)
+                k = (h @ w[f"{p}.self_attn.k_proj.weight"].T).view(-1, kv_heads, head_dim)
+                v = (h @ w[f"{p}.self_attn.v_proj.weight"].T + b(f"{p}.self_attn.v_proj.bias", 1)).view(-1, kv_heads, head_dim)
+                q = plain.rope(plain.rms_norm(q, w[f"{p}.self_attn.q_norm.weight"], eps), positions, theta)
+                k = plain.rope(plain.rms_norm(k, w[f"{p}.self_attn.k_norm.weight"], eps), positions, theta)
+                o = plain.attention_scores_softmax_values(q, k, v, head_dim ** -0.5, positions, None)
+                a = o.reshape(-1, heads * head_dim) @ w[f"{p}.self_attn.o_proj.weight"].T + b(f"{p}.self_attn.o_proj.bias", 1)
+            x = x + a
+            h = n(x, f"{p}.post_attention_layernorm.weight")
+            g = h @ w[f"{p}.mlp.gate_proj.weight"].T
+            u = h @ w[f"{p}.mlp.up_proj.weight"].T + b(f"{p}.mlp.up_proj.bias", 1)
+            act = 0.5 * g * (1 + torch.tanh(math.sqrt(2 / math.pi) * (g + 0.044715 * g ** 3))) * u
+            x = x + act @ w[f"{p}.mlp.down_proj.weight"].T + b(f"{p}.mlp.down_proj.bias", 1)
+        logits = n(x, "model.norm.weight") @ w["model.embed_tokens.weight"].T
+        return torch.tanh(logits / 4.0) * 4.0 + w["logits_cap.bias"]
+
+    ex = Executor(spec, tensors, dtype=dtype, page_size=8, num_pages=64, max_requests=4)
+    assert ex.model.graph_safe
+    tokens = torch.randint(0, vocab, (70,), generator=gen).tolist()
+    want = plain_model(tokens)
+    scale = float(want.abs().max())
+
+    def check(start, logits):
+        got = logits.float().cpu()
+        error = float((got - want[start:start + got.shape[0]]).abs().max()) / scale
+        assert error <= tolerance, (dtype, start, error)
+
+    r = ex.admit("whole")
+    check(0, ex.step([StepEntry(r, tokens, range(70))]))
+    ex.release(r)
+    r = ex.admit("portions")
+    at = 0
+    for n_tokens in (33, 2, 9, 1, 1, 5):                      # 33 rows: the vendor GEMM; the rest: the decode GEMM
+        check(at, ex.step([StepEntry(r, tokens[at:at + n_tokens], range(n_tokens))]))
+        at += n_tokens
+    for i in range(at, 70):                                   # the captured step
+        entries = [StepEntry(r, [tokens[i]], [0])]
+        ex.decode_step(entries)
+        check(i, ex.decode_logits(entries))
+    ex.release(r)
+    ex.cache.check_invariants()

@@ -1,8 +1,12 @@
 """The tiny configurations the tests run on.  They differ in every size and option: head counts and
 groups, sizes that are no power of two, number of layers, vocabulary, the norms' eps, rope base,
 tied or untied head, norm weights, page size.  A and B have small heads (the mma.sync attention
-kernels), C has heads of 64 (the TMA and tcgen05 attention kernels), D sizes that are no
-multiple of 8."""
+kernels), C has heads of 64 and E heads of 128 (the TMA and tcgen05 attention kernels), D sizes
+that are no multiple of 8.
+
+The weights' standard deviations (0.06 to 0.08) are larger than the 0.02 of the measured shapes: at
+widths of 64 to 256 that keeps the logits a few units wide, so that an error in a single head or
+layer shows against the tolerance, which is relative to the largest logit of the configuration."""
 from __future__ import annotations
 
 import numpy as np
@@ -31,6 +35,13 @@ TINY = {
                     head_dim=48, intermediate_size=150, vocab_size=301, max_position_embeddings=1024,
                     rms_norm_eps=2e-5, rope_theta=50000.0, tie_word_embeddings=True),
         seed=41, std=0.08, norm_noise=0.1, page_size=4),
+    # heads of 128, twice the width in heads (heads x head size != width): the head size of the
+    # measured shapes, with its three-stage TMA ring and the tcgen05 tiles of 128
+    "E": dict(
+        config=dict(num_hidden_layers=2, hidden_size=256, num_attention_heads=4, num_key_value_heads=2,
+                    head_dim=128, intermediate_size=384, vocab_size=411, max_position_embeddings=2048,
+                    rms_norm_eps=1e-6, rope_theta=1000000.0, tie_word_embeddings=False),
+        seed=53, std=0.06, norm_noise=0.1, page_size=16),
 }
 
 

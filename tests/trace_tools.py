@@ -17,11 +17,12 @@ Where = List[Tuple[int, int, str, int]]
 
 
 class TraceRunner:
-    def __init__(self, model_dir: str, dtype: str, out_dir: str, max_tokens: int, page_size: int):
+    def __init__(self, model_dir: str, dtype: str, out_dir: str, max_tokens: int, page_size: int,
+                 max_requests: int = 8):
         self.out_dir = out_dir
         self.proc = subprocess.Popen(
             [sys.executable, TRACE_RUN, "--model", model_dir, "--dtype", dtype, "--out", out_dir,
-             "--max-tokens", str(max_tokens), "--page-size", str(page_size)],
+             "--max-tokens", str(max_tokens), "--page-size", str(page_size), "--max-requests", str(max_requests)],
             stdin=subprocess.PIPE, stdout=subprocess.PIPE, text=True)
 
     def run(self, steps: Sequence[dict]) -> None:
