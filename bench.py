@@ -123,10 +123,11 @@ def fill_requests(executor, batch: int, context: int, vocab: int, tag: str):
     return requests
 
 
-def time_decode(executor, requests, vocab: int, steps: int, warmup: int, profiler_range: bool = False):
-    """Device time of ``steps`` decode steps the way generation runs them: a step is launched
-    with the tokens of the step before it taken on the device, then that step's tokens are read
-    back into pinned host memory."""
+def time_decode(executor, requests, vocab: int, steps: int, warmup: int, profiler_range: bool = False,
+                repeats: int = 1):
+    """Device times (ms, one per repeat) of ``steps`` decode steps the way generation runs them: a
+    step is launched with the tokens of the step before it taken on the device, then that step's
+    tokens are read back into pinned host memory.  Also the kernel launches of one repeat."""
     import torch
     from mrun_b200.engine import StepEntry
     n = len(requests)
@@ -149,19 +150,23 @@ def time_decode(executor, requests, vocab: int, steps: int, warmup: int, profile
     one(True)
     for _ in range(warmup - 1):
         one(False)
-    torch.cuda.synchronize()
-    begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    launches = executor.launches.total
-    if profiler_range:                   # lets a profiler started with --profile-from-start off see only this
-        torch.cuda.profiler.start()
-    begin.record()
-    for _ in range(steps):
-        one(False)
-    end.record()
-    torch.cuda.synchronize()
-    if profiler_range:
-        torch.cuda.profiler.stop()
-    return begin.elapsed_time(end), executor.launches.total - launches
+    times, launches = [], 0
+    for repeat in range(repeats):
+        torch.cuda.synchronize()
+        begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        before = executor.launches.total
+        if profiler_range and repeat == 0:   # lets a profiler started with --profile-from-start off see only this
+            torch.cuda.profiler.start()
+        begin.record()
+        for _ in range(steps):
+            one(False)
+        end.record()
+        torch.cuda.synchronize()
+        if profiler_range and repeat == 0:
+            torch.cuda.profiler.stop()
+        times.append(begin.elapsed_time(end))
+        launches = executor.launches.total - before
+    return times, launches
 
 
 def serve(args, config, model_name: str, full_layers: int, page_size: int, peaks: dict) -> int:
@@ -244,6 +249,9 @@ def main() -> int:
     parser.add_argument("--prefill-depth", type=int, default=0,
                         help="tokens already in the cache before the timed portion of 2,048 (0: a fresh prompt)")
     parser.add_argument("--skip-e2e", action="store_true")
+    parser.add_argument("--repeats", type=int, default=5,
+                        help="how many times the K timed steps are run (the line carries the median, the "
+                             "fastest and the slowest)")
     parser.add_argument("--profiler-range", nargs="?", const="decode", default=None, choices=["decode", "prefill"],
                         help="bracket the timed decode steps (or the last timed prefill) with "
                              "cudaProfilerStart/Stop, for a profiler started with --profile-from-start off")
@@ -282,7 +290,8 @@ def main() -> int:
     batches = [8] if args.skip_points else [8, 1, 32 if args.shape == "32b" else 64]
     if args.batches:
         batches = [int(b) for b in args.batches.split(",")]
-    slack = args.steps + args.warmup + 64
+    args.repeats = max(1, args.repeats)
+    slack = args.repeats * args.steps + args.warmup + 64
     context = args.context
     # the requests of every batch size are alive together, so that the clocks can be sampled over all of them
     capacity = max(sum(batches) * (context + slack), 8 * (context + 2 * slack)) + args.prefill_depth + PREFILL_TOKENS + 4 * 64
@@ -295,7 +304,10 @@ def main() -> int:
     executor = engine.executor
     vocab = config.vocab_size
     kv_bytes = config.kv_bytes_per_token(2)
-    weight_bytes = executor.model.weight_bytes() - vocab * config.hidden_size * 2  # embedding rows: B rows only
+    # every weight the step uses, once; of an embedding table that is not also the head only B rows
+    weight_bytes = executor.model.weight_bytes()
+    if not config.tie_word_embeddings:
+        weight_bytes -= vocab * config.hidden_size * 2
 
     # ---------------------------------------------------------------- prefill, 2,048 tokens
     from mrun_b200.engine import StepEntry
@@ -330,6 +342,8 @@ def main() -> int:
     prefill = {"value": round(PREFILL_TOKENS / prefill_ms * 1e3, 1), "tokens": PREFILL_TOKENS,
                "ms": round(prefill_ms, 3), **({"depth": args.prefill_depth} if args.prefill_depth else {}),
                "frac": round(prefill_flops / (prefill_ms * 1e-3) / (peaks["bf16_tflops"] * 1e12), 4)}
+    if "bf16_tflops_sustained" in peaks:
+        prefill["frac_sustained"] = round(prefill_flops / (prefill_ms * 1e-3) / (peaks["bf16_tflops_sustained"] * 1e12), 4)
 
     # ---------------------------------------------------------------- decode at batch 8 / 1 / 64
     results = {}
@@ -338,29 +352,44 @@ def main() -> int:
     sampler = ClockSampler()             # clocks and throttle reasons over every timed decode region
     sampler.start()
     for batch in batches:
-        ms, n_launch = time_decode(executor, all_requests[batch], vocab, args.steps, args.warmup,
-                                   args.profiler_range == "decode")
+        times, n_launch = time_decode(executor, all_requests[batch], vocab, args.steps, args.warmup,
+                                      args.profiler_range == "decode", args.repeats)
         if batch == batches[0]:
             launches = n_launch
-        results[batch] = ms
+        results[batch] = times
     clocks = sampler.stop()
     for requests in all_requests.values():
         for r in requests:
             executor.release(r)
     main_batch = batches[0]
-    ms_per_step = results[main_batch] / args.steps
-    value = main_batch * args.steps / (results[main_batch] * 1e-3)
-    context_mid = context + args.warmup + args.steps / 2.0
-    step_bytes = weight_bytes + main_batch * context_mid * kv_bytes + main_batch * h * 2
-    achieved = step_bytes / (ms_per_step * 1e-3) / 1e9
-    roofline = {"bound": "hbm", "achieved": round(achieved, 1), "peak": peaks["hbm_gbs"], "unit": "GB/s",
-                "frac": round(achieved / peaks["hbm_gbs"], 4), "of": peaks["source"]}
-    points = {f"decode_b{b}": round(b * args.steps / (results[b] * 1e-3), 1) for b in batches if b != main_batch}
+    context_mid = context + args.warmup + args.repeats * args.steps / 2.0
+
+    def point(batch):
+        """tok/s and the HBM roofline of a batch size: every weight once and the live requests' cache."""
+        ms = statistics.median(results[batch]) / args.steps
+        step_bytes = weight_bytes + batch * context_mid * kv_bytes + batch * h * 2
+        achieved = step_bytes / (ms * 1e-3) / 1e9
+        return ms, {"value": round(batch / (ms * 1e-3), 1), "ms_per_step": round(ms, 4),
+                    "ms_per_step_min": round(min(results[batch]) / args.steps, 4),
+                    "ms_per_step_max": round(max(results[batch]) / args.steps, 4),
+                    "bound": "hbm", "achieved": round(achieved, 1), "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                    "frac": round(achieved / peaks["hbm_gbs"], 4), "of": peaks["source"]}
+
+    ms_per_step, main_point = point(main_batch)
+    value = main_point["value"]
+    roofline = {k: main_point[k] for k in ("bound", "achieved", "peak", "unit", "frac", "of")}
+    repeats = {"n": args.repeats, "ms_per_step_min": main_point["ms_per_step_min"],
+               "ms_per_step_max": main_point["ms_per_step_max"], "value_is": "median over the repeats"}
+    others = {f"decode_b{b}": point(b)[1] for b in batches if b != main_batch}
+    points = {name: p["value"] for name, p in others.items()}
+    points_roofline = {name: {k: p[k] for k in ("ms_per_step", "ms_per_step_min", "ms_per_step_max", "achieved", "frac")}
+                       for name, p in others.items()}
 
     # ---------------------------------------------------------------- end to end, Engine.generate
     if args.skip_e2e:
         line = {"metric": f"decode tok/s at batch {main_batch}", "value": round(value, 1), "ms_per_step": round(ms_per_step, 4),
-                "roofline": roofline, "points": points, "gpu_launches": launches, "prefill_ms": prefill_ms}
+                "roofline": roofline, "points": points, "points_roofline": points_roofline, "repeats": repeats,
+                "gpu_launches": launches, "prefill": prefill}
         print(json.dumps(line))
         return 0
     # Token lists in, token lists out, through Engine.generate.  The token budget of this engine
@@ -377,6 +406,9 @@ def main() -> int:
     torch.cuda.synchronize()
     generations = e2e_engine.generate(prompts, max_tokens=out_tokens, ignore_eos=True)
     torch.cuda.synchronize()
+    short = [len(g.tokens) for g in generations if len(g.tokens) != out_tokens or g.finish_reason != "length"]
+    if short:
+        raise RuntimeError(f"end-to-end run: generations ended early ({short} of {out_tokens} tokens)")
     last_first = max(g.first_token_time for g in generations)
     finished = max(g.finished_time for g in generations)
     decoded = sum(sum(1 for t in g.token_times if t > last_first) for g in generations)
@@ -403,8 +435,8 @@ def main() -> int:
             "parallelism": "single GPU", "l2": f"inputs larger than L2 ({weight_bytes / 1e9:.0f} GB of weights per step)",
         },
         "e2e": e2e, "gpu_launches": launches, "clocks": clocks,
-        "prefill": prefill, "roofline": roofline, "points": points,
-        "peaks": peaks, "kernel_entry_calls": kernel_lib.call_count(),
+        "prefill": prefill, "roofline": roofline, "points": points, "points_roofline": points_roofline,
+        "repeats": repeats, "peaks": peaks, "kernel_entry_calls": kernel_lib.call_count(),
     }
     print(json.dumps(line))
     return 0

@@ -14,8 +14,10 @@ pytestmark = pytest.mark.gpu
 
 def plain_tokens_match(cfg, weights, prompt, got, temperature=0.0, seed=0, margin=1e-3):
     """Follows the engine's tokens with the plain implementation; a difference is accepted only at
-    a near-tie (the reference's rule: top-2 margin below 1e-3 and ours is one of the two,
-    crates/mrun-engine/tests/conformance.rs:26-27,162-190)."""
+    a near-tie: the plain score of the engine's token is within ``margin`` of the best plain score
+    (the reference's rule for its own comparisons is a top-2 margin below 1e-3,
+    crates/mrun-engine/tests/conformance.rs:26-27,162-190; with three candidates inside the margin
+    any of them may win)."""
     tokens = list(prompt)
     for n, token in enumerate(got, start=1):
         logits = plain.forward(cfg, weights, tokens)[-1].numpy()
@@ -25,9 +27,8 @@ def plain_tokens_match(cfg, weights, prompt, got, temperature=0.0, seed=0, margi
             score = logits * np.float32(1.0 / temperature) + plain.gumbel_noise(plain.draw_key(seed, n), len(logits))
         want = int(np.argmax(score))
         if token != want:
-            top2 = np.sort(score)[-2:]
-            assert top2[1] - top2[0] < margin and score[token] >= top2[0], \
-                f"token {n}: engine {token}, plain {want}, margin {top2[1] - top2[0]:.4f}"
+            assert score[want] - score[token] < margin, \
+                f"token {n}: engine {token}, plain {want}, behind by {score[want] - score[token]:.4f}"
         tokens.append(token)
 
 

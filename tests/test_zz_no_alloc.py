@@ -73,11 +73,17 @@ def test_static_scratch_entry_point_matches_the_ordinary_one(head_dim, blocks, m
 
     for attempt in range(2):                             # the second call finds the first call's leftovers
         got = torch.full((n, heads * head_dim), 5.0, dtype=torch.bfloat16, device=DEV)
+        torch.cuda.synchronize()
         before = torch.cuda.memory_allocated()
+        free_before = torch.cuda.mem_get_info()[0]
         rc = call_decode(dll, "mrun_attn_decode_static", case, got, blocks, min_tiles)
         assert rc == 0, last_error().decode()
         torch.cuda.synchronize()
-        assert torch.cuda.memory_allocated() == before
+        assert torch.cuda.memory_allocated() == before       # nothing through torch's allocator
+        if attempt == 1:
+            # nor through the driver: the device's free memory is what it was (the first call
+            # looked the array up and loaded the kernel, which may take memory once)
+            assert torch.cuda.mem_get_info()[0] == free_before
         assert (got.float() - want.float()).abs().max().item() <= 2e-2 * plain.abs().max().item(), attempt
         assert torch.equal(got, want), "same kernel, same merge order: the bits should agree"
 
