@@ -119,9 +119,11 @@ def test_gated_mlp_part(dtype, name, rows):
     want = plain.swiglu_mlp(h.float(), w, prefix)
     got = mlp.forward(h.to(DEV).to(rt.precision.act), None).float().cpu()
     assert (got - want).abs().max() <= tolerance(dtype) * want.abs().max()
-    with pytest.raises(ValueError, match="silu"):
-        from dataclasses import replace
-        FEED_FORWARDS.build(replace(config.to_spec().layers[1].feed_forward, activation="gelu"), local(tensors, prefix), rt)
+    # a gate function that no kernel has is refused when the part is built, by name
+    from dataclasses import replace
+    from mrun_b200.kernels.lib import KernelError
+    with pytest.raises(KernelError, match="gate function 'erf_gelu'.*silu"):
+        FEED_FORWARDS.build(replace(config.to_spec().layers[1].feed_forward, activation="erf_gelu"), local(tensors, prefix), rt)
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
