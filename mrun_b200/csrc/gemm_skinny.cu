@@ -17,10 +17,11 @@
 // A decode step is a chain of such products with a residual sum and an RMSNorm between them, and
 // at a handful of rows a stand-alone norm kernel is all launch latency.  So the norm is split
 // over the two products around it.  The product *before* it (epilogue RESIDUAL) adds its result
-// to the 32-bit residual stream in place, writes xw = bf16(stream * norm weight) and, per block,
-// the sum of squares of its 16 stream columns per row.  The product *after* it reads xw as its x
-// and multiplies its sums by rsqrt(sum of all blocks' squares / width + eps), which it adds up
-// itself in a fixed order: RMSNorm(x) · Wᵀ = rsqrt(mean(x²) + eps) · ((x ⊙ w_norm) · Wᵀ).
+// to the 32-bit residual stream in place, writes xw = bf16(stream * norm weight) and adds the sum
+// of squares of its 16 stream columns, per row, to the row's 64-bit fixed-point total (integer
+// atomics: the total does not depend on the order in which the blocks arrive).  The product
+// *after* it reads xw as its x and multiplies its sums by rsqrt(total / width + eps):
+// RMSNorm(x) · Wᵀ = rsqrt(mean(x²) + eps) · ((x ⊙ w_norm) · Wᵀ).
 //
 // Reference call sites: crates/mrun-engine/src/load.rs:294-306 (x · Wᵀ),
 // crates/mrun-engine/src/models/common.rs:336-339 (the gated feed-forward).
@@ -34,21 +35,22 @@ constexpr int THREADS = WARPS * 32;
 constexpr int UNROLL_DEEP = 4;      // chunks per batch with one row tile and one token tile per block
 constexpr int UNROLL_SHALLOW = 2;   // ... with two row tiles or two token tiles (more registers per chunk)
 enum : int { EPI_PLAIN = 0, EPI_GATED = 1, EPI_RESIDUAL = 2 };
-constexpr int MAX_IN_BLOCKS = 512;  // sums of squares a product takes in: a stream of up to 8,192 columns
+// Sums of squares travel as unsigned 64-bit integers in units of 2^-30: room for 1.7e10, steps of
+// 1e-9 (a row of unit-scale values sums to its width; eps times the width is 1e-6 times that).
+constexpr float SUMS_SCALE = 1073741824.f, SUMS_UNIT = 1.f / 1073741824.f;
 
 // What a launch does beside the product itself.
 struct Fusion {
     int act;                     // EPI_GATED: the gate's function (MRUN_GATE_*)
-    // x is the xw of a product before: the row's scale is rsqrt(sum of in_partials / width + eps)
-    const float* in_partials;    // [in_blocks][16] sums of squares, or null: x is taken as it is
-    int in_blocks;
+    // x is the xw of a product before: the row's scale is rsqrt(in_sums[row] * 2^-30 / width + eps)
+    const unsigned long long* in_sums;   // [16] totals of squares, or null: x is taken as it is
     float in_eps, in_inv_width;
-    // EPI_RESIDUAL: resid[M, ldr] += y; xw_out[M, N] = bf16(resid * norm_w); out_partials[block][16]
+    // EPI_RESIDUAL: resid[M, ldr] += y; xw_out[M, N] = bf16(resid * norm_w); out_sums[16] += squares
     float* resid;
     long ldr;
     const float* norm_w;
     bf16* xw_out;
-    float* out_partials;
+    unsigned long long* out_sums;
 };
 
 __device__ __forceinline__ uint4 load_stream(const bf16* p) {
@@ -80,7 +82,7 @@ skinny_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w, TOut* __re
     static_assert(EPI != EPI_RESIDUAL || MT == 1, "the residual epilogue sums 16 columns per block");
     __shared__ float red[WARPS][MT * 16][NT * 8 + 1];
     __shared__ float row_scale[NT * 8];
-    __shared__ __align__(16) float in_sums[MAX_IN_BLOCKS * 16];
+    __shared__ __align__(8) unsigned long long totals[NT * 8];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int g = lane >> 2, t = lane & 3;
     const int n0 = blockIdx.x * (MT * 16);
@@ -158,13 +160,11 @@ skinny_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w, TOut* __re
     load_w(wa[1], c0 + STRIDE);
     load_x(xa[0], c0);
     load_x(xa[1], c0 + STRIDE);
-    // The blocks' sums of squares of the rows of x travel to shared memory beside the weight
-    // stream (asynchronous copies: no registers, nothing waits for them before the last chunk).
-    if (f.in_partials != nullptr) {
-        for (int i = threadIdx.x; i < f.in_blocks * 4; i += THREADS) {
-            const unsigned dst = (unsigned)__cvta_generic_to_shared(in_sums + 4 * i);
-            asm volatile("cp.async.ca.shared.global [%0], [%1], 16;\n" ::"r"(dst), "l"(f.in_partials + 4 * i));
-        }
+    // the rows' totals of squares are asked for with the first weights (an asynchronous copy:
+    // no register waits for it) and used after the last
+    if (f.in_sums != nullptr && threadIdx.x < NT * 8) {
+        const unsigned dst = (unsigned)__cvta_generic_to_shared(totals + threadIdx.x);
+        asm volatile("cp.async.ca.shared.global [%0], [%1], 8;\n" ::"r"(dst), "l"(f.in_sums + threadIdx.x));
     }
     asm volatile("cp.async.commit_group;\n" ::);
     while (c0 < chunks) {
@@ -180,19 +180,10 @@ skinny_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w, TOut* __re
         load_x(xa[1], c0 + STRIDE);
     }
 
-    // The scale of each row of x: the blocks' sums added lane-strided and then across the warp,
-    // an order that depends on in_blocks only.
     asm volatile("cp.async.wait_all;\n" ::: "memory");
-    __syncthreads();
-    for (int token = warp; token < NT * 8; token += WARPS) {
-        float scale = 1.f;
-        if (f.in_partials != nullptr) {
-            float sum = 0.f;
-            for (int b = lane; b < f.in_blocks; b += 32) sum += in_sums[b * 16 + token];
-            scale = rsqrtf(mrun::warp_sum(sum) * f.in_inv_width + f.in_eps);
-        }
-        if (lane == 0) row_scale[token] = scale;
-    }
+    if (threadIdx.x < NT * 8)
+        row_scale[threadIdx.x] = f.in_sums != nullptr
+            ? rsqrtf(__ull2float_rn(totals[threadIdx.x]) * SUMS_UNIT * f.in_inv_width + f.in_eps) : 1.f;
     // partial sums of the eight warps, added in warp order
 #pragma unroll
     for (int mt = 0; mt < MT; ++mt)
@@ -251,7 +242,7 @@ skinny_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w, TOut* __re
             float q = v * v;
 #pragma unroll
             for (int o = 8; o > 0; o >>= 1) q += __shfl_xor_sync(0xffffffffu, q, o);
-            if (row == 0 && token < M) f.out_partials[(size_t)blockIdx.x * 16 + token] = q;
+            if (row == 0 && token < M) atomicAdd(f.out_sums + token, __float2ull_rn(fminf(q, 1.5e10f) * SUMS_SCALE));
         }
     }
 }
@@ -302,41 +293,37 @@ void dispatch(const bf16* x, const bf16* w, TOut* y, int M, int N, int K, long l
 // y[M, N] = x[M, K] · w[N, K]^T for M <= 16.  out_dtype: MRUN_BF16 or MRUN_F32.  gate != 0
 // (MRUN_GATE_*): W holds gate/up rows interleaved in runs of eight and y gets N / 2 columns of
 // act(gate) * up.  x rows are ldx elements apart, y rows ldy.
-// in_partials != null: x is the xw that a call with `resid` made, and every row's sums are
-// multiplied by rsqrt(sum over in_blocks of in_partials[b][row] / K + in_eps).
+// in_sums != null: x is the xw that a call with `resid` made, and every row's sums are
+// multiplied by rsqrt(in_sums[row] * 2^-30 / K + in_eps).
 // resid != null: nothing is written to y; instead resid[M, N] (32-bit, dense) += the product,
-// xw_out[M, N] = bf16(resid * norm_w) and out_partials[(N + 15) / 16][16] gets every block's sums
-// of squares of its 16 columns of resid, per row.
+// xw_out[M, N] = bf16(resid * norm_w) and out_sums[row] (16 unsigned 64-bit integers, zero before
+// the call) gets the row's sum of squares of resid in units of 2^-30.
 MRUN_API int mrun_gemm_skinny(const void* x, const void* w, void* y, int out_dtype, int gate, int M, int N,
-                              int K, long ldx, long ldy, const float* in_partials, int in_blocks, float in_eps,
-                              float* resid, const float* norm_w, void* xw_out, float* out_partials,
+                              int K, long ldx, long ldy, const unsigned long long* in_sums, float in_eps,
+                              float* resid, const float* norm_w, void* xw_out, unsigned long long* out_sums,
                               cudaStream_t stream) {
     MRUN_REQUIRE(M >= 0 && N > 0 && K > 0, "gemm_skinny: bad sizes M=%d N=%d K=%d", M, N, K);
     MRUN_REQUIRE(M <= 16, "gemm_skinny: M=%d exceeds the 16 rows this kernel takes", M);
     MRUN_REQUIRE(K % 32 == 0, "gemm_skinny: K=%d is not a multiple of 32", K);
     MRUN_REQUIRE(ldx >= K && ldx % 8 == 0, "gemm_skinny: ldx=%ld must be a multiple of 8 and at least K=%d", ldx, K);
     MRUN_REQUIRE(((uintptr_t)x & 15) == 0 && ((uintptr_t)w & 15) == 0, "gemm_skinny: x and W must be 16-byte aligned");
-    MRUN_REQUIRE(in_partials == nullptr || (in_blocks > 0 && in_blocks <= MAX_IN_BLOCKS && ((uintptr_t)in_partials & 15) == 0),
-                 "gemm_skinny: a row scale from in_blocks=%d sums (1..%d, 16-byte aligned) cannot be applied", in_blocks,
-                 MAX_IN_BLOCKS);
     Fusion f = {};
     f.act = gate;
-    f.in_partials = in_partials;
-    f.in_blocks = in_blocks;
+    f.in_sums = in_sums;
     f.in_eps = in_eps;
     f.in_inv_width = 1.f / (float)K;
     const bf16* xp = (const bf16*)x;
     const bf16* wp = (const bf16*)w;
     if (resid != nullptr) {
         MRUN_REQUIRE(!gate, "gemm_skinny: the residual epilogue has no gate");
-        MRUN_REQUIRE(norm_w != nullptr && xw_out != nullptr && out_partials != nullptr,
-                     "gemm_skinny: the residual epilogue needs norm_w, xw_out and out_partials");
+        MRUN_REQUIRE(norm_w != nullptr && xw_out != nullptr && out_sums != nullptr,
+                     "gemm_skinny: the residual epilogue needs norm_w, xw_out and out_sums");
         if (M == 0) return 0;
         f.resid = resid;
         f.ldr = N;
         f.norm_w = norm_w;
         f.xw_out = (bf16*)xw_out;
-        f.out_partials = out_partials;
+        f.out_sums = out_sums;
         dispatch<bf16, EPI_RESIDUAL>(xp, wp, (bf16*)nullptr, M, N, K, ldx, ldy, f, stream);
         MRUN_CHECK_LAUNCH("gemm_skinny");
         return 0;
@@ -358,33 +345,24 @@ MRUN_API int mrun_gemm_skinny(const void* x, const void* w, void* y, int out_dty
     return 0;
 }
 
-// out[t, k] = bf16(xw[t, k] * rsqrt(sum over blocks of partials[b][t] / width + eps)): the rows a
-// product with `resid` left as xw, finished into plain RMSNorm output for a consumer that is not
-// one of these products.  The sums are added in the order the products use.
+// out[t, k] = bf16(xw[t, k] * rsqrt(sums[t] * 2^-30 / width + eps)): the rows a product with
+// `resid` left as xw, finished into plain RMSNorm output for a consumer that is not one of these
+// products.
 namespace {
-__global__ void norm_finish_kernel(const bf16* __restrict__ xw, const float* __restrict__ partials, int blocks,
-                                   float eps, float inv_width, bf16* __restrict__ out, int width) {
-    __shared__ float scale;
+__global__ void norm_finish_kernel(const bf16* __restrict__ xw, const unsigned long long* __restrict__ sums, float eps,
+                                   float inv_width, bf16* __restrict__ out, int width) {
     const int token = blockIdx.x;
-    if (threadIdx.x < 32) {
-        float sum = 0.f;
-        for (int b = threadIdx.x; b < blocks; b += 32) sum += partials[b * 16 + token];
-        sum = mrun::warp_sum(sum);
-        if (threadIdx.x == 0) scale = rsqrtf(sum * inv_width + eps);
-    }
-    __syncthreads();
+    const float scale = rsqrtf(__ull2float_rn(sums[token]) * SUMS_UNIT * inv_width + eps);
     for (int k = threadIdx.x; k < width; k += blockDim.x)
         out[(size_t)token * width + k] = __float2bfloat16_rn(__bfloat162float(xw[(size_t)token * width + k]) * scale);
 }
 }  // namespace
 
-MRUN_API int mrun_norm_finish(const void* xw, const float* partials, int blocks, float eps, void* out, int tokens,
+MRUN_API int mrun_norm_finish(const void* xw, const unsigned long long* sums, float eps, void* out, int tokens,
                               int width, cudaStream_t stream) {
-    MRUN_REQUIRE(tokens >= 0 && tokens <= 16 && width > 0 && blocks > 0,
-                 "norm_finish: bad sizes tokens=%d width=%d blocks=%d", tokens, width, blocks);
+    MRUN_REQUIRE(tokens >= 0 && tokens <= 16 && width > 0, "norm_finish: bad sizes tokens=%d width=%d", tokens, width);
     if (tokens == 0) return 0;
-    norm_finish_kernel<<<tokens, 256, 0, stream>>>((const bf16*)xw, partials, blocks, eps, 1.f / (float)width,
-                                                   (bf16*)out, width);
+    norm_finish_kernel<<<tokens, 256, 0, stream>>>((const bf16*)xw, sums, eps, 1.f / (float)width, (bf16*)out, width);
     MRUN_CHECK_LAUNCH("norm_finish");
     return 0;
 }

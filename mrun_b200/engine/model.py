@@ -90,6 +90,7 @@ class Model:
     # ------------------------------------------------------------------ forward
     def hidden_states(self, ctx: StepContext, caches) -> tuple:
         """Runs the layers; returns the 32-bit stream and the last branch output not yet added."""
+        ops.RowSums.begin_step(self.runtime.device)
         resid = torch.empty((ctx.num_tokens, self.spec.hidden_size), dtype=torch.float32,
                             device=self.runtime.device)
         ops.embed(self.embedding, ctx.token_ids, resid)

@@ -196,14 +196,17 @@ def skinny_ok(x, w: torch.Tensor) -> bool:
             and x.data_ptr() % 16 == 0)
 
 
+SUMS_UNIT = 2.0 ** -30        # a row's total of squares is a 64-bit integer in these units
+
+
 class NormedRows:
     """The output of an RMSNorm whose row scale has not been applied yet: ``xw`` holds
-    bf16(stream * norm weight) and ``partials`` [blocks, 16] the sums of squares of the stream's
-    columns, block by block, per row.  The decode GEMM takes it as its x and applies
-    rsqrt(sum / width + eps) to its own sums; :meth:`finish` makes the plain normed rows."""
+    bf16(stream * norm weight) and ``sums`` (int64 [16]) each row's total of squares of the stream
+    in units of 2^-30.  The decode GEMM takes it as its x and applies rsqrt(total / width + eps)
+    to its own sums; :meth:`finish` makes the plain normed rows."""
 
-    def __init__(self, xw: torch.Tensor, partials: torch.Tensor, eps: float):
-        self.xw, self.partials, self.eps = xw, partials, float(eps)
+    def __init__(self, xw: torch.Tensor, sums: torch.Tensor, eps: float):
+        self.xw, self.sums, self.eps = xw, sums, float(eps)
 
     @property
     def shape(self):
@@ -220,9 +223,36 @@ class NormedRows:
     def finish(self) -> torch.Tensor:
         tokens, width = self.xw.shape
         out = torch.empty_like(self.xw)
-        _lib.core().call("mrun_norm_finish", _ptr(self.xw), _ptr(self.partials), _c_int(self.partials.shape[0]),
-                         _c_float(self.eps), _ptr(out), _c_int(tokens), _c_int(width), _stream())
+        _lib.core().call("mrun_norm_finish", _ptr(self.xw), _ptr(self.sums), _c_float(self.eps), _ptr(out),
+                         _c_int(tokens), _c_int(width), _stream())
         return out
+
+
+class RowSums:
+    """Zeroed 16-row totals for the products of one step: one buffer per device, cleared once at
+    the start of a step (:meth:`begin_step`: one memset, which a captured step replays) and handed
+    out slice by slice, so that no product clears its own."""
+
+    SLOTS = 1024
+    _arenas = {}
+
+    @classmethod
+    def begin_step(cls, device: torch.device) -> None:
+        arena = cls._arenas.get(device)
+        if arena is None:
+            arena = cls._arenas[device] = [torch.zeros((cls.SLOTS, 16), dtype=torch.int64, device=device), 0]
+        arena[0].zero_()                   # always: a captured step must clear what other steps left
+        arena[1] = 0
+
+    @classmethod
+    def take(cls, device: torch.device) -> torch.Tensor:
+        """The next zeroed slice of the step, or a fresh zeroed tensor outside a step or when the
+        step has used all of its slices."""
+        arena = cls._arenas.get(device)
+        if arena is None or arena[1] >= cls.SLOTS:
+            return torch.zeros(16, dtype=torch.int64, device=device)
+        arena[1] += 1
+        return arena[0][arena[1] - 1]
 
 
 class PendingLinear:
@@ -242,10 +272,10 @@ class PendingLinear:
 
 
 def _normed(x):
-    """(rows, partials pointer, blocks, eps) of a product's x, which may be :class:`NormedRows`."""
+    """(rows, totals pointer, eps) of a product's x, which may be :class:`NormedRows`."""
     if isinstance(x, NormedRows):
-        return x.xw, _ptr(x.partials), _c_int(x.partials.shape[0]), _c_float(x.eps)
-    return x, _ptr(None), _c_int(0), _c_float(0.0)
+        return x.xw, _ptr(x.sums), _c_float(x.eps)
+    return x, _ptr(None), _c_float(0.0)
 
 
 def gemm_skinny(x, w: torch.Tensor, out_dtype: torch.dtype = torch.bfloat16,
@@ -253,7 +283,7 @@ def gemm_skinny(x, w: torch.Tensor, out_dtype: torch.dtype = torch.bfloat16,
     """y = x @ w.T for at most 16 rows, reading w once at HBM speed.  ``swiglu_rows``: w holds gate
     and up rows interleaved in runs of eight and y = act(gate) * up has half as many columns.
     ``x`` may be :class:`NormedRows`."""
-    x, partials, blocks, eps = _normed(x)
+    x, sums, eps = _normed(x)
     _check(x, "x", torch.bfloat16, dense=False); _check(w, "w", torch.bfloat16)
     m, k = x.shape
     n = w.shape[0]
@@ -263,24 +293,21 @@ def gemm_skinny(x, w: torch.Tensor, out_dtype: torch.dtype = torch.bfloat16,
     _lib.core().call("mrun_gemm_skinny", _ptr(x), _ptr(w), _ptr(out), dtype_code(out_dtype),
                      _c_int(gate_code(activation) if swiglu_rows else 0), _c_int(m), _c_int(n), _c_int(k),
                      _c_long(x.stride(0) if m > 1 else max(k, x.stride(0))), _c_long(out.shape[1]),
-                     partials, blocks, eps, _ptr(None), _ptr(None), _ptr(None), _ptr(None), _stream())
+                     sums, eps, _ptr(None), _ptr(None), _ptr(None), _ptr(None), _stream())
     return out
-
-
-NORM_FUSION_WIDTH = 8192      # the widest stream whose sums of squares the decode GEMM takes in
 
 
 def norm_fusable(pending, resid: torch.Tensor, weight: torch.Tensor) -> bool:
     """Whether :func:`linear_into_norm` takes this pending product and residual stream."""
     return (isinstance(pending, PendingLinear) and skinny_ok(pending.x, pending.w)
             and resid.dtype == torch.float32 and resid.is_contiguous() and resid.shape == pending.shape
-            and resid.shape[1] % 32 == 0 and resid.shape[1] <= NORM_FUSION_WIDTH and weight.numel() == resid.shape[1])
+            and resid.shape[1] % 32 == 0 and weight.numel() == resid.shape[1])
 
 
 def linear_into_norm(pending: PendingLinear, resid: torch.Tensor, weight: torch.Tensor, eps: float) -> NormedRows:
     """resid += pending.x @ pending.w.T (32-bit, in place) and the RMSNorm of the new rows with
     ``weight``, as :class:`NormedRows`: one kernel, at most 16 rows."""
-    x, partials, blocks, in_eps = _normed(pending.x)
+    x, in_sums, in_eps = _normed(pending.x)
     w = pending.w
     _check(x, "x", torch.bfloat16, dense=False); _check(w, "w", torch.bfloat16)
     _check(resid, "resid", torch.float32); _check(weight, "weight", torch.float32)
@@ -290,12 +317,11 @@ def linear_into_norm(pending: PendingLinear, resid: torch.Tensor, weight: torch.
         raise KernelError(f"linear_into_norm: x {tuple(x.shape)}, w {tuple(w.shape)}, resid {tuple(resid.shape)}, "
                           f"weight {tuple(weight.shape)}")
     xw = torch.empty((m, n), dtype=torch.bfloat16, device=x.device)
-    out_partials = torch.empty((-(-n // 16), 16), dtype=torch.float32, device=x.device)
+    out_sums = RowSums.take(x.device)
     _lib.core().call("mrun_gemm_skinny", _ptr(x), _ptr(w), _ptr(None), dtype_code(torch.bfloat16), _c_int(0),
                      _c_int(m), _c_int(n), _c_int(k), _c_long(x.stride(0) if m > 1 else max(k, x.stride(0))),
-                     _c_long(n), partials, blocks, in_eps, _ptr(resid), _ptr(weight), _ptr(xw), _ptr(out_partials),
-                     _stream())
-    return NormedRows(xw, out_partials, eps)
+                     _c_long(n), in_sums, in_eps, _ptr(resid), _ptr(weight), _ptr(xw), _ptr(out_sums), _stream())
+    return NormedRows(xw, out_sums, eps)
 
 
 def gemm_f32_nt(x: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
