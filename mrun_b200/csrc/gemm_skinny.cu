@@ -83,6 +83,7 @@ skinny_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w, TOut* __re
     __shared__ float red[WARPS][MT * 16][NT * 8 + 1];
     __shared__ float row_scale[NT * 8];
     __shared__ __align__(8) unsigned long long totals[NT * 8];
+    __shared__ float stream_tile[EPI == EPI_RESIDUAL ? NT * 8 * 16 : 1], norm_tile[16];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int g = lane >> 2, t = lane & 3;
     const int n0 = blockIdx.x * (MT * 16);
@@ -166,6 +167,19 @@ skinny_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w, TOut* __re
         const unsigned dst = (unsigned)__cvta_generic_to_shared(totals + threadIdx.x);
         asm volatile("cp.async.ca.shared.global [%0], [%1], 8;\n" ::"r"(dst), "l"(f.in_sums + threadIdx.x));
     }
+    if constexpr (EPI == EPI_RESIDUAL) {
+        // so are the block's 16 columns of the stream and of the norm weight (the kernel before
+        // this one wrote the stream; no block of this one writes another block's columns)
+        for (int i = threadIdx.x; i < 16 * NT * 8 + 16; i += THREADS) {
+            const bool is_w = i >= 16 * NT * 8;
+            const int row = i & 15, token = (i >> 4) & (NT * 8 - 1);
+            if (n0 + row < N && (is_w || token < M)) {
+                const float* src = is_w ? f.norm_w + n0 + row : f.resid + (size_t)token * f.ldr + n0 + row;
+                const unsigned dst = (unsigned)__cvta_generic_to_shared(is_w ? norm_tile + row : stream_tile + i);
+                asm volatile("cp.async.ca.shared.global [%0], [%1], 4;\n" ::"r"(dst), "l"(src));
+            }
+        }
+    }
     asm volatile("cp.async.commit_group;\n" ::);
     while (c0 < chunks) {
         compute_batch(wa[0], xa[0], c0);
@@ -234,10 +248,9 @@ skinny_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w, TOut* __re
                 float s = 0.f;
 #pragma unroll
                 for (int wi = 0; wi < WARPS; ++wi) s += red[wi][row][token];
-                float* r = f.resid + (size_t)token * f.ldr + n0 + row;
-                v = *r + s * row_scale[token];
-                *r = v;
-                f.xw_out[(size_t)token * N + n0 + row] = __float2bfloat16_rn(v * f.norm_w[n0 + row]);
+                v = stream_tile[i] + s * row_scale[token];
+                f.resid[(size_t)token * f.ldr + n0 + row] = v;
+                f.xw_out[(size_t)token * N + n0 + row] = __float2bfloat16_rn(v * norm_tile[row]);
             }
             float q = v * v;
 #pragma unroll
