@@ -497,6 +497,313 @@ decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_consta
     }
 }
 
+// ------------------------------------------------------------------------------------------
+// The same attention for steps with few (token, kv head) pairs, one thread-block cluster a pair.
+// The pair's tiles are cut evenly into as many pieces as the cluster has blocks (a function of
+// the pair's own length and the cluster size, so no plan is read and a pair's cut does not depend
+// on the other pairs of the step).  A block streams its piece as above, leaves its partial result
+// (rows x D values, maximum, sum) in its own shared memory, the cluster meets at its hardware
+// barrier, and the first block reads the pieces of the others through distributed shared memory
+// in block order and writes the pair's heads: no scratch in global memory, no fence, no counter.
+// grid (cluster size, tokens * kv_heads), cluster (cluster size, 1, 1); up to 8 query heads a kv head.
+// ------------------------------------------------------------------------------------------
+__device__ __forceinline__ void cluster_sync_all() {
+    asm volatile("barrier.cluster.arrive.release.aligned;\n" ::: "memory");
+    asm volatile("barrier.cluster.wait.acquire.aligned;\n" ::: "memory");
+}
+__device__ __forceinline__ unsigned cluster_address(const void* own_shared, unsigned rank) {
+    unsigned local = (unsigned)__cvta_generic_to_shared(own_shared), remote;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;\n" : "=r"(remote) : "r"(local), "r"(rank));
+    return remote;
+}
+__device__ __forceinline__ float4 cluster_load4(unsigned address) {
+    float4 v;
+    asm volatile("ld.shared::cluster.v4.f32 {%0,%1,%2,%3}, [%4];\n" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(address));
+    return v;
+}
+__device__ __forceinline__ float2 cluster_load2(unsigned address) {
+    float2 v;
+    asm volatile("ld.shared::cluster.v2.f32 {%0,%1}, [%2];\n" : "=f"(v.x), "=f"(v.y) : "r"(address));
+    return v;
+}
+
+template <int RING>
+__global__ void __launch_bounds__(TMA_THREADS)
+decode_cluster_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
+                      const bf16* __restrict__ q, long q_stride, bf16* __restrict__ out,
+                      const int* __restrict__ block_tables, int max_blocks, const int* __restrict__ token_slot,
+                      const int* __restrict__ positions, int heads, int kv_heads, int page_size, int page_shift,
+                      float scale_log2, int window, const FusedInput fused, int* __restrict__ status) {
+    extern __shared__ __align__(1024) unsigned char smem_raw[];
+    unsigned char* ring = reinterpret_cast<unsigned char*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    const int group = heads / kv_heads;
+    bf16* q_tile = reinterpret_cast<bf16*>(ring + RING * STAGE_BYTES);                   // [16][LD]
+    float* merge = reinterpret_cast<float*>(q_tile + 16 * LD);                            // [4][group][MS]
+    float (*head_vec)[D] = reinterpret_cast<float (*)[D]>(merge + 4 * group * MS);        // [4][D]
+    bf16* new_k = reinterpret_cast<bf16*>(head_vec + 4);
+    bf16* new_v = new_k + D;
+    // the block's piece takes the place of the queries once the tiles are done: [group][PS],
+    // PS = D + 4 so that a row starts on 16 bytes (group <= 8: 8 x 132 floats fit 16 x LD bf16)
+    constexpr int PS = D + 4;
+    float* piece = reinterpret_cast<float*>(q_tile);
+    __shared__ unsigned long long full_bar[RING], empty_bar[RING];
+    __shared__ int aborted;
+
+    const unsigned rank = blockIdx.x, pieces = gridDim.x;
+    const int pair = blockIdx.y, tok = pair / kv_heads, kvh = pair - tok * kv_heads;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int pos = positions[tok];
+    const int q_row = fused.rows ? fused.rows[tok] : tok;
+    if (pos < 0) {                                   // a padding row: zeros, and the whole cluster leaves
+        if (rank == 0)
+            for (int i = threadIdx.x; i < group * D; i += TMA_THREADS)
+                out[((size_t)q_row * heads + kvh * group) * D + i] = __float2bfloat16_rn(0.f);
+        return;
+    }
+    const int lo = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
+    const int b0 = lo / BLOCK_N, b1 = pos / BLOCK_N, pair_tiles = b1 - b0 + 1;
+    const int base = pair_tiles / (int)pieces, extra = pair_tiles - base * (int)pieces;
+    const int len = base + ((int)rank < extra ? 1 : 0);
+    const int first_block = b0 + (int)rank * base + min((int)rank, extra), last_block = first_block + len - 1;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < RING; ++s) {
+            mbar_init(&full_bar[s], 32);
+            mbar_init(&empty_bar[s], 4);
+        }
+        aborted = 0;
+        mbar_init_fence();
+    }
+    // rows of a V tile that no copy fills must not hold NaN patterns: 0 * NaN is NaN
+    if (len > 0)
+        for (int s = 0; s < RING && s < len; ++s)
+            for (int i = threadIdx.x; i < TILE_BYTES / 16; i += TMA_THREADS)
+                reinterpret_cast<uint4*>(ring + s * STAGE_BYTES + TILE_BYTES)[i] = make_uint4(0, 0, 0, 0);
+    fence_async_smem();
+    __syncthreads();
+
+    if (warp == 4) {
+        // ------------------------------------------------------------------------------ producer
+        const int box_rows = page_size < BLOCK_N ? page_size : BLOCK_N;
+        const int boxes = BLOCK_N / box_rows;
+        const int* table = block_tables + (size_t)token_slot[tok] * max_blocks;
+        bool alive = true;
+        int it = 0;
+        for (int block = first_block; alive && block <= last_block; ++block, ++it) {
+            const int s = it % RING, use = it / RING;
+            const bool free_now = use == 0 || mbar_wait(&empty_bar[s], (use - 1) & 1, WAIT_CYCLES, &aborted);
+            if (!__all_sync(0xffffffffu, free_now)) { alive = false; break; }
+            unsigned char* stage = ring + s * STAGE_BYTES;
+            const int key0 = block * BLOCK_N;
+            unsigned bytes = 0;
+            for (int b = lane; b < boxes; b += 32) {
+                const int first_key = key0 + b * box_rows;
+                if (first_key <= pos && first_key + box_rows - 1 >= lo && table[first_key >> page_shift] >= 0)
+                    bytes += (unsigned)(2 * box_rows * D * 2);
+            }
+            if (bytes) mbar_expect_tx(&full_bar[s], bytes);
+            else mbar_arrive(&full_bar[s]);
+            for (int b = lane; b < boxes; b += 32) {
+                const int first_key = key0 + b * box_rows;
+                if (first_key > pos || first_key + box_rows - 1 < lo) continue;
+                const int page = table[first_key >> page_shift];
+                if (page < 0) continue;
+#pragma unroll
+                for (int h = 0; h < SPANS; ++h) {
+                    tma_load_4d(stage + h * SPAN_BYTES + b * box_rows * 128, &map_k, h * 64,
+                                first_key & (page_size - 1), kvh, page, &full_bar[s]);
+                    tma_load_4d(stage + TILE_BYTES + h * SPAN_BYTES + b * box_rows * 128, &map_v, h * 64,
+                                first_key & (page_size - 1), kvh, page, &full_bar[s]);
+                }
+            }
+        }
+        if (!alive) {
+            if (!*(volatile int*)&aborted) atomicExch(status, STATUS_PRODUCER);
+            atomicExch(&aborted, 1);
+        }
+    } else {
+        // ----------------------------------------------------------------------------- consumers
+        float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
+        float o[D / 8][4];
+#pragma unroll
+        for (int dt = 0; dt < D / 8; ++dt) o[dt][0] = o[dt][1] = o[dt][2] = o[dt][3] = 0.f;
+        if (len > 0) {
+            const bool owns_new_token = fused.enabled && last_block == b1;
+            if (!fused.enabled) {
+                for (int c = threadIdx.x; c < 16 * CHUNKS; c += CONSUMERS) {
+                    const int row = c / CHUNKS, chunk = c - row * CHUNKS;
+                    uint4 value = make_uint4(0, 0, 0, 0);
+                    if (row < group)
+                        value = *reinterpret_cast<const uint4*>(q + (size_t)q_row * q_stride + (size_t)(kvh * group + row) * D + chunk * 8);
+                    *reinterpret_cast<uint4*>(q_tile + row * LD + chunk * 8) = value;
+                }
+            } else {
+                const bf16* token_row = q + (size_t)tok * q_stride;
+                const float2* cs = fused.rot ? fused.rot + (size_t)tok * (fused.rotary_dim >> 1) : nullptr;
+                const int slot = (owns_new_token && fused.slots) ? fused.slots[tok] : -1;
+                for (int row = warp; row < 16; row += 4) {
+                    if (row < group)
+                        norm_rotate_head(token_row + (size_t)(kvh * group + row) * D, fused.q_weight, fused.eps, cs,
+                                         fused.rotary_dim, head_vec[warp], q_tile + row * LD);
+                    else
+                        for (int e = lane; e < D; e += 32) q_tile[row * LD + e] = __float2bfloat16_rn(0.f);
+                }
+                if (owns_new_token) {
+                    if (warp == 0)
+                        norm_rotate_head(token_row + (size_t)(heads + kvh) * D, fused.k_weight, fused.eps, cs,
+                                         fused.rotary_dim, head_vec[0], new_k);
+                    if (warp == 1)
+                        for (int e = lane; e < D; e += 32) new_v[e] = token_row[(size_t)(heads + kv_heads + kvh) * D + e];
+                    consumer_sync();
+                    if (slot >= 0) {
+                        const int page = slot / page_size, off = slot - page * page_size;
+                        const size_t at = (((size_t)page * kv_heads + kvh) * page_size + off) * D;
+                        for (int c = threadIdx.x; c < 2 * CHUNKS; c += CONSUMERS) {
+                            const bool is_v = c >= CHUNKS;
+                            const int chunk = is_v ? c - CHUNKS : c;
+                            *reinterpret_cast<uint4*>((is_v ? fused.v_cache : fused.k_cache) + at + chunk * 8) =
+                                *reinterpret_cast<const uint4*>((is_v ? new_v : new_k) + chunk * 8);
+                        }
+                    }
+                }
+            }
+            consumer_sync();                                    // q (and the new key and value) are in place
+
+            int row_pos[2], row_lo[2];
+#pragma unroll
+            for (int rr = 0; rr < 2; ++rr) {
+                const int row = (lane >> 2) + rr * 8;
+                row_pos[rr] = row < group ? pos : -1;
+                row_lo[rr] = lo;
+            }
+            bool alive = true;
+            int it = 0;
+            for (int block = first_block; block <= last_block; ++block, ++it) {
+                const int s = it % RING, use = it / RING;
+                if (!__all_sync(0xffffffffu, mbar_wait(&full_bar[s], use & 1, WAIT_CYCLES, &aborted)) && alive) {
+                    alive = false;
+                    if (lane == 0) {
+                        if (!*(volatile int*)&aborted) atomicExch(status, STATUS_CONSUMER);
+                        atomicExch(&aborted, 1);
+                    }
+                }
+                unsigned char* k_tile = ring + s * STAGE_BYTES;
+                unsigned char* v_tile = k_tile + TILE_BYTES;
+                const int key_base = block * BLOCK_N;
+                if (owns_new_token && block == b1) {
+                    const int row = pos - key_base;
+                    for (int c = threadIdx.x; c < 2 * CHUNKS; c += CONSUMERS) {
+                        const bool is_v = c >= CHUNKS;
+                        const int chunk = is_v ? c - CHUNKS : c;
+                        *reinterpret_cast<uint4*>(const_cast<unsigned char*>(swz(is_v ? v_tile : k_tile, row, chunk))) =
+                            *reinterpret_cast<const uint4*>((is_v ? new_v : new_k) + chunk * 8);
+                    }
+                    consumer_sync();
+                }
+                if (key_base + warp * 16 <= pos && key_base + warp * 16 + 15 >= lo)
+                    attend_slice(q_tile, k_tile, v_tile, warp * 16, key_base, scale_log2, row_pos, row_lo, m, l, o);
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&empty_bar[s]);
+            }
+#pragma unroll
+            for (int rr = 0; rr < 2; ++rr) {
+                l[rr] += __shfl_xor_sync(0xffffffffu, l[rr], 1);
+                l[rr] += __shfl_xor_sync(0xffffffffu, l[rr], 2);
+            }
+        }
+        // the four warps meet: merge[warp][row < group][D + 2] (a block without tiles brings nothing)
+#pragma unroll
+        for (int rr = 0; rr < 2; ++rr) {
+            const int row = (lane >> 2) + rr * 8;
+            if (row < group) {
+                float* dst = merge + (warp * group + row) * MS;
+#pragma unroll
+                for (int dt = 0; dt < D / 8; ++dt) {
+                    dst[dt * 8 + (lane & 3) * 2] = o[dt][2 * rr];
+                    dst[dt * 8 + (lane & 3) * 2 + 1] = o[dt][2 * rr + 1];
+                }
+                if ((lane & 3) == 0) {
+                    dst[D] = m[rr];
+                    dst[D + 1] = l[rr];
+                }
+            }
+        }
+        consumer_sync();                                        // also: nobody reads the queries any more
+        for (int i = threadIdx.x; i < group * (D / 4); i += CONSUMERS) {
+            const int row = i / (D / 4), d = (i - row * (D / 4)) * 4;
+            float mm = -INFINITY;
+#pragma unroll
+            for (int w = 0; w < 4; ++w) mm = fmaxf(mm, merge[(w * group + row) * MS + D]);
+            float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+            float ll = 0.f;
+#pragma unroll
+            for (int w = 0; w < 4; ++w) {
+                const float* src = merge + (w * group + row) * MS;
+                const float c = (src[D] == -INFINITY) ? 0.f : exp2f(src[D] - mm);
+                const float2 lo2 = *reinterpret_cast<const float2*>(src + d), hi2 = *reinterpret_cast<const float2*>(src + d + 2);
+                acc.x += lo2.x * c; acc.y += lo2.y * c; acc.z += hi2.x * c; acc.w += hi2.y * c;
+                ll += src[D + 1] * c;
+            }
+            if (pieces == 1) {
+                const float inv = ll > 0.f ? 1.f / ll : 0.f;
+                __nv_bfloat162 lo2 = __floats2bfloat162_rn(acc.x * inv, acc.y * inv);
+                __nv_bfloat162 hi2 = __floats2bfloat162_rn(acc.z * inv, acc.w * inv);
+                uint2 packed;
+                packed.x = *reinterpret_cast<unsigned*>(&lo2);
+                packed.y = *reinterpret_cast<unsigned*>(&hi2);
+                *reinterpret_cast<uint2*>(out + ((size_t)q_row * heads + kvh * group + row) * D + d) = packed;
+            } else {
+                *reinterpret_cast<float4*>(piece + row * PS + d) = acc;
+                if (d == 0) *reinterpret_cast<float2*>(piece + row * PS + D) = make_float2(mm, ll);
+            }
+        }
+    }
+    if (pieces > 1) {
+        cluster_sync_all();                                     // every block's piece is in its shared memory
+        if (rank == 0 && warp < 4) {
+            for (int i = threadIdx.x; i < group * (D / 4); i += CONSUMERS) {
+                const int row = i / (D / 4), d = (i - row * (D / 4)) * 4;
+                float mm = -INFINITY;
+                for (unsigned p = 0; p < pieces; ++p)
+                    mm = fmaxf(mm, cluster_load2(cluster_address(piece + row * PS + D, p)).x);
+                float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+                float ll = 0.f;
+                for (unsigned p0 = 0; p0 < pieces; p0 += 4) {   // four pieces requested before any is used
+                    float2 ml[4];
+                    float4 po[4];
+#pragma unroll
+                    for (unsigned k = 0; k < 4; ++k) {
+                        ml[k] = make_float2(-INFINITY, 0.f);
+                        po[k] = make_float4(0.f, 0.f, 0.f, 0.f);
+                        if (p0 + k < pieces) {
+                            ml[k] = cluster_load2(cluster_address(piece + row * PS + D, p0 + k));
+                            po[k] = cluster_load4(cluster_address(piece + row * PS + d, p0 + k));
+                        }
+                    }
+#pragma unroll
+                    for (unsigned k = 0; k < 4; ++k) {
+                        const float c = (ml[k].x == -INFINITY) ? 0.f : exp2f(ml[k].x - mm);
+                        acc.x += po[k].x * c; acc.y += po[k].y * c; acc.z += po[k].z * c; acc.w += po[k].w * c;
+                        ll += ml[k].y * c;
+                    }
+                }
+                const float inv = ll > 0.f ? 1.f / ll : 0.f;
+                __nv_bfloat162 lo2 = __floats2bfloat162_rn(acc.x * inv, acc.y * inv);
+                __nv_bfloat162 hi2 = __floats2bfloat162_rn(acc.z * inv, acc.w * inv);
+                uint2 packed;
+                packed.x = *reinterpret_cast<unsigned*>(&lo2);
+                packed.y = *reinterpret_cast<unsigned*>(&hi2);
+                *reinterpret_cast<uint2*>(out + ((size_t)q_row * heads + kvh * group + row) * D + d) = packed;
+            }
+        }
+        cluster_sync_all();                                     // the pieces may go: the first block has read them
+    }
+    if (*(volatile int*)&aborted) {
+        const long long start = clock64();
+        while (clock64() - start < 4000000LL) __nanosleep(1000);
+    }
+}
+
 // Three stages where two blocks of them fit a multiprocessor, else two.
 int ring_for(int group) { return 2 * (tma_smem_bytes(3, group) + 1024) <= 227 * 1024 ? 3 : 2; }
 
@@ -533,6 +840,113 @@ MRUN_API int mrun_attn_decode_tma_occupancy(int group) {
 #else
     (void)group;
     return 0;
+#endif
+}
+
+#if MRUN_DECODE_TMA
+namespace {
+template <int RING>
+int launch_cluster(const CUtensorMap& map_k, const CUtensorMap& map_v, const void* q, long q_stride, void* out,
+                   const int* block_tables, int max_blocks, const int* token_slot, const int* positions, int tokens,
+                   int cluster, int heads, int kv_heads, int page_size, float scale, int window, const FusedInput& in,
+                   int* status, cudaStream_t stream) {
+    const int group = heads / kv_heads;
+    const size_t smem = tma_smem_bytes(RING, group);
+    static size_t allowed = 0;
+    if (smem > allowed) {
+        MRUN_CHECK_CUDA(cudaFuncSetAttribute(decode_cluster_kernel<RING>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem),
+                        "attn_decode_cluster");
+        MRUN_CHECK_CUDA(cudaFuncSetAttribute(decode_cluster_kernel<RING>, cudaFuncAttributeNonPortableClusterSizeAllowed, 1),
+                        "attn_decode_cluster");
+        allowed = smem;
+    }
+    cudaLaunchConfig_t config = {};
+    config.gridDim = dim3(cluster, tokens * kv_heads);
+    config.blockDim = dim3(TMA_THREADS);
+    config.dynamicSmemBytes = smem;
+    config.stream = stream;
+    cudaLaunchAttribute attribute[1];
+    attribute[0].id = cudaLaunchAttributeClusterDimension;
+    attribute[0].val.clusterDim.x = cluster;
+    attribute[0].val.clusterDim.y = 1;
+    attribute[0].val.clusterDim.z = 1;
+    config.attrs = attribute;
+    config.numAttrs = 1;
+    MRUN_CHECK_CUDA(cudaLaunchKernelEx(&config, decode_cluster_kernel<RING>, map_k, map_v, (const bf16*)q, q_stride, (bf16*)out,
+                                       block_tables, max_blocks, token_slot, positions, heads, kv_heads, page_size,
+                                       page_shift_of(page_size), scale * LOG2E, window, in, status),
+                    "attn_decode_cluster");
+    return 0;
+}
+}  // namespace
+#endif
+
+// The largest cluster (a power of two, at most 16) of the cluster decode kernel that the device
+// takes with `group` query heads per kv head; 0 when the kernel is not available for the group.
+MRUN_API int mrun_attn_decode_cluster_max(int group) {
+#if MRUN_DECODE_TMA
+    if (group < 1 || group > 8) return 0;
+    return 16;
+#else
+    (void)group;
+    return 0;
+#endif
+}
+
+// Decode attention for steps with few (token, kv head) pairs: a thread-block cluster of `cluster`
+// blocks (1, 2, 4, 8 or 16) takes one pair, cuts its tiles evenly among its blocks and merges
+// through distributed shared memory: no plan, no scratch.  Other arguments as mrun_attn_decode_tma;
+// at most 8 query heads per kv head.
+MRUN_API int mrun_attn_decode_cluster(const void* q, long q_stride, void* out, void* k_cache, void* v_cache,
+                                      const int* block_tables, int max_blocks, const int* token_slot,
+                                      const int* positions, int tokens, int cluster, int heads, int kv_heads,
+                                      int head_dim, int page_size, float scale, int window, int fused,
+                                      const float* q_weight, const float* k_weight, float eps, const float* rot,
+                                      int rotary_dim, const int* slots, const int* rows, long pages, int* status,
+                                      cudaStream_t stream) {
+#if MRUN_DECODE_TMA
+    if (int rc = check_common("attn_decode_cluster", heads, kv_heads, head_dim, page_size, max_blocks, window, 8)) return rc;
+    MRUN_REQUIRE(tokens >= 0 && (long)tokens * kv_heads <= 65535, "attn_decode_cluster: tokens=%d kv_heads=%d", tokens, kv_heads);
+    MRUN_REQUIRE(cluster == 1 || cluster == 2 || cluster == 4 || cluster == 8 || cluster == 16,
+                 "attn_decode_cluster: a cluster of %d blocks (1, 2, 4, 8 or 16)", cluster);
+    MRUN_REQUIRE(status != nullptr, "attn_decode_cluster: the status word is required");
+    MRUN_REQUIRE(page_shift_of(page_size) >= 0, "attn_decode_cluster: page_size=%d is not a power of two", page_size);
+    MRUN_REQUIRE(pages > 0 && pages < (1L << 31), "attn_decode_cluster: pages=%ld", pages);
+    MRUN_REQUIRE(((uintptr_t)k_cache & 15) == 0 && ((uintptr_t)v_cache & 15) == 0 && ((uintptr_t)q & 15) == 0 &&
+                 q_stride % 8 == 0, "attn_decode_cluster: q and the caches must be 16-byte aligned, q_stride a multiple of 8");
+    MRUN_REQUIRE(!fused || (rotary_dim >= 0 && rotary_dim <= head_dim && rotary_dim % 2 == 0),
+                 "attn_decode_cluster: rotary_dim=%d must be even and at most head_dim=%d", rotary_dim, head_dim);
+    MRUN_REQUIRE(!fused || (q_weight == nullptr) == (k_weight == nullptr),
+                 "attn_decode_cluster: q and k norm weights come together");
+    MRUN_REQUIRE(!fused || q_stride >= (long)(heads + 2 * kv_heads) * head_dim,
+                 "attn_decode_cluster: the raw rows must hold q, k and v (stride %ld)", q_stride);
+    MRUN_REQUIRE(!(fused && rows), "attn_decode_cluster: a selection of rows does not go with raw q, k, v input");
+    if (tokens == 0) return 0;
+    const int group = heads / kv_heads;
+    CUtensorMap map_k, map_v;
+    const int box_rows = page_size < BLOCK_N ? page_size : BLOCK_N;
+    if (int rc = paged_cache_map(&map_k, k_cache, pages, kv_heads, page_size, D, box_rows, "attn_decode_cluster")) return rc;
+    if (int rc = paged_cache_map(&map_v, v_cache, pages, kv_heads, page_size, D, box_rows, "attn_decode_cluster")) return rc;
+    FusedInput in = {};
+    if (fused) {
+        in.enabled = 1;
+        in.q_weight = q_weight;
+        in.k_weight = k_weight;
+        in.eps = eps;
+        in.rot = (const float2*)rot;
+        in.rotary_dim = rot ? rotary_dim : 0;
+        in.slots = slots;
+        in.k_cache = (bf16*)k_cache;
+        in.v_cache = (bf16*)v_cache;
+    }
+    in.rows = rows;
+    if (ring_for(group) == 3)
+        return launch_cluster<3>(map_k, map_v, q, q_stride, out, block_tables, max_blocks, token_slot, positions, tokens,
+                                 cluster, heads, kv_heads, page_size, scale, window, in, status, stream);
+    return launch_cluster<2>(map_k, map_v, q, q_stride, out, block_tables, max_blocks, token_slot, positions, tokens, cluster,
+                             heads, kv_heads, page_size, scale, window, in, status, stream);
+#else
+    return mrun_set_error("attn_decode_cluster: not built for head_dim=%d (head sizes 64 and 128 only)", MRUN_HEAD_DIM);
 #endif
 }
 

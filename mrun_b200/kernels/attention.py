@@ -77,6 +77,30 @@ def _split_counters(device: torch.device) -> torch.Tensor:
     return counters
 
 
+CLUSTER_DECODE = True    # False: the planned kernel for every decode step (tests compare the two)
+MAX_CLUSTER = 16
+
+
+def decode_cluster(library, head_dim: int, ratio: int, page_size: int, tokens: int, kv_heads: int) -> int:
+    """Blocks of a thread-block cluster that takes one (token, kv head) pair of a decode step, or
+    0 where the planned kernel runs instead: the cluster kernel takes steps whose pairs fill at
+    most half the device (each pair is then cut into as many pieces as fit), groups of up to 8."""
+    if not CLUSTER_DECODE or ratio > 8 or not decode_uses_tma(library, head_dim, ratio, page_size):
+        return 0
+    pairs = tokens * kv_heads
+    slots = _decode_slots(head_dim, library, ratio)
+    if pairs < 1 or 2 * pairs > slots:
+        return 0
+    cluster = 1
+    while cluster < 8 and 2 * cluster * pairs <= slots:
+        cluster *= 2
+    # sixteen blocks share a part of the device that holds two such clusters: only where the
+    # clusters of the step fill at most half of it
+    if cluster == 8 and MAX_CLUSTER >= 16 and 32 * pairs <= slots:
+        cluster = 16
+    return cluster
+
+
 def supports_tensor_cores(dtype: torch.dtype, head_dim: int, group: int) -> bool:
     return dtype == torch.bfloat16 and head_dim % 16 == 0 and 16 <= head_dim <= 256 and group <= 64
 
@@ -194,15 +218,21 @@ def paged_attention(q: torch.Tensor, q_stride: int, out: torch.Tensor, cache, gr
     if ctx.all_decode and ratio <= 16:
         if tokens * kv_heads > COUNTER_CAPACITY:
             raise ValueError(f"a decode step of {tokens} tokens x {kv_heads} kv heads exceeds {COUNTER_CAPACITY} pairs")
-        tma = decode_uses_tma(library, head_dim, ratio, page_size)
-        blocks, splits = decode_launch(tokens, kv_heads, decode_slots(head_dim, ratio, page_size))
-        part_o = torch.empty((blocks, 2, 16, head_dim), dtype=torch.float32, device=q.device)
-        part_ml = torch.empty((blocks, 2, 16, 2), dtype=torch.float32, device=q.device)
         fused = (_c_int(0), _ptr(None), _ptr(None), _c_float(0.0), _ptr(None), _c_int(0), _ptr(None))
         if raw is not None:
             q_weight, k_weight, eps, rot, rotary_dim, slots = raw
             fused = (_c_int(1), _ptr(q_weight), _ptr(k_weight), _c_float(eps), _ptr(rot), _c_int(rotary_dim),
                      _ptr(slots))
+        cluster = decode_cluster(library, head_dim, ratio, page_size, tokens, kv_heads)
+        if cluster:
+            status = ops.status_word(q.device, "attn_decode_tma", {1: "the TMA producer", 2: "the consumer warps"})
+            library.call("mrun_attn_decode_cluster", _ptr(q), _c_long(q_stride), _ptr(out), *common, _c_int(tokens),
+                         _c_int(cluster), *tail[:-1], *fused, _ptr(None), _c_long(pages), _ptr(status), tail[-1])
+            return out
+        tma = decode_uses_tma(library, head_dim, ratio, page_size)
+        blocks, splits = decode_launch(tokens, kv_heads, decode_slots(head_dim, ratio, page_size))
+        part_o = torch.empty((blocks, 2, 16, head_dim), dtype=torch.float32, device=q.device)
+        part_ml = torch.empty((blocks, 2, 16, 2), dtype=torch.float32, device=q.device)
         prefix, assignment = decode_plan(ctx, library, window, kv_heads, blocks, splits)
         extra = ()
         if tma:
@@ -221,7 +251,16 @@ def paged_attention(q: torch.Tensor, q_stride: int, out: torch.Tensor, cache, gr
     shortest = 0
     if ratio <= 16 and decode_uses_tma(library, head_dim, ratio, page_size):
         rows, row_positions, row_slots, n_single = single_tokens(ctx)
-        if n_single and n_single * kv_heads <= COUNTER_CAPACITY:
+        cluster = decode_cluster(library, head_dim, ratio, page_size, n_single, kv_heads) if n_single else 0
+        if cluster:
+            status = ops.status_word(q.device, "attn_decode_tma", {1: "the TMA producer", 2: "the consumer warps"})
+            library.call("mrun_attn_decode_cluster", _ptr(q), _c_long(q_stride), _ptr(out), _ptr(cache.k), _ptr(cache.v),
+                         _ptr(group.block_tables), _c_int(group.max_blocks), _ptr(row_slots), _ptr(row_positions),
+                         _c_int(n_single), _c_int(cluster), *tail[:-1],
+                         _c_int(0), _ptr(None), _ptr(None), _c_float(0.0), _ptr(None), _c_int(0), _ptr(None),
+                         _ptr(rows), _c_long(pages), _ptr(status), tail[-1])
+            shortest = 1
+        elif n_single and n_single * kv_heads <= COUNTER_CAPACITY:
             blocks, splits = decode_launch(n_single, kv_heads, decode_slots(head_dim, ratio, page_size))
             part_o = torch.empty((blocks, 2, 16, head_dim), dtype=torch.float32, device=q.device)
             part_ml = torch.empty((blocks, 2, 16, 2), dtype=torch.float32, device=q.device)

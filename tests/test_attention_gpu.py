@@ -274,6 +274,116 @@ def test_decode_contexts_of_unequal_length_and_raw_input(contexts, blocks, min_t
         assert torch.equal(v_got, v_want)
 
 
+@pytest.mark.parametrize("cluster", [1, 2, 4, 8, 16])
+@pytest.mark.parametrize("heads,kv_heads,head_dim,page_size", [(8, 2, 64, 16), (32, 8, 128, 16), (8, 1, 128, 4), (6, 2, 128, 1),
+                                                               (12, 4, 64, 128), (3, 3, 64, 32)])
+@pytest.mark.parametrize("raw,window", [(False, 0), (True, 0), (False, 100), (True, 200)])
+def test_cluster_decode_with_every_cluster_size(cluster, heads, kv_heads, head_dim, page_size, raw, window):
+    """The decode kernel that gives every (token, kv head) pair a thread-block cluster, called
+    directly with clusters of 1 to 16 blocks over contexts from one key to thousands (pairs with
+    fewer tiles than blocks leave blocks without work), with padding rows, windows, and the raw
+    q, k, v rows that it norms, rotates and stores itself; twice in a row, against the stand-alone
+    kernel followed by the CUDA-core attention.  Twice the same call gives the same bits."""
+    from mrun_b200.kernels import lib as L, ops
+    from mrun_b200.kernels.ops import _c_float, _c_int, _c_long, _ptr, _stream
+    contexts = [0, 63, 64, 700, 1023, 129, 5000, 17]
+    eps, rotary = 1e-5, head_dim
+    case = Case([(c, 1) for c in contexts], heads, kv_heads, head_dim, page_size, torch.bfloat16, seed=5 + cluster,
+                window=window, pad=2)
+    scale = head_dim ** -0.5
+    n = case.tokens + case.pad
+    g = torch.Generator().manual_seed(17)
+    width = (heads + 2 * kv_heads) * head_dim
+    qkv = torch.randn(n, width, generator=g).to(torch.bfloat16).to(DEV)
+    q_weight = (1 + 0.2 * torch.randn(head_dim, generator=g)).to(DEV)
+    k_weight = (1 + 0.2 * torch.randn(head_dim, generator=g)).to(DEV)
+    angle = torch.rand(n, rotary // 2, generator=g) * 6.28
+    rot = torch.stack([angle.cos(), angle.sin()], dim=-1).contiguous().to(DEV)
+    slots = [case.seg_pages[s][c // page_size] * page_size + c % page_size for s, c in enumerate(contexts)] + [-1] * case.pad
+    slots = torch.tensor(slots, dtype=torch.int32, device=DEV)
+    library = L.attention(head_dim)
+    k_want, v_want = case.kd.clone(), case.vd.clone()
+    if raw:
+        q_want = qkv.clone()
+        ops.qk_norm_rope_cache(q_want, heads, kv_heads, head_dim, q_weight, k_weight, eps, rot, rotary, slots,
+                               k_want, v_want, page_size)
+    else:
+        q_want = case.qd
+    want = torch.zeros((n, heads * head_dim), dtype=torch.bfloat16, device=DEV)
+    ops.paged_attention_generic(q_want, q_want.stride(0), want, k_want, v_want, case.table, case.ctx.token_slot,
+                                case.ctx.positions, heads, scale, window)
+    want = want.float().cpu()
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    outs = []
+    for _ in range(2):
+        k_got, v_got = case.kd.clone(), case.vd.clone()
+        q_in = qkv if raw else case.qd
+        out = torch.full((n, heads * head_dim), 3.0, dtype=torch.bfloat16, device=DEV)
+        fused = ((_c_int(1), _ptr(q_weight), _ptr(k_weight), _c_float(eps), _ptr(rot), _c_int(rotary), _ptr(slots)) if raw
+                 else (_c_int(0), _ptr(None), _ptr(None), _c_float(0.0), _ptr(None), _c_int(0), _ptr(None)))
+        library.call(
+            "mrun_attn_decode_cluster", _ptr(q_in), _c_long(q_in.stride(0)), _ptr(out), _ptr(k_got), _ptr(v_got),
+            _ptr(case.table), _c_int(case.group.max_blocks), _ptr(case.ctx.token_slot), _ptr(case.ctx.positions),
+            _c_int(n), _c_int(cluster), _c_int(heads), _c_int(kv_heads), _c_int(head_dim), _c_int(page_size),
+            _c_float(scale), _c_int(window), *fused, _ptr(None), _c_long(case.kd.shape[0]), _ptr(status), _stream())
+        got = out.float().cpu()
+        assert int(status.item()) == 0
+        assert (got - want).abs().max() <= 2e-2 * want.abs().max()
+        assert got[case.tokens:].abs().max() == 0, "padding rows must come out as zeros"
+        assert (k_got.float() - k_want.float()).abs().max() <= 2e-2 * k_want.float().abs().max()
+        assert torch.equal(v_got, v_want)
+        outs.append(out)
+    assert torch.equal(outs[0], outs[1])
+
+
+def test_cluster_decode_refuses_what_it_cannot_take():
+    from mrun_b200.kernels import lib as L
+    from mrun_b200.kernels.lib import KernelError
+    from mrun_b200.kernels.ops import _c_float, _c_int, _c_long, _ptr, _stream
+    case = Case([(10, 1)], 32, 2, 64, 16, torch.bfloat16)                       # 16 query heads a kv head
+    out = torch.zeros((1, 32 * 64), dtype=torch.bfloat16, device=DEV)
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    def call(cluster, heads):
+        L.attention(64).call(
+            "mrun_attn_decode_cluster", _ptr(case.qd), _c_long(case.qd.stride(0)), _ptr(out), _ptr(case.kd), _ptr(case.vd),
+            _ptr(case.table), _c_int(case.group.max_blocks), _ptr(case.ctx.token_slot), _ptr(case.ctx.positions),
+            _c_int(1), _c_int(cluster), _c_int(heads), _c_int(2), _c_int(64), _c_int(16), _c_float(0.125), _c_int(0),
+            _c_int(0), _ptr(None), _ptr(None), _c_float(0.0), _ptr(None), _c_int(0), _ptr(None), _ptr(None),
+            _c_long(case.kd.shape[0]), _ptr(status), _stream())
+    with pytest.raises(KernelError, match="query heads per kv head exceed"):
+        call(4, 32)
+    with pytest.raises(KernelError, match="cluster of 3 blocks"):
+        call(3, 8)
+
+
+def test_the_router_gives_small_decode_steps_to_clusters_and_large_ones_to_the_plan(monkeypatch):
+    """Seven tokens x 8 kv heads fill less than half the device: a cluster a pair, no plan.  With
+    the cluster kernel switched off, and for steps with more pairs, the planned kernel runs."""
+    from mrun_b200.kernels import attention
+    heads, kv_heads, head_dim, page_size = 32, 8, 128, 16
+    scale = head_dim ** -0.5
+    segments = [(0, 1), (63, 1), (64, 1), (700, 1), (15, 1), (1023, 1), (200, 1)]
+    case = Case(segments, heads, kv_heads, head_dim, page_size, torch.bfloat16, seed=3, pad=1)
+    want = case.reference(scale)
+    library = attention._lib.attention(head_dim)
+    assert attention.decode_cluster(library, head_dim, 4, page_size, 8, kv_heads) == 4
+    assert attention.decode_cluster(library, head_dim, 4, page_size, 1, kv_heads) == 16
+    assert attention.decode_cluster(library, head_dim, 4, page_size, 2, kv_heads) == 8      # sixteen would crowd
+    assert attention.decode_cluster(library, head_dim, 4, page_size, 16, kv_heads) == 2
+    assert attention.decode_cluster(library, head_dim, 4, page_size, 19, kv_heads) == 0     # 152 pairs: more than half
+    assert attention.decode_cluster(library, head_dim, 16, page_size, 1, kv_heads) == 0     # a group of 16
+    got = case.run(scale)
+    assert not any(isinstance(key, tuple) and key[0] == "decode_plan" for key in case.ctx.shared)
+    assert (got[:case.tokens] - want[:case.tokens]).abs().max() <= 2e-2 * want.abs().max()
+    monkeypatch.setattr(attention, "CLUSTER_DECODE", False)
+    case.ctx.shared.clear()
+    planned = case.run(scale)
+    assert any(isinstance(key, tuple) and key[0] == "decode_plan" for key in case.ctx.shared)
+    assert (planned[:case.tokens] - want[:case.tokens]).abs().max() <= 2e-2 * want.abs().max()
+    ops_status = attention.ops.tc5_check
+    ops_status()
+
+
 @pytest.mark.parametrize("far", [0, 15, 16, 63, 64, 65, 127, 255, 256, 400, 511])
 def test_one_far_key_among_hundreds_carries_the_result(far):
     """The query is aligned with one key (score far above the rest) whose value is a marker: the

@@ -146,8 +146,16 @@ def test_single_tokens_beside_portions_take_the_decode_kernel(monkeypatch):
     check_status()
     rows, positions, slots, n = case.ctx.shared["single_tokens"]
     assert n == 4 and rows.tolist() == [300, 301, 302, 343] and positions.tolist() == [2000, 513, 64, 4095]
-    assert any(key[0] == "decode_plan" and key[-1] for key in case.ctx.shared if isinstance(key, tuple))
+    # four single tokens x 8 kv heads: a cluster a pair, no plan
+    assert not any(key[0] == "decode_plan" for key in case.ctx.shared if isinstance(key, tuple))
     assert (got - want).abs().max() <= 2e-2 * want.abs().max()
+    # the planned decode kernel over the same selection of rows
+    monkeypatch.setattr(attention, "CLUSTER_DECODE", False)
+    case.ctx.shared.clear()
+    planned = case.run(scale)
+    check_status()
+    assert any(key[0] == "decode_plan" and key[-1] for key in case.ctx.shared if isinstance(key, tuple))
+    assert (planned - want).abs().max() <= 2e-2 * want.abs().max()
     # the same step with the decode kernel switched off: the 64-row tiles take the single tokens
     monkeypatch.setattr(attention, "TMA_DECODE", False)
     case.ctx.shared.clear()
