@@ -552,7 +552,7 @@ decode_cluster_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_co
     const unsigned rank = blockIdx.x, pieces = gridDim.x;
     const int pair = blockIdx.y, tok = pair / kv_heads, kvh = pair - tok * kv_heads;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int pos = positions[tok];
+    const int pos = positions[tok], slot_row = token_slot[tok];      // asked for together: one trip
     const int q_row = fused.rows ? fused.rows[tok] : tok;
     if (pos < 0) {                                   // a padding row: zeros, and the whole cluster leaves
         if (rank == 0)
@@ -574,19 +574,13 @@ decode_cluster_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_co
         aborted = 0;
         mbar_init_fence();
     }
-    // rows of a V tile that no copy fills must not hold NaN patterns: 0 * NaN is NaN
-    if (len > 0)
-        for (int s = 0; s < RING && s < len; ++s)
-            for (int i = threadIdx.x; i < TILE_BYTES / 16; i += TMA_THREADS)
-                reinterpret_cast<uint4*>(ring + s * STAGE_BYTES + TILE_BYTES)[i] = make_uint4(0, 0, 0, 0);
-    fence_async_smem();
     __syncthreads();
 
     if (warp == 4) {
         // ------------------------------------------------------------------------------ producer
         const int box_rows = page_size < BLOCK_N ? page_size : BLOCK_N;
         const int boxes = BLOCK_N / box_rows;
-        const int* table = block_tables + (size_t)token_slot[tok] * max_blocks;
+        const int* table = block_tables + (size_t)slot_row * max_blocks;
         bool alive = true;
         int it = 0;
         for (int block = first_block; alive && block <= last_block; ++block, ++it) {
@@ -600,6 +594,17 @@ decode_cluster_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_co
                 const int first_key = key0 + b * box_rows;
                 if (first_key <= pos && first_key + box_rows - 1 >= lo && table[first_key >> page_shift] >= 0)
                     bytes += (unsigned)(2 * box_rows * D * 2);
+            }
+            // Rows of a V tile that no copy fills must not hold NaN patterns (0 * NaN is NaN): the
+            // lane that leaves a box out clears the box's V rows itself, before it arrives.
+            for (int b = lane; b < boxes; b += 32) {
+                const int first_key = key0 + b * box_rows;
+                if (first_key <= pos && first_key + box_rows - 1 >= lo && table[first_key >> page_shift] >= 0) continue;
+#pragma unroll
+                for (int h = 0; h < SPANS; ++h) {
+                    uint4* rows = reinterpret_cast<uint4*>(stage + TILE_BYTES + h * SPAN_BYTES + b * box_rows * 128);
+                    for (int i = 0; i < box_rows * 8; ++i) rows[i] = make_uint4(0, 0, 0, 0);
+                }
             }
             if (bytes) mbar_expect_tx(&full_bar[s], bytes);
             else mbar_arrive(&full_bar[s]);
@@ -763,12 +768,11 @@ decode_cluster_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_co
         if (rank == 0 && warp < 4) {
             for (int i = threadIdx.x; i < group * (D / 4); i += CONSUMERS) {
                 const int row = i / (D / 4), d = (i - row * (D / 4)) * 4;
-                float mm = -INFINITY;
-                for (unsigned p = 0; p < pieces; ++p)
-                    mm = fmaxf(mm, cluster_load2(cluster_address(piece + row * PS + D, p)).x);
+                // four pieces a round, all of a round's loads requested before any is used; the
+                // running maximum rescales what the rounds before have added
+                float mm = -INFINITY, ll = 0.f;
                 float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-                float ll = 0.f;
-                for (unsigned p0 = 0; p0 < pieces; p0 += 4) {   // four pieces requested before any is used
+                for (unsigned p0 = 0; p0 < pieces; p0 += 4) {
                     float2 ml[4];
                     float4 po[4];
 #pragma unroll
@@ -780,6 +784,13 @@ decode_cluster_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_co
                             po[k] = cluster_load4(cluster_address(piece + row * PS + d, p0 + k));
                         }
                     }
+                    float round_max = mm;
+#pragma unroll
+                    for (unsigned k = 0; k < 4; ++k) round_max = fmaxf(round_max, ml[k].x);
+                    const float keep = (mm == -INFINITY) ? 0.f : exp2f(mm - round_max);
+                    acc.x *= keep; acc.y *= keep; acc.z *= keep; acc.w *= keep;
+                    ll *= keep;
+                    mm = round_max;
 #pragma unroll
                     for (unsigned k = 0; k < 4; ++k) {
                         const float c = (ml[k].x == -INFINITY) ? 0.f : exp2f(ml[k].x - mm);
