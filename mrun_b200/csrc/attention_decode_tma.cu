@@ -204,7 +204,7 @@ decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_consta
     }
     // The producer looks its first run of tiles up (plan, positions: dependent loads from global
     // memory) while the block prepares its shared memory.  (Also reading the block-table entries
-    // of the first tiles and prefetching the tensor maps here made the kernel slower, 12.7 -> 13.5 us.)
+    // of the first tiles and prefetching the tensor maps here made the kernel slower.)
     Segment first_sg = {};
     int first_kvh = mine.z, first_tok = mine.w;
     if (warp == 4 && u_begin < u_end)
@@ -436,7 +436,7 @@ decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_consta
                     __threadfence();
                     // A thread takes four values of a row.  The pieces are read four at a time, all
                     // loads of a round requested before any is used (one piece after the other the
-                    // merge of four pieces took 3.9 us of a 13 us block).
+                    // merge took a third of a block's time).
                     for (int i = threadIdx.x; i < group * (D / 4); i += CONSUMERS) {
                         const int row = i / (D / 4), d = (i - row * (D / 4)) * 4;
                         // block p's piece of this pair is its first segment iff its range starts inside the pair

@@ -300,7 +300,7 @@ __global__ void qk_norm_rope_cache_kernel(TA* __restrict__ qkv, const float* __r
 // LANES / 2 further along holds j + head_dim / 2) travel by shuffles.  A group of lanes takes
 // QK_HEADS_PER_GROUP consecutive heads of one token, so the token's cosines and sines and the
 // norm weights are read once for all of them.  The arithmetic is the scalar kernel's, value by value.
-constexpr int QK_HEADS_PER_GROUP = 4;    // measured on B200: 8 heads 20 us, 4 heads 15 us, 2 heads 24 us (2048 tokens, 48 heads of 128)
+constexpr int QK_HEADS_PER_GROUP = 4;    // the fastest of 2, 4 and 8 heads a lane group on B200
 
 template <int LANES>
 __global__ void __launch_bounds__(256, 4)
@@ -480,7 +480,7 @@ __global__ void swiglu_kernel(const TA* __restrict__ gate_up, TA* __restrict__ o
 
 // Eight outputs per thread with 16-byte loads and stores, for widths that are a multiple of 8.
 // One group a thread: with two or four groups in flight per thread the kernel was slower
-// (2,048 x 12,288 outputs, bfloat16: 24.8 us, 6.1 TB/s with one; 27 to 29 us with two; 37 us with four).
+// (by 10 to 50 per cent at 2,048 x 12,288 outputs).
 template <typename TA>
 __global__ void __launch_bounds__(256)
 swiglu_vec_kernel(const TA* __restrict__ gate_up, TA* __restrict__ out, long total8, int inter, int block, int act) {

@@ -89,7 +89,7 @@ sample_kernel(const float* __restrict__ logits, int vocab, const float* __restri
     if (!(temp > 0.f)) {  // greedy
         ArgMax best{-INFINITY, 0x7fffffff};
         if ((((uintptr_t)x) & 15) == 0) {
-            // four logits a load, four loads in flight (151,936 logits in L2: 10.9 -> 9.9 us)
+            // four logits a load, four loads in flight
             const int quads = vocab >> 2;
             const float4* x4 = reinterpret_cast<const float4*>(x);
             for (int q0 = tid; q0 < quads; q0 += 4 * THREADS) {

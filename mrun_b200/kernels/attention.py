@@ -112,18 +112,16 @@ MAX_SPLITS = 32    # the most blocks one (token, kv head) pair is cut into when 
 
 
 def decode_launch(tokens: int, kv_heads: int, slots: int):
-    """(blocks, splits) of a decode step.  More (token, kv head) pairs than the device holds
-    blocks: all its blocks, the tiles dealt evenly across pairs (splits = 0).  Else every block
-    stays with one pair, since a block that never changes pair has no partial result to hand over
-    (measured with the TMA kernel at 1,024-token contexts: 288 pairs on 288 blocks 28 us,
-    5.3 TB/s; 320 pairs dealt to 296 blocks 41 us, 4.1 TB/s): the launch fills the device once,
-    every kv head has the same number of blocks, and the plan deals them to the head's pairs by
-    their length, at most ``splits`` to one pair."""
+    """(blocks, splits) of a decode step of the planned kernel.  More (token, kv head) pairs than
+    the device holds blocks: all its blocks, the tiles dealt evenly across pairs (splits = 0).
+    Else every block stays with one pair, since a block that never changes pair has no partial
+    result to hand over: the launch fills the device once, every kv head has the same number of
+    blocks, and the plan deals them to the head's pairs by their length, at most ``splits`` to
+    one pair."""
     pairs = tokens * kv_heads
     if pairs > slots:
         # k pairs a block where that leaves at least four fifths of the blocks busy: with equal
-        # contexts every block then takes whole pairs and hands nothing over (512 pairs of 16
-        # tiles: 296 blocks 57 us, 256 blocks of two pairs 49 us)
+        # contexts every block then takes whole pairs and hands nothing over
         k = -(-pairs // slots)
         aligned = -(-pairs // k)
         return (aligned if 5 * aligned >= 4 * slots else slots), 0

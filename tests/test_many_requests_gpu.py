@@ -117,3 +117,26 @@ def test_captured_decode_steps_of_many_requests(name, dtype, live, tmp_path):
         ex.release(r)
     ex.cache.check_invariants()
     print(f"{name}/{dtype}/{live}: worst {worst:.2e}")
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_forty_requests_through_the_entry_point(dtype, tmp_path):
+    """``Engine.generate`` with 40 prompts live at once: prompt portions beside up to 39 decoding
+    requests, then the pipelined 64-row captured step; every request's tokens are the plain
+    implementation's (bfloat16: up to near-ties), and everything is given back."""
+    from mrun_b200 import Engine
+    from test_engine_gpu import plain_tokens_match
+    name = "E"
+    settings = TINY[name]
+    folder = make_folder(name, str(tmp_path / "model"))
+    cfg, weights = plain.load_folder(folder)
+    prompts = [random_tokens(cfg["vocab_size"], n, seed=9000 + i) for i, n in enumerate(lengths_for(40))]
+    engine = Engine.from_folder(folder, dtype=dtype, page_size=settings["page_size"], context=40 * 192,
+                                max_batch_tokens=96, max_requests=64)
+    runs = engine.generate(prompts, max_tokens=6, ignore_eos=True)
+    assert max(engine.executor._graphs) == 64
+    for prompt, run in zip(prompts, runs):
+        assert run.finish_reason == "length" and len(run.tokens) == 6
+        plain_tokens_match(cfg, weights, prompt, run.tokens, margin=1e-3 if dtype == "float32" else 0.05)
+    engine.executor.cache.check_invariants()
+    assert not engine.executor.cache.live and engine.executor.cache.free_pages() == engine.executor.cache.num_pages
