@@ -133,10 +133,10 @@ def test_forty_requests_through_the_entry_point(dtype, tmp_path):
     prompts = [random_tokens(cfg["vocab_size"], n, seed=9000 + i) for i, n in enumerate(lengths_for(40))]
     engine = Engine.from_folder(folder, dtype=dtype, page_size=settings["page_size"], context=40 * 192,
                                 max_batch_tokens=96, max_requests=64)
-    runs = engine.generate(prompts, max_tokens=6, ignore_eos=True)
+    runs = engine.generate(prompts, max_tokens=48, ignore_eos=True)      # long enough for all 40 to decode side by side
     assert max(engine.executor._graphs) == 64
     for prompt, run in zip(prompts, runs):
-        assert run.finish_reason == "length" and len(run.tokens) == 6
+        assert run.finish_reason == "length" and len(run.tokens) == 48
         plain_tokens_match(cfg, weights, prompt, run.tokens, margin=1e-3 if dtype == "float32" else 0.05)
     engine.executor.cache.check_invariants()
     assert not engine.executor.cache.live and engine.executor.cache.free_pages() == engine.executor.cache.num_pages
