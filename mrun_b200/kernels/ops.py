@@ -457,12 +457,28 @@ def linear(x, w: torch.Tensor, out_dtype: Optional[torch.dtype] = None,
 
 
 def linear_or_pending(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = None):
-    """The last product of a part whose caller accepts a :class:`PendingLinear`: left pending where
-    the decode GEMM would take it (the norm after it then runs it with its epilogue), computed
-    otherwise."""
-    if bias is None and skinny_ok(x, w):
+    """The last product of a part whose caller accepts a :class:`PendingLinear`: left pending in
+    bfloat16 without a bias (the norm after it then runs it with the residual sum folded in: in
+    the decode GEMM's epilogue up to 16 rows, as the vendor GEMM's accumulate-into-C above),
+    computed otherwise."""
+    if bias is None and x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16:
         return PendingLinear(x, w)
     return linear(x, w, bias=bias)
+
+
+def accumulate_ok(pending, resid: torch.Tensor) -> bool:
+    """Whether :func:`linear_add_into` takes this pending product and residual stream."""
+    return (isinstance(pending, PendingLinear) and isinstance(pending.x, torch.Tensor) and not tc5_ok(pending.x, pending.w)
+            and not skinny_ok(pending.x, pending.w)
+            and pending.x.dtype == torch.bfloat16 and pending.w.dtype == torch.bfloat16 and pending.x.dim() == 2
+            and resid.dtype == torch.float32 and resid.is_contiguous() and tuple(resid.shape) == tuple(pending.shape))
+
+
+def linear_add_into(resid: torch.Tensor, pending: PendingLinear) -> torch.Tensor:
+    """resid += pending.x @ pending.w.T in place: the vendor GEMM with bfloat16 operands, 32-bit
+    accumulation and the 32-bit stream as its C and D, so that the product is never rounded to
+    bfloat16, written and read again (prompt portions and decode batches above 16 rows)."""
+    return torch.addmm(resid, pending.x, pending.w.t(), out_dtype=torch.float32, out=resid)
 
 
 def sample(logits: torch.Tensor, out: torch.Tensor, temperature: Optional[torch.Tensor] = None,

@@ -20,7 +20,8 @@ class RMSNorm:
 
     # ``delta`` may be a product that has not run yet (``ops.PendingLinear``): with a handful
     # of rows it runs with the residual sum and this norm folded into its epilogue, and what
-    # comes back is ``ops.NormedRows`` (the row scale is applied by the product that reads it).
+    # comes back is ``ops.NormedRows`` (the row scale is applied by the product that reads it);
+    # with more rows the vendor GEMM adds it into the 32-bit stream itself.
     accepts_pending = True
 
     def __init__(self, spec: RMSNormSpec, tensors, runtime: Runtime):
@@ -32,7 +33,11 @@ class RMSNorm:
         if isinstance(delta, ops.PendingLinear):
             if ops.norm_fusable(delta, resid, self.weight):
                 return ops.linear_into_norm(delta, resid, self.weight, self.eps)
-            delta = delta.compute()
+            if ops.accumulate_ok(delta, resid):
+                ops.linear_add_into(resid, delta)          # the sum rides in the vendor GEMM
+                delta = None
+            else:
+                delta = delta.compute()
         out = torch.empty(resid.shape, dtype=self.act, device=resid.device)
         return ops.add_rmsnorm(resid, delta, self.weight, self.eps, out)
 
