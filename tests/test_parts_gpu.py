@@ -142,6 +142,8 @@ def test_block_and_model(dtype, name):
     for ctx, manager, start, n in one_request_context([block.mixer], [0] * L, rt):
         resid = x.to(DEV).clone()
         delta = block.forward(resid, None, ctx, manager.entries[0])
+        if not isinstance(delta, torch.Tensor):            # the last product, left for the next norm to run
+            delta = delta.compute()
         got = (resid + delta.float()).cpu()
     assert (got - want).abs().max() <= tolerance(dtype) * want.abs().max()
     # the whole model on one request, cut in two steps
