@@ -67,7 +67,12 @@ class Executor:
         self.steps_run = 0
         self.launches = LaunchCounter()
         self.use_graphs = self.model.graph_safe
-        self._graphs: Dict[int, "DecodeGraph"] = {}
+        # captured decode steps: rows (a power of two) -> reach -> graph.  The reach is an upper
+        # bound of the contexts a graph was captured for (parts see it as ``ctx.max_kv_len`` and
+        # may choose kernels by it); the host takes the smallest reach that covers the step.
+        self._graphs: Dict[int, Dict[int, "DecodeGraph"]] = {}
+        self._graph_tokens: Dict[int, torch.Tensor] = {}
+        self._last_graph: Dict[int, "DecodeGraph"] = {}
 
     # ------------------------------------------------------------------ requests
     def admit(self, request_id: object) -> RequestCache:
@@ -136,6 +141,16 @@ class Executor:
             bucket *= 2
         return bucket if bucket <= max(1, self.cache.max_requests) * 2 else None
 
+    REACHES = (4096, 16384)
+
+    def decode_reach(self, longest: int) -> int:
+        """The context bound of the captured step that takes a step whose longest request will
+        hold ``longest`` tokens: 4,096, 16,384 or the model's positions."""
+        for reach in self.REACHES:
+            if longest <= reach < self.spec.max_positions:
+                return reach
+        return self.spec.max_positions
+
     def decode_step(self, entries: Sequence[StepEntry], sampling=None,
                     sources: Optional[Sequence[int]] = None) -> torch.Tensor:
         """One token for each entry (each brings exactly one token) through a captured graph,
@@ -156,9 +171,15 @@ class Executor:
         bucket = self.decode_bucket(len(entries))
         if bucket is None:
             raise StepError(f"no captured decode step takes {len(entries)} requests")
-        graph = self._graphs.get(bucket)
+        reach = self.decode_reach(max(e.request.length for e in entries) + 1)
+        graph = self._graphs.get(bucket, {}).get(reach)
         if graph is None:
-            graph = self._graphs[bucket] = DecodeGraph(self, bucket)
+            tokens = self._graph_tokens.get(bucket)
+            if tokens is None:       # one output a size: a step may take its tokens from a step of another reach
+                tokens = self._graph_tokens[bucket] = torch.zeros(bucket, dtype=torch.int32, device=self.device)
+            graph = DecodeGraph(self, bucket, reach, tokens)
+            self._graphs.setdefault(bucket, {})[reach] = graph
+        self._last_graph[bucket] = graph
         plan = self.cache.plan_append([(e.request, 1) for e in entries])
         try:
             base = sampling if sampling is not None else _greedy_rows
@@ -181,7 +202,7 @@ class Executor:
     def decode_logits(self, entries: Sequence[StepEntry]) -> torch.Tensor:
         """The logits of the last :meth:`decode_step` for its entries."""
         bucket = self.decode_bucket(len(entries))
-        return self._graphs[bucket].logits[:len(entries)]
+        return self._last_graph[bucket].logits[:len(entries)]
 
 
 def _greedy_rows(host, where) -> None:
@@ -195,10 +216,10 @@ class DecodeGraph:
     model runs, one token per row is chosen.  Its inputs live in one static int32 buffer that each
     replay refills; rows beyond the live requests are padding (position -1, no cache slot)."""
 
-    def __init__(self, executor: "Executor", rows: int):
+    def __init__(self, executor: "Executor", rows: int, reach: int, tokens: torch.Tensor):
         from ..kernels import ops
         from .batch import RECENT, GroupView, StepContext, layout
-        self.rows = rows
+        self.rows, self.reach = rows, reach
         cache, model, device = executor.cache, executor.model, executor.device
         keys = list(cache.groups)
         self.where = where = layout(rows, rows, len(keys), rows)
@@ -220,8 +241,8 @@ class DecodeGraph:
             positions=buf[where["positions"]], token_slot=buf[where["token_slot"]],
             seg_q_start=buf[where["seg_q_start"]], seg_kv_len=buf[where["seg_kv_len"]],
             seg_slot=buf[where["seg_slot"]], groups=groups, max_q_len=1,
-            max_kv_len=executor.spec.max_positions, page_size=cache.page_size, real_tokens=rows)
-        self.tokens = torch.zeros(rows, dtype=torch.int32, device=device)
+            max_kv_len=reach, page_size=cache.page_size, real_tokens=rows)
+        self.tokens = tokens
 
         def run():
             self.ctx.shared.clear()

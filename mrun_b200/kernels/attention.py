@@ -81,10 +81,14 @@ CLUSTER_DECODE = True    # False: the planned kernel for every decode step (test
 MAX_CLUSTER = 16
 
 
-def decode_cluster(library, head_dim: int, ratio: int, page_size: int, tokens: int, kv_heads: int) -> int:
+def decode_cluster(library, head_dim: int, ratio: int, page_size: int, tokens: int, kv_heads: int,
+                   max_kv_len: int) -> int:
     """Blocks of a thread-block cluster that takes one (token, kv head) pair of a decode step, or
-    0 where the planned kernel runs instead: the cluster kernel takes steps whose pairs fill at
-    most half the device (each pair is then cut into as many pieces as fit), groups of up to 8."""
+    0 where the planned kernel runs instead.  The cluster kernel takes steps whose pairs fill at
+    most half the device (each pair is then cut into as many pieces as fit), groups of up to 8,
+    and contexts short enough for its pieces: a cluster has at most 16 blocks, so beyond 32 tiles
+    a block (8 where the clusters leave a fifth of the device or more empty) the planned kernel,
+    which cuts a pair into up to 32 pieces, spreads a long context further."""
     if not CLUSTER_DECODE or ratio > 8 or not decode_uses_tma(library, head_dim, ratio, page_size):
         return 0
     pairs = tokens * kv_heads
@@ -98,6 +102,9 @@ def decode_cluster(library, head_dim: int, ratio: int, page_size: int, tokens: i
     # clusters of the step fill at most half of it
     if cluster == 8 and MAX_CLUSTER >= 16 and 32 * pairs <= slots:
         cluster = 16
+    tiles_a_block = -(-(-(-max(1, max_kv_len) // 64)) // cluster)
+    if tiles_a_block > (32 if 5 * cluster * pairs >= 4 * slots else 8):
+        return 0
     return cluster
 
 
@@ -221,7 +228,7 @@ def paged_attention(q: torch.Tensor, q_stride: int, out: torch.Tensor, cache, gr
             q_weight, k_weight, eps, rot, rotary_dim, slots = raw
             fused = (_c_int(1), _ptr(q_weight), _ptr(k_weight), _c_float(eps), _ptr(rot), _c_int(rotary_dim),
                      _ptr(slots))
-        cluster = decode_cluster(library, head_dim, ratio, page_size, tokens, kv_heads)
+        cluster = decode_cluster(library, head_dim, ratio, page_size, tokens, kv_heads, ctx.max_kv_len)
         if cluster:
             status = ops.status_word(q.device, "attn_decode_tma", {1: "the TMA producer", 2: "the consumer warps"})
             library.call("mrun_attn_decode_cluster", _ptr(q), _c_long(q_stride), _ptr(out), *common, _c_int(tokens),
@@ -249,7 +256,7 @@ def paged_attention(q: torch.Tensor, q_stride: int, out: torch.Tensor, cache, gr
     shortest = 0
     if ratio <= 16 and decode_uses_tma(library, head_dim, ratio, page_size):
         rows, row_positions, row_slots, n_single = single_tokens(ctx)
-        cluster = decode_cluster(library, head_dim, ratio, page_size, n_single, kv_heads) if n_single else 0
+        cluster = decode_cluster(library, head_dim, ratio, page_size, n_single, kv_heads, ctx.max_kv_len) if n_single else 0
         if cluster:
             status = ops.status_word(q.device, "attn_decode_tma", {1: "the TMA producer", 2: "the consumer warps"})
             library.call("mrun_attn_decode_cluster", _ptr(q), _c_long(q_stride), _ptr(out), _ptr(cache.k), _ptr(cache.v),

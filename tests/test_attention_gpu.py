@@ -366,12 +366,15 @@ def test_the_router_gives_small_decode_steps_to_clusters_and_large_ones_to_the_p
     case = Case(segments, heads, kv_heads, head_dim, page_size, torch.bfloat16, seed=3, pad=1)
     want = case.reference(scale)
     library = attention._lib.attention(head_dim)
-    assert attention.decode_cluster(library, head_dim, 4, page_size, 8, kv_heads) == 4
-    assert attention.decode_cluster(library, head_dim, 4, page_size, 1, kv_heads) == 16
-    assert attention.decode_cluster(library, head_dim, 4, page_size, 2, kv_heads) == 8      # sixteen would crowd
-    assert attention.decode_cluster(library, head_dim, 4, page_size, 16, kv_heads) == 2
-    assert attention.decode_cluster(library, head_dim, 4, page_size, 19, kv_heads) == 0     # 152 pairs: more than half
-    assert attention.decode_cluster(library, head_dim, 16, page_size, 1, kv_heads) == 0     # a group of 16
+    pick = lambda group, tokens, reach=1024: attention.decode_cluster(library, head_dim, group, page_size, tokens, kv_heads, reach)
+    assert pick(4, 8) == 4 and pick(4, 1) == 16 and pick(4, 16) == 2
+    assert pick(4, 2) == 8                        # sixteen would crowd
+    assert pick(4, 19) == 0                       # 152 pairs: more than half the device
+    assert pick(16, 1) == 0                       # a group of 16
+    # long contexts go to the planned kernel, which cuts a pair into more pieces
+    assert pick(4, 8, 4096) == 4 and pick(4, 8, 16384) == 0
+    assert pick(4, 1, 4096) == 16 and pick(4, 1, 16384) == 0
+    assert pick(4, 4, 16384) == 8 and pick(4, 4, 32768) == 0
     got = case.run(scale)
     assert not any(isinstance(key, tuple) and key[0] == "decode_plan" for key in case.ctx.shared)
     assert (got[:case.tokens] - want[:case.tokens]).abs().max() <= 2e-2 * want.abs().max()

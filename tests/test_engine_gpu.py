@@ -288,3 +288,27 @@ def test_top_logprobs_beside_every_output_token(tiny):
             assert [i for i, _ in top] == [i for i, _ in want] and top[0][0] == token
             assert max(abs(a - b) for (_, a), (_, b) in zip(top, want)) <= 1e-4
             tokens.append(token)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_decoding_across_the_reach_of_a_captured_step(dtype, tmp_path):
+    """Captured decode steps are made for contexts up to 4,096, up to 16,384 or up to the model's
+    positions, and the host takes the smallest that covers the step.  A request whose context
+    crosses 4,096 tokens in the middle of pipelined decoding changes graphs there; its token still
+    comes from the step before, on the device, and the tokens stay the plain implementation's."""
+    from mrun_b200 import Engine
+    from mrun_b200.config import Qwen3Config
+    from mrun_b200.weights import write_random_model
+    from tiny_models import TINY
+    t = TINY["C"]
+    config = Qwen3Config(**dict(t["config"], max_position_embeddings=8192))
+    folder = write_random_model(config, str(tmp_path / "model"), seed=t["seed"], std=t["std"], norm_noise=t["norm_noise"])
+    cfg, weights = plain.load_folder(folder)
+    prompts = [random_tokens(cfg["vocab_size"], n, seed=70 + n) for n in (4090, 37)]
+    engine = Engine.from_folder(folder, dtype=dtype, page_size=16, context=2 * 4224, max_batch_tokens=1024, max_requests=2)
+    runs = engine.generate(prompts, max_tokens=14, ignore_eos=True)
+    graphs = engine.executor._graphs[2]
+    assert sorted(graphs) == [4096, 8192], sorted(graphs)
+    for prompt, run in zip(prompts, runs):
+        assert len(run.tokens) == 14
+        plain_tokens_match(cfg, weights, prompt, run.tokens, margin=1e-3 if dtype == "float32" else 0.05)
