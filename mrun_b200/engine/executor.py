@@ -242,7 +242,9 @@ class DecodeGraph:
             seg_q_start=buf[where["seg_q_start"]], seg_kv_len=buf[where["seg_kv_len"]],
             seg_slot=buf[where["seg_slot"]], groups=groups, max_q_len=1,
             max_kv_len=reach, page_size=cache.page_size, real_tokens=rows)
-        self.tokens = tokens
+        # The warm-up run writes tokens of its own: the shared output may hold the tokens that
+        # the step after this one takes from the device (a graph made in mid-decoding).
+        self.tokens = torch.zeros(rows, dtype=torch.int32, device=device)
 
         def run():
             self.ctx.shared.clear()
@@ -259,6 +261,7 @@ class DecodeGraph:
         run()                               # all rows are padding: nothing is written to the cache
         self.kernels_per_replay = executor.launches.end()
         torch.cuda.synchronize(device)
+        self.tokens = tokens                # the captured step reads and writes the shared output
         self.graph = torch.cuda.CUDAGraph()
         with torch.cuda.graph(self.graph):
             self.logits = run()
