@@ -22,6 +22,10 @@
 // sets the status word (the host reads it after the step and raises) and the block runs to its
 // end without waiting again.
 //
+// A second kernel of the same parts (decode_cluster_kernel, below) serves steps with few pairs:
+// a thread-block cluster takes one pair, cuts its tiles among its blocks and merges their partial
+// results through distributed shared memory, with neither plan nor scratch.
+//
 // Math as in the other attention kernels (crates/mrun-engine/src/models/common.rs:129,199-205).
 #include <cstdio>
 

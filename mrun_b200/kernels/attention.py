@@ -4,11 +4,13 @@ Every kernel reads keys and values from the pages; the tokens of the step were w
 the fused norm/rotary/cache kernel just before.
 
 * float32, or a shape the tensor-core kernels refuse: the CUDA-core kernel in 32-bit arithmetic.
-* bfloat16, every segment a single token: a decode kernel, which deals the key tiles of all
-  (token, kv head) pairs evenly to as many blocks as the device holds (scratch for the partial
-  results of pairs shared between blocks, merged by the block that finishes last).  Head sizes 64
-  and 128 with power-of-two pages: the kernel whose tiles a producer warp brings by TMA into a
-  ring; else the kernel that copies them with cp.async.
+* bfloat16, every segment a single token: a decode kernel.  Head sizes 64 and 128 with
+  power-of-two pages, few pairs and contexts that are not long: a thread-block cluster a
+  (token, kv head) pair, which cuts the pair's tiles among its blocks and merges through
+  distributed shared memory (no plan, no scratch).  Otherwise the planned kernel, which deals the
+  key tiles of all pairs to as many blocks as the device holds (scratch for the partial results
+  of pairs shared between blocks, merged by the block that finishes last): tiles brought by TMA
+  into a ring for those head and page sizes, else copied with cp.async.
 * bfloat16 otherwise: a step with prompt portions.  Its single-token segments (the decoding
   requests beside the prompts) go through the TMA decode kernel as a selection of the step's rows
   where that kernel takes the shape; the rest as follows.  Head sizes 64 and 128: the tcgen05 kernel (128-row tiles
