@@ -55,6 +55,32 @@ inline cudaError_t launch_kernel(void (*kernel)(KArgs...), dim3 grid, dim3 block
     return cudaLaunchKernelEx(&config, kernel, KArgs(args)...);
 }
 
+// Programmatic dependent launch.  A kernel launched with launch_kernel_overlapped() may begin
+// while the kernel before it in the stream is still running, once that kernel has let it
+// (dependents_may_start(), or its end).  Until wait_for_kernel_before() returns it may only read
+// memory that no kernel of the step writes (weights, the step's index arrays) and may write
+// nothing: the memory of its outputs may still be in use by the kernel before.  A kernel lets its
+// own successor start only after its own wait, so that never more than two kernels share the
+// device.  Both calls do nothing in a kernel that was launched the plain way.
+__device__ __forceinline__ void wait_for_kernel_before() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void dependents_may_start() { asm volatile("griddepcontrol.launch_dependents;"); }
+
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_kernel_overlapped(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem,
+                                            cudaStream_t stream, Args... args) {
+    cudaLaunchConfig_t config = {};
+    config.gridDim = grid;
+    config.blockDim = block;
+    config.dynamicSmemBytes = smem;
+    config.stream = stream;
+    cudaLaunchAttribute attribute[1];
+    attribute[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attribute[0].val.programmaticStreamSerializationAllowed = 1;
+    config.attrs = attribute;
+    config.numAttrs = 1;
+    return cudaLaunchKernelEx(&config, kernel, KArgs(args)...);
+}
+
 __device__ __forceinline__ float to_float(float v) { return v; }
 __device__ __forceinline__ float to_float(__nv_bfloat16 v) { return __bfloat162float(v); }
 

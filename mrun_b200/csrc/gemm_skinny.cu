@@ -10,6 +10,9 @@
 //  * tensor-core products m16n8k16 with W as the 16-row operand and the tokens as the 8 columns.
 //    Inside a 32-wide chunk thread t of a quad owns k = 8t .. 8t+7 of *both* operands, which is a
 //    permutation of the instruction's k order applied to both sides alike, so the sum is the same;
+//  * the kernel is launched so that it may start while the kernel before it still runs
+//    (programmatic dependent launch): a block asks for its first weights, then waits for that
+//    kernel, then reads x;
 //  * the eight partial sums are added in shared memory in warp order (fixed, so a row's result
 //    does not depend on the batch), and the epilogue writes y, or act(gate) * up when W holds
 //    gate and up rows interleaved in runs of eight (rows 16j..16j+7 gate, 16j+8..16j+15 up).
@@ -159,6 +162,10 @@ skinny_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w, TOut* __re
     int c0 = warp;
     load_w(wa[0], c0);
     load_w(wa[1], c0 + STRIDE);
+    // The weights depend on no kernel: their first two batches were asked for while the kernel
+    // before this one may still be running.  Everything else waits for it.
+    mrun::wait_for_kernel_before();
+    mrun::dependents_may_start();
     load_x(xa[0], c0);
     load_x(xa[1], c0 + STRIDE);
     // the rows' totals of squares are asked for with the first weights (an asynchronous copy:
@@ -264,7 +271,8 @@ template <int NT, int MT, int UNROLL, typename TOut, int EPI>
 void launch(const bf16* x, const bf16* w, TOut* y, int M, int N, int K, long ldx, long ldy, const Fusion& f,
             cudaStream_t stream) {
     const int blocks = (N + MT * 16 - 1) / (MT * 16);
-    skinny_kernel<NT, MT, UNROLL, TOut, EPI><<<blocks, THREADS, 0, stream>>>(x, w, y, M, N, K, ldx, ldy, f);
+    mrun::launch_kernel_overlapped(skinny_kernel<NT, MT, UNROLL, TOut, EPI>, dim3(blocks), dim3(THREADS), 0, stream, x, w, y,
+                                   M, N, K, ldx, ldy, f);
 }
 
 int sm_count() {

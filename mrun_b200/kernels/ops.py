@@ -282,7 +282,9 @@ def gemm_skinny(x, w: torch.Tensor, out_dtype: torch.dtype = torch.bfloat16,
                 swiglu_rows: bool = False, activation: str = "silu") -> torch.Tensor:
     """y = x @ w.T for at most 16 rows, reading w once at HBM speed.  ``swiglu_rows``: w holds gate
     and up rows interleaved in runs of eight and y = act(gate) * up has half as many columns.
-    ``x`` may be :class:`NormedRows`."""
+    ``x`` may be :class:`NormedRows`.  ``w`` is a weight: the kernel asks for its first rows while
+    the decode GEMM launched before it may still be running, so it must not be that launch's
+    output (x, the stream and every output are touched only after that kernel has finished)."""
     x, sums, eps = _normed(x)
     _check(x, "x", torch.bfloat16, dense=False); _check(w, "w", torch.bfloat16)
     m, k = x.shape
