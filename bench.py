@@ -249,6 +249,7 @@ def main() -> int:
     parser.add_argument("--prefill-depth", type=int, default=0,
                         help="tokens already in the cache before the timed portion of 2,048 (0: a fresh prompt)")
     parser.add_argument("--skip-e2e", action="store_true")
+    parser.add_argument("--page-size", type=int, default=16, help="keys a cache page holds")
     parser.add_argument("--repeats", type=int, default=5,
                         help="how many times the K timed steps are run (the line carries the median, the "
                              "fastest and the slowest)")
@@ -284,7 +285,7 @@ def main() -> int:
     if args.serve:
         sizes["max_position_embeddings"] = max(sizes["max_position_embeddings"], 16384 + 256 + 64)
     config = Qwen3Config(**sizes)
-    page_size = 16
+    page_size = args.page_size
     if args.serve:
         return serve(args, config, model_name, full_layers, page_size, peaks)
     batches = [8] if args.skip_points else [8, 1, 32 if args.shape == "32b" else 64]

@@ -587,23 +587,37 @@ decode_cluster_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_co
         const int* table = block_tables + (size_t)slot_row * max_blocks;
         bool alive = true;
         int it = 0;
+        // The pages of the next tiles are looked up 32 boxes at a time, one a lane, so that the
+        // loop asks the block table once in several tiles and not once a tile (a dependent load
+        // in front of every copy otherwise); pages smaller than two keys look up as they go.
+        const bool windowed = boxes <= 32;
+        const int tiles_a_window = windowed ? 32 / boxes : 1;
+        int window_page = -1;
         for (int block = first_block; alive && block <= last_block; ++block, ++it) {
             const int s = it % RING, use = it / RING;
+            const int in_window = it % tiles_a_window;
+            if (windowed && in_window == 0) {
+                const int first_key = block * BLOCK_N + lane * box_rows;
+                window_page = (first_key <= pos && first_key + box_rows - 1 >= lo) ? table[first_key >> page_shift] : -1;
+            }
             const bool free_now = use == 0 || mbar_wait(&empty_bar[s], (use - 1) & 1, WAIT_CYCLES, &aborted);
             if (!__all_sync(0xffffffffu, free_now)) { alive = false; break; }
             unsigned char* stage = ring + s * STAGE_BYTES;
             const int key0 = block * BLOCK_N;
+            // lane b takes box b of the tile (boxes <= 32), or boxes b, b + 32, ... of it
+            int my_page = -1;
+            if (windowed) my_page = __shfl_sync(0xffffffffu, window_page, (in_window * boxes + lane) & 31);
             unsigned bytes = 0;
             for (int b = lane; b < boxes; b += 32) {
                 const int first_key = key0 + b * box_rows;
-                if (first_key <= pos && first_key + box_rows - 1 >= lo && table[first_key >> page_shift] >= 0)
+                const bool wanted = first_key <= pos && first_key + box_rows - 1 >= lo;
+                const int page = !wanted ? -1 : windowed ? my_page : table[first_key >> page_shift];
+                if (page >= 0) {
                     bytes += (unsigned)(2 * box_rows * D * 2);
-            }
-            // Rows of a V tile that no copy fills must not hold NaN patterns (0 * NaN is NaN): the
-            // lane that leaves a box out clears the box's V rows itself, before it arrives.
-            for (int b = lane; b < boxes; b += 32) {
-                const int first_key = key0 + b * box_rows;
-                if (first_key <= pos && first_key + box_rows - 1 >= lo && table[first_key >> page_shift] >= 0) continue;
+                    continue;
+                }
+                // Rows of a V tile that no copy fills must not hold NaN patterns (0 * NaN is NaN): the
+                // lane that leaves a box out clears the box's V rows itself, before it arrives.
 #pragma unroll
                 for (int h = 0; h < SPANS; ++h) {
                     uint4* rows = reinterpret_cast<uint4*>(stage + TILE_BYTES + h * SPAN_BYTES + b * box_rows * 128);
@@ -615,7 +629,7 @@ decode_cluster_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_co
             for (int b = lane; b < boxes; b += 32) {
                 const int first_key = key0 + b * box_rows;
                 if (first_key > pos || first_key + box_rows - 1 < lo) continue;
-                const int page = table[first_key >> page_shift];
+                const int page = windowed ? my_page : table[first_key >> page_shift];
                 if (page < 0) continue;
 #pragma unroll
                 for (int h = 0; h < SPANS; ++h) {
