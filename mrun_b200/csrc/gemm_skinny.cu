@@ -381,7 +381,7 @@ __global__ void norm_finish_kernel(const bf16* __restrict__ xw, const unsigned l
 
 MRUN_API int mrun_norm_finish(const void* xw, const unsigned long long* sums, float eps, void* out, int tokens,
                               int width, cudaStream_t stream) {
-    MRUN_REQUIRE(tokens >= 0 && tokens <= 16 && width > 0, "norm_finish: bad sizes tokens=%d width=%d", tokens, width);
+    MRUN_REQUIRE(tokens >= 0 && tokens <= 65535 && width > 0, "norm_finish: bad sizes tokens=%d width=%d", tokens, width);
     if (tokens == 0) return 0;
     norm_finish_kernel<<<tokens, 256, 0, stream>>>((const bf16*)xw, sums, eps, 1.f / (float)width, (bf16*)out, width);
     MRUN_CHECK_LAUNCH("norm_finish");

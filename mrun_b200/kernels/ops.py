@@ -201,9 +201,10 @@ SUMS_UNIT = 2.0 ** -30        # a row's total of squares is a 64-bit integer in 
 
 class NormedRows:
     """The output of an RMSNorm whose row scale has not been applied yet: ``xw`` holds
-    bf16(stream * norm weight) and ``sums`` (int64 [16]) each row's total of squares of the stream
+    bf16(stream * norm weight) and ``sums`` (int64, a row each) each row's total of squares of the stream
     in units of 2^-30.  The decode GEMM takes it as its x and applies rsqrt(total / width + eps)
-    to its own sums; :meth:`finish` makes the plain normed rows."""
+    to its own sums (so does the tcgen05 GEMM for 17 to 128 rows); :meth:`finish` makes the plain
+    normed rows."""
 
     def __init__(self, xw: torch.Tensor, sums: torch.Tensor, eps: float):
         self.xw, self.sums, self.eps = xw, sums, float(eps)
@@ -229,30 +230,31 @@ class NormedRows:
 
 
 class RowSums:
-    """Zeroed 16-row totals for the products of one step: one buffer per device, cleared once at
+    """Zeroed per-row totals for the products of one step: one buffer per device, cleared once at
     the start of a step (:meth:`begin_step`: one memset, which a captured step replays) and handed
     out slice by slice, so that no product clears its own."""
 
-    SLOTS = 1024
+    ROWS = 16 * 1024
     _arenas = {}
 
     @classmethod
     def begin_step(cls, device: torch.device) -> None:
         arena = cls._arenas.get(device)
         if arena is None:
-            arena = cls._arenas[device] = [torch.zeros((cls.SLOTS, 16), dtype=torch.int64, device=device), 0]
+            arena = cls._arenas[device] = [torch.zeros(cls.ROWS, dtype=torch.int64, device=device), 0]
         arena[0].zero_()                   # always: a captured step must clear what other steps left
         arena[1] = 0
 
     @classmethod
-    def take(cls, device: torch.device) -> torch.Tensor:
-        """The next zeroed slice of the step, or a fresh zeroed tensor outside a step or when the
-        step has used all of its slices."""
+    def take(cls, device: torch.device, rows: int = 16) -> torch.Tensor:
+        """The next ``rows`` zeroed totals of the step (a multiple of 16 is taken), or a fresh
+        zeroed tensor outside a step or when the step has used all of its buffer."""
+        rows = -(-rows // 16) * 16
         arena = cls._arenas.get(device)
-        if arena is None or arena[1] >= cls.SLOTS:
-            return torch.zeros(16, dtype=torch.int64, device=device)
-        arena[1] += 1
-        return arena[0][arena[1] - 1]
+        if arena is None or arena[1] + rows > cls.ROWS:
+            return torch.zeros(rows, dtype=torch.int64, device=device)
+        arena[1] += rows
+        return arena[0][arena[1] - rows:arena[1]]
 
 
 class PendingLinear:
@@ -301,14 +303,16 @@ def gemm_skinny(x, w: torch.Tensor, out_dtype: torch.dtype = torch.bfloat16,
 
 def norm_fusable(pending, resid: torch.Tensor, weight: torch.Tensor) -> bool:
     """Whether :func:`linear_into_norm` takes this pending product and residual stream."""
-    return (isinstance(pending, PendingLinear) and skinny_ok(pending.x, pending.w)
+    return (isinstance(pending, PendingLinear) and (skinny_ok(pending.x, pending.w) or tc5_ok(pending.x, pending.w))
             and resid.dtype == torch.float32 and resid.is_contiguous() and resid.shape == pending.shape
             and resid.shape[1] % 32 == 0 and weight.numel() == resid.shape[1])
 
 
 def linear_into_norm(pending: PendingLinear, resid: torch.Tensor, weight: torch.Tensor, eps: float) -> NormedRows:
     """resid += pending.x @ pending.w.T (32-bit, in place) and the RMSNorm of the new rows with
-    ``weight``, as :class:`NormedRows`: one kernel, at most 16 rows."""
+    ``weight``, as :class:`NormedRows`: one kernel (the decode GEMM up to 16 rows, the tcgen05
+    GEMM up to 128)."""
+    skinny = skinny_ok(pending.x, pending.w)
     x, in_sums, in_eps = _normed(pending.x)
     w = pending.w
     _check(x, "x", torch.bfloat16, dense=False); _check(w, "w", torch.bfloat16)
@@ -319,10 +323,14 @@ def linear_into_norm(pending: PendingLinear, resid: torch.Tensor, weight: torch.
         raise KernelError(f"linear_into_norm: x {tuple(x.shape)}, w {tuple(w.shape)}, resid {tuple(resid.shape)}, "
                           f"weight {tuple(weight.shape)}")
     xw = torch.empty((m, n), dtype=torch.bfloat16, device=x.device)
-    out_sums = RowSums.take(x.device)
-    _lib.core().call("mrun_gemm_skinny", _ptr(x), _ptr(w), _ptr(None), dtype_code(torch.bfloat16), _c_int(0),
-                     _c_int(m), _c_int(n), _c_int(k), _c_long(x.stride(0) if m > 1 else max(k, x.stride(0))),
-                     _c_long(n), in_sums, in_eps, _ptr(resid), _ptr(weight), _ptr(xw), _ptr(out_sums), _stream())
+    out_sums = RowSums.take(x.device, m)
+    head = (_ptr(x), _ptr(w), _ptr(None), dtype_code(torch.bfloat16), _c_int(0), _c_int(m), _c_int(n), _c_int(k),
+            _c_long(x.stride(0) if m > 1 else max(k, x.stride(0))), _c_long(n), in_sums, in_eps, _ptr(resid),
+            _ptr(weight), _ptr(xw), _ptr(out_sums))
+    if skinny:
+        _lib.core().call("mrun_gemm_skinny", *head, _stream())
+    else:
+        _lib.core().call("mrun_gemm_tc5", *head, _c_int(0), _ptr(_tc5_status(x.device)), _stream())
     return NormedRows(xw, out_sums, eps)
 
 
@@ -343,32 +351,26 @@ def gemm_f32_nt(x: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] = 
     return out
 
 
-TC5_ROWS = 256            # the tcgen05 GEMM takes up to this many rows
-TC5_COUNTERS = 4096       # 128-row tiles of W that one call may split over k
-_tc5_state = {}           # device -> (counters, status)
+TC5_ROWS = 128            # the tcgen05 GEMM takes up to this many rows
+# Whether products of 17 to 128 rows go to the tcgen05 GEMM.  Off: measured on B200 at the
+# Qwen3-8B shapes it loses to the vendor library at 32, 64 and 128 rows (a kernel that holds tensor
+# memory has its multiprocessor to itself, so nothing of its start overlaps the kernel before).
+TC5_GEMM = False
 
 
-def _tc5_buffers(device: torch.device):
-    """Zeroed tile counters (the kernel leaves them zero) and the status word, one set per device,
-    never reallocated, so that captured graphs may keep their addresses."""
-    state = _tc5_state.get(device)
-    if state is None:
-        state = _tc5_state[device] = (torch.zeros(TC5_COUNTERS, dtype=torch.int32, device=device),
-                                      status_word(device, "gemm_tc5", {1: "the TMA producer", 2: "the MMA issuer",
-                                                                       3: "the epilogue"}))
-    return state
+def _tc5_status(device: torch.device) -> torch.Tensor:
+    return status_word(device, "gemm_tc5", {1: "the TMA producer", 2: "the MMA issuer", 3: "the epilogue",
+                                            4: "the exchange inside a cluster"})
 
 
-# The tcgen05 GEMM is used on request only (MRUN_TC5=1): at 17 to 256 rows the vendor GEMM is faster.
-TC5_DEFAULT = os.environ.get("MRUN_TC5", "0") == "1"
-
-
-def tc5_ok(x: torch.Tensor, w: torch.Tensor) -> bool:
-    """Whether the tcgen05 GEMM is to take this product: switched on (MRUN_TC5=1), 17..256 rows,
-    bf16, K a multiple of 64."""
-    return (TC5_DEFAULT and isinstance(x, torch.Tensor) and x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and SKINNY_ROWS < x.shape[0] <= TC5_ROWS
+def tc5_ok(x, w: torch.Tensor) -> bool:
+    """Whether the tcgen05 GEMM takes this product: 17..128 rows, bf16, K a multiple of 64."""
+    if isinstance(x, NormedRows):
+        x = x.xw
+    return (TC5_GEMM and isinstance(x, torch.Tensor) and x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16
+            and x.dim() == 2 and SKINNY_ROWS < x.shape[0] <= TC5_ROWS
             and x.shape[1] % 64 == 0 and x.stride(1) == 1 and x.stride(0) % 8 == 0 and x.data_ptr() % 16 == 0
-            and w.shape[0] <= 128 * TC5_COUNTERS)
+            and w.is_contiguous() and w.data_ptr() % 16 == 0)
 
 
 _sm_count = {}
@@ -381,29 +383,26 @@ def sm_count(device: torch.device) -> int:
     return n
 
 
-def gemm_tc5(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype = torch.bfloat16,
-             swiglu_rows: bool = False, blocks: Optional[int] = None, activation: str = "silu") -> torch.Tensor:
-    """y = x @ w.T for 1..256 rows on the tcgen05 tensor cores (TMA-fed, accumulators in tensor
-    memory, the work dealt evenly to ``blocks`` thread blocks, by default one per SM).
-    ``swiglu_rows`` as in :func:`gemm_skinny`.  A wait inside the kernel that runs out sets the
-    status word that :func:`tc5_check` reads."""
+def gemm_tc5(x, w: torch.Tensor, out_dtype: torch.dtype = torch.bfloat16, swiglu_rows: bool = False,
+             activation: str = "silu", split: int = 0) -> torch.Tensor:
+    """y = x @ w.T for 1..128 rows on the tcgen05 tensor cores (TMA-fed, accumulators in tensor
+    memory, k split over thread-block clusters whose blocks exchange partial sums through
+    distributed shared memory; ``split`` = 0 lets the library choose the cluster size).
+    ``swiglu_rows`` as in :func:`gemm_skinny`; ``x`` may be :class:`NormedRows`; ``w`` is a weight
+    (its first tiles are asked for before the kernel before has finished).  A wait inside the
+    kernel that runs out sets the status word that :func:`tc5_check` reads."""
+    x, sums, eps = _normed(x)
     _check(x, "x", torch.bfloat16, dense=False); _check(w, "w", torch.bfloat16)
     m, k = x.shape
     n = w.shape[0]
     if w.shape[1] != k:
         raise KernelError(f"gemm_tc5: x {tuple(x.shape)} vs w {tuple(w.shape)}")
-    if blocks is None:
-        blocks = sm_count(x.device)
     out = torch.empty((m, n // 2 if swiglu_rows else n), dtype=out_dtype, device=x.device)
-    counters, status = _tc5_buffers(x.device)
-    core = _lib.core()
-    query = core._dll.mrun_gemm_tc5_scratch_floats
-    query.restype = ctypes.c_long
-    partial = torch.empty(max(1, query(_c_int(m), _c_int(blocks))), dtype=torch.float32, device=x.device)
-    core.call("mrun_gemm_tc5", _ptr(x), _ptr(w), _ptr(out), dtype_code(out_dtype),
-              _c_int(gate_code(activation) if swiglu_rows else 0),
-              _c_int(m), _c_int(n), _c_int(k), _c_long(x.stride(0) if m > 1 else max(k, x.stride(0))),
-              _c_long(out.shape[1]), _c_int(blocks), _ptr(partial), _ptr(counters), _ptr(status), _stream())
+    _lib.core().call("mrun_gemm_tc5", _ptr(x), _ptr(w), _ptr(out), dtype_code(out_dtype),
+                     _c_int(gate_code(activation) if swiglu_rows else 0), _c_int(m), _c_int(n), _c_int(k),
+                     _c_long(x.stride(0) if m > 1 else max(k, x.stride(0))), _c_long(out.shape[1]),
+                     sums, eps, _ptr(None), _ptr(None), _ptr(None), _ptr(None), _c_int(split),
+                     _ptr(_tc5_status(x.device)), _stream())
     return out
 
 
@@ -439,8 +438,8 @@ def linear(x, w: torch.Tensor, out_dtype: Optional[torch.dtype] = None,
     accumulation (the reference calls its array library's matmul for the same products and adds
     an optional bias after it, crates/mrun-engine/src/load.rs:294-306)."""
     if isinstance(x, NormedRows):
-        if skinny_ok(x, w):
-            y = gemm_skinny(x, w, out_dtype or torch.bfloat16)
+        if skinny_ok(x, w) or tc5_ok(x, w):
+            y = (gemm_skinny if skinny_ok(x, w) else gemm_tc5)(x, w, out_dtype or torch.bfloat16)
             return y if bias is None else add_bias(y, bias)
         x = x.finish()
     if x.dtype == torch.float32:

@@ -233,10 +233,15 @@ def test_gemm_skinny_with_the_residual_sum_and_the_norm_around_it(m, hidden, k, 
         assert (got_act.double() - want_act).abs().max() <= 2e-2 * want_act.abs().max()
 
 
-def test_norm_fusion_is_refused_where_it_does_not_fit():
+def test_norm_fusion_is_refused_where_it_does_not_fit(monkeypatch):
     o = ops()
     a, w1 = rnd(20, 64, dtype=torch.bfloat16), rnd(64, 64, dtype=torch.bfloat16)
-    assert not o.norm_fusable(o.PendingLinear(a, w1), rnd(20, 64), rnd(64))              # more than 16 rows
+    assert not o.norm_fusable(o.PendingLinear(a, w1), rnd(20, 64), rnd(64))              # more than 16 rows: the vendor GEMM
+    monkeypatch.setattr(o, "TC5_GEMM", True)
+    a, w1 = rnd(20, 64, dtype=torch.bfloat16), rnd(64, 64, dtype=torch.bfloat16)
+    assert o.norm_fusable(o.PendingLinear(a, w1), rnd(20, 64), rnd(64))                  # 17 to 128 rows: the tcgen05 GEMM
+    big = rnd(130, 64, dtype=torch.bfloat16)
+    assert not o.norm_fusable(o.PendingLinear(big, w1), rnd(130, 64), rnd(64))           # more rows than that
     a = rnd(4, 64, dtype=torch.bfloat16)
     assert o.norm_fusable(o.PendingLinear(a, w1), rnd(4, 64), rnd(64))
     assert not o.norm_fusable(o.PendingLinear(a, rnd(48, 64, dtype=torch.bfloat16)), rnd(4, 48), rnd(48))   # width % 32
@@ -285,40 +290,90 @@ def test_linear_with_a_bias(dtype):
         assert got.dtype == dtype and (got.double() - want).abs().max() <= tol * want.abs().max()
 
 
-@pytest.mark.parametrize("m", [1, 17, 32, 33, 64, 100, 128, 200, 256])
-@pytest.mark.parametrize("n,k,blocks", [(128, 64, 1), (509, 192, 5), (6144, 4096, 148), (4096, 12288, 148), (1000, 2560, 7),
-                                        (24576, 4096, 148), (130, 128, 3), (4096, 4096, 1000), (2000, 1024, 11)])
-def test_gemm_tc5(m, n, k, blocks):
+@pytest.mark.parametrize("m", [1, 17, 32, 33, 64, 100, 128])
+@pytest.mark.parametrize("n,k,split", [(128, 64, 1), (509, 192, 3), (6144, 4096, 0), (4096, 12288, 0), (1000, 2560, 7),
+                                       (24576, 4096, 0), (130, 128, 2), (4096, 4096, 8), (2000, 1024, 5), (40000, 512, 4)])
+def test_gemm_tc5(m, n, k, split):
     """The tcgen05 GEMM against a 32-bit product: every token tile, row counts that do not fill a
-    tile, widths that do not fill the last 128-row tile, and the work dealt to one, a few, 148 and
-    more blocks than there are units of work per tile (tiles finished by one block or by several)."""
+    tile, widths that do not fill the last 128-row tile, k split over clusters of one to eight
+    blocks (0: the library's choice), tiles in one round and in many (inboxes used again)."""
     x, w = rnd(m, k, dtype=torch.bfloat16, seed=30), rnd(n, k, dtype=torch.bfloat16, seed=31, scale=0.05)
     want = x.float() @ w.float().T
     for out_dtype, tol in ((torch.float32, 1e-4), (torch.bfloat16, 8e-3)):
-        got = ops().gemm_tc5(x, w, out_dtype=out_dtype, blocks=blocks)
+        got = ops().gemm_tc5(x, w, out_dtype=out_dtype, split=split)
         ops().tc5_check()
         assert got.dtype == out_dtype and got.shape == (m, n)
         assert (got.float() - want).abs().max() <= tol * want.abs().max()
-    # the same call again gives the same bits (the tile counters are back at zero, partials add in order)
-    again = ops().gemm_tc5(x, w, out_dtype=torch.float32, blocks=blocks)
-    assert torch.equal(again, ops().gemm_tc5(x, w, out_dtype=torch.float32, blocks=blocks))
+    # the same call again gives the same bits (partial sums add in rank order)
+    again = ops().gemm_tc5(x, w, out_dtype=torch.float32, split=split)
+    assert torch.equal(again, ops().gemm_tc5(x, w, out_dtype=torch.float32, split=split))
     wide = rnd(m, k + 72, dtype=torch.bfloat16, seed=32)
-    assert torch.equal(ops().gemm_tc5(wide[:, :k], w, blocks=blocks), ops().gemm_tc5(wide[:, :k].contiguous(), w, blocks=blocks))
+    assert torch.equal(ops().gemm_tc5(wide[:, :k], w, split=split), ops().gemm_tc5(wide[:, :k].contiguous(), w, split=split))
+    # a row's result does not depend on the rows beside it, nor on the token tile they select
+    if m > 1:
+        alone = ops().gemm_tc5(x[m // 2:m // 2 + 1], w, out_dtype=torch.float32, split=split)
+        assert torch.equal(alone[0], again[m // 2])
     ops().tc5_check()
 
 
-@pytest.mark.parametrize("m,inter,k,blocks", [(17, 8, 64, 1), (64, 200, 128, 3), (64, 12288, 4096, 148), (130, 1024, 2560, 37)])
-def test_gemm_tc5_gated_epilogue(m, inter, k, blocks):
+@pytest.mark.parametrize("m,inter,k,split", [(17, 8, 64, 1), (64, 200, 128, 2), (64, 12288, 4096, 0), (128, 1024, 2560, 3),
+                                             (40, 3000, 1024, 6)])
+def test_gemm_tc5_gated_epilogue(m, inter, k, split):
     x = rnd(m, k, dtype=torch.bfloat16, seed=33)
     gate, up = rnd(inter, k, dtype=torch.bfloat16, seed=34, scale=0.05), rnd(inter, k, dtype=torch.bfloat16, seed=35, scale=0.05)
     w = torch.stack([gate.view(-1, 8, k), up.view(-1, 8, k)], dim=1).reshape(2 * inter, k).contiguous()
     g = (x.float() @ gate.float().T).bfloat16().float()
     u = (x.float() @ up.float().T).bfloat16().float()
     want = g * torch.sigmoid(g) * u
-    got = ops().gemm_tc5(x, w, swiglu_rows=True, blocks=blocks)
+    got = ops().gemm_tc5(x, w, swiglu_rows=True, split=split)
     ops().tc5_check()
     assert got.shape == (m, inter)
     assert (got.float() - want).abs().max() <= 1.2e-2 * want.abs().max()
+
+
+@pytest.mark.parametrize("m,width,k,inter", [(17, 64, 64, 64), (33, 192, 320, 96), (64, 4096, 4096, 1536), (100, 1024, 2560, 512),
+                                             (128, 2560, 1024, 256)])
+def test_gemm_tc5_residual_epilogue_and_normed_rows(m, width, k, inter, monkeypatch):
+    """A product with the residual sum and the next norm in its epilogue, and the products that
+    read its rows with the norm's scale folded in (plain and gated), at 17 to 128 rows, against
+    the same in 64-bit; and the same product's stream twice gives the same bits."""
+    o = ops()
+    monkeypatch.setattr(o, "TC5_GEMM", True)
+    a, w1 = rnd(m, k, dtype=torch.bfloat16, seed=40), rnd(width, k, dtype=torch.bfloat16, seed=41, scale=0.05)
+    stream = rnd(m, width, seed=42)
+    norm_w = 1 + 0.1 * rnd(width, seed=43)
+    eps = 1e-5
+    want_stream = stream.double() + a.double() @ w1.double().T
+    pending = o.PendingLinear(a, w1)
+    got_stream = stream.clone()
+    assert o.norm_fusable(pending, got_stream, norm_w)
+    rows = o.linear_into_norm(pending, got_stream, norm_w, eps)
+    o.tc5_check()
+    assert isinstance(rows, o.NormedRows) and rows.sums.numel() >= m
+    assert (got_stream.double() - want_stream).abs().max() <= 2e-5 * want_stream.abs().max()
+    want_sums = (got_stream.double() ** 2).sum(dim=1)
+    got_sums = rows.sums[:m].double() * o.SUMS_UNIT
+    assert ((got_sums - want_sums).abs() <= 1e-5 * want_sums).all()
+    normed = got_stream.double() * torch.rsqrt((got_stream.double() ** 2).mean(dim=1, keepdim=True) + eps) * norm_w.double()
+    finished = rows.finish()
+    assert (finished.double() - normed).abs().max() <= 1.2e-2 * normed.abs().max()
+    w2 = rnd(inter, width, dtype=torch.bfloat16, seed=44, scale=0.05)
+    want = normed @ w2.double().T
+    got = o.linear(rows, w2, out_dtype=torch.float32)
+    assert (got.double() - want).abs().max() <= 1.2e-2 * want.abs().max()
+    if inter % 8 == 0:
+        up = rnd(inter, width, dtype=torch.bfloat16, seed=45, scale=0.05)
+        stacked = torch.stack([w2.view(-1, 8, width), up.view(-1, 8, width)], dim=1).reshape(2 * inter, width).contiguous()
+        g, u = normed @ w2.double().T, normed @ up.double().T
+        want_act = g * torch.sigmoid(g) * u
+        got_act = o.gemm_tc5(rows, stacked, swiglu_rows=True)
+        assert (got_act.double() - want_act).abs().max() <= 2e-2 * want_act.abs().max()
+    again, first_sums = stream.clone(), rows.sums[:m].clone()
+    o.RowSums.begin_step(torch.device(DEV))                  # clears the step's totals, the first call's among them
+    rows_again = o.linear_into_norm(pending, again, norm_w, eps)
+    assert torch.equal(again, got_stream) and torch.equal(rows_again.xw, rows.xw)
+    assert torch.equal(rows_again.sums[:m], first_sums)
+    o.tc5_check()
 
 
 def test_linear_bf16_accumulates_in_32_bits():

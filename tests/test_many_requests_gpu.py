@@ -81,11 +81,19 @@ def test_traces_with_up_to_64_live_requests(name, dtype, tmp_path):
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("name", ["C", "E"])
 @pytest.mark.parametrize("live", [17, 33, 64])
-def test_captured_decode_steps_of_many_requests(name, dtype, live, tmp_path):
+@pytest.mark.parametrize("gemm", ["vendor", "tcgen05"])
+def test_captured_decode_steps_of_many_requests(name, dtype, live, gemm, tmp_path, monkeypatch):
     """``decode_step`` (the captured 32- and 64-row steps, sampling inside) with 17, 33 and 64
-    requests of different lengths: greedy tokens and logits against the plain implementation."""
+    requests of different lengths: greedy tokens and logits against the plain implementation;
+    with the vendor library's products and with the tcgen05 GEMM (residual sum and norms in its
+    epilogues) switched on."""
     from mrun_b200.engine import StepEntry
     from mrun_b200.engine.loading import executor_from_folder
+    from mrun_b200.kernels import ops
+    if gemm == "tcgen05":
+        if dtype != "bfloat16" or name != "E":
+            pytest.skip("the tcgen05 GEMM takes bfloat16 products whose k is a multiple of 64")
+        monkeypatch.setattr(ops, "TC5_GEMM", True)
     settings = TINY[name]
     folder = make_folder(name, str(tmp_path / "model"))
     cfg, weights = plain.load_folder(folder)
