@@ -78,10 +78,11 @@ template <> __device__ __forceinline__ void store_out<float>(float* p, float v) 
 // (85 registers a thread), two of the others (128).
 constexpr int resident_blocks(int nt, int mt, int unroll) { return nt * mt * unroll <= 2 ? 3 : 2; }
 
-template <int NT, int MT, int UNROLL, typename TOut, int EPI>
+// CUT: a block takes `rows` < MT * 16 rows of W (see rows_a_block()); else its whole tile.
+template <int NT, int MT, int UNROLL, typename TOut, int EPI, bool CUT>
 __global__ void __launch_bounds__(THREADS, resident_blocks(NT, MT, UNROLL))
 skinny_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w, TOut* __restrict__ y, int M, int N, int K,
-              long ldx, long ldy, const Fusion f) {
+              long ldx, long ldy, const Fusion f, int rows_cut) {
     static_assert(EPI != EPI_RESIDUAL || MT == 1, "the residual epilogue sums 16 columns per block");
     __shared__ float red[WARPS][MT * 16][NT * 8 + 1];
     __shared__ float row_scale[NT * 8];
@@ -89,7 +90,8 @@ skinny_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w, TOut* __re
     __shared__ float stream_tile[EPI == EPI_RESIDUAL ? NT * 8 * 16 : 1], norm_tile[16];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int g = lane >> 2, t = lane & 3;
-    const int n0 = blockIdx.x * (MT * 16);
+    const int rows = CUT ? rows_cut : MT * 16;
+    const int n0 = blockIdx.x * rows;
     const int chunks = K >> 5;          // whole 32-wide chunks; K % 32 == 0 is checked by the host
 
     const bf16* w_rows[MT][2];
@@ -100,6 +102,9 @@ skinny_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w, TOut* __re
             const int row = min(n0 + mt * 16 + g + h * 8, N - 1);   // rows past N are computed and dropped
             w_rows[mt][h] = w + (size_t)row * K + t * 8;
         }
+    // a tile cut short (MT = 1, 8 <= rows < 16) ends in its second half: those rows belong to the
+    // next block and are not read here
+    const bool second_half = !CUT || g + 8 < rows;
     const bf16* x_rows[NT];
     bool x_valid[NT];
 #pragma unroll
@@ -125,7 +130,7 @@ skinny_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w, TOut* __re
 #pragma unroll
                 for (int mt = 0; mt < MT; ++mt) {
                     wb[u][mt][0] = load_stream(w_rows[mt][0] + k);
-                    wb[u][mt][1] = load_stream(w_rows[mt][1] + k);
+                    wb[u][mt][1] = second_half ? load_stream(w_rows[mt][1] + k) : make_uint4(0, 0, 0, 0);
                 }
             }
         }
@@ -180,7 +185,7 @@ skinny_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w, TOut* __re
         for (int i = threadIdx.x; i < 16 * NT * 8 + 16; i += THREADS) {
             const bool is_w = i >= 16 * NT * 8;
             const int row = i & 15, token = (i >> 4) & (NT * 8 - 1);
-            if (n0 + row < N && (is_w || token < M)) {
+            if (row < rows && n0 + row < N && (is_w || token < M)) {
                 const float* src = is_w ? f.norm_w + n0 + row : f.resid + (size_t)token * f.ldr + n0 + row;
                 const unsigned dst = (unsigned)__cvta_generic_to_shared(is_w ? norm_tile + row : stream_tile + i);
                 asm volatile("cp.async.ca.shared.global [%0], [%1], 4;\n" ::"r"(dst), "l"(src));
@@ -219,7 +224,7 @@ skinny_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w, TOut* __re
     if constexpr (EPI == EPI_PLAIN) {
         for (int i = threadIdx.x; i < MT * 16 * NT * 8; i += THREADS) {
             const int row = i % (MT * 16), token = i / (MT * 16);
-            if (token < M && n0 + row < N) {
+            if (token < M && row < rows && n0 + row < N) {
                 float s = 0.f;
 #pragma unroll
                 for (int wi = 0; wi < WARPS; ++wi) s += red[wi][row][token];
@@ -251,7 +256,7 @@ skinny_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w, TOut* __re
         for (int i = threadIdx.x; i < 16 * NT * 8; i += THREADS) {
             const int row = i & 15, token = i >> 4;
             float v = 0.f;
-            if (token < M && n0 + row < N) {
+            if (token < M && row < rows && n0 + row < N) {
                 float s = 0.f;
 #pragma unroll
                 for (int wi = 0; wi < WARPS; ++wi) s += red[wi][row][token];
@@ -267,12 +272,45 @@ skinny_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w, TOut* __re
     }
 }
 
+int sm_count();
+
+// Rows of W a block takes.  A block's tile holds 16 (MT = 1), but the device holds only so many
+// blocks at a time, and with 16 rows each some multiprocessors carry a block more than others
+// (4,096 rows are 256 blocks for 296 places: 108 multiprocessors stream 32 rows, 40 stream 16).
+// Fewer rows a block, 8 at the least, so that the blocks fill the places evenly, shorten what the
+// fullest multiprocessor streams: the count that makes (rounds over the places) x (rows a block)
+// smallest, the larger count at a tie, and only where that is a quarter less than with 16 (a
+// product of 2,560 rows, 160 blocks for 296 places: 9 rows a block; measured on B200, the
+// Qwen3-4B shape's output and down projections gain 8 %, the step 2 to 4 %, while the 12 % that
+// 14 rows promise a 4,096-row product do not show).  A function of N and the device, never of the batch.
+int rows_a_block(int N, int places, int forced) {
+    if (forced >= 8 && forced <= 16) return forced;
+    const long cost16 = (long)(((N + 15) / 16 + places - 1) / places) * 16;
+    int best = 16;
+    long best_cost = cost16;
+    for (int rows = 15; rows >= 8; --rows) {
+        const long cost = (long)(((N + rows - 1) / rows + places - 1) / places) * rows;
+        if (cost < best_cost) {
+            best_cost = cost;
+            best = rows;
+        }
+    }
+    return 4 * best_cost <= 3 * cost16 ? best : 16;
+}
+
 template <int NT, int MT, int UNROLL, typename TOut, int EPI>
 void launch(const bf16* x, const bf16* w, TOut* y, int M, int N, int K, long ldx, long ldy, const Fusion& f,
-            cudaStream_t stream) {
-    const int blocks = (N + MT * 16 - 1) / (MT * 16);
-    mrun::launch_kernel_overlapped(skinny_kernel<NT, MT, UNROLL, TOut, EPI>, dim3(blocks), dim3(THREADS), 0, stream, x, w, y,
-                                   M, N, K, ldx, ldy, f);
+            int forced_rows, cudaStream_t stream) {
+    if constexpr (MT == 1 && EPI != EPI_GATED) {     // the gated epilogue pairs rows inside whole runs of 16
+        const int rows = rows_a_block(N, sm_count() * resident_blocks(NT, MT, UNROLL), forced_rows);
+        if (rows < 16) {
+            mrun::launch_kernel_overlapped(skinny_kernel<NT, MT, UNROLL, TOut, EPI, true>, dim3((N + rows - 1) / rows),
+                                           dim3(THREADS), 0, stream, x, w, y, M, N, K, ldx, ldy, f, rows);
+            return;
+        }
+    }
+    mrun::launch_kernel_overlapped(skinny_kernel<NT, MT, UNROLL, TOut, EPI, false>, dim3((N + MT * 16 - 1) / (MT * 16)),
+                                   dim3(THREADS), 0, stream, x, w, y, M, N, K, ldx, ldy, f, MT * 16);
 }
 
 int sm_count() {
@@ -288,7 +326,7 @@ int sm_count() {
 
 template <typename TOut, int EPI>
 void dispatch(const bf16* x, const bf16* w, TOut* y, int M, int N, int K, long ldx, long ldy, const Fusion& f,
-              cudaStream_t stream) {
+              int rows, cudaStream_t stream) {
     const int sms = sm_count();
     const bool two_rounds = (N + 15) / 16 > 2 * sms;      // more 16-row blocks than two a multiprocessor
     if (M <= 8) {
@@ -297,15 +335,15 @@ void dispatch(const bf16* x, const bf16* w, TOut* y, int M, int N, int K, long l
         // two rounds' worth of 16-row blocks run in one round with the shallow kind; fewer blocks
         // are faster with the deep kind.
         if constexpr (EPI != EPI_RESIDUAL) {
-            if (N >= 32 * sms * 4) return launch<1, 2, UNROLL_SHALLOW, TOut, EPI>(x, w, y, M, N, K, ldx, ldy, f, stream);
+            if (N >= 32 * sms * 4) return launch<1, 2, UNROLL_SHALLOW, TOut, EPI>(x, w, y, M, N, K, ldx, ldy, f, rows, stream);
         }
-        if (two_rounds) launch<1, 1, UNROLL_SHALLOW, TOut, EPI>(x, w, y, M, N, K, ldx, ldy, f, stream);
-        else launch<1, 1, UNROLL_DEEP, TOut, EPI>(x, w, y, M, N, K, ldx, ldy, f, stream);
+        if (two_rounds) launch<1, 1, UNROLL_SHALLOW, TOut, EPI>(x, w, y, M, N, K, ldx, ldy, f, rows, stream);
+        else launch<1, 1, UNROLL_DEEP, TOut, EPI>(x, w, y, M, N, K, ldx, ldy, f, rows, stream);
     } else {
         // 9 to 16 rows of x: every chunk carries twice the x, so one row tile a block, and with
         // more than two rounds' worth of blocks one chunk per batch
-        if (two_rounds) launch<2, 1, 1, TOut, EPI>(x, w, y, M, N, K, ldx, ldy, f, stream);
-        else launch<2, 1, UNROLL_SHALLOW, TOut, EPI>(x, w, y, M, N, K, ldx, ldy, f, stream);
+        if (two_rounds) launch<2, 1, 1, TOut, EPI>(x, w, y, M, N, K, ldx, ldy, f, rows, stream);
+        else launch<2, 1, UNROLL_SHALLOW, TOut, EPI>(x, w, y, M, N, K, ldx, ldy, f, rows, stream);
     }
 }
 
@@ -319,11 +357,13 @@ void dispatch(const bf16* x, const bf16* w, TOut* y, int M, int N, int K, long l
 // resid != null: nothing is written to y; instead resid[M, N] (32-bit, dense) += the product,
 // xw_out[M, N] = bf16(resid * norm_w) and out_sums[row] (16 unsigned 64-bit integers, zero before
 // the call) gets the row's sum of squares of resid in units of 2^-30.
+// rows: the rows of W a block takes, 8..16, or 0 for the count that fills the device most evenly.
 MRUN_API int mrun_gemm_skinny(const void* x, const void* w, void* y, int out_dtype, int gate, int M, int N,
                               int K, long ldx, long ldy, const unsigned long long* in_sums, float in_eps,
                               float* resid, const float* norm_w, void* xw_out, unsigned long long* out_sums,
-                              cudaStream_t stream) {
+                              int rows, cudaStream_t stream) {
     MRUN_REQUIRE(M >= 0 && N > 0 && K > 0, "gemm_skinny: bad sizes M=%d N=%d K=%d", M, N, K);
+    MRUN_REQUIRE(rows == 0 || (rows >= 8 && rows <= 16), "gemm_skinny: rows=%d a block must be 0 (chosen here) or 8..16", rows);
     MRUN_REQUIRE(M <= 16, "gemm_skinny: M=%d exceeds the 16 rows this kernel takes", M);
     MRUN_REQUIRE(K % 32 == 0, "gemm_skinny: K=%d is not a multiple of 32", K);
     MRUN_REQUIRE(ldx >= K && ldx % 8 == 0, "gemm_skinny: ldx=%ld must be a multiple of 8 and at least K=%d", ldx, K);
@@ -345,7 +385,7 @@ MRUN_API int mrun_gemm_skinny(const void* x, const void* w, void* y, int out_dty
         f.norm_w = norm_w;
         f.xw_out = (bf16*)xw_out;
         f.out_sums = out_sums;
-        dispatch<bf16, EPI_RESIDUAL>(xp, wp, (bf16*)nullptr, M, N, K, ldx, ldy, f, stream);
+        dispatch<bf16, EPI_RESIDUAL>(xp, wp, (bf16*)nullptr, M, N, K, ldx, ldy, f, rows, stream);
         MRUN_CHECK_LAUNCH("gemm_skinny");
         return 0;
     }
@@ -354,11 +394,11 @@ MRUN_API int mrun_gemm_skinny(const void* x, const void* w, void* y, int out_dty
     MRUN_REQUIRE(ldy >= (gate ? N / 2 : N), "gemm_skinny: ldy=%ld is below the output width", ldy);
     if (M == 0) return 0;
     if (out_dtype == MRUN_BF16) {
-        if (gate) dispatch<bf16, EPI_GATED>(xp, wp, (bf16*)y, M, N, K, ldx, ldy, f, stream);
-        else dispatch<bf16, EPI_PLAIN>(xp, wp, (bf16*)y, M, N, K, ldx, ldy, f, stream);
+        if (gate) dispatch<bf16, EPI_GATED>(xp, wp, (bf16*)y, M, N, K, ldx, ldy, f, rows, stream);
+        else dispatch<bf16, EPI_PLAIN>(xp, wp, (bf16*)y, M, N, K, ldx, ldy, f, rows, stream);
     } else if (out_dtype == MRUN_F32) {
         MRUN_REQUIRE(!gate, "gemm_skinny: the gated epilogue writes bfloat16");
-        dispatch<float, EPI_PLAIN>(xp, wp, (float*)y, M, N, K, ldx, ldy, f, stream);
+        dispatch<float, EPI_PLAIN>(xp, wp, (float*)y, M, N, K, ldx, ldy, f, rows, stream);
     } else {
         return mrun_set_error("gemm_skinny: unknown output dtype code %d", out_dtype);
     }

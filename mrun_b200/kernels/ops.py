@@ -281,12 +281,13 @@ def _normed(x):
 
 
 def gemm_skinny(x, w: torch.Tensor, out_dtype: torch.dtype = torch.bfloat16,
-                swiglu_rows: bool = False, activation: str = "silu") -> torch.Tensor:
+                swiglu_rows: bool = False, activation: str = "silu", rows: int = 0) -> torch.Tensor:
     """y = x @ w.T for at most 16 rows, reading w once at HBM speed.  ``swiglu_rows``: w holds gate
     and up rows interleaved in runs of eight and y = act(gate) * up has half as many columns.
     ``x`` may be :class:`NormedRows`.  ``w`` is a weight: the kernel asks for its first rows while
     the decode GEMM launched before it may still be running, so it must not be that launch's
-    output (x, the stream and every output are touched only after that kernel has finished)."""
+    output (x, the stream and every output are touched only after that kernel has finished).
+    ``rows``: the rows of w a block takes (8..16; 0: the count that fills the device most evenly)."""
     x, sums, eps = _normed(x)
     _check(x, "x", torch.bfloat16, dense=False); _check(w, "w", torch.bfloat16)
     m, k = x.shape
@@ -297,7 +298,7 @@ def gemm_skinny(x, w: torch.Tensor, out_dtype: torch.dtype = torch.bfloat16,
     _lib.core().call("mrun_gemm_skinny", _ptr(x), _ptr(w), _ptr(out), dtype_code(out_dtype),
                      _c_int(gate_code(activation) if swiglu_rows else 0), _c_int(m), _c_int(n), _c_int(k),
                      _c_long(x.stride(0) if m > 1 else max(k, x.stride(0))), _c_long(out.shape[1]),
-                     sums, eps, _ptr(None), _ptr(None), _ptr(None), _ptr(None), _stream())
+                     sums, eps, _ptr(None), _ptr(None), _ptr(None), _ptr(None), _c_int(rows), _stream())
     return out
 
 
@@ -308,7 +309,8 @@ def norm_fusable(pending, resid: torch.Tensor, weight: torch.Tensor) -> bool:
             and resid.shape[1] % 32 == 0 and weight.numel() == resid.shape[1])
 
 
-def linear_into_norm(pending: PendingLinear, resid: torch.Tensor, weight: torch.Tensor, eps: float) -> NormedRows:
+def linear_into_norm(pending: PendingLinear, resid: torch.Tensor, weight: torch.Tensor, eps: float,
+                     rows: int = 0) -> NormedRows:
     """resid += pending.x @ pending.w.T (32-bit, in place) and the RMSNorm of the new rows with
     ``weight``, as :class:`NormedRows`: one kernel (the decode GEMM up to 16 rows, the tcgen05
     GEMM up to 128)."""
@@ -328,7 +330,7 @@ def linear_into_norm(pending: PendingLinear, resid: torch.Tensor, weight: torch.
             _c_long(x.stride(0) if m > 1 else max(k, x.stride(0))), _c_long(n), in_sums, in_eps, _ptr(resid),
             _ptr(weight), _ptr(xw), _ptr(out_sums))
     if skinny:
-        _lib.core().call("mrun_gemm_skinny", *head, _stream())
+        _lib.core().call("mrun_gemm_skinny", *head, _c_int(rows), _stream())
     else:
         _lib.core().call("mrun_gemm_tc5", *head, _c_int(0), _ptr(_tc5_status(x.device)), _stream())
     return NormedRows(xw, out_sums, eps)

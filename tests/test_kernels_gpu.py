@@ -159,6 +159,36 @@ def test_gemm_skinny(m, n, k):
     assert torch.equal(ops().gemm_skinny(wide[:, :k], w), ops().gemm_skinny(wide[:, :k].contiguous(), w))
 
 
+@pytest.mark.parametrize("m", [1, 8, 13])
+@pytest.mark.parametrize("n,k", [(509, 96), (2560, 4096), (4096, 1024), (24, 160)])
+def test_gemm_skinny_with_tiles_cut_short(m, n, k):
+    """A block of the decode GEMM may take 8 to 15 rows of W instead of its tile's 16, so that a
+    product with few rows fills the device evenly: every count gives the bits of the whole tile
+    (a row's sum does not depend on which block holds it), in the plain and in the residual
+    epilogue, at widths that no count divides."""
+    o = ops()
+    x, w = rnd(m, k, dtype=torch.bfloat16, seed=20), rnd(n, k, dtype=torch.bfloat16, seed=21, scale=0.05)
+    whole = o.gemm_skinny(x, w, out_dtype=torch.float32, rows=16)
+    want = x.float() @ w.float().T
+    assert (whole - want).abs().max() <= 8e-5 * want.abs().max()
+    norm_w = 1 + 0.1 * rnd(n, seed=33)
+    stream = rnd(m, n, seed=34)
+    fusable = n % 32 == 0
+    if fusable:
+        first = stream.clone()
+        rows_whole = o.linear_into_norm(o.PendingLinear(x, w), first, norm_w, 1e-5, rows=16)
+    for rows in (0, 8, 9, 11, 14, 15):
+        assert torch.equal(o.gemm_skinny(x, w, out_dtype=torch.float32, rows=rows), whole), rows
+        if fusable:
+            again = stream.clone()
+            cut = o.linear_into_norm(o.PendingLinear(x, w), again, norm_w, 1e-5, rows=rows)
+            assert torch.equal(again, first) and torch.equal(cut.xw, rows_whole.xw), rows
+            # the totals add the same squares in other groups (each group in 32-bit, then as integers)
+            assert ((cut.sums[:m] - rows_whole.sums[:m]).abs().double() <= 2e-6 * rows_whole.sums[:m].double()).all(), rows
+    with pytest.raises(o.KernelError, match="rows=7"):
+        o.gemm_skinny(x, w, rows=7)
+
+
 @pytest.mark.parametrize("m,inter,k", [(1, 8, 32), (5, 200, 96), (16, 12288, 4096), (9, 9728, 2560)])
 def test_gemm_skinny_gated_epilogue(m, inter, k):
     x = rnd(m, k, dtype=torch.bfloat16, seed=23)
