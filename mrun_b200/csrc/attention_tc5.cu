@@ -275,17 +275,19 @@ prefill_tc5_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_const
             // p = 2^(s * scale - m): one fused multiply-add and one special-function call a score.
             // Masked scores are -inf and give 0; a row that has seen nothing yet keeps m_used = -inf.
             const float m_sub = m_used == -INFINITY ? 0.f : -m_used;
-            float sum0 = 0.f, sum1 = 0.f;
+            // Two scores an instruction where the hardware has one (fma.f32x2, add.f32x2): these
+            // warps are bound by the instructions they issue.
+            const float2 scale2 = make_float2(scale_log2, scale_log2), m_sub2 = make_float2(m_sub, m_sub);
+            float2 sums = make_float2(0.f, 0.f);
             float packed[32];                                         // two bf16 a word, even key low
 #pragma unroll
             for (int i = 0; i < 64; i += 2) {
-                const float p0 = fast_exp2(fmaf(sc[i], scale_log2, m_sub));
-                const float p1 = fast_exp2(fmaf(sc[i + 1], scale_log2, m_sub));
-                sum0 += p0;
-                sum1 += p1;
-                packed[i >> 1] = __uint_as_float(pack_bf16(p0, p1));
+                const float2 x = __ffma2_rn(make_float2(sc[i], sc[i + 1]), scale2, m_sub2);
+                const float2 p = make_float2(fast_exp2(x.x), fast_exp2(x.y));
+                sums = __fadd2_rn(sums, p);
+                packed[i >> 1] = __uint_as_float(pack_bf16(p.x, p.y));
             }
-            l += sum0 + sum1;
+            l += sums.x + sums.y;
             // the P buffer of this tile was read by the second product of the tile before last
             if (j >= 2 && !__all_sync(0xffffffffu, mbar_wait(&bars.v_empty[buf], ((j >> 1) - 1) & 1, WAIT_CYCLES, &aborted))) {
                 alive = false;
