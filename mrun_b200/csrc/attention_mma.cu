@@ -162,7 +162,7 @@ prefill_kernel(const bf16* __restrict__ q, long q_stride, bf16* __restrict__ out
     bf16* k_tiles = q_tile + 64 * LD;                           // [2][64][LD]
     bf16* v_tiles = k_tiles + 2 * BLOCK_N * LD;                 // [2][64][LD]
 
-    const int tile = blockIdx.x, kvh = blockIdx.y;
+    const int tile = blockIdx.y, kvh = blockIdx.x;      // the list's first tile (the longest, the host sorts) for every kv head first
     const int group = heads / kv_heads;
     const int tok0 = tile_tok0[tile], ntok = tile_ntok[tile];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -715,11 +715,14 @@ MRUN_API int mrun_attn_prefill(const void* q, long q_stride, void* out, const vo
                                              (int)PREFILL_SMEM), "attn_prefill");
         configured = true;
     }
-    prefill_kernel<<<dim3(n_tiles, kv_heads), THREADS, PREFILL_SMEM, stream>>>(
-        (const bf16*)q, q_stride, (bf16*)out, (const bf16*)k_cache, (const bf16*)v_cache, block_tables, max_blocks,
-        token_slot, positions, tile_tok0, tile_ntok, heads, kv_heads, page_size, page_shift_of(page_size), scale * LOG2E,
-        window);
-    MRUN_CHECK_LAUNCH("attn_prefill");
+    for (int done = 0; done < n_tiles; done += 65535) {          // the grid's second dimension ends at 65535
+        const int now = n_tiles - done < 65535 ? n_tiles - done : 65535;
+        prefill_kernel<<<dim3(kv_heads, now), THREADS, PREFILL_SMEM, stream>>>(
+            (const bf16*)q, q_stride, (bf16*)out, (const bf16*)k_cache, (const bf16*)v_cache, block_tables, max_blocks,
+            token_slot, positions, tile_tok0 + done, tile_ntok + done, heads, kv_heads, page_size, page_shift_of(page_size),
+            scale * LOG2E, window);
+        MRUN_CHECK_LAUNCH("attn_prefill");
+    }
     return 0;
 }
 

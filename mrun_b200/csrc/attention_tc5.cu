@@ -128,8 +128,9 @@ prefill_tc5_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_const
     __shared__ float pair_max[2][2][ROWS];               // [tile parity][half][row]: the halves' maxima
     __shared__ float pair_sum[2][ROWS];                  // [half][row]: the halves' sums, at the end
 
-    // the longest tiles (latest positions) first
-    const int tile = gridDim.x - 1 - blockIdx.x, kvh = blockIdx.y;
+    // Blocks start in the order of their index, x first: all kv heads of the first tile of the
+    // list, which the host sorted by falling context length, then all of the second, ...
+    const int tile = blockIdx.y, kvh = blockIdx.x;
     const int group = heads / kv_heads;
     const int tok0 = tile_tok0[tile], ntok = tile_ntok[tile];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -464,7 +465,6 @@ MRUN_API int mrun_attn_prefill_tc5(const void* q, long q_stride, void* out, cons
     MRUN_REQUIRE(heads / kv_heads <= ROWS, "attn_prefill_tc5: %d query heads per kv head exceed the supported %d",
                  heads / kv_heads, ROWS);
     MRUN_REQUIRE(page_size > 0 && max_blocks > 0 && window >= 0, "attn_prefill_tc5: bad page_size/max_blocks/window");
-    MRUN_REQUIRE(kv_heads <= 65535, "attn_prefill_tc5: kv_heads=%d exceeds 65535", kv_heads);
     MRUN_REQUIRE(n_tiles >= 0, "attn_prefill_tc5: n_tiles=%d", n_tiles);
     MRUN_REQUIRE(q_stride % 8 == 0 && ((uintptr_t)q & 15) == 0 && ((uintptr_t)out & 15) == 0 &&
                  ((uintptr_t)k_cache & 15) == 0 && ((uintptr_t)v_cache & 15) == 0,
@@ -483,11 +483,14 @@ MRUN_API int mrun_attn_prefill_tc5(const void* q, long q_stride, void* out, cons
                                              SMEM_BYTES), "attn_prefill_tc5");
         configured = true;
     }
-    prefill_tc5_kernel<<<dim3(n_tiles, kv_heads), THREADS, SMEM_BYTES, stream>>>(
-        map_k, map_v, (const bf16*)q, q_stride, (bf16*)out, block_tables, max_blocks,
-        token_slot, positions, tile_tok0, tile_ntok, heads, kv_heads, page_size, page_shift_of(page_size),
-        scale * LOG2E, window, status);
-    MRUN_CHECK_LAUNCH("attn_prefill_tc5");
+    for (int done = 0; done < n_tiles; done += 65535) {          // the grid's second dimension ends at 65535
+        const int now = n_tiles - done < 65535 ? n_tiles - done : 65535;
+        prefill_tc5_kernel<<<dim3(kv_heads, now), THREADS, SMEM_BYTES, stream>>>(
+            map_k, map_v, (const bf16*)q, q_stride, (bf16*)out, block_tables, max_blocks,
+            token_slot, positions, tile_tok0 + done, tile_ntok + done, heads, kv_heads, page_size, page_shift_of(page_size),
+            scale * LOG2E, window, status);
+        MRUN_CHECK_LAUNCH("attn_prefill_tc5");
+    }
     return 0;
 #else
     return mrun_set_error("attn_prefill_tc5: not built for head_dim=%d (head sizes 64 and 128 only)", MRUN_HEAD_DIM);

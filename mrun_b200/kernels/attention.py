@@ -161,18 +161,23 @@ def decode_plan(ctx, library, window: int, kv_heads: int, blocks: int, splits: i
 
 def prefill_tiles(ctx, tokens_per_tile: int, longer_than: int = 0, up_to: int = 1 << 30):
     """(first token row, token count) of every row tile of the segments with more than
-    ``longer_than`` and at most ``up_to`` tokens, as device int32 arrays; made once per step and
-    choice of sizes."""
+    ``longer_than`` and at most ``up_to`` tokens, the tiles with the longest contexts first, as
+    device int32 arrays; made once per step and choice of sizes."""
     key = ("attention_tiles", tokens_per_tile, longer_than, up_to)
     tiles = ctx.shared.get(key)
     if tiles is None:
-        first, count = [], []
+        found = []
         for seg in ctx.segments:
             if not longer_than < seg.q_len <= up_to:
                 continue
             for t0 in range(0, seg.q_len, tokens_per_tile):
-                first.append(seg.q_start + t0)
-                count.append(min(tokens_per_tile, seg.q_len - t0))
+                count = min(tokens_per_tile, seg.q_len - t0)
+                found.append((seg.pos_start + t0 + count, seg.q_start + t0, count))
+        # The tile with the most keys before it first: the kernels start their blocks in this
+        # order, so the long tiles are under way while the short ones fill the gaps (a stable
+        # sort: the order depends on the step's segments only).
+        found.sort(key=lambda tile: -tile[0])
+        first, count = [tile[1] for tile in found], [tile[2] for tile in found]
         n = len(first)
         both = ctx.upload(np.asarray(first + count, dtype=np.int32))
         tiles = ctx.shared[key] = (both[:n], both[n:], n)
