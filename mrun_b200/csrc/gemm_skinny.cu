@@ -2,9 +2,10 @@
 // operands, 32-bit accumulation, bf16 or 32-bit output.  The product is bound by reading W once
 // from HBM, so the kernel is built around that stream:
 //
-//  * a block owns 16 (or 32) rows of W and all of K; its eight warps take the 32-wide k chunks in
-//    turn (chunk c goes to warp c mod 8), so at any moment the block reads 512 contiguous bytes
-//    of each of its rows;
+//  * a block owns 16 (or 32) rows of W and all of K (8 to 15 rows where whole tiles would fill the
+//    device unevenly, see rows_a_block()); its eight warps take the 32-wide k chunks in turn
+//    (chunk c goes to warp c mod 8), so at any moment the block reads 512 contiguous bytes of
+//    each of its rows;
 //  * every thread loads 16 bytes of a W row straight into registers, several chunks ahead, with
 //    no shared-memory staging, and the same 16-byte slice of k from x;
 //  * tensor-core products m16n8k16 with W as the 16-row operand and the tokens as the 8 columns.
