@@ -345,6 +345,8 @@ def main() -> int:
                "frac": round(prefill_flops / (prefill_ms * 1e-3) / (peaks["bf16_tflops"] * 1e12), 4)}
     if "bf16_tflops_sustained" in peaks:
         prefill["frac_sustained"] = round(prefill_flops / (prefill_ms * 1e-3) / (peaks["bf16_tflops_sustained"] * 1e12), 4)
+    if not times:                        # --skip-prefill: nothing was measured, and NaN is no JSON
+        prefill = {"skipped": True, "tokens": PREFILL_TOKENS}
 
     # ---------------------------------------------------------------- decode at batch 8 / 1 / 64
     results = {}
