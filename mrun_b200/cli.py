@@ -2,12 +2,14 @@
 reference's token-ids-in example (crates/mrun-engine/examples/generate.rs:1-13).
 
     mrun run MODEL --prompt IDS [--max-tokens N] [--temperature T] [--top-p P] [--top-k K]
-                   [--min-p P] [--seed S] [--budget-gib GIB | --context TOKENS] [--info]
+                   [--min-p P] [--seed S] [--stop IDS]... [--budget-gib GIB | --context TOKENS] [--info]
     mrun random MODEL_DIR --config CONFIG.json --seed S
 
 ``MODEL`` is a folder with config.json and safetensors.  ``--prompt`` takes token ids, inline or
 as a file, separated by commas or whitespace; this engine has no tokenizer, so the text options
-of ``mrun run`` (--system, --stop, --think, --mcp) do not exist here.  The generated ids go to
+of ``mrun run`` (--system, --think, --mcp) do not exist here, and ``--stop`` (up to 4 times, as
+there: crates/mrun/src/cli/run.rs:56, crates/mrun/src/chat/limits.rs:6) takes a stop sequence of
+token ids instead of a string: the output ends before the first of them that appears.  The generated ids go to
 standard output separated by commas; speeds go to standard error the way the example prints them.
 Sampling defaults come from the model's generation_config.json, else temperature 0, top_p 1,
 top_k 0, min_p 0 (crates/mrun/src/cli/model.rs:380-399).
@@ -99,6 +101,8 @@ def build_parser() -> argparse.ArgumentParser:
     run.add_argument("--page-size", type=int, default=16)
     run.add_argument("--max-batch-tokens", type=int, default=2048)
     run.add_argument("--ignore-eos", action="store_true")
+    run.add_argument("--stop", action="append", default=[], metavar="IDS",
+                     help="a stop sequence of token ids (up to 4 of them): the output ends before it")
 
     rnd = sub.add_parser("random", help="write a model folder with random weights")
     rnd.add_argument("out", help="folder to write config.json and model.safetensors into")
@@ -176,7 +180,7 @@ def command_run(args) -> int:
                              temperature=pick(args.temperature, "temperature"),
                              top_p=pick(args.top_p, "top_p"), top_k=pick(args.top_k, "top_k"),
                              min_p=pick(args.min_p, "min_p"), seed=args.seed,
-                             ignore_eos=args.ignore_eos)[0]
+                             ignore_eos=args.ignore_eos, stop=[parse_ids(ids) for ids in args.stop])[0]
     total = time.perf_counter() - start
     if result.finish_reason in ("invalid", "too_long", "queue_full"):
         print(f"error: {result.message}", file=sys.stderr)
@@ -186,7 +190,8 @@ def command_run(args) -> int:
     print(f"prompt: {len(prompt)} tokens, {len(prompt) / max(ttft, 1e-9):.1f} tokens-per-sec", file=sys.stderr)
     print(f"generation: {len(result.tokens)} tokens, "
           f"{(len(result.tokens) - 1) / max(total - ttft, 1e-9):.1f} tokens-per-sec "
-          f"({result.finish_reason})", file=sys.stderr)
+          f"({result.finish_reason}" + (f" {result.stop_sequence}" if result.stop_sequence else "") + ")",
+          file=sys.stderr)
     return 0
 
 

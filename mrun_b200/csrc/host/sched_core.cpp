@@ -15,7 +15,9 @@
 //    (crates/mrun/src/runtime/lanes.rs:187-196); a portion is at most chunk_len(depth)
 //    (crates/mrun-engine/src/engine.rs:481-486);
 //  * ends: an end token, the output limit, or the last 512 output tokens repeating with a period
-//    of at most 256, looked at every 16 tokens (crates/mrun/src/runtime/generate.rs:27-33, 420-426, 866-919).
+//    of at most 256, looked at every 16 tokens (crates/mrun/src/runtime/generate.rs:27-33, 420-426, 866-919);
+//  * stop sequences of token ids: the output ends where one of them is complete, without it
+//    (crates/mrun/src/chat/stop.rs:24-85).
 #include <algorithm>
 #include <cstdint>
 #include <vector>
@@ -149,6 +151,38 @@ HOST_API int mrun_sched_end_reason(int is_end_token, int ignore_eos, int64_t out
     if (output_len >= limit) return 2;
     if (!ignore_eos && recent != nullptr && output_len % LOOP_CHECK_EVERY == 0 && mrun_sched_looping(recent, recent_len)) return 3;
     return 0;
+}
+
+// Stop sequences, on token ids (the reference matches stop strings on the streamed text, earliest
+// match first, and holds back what may still begin one: crates/mrun/src/chat/stop.rs:24-85; at
+// most 4 of them, crates/mrun/src/chat/limits.rs:6).  `stops` holds the n_stops sequences one after
+// the other, `lens` their lengths; `tail` the last tail_len tokens of the output.
+// The sequence that the output ends with, the longest if several do (it began earliest): its
+// index, or -1.
+HOST_API int mrun_sched_stop_match(const int* tail, int tail_len, const int* stops, const int* lens, int n_stops) {
+    int best = -1, best_len = 0, at = 0;
+    for (int s = 0; s < n_stops; at += lens[s], ++s) {
+        const int len = lens[s];
+        if (len < 1 || len > tail_len || len <= best_len) continue;
+        if (std::equal(stops + at, stops + at + len, tail + tail_len - len)) {
+            best = s;
+            best_len = len;
+        }
+    }
+    return best;
+}
+
+// How many tokens at the end of the output may still begin a stop sequence (a proper prefix of
+// one): they are not streamed yet.
+HOST_API int mrun_sched_stop_held(const int* tail, int tail_len, const int* stops, const int* lens, int n_stops) {
+    int held = 0, at = 0;
+    for (int s = 0; s < n_stops; at += lens[s], ++s)
+        for (int n = std::min(lens[s] - 1, tail_len); n > held; --n)
+            if (std::equal(stops + at, stops + at + n, tail + tail_len - n)) {
+                held = n;
+                break;
+            }
+    return held;
 }
 
 // The running request that gives its pages back when they run out: the one admitted last among

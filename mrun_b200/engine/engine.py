@@ -23,7 +23,7 @@ from .batch import RECENT, StepEntry
 from .budget import MemoryBudget
 from .executor import Executor
 from .loading import executor_from_config, executor_from_folder
-from .scheduler import Request, Scheduler, StepPlan
+from .scheduler import Request, Scheduler, StepPlan, checked_stops
 
 
 @dataclass
@@ -41,6 +41,7 @@ class Generation:
     # with ``logprobs=n``: per output token the n most likely tokens at that place as
     # (id, log-probability), most likely first (crates/mrun-engine/src/engine.rs:740-741)
     top_logprobs: List[list] = field(default_factory=list)
+    stop_sequence: Optional[List[int]] = None     # the stop sequence that ended it (finish reason ``stop``), else None
 
 
 @dataclass
@@ -115,7 +116,7 @@ class Engine:
                  top_p: float = 1.0, top_k: int = 0, min_p: float = 0.0, seed: Optional[int] = None,
                  repetition_penalty: float = 1.0, ignore_eos: bool = False,
                  sampling: Optional[Sequence[SamplingParams]] = None, logprobs: int = 0,
-                 on_token=None) -> List[Generation]:
+                 on_token=None, stop: Optional[Sequence[Sequence[int]]] = None) -> List[Generation]:
         """Generates for every prompt (lists of token ids) and returns the results in order.
         ``sampling`` gives each prompt settings of its own; otherwise all share the keyword
         values, prompt i drawing with ``seed + i`` when a seed is given.  ``logprobs`` = n > 0
@@ -127,9 +128,14 @@ class Engine:
         False, prompt i is cancelled: it ends with finish reason ``cancelled`` and the tokens read
         so far, and the other prompts go on unchanged (the reference's cancel flag,
         crates/mrun-engine/src/engine.rs:463-479).  An end token finishes a prompt with ``stop``
-        and is itself not part of the output (crates/mrun/src/runtime/generate.rs:868-874)."""
+        and is itself not part of the output (crates/mrun/src/runtime/generate.rs:868-874).
+        ``stop``: up to 4 stop sequences of token ids (the reference's ``--stop`` on ids instead of
+        text): a prompt ends with ``stop`` where its output would end with one of them, the
+        sequence left out and named in ``Generation.stop_sequence``; tokens that may begin one are
+        held back from ``on_token`` until they cannot (crates/mrun/src/chat/stop.rs:24-85)."""
         if not 0 <= logprobs <= 1024:
             raise ValueError(f"logprobs must be 0 .. 1024, got {logprobs}")
+        stops = checked_stops(stop)
         requests = []
         for i, prompt in enumerate(prompts):
             if sampling is not None:
@@ -140,7 +146,7 @@ class Engine:
                                         repetition_penalty=repetition_penalty)
             requests.append(Request(request_id=("gen", self._next_id), prompt=list(map(int, prompt)),
                                     max_tokens=max_tokens, sampling=params, ignore_eos=ignore_eos,
-                                    logprobs=logprobs,
+                                    logprobs=logprobs, stop=[list(sequence) for sequence in stops],
                                     on_token=None if on_token is None else (lambda r, t, i=i: on_token(i, t))))
             self._next_id += 1
         self.run(requests)
@@ -149,7 +155,7 @@ class Engine:
                            time_to_first_token_s=max(0.0, r.first_token_at - r.submitted_at) if r.output else 0.0,
                            total_s=r.finished_at - r.submitted_at, preemptions=r.preemptions,
                            first_token_time=r.first_token_at, finished_time=r.finished_at,
-                           token_times=r.token_times, top_logprobs=r.top_logprobs)
+                           token_times=r.token_times, top_logprobs=r.top_logprobs, stop_sequence=r.stop_sequence)
                 for r in requests]
 
     def run(self, requests: Sequence[Request]) -> None:

@@ -35,6 +35,12 @@ Decisions, with the reference's where it has one
   out of the output; the output limit → ``length``; the last 512 output tokens repeating with a
   period of at most 256, checked every 16 tokens and never with ``ignore_eos`` → ``repetition``
   (crates/mrun/src/runtime/generate.rs:27-33, 420-426, 866-919).
+* **Stop sequences** (``Request.stop``: up to 4 lists of token ids, the reference's ``--stop`` on
+  token ids instead of text, crates/mrun/src/chat/stop.rs:24-85, crates/mrun/src/chat/limits.rs:6):
+  the request ends with ``stop`` as soon as its output ends with one of them, the longest if
+  several do; the sequence is cut from the output and named in ``Request.stop_sequence``.  Tokens
+  that may still begin a stop sequence are held back from ``on_token`` until they cannot, or until
+  the request ends for another reason.
 * **Cancelling**: ``on_token`` returning False, or ``Request.cancel_requested`` set by the caller,
   ends the request with ``cancelled`` when its next token is read: the tokens read so far stay,
   a token still in flight for it is dropped, its pages go back, and the other requests of the
@@ -54,6 +60,19 @@ from ..sampling.params import GREEDY, SamplingParams, fresh_seed
 
 LOOP_WINDOW, LOOP_MAX_PERIOD = 512, 256
 END_REASONS = (None, "stop", "length", "repetition")
+MAX_STOPS, MAX_STOP_TOKENS = 4, 64
+
+
+def checked_stops(stop) -> List[List[int]]:
+    """Stop sequences as lists of token ids: at most 4, each of 1 to 64 ids (the reference's
+    messages, crates/mrun/src/chat/stop.rs:7-10, with tokens for bytes)."""
+    stops = [list(map(int, sequence)) for sequence in (stop or [])]
+    if len(stops) > MAX_STOPS:
+        raise ValueError(f"at most {MAX_STOPS} stop sequences are allowed, got {len(stops)}")
+    for sequence in stops:
+        if not 1 <= len(sequence) <= MAX_STOP_TOKENS:
+            raise ValueError(f"stop sequences must be 1..={MAX_STOP_TOKENS} tokens, got {len(sequence)}")
+    return stops
 
 
 def chunk_len(depth: int, budget: int = 2048) -> int:
@@ -78,6 +97,7 @@ class Request:
     ignore_eos: bool = False
     logprobs: int = 0                  # how many of the most likely tokens to report beside each output token
     on_token: Optional[object] = None  # called with (request, token) as each output token is read back
+    stop: List[List[int]] = field(default_factory=list)      # stop sequences of token ids (see checked_stops)
     # ---- run state
     state: str = "new"                 # new | waiting | running | finished
     output: List[int] = field(default_factory=list)
@@ -95,6 +115,8 @@ class Request:
     finished_at: float = 0.0
     token_times: List[float] = field(default_factory=list)   # when each output token was read back
     top_logprobs: List[list] = field(default_factory=list)   # per output token: [(id, log-probability), ...]
+    stop_sequence: Optional[List[int]] = None    # the stop sequence that ended the request, if one did
+    streamed: int = 0                  # output tokens that on_token has seen
     cancel_requested: bool = False     # set from outside (or by on_token returning False): end at the next token read
     inflight: int = 0                  # tokens sampled on the device that the host has not read yet
     retiring: bool = False             # finished, but a step in flight still holds a row of it
@@ -180,7 +202,8 @@ class Scheduler:
         else:
             try:
                 request.sampling.validate()
-            except ValueError as error:
+                request.stop = checked_stops(request.stop)
+            except (ValueError, TypeError) as error:
                 reason, request.message = "invalid", str(error)
         if reason is None:
             limit = ctypes.c_int64(0)
@@ -309,12 +332,21 @@ class Scheduler:
             if reason != "stop":
                 request.output.append(token)
                 request.token_times.append(now)
-                if request.on_token is not None:
-                    cancelled = request.on_token(request, token) is False
-            else:
-                del request.top_logprobs[len(request.output):]       # the end token's row goes with it
+                held = 0
+                if request.stop:
+                    matched, held = self._stop_state(request)
+                    if matched is not None:              # the output ends before the stop sequence
+                        del request.output[-len(matched):]
+                        del request.token_times[len(request.output):]
+                        request.stop_sequence, reason = matched, "stop"
+                if reason is None:
+                    cancelled = self._stream(request, len(request.output) - held)
+            if reason == "stop":
+                del request.top_logprobs[len(request.output):]       # the rows of what is left out go with it
             if reason is None and (cancelled or request.cancel_requested):
                 reason = "cancelled"
+            if reason is not None and not cancelled:
+                self._stream(request, len(request.output))           # what was held back is shown at the end
             if reason is not None:
                 if request.inflight:
                     request.retiring = True          # its row in the step in flight is dropped later
@@ -323,6 +355,31 @@ class Scheduler:
                 self._finish(request, reason)
                 done.append(request)
         return done
+
+    def _stop_state(self, request: Request):
+        """(the stop sequence the output ends with or None, how many of its last tokens may still
+        begin one)."""
+        longest = max(len(sequence) for sequence in request.stop)
+        tail = request.output[-longest:]
+        flat = native.int_array([t for sequence in request.stop for t in sequence])
+        lens = native.int_array([len(sequence) for sequence in request.stop])
+        tail_array = native.int_array(tail)
+        hit = self._core.mrun_sched_stop_match(tail_array, len(tail), flat, lens, len(request.stop))
+        if hit >= 0:
+            return request.stop[hit], 0
+        return None, self._core.mrun_sched_stop_held(tail_array, len(tail), flat, lens, len(request.stop))
+
+    @staticmethod
+    def _stream(request: Request, upto: int) -> bool:
+        """Shows ``on_token`` the output tokens it has not seen, up to ``upto``; True when it asked
+        to cancel."""
+        cancelled = False
+        while request.streamed < upto:
+            token = request.output[request.streamed]
+            request.streamed += 1
+            if request.on_token is not None and request.on_token(request, token) is False:
+                cancelled = True
+        return cancelled
 
     # ------------------------------------------------------------------ out of pages
     def preempt_newest(self) -> Optional[Request]:

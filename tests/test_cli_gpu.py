@@ -50,6 +50,16 @@ def test_random_then_run(tmp_path):
     assert tokens == plain.generate(cfg, weights, prompt, 8)
     assert "prompt: 17 tokens" in result.stderr and "generation: 8 tokens" in result.stderr
 
+    # --stop: the output ends before the first stop sequence (of token ids) that appears
+    stopped = run("run", folder, "--prompt", str(ids), "--max-tokens", "8", "--dtype", "float32", "--ignore-eos",
+                  "--stop", f"{tokens[4]},{tokens[5]}", "--stop", "100000")
+    assert stopped.returncode == 0, stopped.stderr
+    first = next(i for i in range(7) if tokens[i:i + 2] == tokens[4:6])
+    assert [int(t) for t in stopped.stdout.strip().split(",")] == tokens[:first]
+    assert f"(stop [{tokens[4]}, {tokens[5]}])" in stopped.stderr
+    many = run("run", folder, "--prompt", str(ids), "--stop", "1", "--stop", "2", "--stop", "3", "--stop", "4", "--stop", "5")
+    assert many.returncode != 0 and "at most 4 stop sequences" in many.stderr
+
     inline = run("run", folder, "--prompt", ",".join(map(str, prompt)), "--max-tokens", "8", "--dtype", "float32",
                  "--temperature", "0.8", "--seed", "5", "--ignore-eos")
     again = run("run", folder, "--prompt", ",".join(map(str, prompt)), "--max-tokens", "8", "--dtype", "float32",

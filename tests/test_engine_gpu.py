@@ -166,6 +166,42 @@ def test_cancelling_one_request_leaves_the_others_as_they_were(tiny):
     assert not engine.executor.cache.live and engine.executor.cache.free_pages() == engine.executor.cache.num_pages
 
 
+def test_stop_sequences_end_requests_in_the_middle_of_pipelined_decoding(tiny):
+    """``stop=`` through ``Engine.generate``: each prompt ends where its own free-running output
+    would contain a stop sequence (taken from those outputs), without the sequence; the token in
+    flight for it is dropped, the others go on unchanged, what was held back reaches ``on_token``
+    in order, and everything is given back (the reference's ``--stop``, on token ids:
+    crates/mrun/src/chat/stop.rs:24-85)."""
+    from mrun_b200 import Engine
+    name, folder, settings = tiny
+    cfg, weights = plain.load_folder(folder)
+    prompts = [random_tokens(cfg["vocab_size"], n, seed=700 + n) for n in (9, 21, 4)]
+    engine = Engine.from_folder(folder, dtype="float32", page_size=settings["page_size"], context=512,
+                                max_batch_tokens=32, max_requests=4)
+    free = engine.generate(prompts, max_tokens=24, ignore_eos=True)
+    stops = [free[0].tokens[7:10], free[1].tokens[15:16]]
+    def first_end(tokens):
+        ends = [(i + len(s), s) for s in stops for i in range(len(tokens) - len(s) + 1) if tokens[i:i + len(s)] == s]
+        return min(ends, key=lambda e: (e[0], -len(e[1]))) if ends else None
+    seen = {0: [], 1: [], 2: []}
+    cut = engine.generate(prompts, max_tokens=24, ignore_eos=True, stop=stops, on_token=lambda i, t: seen[i].append(t))
+    stopped = 0
+    for i, (a, b) in enumerate(zip(free, cut)):
+        end = first_end(a.tokens)
+        if end is None:
+            assert b.tokens == a.tokens and b.finish_reason == "length" and b.stop_sequence is None
+        else:
+            stopped += 1
+            assert b.finish_reason == "stop" and b.stop_sequence == end[1]
+            assert b.tokens == a.tokens[:end[0] - len(end[1])]
+        assert seen[i] == b.tokens and len(b.token_times) == len(b.tokens)
+    assert stopped >= 2
+    engine.executor.cache.check_invariants()
+    assert not engine.executor.cache.live and engine.executor.cache.free_pages() == engine.executor.cache.num_pages
+    with pytest.raises(ValueError, match="at most 4 stop sequences"):
+        engine.generate(prompts, max_tokens=2, stop=[[1]] * 5)
+
+
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_repetition_penalty_and_filters_through_generate(tiny, dtype):
     """Sampling settings that need the token history (the penalty) keep decoding correct: the

@@ -157,6 +157,50 @@ def test_cancelling_from_the_token_callback_and_from_outside():
     s.cache.check_invariants()
 
 
+def test_stop_sequences_of_token_ids():
+    """The reference's stop strings on token ids (crates/mrun/src/chat/stop.rs:24-85 and its tests
+    at :95-130): a sequence split over steps is found and left out; a false start is shown later;
+    the longest of several that end at one token wins; held tokens are shown when the request
+    ends for another reason; more than four or an empty one are refused."""
+    def run(stream, stop, max_tokens=20, eos=()):
+        s = Scheduler(cache(), eos_token_ids=eos)
+        seen = []
+        r = Request("r", [1, 2, 3], max_tokens=max_tokens, stop=stop, on_token=lambda request, t: seen.append(t))
+        assert s.submit(r) is None
+        drive(s, next_token=lambda request: stream[len(request.output) + (len(request.stop_sequence or []))])
+        return r, seen
+
+    stream = [10, 11, 7, 8, 9, 12, 13, 14] + [0] * 40
+    r, seen = run(stream, [[7, 8, 9]])
+    assert r.finish_reason == "stop" and r.stop_sequence == [7, 8, 9] and r.output == [10, 11] and seen == [10, 11]
+    assert len(r.token_times) == 2
+    # a false start is released once it cannot be a stop sequence any more
+    r, seen = run([7, 8, 5, 7, 8, 9] + [0] * 40, [[7, 8, 9]])
+    assert r.output == [7, 8, 5] and seen == [7, 8, 5] and r.finish_reason == "stop"
+    # the longest of the sequences that end at the same token began earliest
+    r, _ = run(stream, [[9], [8, 9], [30, 31]])
+    assert r.stop_sequence == [8, 9] and r.output == [10, 11, 7]
+    # ... and a sequence that ends earlier wins over a longer one that would end later
+    r, _ = run(stream, [[7, 8, 9, 12], [8]])
+    assert r.stop_sequence == [8] and r.output == [10, 11, 7]
+    # what was held back is shown when the limit ends the request
+    order = []
+    s = Scheduler(cache())
+    r = Request("r", [1, 2, 3], max_tokens=4, stop=[[7, 8, 9]], on_token=lambda request, t: order.append((len(request.output), t)))
+    assert s.submit(r) is None
+    drive(s, next_token=lambda request: [10, 11, 7, 8][len(request.output)])
+    assert r.finish_reason == "length" and r.output == [10, 11, 7, 8] and r.stop_sequence is None
+    assert order == [(1, 10), (2, 11), (4, 7), (4, 8)]            # 7 and 8 only once the request had ended
+    # an end token ends it as before, and shows what was held
+    r, seen = run([10, 7, 99], [[7, 8]], eos=(99,))
+    assert r.finish_reason == "stop" and r.stop_sequence is None and r.output == [10, 7] and seen == [10, 7]
+    # refusals
+    for bad, message in (([[1]] * 5, "at most 4 stop sequences"), ([[]], "1..=64 tokens"), ([list(range(65))], "1..=64 tokens")):
+        s = Scheduler(cache())
+        r = Request("r", [1, 2, 3], stop=bad)
+        assert s.submit(r) == "invalid" and message in r.message
+
+
 def test_out_of_pages_preempts_the_newest_and_recomputes():
     """Without reservations the pool runs out in mid-run: the request admitted last gives
     everything back, waits at the head of the queue, and later feeds prompt + output again."""
