@@ -6,6 +6,7 @@
 """
 __version__ = "0.1.0"
 
+from .sampling.mask import TokenMask  # noqa: E402
 from .sampling.params import SamplingParams  # noqa: E402
 
 
@@ -16,4 +17,4 @@ def __getattr__(name):
     raise AttributeError(name)
 
 
-__all__ = ["Engine", "Generation", "SamplingParams", "__version__"]
+__all__ = ["Engine", "Generation", "SamplingParams", "TokenMask", "__version__"]

@@ -174,6 +174,20 @@ sample_kernel(const float* __restrict__ logits, int vocab, const float* __restri
     if (tid == 0) out[row] = best.index;
 }
 
+// Constrained decoding: logits[rows[m], i] = -inf wherever bit i of mask m is clear or i is at or
+// beyond the mask's own vocabulary (crates/mrun-engine/src/sample.rs:104-116: the reference's
+// where(mask, logprobs, -inf); the filters and the draw after it see differences among the
+// allowed tokens only, so masking the logits is the same).  words: [masks, words_a_mask] of 32
+// tokens each, bit i % 32 of word i / 32 for token i.
+__global__ void token_mask_kernel(float* __restrict__ logits, int vocab, const int* __restrict__ rows,
+                                  const unsigned* __restrict__ words, int words_a_mask,
+                                  const int* __restrict__ mask_vocab) {
+    const int m = blockIdx.y, i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= vocab) return;
+    const bool allowed = i < mask_vocab[m] && ((words[(size_t)m * words_a_mask + (i >> 5)] >> (i & 31)) & 1u);
+    if (!allowed) logits[(size_t)rows[m] * vocab + i] = -INFINITY;
+}
+
 // logits[row, id] of each distinct id in recent[row, :n] is divided by the penalty when it is
 // >= 0 and multiplied when negative (crates/mrun-engine/src/sample.rs:23-36).  A negative id
 // is an empty place.
@@ -262,5 +276,21 @@ MRUN_API int mrun_repetition_penalty(float* logits, int rows, int vocab, const i
     repetition_penalty_kernel<<<rows, ((n_recent + 31) / 32) * 32, 0, stream>>>(logits, vocab, recent,
                                                                                   n_recent, penalty);
     MRUN_CHECK_LAUNCH("repetition_penalty");
+    return 0;
+}
+
+// logits: float32 [*, vocab], changed in place.  rows[m]: the row that mask m applies to;
+// words: [masks, words_a_mask] unsigned, words_a_mask >= ceil(vocab / 32); mask_vocab[m]: the tokens
+// mask m covers (at most vocab; tokens beyond it are not allowed).
+MRUN_API int mrun_apply_token_mask(float* logits, int vocab, const int* rows, const unsigned* words, int words_a_mask,
+                                   const int* mask_vocab, int masks, cudaStream_t stream) {
+    MRUN_REQUIRE(vocab > 0 && masks >= 0, "apply_token_mask: bad sizes vocab=%d masks=%d", vocab, masks);
+    MRUN_REQUIRE(words_a_mask >= (vocab + 31) / 32, "apply_token_mask: %d words a mask do not cover %d tokens",
+                 words_a_mask, vocab);
+    MRUN_REQUIRE(masks <= 65535, "apply_token_mask: %d masks in one call exceed 65535", masks);
+    if (masks == 0) return 0;
+    token_mask_kernel<<<dim3((vocab + 255) / 256, masks), 256, 0, stream>>>(logits, vocab, rows, words, words_a_mask,
+                                                                            mask_vocab);
+    MRUN_CHECK_LAUNCH("apply_token_mask");
     return 0;
 }

@@ -16,6 +16,7 @@ import torch
 
 from ..cache.manager import token_bytes
 from ..cache.pages import OutOfPages
+from ..sampling.mask import TokenMask
 from ..sampling.params import REPETITION_CONTEXT, SamplingParams, draw_key
 from ..sampling.sampler import Sampler
 from . import budget
@@ -61,6 +62,7 @@ class EngineStats:
     tokens_out: int = 0
     h2d_bytes: int = 0
     d2h_bytes: int = 0
+    h2d_mask_bytes: int = 0        # token masks of constrained requests copied to the device
     preemptions: int = 0
 
 
@@ -116,7 +118,8 @@ class Engine:
                  top_p: float = 1.0, top_k: int = 0, min_p: float = 0.0, seed: Optional[int] = None,
                  repetition_penalty: float = 1.0, ignore_eos: bool = False,
                  sampling: Optional[Sequence[SamplingParams]] = None, logprobs: int = 0,
-                 on_token=None, stop: Optional[Sequence[Sequence[int]]] = None) -> List[Generation]:
+                 on_token=None, stop: Optional[Sequence[Sequence[int]]] = None,
+                 allowed_tokens=None) -> List[Generation]:
         """Generates for every prompt (lists of token ids) and returns the results in order.
         ``sampling`` gives each prompt settings of its own; otherwise all share the keyword
         values, prompt i drawing with ``seed + i`` when a seed is given.  ``logprobs`` = n > 0
@@ -132,7 +135,11 @@ class Engine:
         ``stop``: up to 4 stop sequences of token ids (the reference's ``--stop`` on ids instead of
         text): a prompt ends with ``stop`` where its output would end with one of them, the
         sequence left out and named in ``Generation.stop_sequence``; tokens that may begin one are
-        held back from ``on_token`` until they cannot (crates/mrun/src/chat/stop.rs:24-85)."""
+        held back from ``on_token`` until they cannot (crates/mrun/src/chat/stop.rs:24-85).
+        ``allowed_tokens(i, output)``: constrained decoding; called before each token of prompt i
+        is sampled with the tokens generated so far, it returns the tokens allowed next as a
+        ``TokenMask`` or an iterable of ids, or None for no constraint (the reference's token mask,
+        crates/mrun-engine/src/sample.rs:88-116); such prompts are read back step by step."""
         if not 0 <= logprobs <= 1024:
             raise ValueError(f"logprobs must be 0 .. 1024, got {logprobs}")
         stops = checked_stops(stop)
@@ -147,6 +154,8 @@ class Engine:
             requests.append(Request(request_id=("gen", self._next_id), prompt=list(map(int, prompt)),
                                     max_tokens=max_tokens, sampling=params, ignore_eos=ignore_eos,
                                     logprobs=logprobs, stop=[list(sequence) for sequence in stops],
+                                    allowed_tokens=None if allowed_tokens is None
+                                    else (lambda r, i=i: allowed_tokens(i, list(r.output))),
                                     on_token=None if on_token is None else (lambda r, t, i=i: on_token(i, t))))
             self._next_id += 1
         self.run(requests)
@@ -206,8 +215,8 @@ class Engine:
         in the step in flight, and that needs no token history for a repetition penalty."""
         if not all(len(e.tokens) == 1 and e.wants_logits for e in plan.entries):
             return False
-        if any(e.request.logprobs for e in plan.entries):
-            return False                    # the logits themselves are wanted on the host side
+        if any(e.request.logprobs or e.request.allowed_tokens is not None for e in plan.entries):
+            return False                    # the logits themselves are wanted on the host side, or a mask comes from it
         bucket = self.executor.decode_bucket(len(plan.entries))
         if bucket is None:
             return False
@@ -270,16 +279,53 @@ class Engine:
             ids, values = ids.to("cpu").tolist(), values.to("cpu").tolist()
             for row, r in wanted:
                 r.top_logprobs.append(list(zip(ids[row][:r.logprobs], values[row][:r.logprobs])))
+        refused = self._apply_token_masks(logits, sampled)
         tokens = self.sampler.sample(
             logits, [r.sampling for r in sampled], [r.seed for r in sampled],
             [len(r.output) + 1 for r in sampled],
             [r.recent(REPETITION_CONTEXT) for r in sampled])
         host = tokens.to("cpu").tolist()
+        for row in refused:
+            host[row] = None
         if plan.num_tokens > len(plan.entries):          # a step with prompt portions: its kernels wait on one another
             self.executor.check()
         self.stats.tokens_out += len(host)
         self.stats.d2h_bytes += 4 * len(host)
         scheduler.complete(plan, host)
+
+    def _apply_token_masks(self, logits: torch.Tensor, sampled: Sequence[Request]) -> List[int]:
+        """Asks the requests that decode under a constraint for their masks and sets the logits
+        of the tokens they do not allow to -inf.  Returns the rows whose mask cannot be used
+        (their requests' messages say why: crates/mrun-engine/src/engine.rs:571-576)."""
+        from ..kernels import ops
+        vocab = logits.shape[1]
+        words_a_mask = -(-vocab // 32)
+        rows, words, widths, refused = [], [], [], []
+        for row, request in enumerate(sampled):
+            if request.allowed_tokens is None:
+                continue
+            mask = request.allowed_tokens(request)
+            if mask is None:
+                continue
+            if not isinstance(mask, TokenMask):
+                mask = TokenMask.of(mask, vocab)
+            if mask.vocab > vocab:
+                request.message = f"a token mask over {mask.vocab} tokens is wider than the model's {vocab} logits"
+                refused.append(row)
+            elif mask.is_none():
+                request.message = "the token mask allows no token"
+                refused.append(row)
+            else:
+                padded = np.zeros(words_a_mask, dtype=np.uint32)
+                padded[:len(mask.words)] = mask.words
+                rows.append(row); words.append(padded); widths.append(mask.vocab)
+        if rows:
+            device = logits.device
+            ops.apply_token_mask(logits, torch.tensor(rows, dtype=torch.int32).to(device),
+                                 torch.from_numpy(np.stack(words).view(np.int32)).to(device),
+                                 torch.tensor(widths, dtype=torch.int32).to(device))
+            self.stats.h2d_mask_bytes += 4 * words_a_mask * len(rows)
+        return refused
 
     # ------------------------------------------------------------------ direct stepping
     def step(self, entries: Sequence[StepEntry]):

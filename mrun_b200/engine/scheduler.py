@@ -41,6 +41,11 @@ Decisions, with the reference's where it has one
   several do; the sequence is cut from the output and named in ``Request.stop_sequence``.  Tokens
   that may still begin a stop sequence are held back from ``on_token`` until they cannot, or until
   the request ends for another reason.
+* **Constrained decoding** (``Request.allowed_tokens``): before each of the request's tokens is
+  sampled the callable gives the tokens allowed next as a ``sampling.TokenMask`` (or None); such
+  a request is read back step by step.  A mask that allows nothing, or one over more tokens than
+  the model has logits, ends the request with ``invalid`` and the reference's message
+  (crates/mrun-engine/src/engine.rs:571-576).
 * **Cancelling**: ``on_token`` returning False, or ``Request.cancel_requested`` set by the caller,
   ends the request with ``cancelled`` when its next token is read: the tokens read so far stay,
   a token still in flight for it is dropped, its pages go back, and the other requests of the
@@ -98,6 +103,9 @@ class Request:
     logprobs: int = 0                  # how many of the most likely tokens to report beside each output token
     on_token: Optional[object] = None  # called with (request, token) as each output token is read back
     stop: List[List[int]] = field(default_factory=list)      # stop sequences of token ids (see checked_stops)
+    # constrained decoding: called with the request before each of its tokens is sampled, returns
+    # a sampling.TokenMask (the tokens allowed next) or None (no constraint for this token)
+    allowed_tokens: Optional[object] = None
     # ---- run state
     state: str = "new"                 # new | waiting | running | finished
     output: List[int] = field(default_factory=list)
@@ -310,13 +318,20 @@ class Scheduler:
             request = entry.request
             if not entry.wants_logits:
                 continue
-            token = int(sampled[at])
+            token = sampled[at]
             at += 1
             request.inflight -= 1
             if request.retiring:
                 if request.inflight == 0:
                     self._retire(request)
                 continue
+            if token is None:                        # no token could be sampled (request.message says why)
+                self._stream(request, len(request.output))
+                self._retire(request)
+                self._finish(request, "invalid")
+                done.append(request)
+                continue
+            token = int(token)
             # The end token itself is not part of the output: it is neither counted, streamed nor
             # returned (crates/mrun/src/runtime/generate.rs:868-874 returns Stop before pushing).
             count = len(request.output) + 1

@@ -517,6 +517,18 @@ def top_logprobs(logits: torch.Tensor, n: int):
     return ids, values
 
 
+def apply_token_mask(logits: torch.Tensor, rows: torch.Tensor, words: torch.Tensor, mask_vocab: torch.Tensor) -> None:
+    """In place: logits[rows[m], i] = -inf wherever bit i of words[m] is clear or i >= mask_vocab[m].
+    ``words``: int32 [masks, words a mask] (the bits of unsigned 32-bit words), 32 tokens a word."""
+    _check(logits, "logits", torch.float32); _check(rows, "rows", torch.int32)
+    _check(words, "words", torch.int32); _check(mask_vocab, "mask_vocab", torch.int32)
+    masks = rows.numel()
+    if words.dim() != 2 or words.shape[0] != masks or mask_vocab.numel() != masks:
+        raise KernelError(f"apply_token_mask: {masks} rows, words {tuple(words.shape)}, {mask_vocab.numel()} vocabularies")
+    _lib.core().call("mrun_apply_token_mask", _ptr(logits), _c_int(logits.shape[1]), _ptr(rows), _ptr(words),
+                     _c_int(words.shape[1]), _ptr(mask_vocab), _c_int(masks), _stream())
+
+
 def repetition_penalty(logits: torch.Tensor, recent: torch.Tensor, penalty: torch.Tensor) -> None:
     """In place: the logits of the ids in recent[row] (negative = empty) are penalised."""
     _check(logits, "logits", torch.float32); _check(recent, "recent", torch.int32)

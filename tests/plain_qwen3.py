@@ -223,6 +223,16 @@ def top_logprobs(logits: np.ndarray, n: int) -> List[tuple]:
     return [(i, float(lp[i])) for i in order]
 
 
+def apply_token_mask(logits: np.ndarray, allowed: Sequence[int]) -> np.ndarray:
+    """crates/mrun-engine/src/sample.rs:104-116: where(mask, logprobs, -inf); the log-sum-exp it
+    subtracts before is one constant a row, so the filters and the draw after it (which look at
+    differences among the allowed tokens) see the same on masked logits."""
+    out = np.full(len(logits), -np.inf, dtype=np.float32)
+    allowed = [i for i in allowed if 0 <= i < len(logits)]
+    out[allowed] = np.asarray(logits, dtype=np.float32)[allowed]
+    return out
+
+
 def apply_repetition_penalty(logits: np.ndarray, recent: Sequence[int], penalty: float) -> np.ndarray:
     """crates/mrun-engine/src/sample.rs:23-36: logits of recent ids divided by the penalty when
     >= 0, multiplied when negative."""

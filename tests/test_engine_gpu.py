@@ -202,6 +202,53 @@ def test_stop_sequences_end_requests_in_the_middle_of_pipelined_decoding(tiny):
         engine.generate(prompts, max_tokens=2, stop=[[1]] * 5)
 
 
+def test_constrained_decoding_with_token_masks(tiny):
+    """``allowed_tokens`` through ``Engine.generate``: a prompt that decodes under a mask that
+    changes with every token (beside an unconstrained one in the same batch) gives the tokens of
+    a host-side replay on the plain logits, greedy and drawn; the unconstrained prompt is as it
+    was; a mask that allows nothing, and one wider than the logits, end their prompt with the
+    reference's messages (crates/mrun-engine/src/sample.rs:88-116, engine.rs:571-576)."""
+    from mrun_b200 import Engine, TokenMask
+    name, folder, settings = tiny
+    cfg, weights = plain.load_folder(folder)
+    vocab = cfg["vocab_size"]
+    prompts = [random_tokens(vocab, n, seed=800 + n) for n in (11, 6)]
+    engine = Engine.from_folder(folder, dtype="float32", page_size=settings["page_size"], context=512,
+                                max_batch_tokens=32, max_requests=4)
+    def allowed(n):                       # the tokens allowed for the n-th output token: a moving window plus one far token
+        return sorted({(7 * n + j) % vocab for j in range(9)} | {vocab - 1 - n})
+    calls = []
+    def constraint(i, output):
+        calls.append((i, len(output)))
+        if i != 0:
+            return None
+        return TokenMask.of(allowed(len(output)), vocab) if len(output) % 2 else allowed(len(output))
+    free = engine.generate(prompts, max_tokens=10, ignore_eos=True)
+    for temperature, seed in ((0.0, None), (0.9, 4)):
+        runs = engine.generate(prompts, max_tokens=10, ignore_eos=True, temperature=temperature, seed=seed,
+                               top_p=0.95 if temperature else 1.0, allowed_tokens=constraint)
+        tokens = list(prompts[0])
+        for n, token in enumerate(runs[0].tokens):
+            logits = plain.apply_token_mask(plain.forward(cfg, weights, tokens)[-1].numpy(), allowed(n))
+            want = plain.sample_token(logits, temperature, plain.draw_key(seed or 0, n + 1), top_p=0.95 if temperature else 1.0)
+            assert token == want and token in allowed(n), (temperature, n, token, want)
+            tokens.append(token)
+        assert len(runs[0].tokens) == 10 and runs[0].finish_reason == "length"
+        if temperature == 0.0:
+            assert runs[1].tokens == free[1].tokens
+    assert (0, 0) in calls and (0, 9) in calls and (1, 3) in calls
+    # masks that cannot be used
+    nothing = engine.generate(prompts, max_tokens=6, ignore_eos=True,
+                              allowed_tokens=lambda i, output: TokenMask.none_allowed(vocab) if i == 0 and len(output) == 3 else None)
+    assert nothing[0].finish_reason == "invalid" and nothing[0].message == "the token mask allows no token"
+    assert nothing[0].tokens == free[0].tokens[:3] and nothing[1].tokens == free[1].tokens[:6]
+    wide = engine.generate(prompts[:1], max_tokens=6, ignore_eos=True,
+                           allowed_tokens=lambda i, output: TokenMask.of([1], vocab + 1))
+    assert wide[0].finish_reason == "invalid" and f"wider than the model's {vocab} logits" in wide[0].message
+    engine.executor.cache.check_invariants()
+    assert not engine.executor.cache.live and engine.executor.cache.free_pages() == engine.executor.cache.num_pages
+
+
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_repetition_penalty_and_filters_through_generate(tiny, dtype):
     """Sampling settings that need the token history (the penalty) keep decoding correct: the

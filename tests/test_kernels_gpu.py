@@ -406,6 +406,44 @@ def test_gemm_tc5_residual_epilogue_and_normed_rows(m, width, k, inter, monkeypa
     o.tc5_check()
 
 
+@pytest.mark.parametrize("vocab", [37, 300, 151936])
+def test_apply_token_mask(vocab):
+    """Rows under a mask keep the logits of their allowed tokens and get -inf elsewhere, tokens
+    beyond a narrower mask's vocabulary included; the other rows are untouched."""
+    from mrun_b200.sampling import TokenMask
+    o = ops()
+    logits = rnd(5, vocab, seed=3)
+    before = logits.clone()
+    g = torch.Generator().manual_seed(vocab)
+    masks = [TokenMask.of(torch.randint(0, vocab, (max(1, vocab // 3),), generator=g).tolist(), vocab),
+             TokenMask.of([0, vocab // 2, vocab - 5], vocab - 4)]           # a narrower mask: its last token is outside
+    rows = [3, 1]
+    words_a_mask = -(-vocab // 32)
+    words = np.zeros((2, words_a_mask), dtype=np.uint32)
+    for m, mask in enumerate(masks):
+        words[m, :len(mask.words)] = mask.words
+    o.apply_token_mask(logits, torch.tensor(rows, dtype=torch.int32, device=DEV),
+                       torch.from_numpy(words.view(np.int32)).to(DEV),
+                       torch.tensor([m.vocab for m in masks], dtype=torch.int32, device=DEV))
+    got, want = logits.cpu(), before.cpu()
+    for row in (0, 2, 4):
+        assert torch.equal(got[row], want[row])
+    for row, mask in zip(rows, masks):
+        allowed = mask.allowed()
+        expected = torch.full((vocab,), float("-inf"))
+        expected[allowed] = want[row][allowed]
+        assert torch.equal(got[row], expected)
+    assert masks[1].allowed() == [0, vocab // 2, vocab - 5] and got[1][vocab - 1] == float("-inf")
+    # the sampler on masked rows: greedy is the best allowed token, a draw stays inside the mask
+    out = torch.empty(5, dtype=torch.int32, device=DEV)
+    o.sample(logits, out)
+    assert int(out[3]) == max(masks[0].allowed(), key=lambda i: (float(want[3][i]), -i))
+    keys = torch.arange(5, dtype=torch.int64, device=DEV) * 977 + 5
+    o.sample(logits, out, temperature=torch.full((5,), 1.5, device=DEV), top_p=torch.full((5,), 0.9, device=DEV),
+             top_k=torch.full((5,), 7, dtype=torch.int32, device=DEV), min_p=torch.full((5,), 0.01, device=DEV), keys=keys)
+    assert masks[0].is_allowed(int(out[3])) and masks[1].is_allowed(int(out[1]))
+
+
 def test_linear_bf16_accumulates_in_32_bits():
     x, w = rnd(300, 1024, dtype=torch.bfloat16, seed=13), rnd(77, 1024, dtype=torch.bfloat16, seed=14)
     got = ops().linear(x, w, out_dtype=torch.float32)
