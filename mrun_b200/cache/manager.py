@@ -278,6 +278,20 @@ class CacheManager:
         del self._live[request.request_id]
         del self._by_slot[request.slot]
 
+    def trim(self, request: RequestCache, length: int) -> None:
+        """Cuts the request back to its first ``length`` tokens: the pages beyond them go back
+        and the next step writes from position ``length`` on (the reference's ``trim``,
+        crates/mrun-engine/src/engine.rs:746, crates/mrun-engine/src/ledger.rs:400-441).  Refused
+        while a step is uncommitted, and for a group whose window has already given back keys
+        that the shorter request would need.  Per-request state of fixed size is not rewound:
+        a mixer that keeps such state cannot be cut back."""
+        if request.released:
+            raise ValueError(f"request {request.request_id!r} is released")
+        if length != request.length and any(e is not None and isinstance(e.need, FixedState) for e in self.entries):
+            raise ValueError("a request with per-request state of fixed size cannot be cut back")
+        if self._lib.mrun_cache_trim(self._core, request.slot, int(length)):
+            raise ValueError(f"request {request.request_id!r}: {self._message()}")
+
     # ------------------------------------------------------------------ appending
     def pages_needed(self, request: RequestCache, tokens: int) -> Dict[tuple, int]:
         """Pages each group must add so that ``request`` can take ``tokens`` more."""

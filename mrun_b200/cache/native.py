@@ -26,7 +26,7 @@ def library() -> ctypes.CDLL:
             "mrun_cache_free_pages": (I, [P, I]), "mrun_cache_free_slots": (I, [P]),
             "mrun_cache_length": (I, [P, I]), "mrun_cache_pending": (I, [P, I]), "mrun_cache_blocks": (I, [P, I, I]),
             "mrun_cache_is_held": (I, [P, I, I]), "mrun_cache_shortage": (None, [P, IP, IP, IP, IP]),
-            "mrun_cache_admit": (I, [P]), "mrun_cache_release": (I, [P, I]),
+            "mrun_cache_admit": (I, [P]), "mrun_cache_release": (I, [P, I]), "mrun_cache_trim": (I, [P, I, I]),
             "mrun_cache_plan": (I, [P, I, IP, IP]), "mrun_cache_commit": (I, [P, I]),
             "mrun_cache_rollback": (I, [P, I]), "mrun_cache_drain": (I, [P, I, IP, IP, I]),
             "mrun_cache_pending_updates": (I, [P, I]), "mrun_cache_check": (ctypes.c_char_p, [P]),

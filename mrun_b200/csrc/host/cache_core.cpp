@@ -218,6 +218,44 @@ HOST_API int mrun_cache_release(void* core, int slot) {
     return 0;
 }
 
+// Cuts the request back to its first `length` tokens (the reference trims a sequence the same
+// way, crates/mrun-engine/src/ledger.rs:400-441): the pages beyond them go back, what they held is
+// void, and the next step writes from position `length` on.  A group with a window refuses a cut
+// that would need keys whose pages the window has already given back.
+HOST_API int mrun_cache_trim(void* core, int slot, int length) {
+    Core* c = (Core*)core;
+    if (slot < 0 || slot >= c->max_requests || !c->state[slot].live) return c->fail("slot %d is not live", slot);
+    Slot& s = c->state[slot];
+    if (s.pending) return c->fail("the request in slot %d has an uncommitted step", slot);
+    if (length < 0 || length > s.length) return c->fail("slot %d holds %d tokens and cannot be cut to %d", slot, s.length, length);
+    const int target = c->blocks_for(length);
+    for (size_t g = 0; g < c->groups.size(); ++g) {
+        Group& group = c->groups[g];
+        if (group.window >= 0) {
+            const int low = length - group.window + 1;
+            for (int b = (low > 0 ? low : 0) / c->page_size; b < target; ++b)
+                if (group.table[slot * c->max_blocks + b] == FREED)
+                    return c->fail("slot %d: a window of %d keys has given back what a cut to %d tokens needs", slot,
+                                   group.window, length);
+        }
+    }
+    for (size_t g = 0; g < c->groups.size(); ++g) {
+        Group& group = c->groups[g];
+        std::vector<int> pages;
+        for (int b = target; b < s.blocks[g]; ++b) {
+            const int page = group.table[slot * c->max_blocks + b];
+            if (page != FREED) pages.push_back(page);
+        }
+        int bad = 0;
+        if (group.pool.release(pages.data(), (int)pages.size(), &bad)) return c->fail("page %d of slot %d is not held", bad, slot);
+        for (int b = target; b < s.blocks[g]; ++b)
+            if (group.table[slot * c->max_blocks + b] != FREED) c->set(group, slot, b, FREED);
+        if (s.blocks[g] > target) s.blocks[g] = target;
+    }
+    s.length = length;
+    return 0;
+}
+
 // Takes every page the step needs: slots[i] brings tokens[i] new tokens.  Returns a plan id > 0;
 // 0 when the pages (or a request's blocks) do not suffice, with nothing changed (see
 // mrun_cache_shortage); -1 for a misuse, with a message.

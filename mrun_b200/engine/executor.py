@@ -81,6 +81,11 @@ class Executor:
     def release(self, request: RequestCache) -> None:
         self.cache.release(request)
 
+    def trim(self, request: RequestCache, length: int) -> None:
+        """Cuts a request back to its first ``length`` tokens; its next step goes on from there
+        (the reference's ``trim``, crates/mrun-engine/src/engine.rs:746)."""
+        self.cache.trim(request, length)
+
     # ------------------------------------------------------------------ the step
     def _validate(self, entries: Sequence[StepEntry]) -> None:
         if not entries:

@@ -54,6 +54,50 @@ def test_append_commit_release():
     m.check_invariants()
 
 
+def test_trim_gives_back_the_pages_beyond_the_cut():
+    """The reference's trim (crates/mrun-engine/src/ledger.rs:400-441): a request cut back to
+    its first n tokens keeps the pages that hold them, gives the others back, and appends from
+    n on; not during a step, not beyond its length, and not where a window has passed."""
+    m = manager()
+    r = m.admit("a")
+    m.commit(m.plan_append([(r, 5)]))
+    assert m.free_pages() == 30
+    plan = m.plan_append([(r, 9)])
+    with pytest.raises(ValueError, match="uncommitted"):
+        m.trim(r, 2)
+    m.commit(plan)                                             # 14 tokens, 4 pages
+    assert r.length == 14 and m.free_pages() == 28
+    with pytest.raises(ValueError, match="cannot be cut to 15"):
+        m.trim(r, 15)
+    m.trim(r, 14)                                              # no change
+    m.trim(r, 9)                                               # 9 tokens need 3 pages
+    assert r.length == 9 and m.free_pages() == 29 and len(r.blocks[("paged", None)]) == 3
+    m.commit(m.plan_append([(r, 4)]))                          # goes on from 9
+    assert r.length == 13 and m.free_pages() == 28
+    m.trim(r, 0)
+    assert r.length == 0 and m.free_pages() == 32
+    m.commit(m.plan_append([(r, 2)]))
+    m.check_invariants()
+    m.release(r)
+    assert m.free_pages() == 32
+    # a group with a window of 6 keys: at 14 tokens it has given back the pages before position 9
+    w = manager(window=6)
+    r = w.admit("a")
+    w.commit(w.plan_append([(r, 14)]))
+    with pytest.raises(ValueError, match="window of 6 keys"):
+        w.trim(r, 9)                                           # would need keys from position 4 on
+    assert r.length == 14
+    w.trim(r, 13)                                              # needs keys from position 8 on: still held
+    assert r.length == 13
+    w.check_invariants()
+    # per-request state of fixed size is not rewound
+    f = manager(extra=[FixedState((3,))])
+    r = f.admit("a")
+    f.commit(f.plan_append([(r, 6)]))
+    with pytest.raises(ValueError, match="fixed size"):
+        f.trim(r, 3)
+
+
 def test_out_of_pages_changes_nothing():
     m = manager(pages=6)
     a, b = m.admit("a"), m.admit("b")
@@ -176,6 +220,15 @@ def test_random_orders_of_requests(seed, window):
                     m.rollback(plan)
                 else:
                     m.commit(plan)
+        elif action < 0.9 and live:
+            # cut a request back: pages beyond the cut go back; a window may refuse
+            r = rng.choice(live)
+            cut = rng.randint(0, r.length)
+            try:
+                m.trim(r, cut)
+                assert r.length == cut
+            except ValueError as error:
+                assert window and "window" in str(error)
         elif live:
             victim = live.pop(rng.randrange(len(live)))
             m.release(victim)

@@ -202,6 +202,51 @@ def test_stop_sequences_end_requests_in_the_middle_of_pipelined_decoding(tiny):
         engine.generate(prompts, max_tokens=2, stop=[[1]] * 5)
 
 
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_a_request_cut_back_goes_on_as_if_it_had_never_been_longer(tiny, dtype):
+    """``Executor.trim``: 40 tokens fed, the request cut back to 17 (and once to a page's edge),
+    another continuation fed in portions and decoded: the logits equal the plain implementation
+    on the first tokens + the continuation, and in 32-bit they are the bits of a fresh request
+    that was fed the same tokens in the same steps; the pages beyond the cut went back and are
+    used again meanwhile (crates/mrun-engine/tests/tiny_qwen3.rs:213-245, trim exact)."""
+    from mrun_b200.engine import StepEntry
+    from mrun_b200.engine.loading import executor_from_folder
+    name, folder, settings = tiny
+    cfg, weights = plain.load_folder(folder)
+    vocab, page = cfg["vocab_size"], settings["page_size"]
+    ex = executor_from_folder(folder, dtype=dtype, page_size=page, num_pages=-(-256 // page), max_requests=4)
+    first = random_tokens(vocab, 40, seed=31)
+    other = random_tokens(vocab, 21, seed=32)
+    for cut in (17, 2 * page):
+        a = ex.admit(("cut", cut))
+        ex.step([StepEntry(a, first, [])])
+        free_before = ex.cache.free_pages()
+        ex.trim(a, cut)
+        assert a.length == cut and ex.cache.free_pages() == free_before + (-(-40 // page)) - (-(-cut // page))
+        filler = ex.admit(("filler", cut))                       # takes the pages that came back
+        ex.step([StepEntry(filler, random_tokens(vocab, 3 * page, seed=33), [])])
+        b = ex.admit(("fresh", cut))
+        ex.step([StepEntry(b, first[:cut], [])])
+        got_a, got_b = [], []
+        for lo, hi in ((0, 9), (9, 11), (11, 20), (20, 21)):
+            want_rows = list(range(hi - lo))
+            out = ex.step([StepEntry(a, other[lo:hi], want_rows), StepEntry(b, other[lo:hi], want_rows)])
+            rows = out.float().cpu().numpy()
+            got_a.append(rows[:hi - lo]); got_b.append(rows[hi - lo:])
+        got_a, got_b = np.concatenate(got_a), np.concatenate(got_b)
+        want = plain.forward(cfg, weights, first[:cut] + other).numpy()[cut:]
+        scale = float(np.abs(want).max())
+        assert float(np.abs(got_a - want).max()) / scale <= TOLERANCE[dtype]
+        if dtype == "float32":
+            assert np.array_equal(got_a, got_b)
+        else:
+            assert float(np.abs(got_a - got_b).max()) / scale <= TOLERANCE[dtype]
+        for r in (a, b, filler):
+            ex.release(r)
+        ex.cache.check_invariants()
+        assert ex.cache.free_pages() == ex.cache.num_pages
+
+
 def test_constrained_decoding_with_token_masks(tiny):
     """``allowed_tokens`` through ``Engine.generate``: a prompt that decodes under a mask that
     changes with every token (beside an unconstrained one in the same batch) gives the tokens of
