@@ -38,6 +38,7 @@ def library() -> ctypes.CDLL:
             "mrun_sched_plan": (I, [I, LP, LP, IP, LP, LP, IP, LP, I, IP, IP, IP, IP]),
             "mrun_sched_end_reason": (I, [I, I, L, L, IP, L]),
             "mrun_sched_preemption_victim": (I, [I, IP, LP]),
+            "mrun_sched_next_turn": (I, [I, IP, IP, IP, I, I]),
             "mrun_sched_stop_match": (I, [IP, I, IP, IP, I]), "mrun_sched_stop_held": (I, [IP, I, IP, IP, I]),
         }
         for name, (restype, argtypes) in signatures.items():

@@ -9,7 +9,8 @@
 //    (crates/mrun/src/runtime/generate.rs:522-532, 600-636; crates/mrun/src/runtime/queue.rs:80-91);
 //  * admission: a free place among the running requests, a free state slot and, with
 //    reservations, pages for prompt + clamped output beside what is reserved already
-//    (crates/mrun/src/runtime/handle.rs:497-559);
+//    (crates/mrun/src/runtime/handle.rs:497-559); side requests first, then the next member's
+//    turn (crates/mrun/src/runtime/handle.rs:563-587);
 //  * a step: one token of every request that has finished its prompt, then prompt portions while
 //    the token budget lasts, fewest tokens left first, ties by admission order
 //    (crates/mrun/src/runtime/lanes.rs:187-196); a portion is at most chunk_len(depth)
@@ -151,6 +152,23 @@ HOST_API int mrun_sched_end_reason(int is_end_token, int ignore_eos, int64_t out
     if (output_len >= limit) return 2;
     if (!ignore_eos && recent != nullptr && output_len % LOOP_CHECK_EVERY == 0 && mrun_sched_looping(recent, recent_len)) return 3;
     return 0;
+}
+
+// The waiting request to start next (crates/mrun/src/runtime/handle.rs:563-587): the oldest side
+// ("auxiliary") request, else the oldest request of another member's turn than the one served
+// last (has_last = 0: nobody was served yet), else the oldest.  Before all of them, a request
+// that gave its pages back and waits to go on (resumed[i] != 0): it was admitted once already.
+// The arrays are in queue order, oldest first; turn < 0 = no member named.  -1 for an empty queue.
+HOST_API int mrun_sched_next_turn(int n, const int* auxiliary, const int* turn, const int* resumed, int has_last,
+                                  int last_turn) {
+    for (int i = 0; i < n; ++i)
+        if (resumed[i]) return i;
+    for (int i = 0; i < n; ++i)
+        if (auxiliary[i]) return i;
+    if (has_last)
+        for (int i = 0; i < n; ++i)
+            if (turn[i] != last_turn) return i;
+    return n > 0 ? 0 : -1;
 }
 
 // Stop sequences, on token ids (the reference matches stop strings on the streamed text, earliest

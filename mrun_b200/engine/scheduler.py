@@ -35,6 +35,12 @@ Decisions, with the reference's where it has one
   out of the output; the output limit → ``length``; the last 512 output tokens repeating with a
   period of at most 256, checked every 16 tokens and never with ``ignore_eos`` → ``repetition``
   (crates/mrun/src/runtime/generate.rs:27-33, 420-426, 866-919).
+* **Whose turn** (crates/mrun/src/runtime/handle.rs:497-587): among the waiting requests the
+  oldest side request (``Request.auxiliary``) starts first, else the oldest request of another
+  member (``Request.turn``) than the one started last, else the oldest; a request that was
+  preempted goes before all of them.  If the one whose turn it is does not fit, nobody starts.
+  A request cancelled while it waits (``cancel_requested``) ends with ``cancelled`` when its turn
+  comes and never reaches the engine.
 * **Stop sequences** (``Request.stop``: up to 4 lists of token ids, the reference's ``--stop`` on
   token ids instead of text, crates/mrun/src/chat/stop.rs:24-85, crates/mrun/src/chat/limits.rs:6):
   the request ends with ``stop`` as soon as its output ends with one of them, the longest if
@@ -106,6 +112,8 @@ class Request:
     # constrained decoding: called with the request before each of its tokens is sampled, returns
     # a sampling.TokenMask (the tokens allowed next) or None (no constraint for this token)
     allowed_tokens: Optional[object] = None
+    auxiliary: bool = False            # a side request: admitted before the normal ones (handle.rs:563-587)
+    turn: Optional[str] = None         # who waits for it: waiting requests are served in turns between members
     # ---- run state
     state: str = "new"                 # new | waiting | running | finished
     output: List[int] = field(default_factory=list)
@@ -195,6 +203,9 @@ class Scheduler:
         self._admitted = 0
         self._reserved = 0
         self.preemptions = 0
+        self._turn_ids: Dict[str, int] = {}          # members' names as numbers for the native rule
+        self._last_turn: Optional[tuple] = None      # (turn of the request started last,), None before the first
+        self.cancelled_waiting: List[Request] = []   # requests that were cancelled before they were admitted
         self._core = native.library()
         self._loop_check_every = int(self._core.mrun_sched_loop_check_every())
 
@@ -259,9 +270,31 @@ class Scheduler:
             request.sequence_len, len(running), native.long_array(r.sequence_len for r in running),
             native.long_array(r.fed for r in running)))
 
+    def _next_turn(self) -> int:
+        """Index of the waiting request to start next (side requests first, then the oldest of
+        another member than the one served last, else the oldest; a preempted request before all)."""
+        waiting = list(self.waiting)
+        names = self._turn_ids
+        turns = [(-1 if r.turn is None else names.setdefault(r.turn, len(names))) for r in waiting]
+        last = self._last_turn
+        return self._core.mrun_sched_next_turn(
+            len(waiting), native.int_array(1 if r.auxiliary else 0 for r in waiting), native.int_array(turns),
+            native.int_array(1 if r.order >= 0 else 0 for r in waiting), 0 if last is None else 1,
+            -1 if last is None or last[0] is None else names.setdefault(last[0], len(names)))
+
     def _admit(self) -> None:
-        while self.waiting and self._can_admit(self.waiting[0]):
-            request = self.waiting.popleft()
+        while self.waiting:
+            at = self._next_turn()
+            request = self.waiting[at]
+            if not request.cancel_requested and not self._can_admit(request):
+                return
+            del self.waiting[at]
+            self._last_turn = (request.turn,)
+            if request.cancel_requested:
+                # cancelled while waiting: it never reaches the engine (handle.rs:533-549)
+                self._finish(request, "cancelled")
+                self.cancelled_waiting.append(request)
+                continue
             request.cache = self.cache.admit(request.request_id)
             request.state = "running"
             request.fed = 0

@@ -157,6 +157,37 @@ def test_cancelling_from_the_token_callback_and_from_outside():
     s.cache.check_invariants()
 
 
+def test_whose_turn_it_is_to_start():
+    """crates/mrun/src/runtime/handle.rs:563-587: the oldest side request first, else the oldest
+    request of another member than the one started last, else the oldest; a request cancelled
+    while it waited never reaches the engine (:533-549)."""
+    s = Scheduler(cache(requests=4), max_running=1)
+    made = {}
+    def request(name, **kw):
+        made[name] = Request(name, [1, 2, 3], max_tokens=2, **kw)
+        assert s.submit(made[name]) is None
+    request("a1", turn="a"); request("a2", turn="a"); request("a3", turn="a")
+    request("b1", turn="b"); request("side", auxiliary=True); request("gone", turn="c")
+    made["gone"].cancel_requested = True
+    drive(s)
+    started = sorted((r for r in made.values() if r.order >= 0), key=lambda r: r.order)
+    # the side request first; it names no member, so the oldest that names one is next (a1); then
+    # another member than a (b1); then another than b (a2); then "gone" of member c, which is
+    # dropped when its turn comes; a3 is left
+    assert [r.request_id for r in started] == ["side", "a1", "b1", "a2", "a3"]
+    assert made["gone"].finish_reason == "cancelled" and made["gone"].order == -1 and made["gone"].output == []
+    assert made["gone"].cache is None and s.cancelled_waiting == [made["gone"]]
+    assert all(r.finish_reason == "length" for r in started)
+    # the native rule by itself
+    from mrun_b200.cache import native
+    lib, ia = native.library(), native.int_array
+    assert lib.mrun_sched_next_turn(0, ia([]), ia([]), ia([]), 0, -1) == -1
+    assert lib.mrun_sched_next_turn(3, ia([0, 0, 0]), ia([5, 5, 6]), ia([0, 0, 0]), 1, 5) == 2
+    assert lib.mrun_sched_next_turn(3, ia([0, 0, 0]), ia([5, 5, 5]), ia([0, 0, 0]), 1, 5) == 0
+    assert lib.mrun_sched_next_turn(3, ia([0, 0, 1]), ia([5, 6, 5]), ia([0, 0, 0]), 1, 5) == 2
+    assert lib.mrun_sched_next_turn(3, ia([0, 0, 1]), ia([5, 6, 5]), ia([0, 1, 0]), 1, 5) == 1      # a preempted request before all
+
+
 def test_stop_sequences_of_token_ids():
     """The reference's stop strings on token ids (crates/mrun/src/chat/stop.rs:24-85 and its tests
     at :95-130): a sequence split over steps is found and left out; a false start is shown later;
